@@ -1,0 +1,34 @@
+"""hecbench_b200: B200 (sm_100a) kernels for HeCBench's weight-only quantized
+matrix-vector family, behind each benchmark's own launcher signature.
+
+The compute lives in libhq.so (hand-written CUDA, C ABI declared in
+include/hq.h).  This package is the thin Python host layer over it: it mirrors
+the reference launchers (`vecquant3matmul`, `vecquant3matmul_faster`,
+`kQuantize`, `matmul` + `nQWeight_fp16`, `code1x16_matvec`) on torch CUDA
+tensors and adds the pieces the reference names but does not contain (NF4
+dequantize / GEMV, AQLM 2x8).  There is no CPU path: importing works without a
+GPU, but every compute call needs the built library and CUDA tensors.
+"""
+from ._lib import HqError, lib_path, load_library  # noqa: F401
+from .api import (  # noqa: F401
+    NF4_HIGH_NIBBLE_FIRST,
+    NF4_LOW_NIBBLE_FIRST,
+    code1x16_matvec,
+    code2x8_matvec,
+    dequantize_nf4,
+    gemv_nf4,
+    kQuantize,
+    matmul,
+    nQWeight_fp16,
+    vecquant3_dequant,
+    vecquant3matmul,
+    vecquant3matmul_faster,
+)
+
+__all__ = [
+    "HqError", "lib_path", "load_library",
+    "vecquant3matmul", "vecquant3matmul_faster", "vecquant3_dequant",
+    "kQuantize", "dequantize_nf4", "gemv_nf4",
+    "nQWeight_fp16", "matmul", "code1x16_matvec", "code2x8_matvec",
+    "NF4_HIGH_NIBBLE_FIRST", "NF4_LOW_NIBBLE_FIRST",
+]

@@ -1,0 +1,239 @@
+"""Host-side mirror of the reference launchers, on torch CUDA tensors.
+
+Each function keeps the name, argument order and in/out convention of the
+HeCBench launcher it stands in for (file:line given per function; paths
+relative to the HeCBench source tree) and forwards to the C ABI of libhq.so on
+the current torch CUDA stream.  Arguments are validated here the way the C ABI
+validates them; errors surface as HqError / TypeError, never as a silent
+fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from ._lib import check, load_library
+
+NF4_HIGH_NIBBLE_FIRST = 0
+NF4_LOW_NIBBLE_FIRST = 1
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, dtype: torch.dtype, name: str) -> int:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name}: expected a torch.Tensor")
+    if not t.is_cuda:
+        raise TypeError(f"{name}: must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name}: expected dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise TypeError(f"{name}: must be contiguous")
+    return t.data_ptr()
+
+
+# --------------------------------------------------------------------------
+# quant3MatMul
+# --------------------------------------------------------------------------
+
+def vecquant3matmul(vec, mat, mul, scales, zeros, height: int, width: int) -> None:
+    """vecquant3matmul<float> (quant3MatMul-cuda/kernels.h:171-190).
+
+    mul[c] += sum_k (scales[c]*q[k][c] - zeros[c]) * vec[k]; `mul` is
+    accumulated into, exactly like the reference (the caller zeroes it)."""
+    lib = load_library()
+    args = (
+        _dev(vec, torch.float32, "vec"), _dev(mat, torch.int32, "mat"),
+        _dev(mul, torch.float32, "mul"), _dev(scales, torch.float32, "scales"),
+        _dev(zeros, torch.float32, "zeros"), height, width)
+    with torch.cuda.device(mat.device):
+        check("hq_q3_gemv_f32", lib.hq_q3_gemv_f32(*args, _stream()))
+
+
+def vecquant3matmul_faster(vec, mat, mul, scales, zeros, height: int, width: int) -> None:
+    """vecquant3matmul_faster (quant3MatMul-cuda/kernels.h:193-217): fp16 input."""
+    lib = load_library()
+    args = (
+        _dev(vec, torch.float16, "vec"), _dev(mat, torch.int32, "mat"),
+        _dev(mul, torch.float32, "mul"), _dev(scales, torch.float32, "scales"),
+        _dev(zeros, torch.float32, "zeros"), height, width)
+    with torch.cuda.device(mat.device):
+        check("hq_q3_gemv_f16in", lib.hq_q3_gemv_f16in(*args, _stream()))
+
+
+def vecquant3_dequant(mat, scales, zeros, height: int, width: int,
+                      dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Dequantised weights W[K][width] by the fp32 rule (kernels.h:43) or the
+    fp16 rule (kernels.h:121-122,137)."""
+    lib = load_library()
+    K = height * 32 // 3
+    W = torch.empty((K, width), dtype=dtype, device=mat.device)
+    fn = {torch.float32: "hq_q3_dequant_f32", torch.float16: "hq_q3_dequant_f16"}[dtype]
+    args = (
+        _dev(mat, torch.int32, "mat"), _dev(scales, torch.float32, "scales"),
+        _dev(zeros, torch.float32, "zeros"), W.data_ptr(), height, width)
+    with torch.cuda.device(mat.device):
+        check(fn, getattr(lib, fn)(*args, _stream()))
+    return W
+
+
+# --------------------------------------------------------------------------
+# quantBnB
+# --------------------------------------------------------------------------
+
+def kQuantize(code, A, out, n: int) -> None:
+    """kQuantize<256,256><<<grid,block>>>(code, A, out, n)
+    (quantBnB-cuda/main.cu:90-130,176)."""
+    lib = load_library()
+    if n > A.numel() or n > out.numel():
+        raise ValueError("n exceeds the buffers")
+    args = (
+        _dev(code, torch.float32, "code"), _dev(A, torch.float32, "A"),
+        _dev(out, torch.uint8, "out"), n)
+    with torch.cuda.device(A.device):
+        check("hq_bnb_quantize_u8", lib.hq_bnb_quantize_u8(*args, _stream()))
+
+
+def dequantize_nf4(B, absmax, lut16, n: int, blocksize: int = 64,
+                   nibble_order: int = NF4_HIGH_NIBBLE_FIRST,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """NF4 blockwise dequantize to fp16 (no counterpart in the reference tree):
+    out[e] = half_rn(lut16[code_e] * absmax[e // blocksize])."""
+    lib = load_library()
+    if out is None:
+        out = torch.empty(n, dtype=torch.float16, device=B.device)
+    args = (
+        _dev(B, torch.uint8, "B"), _dev(absmax, torch.float32, "absmax"),
+        _dev(lut16, torch.float32, "lut16"), _dev(out, torch.float16, "out"),
+        n, blocksize, nibble_order)
+    with torch.cuda.device(B.device):
+        check("hq_nf4_dequant_f16", lib.hq_nf4_dequant_f16(*args, _stream()))
+    return out
+
+
+def gemv_nf4(A, B, absmax, lut16, N: int, K: int, blocksize: int = 64,
+             nibble_order: int = NF4_HIGH_NIBBLE_FIRST,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """NF4 4-bit GEMV (no counterpart in the reference tree):
+    out[n] = half(sum_k A[k] * lut16[code[n][k]] * absmax[(n*K+k)//blocksize])."""
+    lib = load_library()
+    if out is None:
+        out = torch.empty(N, dtype=torch.float16, device=B.device)
+    args = (
+        _dev(A, torch.float16, "A"), _dev(B, torch.uint8, "B"),
+        _dev(absmax, torch.float32, "absmax"), _dev(lut16, torch.float32, "lut16"),
+        _dev(out, torch.float16, "out"), N, K, blocksize, nibble_order)
+    with torch.cuda.device(B.device):
+        check("hq_nf4_gemv_f16", lib.hq_nf4_gemv_f16(*args, _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------
+# lut-gemm
+# --------------------------------------------------------------------------
+
+class nQWeight_fp16:
+    """Mirror of class nQWeight_fp16 (lut-gemm-cuda/nQWeight_fp16.h:22-45,
+    nQWeight_fp16.cu:22-53): holds the bit-plane weights, fp16 alphas and the
+    optional fp16 q_bias on the device.  `parsing` takes the same host-side
+    arrays (uint32 bit planes [K/32][nb][M], fp32 alpha [groups][nb][M], fp32
+    q_bias [groups][M] or None) and converts alpha / q_bias to fp16."""
+
+    def __init__(self, bW=None, A=None, row: int = 0, col: int = 0, num_bits: int = 0,
+                 is_row_wise_quantize: bool = False, num_alpha_groups: int = 1, q_bias=None,
+                 device="cuda"):
+        self.bWeight = self.alpha = self.q_bias = None
+        self.num_groups = self.group_size = self.mSize = self.kSize = self.nb = 0
+        self.is_row_wise_quantize = False
+        self._ws = None
+        if bW is not None:
+            self.parsing(bW, A, row, col, num_bits, is_row_wise_quantize, num_alpha_groups,
+                         q_bias, device)
+
+    def parsing(self, bW, A, row: int, col: int, num_bits: int, is_row_wise_quantize: bool,
+                num_alpha_groups: int = 1, q_bias=None, device="cuda") -> None:
+        self.num_groups = num_alpha_groups
+        self.nb = num_bits
+        self.is_row_wise_quantize = is_row_wise_quantize
+        self.mSize, self.kSize = (row, col) if is_row_wise_quantize else (col, row)
+        # the reference computes group_size before kSize is set
+        # (nQWeight_fp16.cu:25); its launcher uses kSize/num_groups (mv_fp16.h:235)
+        self.group_size = self.kSize // num_alpha_groups
+        dev = torch.device(device)
+        bW_t = torch.as_tensor(bW)
+        if bW_t.dtype == torch.uint32:
+            bW_t = bW_t.view(torch.int32)
+        self.bWeight = bW_t.to(torch.int32).reshape(-1).contiguous().to(dev)
+        self.alpha = torch.as_tensor(A, dtype=torch.float32).reshape(-1).to(torch.float16).to(dev)
+        self.q_bias = None if q_bias is None else \
+            torch.as_tensor(q_bias, dtype=torch.float32).reshape(-1).to(torch.float16).to(dev)
+        need_w = self.kSize * self.mSize * self.nb // 32
+        if self.bWeight.numel() != need_w:
+            raise ValueError("bW has the wrong number of words")
+        if self.alpha.numel() != self.num_groups * self.mSize * self.nb:
+            raise ValueError("alpha has the wrong number of elements")
+
+    def workspace(self) -> torch.Tensor:
+        """Zero-initialised fp32 scratch the kernel accumulates K tiles into; it
+        is left zero by every call."""
+        if self._ws is None:
+            nbytes = load_library().hq_lutgemm_workspace_bytes(self.mSize)
+            self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.bWeight.device)
+        return self._ws
+
+
+def matmul(output, input, nqW: nQWeight_fp16, m: int = 1, algo: int = 0) -> None:
+    """matmul(void* output, void* input, nQWeight_fp16& nqW, int m, int algo)
+    (lut-gemm-cuda/kernels.cu:27-31): overwrites output[0:mSize] with the
+    mat-vec of one input row (like the reference, only batch 1 is computed)."""
+    lib = load_library()
+    ws = nqW.workspace()
+    args = (
+        _dev(output, torch.float16, "output"), _dev(input, torch.float16, "input"),
+        nqW.bWeight.data_ptr(), nqW.alpha.data_ptr(),
+        0 if nqW.q_bias is None else nqW.q_bias.data_ptr(),
+        nqW.mSize, nqW.kSize, nqW.nb, nqW.group_size,
+        ws.data_ptr(), ws.numel())
+    with torch.cuda.device(nqW.bWeight.device):
+        check("hq_lutgemm_nqmv", lib.hq_lutgemm_nqmv(*args, _stream()))
+
+
+# --------------------------------------------------------------------------
+# quantAQLM
+# --------------------------------------------------------------------------
+
+def code1x16_matvec(A, B, C_out, codebook, prob_m: int, prob_k: int,
+                    codebook_a_sizes: Sequence[int], codebook_stride: int,
+                    scales: Optional[torch.Tensor] = None) -> None:
+    """code1x16_matvec (quantAQLM-cuda/main.cu:113-141).  A = codes (int16 or
+    uint16, [prob_m][prob_k/8]), B = input half[prob_k], C_out = half[prob_m]
+    (overwritten), codebook half[..][65536][8]; `scales` is an extension."""
+    lib = load_library()
+    if A.dtype not in (torch.int16, torch.uint16):
+        raise TypeError("A: expected int16/uint16 codes")
+    sizes = (C.c_int * 4)(*[int(v) for v in codebook_a_sizes])
+    args = (
+        _dev(A, A.dtype, "A"), _dev(B, torch.float16, "B"),
+        _dev(C_out, torch.float16, "C"), _dev(codebook, torch.float16, "codebook"),
+        prob_m, prob_k, sizes, codebook_stride,
+        0 if scales is None else _dev(scales, torch.float16, "scales"))
+    with torch.cuda.device(A.device):
+        check("hq_aqlm_1x16_matvec", lib.hq_aqlm_1x16_matvec(*args, _stream()))
+
+
+def code2x8_matvec(A, B, C_out, codebooks, prob_m: int, prob_k: int,
+                   scales: Optional[torch.Tensor] = None) -> None:
+    """AQLM 2x8 mat-vec (no counterpart in the reference tree).  A = uint8 codes
+    [prob_m][prob_k/8][2], codebooks half[2][256][8]."""
+    lib = load_library()
+    args = (
+        _dev(A, torch.uint8, "A"), _dev(B, torch.float16, "B"),
+        _dev(C_out, torch.float16, "C"), _dev(codebooks, torch.float16, "codebooks"),
+        prob_m, prob_k,
+        0 if scales is None else _dev(scales, torch.float16, "scales"))
+    with torch.cuda.device(A.device):
+        check("hq_aqlm_2x8_matvec", lib.hq_aqlm_2x8_matvec(*args, _stream()))

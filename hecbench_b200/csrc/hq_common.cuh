@@ -1,0 +1,71 @@
+// Shared helpers for the libhq kernels (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "hq.h"
+
+namespace hq {
+
+// Per-thread record of the last failing CUDA runtime call.
+int& last_cuda_error_ref();
+
+inline int cuda_status(cudaError_t e) {
+  if (e == cudaSuccess) return HQ_OK;
+  last_cuda_error_ref() = (int)e;
+  return HQ_ERR_CUDA;
+}
+
+// Launch errors are sticky-free: cudaGetLastError clears and returns them.
+inline int launch_status() { return cuda_status(cudaGetLastError()); }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
+inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// Streaming 128-bit load that does not allocate in L1: packed weights are
+// read exactly once.
+__device__ __forceinline__ uint4 ldg_stream_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_stream_u2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+               : "=r"(v.x), "=r"(v.y)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ __half2 u32_as_half2(uint32_t u) {
+  return *reinterpret_cast<__half2*>(&u);
+}
+__device__ __forceinline__ uint32_t half2_as_u32(__half2 h) {
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+}  // namespace hq

@@ -1,0 +1,135 @@
+/*
+ * hq.h - C ABI of libhq.so: B200 (sm_100a) kernels for HeCBench's weight-only
+ * quantized matrix-vector family.
+ *
+ * Every entry point takes plain device pointers and sizes, is asynchronous on
+ * the given CUDA stream (pass NULL for the default stream), returns 0 on
+ * success or a negative HQ_ERR_* code, never throws, never exits, and never
+ * falls back to the CPU.  Packed-weight pointers must be 16-byte aligned.
+ * "half" buffers are IEEE binary16 (the layout of CUDA's __half), declared
+ * void* so that this header needs no CUDA include.
+ *
+ * File:line citations give the HeCBench interface each entry replaces
+ * (paths relative to the HeCBench source tree).
+ */
+#ifndef HQ_H_
+#define HQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* hq_stream_t; /* == cudaStream_t */
+
+enum {
+  HQ_OK = 0,
+  HQ_ERR_BAD_SHAPE = -1,   /* a size violates the documented divisibility rule */
+  HQ_ERR_NULL_POINTER = -2,
+  HQ_ERR_MISALIGNED = -3,  /* a pointer is not aligned as documented */
+  HQ_ERR_CUDA = -4,        /* a CUDA runtime call failed (see hq_last_cuda_error) */
+  HQ_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+  HQ_ERR_UNSUPPORTED = -6, /* valid arguments the kernels do not cover */
+  HQ_ERR_TOO_LARGE = -7    /* size beyond a documented fixed maximum */
+};
+
+int hq_version(void);
+const char* hq_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+int hq_last_cuda_error(void);
+
+/* ---------------- GPTQ 3-bit GEMV (quant3MatMul) ---------------- */
+
+/* Replaces vecquant3matmul<float> (quant3MatMul-cuda/kernels.h:171-190).
+ * mul[c] += sum_k (scales[c]*q[k][c] - zeros[c]) * vec[k]; mat is
+ * int32[height][width], 32 codes per 3 consecutive rows; height % 3 == 0,
+ * width % 4 == 0.  Accumulates into mul (the caller zeroes it), like the
+ * reference. */
+int hq_q3_gemv_f32(const float* vec, const int32_t* mat, float* mul, const float* scales,
+                   const float* zeros, int height, int width, hq_stream_t stream);
+
+/* Replaces vecquant3matmul_faster (quant3MatMul-cuda/kernels.h:193-217):
+ * fp16 input vector, fp32 parameters and output, fp16 dequant rule. */
+int hq_q3_gemv_f16in(const void* vec_half, const int32_t* mat, float* mul,
+                     const float* scales, const float* zeros, int height, int width,
+                     hq_stream_t stream);
+
+/* Dequantised weights W[K][width], K = height*32/3, by the fp32 rule of
+ * kernels.h:43 (fma(scale, q, -zero)) resp. the fp16 rule of
+ * kernels.h:121-122,137 (hfma(half(q), half(scale), half(-zero))).
+ * No counterpart launcher in the reference; exists for bit-exact checks. */
+int hq_q3_dequant_f32(const int32_t* mat, const float* scales, const float* zeros, float* W,
+                      int height, int width, hq_stream_t stream);
+int hq_q3_dequant_f16(const int32_t* mat, const float* scales, const float* zeros,
+                      void* W_half, int height, int width, hq_stream_t stream);
+
+/* ---------------- bitsandbytes blockwise (quantBnB) ---------------- */
+
+/* Replaces the launch kQuantize<256,256><<<grid,block>>>(code, A, out, n)
+ * (quantBnB-cuda/main.cu:90-130,176): out[i] = index of the code-table entry
+ * that dQuantize<0> (main.cu:13-66) selects for A[i].  Bit exact. */
+int hq_bnb_quantize_u8(const float* code256, const float* A, uint8_t* out, size_t n,
+                       hq_stream_t stream);
+
+/* flags for the NF4 entry points */
+#define HQ_NF4_HIGH_NIBBLE_FIRST 0 /* even element = high nibble (default) */
+#define HQ_NF4_LOW_NIBBLE_FIRST 1  /* even element = low nibble */
+
+/* NF4 blockwise dequantize (no counterpart in the reference tree):
+ * out[e] = half_rn(lut16[code_e] * absmax[e / blocksize]), n elements, two
+ * codes per byte, n % 32 == 0, blocksize a multiple of 32. */
+int hq_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut16,
+                       void* out_half, size_t n, int blocksize, int flags,
+                       hq_stream_t stream);
+
+/* NF4 4-bit GEMV (no counterpart in the reference tree):
+ * out[n] = half_rn(sum_k A[k] * lut16[code[n][k]] * absmax[(n*K+k)/blocksize]),
+ * B is [N][K/2] bytes row-major; K % 32 == 0, blocksize a multiple of 32 that
+ * divides K. */
+int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax,
+                    const float* lut16, void* out_half, int N, int K, int blocksize,
+                    int flags, hq_stream_t stream);
+
+/* ---------------- LUT-GEMM binary-coding mat-vec (lut-gemm) ---------------- */
+
+/* Bytes of zero-initialised device scratch hq_lutgemm_nqmv needs for M
+ * outputs.  The scratch must be zero before the first call; every call leaves
+ * it zero again, so one buffer can serve a sequence of calls on one stream. */
+size_t hq_lutgemm_workspace_bytes(int M);
+
+/* Replaces matmul(output, input, nqW, m) -> nqmv / nqmv_bias
+ * (lut-gemm-cuda/kernels.cu:22-31, mv_fp16.h:101-131,228-259) for one input
+ * row.  bW uint32[K/32][nb][M], alpha half[K/group][nb][M], q_bias
+ * half[K/group][M] or NULL, x half[K], out half[M] (overwritten).
+ * K % 32 == 0, group_size % 32 == 0, M % 4 == 0, 1 <= nb <= 8. */
+int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW,
+                    const void* alpha_half, const void* q_bias_half, int M, int K, int nb,
+                    int group_size, void* workspace, size_t workspace_bytes,
+                    hq_stream_t stream);
+
+/* ---------------- AQLM additive codebooks (quantAQLM) ---------------- */
+
+/* Replaces code1x16_matvec (quantAQLM-cuda/main.cu:113-141).  codes
+ * uint16[prob_m][prob_k/8], x half[prob_k], out half[prob_m] (overwritten),
+ * codebook half[.][65536][8] with up to three stacked codebooks selected by
+ * the cumulative row ranges cb_sizes[0..3] (main.cu:43-51), cb_stride_int4 =
+ * 16-byte units between codebooks.  scales (half[prob_m], nullable) is an
+ * extension: the row sum is multiplied by it before rounding.
+ * prob_k % 64 == 0. */
+int hq_aqlm_1x16_matvec(const void* codes, const void* x_half, void* out_half,
+                        const void* codebook, int prob_m, int prob_k, const int cb_sizes[4],
+                        int cb_stride_int4, const void* scales_half, hq_stream_t stream);
+
+/* AQLM 2x8 (no counterpart in the reference tree): codes
+ * uint8[prob_m][prob_k/8][2], codebooks half[2][256][8], scales nullable.
+ * prob_k % 64 == 0. */
+int hq_aqlm_2x8_matvec(const void* codes, const void* x_half, void* out_half,
+                       const void* codebooks, int prob_m, int prob_k, const void* scales_half,
+                       hq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HQ_H_ */

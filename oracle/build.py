@@ -1,0 +1,90 @@
+"""Builds the test oracles.  TEST INFRASTRUCTURE ONLY.
+
+  oracle/liboracle.so          plain-C restatement (hq_oracle.c), gcc -fopenmp
+  oracle/_ref/libref_cpu.so    the reference's own CPU quantBnB code, g++
+  oracle/_ref/libref_gpu.so    the reference's own CUDA kernels for sm_100a, nvcc
+
+The two _ref libraries are compiled from the reference sources where they lie
+(REFERENCE_ROOT, default /root/reference); they are only (re)built when that
+tree is present, and never needed by the shipped library.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+
+
+def _run(cmd):
+    r = subprocess.run(list(map(str, cmd)), capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build failed: " + " ".join(map(str, cmd)) + "\n" + r.stderr)
+
+
+def _stale(target: Path, deps) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(d).exists() and Path(d).stat().st_mtime > t for d in deps)
+
+
+def build_oracle(force: bool = False) -> Path:
+    out = HERE / "liboracle.so"
+    src = HERE / "hq_oracle.c"
+    if force or _stale(out, [src]):
+        _run(["gcc", "-O3", "-march=native", "-fopenmp", "-fPIC", "-shared", "-std=c11",
+              "-fno-fast-math", "-ffp-contract=off", src, "-o", out, "-lm"])
+    return out
+
+
+def build_ref_cpu(force: bool = False):
+    out = HERE / "_ref" / "libref_cpu.so"
+    if not (REF / "src" / "quantBnB-omp" / "main.cpp").exists():
+        return out if out.exists() else None
+    src = HERE / "ref_cpu.cpp"
+    if force or _stale(out, [src]):
+        out.parent.mkdir(exist_ok=True)
+        _run(["g++", "-O3", "-std=c++17", "-pthread", "-fPIC", "-shared", "-w",
+              f"-I{REF / 'src' / 'quantBnB-omp'}", f"-I{REF / 'src' / 'quantBnB-cuda'}",
+              src, "-o", out])
+    return out
+
+
+def build_ref_gpu(force: bool = False):
+    out = HERE / "_ref" / "libref_gpu.so"
+    if not (REF / "src" / "quant3MatMul-cuda" / "kernels.h").exists():
+        return out if out.exists() else None
+    parts = {
+        "ref_gpu_q3.cu": ["quant3MatMul-cuda"],
+        "ref_gpu_bnb.cu": ["quantBnB-cuda"],
+        "ref_gpu_lut.cu": ["lut-gemm-cuda"],
+        "ref_gpu_aqlm.cu": ["quantAQLM-cuda"],
+    }
+    srcs = [HERE / p for p in parts]
+    if not (force or _stale(out, srcs)):
+        return out
+    out.parent.mkdir(exist_ok=True)
+    objs = []
+    for name, dirs in parts.items():
+        obj = out.parent / (Path(name).stem + ".o")
+        inc = [f"-I{REF / 'src' / d}" for d in dirs]
+        _run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w",
+              "-Xcompiler", "-fPIC", *inc, "-c", HERE / name, "-o", obj])
+        objs.append(obj)
+    _run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", out, *objs,
+          "-lcudart"])
+    return out
+
+
+def build_all(force: bool = False):
+    return build_oracle(force), build_ref_cpu(force), build_ref_gpu(force)
+
+
+if __name__ == "__main__":
+    for p in build_all(force="-f" in sys.argv):
+        print(p)

@@ -1,0 +1,634 @@
+/*
+ * CPU oracle for the weight-only quantized mat-vec family.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is a plain-C restatement of the
+ * algorithms of four HeCBench benchmarks (quant3MatMul, quantBnB, lut-gemm,
+ * quantAQLM) plus the written semantics of the pieces that have no reference
+ * implementation (NF4 dequantize / 4-bit GEMV, AQLM 2x8, per-output scales,
+ * batched dequant-GEMM).  It is used as the checker by the tests, by the smoke
+ * entry and as the timed CPU baseline of the bench.  Nothing in the shipped
+ * library calls it, and it is never a fallback for a missing GPU.
+ *
+ * Parity pins:
+ *   q3    - known-answer vector of quant3MatMul-cuda/main.cu:28-53,86 (-49152).
+ *   bnb   - byte-exact against the reference dQuantize compiled from
+ *           quantBnB-omp/main.cpp (see oracle/ref_cpu.cpp and tests/golden).
+ *   lut-gemm, aqlm 1x16 - no usable known-answer test exists in the reference;
+ *           pinned on the GPU box against the reference CUDA kernels compiled
+ *           from their own sources (oracle/ref_gpu.cu).
+ *   nf4, aqlm 2x8, scales, batched - PARITY UNPINNED: the reference has no
+ *           implementation or test of these; semantics are the ones written in
+ *           each function's comment.
+ *
+ * Every function cites the reference file:line it follows (paths relative to
+ * the HeCBench source tree).
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* ------------------------------------------------------------------ */
+/* fp16 helpers (IEEE binary16, round-to-nearest-even), bit exact      */
+/* ------------------------------------------------------------------ */
+
+static inline float orc_h2f(uint16_t h) {
+  uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1fu;
+  uint32_t man = h & 0x3ffu;
+  uint32_t bits;
+  if (exp == 0) {
+    if (man == 0) {
+      bits = sign;
+    } else { /* subnormal: normalise */
+      int e = -1;
+      do { man <<= 1; e++; } while (!(man & 0x400u));
+      man &= 0x3ffu;
+      bits = sign | ((uint32_t)(127 - 15 - e) << 23) | (man << 13);
+    }
+  } else if (exp == 31) {
+    bits = sign | 0x7f800000u | (man << 13);
+  } else {
+    bits = sign | ((exp + 112u) << 23) | (man << 13);
+  }
+  float f;
+  memcpy(&f, &bits, 4);
+  return f;
+}
+
+/* double -> half, RN-even, single rounding (the argument is exact). */
+static inline uint16_t orc_d2h(double d) {
+  uint16_t sign = 0;
+  if (d != d) return 0x7fffu;
+  if (signbit(d)) { sign = 0x8000u; d = -d; }
+  if (d == 0.0) return sign;
+  if (isinf(d)) return sign | 0x7c00u;
+  int e;
+  double m = frexp(d, &e); /* d = m * 2^e, m in [0.5,1) */
+  /* value = (2m) * 2^(e-1); half normal exponent range -14..15 */
+  int he = e - 1;
+  double q;
+  if (he < -14) {
+    /* subnormal: units of 2^-24 */
+    q = ldexp(d, 24);
+    double r = nearbyint(q); /* default rounding mode = RN-even */
+    uint32_t mi = (uint32_t)r;
+    if (mi >= 0x400u) return sign | 0x0400u; /* rounded up to min normal */
+    return sign | (uint16_t)mi;
+  }
+  q = ldexp(d, 10 - he); /* in [1024, 2048) */
+  double r = nearbyint(q);
+  uint32_t mi = (uint32_t)r;
+  if (mi >= 2048u) { mi >>= 1; he++; }
+  if (he > 15) return sign | 0x7c00u;
+  return sign | (uint16_t)(((uint32_t)(he + 15) << 10) | (mi & 0x3ffu));
+}
+
+static inline uint16_t orc_f2h(float f) { return orc_d2h((double)f); }
+
+/* fp16 fused multiply-add: one rounding of a*b+c (done in double; the
+ * product of two halves is exact in double, the sum is rounded to 53 bits
+ * before the final rounding to 11 bits - a double rounding that can differ
+ * only on exact 53-bit ties, which 22+11-bit operands cannot produce unless
+ * the exponent gap exceeds 30 binades). */
+static inline uint16_t orc_hfma(uint16_t a, uint16_t b, uint16_t c) {
+  return orc_d2h(fma((double)orc_h2f(a), (double)orc_h2f(b), (double)orc_h2f(c)));
+}
+static inline uint16_t orc_hadd(uint16_t a, uint16_t b) {
+  return orc_d2h((double)orc_h2f(a) + (double)orc_h2f(b));
+}
+static inline uint16_t orc_hmul(uint16_t a, uint16_t b) {
+  return orc_d2h((double)orc_h2f(a) * (double)orc_h2f(b));
+}
+
+void orc_f32_to_f16(const float* src, uint16_t* dst, size_t n) {
+  for (size_t i = 0; i < n; i++) dst[i] = orc_f2h(src[i]);
+}
+void orc_f16_to_f32(const uint16_t* src, float* dst, size_t n) {
+  for (size_t i = 0; i < n; i++) dst[i] = orc_h2f(src[i]);
+}
+
+/* ------------------------------------------------------------------ */
+/* GPTQ 3-bit (quant3MatMul)                                           */
+/* ------------------------------------------------------------------ */
+
+/* Code j (0..31) of K-group r for column c lives in the 96-bit little-endian
+ * integer formed by rows 3r,3r+1,3r+2 of mat[:,c], at bits 3j..3j+2.
+ * Follows the extraction order of quant3MatMul-cuda/kernels.h:41-87
+ * (codes 10 and 21 straddle the word boundaries, :55 and :71). */
+static inline unsigned q3_code(const int32_t* mat, int width, int r, int c, int j) {
+  uint32_t w0 = (uint32_t)mat[(size_t)(3 * r + 0) * width + c];
+  uint32_t w1 = (uint32_t)mat[(size_t)(3 * r + 1) * width + c];
+  uint32_t w2 = (uint32_t)mat[(size_t)(3 * r + 2) * width + c];
+  int bit = 3 * j;
+  uint64_t lo = (uint64_t)w0 | ((uint64_t)w1 << 32);
+  if (bit + 3 <= 64) return (unsigned)((lo >> bit) & 7u);
+  uint64_t hi = (uint64_t)w1 | ((uint64_t)w2 << 32); /* bits 32..95 */
+  return (unsigned)((hi >> (bit - 32)) & 7u);
+}
+
+/* codes[K][width] (uint8, 0..7) -> mat[K*3/32][width]. K multiple of 32. */
+void orc_q3_pack(const uint8_t* codes, int32_t* mat, int K, int width) {
+  int groups = K / 32;
+  memset(mat, 0, (size_t)groups * 3 * width * sizeof(int32_t));
+  for (int r = 0; r < groups; r++)
+    for (int c = 0; c < width; c++) {
+      uint32_t w[3] = {0, 0, 0};
+      for (int j = 0; j < 32; j++) {
+        uint32_t q = codes[(size_t)(32 * r + j) * width + c] & 7u;
+        int bit = 3 * j;
+        w[bit >> 5] |= q << (bit & 31);
+        if ((bit & 31) > 29) w[(bit >> 5) + 1] |= q >> (32 - (bit & 31));
+      }
+      for (int t = 0; t < 3; t++) mat[(size_t)(3 * r + t) * width + c] = (int32_t)w[t];
+    }
+}
+
+void orc_q3_unpack(const int32_t* mat, uint8_t* codes, int height, int width) {
+  int groups = height / 3;
+  for (int r = 0; r < groups; r++)
+    for (int j = 0; j < 32; j++)
+      for (int c = 0; c < width; c++)
+        codes[(size_t)(32 * r + j) * width + c] = (uint8_t)q3_code(mat, width, r, c, j);
+}
+
+/* fp32 dequant rule of VecQuant3MatMulKernel<float>: the expression
+ * (scale * float(q) - zero) of kernels.h:43 is contracted by nvcc's default
+ * -fmad=true into one fused multiply-add.  W is [K][width]. */
+void orc_q3_dequant_f32(const int32_t* mat, const float* scales, const float* zeros,
+                        float* W, int height, int width) {
+  int groups = height / 3;
+#pragma omp parallel for
+  for (int r = 0; r < groups; r++)
+    for (int j = 0; j < 32; j++)
+      for (int c = 0; c < width; c++)
+        W[(size_t)(32 * r + j) * width + c] =
+            fmaf(scales[c], (float)q3_code(mat, width, r, c, j), -zeros[c]);
+}
+
+/* fp16 dequant rule of VecQuant3MatMulKernelFaster (kernels.h:121-122,137):
+ * W = hfma(half(q), half_rn(scale), half_rn(-zero)), one fp16 rounding. */
+void orc_q3_dequant_f16(const int32_t* mat, const float* scales, const float* zeros,
+                        uint16_t* W, int height, int width) {
+  int groups = height / 3;
+#pragma omp parallel for
+  for (int r = 0; r < groups; r++)
+    for (int j = 0; j < 32; j++)
+      for (int c = 0; c < width; c++) {
+        uint16_t q = orc_f2h((float)q3_code(mat, width, r, c, j));
+        W[(size_t)(32 * r + j) * width + c] =
+            orc_hfma(q, orc_f2h(scales[c]), orc_f2h(-zeros[c]));
+      }
+}
+
+/* mul[c] += sum_k W[k][c]*vec[k] in the reference's fp32 order
+ * (kernels.h:33-89): one fp32 running sum per 256-deep K slab, each term
+ * fma(fma(scale,q,-zero), vec[k], res); slabs are added to mul in slab order
+ * (the reference uses atomicAdd, whose order is unspecified). */
+void orc_q3_gemv_f32(const float* vec, const int32_t* mat, float* mul,
+                     const float* scales, const float* zeros, int height, int width) {
+  int slabs = height / 24;
+#pragma omp parallel for
+  for (int c = 0; c < width; c++) {
+    float out = mul[c];
+    for (int s = 0; s < slabs; s++) {
+      float res = 0.f;
+      for (int g = 0; g < 8; g++)
+        for (int j = 0; j < 32; j++) {
+          int r = s * 8 + g;
+          float w = fmaf(scales[c], (float)q3_code(mat, width, r, c, j), -zeros[c]);
+          res = fmaf(w, vec[(size_t)s * 256 + g * 32 + j], res);
+        }
+      out += res;
+    }
+    mul[c] = out;
+  }
+}
+
+/* The fp16 "faster" kernel restated (kernels.h:93-169): per 32 weights a
+ * half2 accumulator starts at zero, res2 = hfma2(hfma2(q2,scale,-zero),x2,res2)
+ * for the 16 pairs (even k in .x, odd k in .y), then
+ * res += float(res2.x) + float(res2.y) in fp32; slabs added in slab order. */
+void orc_q3_gemv_f16in(const uint16_t* vec, const int32_t* mat, float* mul,
+                       const float* scales, const float* zeros, int height, int width) {
+  int slabs = height / 24;
+#pragma omp parallel for
+  for (int c = 0; c < width; c++) {
+    uint16_t sc = orc_f2h(scales[c]);
+    uint16_t nz = orc_f2h(-zeros[c]);
+    float out = mul[c];
+    for (int s = 0; s < slabs; s++) {
+      float res = 0.f;
+      for (int g = 0; g < 8; g++) {
+        int r = s * 8 + g;
+        uint16_t ax = 0, ay = 0;
+        for (int p = 0; p < 16; p++) {
+          uint16_t q0 = orc_f2h((float)q3_code(mat, width, r, c, 2 * p));
+          uint16_t q1 = orc_f2h((float)q3_code(mat, width, r, c, 2 * p + 1));
+          size_t k = (size_t)s * 256 + g * 32 + 2 * p;
+          ax = orc_hfma(orc_hfma(q0, sc, nz), vec[k], ax);
+          ay = orc_hfma(orc_hfma(q1, sc, nz), vec[k + 1], ay);
+        }
+        res += orc_h2f(ax) + orc_h2f(ay);
+      }
+      out += res;
+    }
+    mul[c] = out;
+  }
+}
+
+/* fp64 truth: mul64[c] = sum_k W32[k][c]*vec[k], W32 by the fp32 dequant rule
+ * (f16in = 0) or the fp16 rule (f16in = 1, vec given as fp32 values that are
+ * exactly representable in fp16). */
+void orc_q3_gemv_f64(const float* vec, const int32_t* mat, double* out,
+                     const float* scales, const float* zeros, int height, int width,
+                     int f16rule) {
+  int groups = height / 3;
+#pragma omp parallel for
+  for (int c = 0; c < width; c++) {
+    double acc = 0.0;
+    uint16_t sc = orc_f2h(scales[c]), nz = orc_f2h(-zeros[c]);
+    for (int r = 0; r < groups; r++)
+      for (int j = 0; j < 32; j++) {
+        unsigned q = q3_code(mat, width, r, c, j);
+        double w = f16rule ? (double)orc_h2f(orc_hfma(orc_f2h((float)q), sc, nz))
+                           : (double)fmaf(scales[c], (float)q, -zeros[c]);
+        acc += w * (double)vec[(size_t)32 * r + j];
+      }
+    out[c] = acc;
+  }
+}
+
+/* ------------------------------------------------------------------ */
+/* bitsandbytes 8-bit dynamic-map blockwise quantize (quantBnB)        */
+/* ------------------------------------------------------------------ */
+
+/* dQuantize<0> restated (quantBnB-cuda/main.cu:13-66): seven-step pivot
+ * search from index 127 with strides 64..1 over a 256-entry table, then a
+ * midpoint test against the nearest bracket that was visited. */
+static inline uint8_t bnb_quantize_one(const float* code, float x) {
+  int pivot = 127, upper_pivot = 255, lower_pivot = 0;
+  float lower = -1.0f, upper = 1.0f;
+  float val = code[pivot];
+  for (int i = 64; i > 0; i >>= 1) {
+    if (x > val) { lower_pivot = pivot; lower = val; pivot += i; }
+    else         { upper_pivot = pivot; upper = val; pivot -= i; }
+    val = code[pivot];
+  }
+  if (upper_pivot == 255) upper = code[upper_pivot];
+  if (lower_pivot == 0) lower = code[lower_pivot];
+  if (x > val) {
+    float midpoint = (upper + val) * 0.5f;
+    return (uint8_t)(x > midpoint ? upper_pivot : pivot);
+  } else {
+    float midpoint = (lower + val) * 0.5f;
+    return (uint8_t)(x < midpoint ? lower_pivot : pivot);
+  }
+}
+
+/* Loop of quantBnB-omp/main.cpp:105-108,119-122 under a host parallel-for. */
+void orc_bnb_quantize(const float* code, const float* A, uint8_t* out, size_t n) {
+#pragma omp parallel for
+  for (size_t i = 0; i < n; i++) out[i] = bnb_quantize_one(code, A[i]);
+}
+
+/* ------------------------------------------------------------------ */
+/* NF4 blockwise 4-bit (no reference implementation - parity unpinned) */
+/* ------------------------------------------------------------------ */
+
+/* Semantics (ours): element e of the flattened [N][K] matrix has its 4-bit
+ * code in byte e/2; with low_first == 0 the even element is the HIGH nibble,
+ * with low_first != 0 it is the LOW nibble.  The 16 levels are a runtime
+ * table lut16 (fp32).  One fp32 absmax per `blocksize` consecutive elements. */
+static inline unsigned nf4_code(const uint8_t* B, size_t e, int low_first) {
+  uint8_t b = B[e >> 1];
+  int want_low = ((e & 1) != 0) ^ (low_first != 0);
+  return want_low ? (b & 15u) : (b >> 4);
+}
+
+/* out[e] = half_rn( lut16[code_e] * absmax[e / blocksize] ), fp32 multiply. */
+void orc_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut16,
+                         uint16_t* out, size_t n, int blocksize, int low_first) {
+#pragma omp parallel for
+  for (size_t e = 0; e < n; e++)
+    out[e] = orc_f2h(lut16[nf4_code(B, e, low_first)] * absmax[e / (size_t)blocksize]);
+}
+
+/* fp64 truth of the 4-bit GEMV: out[n] = sum_k A[k] * (lut16[c]*absmax) with
+ * the weight taken as the exact fp32 product (not rounded to fp16). */
+void orc_nf4_gemv_f64(const uint16_t* A, const uint8_t* B, const float* absmax,
+                      const float* lut16, double* out, int N, int K, int blocksize,
+                      int low_first) {
+#pragma omp parallel for
+  for (int n = 0; n < N; n++) {
+    double acc = 0.0;
+    for (int k = 0; k < K; k++) {
+      size_t e = (size_t)n * K + k;
+      float w = lut16[nf4_code(B, e, low_first)] * absmax[e / (size_t)blocksize];
+      acc += (double)w * (double)orc_h2f(A[k]);
+    }
+    out[n] = acc;
+  }
+}
+
+/* fp32-accumulating version used as the timed CPU baseline. */
+void orc_nf4_gemv_f32(const uint16_t* A, const uint8_t* B, const float* absmax,
+                      const float* lut16, uint16_t* out, int N, int K, int blocksize,
+                      int low_first) {
+  float* Af = (float*)malloc((size_t)K * sizeof(float));
+  for (int k = 0; k < K; k++) Af[k] = orc_h2f(A[k]);
+#pragma omp parallel for
+  for (int n = 0; n < N; n++) {
+    float acc = 0.f;
+    size_t e0 = (size_t)n * K;
+    if ((e0 % (size_t)blocksize) == 0 && (K % blocksize) == 0 && (blocksize % 2) == 0) {
+      for (int kb = 0; kb < K; kb += blocksize) {
+        float part = 0.f;
+        const uint8_t* bp = B + ((e0 + kb) >> 1);
+        for (int j = 0; j < blocksize; j += 2) {
+          uint8_t b = bp[j >> 1];
+          unsigned c0 = low_first ? (b & 15u) : (b >> 4);
+          unsigned c1 = low_first ? (b >> 4) : (b & 15u);
+          part += lut16[c0] * Af[kb + j] + lut16[c1] * Af[kb + j + 1];
+        }
+        acc += part * absmax[(e0 + kb) / (size_t)blocksize];
+      }
+    } else {
+      for (int k = 0; k < K; k++) {
+        size_t e = e0 + k;
+        acc += lut16[nf4_code(B, e, low_first)] * absmax[e / (size_t)blocksize] * Af[k];
+      }
+    }
+    out[n] = orc_f2h(acc);
+  }
+  free(Af);
+}
+
+/* ------------------------------------------------------------------ */
+/* LUT-GEMM binary-coding mat-vec (lut-gemm)                           */
+/* ------------------------------------------------------------------ */
+
+/* Layouts of lut-gemm-cuda/main.cu:27-30,118-134 and nQWeight_fp16.h:24-26:
+ * bW[K/32][nb][M] (bit t of a word <-> k = 32*row + t, 1 => +1, 0 => -1),
+ * alpha[K/group][nb][M], q_bias[K/group][M] (nullable).  The dequantised
+ * weight (main.cu:136-146, with the [K][M] layout the check intended) is
+ * W[k][m] = q_bias[g][m] + sum_b alpha[g][b][m]*(2*bit-1).  Everything fp16
+ * in storage; the truth is accumulated in fp64 from the exact fp16 values. */
+void orc_lutgemm_dequant_f32(const uint32_t* bW, const uint16_t* alpha,
+                             const uint16_t* q_bias, float* W, int M, int K, int nb,
+                             int group_size) {
+#pragma omp parallel for
+  for (int k = 0; k < K; k++) {
+    int g = k / group_size;
+    for (int m = 0; m < M; m++) {
+      double w = q_bias ? (double)orc_h2f(q_bias[(size_t)g * M + m]) : 0.0;
+      for (int b = 0; b < nb; b++) {
+        uint32_t word = bW[((size_t)(k >> 5) * nb + b) * M + m];
+        double s = ((word >> (k & 31)) & 1u) ? 1.0 : -1.0;
+        w += s * (double)orc_h2f(alpha[((size_t)g * nb + b) * M + m]);
+      }
+      W[(size_t)k * M + m] = (float)w;
+    }
+  }
+}
+
+void orc_lutgemm_gemv_f64(const uint16_t* x, const uint32_t* bW, const uint16_t* alpha,
+                          const uint16_t* q_bias, double* out, int M, int K, int nb,
+                          int group_size) {
+  int G = K / group_size;
+  double* xs = (double*)malloc((size_t)K * sizeof(double));
+  for (int k = 0; k < K; k++) xs[k] = (double)orc_h2f(x[k]);
+#pragma omp parallel for
+  for (int m = 0; m < M; m++) {
+    double acc = 0.0;
+    for (int g = 0; g < G; g++) {
+      double sumx = 0.0;
+      for (int k = g * group_size; k < (g + 1) * group_size; k++) sumx += xs[k];
+      if (q_bias) acc += (double)orc_h2f(q_bias[(size_t)g * M + m]) * sumx;
+      for (int b = 0; b < nb; b++) {
+        double pos = 0.0; /* sum of x where bit = 1 */
+        for (int k = g * group_size; k < (g + 1) * group_size; k++) {
+          uint32_t word = bW[((size_t)(k >> 5) * nb + b) * M + m];
+          if ((word >> (k & 31)) & 1u) pos += xs[k];
+        }
+        acc += (double)orc_h2f(alpha[((size_t)g * nb + b) * M + m]) * (2.0 * pos - sumx);
+      }
+    }
+    out[m] = acc;
+  }
+  free(xs);
+}
+
+/* fp32 version for CPU timing (same loop nest, float accumulators). */
+void orc_lutgemm_gemv_f32(const uint16_t* x, const uint32_t* bW, const uint16_t* alpha,
+                          const uint16_t* q_bias, uint16_t* out, int M, int K, int nb,
+                          int group_size) {
+  int G = K / group_size;
+  float* xs = (float*)malloc((size_t)K * sizeof(float));
+  for (int k = 0; k < K; k++) xs[k] = orc_h2f(x[k]);
+#pragma omp parallel for
+  for (int m = 0; m < M; m++) {
+    float acc = 0.f;
+    for (int g = 0; g < G; g++) {
+      float sumx = 0.f;
+      for (int k = g * group_size; k < (g + 1) * group_size; k++) sumx += xs[k];
+      if (q_bias) acc += orc_h2f(q_bias[(size_t)g * M + m]) * sumx;
+      for (int b = 0; b < nb; b++) {
+        float pos = 0.f;
+        for (int k0 = g * group_size; k0 < (g + 1) * group_size; k0 += 32) {
+          uint32_t word = bW[((size_t)(k0 >> 5) * nb + b) * M + m];
+          int lim = (g + 1) * group_size - k0;
+          if (lim > 32) lim = 32;
+          for (int t = 0; t < lim; t++)
+            if ((word >> t) & 1u) pos += xs[k0 + t];
+        }
+        acc += orc_h2f(alpha[((size_t)g * nb + b) * M + m]) * (2.f * pos - sumx);
+      }
+    }
+    out[m] = orc_f2h(acc);
+  }
+  free(xs);
+}
+
+/* ------------------------------------------------------------------ */
+/* AQLM additive codebooks (quantAQLM)                                 */
+/* ------------------------------------------------------------------ */
+
+/* Code1x16MatVec restated bit for bit (quantAQLM-cuda/main.cu:39-108).
+ * Row m has prob_k/8 uint16 codes, read as int4 (8 codes); lane l of the
+ * row's warp takes int4 indices l, l+32, ...; code i of int4 idx multiplies
+ * inputs 8*(8*idx+i)..+7 with four fp16 hfma2 (main.cu:94-96), whose two
+ * halves are added to the lane's fp32 sum (:97); lanes are combined with the
+ * shfl_down tree 16,8,4,2,1 (:106); lane 0 stores half_rn (:108).  The
+ * codebook of a row is picked by the cumulative row ranges cb_sizes
+ * (:43-51).  `scales` (nullable, fp16 per output) is OUR extension: the fp32
+ * sum is multiplied by float(scale[m]) before the final rounding. */
+void orc_aqlm_1x16_ref(const uint16_t* codes, const uint16_t* x, uint16_t* out,
+                       const uint16_t* codebook, int prob_m, int prob_k,
+                       const int* cb_sizes, int cb_stride_int4, const uint16_t* scales) {
+  int n_int4 = prob_k / 64; /* int4 per row */
+#pragma omp parallel for
+  for (int m = 0; m < prob_m; m++) {
+    const uint16_t* cb = codebook;
+    int s = 0;
+    while (s < 3 && m >= cb_sizes[s]) { cb += (size_t)cb_stride_int4 * 8; s++; }
+    float lane[32];
+    for (int l = 0; l < 32; l++) {
+      float res = 0.f;
+      for (int idx = l; idx < n_int4; idx += 32) {
+        for (int i = 0; i < 8; i++) {
+          uint16_t code = codes[(size_t)m * (prob_k / 8) + (size_t)idx * 8 + i];
+          const uint16_t* a = cb + (size_t)code * 8;
+          const uint16_t* b = x + (size_t)8 * (8 * idx + i);
+          uint16_t rx = 0, ry = 0;
+          for (int j = 0; j < 4; j++) {
+            rx = orc_hfma(a[2 * j], b[2 * j], rx);
+            ry = orc_hfma(a[2 * j + 1], b[2 * j + 1], ry);
+          }
+          res += orc_h2f(rx) + orc_h2f(ry);
+        }
+      }
+      lane[l] = res;
+    }
+    for (int off = 16; off > 0; off >>= 1)
+      for (int l = 0; l < off; l++) lane[l] += lane[l + off];
+    float r = lane[0];
+    if (scales) r *= orc_h2f(scales[m]);
+    out[m] = orc_f2h(r);
+  }
+}
+
+/* fp64 truth for 1x16 (same indexing, exact products). */
+void orc_aqlm_1x16_f64(const uint16_t* codes, const uint16_t* x, double* out,
+                       const uint16_t* codebook, int prob_m, int prob_k,
+                       const int* cb_sizes, int cb_stride_int4, const uint16_t* scales) {
+  int groups = prob_k / 8;
+#pragma omp parallel for
+  for (int m = 0; m < prob_m; m++) {
+    const uint16_t* cb = codebook;
+    int s = 0;
+    while (s < 3 && m >= cb_sizes[s]) { cb += (size_t)cb_stride_int4 * 8; s++; }
+    double acc = 0.0;
+    for (int g = 0; g < groups; g++) {
+      const uint16_t* a = cb + (size_t)codes[(size_t)m * groups + g] * 8;
+      for (int j = 0; j < 8; j++)
+        acc += (double)orc_h2f(a[j]) * (double)orc_h2f(x[(size_t)8 * g + j]);
+    }
+    if (scales) acc *= (double)orc_h2f(scales[m]);
+    out[m] = acc;
+  }
+}
+
+/* AQLM 2x8 (no reference implementation - parity unpinned).  Semantics
+ * (ours): codes uint8[prob_m][prob_k/8][2]; codebooks fp16[2][256][8];
+ * out[m] = scale[m] * sum_g sum_{c<2} codebooks[c][codes[m][g][c]] . x[8g..8g+7]. */
+void orc_aqlm_2x8_f64(const uint8_t* codes, const uint16_t* x, double* out,
+                      const uint16_t* codebooks, int prob_m, int prob_k,
+                      const uint16_t* scales) {
+  int groups = prob_k / 8;
+#pragma omp parallel for
+  for (int m = 0; m < prob_m; m++) {
+    double acc = 0.0;
+    for (int g = 0; g < groups; g++)
+      for (int c = 0; c < 2; c++) {
+        const uint16_t* a =
+            codebooks + ((size_t)c * 256 + codes[((size_t)m * groups + g) * 2 + c]) * 8;
+        for (int j = 0; j < 8; j++)
+          acc += (double)orc_h2f(a[j]) * (double)orc_h2f(x[(size_t)8 * g + j]);
+      }
+    if (scales) acc *= (double)orc_h2f(scales[m]);
+    out[m] = acc;
+  }
+}
+
+/* fp32 versions for CPU timing. */
+void orc_aqlm_1x16_f32(const uint16_t* codes, const uint16_t* x, uint16_t* out,
+                       const uint16_t* codebook, int prob_m, int prob_k,
+                       const int* cb_sizes, int cb_stride_int4, const uint16_t* scales) {
+  int groups = prob_k / 8;
+  float* xs = (float*)malloc((size_t)prob_k * sizeof(float));
+  for (int k = 0; k < prob_k; k++) xs[k] = orc_h2f(x[k]);
+#pragma omp parallel for
+  for (int m = 0; m < prob_m; m++) {
+    const uint16_t* cb = codebook;
+    int s = 0;
+    while (s < 3 && m >= cb_sizes[s]) { cb += (size_t)cb_stride_int4 * 8; s++; }
+    float acc = 0.f;
+    for (int g = 0; g < groups; g++) {
+      const uint16_t* a = cb + (size_t)codes[(size_t)m * groups + g] * 8;
+      for (int j = 0; j < 8; j++) acc += orc_h2f(a[j]) * xs[8 * g + j];
+    }
+    if (scales) acc *= orc_h2f(scales[m]);
+    out[m] = orc_f2h(acc);
+  }
+  free(xs);
+}
+
+/* ------------------------------------------------------------------ */
+/* Batched dequant-GEMM (no reference implementation - parity unpinned)*/
+/* ------------------------------------------------------------------ */
+
+/* Y[Mb][N] = X[Mb][K] * Wd[K][N] in fp64 from fp16 operands; Wd is a
+ * dequantised fp16 weight matrix produced by one of the dequant rules above
+ * (row-major [K][N]). */
+void orc_gemm_f16_f64(const uint16_t* X, const uint16_t* Wd, double* Y, int Mb, int N,
+                      int K) {
+#pragma omp parallel for
+  for (int n0 = 0; n0 < N; n0 += 64) {
+    int n1 = n0 + 64 < N ? n0 + 64 : N;
+    for (int i = 0; i < Mb; i++) {
+      double acc[64];
+      for (int n = n0; n < n1; n++) acc[n - n0] = 0.0;
+      for (int k = 0; k < K; k++) {
+        double xv = (double)orc_h2f(X[(size_t)i * K + k]);
+        const uint16_t* wr = Wd + (size_t)k * N;
+        for (int n = n0; n < n1; n++) acc[n - n0] += xv * (double)orc_h2f(wr[n]);
+      }
+      for (int n = n0; n < n1; n++) Y[(size_t)i * N + n] = acc[n - n0];
+    }
+  }
+}
+
+/* Same with Wd stored [N][K] (the NF4 dequant output orientation). */
+void orc_gemm_f16_nk_f64(const uint16_t* X, const uint16_t* Wd, double* Y, int Mb, int N,
+                         int K) {
+#pragma omp parallel for
+  for (int n = 0; n < N; n++)
+    for (int i = 0; i < Mb; i++) {
+      double acc = 0.0;
+      for (int k = 0; k < K; k++)
+        acc += (double)orc_h2f(X[(size_t)i * K + k]) * (double)orc_h2f(Wd[(size_t)n * K + k]);
+      Y[(size_t)i * N + n] = acc;
+    }
+}
+
+/* Group-wise 3-bit dequant for the batched path (ours): same packed layout as
+ * quant3MatMul (mat[K*3/32][N]); per-group fp16 scale and zero,
+ * scales/zeros[K/group][N]; W[k][n] = hfma(half(q), scale, -zero) in fp16
+ * (the rule of kernels.h:121-122,137 with the column parameters replaced by
+ * the (group, column) ones). */
+void orc_q3g_dequant_f16(const int32_t* mat, const uint16_t* scales, const uint16_t* zeros,
+                         uint16_t* W, int K, int N, int group) {
+#pragma omp parallel for
+  for (int k = 0; k < K; k++) {
+    int g = k / group;
+    for (int n = 0; n < N; n++) {
+      uint16_t q = orc_f2h((float)q3_code(mat, N, k >> 5, n, k & 31));
+      uint16_t z = zeros[(size_t)g * N + n] ^ 0x8000u;
+      W[(size_t)k * N + n] = orc_hfma(q, scales[(size_t)g * N + n], z);
+    }
+  }
+}
+
+int orc_num_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}

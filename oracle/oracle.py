@@ -1,0 +1,305 @@
+"""numpy front end of oracle/liboracle.so (hq_oracle.c) and, when present, of
+the reference-built oracle/_ref/libref_cpu.so.  TEST INFRASTRUCTURE ONLY.
+
+fp16 tensors travel as numpy float16 arrays (viewed as uint16 for the C side).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+_lib = None
+_ref_cpu = None
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        p = HERE / "liboracle.so"
+        if not p.exists():
+            from . import build
+            build.build_oracle()
+        _lib = C.CDLL(str(p))
+        _lib.orc_num_threads.restype = C.c_int
+    return _lib
+
+
+def ref_cpu():
+    """The reference's own quantBnB CPU code (None if it was never built)."""
+    global _ref_cpu
+    if _ref_cpu is None:
+        p = HERE / "_ref" / "libref_cpu.so"
+        if not p.exists():
+            return None
+        _ref_cpu = C.CDLL(str(p))
+        _ref_cpu.ref_bnb_code_table.restype = C.POINTER(C.c_float)
+    return _ref_cpu
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def _c(a, dtype):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.float16 and dtype == np.uint16:
+        a = a.view(np.uint16)
+    assert a.dtype == dtype, (a.dtype, dtype)
+    return a
+
+
+# ---------------- q3 ----------------
+
+def q3_pack(codes: np.ndarray) -> np.ndarray:
+    """codes uint8[K][width] -> int32[K*3/32][width]."""
+    codes = _c(codes, np.uint8)
+    K, width = codes.shape
+    assert K % 32 == 0
+    mat = np.empty((K * 3 // 32, width), dtype=np.int32)
+    lib().orc_q3_pack(_ptr(codes), _ptr(mat), C.c_int(K), C.c_int(width))
+    return mat
+
+
+def q3_unpack(mat: np.ndarray) -> np.ndarray:
+    mat = _c(mat, np.int32)
+    height, width = mat.shape
+    codes = np.empty((height * 32 // 3, width), dtype=np.uint8)
+    lib().orc_q3_unpack(_ptr(mat), _ptr(codes), C.c_int(height), C.c_int(width))
+    return codes
+
+
+def q3_dequant_f32(mat, scales, zeros) -> np.ndarray:
+    mat, scales, zeros = _c(mat, np.int32), _c(scales, np.float32), _c(zeros, np.float32)
+    height, width = mat.shape
+    W = np.empty((height * 32 // 3, width), dtype=np.float32)
+    lib().orc_q3_dequant_f32(_ptr(mat), _ptr(scales), _ptr(zeros), _ptr(W), C.c_int(height),
+                             C.c_int(width))
+    return W
+
+
+def q3_dequant_f16(mat, scales, zeros) -> np.ndarray:
+    mat, scales, zeros = _c(mat, np.int32), _c(scales, np.float32), _c(zeros, np.float32)
+    height, width = mat.shape
+    W = np.empty((height * 32 // 3, width), dtype=np.uint16)
+    lib().orc_q3_dequant_f16(_ptr(mat), _ptr(scales), _ptr(zeros), _ptr(W), C.c_int(height),
+                             C.c_int(width))
+    return W.view(np.float16)
+
+
+def q3_gemv_f32(vec, mat, mul, scales, zeros) -> np.ndarray:
+    """Reference-order fp32 result; returns mul + product."""
+    vec, mat = _c(vec, np.float32), _c(mat, np.int32)
+    out = np.array(mul, dtype=np.float32, copy=True)
+    height, width = mat.shape
+    lib().orc_q3_gemv_f32(_ptr(vec), _ptr(mat), _ptr(out), _ptr(_c(scales, np.float32)),
+                          _ptr(_c(zeros, np.float32)), C.c_int(height), C.c_int(width))
+    return out
+
+
+def q3_gemv_f16in(vec_half, mat, mul, scales, zeros) -> np.ndarray:
+    vec, mat = _c(vec_half, np.uint16), _c(mat, np.int32)
+    out = np.array(mul, dtype=np.float32, copy=True)
+    height, width = mat.shape
+    lib().orc_q3_gemv_f16in(_ptr(vec), _ptr(mat), _ptr(out), _ptr(_c(scales, np.float32)),
+                            _ptr(_c(zeros, np.float32)), C.c_int(height), C.c_int(width))
+    return out
+
+
+def q3_gemv_f64(vec, mat, scales, zeros, f16rule: bool = False) -> np.ndarray:
+    vec = np.ascontiguousarray(np.asarray(vec, dtype=np.float32))
+    mat = _c(mat, np.int32)
+    height, width = mat.shape
+    out = np.empty(width, dtype=np.float64)
+    lib().orc_q3_gemv_f64(_ptr(vec), _ptr(mat), _ptr(out), _ptr(_c(scales, np.float32)),
+                          _ptr(_c(zeros, np.float32)), C.c_int(height), C.c_int(width),
+                          C.c_int(1 if f16rule else 0))
+    return out
+
+
+# ---------------- bnb ----------------
+
+def bnb_quantize(code, A) -> np.ndarray:
+    code, A = _c(code, np.float32), _c(A, np.float32)
+    assert code.size == 256
+    out = np.empty(A.size, dtype=np.uint8)
+    lib().orc_bnb_quantize(_ptr(code), _ptr(A), _ptr(out), C.c_size_t(A.size))
+    return out
+
+
+def ref_bnb_code_table():
+    r = ref_cpu()
+    if r is None:
+        return None
+    return np.ctypeslib.as_array(r.ref_bnb_code_table(), shape=(256,)).copy()
+
+
+def ref_bnb_quantize(A, threads: int = 0):
+    r = ref_cpu()
+    if r is None:
+        return None
+    A = _c(A, np.float32)
+    out = np.empty(A.size, dtype=np.uint8)
+    r.ref_bnb_quantize(_ptr(A), _ptr(out), C.c_size_t(A.size),
+                       C.c_int(threads or (os.cpu_count() or 1)))
+    return out
+
+
+# ---------------- nf4 ----------------
+
+def nf4_dequant_f16(B, absmax, lut16, n, blocksize=64, low_first=0) -> np.ndarray:
+    B, absmax, lut16 = _c(B, np.uint8), _c(absmax, np.float32), _c(lut16, np.float32)
+    out = np.empty(n, dtype=np.uint16)
+    lib().orc_nf4_dequant_f16(_ptr(B), _ptr(absmax), _ptr(lut16), _ptr(out), C.c_size_t(n),
+                              C.c_int(blocksize), C.c_int(low_first))
+    return out.view(np.float16)
+
+
+def nf4_gemv_f64(A, B, absmax, lut16, N, K, blocksize=64, low_first=0) -> np.ndarray:
+    A, B = _c(A, np.uint16), _c(B, np.uint8)
+    out = np.empty(N, dtype=np.float64)
+    lib().orc_nf4_gemv_f64(_ptr(A), _ptr(B), _ptr(_c(absmax, np.float32)),
+                           _ptr(_c(lut16, np.float32)), _ptr(out), C.c_int(N), C.c_int(K),
+                           C.c_int(blocksize), C.c_int(low_first))
+    return out
+
+
+def nf4_gemv_f32(A, B, absmax, lut16, N, K, blocksize=64, low_first=0) -> np.ndarray:
+    A, B = _c(A, np.uint16), _c(B, np.uint8)
+    out = np.empty(N, dtype=np.uint16)
+    lib().orc_nf4_gemv_f32(_ptr(A), _ptr(B), _ptr(_c(absmax, np.float32)),
+                           _ptr(_c(lut16, np.float32)), _ptr(out), C.c_int(N), C.c_int(K),
+                           C.c_int(blocksize), C.c_int(low_first))
+    return out.view(np.float16)
+
+
+# ---------------- lut-gemm ----------------
+
+def lutgemm_dequant_f32(bW, alpha, q_bias, M, K, nb, group_size) -> np.ndarray:
+    bW, alpha = _c(bW, np.uint32), _c(alpha, np.uint16)
+    qb = None if q_bias is None else _c(q_bias, np.uint16)
+    W = np.empty((K, M), dtype=np.float32)
+    lib().orc_lutgemm_dequant_f32(_ptr(bW), _ptr(alpha), _ptr(qb) if qb is not None else None,
+                                  _ptr(W), C.c_int(M), C.c_int(K), C.c_int(nb),
+                                  C.c_int(group_size))
+    return W
+
+
+def lutgemm_gemv_f64(x, bW, alpha, q_bias, M, K, nb, group_size) -> np.ndarray:
+    x, bW, alpha = _c(x, np.uint16), _c(bW, np.uint32), _c(alpha, np.uint16)
+    qb = None if q_bias is None else _c(q_bias, np.uint16)
+    out = np.empty(M, dtype=np.float64)
+    lib().orc_lutgemm_gemv_f64(_ptr(x), _ptr(bW), _ptr(alpha),
+                               _ptr(qb) if qb is not None else None, _ptr(out), C.c_int(M),
+                               C.c_int(K), C.c_int(nb), C.c_int(group_size))
+    return out
+
+
+def lutgemm_gemv_f32(x, bW, alpha, q_bias, M, K, nb, group_size) -> np.ndarray:
+    x, bW, alpha = _c(x, np.uint16), _c(bW, np.uint32), _c(alpha, np.uint16)
+    qb = None if q_bias is None else _c(q_bias, np.uint16)
+    out = np.empty(M, dtype=np.uint16)
+    lib().orc_lutgemm_gemv_f32(_ptr(x), _ptr(bW), _ptr(alpha),
+                               _ptr(qb) if qb is not None else None, _ptr(out), C.c_int(M),
+                               C.c_int(K), C.c_int(nb), C.c_int(group_size))
+    return out.view(np.float16)
+
+
+# ---------------- aqlm ----------------
+
+def _sizes(cb_sizes):
+    return (C.c_int * 4)(*[int(v) for v in cb_sizes])
+
+
+def aqlm_1x16_ref(codes, x, codebook, prob_m, prob_k, cb_sizes, cb_stride_int4, scales=None):
+    codes, x, codebook = _c(codes, np.uint16), _c(x, np.uint16), _c(codebook, np.uint16)
+    sc = None if scales is None else _c(scales, np.uint16)
+    out = np.empty(prob_m, dtype=np.uint16)
+    lib().orc_aqlm_1x16_ref(_ptr(codes), _ptr(x), _ptr(out), _ptr(codebook), C.c_int(prob_m),
+                            C.c_int(prob_k), _sizes(cb_sizes), C.c_int(cb_stride_int4),
+                            _ptr(sc) if sc is not None else None)
+    return out.view(np.float16)
+
+
+def aqlm_1x16_f64(codes, x, codebook, prob_m, prob_k, cb_sizes, cb_stride_int4, scales=None):
+    codes, x, codebook = _c(codes, np.uint16), _c(x, np.uint16), _c(codebook, np.uint16)
+    sc = None if scales is None else _c(scales, np.uint16)
+    out = np.empty(prob_m, dtype=np.float64)
+    lib().orc_aqlm_1x16_f64(_ptr(codes), _ptr(x), _ptr(out), _ptr(codebook), C.c_int(prob_m),
+                            C.c_int(prob_k), _sizes(cb_sizes), C.c_int(cb_stride_int4),
+                            _ptr(sc) if sc is not None else None)
+    return out
+
+
+def aqlm_1x16_f32(codes, x, codebook, prob_m, prob_k, cb_sizes, cb_stride_int4, scales=None):
+    codes, x, codebook = _c(codes, np.uint16), _c(x, np.uint16), _c(codebook, np.uint16)
+    sc = None if scales is None else _c(scales, np.uint16)
+    out = np.empty(prob_m, dtype=np.uint16)
+    lib().orc_aqlm_1x16_f32(_ptr(codes), _ptr(x), _ptr(out), _ptr(codebook), C.c_int(prob_m),
+                            C.c_int(prob_k), _sizes(cb_sizes), C.c_int(cb_stride_int4),
+                            _ptr(sc) if sc is not None else None)
+    return out.view(np.float16)
+
+
+def aqlm_2x8_f64(codes, x, codebooks, prob_m, prob_k, scales=None):
+    codes, x, codebooks = _c(codes, np.uint8), _c(x, np.uint16), _c(codebooks, np.uint16)
+    sc = None if scales is None else _c(scales, np.uint16)
+    out = np.empty(prob_m, dtype=np.float64)
+    lib().orc_aqlm_2x8_f64(_ptr(codes), _ptr(x), _ptr(out), _ptr(codebooks), C.c_int(prob_m),
+                           C.c_int(prob_k), _ptr(sc) if sc is not None else None)
+    return out
+
+
+# ---------------- batched ----------------
+
+def gemm_f16_f64(X, Wd_kn) -> np.ndarray:
+    """Y[Mb][N] = X[Mb][K] @ Wd[K][N], fp64 accumulation of fp16 operands."""
+    X, Wd = _c(X, np.uint16), _c(Wd_kn, np.uint16)
+    Mb, K = X.shape
+    K2, N = Wd.shape
+    assert K == K2
+    Y = np.empty((Mb, N), dtype=np.float64)
+    lib().orc_gemm_f16_f64(_ptr(X), _ptr(Wd), _ptr(Y), C.c_int(Mb), C.c_int(N), C.c_int(K))
+    return Y
+
+
+def gemm_f16_nk_f64(X, Wd_nk) -> np.ndarray:
+    X, Wd = _c(X, np.uint16), _c(Wd_nk, np.uint16)
+    Mb, K = X.shape
+    N, K2 = Wd.shape
+    assert K == K2
+    Y = np.empty((Mb, N), dtype=np.float64)
+    lib().orc_gemm_f16_nk_f64(_ptr(X), _ptr(Wd), _ptr(Y), C.c_int(Mb), C.c_int(N), C.c_int(K))
+    return Y
+
+
+def q3g_dequant_f16(mat, scales_h, zeros_h, K, N, group) -> np.ndarray:
+    mat = _c(mat, np.int32)
+    W = np.empty((K, N), dtype=np.uint16)
+    lib().orc_q3g_dequant_f16(_ptr(mat), _ptr(_c(scales_h, np.uint16)),
+                              _ptr(_c(zeros_h, np.uint16)), _ptr(W), C.c_int(K), C.c_int(N),
+                              C.c_int(group))
+    return W.view(np.float16)
+
+
+def rel_err(y, ref) -> float:
+    """max_i |y_i - ref_i| / max(|ref_i|, rms(ref)).
+
+    A dot product whose terms cancel has no bounded element-wise relative
+    error in any finite precision (the reference kernels included), so
+    outputs smaller than the vector's RMS are measured against the RMS."""
+    y = np.asarray(y, dtype=np.float64).ravel()
+    ref = np.asarray(ref, dtype=np.float64).ravel()
+    if ref.size == 0:
+        return 0.0
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    den = np.maximum(np.abs(ref), rms)
+    den[den == 0] = 1.0
+    return float(np.max(np.abs(y - ref) / den))

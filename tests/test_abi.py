@@ -1,0 +1,65 @@
+"""CPU checks of the drop-in boundary: libhq.so loads and exports exactly the
+symbols include/hq.h declares (no compute call is made without a GPU)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "hq.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_family():
+    names = declared_symbols()
+    for needed in ["hq_q3_gemv_f32", "hq_q3_gemv_f16in", "hq_bnb_quantize_u8",
+                   "hq_nf4_dequant_f16", "hq_nf4_gemv_f16", "hq_lutgemm_nqmv",
+                   "hq_aqlm_1x16_matvec", "hq_aqlm_2x8_matvec"]:
+        assert needed in names
+
+
+def test_library_exports_every_declared_symbol(hq):
+    lib = ctypes.CDLL(str(hq.lib_path()))
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} declared in hq.h but not exported"
+
+
+def test_python_binding_covers_every_declared_symbol(hq):
+    from hecbench_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+
+
+def test_version_and_status_strings(hq):
+    lib = hq.load_library()
+    assert lib.hq_version() >= 100
+    assert lib.hq_status_string(0) == b"ok"
+    assert lib.hq_status_string(-1) == b"bad shape"
+    assert lib.hq_lutgemm_workspace_bytes(12288) >= 12288 * 4 + 4
+    assert lib.hq_lutgemm_workspace_bytes(0) == 0
+
+
+def test_argument_errors_need_no_gpu(hq):
+    """Shape / null checks run before any CUDA call."""
+    lib = hq.load_library()
+    assert lib.hq_q3_gemv_f32(None, None, None, None, None, 24, 256, None) == -2
+    assert lib.hq_q3_gemv_f32(16, 16, 16, 16, 16, 25, 256, None) == -1
+    assert lib.hq_q3_gemv_f32(16, 16, 16, 16, 16, 24, 254, None) == -1
+    assert lib.hq_q3_gemv_f32(16, 8, 16, 16, 16, 24, 256, None) == -3
+    assert lib.hq_nf4_gemv_f16(16, 16, 16, 16, 16, 8, 100, 64, 0, None) == -1
+    assert lib.hq_nf4_dequant_f16(16, 16, 16, 16, 64, 48, 0, None) == -1
+    assert lib.hq_lutgemm_nqmv(16, 16, 16, 16, None, 256, 128, 3, 128, None, 0, None) == -5
+    assert lib.hq_lutgemm_nqmv(16, 16, 16, 16, None, 256, 128, 9, 128, 16, 1 << 20, None) == -1
+    assert lib.hq_aqlm_1x16_matvec(16, 16, 16, 16, 64, 100, (ctypes.c_int * 4)(64, 64, 64, 64),
+                                   0, None, None) == -1
+
+
+def test_python_layer_rejects_cpu_tensors(hq):
+    import torch
+    t = torch.zeros(256)
+    with pytest.raises(TypeError):
+        hq.vecquant3matmul(t, t.int(), t, t, t, 24, 256)

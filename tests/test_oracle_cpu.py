@@ -1,0 +1,218 @@
+"""CPU tests that pin the oracle: against the reference's own known-answer
+vector (quant3MatMul), against golden vectors produced by the reference's own
+CPU build (quantBnB), and against independent numpy restatements."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from hecbench_b200 import synth
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+# ---------- fp16 helpers ----------
+
+def test_half_conversion_matches_numpy(oracle):
+    import ctypes as C
+    rng = np.random.default_rng(1)
+    f = np.concatenate([
+        rng.standard_normal(20000).astype(np.float32) * 10,
+        rng.standard_normal(20000).astype(np.float32) * 1e-5,
+        np.array([0, -0.0, 65504, 65520, 65519.99, 1e-8, 6e-8, 5.96e-8, 2.98e-8, 2.9802322e-8,
+                  np.inf, -np.inf, 1e10, 6.1035156e-05, 6.1e-05], dtype=np.float32)])
+    out = np.empty(f.size, dtype=np.uint16)
+    oracle.lib().orc_f32_to_f16(f.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p),
+                                C.c_size_t(f.size))
+    assert np.array_equal(out, f.astype(np.float16).view(np.uint16))
+    allh = np.arange(65536, dtype=np.uint16)
+    back = np.empty(65536, dtype=np.float32)
+    oracle.lib().orc_f16_to_f32(allh.ctypes.data_as(C.c_void_p), back.ctypes.data_as(C.c_void_p),
+                                C.c_size_t(65536))
+    want = allh.view(np.float16).astype(np.float32)
+    assert np.array_equal(back.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)])
+
+
+# ---------- quant3MatMul ----------
+
+def test_q3_reference_known_answer(oracle):
+    """quant3MatMul-cuda/main.cu:28-53,84-105: all codes 1 (pattern p1, p1<<1,
+    p1<<2), vec 1, scale -1, zero 0 => every output is exactly -K; checked at a
+    reduced K (multiple of 256) and at the driver's own K = 49152 on a few
+    columns."""
+    p1 = 0b01001001001001001001001001001001
+    for K, width in [(1024, 256), (49152, 4)]:
+        height = K // 32 * 3
+        mat = np.empty((height, width), dtype=np.uint32)
+        mat[0::3] = p1
+        mat[1::3] = (p1 << 1) & 0xFFFFFFFF
+        mat[2::3] = (p1 << 2) & 0xFFFFFFFF
+        mat = mat.view(np.int32)
+        assert np.all(oracle.q3_unpack(mat) == 1)
+        vec = np.ones(K, dtype=np.float32)
+        sc = -np.ones(width, dtype=np.float32)
+        z = np.zeros(width, dtype=np.float32)
+        zero = np.zeros(width, dtype=np.float32)
+        assert np.all(oracle.q3_gemv_f32(vec, mat, zero, sc, z) == -float(K))
+        assert np.all(oracle.q3_gemv_f16in(vec.astype(np.float16), mat, zero, sc, z) == -float(K))
+        assert np.all(oracle.q3_gemv_f64(vec, mat, sc, z) == -float(K))
+
+
+def test_q3_pack_unpack_and_bit_order(oracle):
+    K, width = 256, 8
+    codes = synth.q3_case(K, width, seed=3)[1]
+    mat = oracle.q3_pack(codes)
+    assert np.array_equal(oracle.q3_unpack(mat), codes)
+    # independent restatement: 96-bit little-endian stream per (group, column)
+    m = mat.view(np.uint32).astype(object)
+    for r in range(K // 32):
+        for c in range(width):
+            B = int(m[3 * r, c]) | (int(m[3 * r + 1, c]) << 32) | (int(m[3 * r + 2, c]) << 64)
+            got = [(B >> (3 * j)) & 7 for j in range(32)]
+            assert got == list(codes[32 * r:32 * r + 32, c])
+    # the extraction of the fp16 kernel: 6 bits at a time, low 3 bits = even k
+    for r in range(K // 32):
+        B = int(m[3 * r, 0]) | (int(m[3 * r + 1, 0]) << 32) | (int(m[3 * r + 2, 0]) << 64)
+        for i in range(16):
+            pair = (B >> (6 * i)) & 63
+            assert pair & 7 == codes[32 * r + 2 * i, 0] and pair >> 3 == codes[32 * r + 2 * i + 1, 0]
+
+
+def test_q3_dequant_rules(oracle):
+    vec, codes, sc, z = synth.q3_case(64, 16, seed=4)
+    mat = oracle.q3_pack(codes)
+    W = oracle.q3_dequant_f32(mat, sc, z)
+    want = (sc.astype(np.float64) * codes - z.astype(np.float64)).astype(np.float32)  # one rounding
+    assert np.array_equal(W, want)
+    W16 = oracle.q3_dequant_f16(mat, sc, z)
+    s16 = sc.astype(np.float16).astype(np.float64)
+    z16 = (-z).astype(np.float16).astype(np.float64)
+    want16 = (codes * s16 + z16).astype(np.float16)
+    assert np.array_equal(W16.view(np.uint16), want16.view(np.uint16))
+
+
+def test_q3_gemv_orders_agree_with_fp64(oracle):
+    vec, codes, sc, z = synth.q3_case(1024, 64, seed=5)
+    mat = oracle.q3_pack(codes)
+    zero = np.zeros(64, dtype=np.float32)
+    y64 = oracle.q3_gemv_f64(vec, mat, sc, z)
+    assert oracle.rel_err(oracle.q3_gemv_f32(vec, mat, zero, sc, z), y64) < 1e-5
+    dense = oracle.q3_dequant_f32(mat, sc, z).astype(np.float64).T @ vec.astype(np.float64)
+    assert np.allclose(dense, y64, rtol=1e-12, atol=1e-12)
+    vh = vec.astype(np.float16)
+    y64h = oracle.q3_gemv_f64(vh.astype(np.float32), mat, sc, z, f16rule=True)
+    assert oracle.rel_err(oracle.q3_gemv_f16in(vh, mat, zero, sc, z), y64h) < 1e-2
+    # accumulation into mul
+    base = np.full(64, 3.0, dtype=np.float32)
+    assert np.allclose(oracle.q3_gemv_f32(vec, mat, base, sc, z),
+                       oracle.q3_gemv_f32(vec, mat, zero, sc, z) + 3.0, rtol=1e-6, atol=1e-6)
+
+
+# ---------- quantBnB ----------
+
+def test_bnb_oracle_matches_reference_golden(oracle):
+    g = np.load(GOLDEN / "bnb_golden.npz")
+    assert np.array_equal(oracle.bnb_quantize(g["code"], g["A"]), g["out"])
+
+
+def test_bnb_table_properties_and_nearest_neighbour(oracle):
+    g = np.load(GOLDEN / "bnb_golden.npz")
+    code = g["code"]
+    assert code.size == 256 and np.all(np.diff(code) > 0) and code[127] == 0.0 and code[255] == 1.0
+    rng = np.random.default_rng(7)
+    x = rng.uniform(-1.2, 1.2, 50000).astype(np.float32)
+    q = oracle.bnb_quantize(code, x)
+    # away from exact ties the selected entry is the nearest table entry
+    d = np.abs(x[:, None].astype(np.float64) - code[None, :].astype(np.float64))
+    nearest = d.argmin(axis=1)
+    best = d.min(axis=1)
+    second = np.partition(d, 1, axis=1)[:, 1]
+    clear = (second - best) > 1e-6
+    assert np.array_equal(q[clear], nearest[clear].astype(np.uint8))
+
+
+def test_bnb_reference_build_when_present(oracle):
+    if oracle.ref_cpu() is None:
+        pytest.skip("reference CPU build not present")
+    g = np.load(GOLDEN / "bnb_golden.npz")
+    assert np.array_equal(oracle.ref_bnb_code_table(), g["code"])
+    x = np.random.default_rng(9).standard_normal(200000).astype(np.float32)
+    assert np.array_equal(oracle.ref_bnb_quantize(x), oracle.bnb_quantize(g["code"], x))
+
+
+# ---------- NF4 (parity unpinned: checked against an independent numpy restatement) ----------
+
+@pytest.mark.parametrize("low_first", [0, 1])
+def test_nf4_dequant_and_gemv(oracle, low_first):
+    N, K, bs = 12, 256, 64
+    A, B, absmax, lut = synth.nf4_case(N, K, bs, seed=6)
+    hi, lo = B >> 4, B & 15
+    codes = np.stack([lo, hi] if low_first else [hi, lo], axis=1).reshape(-1)
+    w32 = (lut[codes] * np.repeat(absmax, bs)[:codes.size]).astype(np.float32)
+    deq = oracle.nf4_dequant_f16(B, absmax, lut, N * K, bs, low_first)
+    assert np.array_equal(deq.view(np.uint16), w32.astype(np.float16).view(np.uint16))
+    y = oracle.nf4_gemv_f64(A, B, absmax, lut, N, K, bs, low_first)
+    want = w32.reshape(N, K).astype(np.float64) @ A.astype(np.float64)
+    assert np.allclose(y, want, rtol=1e-12, atol=1e-12)
+    y32 = oracle.nf4_gemv_f32(A, B, absmax, lut, N, K, bs, low_first)
+    assert oracle.rel_err(y32.astype(np.float64), y) < 2e-3
+
+
+# ---------- LUT-GEMM ----------
+
+@pytest.mark.parametrize("bias", [True, False])
+def test_lutgemm_oracle(oracle, bias):
+    M, K, nb, gs = 32, 256, 3, 128
+    x, bW, alpha, qb = synth.lutgemm_case(M, K, nb, gs, seed=8, bias=bias)
+    W = oracle.lutgemm_dequant_f32(bW, alpha, qb, M, K, nb, gs)
+    # independent restatement (lut-gemm-cuda/main.cu:118-146 with the [K][M] layout)
+    bits = ((bW[:, :, None, :] >> np.arange(32, dtype=np.uint32)[None, None, :, None]) & 1)
+    signs = (2.0 * bits - 1.0).transpose(0, 2, 1, 3).reshape(K, nb, M)
+    a = np.repeat(alpha.astype(np.float64), gs, axis=0)
+    want = (signs * a).sum(axis=1)
+    if bias:
+        want = want + np.repeat(qb.astype(np.float64), gs, axis=0)
+    assert np.allclose(W, want, rtol=1e-6, atol=1e-7)
+    y = oracle.lutgemm_gemv_f64(x, bW, alpha, qb, M, K, nb, gs)
+    assert np.allclose(y, want.T @ x.astype(np.float64), rtol=1e-10, atol=1e-10)
+    y32 = oracle.lutgemm_gemv_f32(x, bW, alpha, qb, M, K, nb, gs)
+    assert oracle.rel_err(y32.astype(np.float64), y) < 2e-3
+
+
+# ---------- AQLM ----------
+
+def test_aqlm_1x16_oracle(oracle):
+    m, k = 24, 512
+    codes, x, cb, scales = synth.aqlm_1x16_case(m, k, n_codebooks=3, seed=9)
+    sizes = [8, 16, 24, 1 << 30]
+    stride = 65536 * 8 * 2 // 16
+    y64 = oracle.aqlm_1x16_f64(codes, x, cb, m, k, sizes, stride)
+    want = np.empty(m)
+    for r in range(m):
+        book = cb[r // 8].astype(np.float64)
+        want[r] = (book[codes[r]].reshape(-1) * x.astype(np.float64)).sum()
+    assert np.allclose(y64, want, rtol=1e-12, atol=1e-12)
+    yref = oracle.aqlm_1x16_ref(codes, x, cb, m, k, sizes, stride)
+    assert oracle.rel_err(yref.astype(np.float64), y64) < 1e-2
+    ys = oracle.aqlm_1x16_f64(codes, x, cb, m, k, sizes, stride, scales)
+    assert np.allclose(ys, want * scales.astype(np.float64), rtol=1e-12)
+
+
+def test_aqlm_2x8_oracle(oracle):
+    m, k = 16, 256
+    codes, x, cbs, scales = synth.aqlm_2x8_case(m, k, seed=10)
+    y = oracle.aqlm_2x8_f64(codes, x, cbs, m, k, scales)
+    w = cbs[0].astype(np.float64)[codes[:, :, 0]] + cbs[1].astype(np.float64)[codes[:, :, 1]]
+    want = (w.reshape(m, k) @ x.astype(np.float64)) * scales.astype(np.float64)
+    assert np.allclose(y, want, rtol=1e-12, atol=1e-12)
+
+
+# ---------- batched ----------
+
+def test_gemm_oracles(oracle):
+    rng = np.random.default_rng(11)
+    X = rng.standard_normal((5, 96)).astype(np.float16)
+    W = rng.standard_normal((96, 40)).astype(np.float16)
+    assert np.allclose(oracle.gemm_f16_f64(X, W), X.astype(np.float64) @ W.astype(np.float64))
+    assert np.allclose(oracle.gemm_f16_nk_f64(X, np.ascontiguousarray(W.T)),
+                       X.astype(np.float64) @ W.astype(np.float64))
