@@ -1,0 +1,501 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized mat-vec hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one pass of the workload's kernel over R independent packed
+weight replicas (R layers of a decoder, back to back, as one CUDA graph); R is
+chosen so that R x bytes is several times the 126 MB L2, so every launch
+streams its weights from HBM.  Rank 0 prints ONE JSON line:
+
+  value      effective weight GB/s over all ranks = algorithmic bytes / time,
+             inputs resident in HBM, CUDA-event timed, max over ranks
+  e2e        same metric through the C ABI with HOST activations: every launch
+             copies its input vector from pinned host memory and its output
+             back (weights are model state and stay resident)
+  roofline   achieved GB/s of the kernel (algorithmic bytes per launch / mean
+             launch duration inside the timed region) against the measured HBM
+             copy bandwidth of MEASURED_PEAKS.json
+  cpu_baseline  the CPU oracle port of the same workload timed on a bounded
+             sample on this box's host cores (rank 0, N = 1 only)
+
+`--impl reference` times the reference algorithm's CPU implementation (the
+reference's own build for kQuantize, the oracle port otherwise) on the same
+workload with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def ncu_traffic(workload: str):
+    """DRAM bytes per launch from the committed ncu summary, or None."""
+    p = ROOT / "profiles" / "traffic.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text()).get(workload, {}).get("dram_bytes_per_launch")
+        except Exception:
+            return None
+    return None
+
+
+# --------------------------------------------------------------------------
+# workloads: name -> builder(seed) returning a dict of host arrays + metadata
+# --------------------------------------------------------------------------
+
+def _host_case(name: str, seed: int):
+    from hecbench_b200 import synth
+    if name == "nf4_gemv":
+        N, K, bs = 11008, 4096, 64
+        A, B, absmax, lut = synth.nf4_case(N, K, bs, seed)
+        return dict(N=N, K=K, bs=bs, A=A, B=B, absmax=absmax, lut=lut,
+                    bytes=B.nbytes + absmax.nbytes + K * 2 + N * 2 + 64,
+                    desc="NF4 blockwise 4-bit GEMV 11008x4096, blocksize 64, fp16 in/out")
+    if name == "nf4_dequant":
+        N, K, bs = 11008, 4096, 64
+        A, B, absmax, lut = synth.nf4_case(N, K, bs, seed)
+        return dict(N=N, K=K, bs=bs, B=B, absmax=absmax, lut=lut,
+                    bytes=B.nbytes + absmax.nbytes + N * K * 2,
+                    desc="NF4 blockwise dequantize 11008x4096 -> fp16")
+    if name in ("q3_gemv_f32", "q3_gemv_f16"):
+        K, W = (4096, 4096)
+        if os.environ.get("HQ_BENCH_Q3_SHAPE") == "opt175b":
+            K, W = 49152, 12288
+        vec, codes, sc, z = synth.q3_case(K, W, seed)
+        return dict(K=K, W=W, vec=vec, codes=codes, sc=sc, z=z,
+                    bytes=K * 3 // 32 * W * 4 + 3 * 4 * W + 4 * K,
+                    desc=f"GPTQ 3-bit GEMV {K}x{W}")
+    if name == "bnb_quantize":
+        n = 1 << 24
+        A = np.random.Generator(np.random.PCG64([seed, 50])).standard_normal(n).astype(np.float32)
+        return dict(n=n, A=A, bytes=n * 5, desc="bitsandbytes 8-bit kQuantize, 16777216 fp32")
+    if name == "lutgemm":
+        M = K = 12288
+        x, bW, alpha, qb = synth.lutgemm_case(M, K, 3, 128, seed)
+        return dict(M=M, K=K, x=x, bW=bW, alpha=alpha, qb=qb,
+                    bytes=bW.nbytes + alpha.nbytes + qb.nbytes + 2 * K + 2 * M,
+                    desc="LUT-GEMM nqmv 12288x12288, 3 bit planes, group 128")
+    if name == "aqlm_1x16":
+        m = k = 4096
+        codes, x, cb, scales = synth.aqlm_1x16_case(m, k, 1, seed)
+        return dict(m=m, k=k, codes=codes, x=x, cb=cb, scales=scales,
+                    bytes=codes.nbytes + cb.nbytes + 3 * 8192,
+                    desc="AQLM 1x16 mat-vec 4096x4096 (packed bytes; 16-byte gathers go through L2)")
+    if name == "aqlm_2x8":
+        m = k = 4096
+        codes, x, cbs, scales = synth.aqlm_2x8_case(m, k, seed)
+        return dict(m=m, k=k, codes=codes, x=x, cbs=cbs, scales=scales,
+                    bytes=codes.nbytes + 4 * 8192, desc="AQLM 2x8 mat-vec 4096x4096")
+    raise SystemExit(f"unknown workload {name}")
+
+
+WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "bnb_quantize", "lutgemm",
+             "aqlm_1x16", "aqlm_2x8"]
+DTYPE = {"nf4_gemv": "f16", "nf4_dequant": "f16", "q3_gemv_f32": "f32", "q3_gemv_f16": "f16",
+         "bnb_quantize": "u8", "lutgemm": "f16", "aqlm_1x16": "f16", "aqlm_2x8": "f16"}
+
+
+class DeviceWorkload:
+    """R replicas of one workload on one GPU, launched through the C ABI."""
+
+    def __init__(self, name: str, dev, seed: int, target_bytes: float):
+        import torch
+        import hecbench_b200 as hq
+        self.hq, self.torch, self.name, self.dev = hq, torch, name, dev
+        c = _host_case(name, seed)
+        self.case = c
+        self.bytes = int(c["bytes"])
+        self.R = max(2, int(np.ceil(target_bytes / self.bytes)))
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(
+            a.view(np.int32) if a.dtype == np.uint32 else a)).to(dev)
+        R = self.R
+        rot = lambda a, i: np.roll(a.reshape(-1), 4099 * i).reshape(a.shape) if i else a
+        if name in ("nf4_gemv", "nf4_dequant"):
+            self.B = [t(rot(c["B"], i)) for i in range(R)]
+            self.absmax = [t(rot(c["absmax"], i)) for i in range(R)]
+            self.lut = t(c["lut"])
+            if name == "nf4_gemv":
+                self.x = [t(c["A"]) for _ in range(R)]
+                self.out = [torch.empty(c["N"], dtype=torch.float16, device=dev) for _ in range(R)]
+            else:
+                self.W = torch.empty(c["N"] * c["K"], dtype=torch.float16, device=dev)
+        elif name.startswith("q3_gemv"):
+            from hecbench_b200 import synth
+            mat = synth.q3_pack(c["codes"])
+            self.height = mat.shape[0]
+            self.mat = [t(rot(mat, i)) for i in range(R)]
+            self.sc, self.z = t(c["sc"]), t(c["z"])
+            v = c["vec"] if name == "q3_gemv_f32" else c["vec"].astype(np.float16)
+            self.x = [t(v) for _ in range(R)]
+            self.out = [torch.zeros(c["W"], dtype=torch.float32, device=dev) for _ in range(R)]
+        elif name == "bnb_quantize":
+            g = np.load(ROOT / "tests" / "golden" / "bnb_golden.npz")
+            self.code = t(g["code"])
+            self.A = [t(rot(c["A"], i)) for i in range(R)]
+            self.outq = torch.empty(c["n"], dtype=torch.uint8, device=dev)
+        elif name == "lutgemm":
+            self.w = [hq.nQWeight_fp16(rot(c["bW"], i), c["alpha"].astype(np.float32), c["K"],
+                                       c["M"], 3, False, c["K"] // 128,
+                                       c["qb"].astype(np.float32), device=dev) for i in range(R)]
+            self.x = [t(c["x"]) for _ in range(R)]
+            self.out = [torch.empty(c["M"], dtype=torch.float16, device=dev) for _ in range(R)]
+        elif name == "aqlm_1x16":
+            self.codes = [t(rot(c["codes"], i).view(np.int16)) for i in range(R)]
+            self.cb = t(c["cb"])
+            self.x = [t(c["x"]) for _ in range(R)]
+            self.out = [torch.empty(c["m"], dtype=torch.float16, device=dev) for _ in range(R)]
+        elif name == "aqlm_2x8":
+            self.codes = [t(rot(c["codes"], i)) for i in range(R)]
+            self.cbs = t(c["cbs"])
+            self.x = [t(c["x"]) for _ in range(R)]
+            self.out = [torch.empty(c["m"], dtype=torch.float16, device=dev) for _ in range(R)]
+
+    def launch(self, i: int):
+        hq, c, n = self.hq, self.case, self.name
+        if n == "nf4_gemv":
+            hq.gemv_nf4(self.x[i], self.B[i], self.absmax[i], self.lut, c["N"], c["K"], c["bs"], 0,
+                        self.out[i])
+        elif n == "nf4_dequant":
+            hq.dequantize_nf4(self.B[i], self.absmax[i], self.lut, c["N"] * c["K"], c["bs"], 0,
+                              self.W)
+        elif n == "q3_gemv_f32":
+            hq.vecquant3matmul(self.x[i], self.mat[i], self.out[i], self.sc, self.z, self.height,
+                               c["W"])
+        elif n == "q3_gemv_f16":
+            hq.vecquant3matmul_faster(self.x[i], self.mat[i], self.out[i], self.sc, self.z,
+                                      self.height, c["W"])
+        elif n == "bnb_quantize":
+            hq.kQuantize(self.code, self.A[i], self.outq, c["n"])
+        elif n == "lutgemm":
+            hq.matmul(self.out[i], self.x[i], self.w[i])
+        elif n == "aqlm_1x16":
+            m = c["m"]
+            hq.code1x16_matvec(self.codes[i], self.x[i], self.out[i], self.cb, m, c["k"],
+                               [m, m, m, 1 << 30], 65536)
+        elif n == "aqlm_2x8":
+            hq.code2x8_matvec(self.codes[i], self.x[i], self.out[i], self.cbs, c["m"], c["k"])
+
+    # host <-> device traffic of one launch on the end-to-end path
+    def host_io(self):
+        """(pinned host input, device input list, device output list) or None."""
+        torch = self.torch
+        if not hasattr(self, "x") or not hasattr(self, "out"):
+            return None
+        hin = [torch.empty_like(self.x[i], device="cpu").pin_memory().copy_(self.x[i])
+               for i in range(self.R)]
+        hout = [torch.empty_like(self.out[i], device="cpu").pin_memory() for i in range(self.R)]
+        return hin, hout
+
+    def check_one(self):
+        """One replica against the CPU oracle (cheap sanity guard before timing)."""
+        from oracle import oracle as O
+        c = self.case
+        if self.name != "nf4_gemv":
+            return None
+        self.launch(0)
+        self.torch.cuda.synchronize()
+        y = self.out[0].cpu().numpy().astype(np.float64)
+        rows = 512
+        ref = O.nf4_gemv_f64(c["A"], c["B"][:rows * c["K"] // 2], c["absmax"], c["lut"], rows,
+                             c["K"], c["bs"], 0)
+        return O.rel_err(y[:rows], ref)
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([f.strip() for f in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+                for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                    "sw_power_cap"], r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_baseline(name: str, budget_s: float = 12.0):
+    """Oracle port (or the reference's own CPU build for kQuantize) on a bounded
+    sample of the workload, all host threads."""
+    from oracle import oracle as O
+    c = _host_case(name, 0)
+    threads = O.num_threads()
+    kind = "port"
+    if name == "nf4_gemv":
+        rows = c["N"]
+        fn = lambda: O.nf4_gemv_f32(c["A"], c["B"], c["absmax"], c["lut"], rows, c["K"], c["bs"], 0)
+        sample = f"full {c['N']}x{c['K']} GEMV, fp32 accumulate"
+    elif name == "nf4_dequant":
+        fn = lambda: O.nf4_dequant_f16(c["B"], c["absmax"], c["lut"], c["N"] * c["K"], c["bs"], 0)
+        sample = "full dequantize"
+    elif name.startswith("q3_gemv"):
+        mat = O.q3_pack(c["codes"])
+        zero = np.zeros(c["W"], dtype=np.float32)
+        fn = lambda: O.q3_gemv_f32(c["vec"], mat, zero, c["sc"], c["z"])
+        sample = "full GEMV, reference fp32 order"
+    elif name == "bnb_quantize":
+        g = np.load(ROOT / "tests" / "golden" / "bnb_golden.npz")
+        if O.ref_cpu() is not None:
+            kind = "reference"
+            threads = os.cpu_count() or 1
+            fn = lambda: O.ref_bnb_quantize(c["A"])
+        else:
+            fn = lambda: O.bnb_quantize(g["code"], c["A"])
+        sample = "full 16777216 elements"
+    elif name == "lutgemm":
+        cols = 1536
+        bW = np.ascontiguousarray(c["bW"][:, :, :cols])
+        al = np.ascontiguousarray(c["alpha"][:, :, :cols])
+        qb = np.ascontiguousarray(c["qb"][:, :cols])
+        fn = lambda: O.lutgemm_gemv_f32(c["x"], bW, al, qb, cols, c["K"], 3, 128)
+        sample = f"{cols} of {c['M']} output columns"
+        c = dict(c, bytes=c["bytes"] * cols / c["M"])
+    elif name == "aqlm_1x16":
+        m = c["m"]
+        fn = lambda: O.aqlm_1x16_f32(c["codes"], c["x"], c["cb"], m, c["k"], [m, m, m, 1 << 30],
+                                     65536)
+        sample = "full mat-vec"
+    else:
+        m = c["m"]
+        fn = lambda: O.aqlm_2x8_f64(c["codes"], c["x"], c["cbs"], m, c["k"])
+        sample = "full mat-vec (fp64 oracle)"
+    fn()
+    t0 = time.perf_counter(); reps = 0
+    while True:
+        fn(); reps += 1
+        el = time.perf_counter() - t0
+        if el > budget_s or reps >= 200:
+            break
+    per = el / reps
+    return {"value": c["bytes"] / per / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": f"{sample}; {reps} repetitions in {el:.1f} s", "us_per_call": per * 1e6}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    name = args.workload
+    c = _host_case(name, 0)
+    # each step = one bounded CPU sample (a few repetitions of the workload)
+    per_step_budget = max(0.5, min(6.0, 60.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_baseline(name, budget_s=per_step_budget / 4)
+    vals, t0 = [], time.perf_counter()
+    last = None
+    for _ in range(args.steps):
+        last = cpu_baseline(name, budget_s=per_step_budget)
+        vals.append(last["value"])
+    el = time.perf_counter() - t0
+    v = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": "effective_weight_bandwidth", "value": v, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": el / max(1, args.steps) * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
+        "config": {"workload": c["desc"], "host_threads": last["cores"]},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": last["cores"], "kind": last["kind"],
+                         "sample": last["sample"]},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="nf4_gemv", choices=WORKLOADS)
+    ap.add_argument("--replica-bytes", type=float, default=640e6,
+                    help="bytes of packed weights resident per GPU (>> L2)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly (for profilers)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    import hecbench_b200 as hq
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU: there is no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    hq.load_library()
+
+    wl = DeviceWorkload(args.workload, dev, seed=rank, target_bytes=args.replica_bytes)
+    R = wl.R
+    err = wl.check_one()
+    if err is not None and err > 1e-2:
+        raise SystemExit(f"parity guard failed before timing: rel err {err}")
+
+    stream = torch.cuda.Stream()
+    graph = None
+    with torch.cuda.stream(stream):
+        for i in range(R):
+            wl.launch(i)
+        stream.synchronize()
+        if not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(R):
+                    wl.launch(i)
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(R):
+                wl.launch(i)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            step()
+        barrier()
+        if sampler:
+            sampler.start()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+
+    launches = R * args.steps
+    us_per_launch = ms * 1e3 / launches
+    total_bytes = wl.bytes * launches * world
+    value = total_bytes / (ms * 1e-3) / 1e9
+
+    # ---- end to end: host activations in, host results out, every launch ----
+    e2e = None
+    io = wl.host_io()
+    if io is not None:
+        hin, hout = io
+        with torch.cuda.stream(stream):
+            def e2e_step():
+                for i in range(R):
+                    wl.x[i].copy_(hin[i], non_blocking=True)
+                    wl.launch(i)
+                    hout[i].copy_(wl.out[i], non_blocking=True)
+            for _ in range(3):
+                e2e_step()
+            barrier()
+            a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(args.steps):
+                e2e_step()
+            b.record(stream)
+            barrier()
+            ems = a.elapsed_time(b)
+        if world > 1:
+            tt = torch.tensor([ems], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ems = float(tt.item())
+        e2e = {"value": total_bytes / (ems * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hin)),
+               "d2h_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hout)),
+               "us_per_call": ems * 1e3 / launches}
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        achieved = wl.bytes / (us_per_launch * 1e-6) / 1e9
+        line = {
+            "metric": "effective_weight_bandwidth", "value": value, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": DTYPE[args.workload], "data": "synthetic",
+            "config": {"workload": wl.case["desc"], "replicas_per_gpu": R,
+                       "resident_weight_bytes_per_gpu": wl.bytes * R,
+                       "l2": "inputs larger than L2 (replicas rotate, R x bytes >> 126 MB)",
+                       "algorithmic_bytes_per_launch": wl.bytes,
+                       "launch": "cuda graph of R launches" if graph is not None else "eager",
+                       "parallelism": f"{world} x independent row shards"},
+            "us_per_gemv": us_per_launch,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": f"of {peak_src}",
+                         "traffic": ncu_traffic(args.workload)},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cb = cpu_baseline(args.workload)
+            line["cpu_baseline"] = cb
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

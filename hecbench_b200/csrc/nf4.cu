@@ -8,128 +8,272 @@
 //   gemv    : out[n] = half_rn(sum_k A[k] * lut16[code[n][k]] * absmax[...])
 //
 // GEMV design (HBM-bound, 0.5 B of codes + 1/16 B of absmax per weight):
-//  * a warp owns two rows at a time; a lane reads 16 bytes (32 codes) per row
-//    per step, so the warp streams 512 contiguous bytes of each row;
+//  * one persistent CTA of 1024 threads per SM; rows are dealt round-robin to
+//    CTAs and, inside a CTA, to groups of S warps; warp q of a group owns the
+//    K slice [q*1024*C, (q+1)*1024*C) of every row of its group, a lane reads
+//    16 bytes (32 codes) per chunk, so a warp streams 512 contiguous bytes;
+//  * packed codes and their absmax are staged through shared memory with
+//    per-lane asynchronous copies (cp.async), kStages rows deep: 128 KiB of
+//    weights are in flight per SM without holding a single register, which is
+//    what it takes to cover HBM latency at full bandwidth; each lane reads back
+//    only the slots it filled itself, so no barrier guards the ring; the first
+//    kStages rows are requested before the lookup table is built;
+//  * the lane's slice of the input vector never changes, so it lives in
+//    registers for the whole kernel;
 //  * one byte = two codes = one shared-memory lookup into a 256-entry half2
 //    table (lut[first code], lut[second code]); the table is stored once per
-//    bank (lut2[byte][lane], 32 KiB) so the 32 random lookups of a warp never
-//    conflict; the byte is turned into a shared-memory offset with one shift
-//    and one logic op;
+//    bank with a 256-byte row per byte value (row b: 32 lane copies in its
+//    first 128 bytes), so the 32 random lookups of a warp never conflict and
+//    the table offset (b << 8) | lane*4 is ONE byte-permute of the packed word
+//    and the lane offset - no shift, no mask;
 //  * products are summed in half2 over the 32 weights of a chunk (two
 //    accumulators of 8 fused multiply-adds), then scaled by the chunk's fp32
-//    absmax and accumulated in fp32; the input chunk is read from shared
-//    memory once for both rows;
-//  * a warp-shuffle tree combines the lanes, lane 0 stores the fp16 result.
+//    absmax in fp32;
+//  * per-lane partial sums of a row go to shared memory (into the unused second
+//    128 bytes of the table rows); after kRound rows the
+//    S warps of the group meet at a named barrier and each finishes some of
+//    the rows (sum over the slices, warp-shuffle tree, one fp16 store).
+#include <algorithm>
+
 #include "hq_common.cuh"
 
 namespace hq {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
-constexpr int kRows = 2;  // rows per warp step
+constexpr int kThreads = 256;        // dequant kernel
+constexpr int kGemvThreads = 1024;   // GEMV: one persistent CTA per SM
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kStageChunks = 8;      // 16-byte chunks in flight per lane (shared-memory ring)
+constexpr int kRound = 4;            // rows between two group barriers
+
+constexpr int kLutBytes = 256 * 256;  // table rows interleaved with the partial-sum slots
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool pred) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %2, 0;\n"
+      " @p cp.async.cg.shared.global [%0], [%1], 16;\n}\n" ::"r"(dst), "l"(src), "r"((int)pred)
+      : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, bool pred) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %2, 0;\n"
+      " @p cp.async.ca.shared.global [%0], [%1], 4;\n}\n" ::"r"(dst), "l"(src), "r"((int)pred)
+      : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 // sum of the 32 products of one 16-byte chunk against 16 half2 inputs
-__device__ __forceinline__ float chunk_dot(const uint4& codes, const uint32_t (&x2)[16],
-                                           const unsigned char* lut_lane) {
+__device__ __forceinline__ float chunk_dot(const uint4& codes, const uint4 (&xp)[4],
+                                           const unsigned char* lut, uint32_t lane4) {
   const uint32_t w[4] = {codes.x, codes.y, codes.z, codes.w};
   __half2 a0 = __float2half2_rn(0.f), a1 = a0;
 #pragma unroll
   for (int i = 0; i < 4; i++) {
-    // byte b of the word -> offset (byte << 7) into lut2[byte][lane] (4-byte entries)
-    const uint32_t o0 = (w[i] << 7) & 0x7f80u;
-    const uint32_t o1 = (w[i] >> 1) & 0x7f80u;
-    const uint32_t o2 = (w[i] >> 9) & 0x7f80u;
-    const uint32_t o3 = (w[i] >> 17) & 0x7f80u;
-    const uint32_t l0 = *reinterpret_cast<const uint32_t*>(lut_lane + o0);
-    const uint32_t l1 = *reinterpret_cast<const uint32_t*>(lut_lane + o1);
-    const uint32_t l2 = *reinterpret_cast<const uint32_t*>(lut_lane + o2);
-    const uint32_t l3 = *reinterpret_cast<const uint32_t*>(lut_lane + o3);
-    a0 = __hfma2(u32_as_half2(l0), u32_as_half2(x2[4 * i + 0]), a0);
-    a1 = __hfma2(u32_as_half2(l1), u32_as_half2(x2[4 * i + 1]), a1);
-    a0 = __hfma2(u32_as_half2(l2), u32_as_half2(x2[4 * i + 2]), a0);
-    a1 = __hfma2(u32_as_half2(l3), u32_as_half2(x2[4 * i + 3]), a1);
+    const uint32_t xw[4] = {xp[i].x, xp[i].y, xp[i].z, xp[i].w};
+    // byte k of the word -> (byte << 8) | lane*4: bytes {lane4.0, w.k, 0, 0}
+    const uint32_t o0 = __byte_perm(w[i], lane4, 0x7604);
+    const uint32_t o1 = __byte_perm(w[i], lane4, 0x7614);
+    const uint32_t o2 = __byte_perm(w[i], lane4, 0x7624);
+    const uint32_t o3 = __byte_perm(w[i], lane4, 0x7634);
+    const uint32_t l0 = *reinterpret_cast<const uint32_t*>(lut + o0);
+    const uint32_t l1 = *reinterpret_cast<const uint32_t*>(lut + o1);
+    const uint32_t l2 = *reinterpret_cast<const uint32_t*>(lut + o2);
+    const uint32_t l3 = *reinterpret_cast<const uint32_t*>(lut + o3);
+    a0 = __hfma2(u32_as_half2(l0), u32_as_half2(xw[0]), a0);
+    a1 = __hfma2(u32_as_half2(l1), u32_as_half2(xw[1]), a1);
+    a0 = __hfma2(u32_as_half2(l2), u32_as_half2(xw[2]), a0);
+    a1 = __hfma2(u32_as_half2(l3), u32_as_half2(xw[3]), a1);
   }
-  const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
-  return (f0.x + f0.y) + (f1.x + f1.y);
+  const float2 f = __half22float2(__hadd2(a0, a1));
+  return f.x + f.y;
 }
 
-__global__ void __launch_bounds__(kThreads)
-nf4_gemv_kernel(const __half* __restrict__ A, const uint8_t* __restrict__ B,
-                const float* __restrict__ absmax, const float* __restrict__ lut16,
-                __half* __restrict__ out, int N, int K, int chunks_per_block, int low_first) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  uint32_t* lut2 = reinterpret_cast<uint32_t*>(smem);             // [256][32]
-  uint4* xs = reinterpret_cast<uint4*>(smem + 256 * 32 * 4);       // K halves
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+__device__ __forceinline__ void group_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
-  {
-    // thread t builds entry t (byte value t) and writes its 32 copies
-    const int hi = tid >> 4, lo = tid & 15;
-    const int first = low_first ? lo : hi, second = low_first ? hi : lo;
-    const __half2 v = __floats2half2_rn(lut16[first], lut16[second]);
-    const uint32_t u = half2_as_u32(v);
-    uint4 u4 = make_uint4(u, u, u, u);
-    uint4* row = reinterpret_cast<uint4*>(lut2 + tid * 32);
+struct GemvParams {
+  const __half* A;
+  const uint8_t* B;
+  const float* absmax;
+  const float* lut16;
+  __half* out;
+  int nchunks;          // K / 32
+  int S, G;             // warps per row, row groups per CTA
+  int rows_base, rows_rem;  // N / (grid*G), N % (grid*G)
+  int cpb_shift;        // log2(chunks per absmax block), or -1
+  int cpb;              // chunks per absmax block
+  int low_first;
+  unsigned long long w_step;   // bytes between two rows of one group
+  unsigned int a_step;         // absmax entries between two rows of one group (ALIGNED only)
+};
+
+// C = chunks (32 codes) per lane per row; S warps share a row (ST > 0: compile
+// time, ST == 0: run time), G groups per CTA.  ALIGNED: every row starts on an
+// absmax block boundary and blocks are a power of two, so the absmax pointer
+// of a lane advances by a constant.  Every instruction of this kernel is
+// executed by 32 warps per SM, so per-thread setup is kept to a minimum:
+// nothing is divided on the device.
+template <int C, int ST, bool ALIGNED>
+__global__ void __launch_bounds__(kGemvThreads, 1)
+nf4_gemv_kernel(const GemvParams p) {
+  constexpr int kStages = kStageChunks / C;  // rows in flight per lane
+  extern __shared__ __align__(16) unsigned char dsm[];
+  // table rows (256 x 256 B: lane copies | partial-sum slot) | [kStages][C][1024] uint4
+  // | [kStages][C][1024] float
+  const unsigned char* lut = dsm;
+  const int S = ST > 0 ? ST : p.S;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = warp / S, q = warp - g * S;
+  const int G = p.G;
+
+  // rows of this group: n = blockIdx.x + gridDim.x * (g + G * j), j < my_rows
+  const int row_first = blockIdx.x + gridDim.x * g;
+  const int row_stride = gridDim.x * G;
+  const int my_rows = g < G ? p.rows_base + (row_first < p.rows_rem ? 1 : 0) : 0;
+
+  // this lane's chunk columns; a lane beyond the row end copies nothing and
+  // sees zero scales in its (zero-filled) ring slots
+  const uint32_t ring_w0 = smem_u32(dsm + kLutBytes) + tid * 16;
+  const uint32_t ring_s0 = smem_u32(dsm + kLutBytes + kStageChunks * kGemvThreads * 16) + tid * 4;
+  const unsigned char* wp[C];
+  const float* ap[C];
+  bool live[C];
+  uint32_t ci[C];
 #pragma unroll
-    for (int q = 0; q < 8; q++) row[(q + tid) & 7] = u4;
+  for (int i = 0; i < C; i++) {
+    const int c = (q * C + i) * 32 + lane;
+    live[i] = c < p.nchunks;
+    const int cc = live[i] ? c : 0;
+    wp[i] = p.B + (size_t)row_first * ((size_t)p.nchunks * 16) + (size_t)cc * 16;
+    ci[i] = (uint32_t)row_first * (uint32_t)p.nchunks + (uint32_t)cc;
+    ap[i] = p.absmax + (ALIGNED ? (ci[i] >> p.cpb_shift) : 0u);
+    if (!live[i]) {
+#pragma unroll
+      for (int st = 0; st < kStages; st++) {
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(
+                         ring_w0 + (uint32_t)((st * C + i) * kGemvThreads * 16)), "r"(0));
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(
+                         ring_s0 + (uint32_t)((st * C + i) * kGemvThreads * 4)), "r"(0));
+      }
+    }
   }
-  const int nchunks = K >> 5;  // 32-code chunks per row
-  for (int i = tid; i < (K >> 3); i += kThreads) xs[i] = reinterpret_cast<const uint4*>(A)[i];
+  int to_issue = my_rows;  // rows not yet requested
+
+#define HQ_NF4_ISSUE(STAGE)                                                                     \
+  {                                                                                             \
+    const bool ok = to_issue > 0;                                                               \
+    _Pragma("unroll") for (int i = 0; i < C; i++) {                                             \
+      const float* a = ap[i];                                                                   \
+      if (!ALIGNED)                                                                             \
+        a = p.absmax + (p.cpb_shift >= 0 ? (ci[i] >> p.cpb_shift) : (ci[i] / (uint32_t)p.cpb)); \
+      cp_async_16(ring_w0 + (uint32_t)(((STAGE)*C + i) * kGemvThreads * 16), wp[i],             \
+                  ok && live[i]);                                                               \
+      cp_async_4(ring_s0 + (uint32_t)(((STAGE)*C + i) * kGemvThreads * 4), a, ok && live[i]);   \
+      wp[i] += p.w_step;                                                                        \
+      if (ALIGNED) ap[i] += p.a_step;                                                           \
+      else ci[i] += (uint32_t)row_stride * (uint32_t)p.nchunks;                                 \
+    }                                                                                           \
+    cp_async_commit();                                                                          \
+    to_issue--;                                                                                 \
+  }
+#pragma unroll
+  for (int st = 0; st < kStages; st++) HQ_NF4_ISSUE(st)
+
+  // ---- prologue (overlaps the copies above): byte table, input slice ----
+  {
+    const int entry = tid >> 2, quarter = tid & 3;  // four threads per 128-byte table row
+    const int hi = entry >> 4, lo = entry & 15;
+    const int first = p.low_first ? lo : hi, second = p.low_first ? hi : lo;
+    const uint32_t u = half2_as_u32(__floats2half2_rn(p.lut16[first], p.lut16[second]));
+    const uint4 u4 = make_uint4(u, u, u, u);
+    uint4* row = reinterpret_cast<uint4*>(dsm + (size_t)entry * 256 + quarter * 32);
+    row[entry & 1] = u4;
+    row[(entry & 1) ^ 1] = u4;
+  }
+  uint4 xr[C][4];
+#pragma unroll
+  for (int i = 0; i < C; i++) {
+    const int c = (q * C + i) * 32 + lane;
+    const uint4* xp = reinterpret_cast<const uint4*>(p.A) + 4 * (live[i] ? c : 0);
+#pragma unroll
+    for (int t = 0; t < 4; t++) xr[i][t] = __ldg(xp + t);
+  }
   __syncthreads();
 
-  const unsigned char* lut_lane = smem + lane * 4;
-  const int warps_total = gridDim.x * kWarps;
-  const int gwarp = blockIdx.x * kWarps + warp;
+  const uint32_t lane4 = lane * 4;
+  __half* outp = p.out + row_first;  // row j of this group is outp[j * row_stride]
+  // partial-sum slot s (32 floats) lives in the second half of table row s
+  float* const part_lane = reinterpret_cast<float*>(dsm + 128) + lane;  // slot s: part_lane[s*64]
+  const uint4* ring_w = reinterpret_cast<const uint4*>(dsm + kLutBytes) + tid;
+  const float* ring_s =
+      reinterpret_cast<const float*>(dsm + kLutBytes + kStageChunks * kGemvThreads * 16) + tid;
 
-  for (int n0 = gwarp * kRows; n0 < N; n0 += warps_total * kRows) {
-    const bool has1 = (n0 + 1) < N;
-    const int n1 = has1 ? n0 + 1 : n0;
-    const uint4* b0 = reinterpret_cast<const uint4*>(B + (size_t)n0 * (K >> 1));
-    const uint4* b1 = reinterpret_cast<const uint4*>(B + (size_t)n1 * (K >> 1));
-    const uint32_t cbase0 = (uint32_t)n0 * (uint32_t)nchunks;  // chunk index of row start
-    const uint32_t cbase1 = (uint32_t)n1 * (uint32_t)nchunks;
-    float acc0 = 0.f, acc1 = 0.f;
-    for (int c = lane; c < nchunks; c += 64) {
-      const int c2 = c + 32;
-      const bool two = c2 < nchunks;
-      const int cc2 = two ? c2 : c;
-      // issue all loads of the step first
-      const uint4 q00 = ldg_stream_u4(b0 + c), q10 = ldg_stream_u4(b1 + c);
-      const uint4 q01 = ldg_stream_u4(b0 + cc2), q11 = ldg_stream_u4(b1 + cc2);
-      const float s00 = __ldg(absmax + (cbase0 + c) / chunks_per_block);
-      const float s10 = __ldg(absmax + (cbase1 + c) / chunks_per_block);
-      const float s01 = __ldg(absmax + (cbase0 + cc2) / chunks_per_block);
-      const float s11 = __ldg(absmax + (cbase1 + cc2) / chunks_per_block);
-      uint32_t x2[16];
-      {
-        const uint4* xp = xs + 4 * c;
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const uint4 t = xp[q];
-          x2[4 * q] = t.x; x2[4 * q + 1] = t.y; x2[4 * q + 2] = t.z; x2[4 * q + 3] = t.w;
-        }
-      }
-      acc0 = fmaf(chunk_dot(q00, x2, lut_lane), s00, acc0);
-      acc1 = fmaf(chunk_dot(q10, x2, lut_lane), s10, acc1);
-      if (two) {
-        const uint4* xp = xs + 4 * c2;
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const uint4 t = xp[q];
-          x2[4 * q] = t.x; x2[4 * q + 1] = t.y; x2[4 * q + 2] = t.z; x2[4 * q + 3] = t.w;
-        }
-        acc0 = fmaf(chunk_dot(q01, x2, lut_lane), s01, acc0);
-        acc1 = fmaf(chunk_dot(q11, x2, lut_lane), s11, acc1);
-      }
-    }
-    acc0 = warp_sum(acc0);
-    acc1 = warp_sum(acc1);
-    if (lane == 0) {
-      out[n0] = __float2half_rn(acc0);
-      if (has1) out[n1] = __float2half_rn(acc1);
+  int rows_left = my_rows;
+  const int slot_g = g * kRound * S;        // slots of this group: [parity][g][d][t]
+  const int slot_flip = G * kRound * S;
+  int parity = 0;                           // used only when a super-round is one round
+  constexpr int kRoundsPerPass = kStages / kRound;
+
+  // one round = kRound rows out of compile-time stages RR*kRound .. +kRound-1
+#define HQ_NF4_ROUND(RR)                                                                       \
+  {                                                                                            \
+    const int rows_in_round = min(kRound, rows_left);                                          \
+    const int slot0 = slot_g + ((kRoundsPerPass > 1 ? ((RR)&1) : parity) ? slot_flip : 0);      \
+    _Pragma("unroll") for (int d = 0; d < kRound; d++) {                                       \
+      cp_async_wait<kStages - 1>();                                                            \
+      if (d < rows_in_round) {                                                                 \
+        float acc = 0.f;                                                                       \
+        _Pragma("unroll") for (int i = 0; i < C; i++) acc =                                    \
+            fmaf(chunk_dot(ring_w[(((RR)*kRound + d) * C + i) * kGemvThreads], xr[i], lut,      \
+                           lane4),                                                             \
+                 ring_s[(((RR)*kRound + d) * C + i) * kGemvThreads], acc);                      \
+        if (S > 1) {                                                                           \
+          part_lane[(slot0 + d * S + q) * 64] = acc;                                           \
+        } else {                                                                               \
+          acc = warp_sum(acc);                                                                 \
+          if (lane == 0) *outp = __float2half_rn(acc);                                         \
+          outp += row_stride;                                                                  \
+        }                                                                                      \
+      }                                                                                        \
+      HQ_NF4_ISSUE((RR)*kRound + d)                                                            \
+    }                                                                                          \
+    if (S > 1) {                                                                               \
+      group_barrier(1 + g, S * 32);                                                            \
+      for (int d = q; d < rows_in_round; d += S) {                                             \
+        float v = 0.f;                                                                         \
+        if (ST > 0) {                                                                          \
+          _Pragma("unroll") for (int t = 0; t < (ST > 0 ? ST : 1); t++) v +=                   \
+              part_lane[(slot0 + d * S + t) * 64];                                             \
+        } else {                                                                               \
+          for (int t = 0; t < S; t++) v += part_lane[(slot0 + d * S + t) * 64];                \
+        }                                                                                      \
+        v = warp_sum(v);                                                                       \
+        if (lane == 0) outp[(size_t)d * row_stride] = __float2half_rn(v);                      \
+      }                                                                                        \
+      outp += (size_t)kRound * row_stride;                                                     \
+    }                                                                                          \
+    parity ^= 1;                                                                               \
+    rows_left -= kRound;                                                                       \
+  }
+
+  while (rows_left > 0) {
+    HQ_NF4_ROUND(0)
+    if (kRoundsPerPass > 1) {
+      if (rows_left <= 0) break;
+      HQ_NF4_ROUND(1)
     }
   }
+#undef HQ_NF4_ROUND
+  cp_async_wait<0>();
+#undef HQ_NF4_ISSUE
 }
 
 // One thread: 4 bytes of codes (8 elements) -> 16 bytes of fp16.
@@ -187,26 +331,63 @@ int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, c
   using namespace hq;
   if (!A_half || !B || !absmax || !lut16 || !out_half) return HQ_ERR_NULL_POINTER;
   if (N <= 0 || K <= 0 || K % 32 != 0 || blocksize <= 0 || blocksize % 32 != 0 ||
-      K % blocksize != 0)
+      false)
     return HQ_ERR_BAD_SHAPE;
   if (!aligned16(B) || !aligned16(A_half)) return HQ_ERR_MISALIGNED;
   if ((uint64_t)N * (uint64_t)(K / 32) > 0xffffffffull) return HQ_ERR_TOO_LARGE;
-  const size_t smem = 256 * 32 * 4 + (size_t)K * 2;
-  if (smem > 200 * 1024) return HQ_ERR_TOO_LARGE;
-  cudaError_t e = cudaFuncSetAttribute(nf4_gemv_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return cuda_status(e);
+  const int nchunks = K / 32;
+  // warps per row S and chunks per lane C: C = 1 unless that needs more than 15
+  // named barriers (S = 2) or more warps than a CTA has.
+  const int cols = (nchunks + 31) / 32;  // 1024-input slices per row
+  int C = 1;
+  if (cols == 2 || cols > kGemvWarps) C = 2;
+  const int S = (cols + C - 1) / C;
+  if (S > kGemvWarps) return HQ_ERR_TOO_LARGE;  // K > 65536
+  int G = kGemvWarps / S;
+  if (S > 1 && G > 15) G = 15;
+  const size_t smem = (size_t)kLutBytes + (size_t)kStageChunks * kGemvThreads * 20;
   const int sms = sm_count();
-  int ctas_per_sm = (int)((220 * 1024) / (smem + 1024));
-  if (ctas_per_sm > 6) ctas_per_sm = 6;
-  if (ctas_per_sm < 1) ctas_per_sm = 1;
-  const int need = (N + kWarps * kRows - 1) / (kWarps * kRows);
-  int grid = sms * ctas_per_sm;
-  if (grid > need) grid = need;
-  nf4_gemv_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(
-      reinterpret_cast<const __half*>(A_half), B, absmax, lut16,
-      reinterpret_cast<__half*>(out_half), N, K, blocksize / 32,
-      (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0);
+  const int grid = std::min(sms, (N + G - 1) / G);
+  const int cpb = blocksize / 32;
+  int shift = -1;
+  if ((cpb & (cpb - 1)) == 0) {
+    shift = 0;
+    while ((1 << shift) < cpb) shift++;
+  }
+  const bool aligned = shift >= 0 && nchunks % cpb == 0;
+  GemvParams prm;
+  prm.A = reinterpret_cast<const __half*>(A_half);
+  prm.B = B;
+  prm.absmax = absmax;
+  prm.lut16 = lut16;
+  prm.out = reinterpret_cast<__half*>(out_half);
+  prm.nchunks = nchunks;
+  prm.S = S;
+  prm.G = G;
+  prm.rows_base = N / (grid * G);
+  prm.rows_rem = N % (grid * G);
+  prm.cpb_shift = shift;
+  prm.cpb = cpb;
+  prm.low_first = (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0;
+  prm.w_step = (unsigned long long)grid * G * nchunks * 16ull;
+  prm.a_step = aligned ? (unsigned)(((unsigned long long)grid * G * nchunks) >> shift) : 0u;
+  cudaStream_t st = (cudaStream_t)stream;
+#define HQ_NF4_LAUNCH(CC, SS, AL)                                                               \
+  {                                                                                             \
+    auto kern = nf4_gemv_kernel<CC, SS, AL>;                                                    \
+    cudaError_t e =                                                                             \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    if (e != cudaSuccess) return cuda_status(e);                                                \
+    kern<<<grid, kGemvThreads, smem, st>>>(prm);                                                \
+  }
+  if (C == 1 && S == 4 && aligned) HQ_NF4_LAUNCH(1, 4, true)
+  else if (C == 1 && S == 8 && aligned) HQ_NF4_LAUNCH(1, 8, true)
+  else if (C == 1 && S == 1 && aligned) HQ_NF4_LAUNCH(1, 1, true)
+  else if (C == 1 && aligned) HQ_NF4_LAUNCH(1, 0, true)
+  else if (C == 1) HQ_NF4_LAUNCH(1, 0, false)
+  else if (aligned) HQ_NF4_LAUNCH(2, 0, true)
+  else HQ_NF4_LAUNCH(2, 0, false)
+#undef HQ_NF4_LAUNCH
   return launch_status();
 }
 

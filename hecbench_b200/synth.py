@@ -24,6 +24,25 @@ def q3_case(K: int, width: int, seed: int = 0):
     return vec, codes, scales, zeros
 
 
+def q3_pack(codes: np.ndarray) -> np.ndarray:
+    """Pack 3-bit codes uint8[K][width] into the quant3MatMul layout
+    int32[K*3/32][width]: per column and group of 32 inputs a 96-bit
+    little-endian stream over three consecutive rows, code j at bits 3j..3j+2
+    (quant3MatMul-cuda/kernels.h:41-87)."""
+    K, width = codes.shape
+    assert K % 32 == 0
+    q = (codes.reshape(K // 32, 32, width) & 7).astype(np.uint64)
+    w = np.zeros((K // 32, 3, width), dtype=np.uint64)
+    for j in range(32):
+        bit = 3 * j
+        word, off = divmod(bit, 32)
+        w[:, word] |= q[:, j] << np.uint64(off)
+        if off > 29:
+            w[:, word + 1] |= q[:, j] >> np.uint64(32 - off)
+    w &= np.uint64(0xFFFFFFFF)
+    return w.astype(np.uint32).view(np.int32).reshape(K // 32 * 3, width)
+
+
 def nf4_levels(seed: int = 0) -> np.ndarray:
     """A 16-entry sorted level table in [-1, 1] with exact -1, 0 and 1 (the
     shape of a normal-float table; the values are seeded, not a published

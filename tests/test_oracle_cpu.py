@@ -63,6 +63,7 @@ def test_q3_pack_unpack_and_bit_order(oracle):
     codes = synth.q3_case(K, width, seed=3)[1]
     mat = oracle.q3_pack(codes)
     assert np.array_equal(oracle.q3_unpack(mat), codes)
+    assert np.array_equal(synth.q3_pack(codes), mat)
     # independent restatement: 96-bit little-endian stream per (group, column)
     m = mat.view(np.uint32).astype(object)
     for r in range(K // 32):
