@@ -1,0 +1,88 @@
+"""Builds the C++ host-side drop-ins against libhq.so when the HeCBench tree is
+present (REFERENCE_ROOT, default /root/reference); used by the GPU drop-in
+tests.  Outputs (binaries only) go to oracle/_ref/:
+
+  dropin_quant3MatMul  reference main.cu + shim/quant3MatMul/kernels.h
+  dropin_lutgemm       reference main.cu, nQWeight_fp16.cu + shim/lut-gemm/kernels.cu
+  dropin_quantBnB      shim/quantBnB/main.cu (reference code.h on the include path)
+  dropin_quantAQLM     shim/quantAQLM/main.cu
+
+The reference sources are compiled from where they lie; for quant3MatMul the
+driver is copied into a temporary directory first, because `#include
+"kernels.h"` resolves in the including file's own directory before any -I.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import tempfile
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+SHIM = PKG / "shim"
+OUT = ROOT / "oracle" / "_ref"
+REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w",
+          f"-I{ROOT / 'include'}", f"-L{PKG}", "-lhq", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../hecbench_b200"]
+
+
+def _run(cmd, cwd=None):
+    r = subprocess.run(list(map(str, cmd)), capture_output=True, text=True, cwd=cwd)
+    if r.returncode != 0:
+        raise RuntimeError("build failed: " + " ".join(map(str, cmd)) + "\n" + r.stderr)
+
+
+def build(force: bool = False):
+    """Returns the list of binaries built (empty when the reference tree is absent)."""
+    src = REF / "src"
+    if not (src / "quant3MatMul-cuda" / "main.cu").exists():
+        return []
+    OUT.mkdir(parents=True, exist_ok=True)
+    lib = PKG / "libhq.so"
+    built = []
+
+    def stale(target: Path, deps):
+        if force or not target.exists():
+            return True
+        t = target.stat().st_mtime
+        return any(Path(d).exists() and Path(d).stat().st_mtime > t for d in [lib, *deps])
+
+    # quant3MatMul: reference driver + our kernels.h
+    tgt = OUT / "dropin_quant3MatMul"
+    shim_h = SHIM / "quant3MatMul" / "kernels.h"
+    if stale(tgt, [shim_h]):
+        with tempfile.TemporaryDirectory() as tmp:
+            shutil.copy(src / "quant3MatMul-cuda" / "main.cu", Path(tmp) / "main.cu")
+            shutil.copy(shim_h, Path(tmp) / "kernels.h")
+            _run([NVCC, *COMMON, "main.cu", "-o", tgt], cwd=tmp)
+    built.append(tgt)
+
+    # lut-gemm: reference driver and weight container + our kernels.cu
+    tgt = OUT / "dropin_lutgemm"
+    shim_cu = SHIM / "lut-gemm" / "kernels.cu"
+    if stale(tgt, [shim_cu]):
+        d = src / "lut-gemm-cuda"
+        _run([NVCC, *COMMON, f"-I{d}", d / "main.cu", d / "nQWeight_fp16.cu", shim_cu, "-lcublas",
+              "-o", tgt])
+    built.append(tgt)
+
+    tgt = OUT / "dropin_quantBnB"
+    drv = SHIM / "quantBnB" / "main.cu"
+    if stale(tgt, [drv]):
+        _run([NVCC, *COMMON, f"-I{src / 'quantBnB-cuda'}", drv, "-o", tgt])
+    built.append(tgt)
+
+    tgt = OUT / "dropin_quantAQLM"
+    drv = SHIM / "quantAQLM" / "main.cu"
+    if stale(tgt, [drv]):
+        _run([NVCC, *COMMON, drv, "-o", tgt])
+    built.append(tgt)
+    return built
+
+
+if __name__ == "__main__":
+    for b in build(force=True):
+        print(b)
