@@ -19,6 +19,8 @@
 //    adds its tile's partial sums to an fp32 scratch row with one coalesced
 //    reduction per 32 columns, and the last CTA to finish converts the scratch
 //    to fp16, stores the output and re-zeroes the scratch.
+#include <mutex>
+
 #include "hq_common.cuh"
 
 namespace hq {
@@ -292,4 +294,59 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW, cons
   return HQ_ERR_BAD_SHAPE;
 }
 
+
+// ---- entry point that allocates nothing ----------------------------------
+
 }  // extern "C"
+
+namespace hq {
+namespace {
+
+// Scratch row of the allocation-free entry point: fp32 partial sums for up to
+// HQ_LUTGEMM_NOALLOC_MAX_M outputs plus the completion counter.  Every GPU
+// that loads the library holds these 257 KiB until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[HQ_LUTGEMM_NOALLOC_MAX_M * 4 + 256];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kMaxDevices];  // device address of the array, per device; null = not set up
+
+// Device address of g_noalloc_scratch on the current device.  In host code the
+// array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int noalloc_scratch(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (dev < 0 || dev >= kMaxDevices) return HQ_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_status(e);
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return HQ_OK;
+}
+
+}  // namespace
+}  // namespace hq
+
+extern "C" int hq_lutgemm_nqmv_noalloc(void* out_half, const void* x_half, const uint32_t* bW,
+                                       const void* alpha_half, const void* q_bias_half, int M,
+                                       int K, int nb, int group_size, hq_stream_t stream) {
+  using namespace hq;
+  if (M > HQ_LUTGEMM_NOALLOC_MAX_M) return HQ_ERR_TOO_LARGE;
+  if (M <= 0) return HQ_ERR_BAD_SHAPE;
+  void* ws = nullptr;
+  const int st = noalloc_scratch(&ws);
+  if (st != HQ_OK) return st;
+  const size_t bytes = hq_lutgemm_workspace_bytes(M);
+  // The array keeps whatever the previous call (of any caller) left in it, and
+  // the kernel needs partial sums and counter to start at zero.
+  cudaError_t e = cudaMemsetAsync(ws, 0, bytes, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_status(e);
+  return hq_lutgemm_nqmv(out_half, x_half, bW, alpha_half, q_bias_half, M, K, nb, group_size, ws,
+                         bytes, stream);
+}

@@ -109,6 +109,34 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW,
                     int group_size, void* workspace, size_t workspace_bytes,
                     hq_stream_t stream);
 
+/* Largest M hq_lutgemm_nqmv_noalloc accepts. */
+#define HQ_LUTGEMM_NOALLOC_MAX_M 65536
+
+/* hq_lutgemm_nqmv for callers that must not allocate device memory.  It has no
+ * counterpart in the reference.  Some hosts of this library cannot call
+ * cudaMalloc at the point where they need the mat-vec: a plugin that runs
+ * inside another framework's memory pool and owns no allocator of its own, a
+ * real-time or serving loop in which a cudaMalloc (which synchronises the
+ * device) is forbidden, or code whose memory budget was fixed at start-up.
+ * For them the fp32 scratch row the kernel needs is a fixed array inside the
+ * library's device image instead of a caller-provided workspace, so the call
+ * takes only inputs and outputs and performs no cudaMalloc / cudaFree and uses
+ * no allocating library routine.
+ *   - M must not exceed HQ_LUTGEMM_NOALLOC_MAX_M; larger sizes return
+ *     HQ_ERR_TOO_LARGE and nothing is launched.  All other argument rules are
+ *     those of hq_lutgemm_nqmv.
+ *   - The array (257 KiB) is held by every GPU that loads the library, until
+ *     the process exits.
+ *   - The first call on each device looks up the array's device address (with
+ *     that device current).  Make that first call outside any stream capture.
+ *   - Every call on a device uses the same array and begins by clearing the
+ *     part it needs on the given stream.  Calls whose execution overlaps on
+ *     the GPU (different streams, or several host threads on one device) race
+ *     on it and give wrong results: serialise them. */
+int hq_lutgemm_nqmv_noalloc(void* out_half, const void* x_half, const uint32_t* bW,
+                            const void* alpha_half, const void* q_bias_half, int M, int K, int nb,
+                            int group_size, hq_stream_t stream);
+
 /* ---------------- AQLM additive codebooks (quantAQLM) ---------------- */
 
 /* Replaces code1x16_matvec (quantAQLM-cuda/main.cu:113-141).  codes
