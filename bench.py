@@ -237,7 +237,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                 "-lms", "20", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
             self.proc = None
@@ -249,7 +249,7 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         sm, mx, reasons = [], [], set()
         for r in self.rows:
@@ -316,7 +316,7 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
     while True:
         fn(); reps += 1
         el = time.perf_counter() - t0
-        if el > budget_s or reps >= 200:
+        if el > budget_s or reps >= 20000:
             break
     per = el / reps
     return {"value": c["bytes"] / per / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
@@ -357,8 +357,8 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="nf4_gemv", choices=WORKLOADS)
     ap.add_argument("--replica-bytes", type=float, default=640e6,

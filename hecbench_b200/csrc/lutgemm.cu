@@ -9,10 +9,15 @@
 //
 // Like the reference (mv_fp16.h:133-227) the +-sums over 8 inputs are looked up
 // by bit-plane byte in a table built from x, but:
-//  * a CTA owns a K tile of 128 inputs (4 packed rows) and a range of columns;
-//    the 16 tables of a tile are laid out lut[row][byte][replica c][byte-lane j]
-//    so that lane (c,j) of a warp - which handles byte j of the words of
-//    columns 4c..4c+3 - always reads bank 4c+j: no lookup ever conflicts;
+//  * a CTA of 512 threads owns a K tile of 128 inputs (4 packed rows) and a
+//    range of columns; lane (c,j) of a warp handles byte j of the words of
+//    columns 4c..4c+3 and reads replica c of table (row, j): the 16 tables are
+//    stored with one 256-byte line per (row pair, byte value) holding
+//    [row parity][replica c][byte-lane j], so every lane of a warp reads its
+//    own bank - no lookup ever conflicts - and, the table block being aligned
+//    to 64 KiB in the shared window, the address of a lookup is ONE
+//    byte-permute of the packed word and a per-lane constant (the row is an
+//    immediate offset);
 //  * table entries and all sums are fp32 (the reference uses fp16 throughout
 //    and half2 atomics on the output);
 //  * the four lanes of a column quad are combined with two shuffles, each CTA
@@ -26,33 +31,158 @@
 namespace hq {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = 8;
-constexpr int kTileRows = 4;                       // packed rows (32 inputs each) per tile
-constexpr int kLutWords = kTileRows * 256 * 32;    // replicated tables, 128 KiB
-constexpr int kCompactWords = kTileRows * 256 * 4; // [row][byte value][j], 16 KiB
-constexpr size_t kSmemBytes = (size_t)(kLutWords + kCompactWords + 128) * 4;
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+constexpr int kQuads = kThreads / 4;
+constexpr int kTileRows = 4;                  // packed rows (32 inputs each) per tile
+constexpr int kLutBytes = 2 * 65536;          // 2 row pairs x 256 byte values x 256 B
+constexpr int kLutImm = 2048;                 // table block sits at shared address 64Ki*h + kLutImm
+constexpr int kCompactWords = kTileRows * 256 * 4;  // [row][byte value][j]
+
+// dynamic shared memory: [pad to the table address][tables 128 KiB][word ring][compact][inputs]
+// bytes of one column step in a quad's ring: packed words, then per alpha group
+// NB alpha vectors and one bias vector of four halves each
+template <int NB, int RPG>
+constexpr int step_bytes() {
+  return (kTileRows * NB * 16 + (kTileRows / RPG) * (NB + 1) * 8 + 15) / 16 * 16;
+}
+// The build scratch (compact tables + inputs) aliases the last ring buffer,
+// which is not written before the tables are complete.
+constexpr size_t kBuildBytes = (size_t)kCompactWords * 4 + 512 + 64;
+template <int NB, int RPG, int kBufs>
+constexpr size_t smem_bytes() {
+  constexpr size_t buf = (size_t)kQuads * step_bytes<NB, RPG>();
+  return (size_t)kLutImm + kLutBytes + (kBufs - 1) * buf + (buf > kBuildBytes ? buf : kBuildBytes);
+}
+// deepest ring (3 or 2 column steps per quad) that fits the 227 KiB of an SM
+template <int NB, int RPG>
+constexpr int pick_bufs() {
+  return smem_bytes<NB, RPG, 3>() <= 227 * 1024 ? 3 : 2;
+}
 
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
+template <int IMM>
+__device__ __forceinline__ float lds_f32_imm(uint32_t addr) {
+  // not volatile: the tables are constant once built, and every address depends
+  // on ring data that is read behind the proper barrier, so the scheduler is
+  // free to batch these loads
+  float v;
+  asm("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
-// RPG: packed rows that share one alpha group inside a tile (4, 2 or 1).
-template <int NB, int RPG>
+// One launch handles NB bit planes b0 .. b0+NB-1 of nb_total (more than four
+// planes are split over two launches that accumulate into the same scratch
+// row; only the last one converts it).  RPG: packed rows that share one alpha
+// group inside a tile (4, 2 or 1).  kBufs: column steps resident in the word
+// ring per quad (kBufs - 1 in flight).
+template <int NB, int RPG, int kBufs>
 __global__ void __launch_bounds__(kThreads, 1)
 lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha,
                const __half* __restrict__ q_bias, const __half* __restrict__ x,
                __half* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ counter,
-               int M, int K, int rows_per_group, int cols_per_cta) {
-  extern __shared__ __align__(16) float smem[];
-  float* lut = smem;                          // [row][byte][32]
-  float* compact = smem + kLutWords;          // [row][byte][4]
-  float* xs = compact + kCompactWords;        // 128 inputs of the tile
+               int M, int K, int rows_per_group, int cols_per_cta, int nb_total, int b0,
+               int finalize) {
+  constexpr int kWords = kTileRows * NB;  // 16-byte word vectors per column step
+  constexpr int kStep =
+      (kTileRows * NB * 16 + (kTileRows / RPG) * (NB + 1) * 8 + 15) / 16 * 16;  // 16-byte slots
+  static_assert(kStep % 16 == 0, "ring slots hold 16-byte asynchronous copies");
+  constexpr int kGroups = kTileRows / RPG;
+  constexpr int kItems = kGroups * (NB + 1);  // alpha / bias vectors per column step
+  extern __shared__ __align__(16) unsigned char dsm[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // The table block sits at shared-window address 64Ki*h + kLutImm (h = 0 unless
+  // the dynamic region starts beyond kLutImm), so that a lookup address is a
+  // byte-permute {h, byte value, lane*4} plus the immediate kLutImm + row offset.
+  const uint32_t dsm_addr = (uint32_t)__cvta_generic_to_shared(dsm);
+  const uint32_t h = dsm_addr > (uint32_t)kLutImm ? (dsm_addr - kLutImm + 0xffffu) >> 16 : 0u;
+  const uint32_t lut_addr = (h << 16) + kLutImm;
+  unsigned char* lut = dsm + (lut_addr - dsm_addr);
+  unsigned char* ring = lut + kLutBytes;
+  // ring layout: [buffer][quad][step bytes]; the build scratch aliases the last buffer
+  float* compact = reinterpret_cast<float*>(ring + (size_t)(kBufs - 1) * kQuads * kStep);
+  float* xs = compact + kCompactWords;  // 128 inputs of the tile
+  __shared__ unsigned s_last;
   const int tile = blockIdx.y;
-  const int row0 = tile * kTileRows;               // first packed row of the tile
+  const int row0 = tile * kTileRows;  // first packed row of the tile
   const int total_rows = K >> 5;
   const int nrows = min(kTileRows, total_rows - row0);
+
+  // ---- column steps of this warp and the quad's word ring ----
+  const int j = lane & 3;   // byte of the word this lane looks up
+  const int cq = lane >> 2; // column quad inside the 32-column step
+  const int m_begin = blockIdx.x * cols_per_cta;
+  const int m_end = min(M, m_begin + cols_per_cta);
+  const int m0 = m_begin + warp * 32 + cq * 4;  // step s handles columns m0 + s*kWarps*32 ..+3
+  const int nsteps = (m_end - (m_begin + warp * 32) + kWarps * 32 - 1) / (kWarps * 32);
+  const uint32_t ring_quad = (uint32_t)__cvta_generic_to_shared(ring) +
+                             (uint32_t)((warp * 8 + cq) * kStep);
+  const uint32_t* src0 = bW + ((size_t)row0 * nb_total + b0) * M + m0;
+  const int g0 = row0 / rows_per_group;  // alpha group of the tile's first row
+
+  // lane j of a quad copies word vectors j, j+4, ... of a step (rows past the end
+  // of K are skipped: their tables are all zero, so stale ring bytes are harmless)
+  auto issue = [&](int s) {
+    if (s < nsteps) {
+      const int m = m0 + s * (kWarps * 32);
+      if (m < m_end) {
+        const uint32_t dst = ring_quad + (uint32_t)((s % kBufs) * (kQuads * kStep));
+        const uint32_t* src = src0 + (size_t)s * (kWarps * 32);
+        // alpha / bias vectors: item (group gi, plane b) with b == NB meaning the bias
+#pragma unroll
+        for (int t = 0; t < (kItems + 3) / 4; t++) {
+          const int it = j + 4 * t;
+          if (it < kItems) {
+            const int gi = it / (NB + 1), b = it - gi * (NB + 1);
+            const int g = g0 + gi;
+            if (gi * RPG < nrows) {
+              if (b < NB)
+                cp_async_8(dst + kWords * 16 + it * 8,
+                           alpha + ((size_t)g * nb_total + b0 + b) * M + m);
+              else if (q_bias != nullptr)
+                cp_async_8(dst + kWords * 16 + it * 8, q_bias + (size_t)g * M + m);
+            }
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < NB; t++) {
+          const int i = j + 4 * t;  // word vector (row i / NB, plane i % NB)
+          const int r = i / NB, b = i - r * NB;
+          if (r < nrows) cp_async_16(dst + i * 16, src + (size_t)(r * nb_total + b) * M);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < kBufs - 1; s++) issue(s);
 
   // ---- stage the tile's inputs (zero beyond K) ----
   if (tid < kTileRows * 32) {
@@ -61,120 +191,119 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   }
   __syncthreads();
 
-  // ---- phase A: thread = byte value; signed sums of 8 inputs for 16 byte groups ----
+  // ---- phase A: thread = (byte value, row pair); signed sums of 8 inputs ----
   {
+    const int bv = tid & 255, rp = tid >> 8;
     uint32_t sgn[8];
 #pragma unroll
-    for (int t = 0; t < 8; t++) sgn[t] = ((tid >> t) & 1) ? 0u : 0x80000000u;
+    for (int t = 0; t < 8; t++) sgn[t] = ((bv >> t) & 1) ? 0u : 0x80000000u;
 #pragma unroll
-    for (int r = 0; r < kTileRows; r++) {
+    for (int rr = 0; rr < 2; rr++) {
+      const int r = rp * 2 + rr;
       float v[4];
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const float4 xa = *reinterpret_cast<const float4*>(xs + r * 32 + j * 8);
-        const float4 xb = *reinterpret_cast<const float4*>(xs + r * 32 + j * 8 + 4);
-        float s = __uint_as_float(__float_as_uint(xa.x) ^ sgn[0]);
-        s += __uint_as_float(__float_as_uint(xa.y) ^ sgn[1]);
-        s += __uint_as_float(__float_as_uint(xa.z) ^ sgn[2]);
-        s += __uint_as_float(__float_as_uint(xa.w) ^ sgn[3]);
-        s += __uint_as_float(__float_as_uint(xb.x) ^ sgn[4]);
-        s += __uint_as_float(__float_as_uint(xb.y) ^ sgn[5]);
-        s += __uint_as_float(__float_as_uint(xb.z) ^ sgn[6]);
-        s += __uint_as_float(__float_as_uint(xb.w) ^ sgn[7]);
-        v[j] = s;
+      for (int jj = 0; jj < 4; jj++) {
+        const float4 xa = *reinterpret_cast<const float4*>(xs + r * 32 + jj * 8);
+        const float4 xb = *reinterpret_cast<const float4*>(xs + r * 32 + jj * 8 + 4);
+        const float s0 = __uint_as_float(__float_as_uint(xa.x) ^ sgn[0]) +
+                         __uint_as_float(__float_as_uint(xa.y) ^ sgn[1]);
+        const float s1 = __uint_as_float(__float_as_uint(xa.z) ^ sgn[2]) +
+                         __uint_as_float(__float_as_uint(xa.w) ^ sgn[3]);
+        const float s2 = __uint_as_float(__float_as_uint(xb.x) ^ sgn[4]) +
+                         __uint_as_float(__float_as_uint(xb.y) ^ sgn[5]);
+        const float s3 = __uint_as_float(__float_as_uint(xb.z) ^ sgn[6]) +
+                         __uint_as_float(__float_as_uint(xb.w) ^ sgn[7]);
+        v[jj] = (s0 + s1) + (s2 + s3);
       }
-      *reinterpret_cast<float4*>(compact + (r * 256 + tid) * 4) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(compact + (r * 256 + bv) * 4) = make_float4(v[0], v[1], v[2], v[3]);
     }
   }
   __syncthreads();
-  // ---- phase B: replicate each (row, byte) entry 8 times: lane = (byte&3, replica) ----
+  // ---- phase B: replicate each (row, byte) entry 8 times into its table line ----
+  // line (row pair p, byte b) at lut + p*65536 + b*256; inside: [row parity][c][j] floats
   {
     const int c = lane & 7, bl = lane >> 3;
 #pragma unroll 4
     for (int it = 0; it < kTileRows * 256 / (kWarps * 4); it++) {
-      const int e = (it * kWarps + warp) * 4 + bl;  // (row*256 + byte)
+      const int e = (it * kWarps + warp) * 4 + bl;  // row*256 + byte
+      const int r = e >> 8, b = e & 255;
       const float4 v = *reinterpret_cast<const float4*>(compact + e * 4);
-      *reinterpret_cast<float4*>(lut + e * 32 + c * 4) = v;
+      *reinterpret_cast<float4*>(lut + (r >> 1) * 65536 + b * 256 + (r & 1) * 128 + c * 16) = v;
     }
   }
   __syncthreads();
 
   // ---- lookup phase ----
-  const int j = lane & 3;            // byte of the word this lane looks up
-  const int cq = lane >> 2;          // column quad inside the 32-column step
-  const unsigned char* lut_lane = reinterpret_cast<const unsigned char*>(lut) + lane * 4;
-  const int shift = 8 * j;
-  const int m_begin = blockIdx.x * cols_per_cta;
-  const int m_end = min(M, m_begin + cols_per_cta);
-  const int g0 = row0 / rows_per_group;  // alpha group of the tile's first row
+  // lookup of byte value b in row r: [byteperm(word, hi, sel) + kLutImm + (r>>1)*65536 + (r&1)*128]
+  const uint32_t hi = (h << 16) | (uint32_t)(lane * 4);
+  const uint32_t sel = 0x7604u | ((uint32_t)j << 4);
 
   // bias uses the all-ones entry (byte 255): sum of this lane's 8 inputs per row
-  float ones[kTileRows];
+  float ones[kTileRows / RPG];
 #pragma unroll
-  for (int r = 0; r < kTileRows; r++)
-    ones[r] = *reinterpret_cast<const float*>(lut_lane + (size_t)(r * 256 + 255) * 128);
+  for (int gi = 0; gi < kTileRows / RPG; gi++) {
+    float o = 0.f;
+#pragma unroll
+    for (int r = gi * RPG; r < (gi + 1) * RPG; r++)
+      o += *reinterpret_cast<const float*>(lut + (r >> 1) * 65536 + 255 * 256 + (r & 1) * 128 +
+                                           lane * 4);
+    ones[gi] = o;
+  }
 
-  for (int ms = m_begin + warp * 32; ms < m_end; ms += kWarps * 32) {
-    const int m = ms + cq * 4;
+  for (int s = 0; s < nsteps; s++) {
+    issue(s + kBufs - 1);
+    const int m = m0 + s * (kWarps * 32);
     const bool active = m < m_end;
+    cp_async_wait<kBufs - 1>();
+    __syncwarp();
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (active) {
-      uint4 wv[kTileRows][NB];
+      const uint32_t buf = ring_quad + (uint32_t)((s % kBufs) * (kQuads * kStep));
 #pragma unroll
-      for (int r = 0; r < kTileRows; r++)
+      for (int gi = 0; gi < kTileRows / RPG; gi++) {
+        float t[NB][4];
 #pragma unroll
-        for (int b = 0; b < NB; b++)
-          wv[r][b] = (r < nrows)
-                         ? ldg_stream_u4(bW + ((size_t)(row0 + r) * NB + b) * M + m)
-                         : make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int r0 = 0; r0 < kTileRows; r0 += RPG) {
-        if (r0 < nrows) {
-          const int g = g0 + (RPG == kTileRows ? 0 : r0 / RPG);
-          float t[NB][4];
-#pragma unroll
-          for (int b = 0; b < NB; b++)
-#pragma unroll
-            for (int c = 0; c < 4; c++) t[b][c] = 0.f;
-          float ones_g = 0.f;
-#pragma unroll
-          for (int r = r0; r < r0 + RPG; r++) {
-            if (r < nrows) {
-              ones_g += ones[r];
-              const unsigned char* lr = lut_lane + (size_t)r * 256 * 128;
-#pragma unroll
-              for (int b = 0; b < NB; b++) {
-                const uint32_t w4[4] = {wv[r][b].x, wv[r][b].y, wv[r][b].z, wv[r][b].w};
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                  const uint32_t off = ((w4[c] >> shift) & 0xffu) << 7;
-                  t[b][c] += *reinterpret_cast<const float*>(lr + off);
-                }
-              }
-            }
-          }
+        for (int rr = 0; rr < RPG; rr++) {
+          const int r = gi * RPG + rr;
 #pragma unroll
           for (int b = 0; b < NB; b++) {
-            const uint2 av = *reinterpret_cast<const uint2*>(alpha + ((size_t)g * NB + b) * M + m);
-            const float2 a01 = __half22float2(u32_as_half2(av.x));
-            const float2 a23 = __half22float2(u32_as_half2(av.y));
-            acc[0] = fmaf(a01.x, t[b][0], acc[0]);
-            acc[1] = fmaf(a01.y, t[b][1], acc[1]);
-            acc[2] = fmaf(a23.x, t[b][2], acc[2]);
-            acc[3] = fmaf(a23.y, t[b][3], acc[3]);
+            const uint4 wv = lds_u4(buf + (uint32_t)((r * NB + b) * 16));
+            const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+              const uint32_t a = __byte_perm(w4[c], hi, sel);
+              float v;
+              if (r == 0) v = lds_f32_imm<kLutImm>(a);
+              else if (r == 1) v = lds_f32_imm<kLutImm + 128>(a);
+              else if (r == 2) v = lds_f32_imm<kLutImm + 65536>(a);
+              else v = lds_f32_imm<kLutImm + 65536 + 128>(a);
+              t[b][c] = (rr == 0) ? v : t[b][c] + v;
+            }
           }
-          if (q_bias != nullptr) {
-            const uint2 bv = *reinterpret_cast<const uint2*>(q_bias + (size_t)g * M + m);
-            const float2 b01 = __half22float2(u32_as_half2(bv.x));
-            const float2 b23 = __half22float2(u32_as_half2(bv.y));
-            acc[0] = fmaf(b01.x, ones_g, acc[0]);
-            acc[1] = fmaf(b01.y, ones_g, acc[1]);
-            acc[2] = fmaf(b23.x, ones_g, acc[2]);
-            acc[3] = fmaf(b23.y, ones_g, acc[3]);
-          }
+        }
+        if (gi * RPG >= nrows) continue;  // rows past the end of K (no alpha was copied)
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+          const uint2 avb = lds_u2(buf + (uint32_t)(kWords * 16 + (gi * (NB + 1) + b) * 8));
+          const float2 a01 = __half22float2(u32_as_half2(avb.x));
+          const float2 a23 = __half22float2(u32_as_half2(avb.y));
+          acc[0] = fmaf(a01.x, t[b][0], acc[0]);
+          acc[1] = fmaf(a01.y, t[b][1], acc[1]);
+          acc[2] = fmaf(a23.x, t[b][2], acc[2]);
+          acc[3] = fmaf(a23.y, t[b][3], acc[3]);
+        }
+        if (q_bias != nullptr) {
+          const uint2 bvv = lds_u2(buf + (uint32_t)(kWords * 16 + (gi * (NB + 1) + NB) * 8));
+          const float2 b01 = __half22float2(u32_as_half2(bvv.x));
+          const float2 b23 = __half22float2(u32_as_half2(bvv.y));
+          acc[0] = fmaf(b01.x, ones[gi], acc[0]);
+          acc[1] = fmaf(b01.y, ones[gi], acc[1]);
+          acc[2] = fmaf(b23.x, ones[gi], acc[2]);
+          acc[3] = fmaf(b23.y, ones[gi], acc[3]);
         }
       }
     }
+    __syncwarp();  // all lanes are done with this step's ring buffer
     // combine the four byte lanes of each column quad
 #pragma unroll
     for (int c = 0; c < 4; c++) {
@@ -182,11 +311,12 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
       acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 2);
     }
     const float mine = j == 0 ? acc[0] : j == 1 ? acc[1] : j == 2 ? acc[2] : acc[3];
-    if (active) red_add_f32(ws + m + j, mine);  // lane (cq,j) -> column ms + lane
+    if (active) red_add_f32(ws + m + j, mine);  // lane (cq,j) -> column of this step + lane
   }
+  cp_async_wait<0>();
 
   // ---- last CTA converts the scratch row to fp16 and re-zeroes it ----
-  __shared__ unsigned s_last;
+  if (!finalize) return;
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -197,33 +327,66 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   __syncthreads();
   if (s_last) {
     __threadfence();
-    for (int m = tid; m < M; m += kThreads) {
-      const float v = __ldcg(ws + m);
-      out[m] = __float2half_rn(v);
-      ws[m] = 0.f;
+    for (int mm = tid; mm < M; mm += kThreads) {
+      const float v = __ldcg(ws + mm);
+      out[mm] = __float2half_rn(v);
+      ws[mm] = 0.f;
     }
     if (tid == 0) *counter = 0u;
   }
 }
 
-template <int NB>
-int launch_nb(int rpg_in_tile, dim3 grid, cudaStream_t st, const uint32_t* bW, const __half* alpha,
-              const __half* q_bias, const __half* x, __half* out, float* ws, unsigned* counter,
-              int M, int K, int rows_per_group, int cols_per_cta) {
-#define HQ_LUT_LAUNCH(RPG)                                                                    \
-  {                                                                                           \
-    auto kern = lutgemm_kernel<NB, RPG>;                                                      \
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                         (int)kSmemBytes);                                    \
-    if (e != cudaSuccess) return cuda_status(e);                                              \
-    kern<<<grid, kThreads, kSmemBytes, st>>>(bW, alpha, q_bias, x, out, ws, counter, M, K,     \
-                                             rows_per_group, cols_per_cta);                   \
-  }
-  if (rpg_in_tile == 4) HQ_LUT_LAUNCH(4)
-  else if (rpg_in_tile == 2) HQ_LUT_LAUNCH(2)
-  else HQ_LUT_LAUNCH(1)
-#undef HQ_LUT_LAUNCH
+struct LaunchArgs {
+  dim3 grid;
+  cudaStream_t st;
+  const uint32_t* bW;
+  const __half* alpha;
+  const __half* q_bias;
+  const __half* x;
+  __half* out;
+  float* ws;
+  unsigned* counter;
+  int M, K, rows_per_group, cols_per_cta, nb_total;
+};
+
+template <int NB, int RPG, int kBufs>
+int launch_one(const LaunchArgs& a, int b0, const __half* bias, int finalize) {
+  auto kern = lutgemm_kernel<NB, RPG, kBufs>;
+  constexpr size_t smem = smem_bytes<NB, RPG, kBufs>();
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_status(e);
+  kern<<<a.grid, kThreads, smem, a.st>>>(a.bW, a.alpha, bias, a.x, a.out, a.ws, a.counter, a.M,
+                                         a.K, a.rows_per_group, a.cols_per_cta, a.nb_total, b0,
+                                         finalize);
   return launch_status();
+}
+
+template <int NB, int RPG>
+int launch_sub(const LaunchArgs& a, int b0, const __half* bias, int finalize) {
+  return launch_one<NB, RPG, pick_bufs<NB, RPG>()>(a, b0, bias, finalize);
+}
+
+// Bit planes are handled up to kMax at a time (what fits the shared-memory
+// ring); further planes go to follow-up launches that accumulate into the same
+// scratch row.  Only the first launch adds the bias term, only the last one
+// converts the scratch row.
+template <int RPG>
+int launch_planes(const LaunchArgs& a) {
+  constexpr int kMax = RPG == 1 ? 3 : 4;
+  const int nb = a.nb_total;
+  for (int b0 = 0; b0 < nb; b0 += kMax) {
+    const int n = nb - b0 < kMax ? nb - b0 : kMax;
+    const int last = (b0 + n == nb) ? 1 : 0;
+    const __half* bias = b0 == 0 ? a.q_bias : nullptr;
+    int st;
+    if (n == 1) st = launch_sub<1, RPG>(a, b0, bias, last);
+    else if (n == 2) st = launch_sub<2, RPG>(a, b0, bias, last);
+    else if (n == 3) st = launch_sub<3, RPG>(a, b0, bias, last);
+    else st = launch_sub<(kMax >= 4 ? 4 : 3), RPG>(a, b0, bias, last);
+    if (st != HQ_OK) return st;
+  }
+  return HQ_OK;
 }
 
 }  // namespace
@@ -272,28 +435,26 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW, cons
     if (score > best_score) { best_score = score; best_cols = chunk256 * 256; }
   }
   const int mblocks = (M + best_cols - 1) / best_cols;
-  dim3 grid(mblocks, tiles);
-  float* ws = reinterpret_cast<float*>(workspace);
-  unsigned* counter =
-      reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
-                                  (hq_lutgemm_workspace_bytes(M) - 256));
-  const __half* alpha = reinterpret_cast<const __half*>(alpha_half);
-  const __half* qb = reinterpret_cast<const __half*>(q_bias_half);
-  const __half* x = reinterpret_cast<const __half*>(x_half);
-  __half* out = reinterpret_cast<__half*>(out_half);
-  cudaStream_t st = (cudaStream_t)stream;
-#define HQ_NB_CASE(NB)                                                                        \
-  case NB:                                                                                    \
-    return launch_nb<NB>(rpg_in_tile, grid, st, bW, alpha, qb, x, out, ws, counter, M, K, rpg, \
-                         best_cols);
-  switch (nb) {
-    HQ_NB_CASE(1) HQ_NB_CASE(2) HQ_NB_CASE(3) HQ_NB_CASE(4)
-    HQ_NB_CASE(5) HQ_NB_CASE(6) HQ_NB_CASE(7) HQ_NB_CASE(8)
-  }
-#undef HQ_NB_CASE
-  return HQ_ERR_BAD_SHAPE;
+  LaunchArgs a;
+  a.grid = dim3(mblocks, tiles);
+  a.st = (cudaStream_t)stream;
+  a.bW = bW;
+  a.alpha = reinterpret_cast<const __half*>(alpha_half);
+  a.q_bias = reinterpret_cast<const __half*>(q_bias_half);
+  a.x = reinterpret_cast<const __half*>(x_half);
+  a.out = reinterpret_cast<__half*>(out_half);
+  a.ws = reinterpret_cast<float*>(workspace);
+  a.counter = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
+                                          (hq_lutgemm_workspace_bytes(M) - 256));
+  a.M = M;
+  a.K = K;
+  a.rows_per_group = rpg;
+  a.cols_per_cta = best_cols;
+  a.nb_total = nb;
+  if (rpg_in_tile == 4) return launch_planes<4>(a);
+  if (rpg_in_tile == 2) return launch_planes<2>(a);
+  return launch_planes<1>(a);
 }
-
 
 // ---- entry point that allocates nothing ----------------------------------
 
