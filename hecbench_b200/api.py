@@ -237,3 +237,27 @@ def code2x8_matvec(A, B, C_out, codebooks, prob_m: int, prob_k: int,
         0 if scales is None else _dev(scales, torch.float16, "scales"))
     with torch.cuda.device(A.device):
         check("hq_aqlm_2x8_matvec", lib.hq_aqlm_2x8_matvec(*args, _stream()))
+
+
+# --------------------------------------------------------------------------
+# batched dequant-GEMM (tensor cores)
+# --------------------------------------------------------------------------
+
+def qgemm_q3(X, mat, scales, zeros, N: int, K: int, group_size: int = 128,
+             out: Optional[torch.Tensor] = None,
+             status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Y[Mb][N] = X[Mb][K] @ dequant(mat) for the GPTQ 3-bit layout with per-group
+    fp16 scales / zeros [K/group_size][N] (no counterpart in the reference tree).
+    `status` (int32[1], optional) receives 1 if a bounded in-kernel wait ran out."""
+    lib = load_library()
+    Mb = X.shape[0]
+    if out is None:
+        out = torch.empty((Mb, N), dtype=torch.float16, device=X.device)
+    args = (
+        _dev(X, torch.float16, "X"), _dev(mat, torch.int32, "mat"),
+        _dev(scales, torch.float16, "scales"), _dev(zeros, torch.float16, "zeros"),
+        _dev(out, torch.float16, "out"), Mb, N, K, group_size,
+        0 if status is None else _dev(status, torch.int32, "status"))
+    with torch.cuda.device(X.device):
+        check("hq_qgemm_q3_f16", lib.hq_qgemm_q3_f16(*args, _stream()))
+    return out

@@ -91,3 +91,14 @@ def aqlm_2x8_case(prob_m: int, prob_k: int, seed: int = 0):
     x = _rng(seed, 43).standard_normal(prob_k).astype(np.float16)
     scales = _rng(seed, 44).uniform(0.5, 2.0, prob_m).astype(np.float16)
     return codes, x, codebooks, scales
+
+
+def qgemm_q3_case(Mb: int, K: int, N: int, group_size: int = 128, seed: int = 0):
+    """Batched path: fp16 X~N(0,1), 3-bit codes uniform, per-group fp16
+    scales~U(0.001,0.01) and zeros = scale*U{0..7}."""
+    codes = _rng(seed, 51).integers(0, 8, size=(K, N), dtype=np.uint8)
+    X = _rng(seed, 52).standard_normal((Mb, K)).astype(np.float16)
+    G = K // group_size
+    scales = _rng(seed, 53).uniform(0.001, 0.01, (G, N)).astype(np.float16)
+    zeros = (scales.astype(np.float32) * _rng(seed, 54).integers(0, 8, (G, N))).astype(np.float16)
+    return X, codes, scales, zeros

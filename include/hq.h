@@ -157,6 +157,19 @@ int hq_aqlm_2x8_matvec(const void* codes, const void* x_half, void* out_half,
                        const void* codebooks, int prob_m, int prob_k, const void* scales_half,
                        hq_stream_t stream);
 
+/* ---------------- batched dequant-GEMM (tensor cores) ---------------- */
+
+/* Y[Mb][N] = X[Mb][K] * W[K][N] with W the GPTQ 3-bit layout of quant3MatMul
+ * (mat int32[K*3/32][N]) and per-group fp16 parameters scales/zeros
+ * half[K/group_size][N]: W[k][n] = hfma(half(q), scale, -zero), fp32
+ * accumulation on the sm_100a tensor cores (tcgen05 / tensor memory), fp16
+ * output.  No counterpart in the reference tree.  1 <= Mb <= 128,
+ * N % 128 == 0, K % group_size == 0, group_size % 64 == 0.  status_word
+ * (device int, nullable) is set to 1 if a bounded in-kernel wait ran out. */
+int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_half,
+                    const void* zeros_half, void* Y_half, int Mb, int N, int K, int group_size,
+                    int* status_word, hq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
