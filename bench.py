@@ -110,13 +110,23 @@ def _host_case(name: str, seed: int):
         codes, x, cbs, scales = synth.aqlm_2x8_case(m, k, seed)
         return dict(m=m, k=k, codes=codes, x=x, cbs=cbs, scales=scales,
                     bytes=codes.nbytes + 4 * 8192, desc="AQLM 2x8 mat-vec 4096x4096")
+    if name == "qgemm_q3":
+        Mb, K, N = 64, 8192, 28672
+        if os.environ.get("HQ_BENCH_QGEMM_SHAPE") == "down":
+            K, N = 28672, 8192
+        X, codes, scales, zeros = synth.qgemm_q3_case(Mb, K, N, 128, seed)
+        return dict(Mb=Mb, K=K, N=N, X=X, codes=codes, scales=scales, zeros=zeros,
+                    bytes=K * 3 // 32 * N * 4 + 2 * (K // 128) * N * 2 + Mb * K * 2 + Mb * N * 2,
+                    flops=2.0 * Mb * K * N,
+                    desc=f"batched dequant-GEMM, 3-bit g128, X[{Mb}x{K}] x W[{K}x{N}] (Llama-3-70B MLP)")
     raise SystemExit(f"unknown workload {name}")
 
 
 WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "bnb_quantize", "lutgemm",
-             "aqlm_1x16", "aqlm_2x8"]
+             "aqlm_1x16", "aqlm_2x8", "qgemm_q3"]
 DTYPE = {"nf4_gemv": "f16", "nf4_dequant": "f16", "q3_gemv_f32": "f32", "q3_gemv_f16": "f16",
-         "bnb_quantize": "u8", "lutgemm": "f16", "aqlm_1x16": "f16", "aqlm_2x8": "f16"}
+         "bnb_quantize": "u8", "lutgemm": "f16", "aqlm_1x16": "f16", "aqlm_2x8": "f16",
+         "qgemm_q3": "f16"}
 
 
 class DeviceWorkload:
@@ -168,6 +178,14 @@ class DeviceWorkload:
             self.cb = t(c["cb"])
             self.x = [t(c["x"]) for _ in range(R)]
             self.out = [torch.empty(c["m"], dtype=torch.float16, device=dev) for _ in range(R)]
+        elif name == "qgemm_q3":
+            from hecbench_b200 import synth
+            mat = synth.q3_pack(c["codes"])
+            self.mat = [t(rot(mat, i)) for i in range(R)]
+            self.sc, self.z = t(c["scales"]), t(c["zeros"])
+            self.x = [t(c["X"]) for _ in range(R)]
+            self.out = [torch.empty((c["Mb"], c["N"]), dtype=torch.float16, device=dev)
+                        for _ in range(R)]
         elif name == "aqlm_2x8":
             self.codes = [t(rot(c["codes"], i)) for i in range(R)]
             self.cbs = t(c["cbs"])
@@ -198,6 +216,9 @@ class DeviceWorkload:
                                [m, m, m, 1 << 30], 65536)
         elif n == "aqlm_2x8":
             hq.code2x8_matvec(self.codes[i], self.x[i], self.out[i], self.cbs, c["m"], c["k"])
+        elif n == "qgemm_q3":
+            hq.qgemm_q3(self.x[i], self.mat[i], self.sc, self.z, c["N"], c["K"], 128,
+                        out=self.out[i])
 
     # host <-> device traffic of one launch on the end-to-end path
     def host_io(self):

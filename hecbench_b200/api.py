@@ -243,20 +243,33 @@ def code2x8_matvec(A, B, C_out, codebooks, prob_m: int, prob_k: int,
 # batched dequant-GEMM (tensor cores)
 # --------------------------------------------------------------------------
 
+_qgemm_ws = {}
+
+
 def qgemm_q3(X, mat, scales, zeros, N: int, K: int, group_size: int = 128,
              out: Optional[torch.Tensor] = None,
-             status: Optional[torch.Tensor] = None) -> torch.Tensor:
+             status: Optional[torch.Tensor] = None, split_k: bool = True) -> torch.Tensor:
     """Y[Mb][N] = X[Mb][K] @ dequant(mat) for the GPTQ 3-bit layout with per-group
     fp16 scales / zeros [K/group_size][N] (no counterpart in the reference tree).
-    `status` (int32[1], optional) receives 1 if a bounded in-kernel wait ran out."""
+    `status` (int32[1], optional) receives 1 if a bounded in-kernel wait ran out.
+    With split_k a zero-initialised scratch matrix is kept per (device, Mb, N)."""
     lib = load_library()
     Mb = X.shape[0]
     if out is None:
         out = torch.empty((Mb, N), dtype=torch.float16, device=X.device)
+    ws_ptr, ws_bytes = 0, 0
+    if split_k:
+        key = (X.device, Mb, N)
+        ws = _qgemm_ws.get(key)
+        if ws is None:
+            ws = torch.zeros(lib.hq_qgemm_workspace_bytes(Mb, N), dtype=torch.uint8,
+                             device=X.device)
+            _qgemm_ws[key] = ws
+        ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
     args = (
         _dev(X, torch.float16, "X"), _dev(mat, torch.int32, "mat"),
         _dev(scales, torch.float16, "scales"), _dev(zeros, torch.float16, "zeros"),
-        _dev(out, torch.float16, "out"), Mb, N, K, group_size,
+        _dev(out, torch.float16, "out"), Mb, N, K, group_size, ws_ptr, ws_bytes,
         0 if status is None else _dev(status, torch.int32, "status"))
     with torch.cuda.device(X.device):
         check("hq_qgemm_q3_f16", lib.hq_qgemm_q3_f16(*args, _stream()))

@@ -9,22 +9,28 @@
 // The contraction is computed transposed so that the weight dimension fills
 // the 128 rows of a tcgen05.mma tile and the token batch is its N dimension:
 //   D[128 n][Mb] += A[128 n][16 k] * B[16 k][Mb],  A = W^T (K-major), B = X^T (K-major)
-// One CTA owns 128 output features and walks K in blocks of 64:
-//   warps 0-3  producers: each thread owns one output feature, reads its six
-//              packed words of the block (coalesced across the warp), turns
-//              every 6-bit pair into half2(q0, q1) with one lookup in a
-//              bank-replicated shared table, applies hfma2 with the group's
-//              scale / -zero, and stores the 64 halves of its row into the
-//              stage's A tile in the 128-byte-swizzled K-major layout the
-//              tensor core reads; the same threads copy the X block into the
-//              B tile; then fence.proxy.async + mbarrier arrive;
-//   warp 4     one elected lane waits for the stage, issues four
+// One CTA owns 128 output features and a range of K blocks of 64 inputs:
+//   warps 0-7  producers: thread (row, half) owns one output feature and one
+//              group of 32 inputs of the block; it reads its three packed
+//              words TWO blocks ahead (registers), turns every 6-bit pair into
+//              half2(q0, q1) with one lookup in a bank-replicated shared table,
+//              applies hfma2 with the group's scale / -zero, and stores its 32
+//              halves into the stage's A tile in the 128-byte-swizzled K-major
+//              layout the tensor core reads; the X block reaches the B tile by
+//              cp.async, also two blocks ahead; then fence.proxy.async +
+//              mbarrier arrive;
+//   warp 8     one elected lane waits for the stage, issues four
 //              tcgen05.mma.cta_group::1.kind::f16 (K = 16 each) with shared
 //              memory descriptors, and commits them to the stage's "empty"
 //              mbarrier; after the last block it commits to the accumulator
 //              barrier;
-//   warps 0-3  epilogue: tcgen05.ld of the warp's 32 TMEM lanes, fp32 -> fp16,
-//              transposed store into Y.
+//   warps 0-7  epilogue: tcgen05.ld of the warp's 32 TMEM lanes, then either
+//              fp32 -> fp16 and a transposed store into Y, or (K split over
+//              several CTAs) fp32 reductions into a scratch matrix that the
+//              last CTA of the tile converts and re-zeroes.
+// Two CTAs share an SM (about 105 KiB of shared memory and 128 TMEM columns
+// each for up to 64 tokens), so one CTA's epilogue and ramp-up hide behind the
+// other's main loop.
 // Every mbarrier wait is bounded: when the limit is hit the thread records a
 // status code, stops waiting and carries on, so the kernel always terminates
 // and frees its tensor memory; the host reads the status word.
@@ -33,17 +39,22 @@
 namespace hq {
 namespace {
 
-constexpr int kStages = 4;
+constexpr int kStages = 3;
+constexpr int kAhead = 1;                   // X blocks requested ahead of the one being unpacked
+constexpr int kWordAhead = 8;               // packed-word blocks in flight (shared-memory ring)
 constexpr int kBlockK = 64;                 // halves per smem row (128 bytes)
 constexpr int kTileN = 128;                 // output features per CTA (UMMA M)
 constexpr int kMaxTokens = 128;             // UMMA N upper bound handled here
 constexpr int kATile = kTileN * 128;        // bytes
-constexpr int kBTile = kMaxTokens * 128;    // bytes
 constexpr int kDeqLut = 64 * 128;           // 64 pair values x 32 lane copies x 4 B
-constexpr int kProducerThreads = 128;
-constexpr int kThreads = 160;
+constexpr int kWordRing = kWordAhead * 256 * 3 * 4;  // 3 words per producer thread per block
+constexpr int kProducerThreads = 256;
+constexpr int kThreads = 288;
 constexpr uint32_t kSpinLimit = 1u << 20;   // bounded mbarrier polls
-constexpr int kSmemBytes = 1024 + kStages * (kATile + kBTile) + kDeqLut + 256;
+
+inline size_t qgemm_smem_bytes(int tokens_padded) {
+  return 1024 + (size_t)kStages * (kATile + tokens_padded * 128) + kWordRing + 256;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -107,34 +118,60 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// pair table: entry v (6 bits) = half2(v & 7, v >> 3), one copy per bank
+__shared__ __align__(16) uint32_t g_pair_lut[64 * 32];
+
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+
 struct QgemmParams {
   const __half* X;
   const int32_t* mat;
   const __half* scales;
   const __half* zeros;
   __half* Y;
+  float* ws;            // fp32 [Mb][N] scratch + per-tile counters, used when ksplit > 1
+  unsigned* counters;
   int* status;
-  int Mb, N, K, group_size, tokens_padded;
+  int Mb, N, K, group_size, tokens_padded, ksplit;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) qgemm_q3_kernel(const QgemmParams p) {
+__global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams p) {
   extern __shared__ unsigned char dsm_raw[];
   // 1024-byte aligned tiles (the swizzle pattern repeats every 1024 bytes)
   const uint32_t raw = smem_u32(dsm_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* sm = dsm_raw + (base - raw);
+  const int kBTile = p.tokens_padded * 128;
   const uint32_t a_tiles = base;
   const uint32_t b_tiles = base + kStages * kATile;
-  unsigned char* deq_lut = sm + kStages * (kATile + kBTile);
-  const uint32_t bars = base + kStages * (kATile + kBTile) + kDeqLut;
+  const uint32_t tiles_bytes = (uint32_t)(kStages * (kATile + kBTile));
+  const uint32_t word_ring = base + tiles_bytes;  // [kWordAhead][3][256] words
+  const uint32_t bars = base + tiles_bytes + kWordRing;
   // barrier slots (8 bytes each): full[kStages], empty[kStages], accum; then the TMEM address
   const uint32_t full0 = bars, empty0 = bars + 8 * kStages, accum_bar = bars + 16 * kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kStages * (kATile + kBTile) + kDeqLut +
-                                                    16 * kStages + 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + tiles_bytes + kWordRing + 16 * kStages + 8);
+  __shared__ unsigned s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kTileN;
-  const int nkb = p.K / kBlockK;
+  // K blocks of this CTA: split index blockIdx.y of p.ksplit
+  const int nkb_total = p.K / kBlockK;
+  const int kb0 = (int)(((long long)nkb_total * blockIdx.y) / p.ksplit);
+  const int kb1 = (int)(((long long)nkb_total * (blockIdx.y + 1)) / p.ksplit);
+  const int nloc = kb1 - kb0;
   bool ok = true;
 
   if (tid == 0) {
@@ -145,13 +182,22 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_q3_kernel(const QgemmParams
     mbar_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // pair table: entry v (6 bits) = half2(v & 7, v >> 3), one copy per bank
   for (int i = tid; i < 64 * 32; i += kThreads) {
     const int v = i >> 5;
-    reinterpret_cast<uint32_t*>(deq_lut)[i] =
-        half2_as_u32(__halves2half2(__int2half_rn(v & 7), __int2half_rn(v >> 3)));
+    g_pair_lut[i] = half2_as_u32(__halves2half2(__int2half_rn(v & 7), __int2half_rn(v >> 3)));
   }
-  if (warp == 4) {
+  // rows of the B tiles beyond the real token count stay zero for the whole kernel
+  for (int idx = tid; idx < kStages * (p.tokens_padded - p.Mb) * 8; idx += kThreads) {
+    const int per = (p.tokens_padded - p.Mb) * 8;
+    const int s = idx / per, r = idx - s * per;
+    const int row = p.Mb + (r >> 3), c = r & 7;
+    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(
+                     b_tiles + (uint32_t)(s * kBTile + (row >> 3) * 1024 + (row & 7) * 128 +
+                                          ((c ^ (row & 7)) * 16))),
+                 "r"(0)
+                 : "memory");
+  }
+  if (warp == 8) {
     // 128 columns of tensor memory: accumulator D[128 lanes][tokens <= 128] fp32
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
@@ -164,105 +210,166 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_q3_kernel(const QgemmParams
   tc_fence_after();
   const uint32_t tmem_d = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < 8) {
     // ------------------------------ producers ------------------------------
-    const int t = tid;              // output feature n0 + t, A-tile row t
-    const int n = n0 + t;
-    const unsigned char* lut_lane = deq_lut + lane * 4;
-    const uint32_t a_row = (uint32_t)((t >> 3) * 1024 + (t & 7) * 128);
-    const int swz = t & 7;
-    __half2 sc2 = __float2half2_rn(0.f), nz2 = sc2;
-    int cur_group = -1;
-    for (int kb = 0; kb < nkb; kb++) {
-      const int s = kb % kStages;
-      const uint32_t round = (uint32_t)(kb / kStages);
-      // packed words of this block: rows 6*kb .. 6*kb+5 (two groups of 32 inputs)
-      uint32_t w[6];
+    const int row = tid & 127;      // output feature n0 + row, A-tile row
+    const int hf = tid >> 7;        // which group of 32 inputs of the block
+    const int n = n0 + row;
+    // Every instruction here runs once per K block in all 16 producer warps of
+    // the SM, so the loop carries running pointers, stage counters and phase
+    // bits instead of recomputing them (no division, no modulo).
+    const unsigned char* lut = reinterpret_cast<const unsigned char*>(g_pair_lut);
+    const uint32_t lane4 = (uint32_t)lane * 4u;
+    const uint32_t a_row = a_tiles + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);
+    const uint32_t chunk0 = (uint32_t)(((hf * 4 + 0) ^ (row & 7)) * 16);
+    const uint32_t chunk1 = (uint32_t)(((hf * 4 + 1) ^ (row & 7)) * 16);
+    const uint32_t chunk2 = (uint32_t)(((hf * 4 + 2) ^ (row & 7)) * 16);
+    const uint32_t chunk3 = (uint32_t)(((hf * 4 + 3) ^ (row & 7)) * 16);
+    const uint32_t my_ring = word_ring + (uint32_t)tid * 4u;  // slot (blk, i): + (blk*3 + i)*1024
+    const int32_t* wsrc = p.mat + (size_t)(6 * kb0 + 3 * hf) * p.N + n;  // next block to request
+    const size_t wstep = (size_t)6 * p.N;
+    // X copy: this thread moves up to four 16-byte chunks (token r, chunk c) per block
+    uint32_t xdst[4];
+    const uint4* xsrc[4];
+    bool xok[4];
 #pragma unroll
-      for (int i = 0; i < 6; i++) w[i] = ldg_stream_u32(p.mat + (size_t)(6 * kb + i) * p.N + n);
-      const int g = (kb * kBlockK) / p.group_size;
-      if (g != cur_group) {
-        cur_group = g;
-        const __half sc = p.scales[(size_t)g * p.N + n];
-        const __half z = p.zeros[(size_t)g * p.N + n];
-        sc2 = __half2half2(sc);
-        nz2 = __half2half2(__hneg(z));
-      }
-      if (!mbar_wait(empty0 + 8 * s, (round & 1u) ^ 1u, ok)) ok = false;
+    for (int q = 0; q < 4; q++) {
+      const int idx = tid + q * kProducerThreads;
+      const int r = idx >> 3, c = idx & 7;
+      xok[q] = idx < p.Mb * 8;
+      xdst[q] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) * 16));
+      xsrc[q] = reinterpret_cast<const uint4*>(p.X + (size_t)(xok[q] ? r : 0) * p.K +
+                                               (size_t)kb0 * kBlockK) + c;
+    }
+    const __half* scp = p.scales + (size_t)((kb0 * kBlockK) / p.group_size) * p.N + n;
+    const __half* zp = p.zeros + (size_t)((kb0 * kBlockK) / p.group_size) * p.N + n;
+    const int blocks_per_group = p.group_size / kBlockK;
+    int group_left = blocks_per_group - (kb0 % blocks_per_group);  // blocks left in the group
+    __half2 sc2 = __half2half2(*scp), nz2 = __half2half2(__hneg(*zp));
 
-      // ---- A tile: 64 weights of row t, 8 chunks of 16 bytes ----
-      const uint32_t a_stage = a_tiles + s * kATile + a_row;
-#pragma unroll
-      for (int half = 0; half < 2; half++) {
-        const uint32_t w0 = w[3 * half], w1 = w[3 * half + 1], w2 = w[3 * half + 2];
-        // sixteen 6-bit pair values of the 96-bit stream
-        uint32_t pv[16];
-#pragma unroll
-        for (int i = 0; i < 5; i++) pv[i] = (w0 >> (6 * i)) & 63u;
-        pv[5] = __funnelshift_r(w0, w1, 30) & 63u;
-#pragma unroll
-        for (int i = 0; i < 4; i++) pv[6 + i] = (w1 >> (4 + 6 * i)) & 63u;
-        pv[10] = __funnelshift_r(w1, w2, 28) & 63u;
-#pragma unroll
-        for (int i = 0; i < 5; i++) pv[11 + i] = (w2 >> (2 + 6 * i)) & 63u;
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-          uint32_t o[4];
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const uint32_t q2 = *reinterpret_cast<const uint32_t*>(lut_lane + (pv[4 * c + e] << 7));
-            o[e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
-          }
-          const int chunk = half * 4 + c;  // 16-byte chunk (8 halves) of the 128-byte row
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                           a_stage + (uint32_t)((chunk ^ swz) * 16)),
-                       "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                       : "memory");
-        }
+    int words_left = nloc;  // word blocks not yet requested
+    auto request_words = [&](uint32_t slot) {
+      if (words_left > 0) {
+        const uint32_t dst = my_ring + slot * (3 * 1024);
+        cp_async_4(dst, wsrc);
+        cp_async_4(dst + 1024, wsrc + p.N);
+        cp_async_4(dst + 2048, wsrc + 2 * (size_t)p.N);
+        wsrc += wstep;
       }
-      // ---- B tile: X[token][kb*64 .. +63], tokens_padded rows of 8 chunks ----
-      const uint32_t b_stage = b_tiles + s * kBTile;
-      for (int idx = t; idx < p.tokens_padded * 8; idx += kProducerThreads) {
-        const int row = idx >> 3, c = idx & 7;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < p.Mb)
-          v = __ldg(reinterpret_cast<const uint4*>(p.X + (size_t)row * p.K + kb * kBlockK) + c);
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                         b_stage + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 +
-                                              ((c ^ (row & 7)) * 16))),
-                     "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+      words_left--;
+      cp_async_commit();
+    };
+    int x_left = nloc;            // X blocks not yet requested
+    uint32_t x_stage = 0;         // stage of the next X block to request
+    uint32_t x_parity = 1;        // parity that means "the tensor core released that stage"
+    auto request_x = [&]() {
+      if (x_left > 0) {
+        if (!mbar_wait(empty0 + 8 * x_stage, x_parity, ok)) ok = false;
+        const uint32_t b_stage = b_tiles + x_stage * (uint32_t)kBTile;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          if (xok[q]) cp_async_16(b_stage + xdst[q], xsrc[q]);
+          xsrc[q] += kBlockK * 2 / 16;
+        }
+        if (++x_stage == kStages) { x_stage = 0; x_parity ^= 1u; }
+      }
+      x_left--;
+      cp_async_commit();
+    };
+    // cp.async group order: x(0..kAhead-1), words(0..kWordAhead-1), then per
+    // iteration i: x(i+kAhead), words(i+kWordAhead).
+#pragma unroll
+    for (int d = 0; d < kAhead; d++) request_x();
+#pragma unroll
+    for (int d = 0; d < kWordAhead; d++) request_words((uint32_t)d);
+
+    uint32_t a_stage = 0;
+    for (int i = 0; i < nloc; i++) {
+      request_x();
+      // newest group index is now P + 2*i with P = kAhead + kWordAhead; x(i) is
+      // group i (prologue) or P + 2*(i - kAhead), words(i) is group kAhead + i
+      // (prologue) or P + 2*(i - kWordAhead) + 1: all of them are at or below
+      // P + 2*i - 2*kAhead, so the newest 2*kAhead groups may stay pending
+      cp_async_wait<2 * kAhead>();
+      const uint32_t slot = (uint32_t)i & (kWordAhead - 1);
+      uint32_t w0, w1, w2;
+      {
+        const uint32_t src = my_ring + slot * (3 * 1024);
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+1024];" : "=r"(w1) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+2048];" : "=r"(w2) : "r"(src));
+      }
+      request_words(slot);
+      // sixteen 6-bit pair values of the 96-bit stream, as byte offsets (v << 7) | lane*4
+      uint32_t po[16];
+      po[0] = ((w0 << 7) & 0x1f80u) | lane4;
+      po[1] = ((w0 << 1) & 0x1f80u) | lane4;
+#pragma unroll
+      for (int q = 2; q < 5; q++) po[q] = ((w0 >> (6 * q - 7)) & 0x1f80u) | lane4;
+      po[5] = (__funnelshift_r(w0, w1, 23) & 0x1f80u) | lane4;
+      po[6] = ((w1 << 3) & 0x1f80u) | lane4;
+#pragma unroll
+      for (int q = 1; q < 4; q++) po[6 + q] = ((w1 >> (6 * q - 3)) & 0x1f80u) | lane4;
+      po[10] = (__funnelshift_r(w1, w2, 21) & 0x1f80u) | lane4;
+      po[11] = ((w2 << 5) & 0x1f80u) | lane4;
+#pragma unroll
+      for (int q = 1; q < 5; q++) po[11 + q] = ((w2 >> (6 * q - 5)) & 0x1f80u) | lane4;
+      const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
+      const uint32_t chunk[4] = {chunk0, chunk1, chunk2, chunk3};
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const uint32_t q2 = *reinterpret_cast<const uint32_t*>(lut + po[4 * c + e]);
+          o[e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
+        }
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + chunk[c]), "r"(o[0]),
+                     "r"(o[1]), "r"(o[2]), "r"(o[3])
                      : "memory");
       }
       fence_async_smem();
-      mbar_arrive(full0 + 8 * s);
+      mbar_arrive(full0 + 8 * a_stage);
+      if (++a_stage == kStages) a_stage = 0;
+      if (--group_left == 0) {  // next block starts a new scale / zero group
+        group_left = blocks_per_group;
+        scp += p.N;
+        zp += p.N;
+        if (i + 1 < nloc) {
+          sc2 = __half2half2(*scp);
+          nz2 = __half2half2(__hneg(*zp));
+        }
+      }
     }
+    cp_async_wait<0>();
   } else if (lane == 0) {
     // ------------------------------ MMA issuer ------------------------------
     // instruction descriptor: D fp32, A/B fp16, both K-major, N = tokens_padded, M = 128
     const uint32_t idesc = (1u << 4) | ((uint32_t)(p.tokens_padded >> 3) << 17) |
                            ((uint32_t)(kTileN >> 4) << 24);
-    for (int kb = 0; kb < nkb; kb++) {
-      const int s = kb % kStages;
-      const uint32_t round = (uint32_t)(kb / kStages);
-      if (!mbar_wait(full0 + 8 * s, round & 1u, ok)) ok = false;
+    uint32_t st = 0, parity = 0;
+    for (int i = 0; i < nloc; i++) {
+      if (!mbar_wait(full0 + 8 * st, parity, ok)) ok = false;
       tc_fence_after();
-      const uint64_t adesc = smem_desc(a_tiles + s * kATile);
-      const uint64_t bdesc = smem_desc(b_tiles + s * kBTile);
+      const uint64_t adesc = smem_desc(a_tiles + st * kATile);
+      const uint64_t bdesc = smem_desc(b_tiles + st * kBTile);
 #pragma unroll
-      for (int i = 0; i < kBlockK / 16; i++)
-        umma_f16(tmem_d, adesc + 2 * i, bdesc + 2 * i, idesc, (kb | i) != 0 ? 1u : 0u);
-      umma_commit(empty0 + 8 * s);
+      for (int k = 0; k < kBlockK / 16; k++)
+        umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+      umma_commit(empty0 + 8 * st);
+      if (++st == kStages) { st = 0; parity ^= 1u; }
     }
     umma_commit(accum_bar);
   }
 
-  if (warp < 4) {
+  if (warp < 8) {
     // ------------------------------ epilogue ------------------------------
     if (!mbar_wait(accum_bar, 0, ok)) ok = false;
     tc_fence_after();
-    const int n = n0 + tid;  // TMEM lane = D row = output feature
-    const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
-    for (int j0 = 0; j0 < p.tokens_padded; j0 += 16) {
+    const int n = n0 + (warp & 3) * 32 + lane;  // TMEM lane = D row = output feature
+    const uint32_t taddr = tmem_d + ((uint32_t)((warp & 3) * 32) << 16);
+    // warps 0-3 take the even 16-token chunks, warps 4-7 the odd ones
+    for (int j0 = (warp >> 2) * 16; j0 < p.tokens_padded; j0 += 32) {
       uint32_t r[16];
       asm volatile(
           "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -272,47 +379,105 @@ __global__ void __launch_bounds__(kThreads, 1) qgemm_q3_kernel(const QgemmParams
             "=r"(r[14]), "=r"(r[15])
           : "r"(taddr + (uint32_t)j0));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (p.ksplit == 1) {
 #pragma unroll
-      for (int j = 0; j < 16; j++)
-        if (j0 + j < p.Mb) p.Y[(size_t)(j0 + j) * p.N + n] = __float2half_rn(__uint_as_float(r[j]));
+        for (int j = 0; j < 16; j++)
+          if (j0 + j < p.Mb)
+            p.Y[(size_t)(j0 + j) * p.N + n] = __float2half_rn(__uint_as_float(r[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          if (j0 + j < p.Mb)
+            asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p.ws + (size_t)(j0 + j) * p.N + n),
+                         "f"(__uint_as_float(r[j]))
+                         : "memory");
+      }
     }
   }
   if (!ok && p.status != nullptr) atomicExch(p.status, 1);
   tc_fence_before();
+  if (p.ksplit > 1) __threadfence();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(128)
                  : "memory");
+  }
+  if (p.ksplit > 1) {
+    // the last CTA of this tile converts the scratch tile to fp16 and re-zeroes it
+    if (tid == 0) {
+      const unsigned prev = atomicAdd(p.counters + blockIdx.x, 1u);
+      s_last = (prev == (unsigned)p.ksplit - 1u) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      for (int idx = tid; idx < p.Mb * kTileN; idx += kThreads) {
+        const int j = idx / kTileN, c = idx - j * kTileN;
+        float* w = p.ws + (size_t)j * p.N + n0 + c;
+        p.Y[(size_t)j * p.N + n0 + c] = __float2half_rn(__ldcg(w));
+        *w = 0.f;
+      }
+      if (tid == 0) p.counters[blockIdx.x] = 0u;
+    }
   }
 }
 
 }  // namespace
 }  // namespace hq
 
-extern "C" int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_half,
-                               const void* zeros_half, void* Y_half, int Mb, int N, int K,
-                               int group_size, int* status_word, hq_stream_t stream) {
+extern "C" {
+
+size_t hq_qgemm_workspace_bytes(int Mb, int N) {
+  if (Mb <= 0 || N <= 0) return 0;
+  return ((size_t)Mb * N * 4 + 255) / 256 * 256 + ((size_t)(N / hq::kTileN + 1) * 4 + 255) / 256 * 256;
+}
+
+int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_half,
+                    const void* zeros_half, void* Y_half, int Mb, int N, int K, int group_size,
+                    void* workspace, size_t workspace_bytes, int* status_word,
+                    hq_stream_t stream) {
   using namespace hq;
   if (!X_half || !mat || !scales_half || !zeros_half || !Y_half) return HQ_ERR_NULL_POINTER;
   if (Mb <= 0 || Mb > kMaxTokens || N <= 0 || K <= 0 || N % kTileN != 0 || K % kBlockK != 0)
     return HQ_ERR_BAD_SHAPE;
   if (group_size <= 0 || group_size % kBlockK != 0 || K % group_size != 0) return HQ_ERR_BAD_SHAPE;
   if (!aligned16(X_half) || !aligned4(mat) || (K % 8) != 0) return HQ_ERR_MISALIGNED;
+  const int tokens_padded = (Mb + 15) / 16 * 16;
+  const size_t smem = qgemm_smem_bytes(tokens_padded);
   cudaError_t e = cudaFuncSetAttribute(qgemm_q3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kSmemBytes);
+                                       (int)smem);
   if (e != cudaSuccess) return cuda_status(e);
+  // K split: only with a workspace, and only when the tiles alone cannot fill
+  // the CTA slots of the machine (two per SM)
+  const int tiles = N / kTileN;
+  const int slots = 2 * sm_count();
+  int ksplit = 1;
+  if (workspace != nullptr && workspace_bytes >= hq_qgemm_workspace_bytes(Mb, N) &&
+      aligned16(workspace)) {
+    ksplit = slots / tiles;
+    const int nkb = K / kBlockK;
+    if (ksplit > nkb / 8) ksplit = nkb / 8;
+    if (ksplit < 1) ksplit = 1;
+  }
   QgemmParams prm;
   prm.X = reinterpret_cast<const __half*>(X_half);
   prm.mat = mat;
   prm.scales = reinterpret_cast<const __half*>(scales_half);
   prm.zeros = reinterpret_cast<const __half*>(zeros_half);
   prm.Y = reinterpret_cast<__half*>(Y_half);
+  prm.ws = reinterpret_cast<float*>(workspace);
+  prm.counters = workspace ? reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
+                                                         ((size_t)Mb * N * 4 + 255) / 256 * 256)
+                           : nullptr;
   prm.status = status_word;
   prm.Mb = Mb;
   prm.N = N;
   prm.K = K;
   prm.group_size = group_size;
-  prm.tokens_padded = (Mb + 15) / 16 * 16;
-  qgemm_q3_kernel<<<N / kTileN, kThreads, kSmemBytes, (cudaStream_t)stream>>>(prm);
+  prm.tokens_padded = tokens_padded;
+  prm.ksplit = ksplit;
+  qgemm_q3_kernel<<<dim3(tiles, ksplit), kThreads, smem, (cudaStream_t)stream>>>(prm);
   return launch_status();
 }
+
+}  // extern "C"

@@ -164,11 +164,16 @@ int hq_aqlm_2x8_matvec(const void* codes, const void* x_half, void* out_half,
  * half[K/group_size][N]: W[k][n] = hfma(half(q), scale, -zero), fp32
  * accumulation on the sm_100a tensor cores (tcgen05 / tensor memory), fp16
  * output.  No counterpart in the reference tree.  1 <= Mb <= 128,
- * N % 128 == 0, K % group_size == 0, group_size % 64 == 0.  status_word
- * (device int, nullable) is set to 1 if a bounded in-kernel wait ran out. */
+ * N % 128 == 0, K % group_size == 0, group_size % 64 == 0.  workspace
+ * (nullable) is zero-initialised device scratch of hq_qgemm_workspace_bytes
+ * bytes that lets the kernel split K over several CTAs when N alone gives too
+ * few tiles to fill the GPU; every call leaves it zero.  status_word (device
+ * int, nullable) is set to 1 if a bounded in-kernel wait ran out. */
+size_t hq_qgemm_workspace_bytes(int Mb, int N);
 int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_half,
                     const void* zeros_half, void* Y_half, int Mb, int N, int K, int group_size,
-                    int* status_word, hq_stream_t stream);
+                    void* workspace, size_t workspace_bytes, int* status_word,
+                    hq_stream_t stream);
 
 #ifdef __cplusplus
 }
