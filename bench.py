@@ -411,24 +411,42 @@ def main():
     if err is not None and err > 1e-2:
         raise SystemExit(f"parity guard failed before timing: rel err {err}")
 
+    # N > 1: every rank holds its output-feature shard of each of the R layers
+    # (weak scaling: the layer grows with N) and the slices of every layer are
+    # all-gathered over NCCL right after its kernel, as a decoder needs them.
+    gathered = None
+    if world > 1 and hasattr(wl, "out"):
+        gathered = [torch.empty(world * wl.out[i].numel(), dtype=wl.out[i].dtype, device=dev)
+                    for i in range(R)]
+
+    def layer(i):
+        wl.launch(i)
+        if gathered is not None:
+            dist.all_gather_into_tensor(gathered[i], wl.out[i].view(-1))
+
     stream = torch.cuda.Stream()
     graph = None
     with torch.cuda.stream(stream):
         for i in range(R):
-            wl.launch(i)
+            layer(i)
         stream.synchronize()
         if not args.no_graph:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                for i in range(R):
-                    wl.launch(i)
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for i in range(R):
+                        layer(i)
+            except Exception as exc:  # NCCL capture not available: launch eagerly
+                print(f"[bench] graph capture failed ({exc}); running eagerly", file=sys.stderr)
+                graph = None
+                torch.cuda.synchronize()
 
     def step():
         if graph is not None:
             graph.replay()
         else:
             for i in range(R):
-                wl.launch(i)
+                layer(i)
 
     def barrier():
         if world > 1:
@@ -469,7 +487,7 @@ def main():
             def e2e_step():
                 for i in range(R):
                     wl.x[i].copy_(hin[i], non_blocking=True)
-                    wl.launch(i)
+                    layer(i)
                     hout[i].copy_(wl.out[i], non_blocking=True)
             for _ in range(3):
                 e2e_step()
@@ -503,7 +521,9 @@ def main():
                        "l2": "inputs larger than L2 (replicas rotate, R x bytes >> 126 MB)",
                        "algorithmic_bytes_per_launch": wl.bytes,
                        "launch": "cuda graph of R launches" if graph is not None else "eager",
-                       "parallelism": f"{world} x independent row shards"},
+                       "parallelism": ("single GPU" if world == 1 else
+                                       f"output features sharded over {world} GPUs, NCCL "
+                                       "all-gather of the slices after every layer")},
             "us_per_gemv": us_per_launch,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_src}",

@@ -10,16 +10,22 @@
 // the 128 rows of a tcgen05.mma tile and the token batch is its N dimension:
 //   D[128 n][Mb] += A[128 n][16 k] * B[16 k][Mb],  A = W^T (K-major), B = X^T (K-major)
 // One CTA owns 128 output features and a range of K blocks of 64 inputs:
-//   warps 0-7  producers: thread (row, half) owns one output feature and one
+//   warp 9     (one lane) streams the packed words: one TMA box of 6 rows x 128
+//              columns per block into an 8-deep shared-memory ring;
+//   warp 10    (one lane) streams X: one TMA box of 64 inputs x all tokens per
+//              block straight into the stage's B tile in the 128-byte-swizzled
+//              K-major layout (rows beyond the token count are zero-filled by
+//              the TMA unit);
+//   warps 0-7  unpack: thread (row, half) owns one output feature and one
 //              group of 32 inputs of the block; it reads its three packed
-//              words TWO blocks ahead (registers), turns every 6-bit pair into
-//              half2(q0, q1) with one lookup in a bank-replicated shared table,
-//              applies hfma2 with the group's scale / -zero, and stores its 32
-//              halves into the stage's A tile in the 128-byte-swizzled K-major
-//              layout the tensor core reads; the X block reaches the B tile by
-//              cp.async, also two blocks ahead; then fence.proxy.async +
-//              mbarrier arrive;
-//   warp 8     one elected lane waits for the stage, issues four
+//              words from the ring, turns every 6-bit pair into half2(q0, q1)
+//              with one lookup in a bank-replicated shared table, applies
+//              hfma2 with the group's scale / -zero, and stores its 32 halves
+//              into the stage's A tile in the swizzled K-major layout; then
+//              fence.proxy.async + mbarrier arrive.  These threads have no
+//              asynchronous copies of their own in flight, so the fence only
+//              orders their four stores;
+//   warp 8     (one lane) waits for both tiles of the stage, issues four
 //              tcgen05.mma.cta_group::1.kind::f16 (K = 16 each) with shared
 //              memory descriptors, and commits them to the stage's "empty"
 //              mbarrier; after the last block it commits to the accumulator
@@ -30,30 +36,31 @@
 //              last CTA of the tile converts and re-zeroes.
 // Two CTAs share an SM (about 105 KiB of shared memory and 128 TMEM columns
 // each for up to 64 tokens), so one CTA's epilogue and ramp-up hide behind the
-// other's main loop.
+// other's main loop.  No TMA load uses cluster multicast.
 // Every mbarrier wait is bounded: when the limit is hit the thread records a
 // status code, stops waiting and carries on, so the kernel always terminates
 // and frees its tensor memory; the host reads the status word.
+#include <cuda.h>
+
 #include "hq_common.cuh"
 
 namespace hq {
 namespace {
 
 constexpr int kStages = 3;
-constexpr int kAhead = 1;                   // X blocks requested ahead of the one being unpacked
 constexpr int kWordAhead = 8;               // packed-word blocks in flight (shared-memory ring)
 constexpr int kBlockK = 64;                 // halves per smem row (128 bytes)
 constexpr int kTileN = 128;                 // output features per CTA (UMMA M)
 constexpr int kMaxTokens = 128;             // UMMA N upper bound handled here
 constexpr int kATile = kTileN * 128;        // bytes
 constexpr int kDeqLut = 64 * 128;           // 64 pair values x 32 lane copies x 4 B
-constexpr int kWordRing = kWordAhead * 256 * 3 * 4;  // 3 words per producer thread per block
+constexpr int kWordRing = kWordAhead * 6 * 512;  // one box of 6 rows x 128 columns per block
 constexpr int kProducerThreads = 256;
-constexpr int kThreads = 288;
+constexpr int kThreads = 352;               // 8 unpack warps, MMA warp, two TMA warps
 constexpr uint32_t kSpinLimit = 1u << 20;   // bounded mbarrier polls
 
 inline size_t qgemm_smem_bytes(int tokens_padded) {
-  return 1024 + (size_t)kStages * (kATile + tokens_padded * 128) + kWordRing + 256;
+  return 1024 + (size_t)kStages * (kATile + tokens_padded * 128) + kWordRing + 512;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -81,6 +88,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool he
     if (done) return true;
   }
   return false;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+// 2-D tiled TMA load (no multicast) completing on an mbarrier of this CTA
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -132,13 +152,7 @@ __device__ __forceinline__ void cp_async_wait() {
 // pair table: entry v (6 bits) = half2(v & 7, v >> 3), one copy per bank
 __shared__ __align__(16) uint32_t g_pair_lut[64 * 32];
 
-__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
-
 struct QgemmParams {
-  const __half* X;
-  const int32_t* mat;
   const __half* scales;
   const __half* zeros;
   __half* Y;
@@ -148,7 +162,9 @@ struct QgemmParams {
   int Mb, N, K, group_size, tokens_padded, ksplit;
 };
 
-__global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams p) {
+__global__ void __launch_bounds__(kThreads, 2)
+qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                const QgemmParams p) {
   extern __shared__ unsigned char dsm_raw[];
   // 1024-byte aligned tiles (the swizzle pattern repeats every 1024 bytes)
   const uint32_t raw = smem_u32(dsm_raw);
@@ -158,11 +174,17 @@ __global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams
   const uint32_t a_tiles = base;
   const uint32_t b_tiles = base + kStages * kATile;
   const uint32_t tiles_bytes = (uint32_t)(kStages * (kATile + kBTile));
-  const uint32_t word_ring = base + tiles_bytes;  // [kWordAhead][3][256] words
+  const uint32_t word_ring = base + tiles_bytes;  // [kWordAhead][6 rows][128 columns] words
   const uint32_t bars = base + tiles_bytes + kWordRing;
-  // barrier slots (8 bytes each): full[kStages], empty[kStages], accum; then the TMEM address
-  const uint32_t full0 = bars, empty0 = bars + 8 * kStages, accum_bar = bars + 16 * kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + tiles_bytes + kWordRing + 16 * kStages + 8);
+  // barrier slots (8 bytes each)
+  const uint32_t full0 = bars;                          // A tile written (256 arrivals)
+  const uint32_t empty0 = full0 + 8 * kStages;          // stage released by the tensor core
+  const uint32_t xfull0 = empty0 + 8 * kStages;         // B tile landed (TMA bytes)
+  const uint32_t wfull0 = xfull0 + 8 * kStages;         // word box landed (TMA bytes)
+  const uint32_t wempty0 = wfull0 + 8 * kWordAhead;     // word box read by all 256 threads
+  const uint32_t accum_bar = wempty0 + 8 * kWordAhead;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(
+      sm + tiles_bytes + kWordRing + 8 * (3 * kStages + 2 * kWordAhead + 1));
   __shared__ unsigned s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -178,6 +200,11 @@ __global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams
     for (int s = 0; s < kStages; s++) {
       mbar_init(full0 + 8 * s, kProducerThreads);
       mbar_init(empty0 + 8 * s, 1);
+      mbar_init(xfull0 + 8 * s, 1);
+    }
+    for (int s = 0; s < kWordAhead; s++) {
+      mbar_init(wfull0 + 8 * s, 1);
+      mbar_init(wempty0 + 8 * s, kProducerThreads);
     }
     mbar_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -185,17 +212,6 @@ __global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams
   for (int i = tid; i < 64 * 32; i += kThreads) {
     const int v = i >> 5;
     g_pair_lut[i] = half2_as_u32(__halves2half2(__int2half_rn(v & 7), __int2half_rn(v >> 3)));
-  }
-  // rows of the B tiles beyond the real token count stay zero for the whole kernel
-  for (int idx = tid; idx < kStages * (p.tokens_padded - p.Mb) * 8; idx += kThreads) {
-    const int per = (p.tokens_padded - p.Mb) * 8;
-    const int s = idx / per, r = idx - s * per;
-    const int row = p.Mb + (r >> 3), c = r & 7;
-    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(
-                     b_tiles + (uint32_t)(s * kBTile + (row >> 3) * 1024 + (row & 7) * 128 +
-                                          ((c ^ (row & 7)) * 16))),
-                 "r"(0)
-                 : "memory");
   }
   if (warp == 8) {
     // 128 columns of tensor memory: accumulator D[128 lanes][tokens <= 128] fp32
@@ -211,95 +227,38 @@ __global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams
   const uint32_t tmem_d = *tmem_slot;
 
   if (warp < 8) {
-    // ------------------------------ producers ------------------------------
+    // ------------------------------ unpack warps ------------------------------
+    // Every instruction here runs once per K block in all 16 unpack warps of the
+    // SM, so the loop carries running counters and phase bits (no division).
     const int row = tid & 127;      // output feature n0 + row, A-tile row
     const int hf = tid >> 7;        // which group of 32 inputs of the block
     const int n = n0 + row;
-    // Every instruction here runs once per K block in all 16 producer warps of
-    // the SM, so the loop carries running pointers, stage counters and phase
-    // bits instead of recomputing them (no division, no modulo).
     const unsigned char* lut = reinterpret_cast<const unsigned char*>(g_pair_lut);
     const uint32_t lane4 = (uint32_t)lane * 4u;
     const uint32_t a_row = a_tiles + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);
-    const uint32_t chunk0 = (uint32_t)(((hf * 4 + 0) ^ (row & 7)) * 16);
-    const uint32_t chunk1 = (uint32_t)(((hf * 4 + 1) ^ (row & 7)) * 16);
-    const uint32_t chunk2 = (uint32_t)(((hf * 4 + 2) ^ (row & 7)) * 16);
-    const uint32_t chunk3 = (uint32_t)(((hf * 4 + 3) ^ (row & 7)) * 16);
-    const uint32_t my_ring = word_ring + (uint32_t)tid * 4u;  // slot (blk, i): + (blk*3 + i)*1024
-    const int32_t* wsrc = p.mat + (size_t)(6 * kb0 + 3 * hf) * p.N + n;  // next block to request
-    const size_t wstep = (size_t)6 * p.N;
-    // X copy: this thread moves up to four 16-byte chunks (token r, chunk c) per block
-    uint32_t xdst[4];
-    const uint4* xsrc[4];
-    bool xok[4];
-#pragma unroll
-    for (int q = 0; q < 4; q++) {
-      const int idx = tid + q * kProducerThreads;
-      const int r = idx >> 3, c = idx & 7;
-      xok[q] = idx < p.Mb * 8;
-      xdst[q] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) * 16));
-      xsrc[q] = reinterpret_cast<const uint4*>(p.X + (size_t)(xok[q] ? r : 0) * p.K +
-                                               (size_t)kb0 * kBlockK) + c;
-    }
+    const uint32_t chunk[4] = {(uint32_t)(((hf * 4 + 0) ^ (row & 7)) * 16),
+                               (uint32_t)(((hf * 4 + 1) ^ (row & 7)) * 16),
+                               (uint32_t)(((hf * 4 + 2) ^ (row & 7)) * 16),
+                               (uint32_t)(((hf * 4 + 3) ^ (row & 7)) * 16)};
+    // word box: [6 rows][128 columns]; this thread reads rows 3*hf..3*hf+2 of column `row`
+    const uint32_t my_words = word_ring + (uint32_t)((3 * hf) * 512 + row * 4);
     const __half* scp = p.scales + (size_t)((kb0 * kBlockK) / p.group_size) * p.N + n;
     const __half* zp = p.zeros + (size_t)((kb0 * kBlockK) / p.group_size) * p.N + n;
     const int blocks_per_group = p.group_size / kBlockK;
     int group_left = blocks_per_group - (kb0 % blocks_per_group);  // blocks left in the group
     __half2 sc2 = __half2half2(*scp), nz2 = __half2half2(__hneg(*zp));
 
-    int words_left = nloc;  // word blocks not yet requested
-    auto request_words = [&](uint32_t slot) {
-      if (words_left > 0) {
-        const uint32_t dst = my_ring + slot * (3 * 1024);
-        cp_async_4(dst, wsrc);
-        cp_async_4(dst + 1024, wsrc + p.N);
-        cp_async_4(dst + 2048, wsrc + 2 * (size_t)p.N);
-        wsrc += wstep;
-      }
-      words_left--;
-      cp_async_commit();
-    };
-    int x_left = nloc;            // X blocks not yet requested
-    uint32_t x_stage = 0;         // stage of the next X block to request
-    uint32_t x_parity = 1;        // parity that means "the tensor core released that stage"
-    auto request_x = [&]() {
-      if (x_left > 0) {
-        if (!mbar_wait(empty0 + 8 * x_stage, x_parity, ok)) ok = false;
-        const uint32_t b_stage = b_tiles + x_stage * (uint32_t)kBTile;
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          if (xok[q]) cp_async_16(b_stage + xdst[q], xsrc[q]);
-          xsrc[q] += kBlockK * 2 / 16;
-        }
-        if (++x_stage == kStages) { x_stage = 0; x_parity ^= 1u; }
-      }
-      x_left--;
-      cp_async_commit();
-    };
-    // cp.async group order: x(0..kAhead-1), words(0..kWordAhead-1), then per
-    // iteration i: x(i+kAhead), words(i+kWordAhead).
-#pragma unroll
-    for (int d = 0; d < kAhead; d++) request_x();
-#pragma unroll
-    for (int d = 0; d < kWordAhead; d++) request_words((uint32_t)d);
-
-    uint32_t a_stage = 0;
+    uint32_t a_stage = 0, a_parity = 1;  // parity meaning "stage released" (first pass: free)
+    uint32_t w_slot = 0, w_parity = 0;
     for (int i = 0; i < nloc; i++) {
-      request_x();
-      // newest group index is now P + 2*i with P = kAhead + kWordAhead; x(i) is
-      // group i (prologue) or P + 2*(i - kAhead), words(i) is group kAhead + i
-      // (prologue) or P + 2*(i - kWordAhead) + 1: all of them are at or below
-      // P + 2*i - 2*kAhead, so the newest 2*kAhead groups may stay pending
-      cp_async_wait<2 * kAhead>();
-      const uint32_t slot = (uint32_t)i & (kWordAhead - 1);
+      if (!mbar_wait(wfull0 + 8 * w_slot, w_parity, ok)) ok = false;
       uint32_t w0, w1, w2;
       {
-        const uint32_t src = my_ring + slot * (3 * 1024);
+        const uint32_t src = my_words + w_slot * (6 * 512);
         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+1024];" : "=r"(w1) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+2048];" : "=r"(w2) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+512];" : "=r"(w1) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+1024];" : "=r"(w2) : "r"(src));
       }
-      request_words(slot);
       // sixteen 6-bit pair values of the 96-bit stream, as byte offsets (v << 7) | lane*4
       uint32_t po[16];
       po[0] = ((w0 << 7) & 0x1f80u) | lane4;
@@ -314,23 +273,27 @@ __global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams
       po[11] = ((w2 << 5) & 0x1f80u) | lane4;
 #pragma unroll
       for (int q = 1; q < 5; q++) po[11 + q] = ((w2 >> (6 * q - 5)) & 0x1f80u) | lane4;
-      const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
-      const uint32_t chunk[4] = {chunk0, chunk1, chunk2, chunk3};
+      uint32_t o[16];
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
-        uint32_t o[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const uint32_t q2 = *reinterpret_cast<const uint32_t*>(lut + po[4 * c + e]);
-          o[e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
-        }
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + chunk[c]), "r"(o[0]),
-                     "r"(o[1]), "r"(o[2]), "r"(o[3])
-                     : "memory");
+      for (int e = 0; e < 16; e++) {
+        const uint32_t q2 = *reinterpret_cast<const uint32_t*>(lut + po[e]);
+        o[e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
       }
+      // the ring slot is released only now: the lookups above consumed the words,
+      // so the three loads have certainly returned
+      mbar_arrive(wempty0 + 8 * w_slot);
+      if (++w_slot == kWordAhead) { w_slot = 0; w_parity ^= 1u; }
+      // the A tile of this stage must have been released by the tensor core
+      if (!mbar_wait(empty0 + 8 * a_stage, a_parity, ok)) ok = false;
+      const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
+#pragma unroll
+      for (int c = 0; c < 4; c++)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + chunk[c]),
+                     "r"(o[4 * c]), "r"(o[4 * c + 1]), "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
+                     : "memory");
       fence_async_smem();
       mbar_arrive(full0 + 8 * a_stage);
-      if (++a_stage == kStages) a_stage = 0;
+      if (++a_stage == kStages) { a_stage = 0; a_parity ^= 1u; }
       if (--group_left == 0) {  // next block starts a new scale / zero group
         group_left = blocks_per_group;
         scp += p.N;
@@ -341,14 +304,14 @@ __global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams
         }
       }
     }
-    cp_async_wait<0>();
-  } else if (lane == 0) {
+  } else if (warp == 8 && lane == 0) {
     // ------------------------------ MMA issuer ------------------------------
     // instruction descriptor: D fp32, A/B fp16, both K-major, N = tokens_padded, M = 128
     const uint32_t idesc = (1u << 4) | ((uint32_t)(p.tokens_padded >> 3) << 17) |
                            ((uint32_t)(kTileN >> 4) << 24);
     uint32_t st = 0, parity = 0;
     for (int i = 0; i < nloc; i++) {
+      if (!mbar_wait(xfull0 + 8 * st, parity, ok)) ok = false;
       if (!mbar_wait(full0 + 8 * st, parity, ok)) ok = false;
       tc_fence_after();
       const uint64_t adesc = smem_desc(a_tiles + st * kATile);
@@ -360,6 +323,24 @@ __global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams
       if (++st == kStages) { st = 0; parity ^= 1u; }
     }
     umma_commit(accum_bar);
+  } else if (warp == 9 && lane == 0) {
+    // ------------------------------ packed-word TMA ------------------------------
+    uint32_t slot = 0, parity = 1;  // first pass over the ring: slots are free
+    for (int i = 0; i < nloc; i++) {
+      if (!mbar_wait(wempty0 + 8 * slot, parity, ok)) ok = false;
+      mbar_expect_tx(wfull0 + 8 * slot, 6 * 512);
+      tma_load_2d(word_ring + slot * (6 * 512), &map_w, n0, 6 * (kb0 + i), wfull0 + 8 * slot);
+      if (++slot == kWordAhead) { slot = 0; parity ^= 1u; }
+    }
+  } else if (warp == 10 && lane == 0) {
+    // ------------------------------ X TMA ------------------------------
+    uint32_t st = 0, parity = 1;
+    for (int i = 0; i < nloc; i++) {
+      if (!mbar_wait(empty0 + 8 * st, parity, ok)) ok = false;
+      mbar_expect_tx(xfull0 + 8 * st, (uint32_t)kBTile);
+      tma_load_2d(b_tiles + st * (uint32_t)kBTile, &map_x, (kb0 + i) * kBlockK, 0, xfull0 + 8 * st);
+      if (++st == kStages) { st = 0; parity ^= 1u; }
+    }
   }
 
   if (warp < 8) {
@@ -422,6 +403,24 @@ __global__ void __launch_bounds__(kThreads, 2) qgemm_q3_kernel(const QgemmParams
   }
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) !=
+            cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return (EncodeTiledFn) nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
 }  // namespace
 }  // namespace hq
 
@@ -441,7 +440,7 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
   if (Mb <= 0 || Mb > kMaxTokens || N <= 0 || K <= 0 || N % kTileN != 0 || K % kBlockK != 0)
     return HQ_ERR_BAD_SHAPE;
   if (group_size <= 0 || group_size % kBlockK != 0 || K % group_size != 0) return HQ_ERR_BAD_SHAPE;
-  if (!aligned16(X_half) || !aligned4(mat) || (K % 8) != 0) return HQ_ERR_MISALIGNED;
+  if (!aligned16(X_half) || !aligned16(mat) || (K % 8) != 0) return HQ_ERR_MISALIGNED;
   const int tokens_padded = (Mb + 15) / 16 * 16;
   const size_t smem = qgemm_smem_bytes(tokens_padded);
   cudaError_t e = cudaFuncSetAttribute(qgemm_q3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -459,9 +458,33 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
     if (ksplit > nkb / 8) ksplit = nkb / 8;
     if (ksplit < 1) ksplit = 1;
   }
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return HQ_ERR_UNSUPPORTED;
+  CUtensorMap map_x, map_w;
+  {
+    // X[Mb][K] fp16: box = 64 inputs x tokens_padded rows, 128-byte swizzle; rows
+    // beyond Mb are out of bounds and arrive as zeros
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Mb};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)tokens_padded};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(X_half), dims,
+               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return HQ_ERR_UNSUPPORTED;
+  }
+  {
+    // mat int32[K*3/32][N]: box = 128 columns x 6 rows (one block of 64 inputs)
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 32 * 3)};
+    const cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileN, 6};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&map_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t*>(mat), dims, strides,
+               box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return HQ_ERR_UNSUPPORTED;
+  }
   QgemmParams prm;
-  prm.X = reinterpret_cast<const __half*>(X_half);
-  prm.mat = mat;
   prm.scales = reinterpret_cast<const __half*>(scales_half);
   prm.zeros = reinterpret_cast<const __half*>(zeros_half);
   prm.Y = reinterpret_cast<__half*>(Y_half);
@@ -476,7 +499,7 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
   prm.group_size = group_size;
   prm.tokens_padded = tokens_padded;
   prm.ksplit = ksplit;
-  qgemm_q3_kernel<<<dim3(tiles, ksplit), kThreads, smem, (cudaStream_t)stream>>>(prm);
+  qgemm_q3_kernel<<<dim3(tiles, ksplit), kThreads, smem, (cudaStream_t)stream>>>(map_x, map_w, prm);
   return launch_status();
 }
 
