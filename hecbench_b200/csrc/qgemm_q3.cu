@@ -48,13 +48,14 @@ namespace hq {
 namespace {
 
 constexpr int kStages = 3;
-constexpr int kWordAhead = 8;               // packed-word blocks in flight (shared-memory ring)
+constexpr int kWordAhead = 6;               // packed-word blocks in flight (shared-memory ring)
 constexpr int kBlockK = 64;                 // halves per smem row (128 bytes)
 constexpr int kTileN = 128;                 // output features per CTA (UMMA M)
 constexpr int kMaxTokens = 128;             // UMMA N upper bound handled here
 constexpr int kATile = kTileN * 128;        // bytes
 constexpr int kDeqLut = 64 * 128;           // 64 pair values x 32 lane copies x 4 B
-constexpr int kWordRing = kWordAhead * 6 * 512;  // one box of 6 rows x 128 columns per block
+constexpr int kWordSlot = 6 * 512 + 2 * 256;  // 6 rows x 128 words, then 128 scales and 128 zeros
+constexpr int kWordRing = kWordAhead * kWordSlot;
 constexpr int kProducerThreads = 256;
 constexpr int kThreads = 352;               // 8 unpack warps, MMA warp, two TMA warps
 constexpr uint32_t kSpinLimit = 1u << 20;   // bounded mbarrier polls
@@ -153,8 +154,6 @@ __device__ __forceinline__ void cp_async_wait() {
 __shared__ __align__(16) uint32_t g_pair_lut[64 * 32];
 
 struct QgemmParams {
-  const __half* scales;
-  const __half* zeros;
   __half* Y;
   float* ws;            // fp32 [Mb][N] scratch + per-tile counters, used when ksplit > 1
   unsigned* counters;
@@ -164,6 +163,7 @@ struct QgemmParams {
 
 __global__ void __launch_bounds__(kThreads, 2)
 qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_z,
                 const QgemmParams p) {
   extern __shared__ unsigned char dsm_raw[];
   // 1024-byte aligned tiles (the swizzle pattern repeats every 1024 bytes)
@@ -198,13 +198,13 @@ qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
   if (tid == 0) {
     for (int s = 0; s < kStages; s++) {
-      mbar_init(full0 + 8 * s, kProducerThreads);
+      mbar_init(full0 + 8 * s, kProducerThreads / 2);
       mbar_init(empty0 + 8 * s, 1);
       mbar_init(xfull0 + 8 * s, 1);
     }
     for (int s = 0; s < kWordAhead; s++) {
       mbar_init(wfull0 + 8 * s, 1);
-      mbar_init(wempty0 + 8 * s, kProducerThreads);
+      mbar_init(wempty0 + 8 * s, kProducerThreads / 2);
     }
     mbar_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -228,81 +228,82 @@ qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
   if (warp < 8) {
     // ------------------------------ unpack warps ------------------------------
-    // Every instruction here runs once per K block in all 16 unpack warps of the
-    // SM, so the loop carries running counters and phase bits (no division).
+    // Two groups of four warps take alternate K blocks, so the groups (and the
+    // two CTAs of the SM) sit in different phases of the loop and fill each
+    // other's barrier and shared-memory latencies.  Thread = one output feature:
+    // it unpacks the 64 weights of its row for the block.  The loop carries
+    // running counters and phase bits (no division, no modulo).
     const int row = tid & 127;      // output feature n0 + row, A-tile row
-    const int hf = tid >> 7;        // which group of 32 inputs of the block
-    const int n = n0 + row;
+    const int grp = tid >> 7;       // blocks grp, grp + 2, ...
     const unsigned char* lut = reinterpret_cast<const unsigned char*>(g_pair_lut);
     const uint32_t lane4 = (uint32_t)lane * 4u;
     const uint32_t a_row = a_tiles + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);
-    const uint32_t chunk[4] = {(uint32_t)(((hf * 4 + 0) ^ (row & 7)) * 16),
-                               (uint32_t)(((hf * 4 + 1) ^ (row & 7)) * 16),
-                               (uint32_t)(((hf * 4 + 2) ^ (row & 7)) * 16),
-                               (uint32_t)(((hf * 4 + 3) ^ (row & 7)) * 16)};
-    // word box: [6 rows][128 columns]; this thread reads rows 3*hf..3*hf+2 of column `row`
-    const uint32_t my_words = word_ring + (uint32_t)((3 * hf) * 512 + row * 4);
-    const __half* scp = p.scales + (size_t)((kb0 * kBlockK) / p.group_size) * p.N + n;
-    const __half* zp = p.zeros + (size_t)((kb0 * kBlockK) / p.group_size) * p.N + n;
-    const int blocks_per_group = p.group_size / kBlockK;
-    int group_left = blocks_per_group - (kb0 % blocks_per_group);  // blocks left in the group
-    __half2 sc2 = __half2half2(*scp), nz2 = __half2half2(__hneg(*zp));
+    const uint32_t swz = (uint32_t)(row & 7);
+    // word box: [6 rows][128 columns] words, then 128 scales, then 128 zeros
+    const uint32_t my_words = word_ring + (uint32_t)(row * 4);
+    const uint32_t my_param = word_ring + 6 * 512 + (uint32_t)(row * 2);
 
-    uint32_t a_stage = 0, a_parity = 1;  // parity meaning "stage released" (first pass: free)
-    uint32_t w_slot = 0, w_parity = 0;
-    for (int i = 0; i < nloc; i++) {
+    uint32_t a_stage = (uint32_t)grp % kStages, a_parity = 1;  // parity meaning "stage released"
+    uint32_t w_slot = (uint32_t)grp, w_parity = 0;
+    for (int i = grp; i < nloc; i += 2) {
       if (!mbar_wait(wfull0 + 8 * w_slot, w_parity, ok)) ok = false;
-      uint32_t w0, w1, w2;
+      uint32_t w[6];
+      uint16_t sc_bits, z_bits;
       {
-        const uint32_t src = my_words + w_slot * (6 * 512);
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+512];" : "=r"(w1) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+1024];" : "=r"(w2) : "r"(src));
+        const uint32_t src = my_words + w_slot * kWordSlot;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+512];" : "=r"(w[1]) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+1024];" : "=r"(w[2]) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+1536];" : "=r"(w[3]) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+2048];" : "=r"(w[4]) : "r"(src));
+        asm volatile("ld.shared.u32 %0, [%1+2560];" : "=r"(w[5]) : "r"(src));
+        const uint32_t par = my_param + w_slot * kWordSlot;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc_bits) : "r"(par));
+        asm volatile("ld.shared.u16 %0, [%1+256];" : "=h"(z_bits) : "r"(par));
       }
-      // sixteen 6-bit pair values of the 96-bit stream, as byte offsets (v << 7) | lane*4
-      uint32_t po[16];
-      po[0] = ((w0 << 7) & 0x1f80u) | lane4;
-      po[1] = ((w0 << 1) & 0x1f80u) | lane4;
+      const __half2 sc2 = __half2half2(__ushort_as_half(sc_bits));
+      const __half2 nz2 = __half2half2(__hneg(__ushort_as_half(z_bits)));
+      uint32_t o[32];
 #pragma unroll
-      for (int q = 2; q < 5; q++) po[q] = ((w0 >> (6 * q - 7)) & 0x1f80u) | lane4;
-      po[5] = (__funnelshift_r(w0, w1, 23) & 0x1f80u) | lane4;
-      po[6] = ((w1 << 3) & 0x1f80u) | lane4;
+      for (int hf = 0; hf < 2; hf++) {
+        const uint32_t w0 = w[3 * hf], w1 = w[3 * hf + 1], w2 = w[3 * hf + 2];
+        // sixteen 6-bit pair values of the 96-bit stream, as byte offsets (v << 7) | lane*4
+        uint32_t po[16];
+        po[0] = ((w0 << 7) & 0x1f80u) | lane4;
+        po[1] = ((w0 << 1) & 0x1f80u) | lane4;
 #pragma unroll
-      for (int q = 1; q < 4; q++) po[6 + q] = ((w1 >> (6 * q - 3)) & 0x1f80u) | lane4;
-      po[10] = (__funnelshift_r(w1, w2, 21) & 0x1f80u) | lane4;
-      po[11] = ((w2 << 5) & 0x1f80u) | lane4;
+        for (int q = 2; q < 5; q++) po[q] = ((w0 >> (6 * q - 7)) & 0x1f80u) | lane4;
+        po[5] = (__funnelshift_r(w0, w1, 23) & 0x1f80u) | lane4;
+        po[6] = ((w1 << 3) & 0x1f80u) | lane4;
 #pragma unroll
-      for (int q = 1; q < 5; q++) po[11 + q] = ((w2 >> (6 * q - 5)) & 0x1f80u) | lane4;
-      uint32_t o[16];
+        for (int q = 1; q < 4; q++) po[6 + q] = ((w1 >> (6 * q - 3)) & 0x1f80u) | lane4;
+        po[10] = (__funnelshift_r(w1, w2, 21) & 0x1f80u) | lane4;
+        po[11] = ((w2 << 5) & 0x1f80u) | lane4;
 #pragma unroll
-      for (int e = 0; e < 16; e++) {
-        const uint32_t q2 = *reinterpret_cast<const uint32_t*>(lut + po[e]);
-        o[e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
+        for (int q = 1; q < 5; q++) po[11 + q] = ((w2 >> (6 * q - 5)) & 0x1f80u) | lane4;
+#pragma unroll
+        for (int e = 0; e < 16; e++) {
+          const uint32_t q2 = *reinterpret_cast<const uint32_t*>(lut + po[e]);
+          o[16 * hf + e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
+        }
       }
       // the ring slot is released only now: the lookups above consumed the words,
-      // so the three loads have certainly returned
+      // so the loads have certainly returned
       mbar_arrive(wempty0 + 8 * w_slot);
-      if (++w_slot == kWordAhead) { w_slot = 0; w_parity ^= 1u; }
+      w_slot += 2;
+      if (w_slot >= kWordAhead) { w_slot -= kWordAhead; w_parity ^= 1u; }
       // the A tile of this stage must have been released by the tensor core
       if (!mbar_wait(empty0 + 8 * a_stage, a_parity, ok)) ok = false;
       const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
 #pragma unroll
-      for (int c = 0; c < 4; c++)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + chunk[c]),
+      for (int c = 0; c < 8; c++)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + (((uint32_t)c ^ swz) * 16)),
                      "r"(o[4 * c]), "r"(o[4 * c + 1]), "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
                      : "memory");
       fence_async_smem();
       mbar_arrive(full0 + 8 * a_stage);
-      if (++a_stage == kStages) { a_stage = 0; a_parity ^= 1u; }
-      if (--group_left == 0) {  // next block starts a new scale / zero group
-        group_left = blocks_per_group;
-        scp += p.N;
-        zp += p.N;
-        if (i + 1 < nloc) {
-          sc2 = __half2half2(*scp);
-          nz2 = __half2half2(__hneg(*zp));
-        }
-      }
+      a_stage += 2;
+      if (a_stage >= kStages) { a_stage -= kStages; a_parity ^= 1u; }
     }
   } else if (warp == 8 && lane == 0) {
     // ------------------------------ MMA issuer ------------------------------
@@ -328,8 +329,12 @@ qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     uint32_t slot = 0, parity = 1;  // first pass over the ring: slots are free
     for (int i = 0; i < nloc; i++) {
       if (!mbar_wait(wempty0 + 8 * slot, parity, ok)) ok = false;
-      mbar_expect_tx(wfull0 + 8 * slot, 6 * 512);
-      tma_load_2d(word_ring + slot * (6 * 512), &map_w, n0, 6 * (kb0 + i), wfull0 + 8 * slot);
+      const int g = ((kb0 + i) * kBlockK) / p.group_size;
+      const uint32_t dst = word_ring + slot * kWordSlot;
+      mbar_expect_tx(wfull0 + 8 * slot, kWordSlot);
+      tma_load_2d(dst, &map_w, n0, 6 * (kb0 + i), wfull0 + 8 * slot);
+      tma_load_2d(dst + 6 * 512, &map_s, n0, g, wfull0 + 8 * slot);
+      tma_load_2d(dst + 6 * 512 + 256, &map_z, n0, g, wfull0 + 8 * slot);
       if (++slot == kWordAhead) { slot = 0; parity ^= 1u; }
     }
   } else if (warp == 10 && lane == 0) {
@@ -440,7 +445,9 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
   if (Mb <= 0 || Mb > kMaxTokens || N <= 0 || K <= 0 || N % kTileN != 0 || K % kBlockK != 0)
     return HQ_ERR_BAD_SHAPE;
   if (group_size <= 0 || group_size % kBlockK != 0 || K % group_size != 0) return HQ_ERR_BAD_SHAPE;
-  if (!aligned16(X_half) || !aligned16(mat) || (K % 8) != 0) return HQ_ERR_MISALIGNED;
+  if (!aligned16(X_half) || !aligned16(mat) || !aligned16(scales_half) || !aligned16(zeros_half) ||
+      (K % 8) != 0)
+    return HQ_ERR_MISALIGNED;
   const int tokens_padded = (Mb + 15) / 16 * 16;
   const size_t smem = qgemm_smem_bytes(tokens_padded);
   cudaError_t e = cudaFuncSetAttribute(qgemm_q3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -484,9 +491,20 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return HQ_ERR_UNSUPPORTED;
   }
+  CUtensorMap map_s, map_z;
+  for (int which = 0; which < 2; which++) {
+    // scales / zeros fp16 [K/group_size][N]: box = 128 columns x 1 group
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / group_size)};
+    const cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileN, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(which ? &map_z : &map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+               const_cast<void*>(which ? zeros_half : scales_half), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return HQ_ERR_UNSUPPORTED;
+  }
   QgemmParams prm;
-  prm.scales = reinterpret_cast<const __half*>(scales_half);
-  prm.zeros = reinterpret_cast<const __half*>(zeros_half);
   prm.Y = reinterpret_cast<__half*>(Y_half);
   prm.ws = reinterpret_cast<float*>(workspace);
   prm.counters = workspace ? reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
@@ -499,7 +517,8 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
   prm.group_size = group_size;
   prm.tokens_padded = tokens_padded;
   prm.ksplit = ksplit;
-  qgemm_q3_kernel<<<dim3(tiles, ksplit), kThreads, smem, (cudaStream_t)stream>>>(map_x, map_w, prm);
+  qgemm_q3_kernel<<<dim3(tiles, ksplit), kThreads, smem, (cudaStream_t)stream>>>(map_x, map_w, map_s,
+                                                                               map_z, prm);
   return launch_status();
 }
 
