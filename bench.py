@@ -348,6 +348,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1; the CPU arm uses every host thread
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     name = args.workload
     c = _host_case(name, 0)
     # each step = one bounded CPU sample (a few repetitions of the workload)
@@ -402,7 +404,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     hq.load_library()
 
     wl = DeviceWorkload(args.workload, dev, seed=rank, target_bytes=args.replica_bytes)
@@ -535,7 +538,14 @@ def main():
             line["cpu_baseline"] = cb
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tearing the NCCL communicator down after its collectives were captured in
+        # a CUDA graph blocked forever on this stack; the ranks agree that they are
+        # done and leave without the teardown.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
