@@ -476,6 +476,33 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms = float(tt.item())
 
+    # ceiling of a kernel with this footprint: pure streaming read of the same
+    # number of bytes per launch over the same rotating buffers, same graph setup
+    read_us = None
+    if args.workload == "nf4_gemv" and world == 1:
+        lib = hq.load_library()
+        sink = torch.zeros(1, dtype=torch.int32, device=dev)
+        nbytes = wl.B[0].numel()
+        with torch.cuda.stream(stream):
+            def reads():
+                for i in range(R):
+                    lib.hq_probe_stream_read(wl.B[i].data_ptr(), nbytes, sink.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream)
+            reads()
+            stream.synchronize()
+            rg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(rg, stream=stream):
+                reads()
+            for _ in range(3):
+                rg.replay()
+            ra = torch.cuda.Event(enable_timing=True); rb = torch.cuda.Event(enable_timing=True)
+            ra.record(stream)
+            for _ in range(min(args.steps, 100)):
+                rg.replay()
+            rb.record(stream)
+            stream.synchronize()
+            read_us = ra.elapsed_time(rb) * 1e3 / (R * min(args.steps, 100))
+
     launches = R * args.steps
     us_per_launch = ms * 1e3 / launches
     total_bytes = wl.bytes * launches * world
@@ -530,7 +557,8 @@ def main():
             "us_per_gemv": us_per_launch,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_src}",
-                         "traffic": ncu_traffic(args.workload)},
+                         "traffic": ncu_traffic(args.workload),
+                         "same_size_pure_read_us": read_us},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }
         if world == 1 and not args.no_cpu_baseline:

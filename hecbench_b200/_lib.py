@@ -16,6 +16,7 @@ SIGNATURES = {
     "hq_version": (c_int, []),
     "hq_status_string": (C.c_char_p, [c_int]),
     "hq_last_cuda_error": (c_int, []),
+    "hq_probe_stream_read": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p]),
     "hq_q3_gemv_f32": (c_int, [c_void_p] * 5 + [c_int, c_int, c_void_p]),
     "hq_q3_gemv_f16in": (c_int, [c_void_p] * 5 + [c_int, c_int, c_void_p]),
     "hq_q3_dequant_f32": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p]),

@@ -47,6 +47,17 @@ constexpr int kStageChunks = 8;      // 16-byte chunks in flight per lane (share
 constexpr int kRound = 4;            // rows between two group barriers
 
 constexpr int kLutBytes = 256 * 256;  // table rows interleaved with the partial-sum slots
+// The table sits at the fixed shared-window address kLutImm, so that a lookup
+// address is the byte-permute {0, 0, byte value, lane*4} plus an immediate.
+constexpr int kLutImm = 2048;
+
+template <int IMM>
+__device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
+  // not volatile: the table is constant after the prologue barrier
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+  return v;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -71,7 +82,7 @@ __device__ __forceinline__ void cp_async_wait() {
 
 // sum of the 32 products of one 16-byte chunk against 16 half2 inputs
 __device__ __forceinline__ float chunk_dot(const uint4& codes, const uint4 (&xp)[4],
-                                           const unsigned char* lut, uint32_t lane4) {
+                                           uint32_t lane4) {
   const uint32_t w[4] = {codes.x, codes.y, codes.z, codes.w};
   __half2 a0 = __float2half2_rn(0.f), a1 = a0;
 #pragma unroll
@@ -82,10 +93,10 @@ __device__ __forceinline__ float chunk_dot(const uint4& codes, const uint4 (&xp)
     const uint32_t o1 = __byte_perm(w[i], lane4, 0x7614);
     const uint32_t o2 = __byte_perm(w[i], lane4, 0x7624);
     const uint32_t o3 = __byte_perm(w[i], lane4, 0x7634);
-    const uint32_t l0 = *reinterpret_cast<const uint32_t*>(lut + o0);
-    const uint32_t l1 = *reinterpret_cast<const uint32_t*>(lut + o1);
-    const uint32_t l2 = *reinterpret_cast<const uint32_t*>(lut + o2);
-    const uint32_t l3 = *reinterpret_cast<const uint32_t*>(lut + o3);
+    const uint32_t l0 = lds_u32_imm<kLutImm>(o0);
+    const uint32_t l1 = lds_u32_imm<kLutImm>(o1);
+    const uint32_t l2 = lds_u32_imm<kLutImm>(o2);
+    const uint32_t l3 = lds_u32_imm<kLutImm>(o3);
     a0 = __hfma2(u32_as_half2(l0), u32_as_half2(xw[0]), a0);
     a1 = __hfma2(u32_as_half2(l1), u32_as_half2(xw[1]), a1);
     a0 = __hfma2(u32_as_half2(l2), u32_as_half2(xw[2]), a0);
@@ -125,10 +136,11 @@ template <int C, int ST, bool ALIGNED>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 nf4_gemv_kernel(const GemvParams p) {
   constexpr int kStages = kStageChunks / C;  // rows in flight per lane
-  extern __shared__ __align__(16) unsigned char dsm[];
-  // table rows (256 x 256 B: lane copies | partial-sum slot) | [kStages][C][1024] uint4
-  // | [kStages][C][1024] float
-  const unsigned char* lut = dsm;
+  extern __shared__ __align__(16) unsigned char dsm_raw[];
+  // [pad up to shared address kLutImm] table rows (256 x 256 B: lane copies |
+  // partial-sum slot) | [kStages][C][1024] uint4 | [kStages][C][1024] float
+  if (smem_u32(dsm_raw) > (uint32_t)kLutImm) return;  // never on sm_100 (1 KiB reserved)
+  unsigned char* dsm = dsm_raw + (kLutImm - smem_u32(dsm_raw));
   const int S = ST > 0 ? ST : p.S;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = warp / S, q = warp - g * S;
@@ -232,8 +244,7 @@ nf4_gemv_kernel(const GemvParams p) {
       if (d < rows_in_round) {                                                                 \
         float acc = 0.f;                                                                       \
         _Pragma("unroll") for (int i = 0; i < C; i++) acc =                                    \
-            fmaf(chunk_dot(ring_w[(((RR)*kRound + d) * C + i) * kGemvThreads], xr[i], lut,      \
-                           lane4),                                                             \
+            fmaf(chunk_dot(ring_w[(((RR)*kRound + d) * C + i) * kGemvThreads], xr[i], lane4),       \
                  ring_s[(((RR)*kRound + d) * C + i) * kGemvThreads], acc);                      \
         if (S > 1) {                                                                           \
           part_lane[(slot0 + d * S + q) * 64] = acc;                                           \
@@ -345,7 +356,9 @@ int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, c
   if (S > kGemvWarps) return HQ_ERR_TOO_LARGE;  // K > 65536
   int G = kGemvWarps / S;
   if (S > 1 && G > 15) G = 15;
-  const size_t smem = (size_t)kLutBytes + (size_t)kStageChunks * kGemvThreads * 20;
+  // room for the pad that brings the table to shared address kLutImm wherever the
+  // dynamic region starts (at or below kLutImm)
+  const size_t smem = (size_t)kLutImm + kLutBytes + (size_t)kStageChunks * kGemvThreads * 20;
   const int sms = sm_count();
   const int grid = std::min(sms, (N + G - 1) / G);
   const int cpb = blocksize / 32;
@@ -385,6 +398,7 @@ int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, c
   else if (C == 1 && S == 1 && aligned) HQ_NF4_LAUNCH(1, 1, true)
   else if (C == 1 && aligned) HQ_NF4_LAUNCH(1, 0, true)
   else if (C == 1) HQ_NF4_LAUNCH(1, 0, false)
+  else if (S == 2 && aligned) HQ_NF4_LAUNCH(2, 2, true)
   else if (aligned) HQ_NF4_LAUNCH(2, 0, true)
   else HQ_NF4_LAUNCH(2, 0, false)
 #undef HQ_NF4_LAUNCH

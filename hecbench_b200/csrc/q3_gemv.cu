@@ -111,15 +111,22 @@ q3_gemv_kernel(const void* __restrict__ vec_, const int32_t* __restrict__ mat,
   const bool active = col0 < width;
   const int32_t* base = mat + (size_t)g0 * 3 * width + col0;
 
+  // software pipeline: the three packed rows of the next group are requested
+  // before the current group is unpacked
+  uint4 n0 = make_uint4(0, 0, 0, 0), n1 = n0, n2 = n0;
+  if (active && warp < ng) {
+    const int32_t* p = base + (size_t)warp * 3 * width;
+    n0 = ldg_stream_u4(p);
+    n1 = ldg_stream_u4(p + width);
+    n2 = ldg_stream_u4(p + 2 * (size_t)width);
+  }
   for (int gi = warp; gi < ng; gi += kWarps) {
-    uint4 u0, u1, u2;
-    if (active) {
-      const int32_t* p = base + (size_t)gi * 3 * width;
-      u0 = ldg_stream_u4(p);
-      u1 = ldg_stream_u4(p + width);
-      u2 = ldg_stream_u4(p + 2 * (size_t)width);
-    } else {
-      u0 = u1 = u2 = make_uint4(0, 0, 0, 0);
+    const uint4 u0 = n0, u1 = n1, u2 = n2;
+    if (active && gi + kWarps < ng) {
+      const int32_t* p = base + (size_t)(gi + kWarps) * 3 * width;
+      n0 = ldg_stream_u4(p);
+      n1 = ldg_stream_u4(p + width);
+      n2 = ldg_stream_u4(p + 2 * (size_t)width);
     }
     sumx += gsum[gi];
     const uint32_t w0s[4] = {u0.x, u0.y, u0.z, u0.w};

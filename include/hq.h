@@ -40,6 +40,13 @@ const char* hq_status_string(int status);
 /* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
 int hq_last_cuda_error(void);
 
+/* Measurement aid (no counterpart in the reference): a kernel that reads
+ * `bytes` bytes from src exactly once with 128-bit streaming loads and does
+ * nothing else.  Timed like the real kernels it gives the ceiling a kernel of
+ * that footprint can reach on this GPU, launch and ramp included.  sink is one
+ * device word. */
+int hq_probe_stream_read(const void* src, size_t bytes, unsigned* sink, hq_stream_t stream);
+
 /* ---------------- GPTQ 3-bit GEMV (quant3MatMul) ---------------- */
 
 /* Replaces vecquant3matmul<float> (quant3MatMul-cuda/kernels.h:171-190).
