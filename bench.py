@@ -388,6 +388,8 @@ def main():
                     help="bytes of packed weights resident per GPU (>> L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly (for profilers)")
+    ap.add_argument("--gather", default="publish", choices=["publish", "fused", "nccl"],
+                    help="N > 1: how the output slices of a layer are gathered")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -418,11 +420,30 @@ def main():
     # (weak scaling: the layer grows with N) and the slices of every layer are
     # all-gathered over NCCL right after its kernel, as a decoder needs them.
     gathered = None
-    if world > 1 and hasattr(wl, "out"):
+    peer = None
+    if world > 1 and args.workload == "nf4_gemv" and args.gather in ("publish", "fused"):
+        # fused GEMV + gather: the kernel stores its slice into every GPU's
+        # gathered vector over NVLink and flags it; a bounded wait follows
+        from hecbench_b200.shard import FeatureShard, PeerGather
+        c = wl.case
+        peer = PeerGather(FeatureShard(rank, world, world * c["N"]), slots=R, device=dev)
+    elif world > 1 and hasattr(wl, "out"):
         gathered = [torch.empty(world * wl.out[i].numel(), dtype=wl.out[i].dtype, device=dev)
                     for i in range(R)]
 
     def layer(i):
+        if peer is not None:
+            c = wl.case
+            if args.gather == "fused":
+                # the GEMV's last CTA sends the slice itself; bounded wait after it
+                peer.gemv_nf4(i, wl.x[i], wl.B[i], wl.absmax[i], wl.lut, c["K"], c["bs"])
+            else:
+                # ordinary GEMV into this rank's slice of its own gathered vector,
+                # then one small kernel: peer stores over NVLink, flags, bounded wait
+                hq.gemv_nf4(wl.x[i], wl.B[i], wl.absmax[i], wl.lut, c["N"], c["K"], c["bs"], 0,
+                            peer.local_slice(i))
+                peer.publish(i)
+            return
         wl.launch(i)
         if gathered is not None:
             dist.all_gather_into_tensor(gathered[i], wl.out[i].view(-1))
@@ -518,7 +539,12 @@ def main():
                 for i in range(R):
                     wl.x[i].copy_(hin[i], non_blocking=True)
                     layer(i)
-                    hout[i].copy_(wl.out[i], non_blocking=True)
+                    if peer is not None:  # this rank's slice of the gathered vector
+                        c = wl.case
+                        hout[i].copy_(peer.slot(i)[rank * c["N"]:(rank + 1) * c["N"]],
+                                      non_blocking=True)
+                    else:
+                        hout[i].copy_(wl.out[i], non_blocking=True)
             for _ in range(3):
                 e2e_step()
             barrier()
@@ -538,6 +564,8 @@ def main():
                "d2h_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hout)),
                "us_per_call": ems * 1e3 / launches}
 
+    if peer is not None and int(peer.status.item()) != 0:
+        raise SystemExit("a bounded gather wait ran out")
     if rank == 0:
         peak, peak_src = measured_peak()
         achieved = wl.bytes / (us_per_launch * 1e-6) / 1e9
@@ -552,8 +580,12 @@ def main():
                        "algorithmic_bytes_per_launch": wl.bytes,
                        "launch": "cuda graph of R launches" if graph is not None else "eager",
                        "parallelism": ("single GPU" if world == 1 else
-                                       f"output features sharded over {world} GPUs, NCCL "
-                                       "all-gather of the slices after every layer")},
+                                       f"output features sharded over {world} GPUs, " +
+                                       (f"gather '{args.gather}': slices stored into every GPU's "
+                                        "gathered vector by our own kernel (peer stores over "
+                                        "NVLink + flags), bounded wait after every layer"
+                                        if peer is not None else
+                                        "NCCL all-gather of the slices after every layer"))},
             "us_per_gemv": us_per_launch,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"of {peak_src}",

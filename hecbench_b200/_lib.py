@@ -24,6 +24,12 @@ SIGNATURES = {
     "hq_bnb_quantize_u8": (c_int, [c_void_p] * 3 + [c_size_t, c_void_p]),
     "hq_nf4_dequant_f16": (c_int, [c_void_p] * 4 + [c_size_t, c_int, c_int, c_void_p]),
     "hq_nf4_gemv_f16": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "hq_nf4_gemv_f16_gather": (c_int, [c_void_p] * 4 + [c_int] * 4 + [c_void_p, C.c_longlong,
+                                                              c_void_p, c_void_p, c_int, c_int,
+                                                              c_void_p, c_void_p, c_void_p]),
+    "hq_gather_publish": (c_int, [c_void_p, C.c_longlong, c_int, c_void_p, c_void_p, c_int, c_int,
+                                  c_void_p, c_void_p]),
+    "hq_gather_wait": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "hq_lutgemm_workspace_bytes": (c_size_t, [c_int]),
     "hq_lutgemm_nqmv": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p, c_size_t, c_void_p]),
     "hq_lutgemm_nqmv_noalloc": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),

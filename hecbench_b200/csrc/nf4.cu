@@ -124,7 +124,27 @@ struct GemvParams {
   int low_first;
   unsigned long long w_step;   // bytes between two rows of one group
   unsigned int a_step;         // absmax entries between two rows of one group (ALIGNED only)
+  // fused gather (null when unused): every result is also stored into the
+  // gathered vector of each GPU of the node at element gather_offset + n
+  __half* const* peer_out;
+  uint32_t* const* peer_flags;  // flags array of each rank; this rank writes word `rank`
+  unsigned* sync_words;         // local: [0] CTAs finished, [1] launches completed
+  int world, rank;
+  long long gather_offset;
+  // optional: before the input vector is read, wait (bounded) until every rank's
+  // flag has reached this rank's launch count, i.e. until the previous fused
+  // gather - which produced the input of this layer - has landed everywhere
+  const uint32_t* wait_flags;
+  int* status;
 };
+
+// store one result locally and, for the fused gather, into every peer's vector
+__device__ __forceinline__ void store_result(const GemvParams& p, __half* local, long long n,
+                                             float v) {
+  const __half h = __float2half_rn(v);
+  if (p.peer_out == nullptr) *local = h;
+  else p.peer_out[p.rank][p.gather_offset + n] = h;  // own copy first; peers get it in bulk
+}
 
 // C = chunks (32 codes) per lane per row; S warps share a row (ST > 0: compile
 // time, ST == 0: run time), G groups per CTA.  ALIGNED: every row starts on an
@@ -210,13 +230,27 @@ nf4_gemv_kernel(const GemvParams p) {
     row[entry & 1] = u4;
     row[(entry & 1) ^ 1] = u4;
   }
+  if (p.wait_flags != nullptr) {
+    if (tid < p.world) {
+      const unsigned want = *reinterpret_cast<volatile unsigned*>(p.sync_words + 1);
+      const volatile uint32_t* f = p.wait_flags + tid;
+      bool landed = false;
+      for (unsigned spin = 0; spin < (1u << 20); spin++) {
+        if ((int)(*f - want) >= 0) { landed = true; break; }
+        __nanosleep(32);
+      }
+      if (landed) __threadfence_system();
+      else if (p.status != nullptr) atomicExch(p.status, 1);
+    }
+    __syncthreads();
+  }
   uint4 xr[C][4];
 #pragma unroll
   for (int i = 0; i < C; i++) {
     const int c = (q * C + i) * 32 + lane;
     const uint4* xp = reinterpret_cast<const uint4*>(p.A) + 4 * (live[i] ? c : 0);
 #pragma unroll
-    for (int t = 0; t < 4; t++) xr[i][t] = __ldg(xp + t);
+    for (int t = 0; t < 4; t++) xr[i][t] = p.wait_flags ? __ldcg(xp + t) : __ldg(xp + t);
   }
   __syncthreads();
 
@@ -250,7 +284,7 @@ nf4_gemv_kernel(const GemvParams p) {
           part_lane[(slot0 + d * S + q) * 64] = acc;                                           \
         } else {                                                                               \
           acc = warp_sum(acc);                                                                 \
-          if (lane == 0) *outp = __float2half_rn(acc);                                         \
+          if (lane == 0) store_result(p, outp, outp - p.out, acc);                             \
           outp += row_stride;                                                                  \
         }                                                                                      \
       }                                                                                        \
@@ -267,7 +301,8 @@ nf4_gemv_kernel(const GemvParams p) {
           for (int t = 0; t < S; t++) v += part_lane[(slot0 + d * S + t) * 64];                \
         }                                                                                      \
         v = warp_sum(v);                                                                       \
-        if (lane == 0) outp[(size_t)d * row_stride] = __float2half_rn(v);                      \
+        if (lane == 0)                                                                         \
+          store_result(p, outp + (size_t)d * row_stride, (outp - p.out) + (long long)d * row_stride, v); \
       }                                                                                        \
       outp += (size_t)kRound * row_stride;                                                     \
     }                                                                                          \
@@ -284,6 +319,49 @@ nf4_gemv_kernel(const GemvParams p) {
   }
 #undef HQ_NF4_ROUND
   cp_async_wait<0>();
+  if (p.peer_out != nullptr) {
+    // Fused gather epilogue: every CTA has stored its results into this GPU's own
+    // copy of the gathered vector; the last CTA of the grid to finish copies the
+    // whole slice to every peer with 16-byte stores over NVLink, makes them
+    // visible system-wide and then tells every peer, by one flag word per
+    // (receiver, sender), that this launch's slice has landed.
+    __shared__ unsigned s_last_cta;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned prev = atomicAdd(p.sync_words, 1u);
+      s_last_cta = (prev == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last_cta) {
+      __threadfence();
+      const int n_slice = p.rows_base * (int)(gridDim.x * p.G) + p.rows_rem;  // rows of this rank
+      const __half* mine = p.peer_out[p.rank] + p.gather_offset;
+      const bool vec_ok = ((p.gather_offset | (long long)n_slice) & 7) == 0;
+      for (int r = 0; r < p.world; r++) {
+        if (r == p.rank) continue;
+        __half* dst = p.peer_out[r] + p.gather_offset;
+        if (vec_ok) {
+          for (int i = tid; i < n_slice / 8; i += kGemvThreads)
+            reinterpret_cast<uint4*>(dst)[i] = __ldcg(reinterpret_cast<const uint4*>(mine) + i);
+        } else {
+          for (int i = tid; i < n_slice; i += kGemvThreads)
+            reinterpret_cast<unsigned short*>(dst)[i] =
+                __ldcg(reinterpret_cast<const unsigned short*>(mine) + i);
+        }
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (tid == 0) {
+        p.sync_words[0] = 0u;
+        const unsigned epoch = p.sync_words[1] + 1u;
+        p.sync_words[1] = epoch;
+        __threadfence_system();
+        for (int r = 0; r < p.world; r++)
+          *reinterpret_cast<volatile uint32_t*>(p.peer_flags[r] + p.rank) = epoch;
+      }
+    }
+  }
 #undef HQ_NF4_ISSUE
 }
 
@@ -315,10 +393,96 @@ nf4_dequant_kernel(const uint8_t* __restrict__ B, const float* __restrict__ absm
   }
 }
 
+// One warp: lane r waits (bounded) until rank r's flag has reached this rank's
+// own launch count, i.e. until rank r's slice of the latest gather has landed.
+__global__ void gather_wait_kernel(const uint32_t* flags, const unsigned* sync_words, int world,
+                                   int* status) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  const unsigned want = sync_words[1];
+  const volatile uint32_t* f = flags + r;
+  bool ok = false;
+  for (unsigned spin = 0; spin < (1u << 22); spin++) {
+    // flags only grow; "reached" is tested modulo 2^32
+    if ((int)(*f - want) >= 0) { ok = true; break; }
+    __nanosleep(64);
+  }
+  if (ok) __threadfence_system();
+  else if (status != nullptr) atomicExch(status, 1);
+}
+
+// One CTA: copy this rank's finished slice (already in its own gathered vector)
+// into every peer's vector with 16-byte stores over NVLink, make the stores
+// visible system-wide, raise this rank's flag on every GPU, then wait (bounded)
+// until every rank's flag on this GPU has reached the same launch count.
+__global__ void __launch_bounds__(1024, 1)
+gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
+                      uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
+                      int* status) {
+  const int tid = threadIdx.x;
+  const __half* mine = peer_out[rank] + offset;
+  const bool vec_ok = ((offset | (long long)n_slice) & 7) == 0;
+  for (int r = 0; r < world; r++) {
+    if (r == rank) continue;
+    __half* dst = peer_out[r] + offset;
+    if (vec_ok) {
+      for (int i = tid; i < n_slice / 8; i += 1024)
+        reinterpret_cast<uint4*>(dst)[i] = __ldcg(reinterpret_cast<const uint4*>(mine) + i);
+    } else {
+      for (int i = tid; i < n_slice; i += 1024)
+        reinterpret_cast<unsigned short*>(dst)[i] =
+            __ldcg(reinterpret_cast<const unsigned short*>(mine) + i);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned s_epoch;
+  if (tid == 0) {
+    const unsigned epoch = sync_words[1] + 1u;
+    sync_words[1] = epoch;
+    s_epoch = epoch;
+    for (int r = 0; r < world; r++)
+      *reinterpret_cast<volatile uint32_t*>(peer_flags[r] + rank) = epoch;
+  }
+  __syncthreads();
+  if (tid < world) {
+    const unsigned want = s_epoch;
+    const volatile uint32_t* f = peer_flags[rank] + tid;
+    bool landed = false;
+    for (unsigned spin = 0; spin < (1u << 22); spin++) {
+      if ((int)(*f - want) >= 0) { landed = true; break; }
+      __nanosleep(32);
+    }
+    if (landed) __threadfence_system();
+    else if (status != nullptr) atomicExch(status, 1);
+  }
+}
+
 }  // namespace
 }  // namespace hq
 
 extern "C" {
+
+int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
+                      uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
+                      int* status, hq_stream_t stream) {
+  using namespace hq;
+  if (!peer_out_half || !peer_flags || !sync_words) return HQ_ERR_NULL_POINTER;
+  if (world < 1 || world > 32 || rank < 0 || rank >= world || n_slice <= 0) return HQ_ERR_BAD_SHAPE;
+  gather_publish_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<__half* const*>(peer_out_half), offset, n_slice, peer_flags, sync_words,
+      world, rank, status);
+  return launch_status();
+}
+
+int hq_gather_wait(const uint32_t* local_flags, const unsigned* sync_words, int world, int* status,
+                   hq_stream_t stream) {
+  using namespace hq;
+  if (!local_flags || !sync_words) return HQ_ERR_NULL_POINTER;
+  if (world < 1 || world > 32) return HQ_ERR_BAD_SHAPE;
+  gather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(local_flags, sync_words, world, status);
+  return launch_status();
+}
 
 int hq_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut16, void* out_half,
                        size_t n, int blocksize, int flags, hq_stream_t stream) {
@@ -337,10 +501,13 @@ int hq_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut16
   return launch_status();
 }
 
-int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, const float* lut16,
-                    void* out_half, int N, int K, int blocksize, int flags, hq_stream_t stream) {
+static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absmax,
+                         const float* lut16, void* out_half, int N, int K, int blocksize, int flags,
+                         void* const* peer_out, uint32_t* const* peer_flags, unsigned* sync_words,
+                         int world, int rank, long long gather_offset, const uint32_t* wait_flags,
+                         int* status, hq_stream_t stream) {
   using namespace hq;
-  if (!A_half || !B || !absmax || !lut16 || !out_half) return HQ_ERR_NULL_POINTER;
+  if (!A_half || !B || !absmax || !lut16 || (!out_half && !peer_out)) return HQ_ERR_NULL_POINTER;
   if (N <= 0 || K <= 0 || K % 32 != 0 || blocksize <= 0 || blocksize % 32 != 0 ||
       false)
     return HQ_ERR_BAD_SHAPE;
@@ -384,6 +551,14 @@ int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, c
   prm.low_first = (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0;
   prm.w_step = (unsigned long long)grid * G * nchunks * 16ull;
   prm.a_step = aligned ? (unsigned)(((unsigned long long)grid * G * nchunks) >> shift) : 0u;
+  prm.peer_out = reinterpret_cast<__half* const*>(peer_out);
+  prm.peer_flags = peer_flags;
+  prm.sync_words = sync_words;
+  prm.world = world;
+  prm.rank = rank;
+  prm.gather_offset = gather_offset;
+  prm.wait_flags = wait_flags;
+  prm.status = status;
   cudaStream_t st = (cudaStream_t)stream;
 #define HQ_NF4_LAUNCH(CC, SS, AL)                                                               \
   {                                                                                             \
@@ -403,6 +578,24 @@ int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, c
   else HQ_NF4_LAUNCH(2, 0, false)
 #undef HQ_NF4_LAUNCH
   return launch_status();
+}
+
+int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, const float* lut16,
+                    void* out_half, int N, int K, int blocksize, int flags, hq_stream_t stream) {
+  return nf4_gemv_impl(A_half, B, absmax, lut16, out_half, N, K, blocksize, flags, nullptr, nullptr,
+                       nullptr, 1, 0, 0, nullptr, nullptr, stream);
+}
+
+int hq_nf4_gemv_f16_gather(const void* A_half, const uint8_t* B, const float* absmax,
+                           const float* lut16, int N, int K, int blocksize, int flags,
+                           void* const* peer_out_half, long long gather_offset,
+                           uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
+                           const uint32_t* wait_flags, int* status, hq_stream_t stream) {
+  if (!peer_out_half || !peer_flags || !sync_words) return HQ_ERR_NULL_POINTER;
+  if (world < 1 || world > 32 || rank < 0 || rank >= world) return HQ_ERR_BAD_SHAPE;
+  return nf4_gemv_impl(A_half, B, absmax, lut16, nullptr, N, K, blocksize, flags, peer_out_half,
+                       peer_flags, sync_words, world, rank, gather_offset, wait_flags, status,
+                       stream);
 }
 
 }  // extern "C"

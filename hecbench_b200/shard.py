@@ -82,3 +82,84 @@ def gather_features(local_out: torch.Tensor, shard: FeatureShard, group=None,
 def sharded_apply(local_fn: Callable[[], torch.Tensor], shard: FeatureShard, group=None):
     """Run the rank-local kernel and gather the feature slices."""
     return gather_features(local_fn(), shard, group)
+
+
+class PeerGather:
+    """Buffers for the fused GEMV + all-gather: every rank's gathered vectors and
+    flag words live in peer-mapped ("symmetric") device memory, so the kernel of
+    one GPU stores its output slice directly into the vectors of all GPUs over
+    NVLink and announces it with one flag word per (receiver, sender).
+
+    Layout of each rank's symmetric buffer: [256 bytes of flags][slots] with
+    slot = world * n_local fp16 values.  `sync` is a rank-local pair of words
+    (CTA counter, launch count) and `status` a rank-local error word.
+    """
+
+    def __init__(self, shard: FeatureShard, slots: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.shard, self.slots = shard, slots
+        self.slot_elems = shard.world * shard.n_local
+        nbytes = 256 + slots * self.slot_elems * 2
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        grp = group if group is not None else dist.group.WORLD
+        self.handle = symm_mem.rendezvous(self.buf, grp.group_name)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # device arrays of pointers: flag arrays and data regions of every rank
+        self.peer_flags = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self.peer_data = torch.tensor([p + 256 for p in ptrs], dtype=torch.int64, device=device)
+        self.sync = torch.zeros(2, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=grp)
+
+    def slot(self, i: int) -> torch.Tensor:
+        """This rank's copy of gathered vector i (fp16 [world * n_local])."""
+        off = 256 + i * self.slot_elems * 2
+        return self.buf[off:off + self.slot_elems * 2].view(torch.float16)
+
+    def gemv_nf4(self, i: int, A, B, absmax, lut16, K: int, blocksize: int = 64,
+                 nibble_order: int = 0, wait: bool = True, wait_previous: bool = False) -> None:
+        """Fused NF4 GEMV of this rank's rows into gathered vector i of every rank.
+
+        wait: enqueue the bounded wait for THIS gather right after the kernel.
+        wait_previous: let the kernel wait, before it reads A, for the gather of
+        the previous fused call (a layer's input is the previous layer's gathered
+        output); the caller then only needs `wait_all()` after the last layer."""
+        from ._lib import check, load_library
+        lib = load_library()
+        sh = self.shard
+        stream = torch.cuda.current_stream().cuda_stream
+        off = i * self.slot_elems + sh.rank * sh.n_local
+        check("hq_nf4_gemv_f16_gather", lib.hq_nf4_gemv_f16_gather(
+            A.data_ptr(), B.data_ptr(), absmax.data_ptr(), lut16.data_ptr(), sh.n_local, K,
+            blocksize, nibble_order, self.peer_data.data_ptr(), off, self.peer_flags.data_ptr(),
+            self.sync.data_ptr(), sh.world, sh.rank,
+            self.buf.data_ptr() if wait_previous else 0, self.status.data_ptr(), stream))
+        if wait:
+            check("hq_gather_wait", lib.hq_gather_wait(
+                self.buf.data_ptr(), self.sync.data_ptr(), sh.world, self.status.data_ptr(),
+                stream))
+
+    def wait_all(self) -> None:
+        """Bounded wait until the slices of the latest fused call have landed here."""
+        from ._lib import check, load_library
+        check("hq_gather_wait", load_library().hq_gather_wait(
+            self.buf.data_ptr(), self.sync.data_ptr(), self.shard.world, self.status.data_ptr(),
+            torch.cuda.current_stream().cuda_stream))
+
+    def local_slice(self, i: int) -> torch.Tensor:
+        """This rank's own slice inside its copy of gathered vector i: an ordinary
+        kernel writes its outputs here, then `publish(i)` sends them to the peers."""
+        sh = self.shard
+        return self.slot(i)[sh.rank * sh.n_local:(sh.rank + 1) * sh.n_local]
+
+    def publish(self, i: int) -> None:
+        """Copy the local slice of vector i to all peers, flag it, and wait (bounded)
+        for the peers' slices of the same round."""
+        from ._lib import check, load_library
+        sh = self.shard
+        check("hq_gather_publish", load_library().hq_gather_publish(
+            self.peer_data.data_ptr(), i * self.slot_elems + sh.rank * sh.n_local, sh.n_local,
+            self.peer_flags.data_ptr(), self.sync.data_ptr(), sh.world, sh.rank,
+            self.status.data_ptr(), torch.cuda.current_stream().cuda_stream))

@@ -99,6 +99,42 @@ int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax,
                     const float* lut16, void* out_half, int N, int K, int blocksize,
                     int flags, hq_stream_t stream);
 
+/* NF4 GEMV of one GPU's output-feature slice, fused with the all-gather of the
+ * slices over NVLink (no counterpart in the reference tree).  Every GPU of the
+ * node runs the same call on its own N rows; each result is stored straight
+ * into the gathered vector of EVERY GPU (peer_out_half[r], r = 0..world-1,
+ * device-resident array of pointers to peer-mapped memory) at element
+ * gather_offset + n, n = 0..N-1 of this rank (normally gather_offset =
+ * rank * N).  When the last CTA has finished, the kernel bumps this rank's
+ * launch count (sync_words[1]; sync_words[0] is a CTA counter; both zero
+ * before the first call) and writes it to word `rank` of every GPU's flag array
+ * (peer_flags[r], `world` words each, zero before the first call).
+ * hq_gather_wait, enqueued after the call on the same stream, returns once all
+ * `world` flags of this GPU have reached this GPU's own launch count, i.e. once
+ * every slice of that gather has landed; its wait is bounded and sets *status
+ * (device int, nullable) to 1 if it runs out.  wait_flags (nullable; this
+ * GPU's own flag array) makes the kernel itself perform that wait for the
+ * PREVIOUS fused call before it reads A - the input of a layer is the gathered
+ * output of the layer before - so that its weights already stream while the
+ * last slices arrive; the wait is bounded and reports through *status.  Plain
+ * peer stores and loads only: no NCCL, no multicast. */
+int hq_nf4_gemv_f16_gather(const void* A_half, const uint8_t* B, const float* absmax,
+                           const float* lut16, int N, int K, int blocksize, int flags,
+                           void* const* peer_out_half, long long gather_offset,
+                           uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
+                           const uint32_t* wait_flags, int* status, hq_stream_t stream);
+int hq_gather_wait(const uint32_t* local_flags, const unsigned* sync_words, int world, int* status,
+                   hq_stream_t stream);
+/* The gather as a kernel of its own, for a slice that an ordinary launch has
+ * already written into this GPU's gathered vector (elements offset ..
+ * offset + n_slice of peer_out_half[rank]): copies the slice to every peer over
+ * NVLink, raises this rank's flag everywhere and waits (bounded, *status = 1 on
+ * expiry) until all ranks' slices of the same round have landed here.  Same
+ * buffers and conventions as hq_nf4_gemv_f16_gather. */
+int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
+                      uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
+                      int* status, hq_stream_t stream);
+
 /* ---------------- LUT-GEMM binary-coding mat-vec (lut-gemm) ---------------- */
 
 /* Bytes of zero-initialised device scratch hq_lutgemm_nqmv needs for M
