@@ -34,30 +34,44 @@ namespace {
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 constexpr int kQuads = kThreads / 4;
-constexpr int kTileRows = 4;                  // packed rows (32 inputs each) per tile
-constexpr int kLutBytes = 2 * 65536;          // 2 row pairs x 256 byte values x 256 B
-constexpr int kLutImm = 2048;                 // table block sits at shared address 64Ki*h + kLutImm
-constexpr int kCompactWords = kTileRows * 256 * 4;  // [row][byte value][j]
+// Shared-window address at which a CTA's dynamic region starts: the 1 KiB the
+// system reserves per CTA (the kernels have no static shared memory).  The
+// host checks the device attribute before launching and the kernel checks the
+// address itself; kSlack bytes of padding absorb a start up to kSlack later.
+constexpr int kDynBase = 1024;
+constexpr int kSlack = 256;
 
-// dynamic shared memory: [pad to the table address][tables 128 KiB][word ring][compact][inputs]
-// bytes of one column step in a quad's ring: packed words, then per alpha group
-// NB alpha vectors and one bias vector of four halves each
-template <int NB, int RPG>
-constexpr int step_bytes() {
-  return (kTileRows * NB * 16 + (kTileRows / RPG) * (NB + 1) * 8 + 15) / 16 * 16;
-}
-// The build scratch (compact tables + inputs) aliases the last ring buffer,
-// which is not written before the tables are complete.
-constexpr size_t kBuildBytes = (size_t)kCompactWords * 4 + 512 + 64;
-template <int NB, int RPG, int kBufs>
-constexpr size_t smem_bytes() {
-  constexpr size_t buf = (size_t)kQuads * step_bytes<NB, RPG>();
-  return (size_t)kLutImm + kLutBytes + (kBufs - 1) * buf + (buf > kBuildBytes ? buf : kBuildBytes);
-}
-// deepest ring (3 or 2 column steps per quad) that fits the 227 KiB of an SM
-template <int NB, int RPG>
+// Compile-time layout of one variant.  TR: packed rows (32 inputs each) per K
+// tile, 4 with one CTA per SM or 2 with two CTAs per SM.  Dynamic shared memory:
+//   [flag 16 B][word ring, kBufs buffers][padding][tables TR/2 x 64 KiB]
+// The tables start at the FIXED shared-window address kLutImm so that the
+// address of a lookup is a byte-permute plus an immediate.  The build scratch
+// (compact tables + inputs) aliases the last ring buffer, which is not written
+// before the tables are complete.
+template <int TR, int NB, int RPG, int kBufs>
+struct Layout {
+  static constexpr int kGroups = TR / RPG;
+  static constexpr int kWords = TR * NB;  // 16-byte word vectors per column step
+  // bytes of one column step in a quad's ring: packed words, then per alpha
+  // group NB alpha vectors and one bias vector of four halves each
+  static constexpr int kStep = (TR * NB * 16 + kGroups * (NB + 1) * 8 + 15) / 16 * 16;
+  static constexpr int kBuf = kQuads * kStep;
+  static constexpr int kCompactWords = TR * 256 * 4;  // [row][byte value][j]
+  static constexpr int kBuildBytes = kCompactWords * 4 + TR * 32 * 4 + 64;
+  static constexpr int kRing = (kBufs - 1) * kBuf + (kBuf > kBuildBytes ? kBuf : kBuildBytes);
+  static constexpr int kRingOff = 16;
+  static constexpr int kLutBytes = (TR / 2) * 65536;
+  static constexpr int kLutImm = (kDynBase + kSlack + kRingOff + kRing + 255) / 256 * 256;
+  static constexpr int kSmem = kLutImm - kDynBase + kLutBytes;
+  static constexpr int kCtasPerSm = TR == 2 ? 2 : 1;
+  // an SM has 228 KiB; each resident CTA also takes the reserved 1 KiB
+  static constexpr int kSmemLimit = 228 * 1024 / kCtasPerSm - kDynBase;
+  static_assert(kStep % 16 == 0, "ring slots hold 16-byte asynchronous copies");
+};
+// deepest ring (3 or 2 column steps per quad) that fits
+template <int TR, int NB, int RPG>
 constexpr int pick_bufs() {
-  return smem_bytes<NB, RPG, 3>() <= 227 * 1024 ? 3 : 2;
+  return Layout<TR, NB, RPG, 3>::kSmem <= Layout<TR, NB, RPG, 3>::kSmemLimit ? 3 : 2;
 }
 
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
@@ -98,42 +112,40 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// One launch handles NB bit planes b0 .. b0+NB-1 of nb_total (more than four
-// planes are split over two launches that accumulate into the same scratch
-// row; only the last one converts it).  RPG: packed rows that share one alpha
-// group inside a tile (4, 2 or 1).  kBufs: column steps resident in the word
-// ring per quad (kBufs - 1 in flight).
-template <int NB, int RPG, int kBufs>
-__global__ void __launch_bounds__(kThreads, 1)
+// One launch handles NB bit planes b0 .. b0+NB-1 of nb_total (more planes than
+// fit are split over launches that accumulate into the same scratch row; only
+// the last one converts it).  RPG: packed rows that share one alpha group
+// inside a tile.  kBufs: column steps resident in the word ring per quad
+// (kBufs - 1 in flight).  The word after the completion counter receives 1 if
+// the shared-memory layout does not fit where the CTA's dynamic region starts.
+template <int TR, int NB, int RPG, int kBufs>
+__global__ void __launch_bounds__(kThreads, (TR == 2 ? 2 : 1))
 lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha,
                const __half* __restrict__ q_bias, const __half* __restrict__ x,
                __half* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ counter,
                int M, int K, int rows_per_group, int cols_per_cta, int nb_total, int b0,
                int finalize) {
-  constexpr int kWords = kTileRows * NB;  // 16-byte word vectors per column step
-  constexpr int kStep =
-      (kTileRows * NB * 16 + (kTileRows / RPG) * (NB + 1) * 8 + 15) / 16 * 16;  // 16-byte slots
-  static_assert(kStep % 16 == 0, "ring slots hold 16-byte asynchronous copies");
-  constexpr int kGroups = kTileRows / RPG;
+  using L = Layout<TR, NB, RPG, kBufs>;
+  constexpr int kWords = L::kWords, kStep = L::kStep, kGroups = L::kGroups;
   constexpr int kItems = kGroups * (NB + 1);  // alpha / bias vectors per column step
+  constexpr int kLutImm = L::kLutImm;
   extern __shared__ __align__(16) unsigned char dsm[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // The table block sits at shared-window address 64Ki*h + kLutImm (h = 0 unless
-  // the dynamic region starts beyond kLutImm), so that a lookup address is a
-  // byte-permute {h, byte value, lane*4} plus the immediate kLutImm + row offset.
   const uint32_t dsm_addr = (uint32_t)__cvta_generic_to_shared(dsm);
-  const uint32_t h = dsm_addr > (uint32_t)kLutImm ? (dsm_addr - kLutImm + 0xffffu) >> 16 : 0u;
-  const uint32_t lut_addr = (h << 16) + kLutImm;
-  unsigned char* lut = dsm + (lut_addr - dsm_addr);
-  unsigned char* ring = lut + kLutBytes;
+  if (dsm_addr < (uint32_t)kDynBase || dsm_addr > (uint32_t)(kDynBase + kSlack)) {
+    if (tid == 0) counter[1] = 1u;  // same decision in every CTA: nothing is computed
+    return;
+  }
+  unsigned char* lut = dsm + ((uint32_t)kLutImm - dsm_addr);
+  unsigned char* ring = dsm + L::kRingOff;
+  unsigned* s_last = reinterpret_cast<unsigned*>(dsm);
   // ring layout: [buffer][quad][step bytes]; the build scratch aliases the last buffer
-  float* compact = reinterpret_cast<float*>(ring + (size_t)(kBufs - 1) * kQuads * kStep);
-  float* xs = compact + kCompactWords;  // 128 inputs of the tile
-  __shared__ unsigned s_last;
+  float* compact = reinterpret_cast<float*>(ring + (size_t)(kBufs - 1) * L::kBuf);
+  float* xs = compact + L::kCompactWords;  // the tile's inputs
   const int tile = blockIdx.y;
-  const int row0 = tile * kTileRows;  // first packed row of the tile
+  const int row0 = tile * TR;  // first packed row of the tile
   const int total_rows = K >> 5;
-  const int nrows = min(kTileRows, total_rows - row0);
+  const int nrows = min(TR, total_rows - row0);
 
   // ---- column steps of this warp and the quad's word ring ----
   const int j = lane & 3;   // byte of the word this lane looks up
@@ -142,8 +154,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   const int m_end = min(M, m_begin + cols_per_cta);
   const int m0 = m_begin + warp * 32 + cq * 4;  // step s handles columns m0 + s*kWarps*32 ..+3
   const int nsteps = (m_end - (m_begin + warp * 32) + kWarps * 32 - 1) / (kWarps * 32);
-  const uint32_t ring_quad = (uint32_t)__cvta_generic_to_shared(ring) +
-                             (uint32_t)((warp * 8 + cq) * kStep);
+  const uint32_t ring_quad = dsm_addr + L::kRingOff + (uint32_t)((warp * 8 + cq) * kStep);
   const uint32_t* src0 = bW + ((size_t)row0 * nb_total + b0) * M + m0;
   const int g0 = row0 / rows_per_group;  // alpha group of the tile's first row
 
@@ -153,7 +164,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     if (s < nsteps) {
       const int m = m0 + s * (kWarps * 32);
       if (m < m_end) {
-        const uint32_t dst = ring_quad + (uint32_t)((s % kBufs) * (kQuads * kStep));
+        const uint32_t dst = ring_quad + (uint32_t)((s % kBufs) * L::kBuf);
         const uint32_t* src = src0 + (size_t)s * (kWarps * 32);
         // alpha / bias vectors: item (group gi, plane b) with b == NB meaning the bias
 #pragma unroll
@@ -172,10 +183,11 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
           }
         }
 #pragma unroll
-        for (int t = 0; t < NB; t++) {
+        for (int t = 0; t < (kWords + 3) / 4; t++) {
           const int i = j + 4 * t;  // word vector (row i / NB, plane i % NB)
           const int r = i / NB, b = i - r * NB;
-          if (r < nrows) cp_async_16(dst + i * 16, src + (size_t)(r * nb_total + b) * M);
+          if (i < kWords && r < nrows)
+            cp_async_16(dst + i * 16, src + (size_t)(r * nb_total + b) * M);
         }
       }
     }
@@ -185,21 +197,21 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   for (int s = 0; s < kBufs - 1; s++) issue(s);
 
   // ---- stage the tile's inputs (zero beyond K) ----
-  if (tid < kTileRows * 32) {
+  if (tid < TR * 32) {
     const int k = row0 * 32 + tid;
     xs[tid] = (k < K) ? __half2float(x[k]) : 0.f;
   }
   __syncthreads();
 
-  // ---- phase A: thread = (byte value, row pair); signed sums of 8 inputs ----
+  // ---- phase A: thread = (byte value, TR/2 rows); signed sums of 8 inputs ----
   {
     const int bv = tid & 255, rp = tid >> 8;
     uint32_t sgn[8];
 #pragma unroll
     for (int t = 0; t < 8; t++) sgn[t] = ((bv >> t) & 1) ? 0u : 0x80000000u;
 #pragma unroll
-    for (int rr = 0; rr < 2; rr++) {
-      const int r = rp * 2 + rr;
+    for (int rr = 0; rr < TR / 2; rr++) {
+      const int r = rp * (TR / 2) + rr;
       float v[4];
 #pragma unroll
       for (int jj = 0; jj < 4; jj++) {
@@ -224,7 +236,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   {
     const int c = lane & 7, bl = lane >> 3;
 #pragma unroll 4
-    for (int it = 0; it < kTileRows * 256 / (kWarps * 4); it++) {
+    for (int it = 0; it < TR * 256 / (kWarps * 4); it++) {
       const int e = (it * kWarps + warp) * 4 + bl;  // row*256 + byte
       const int r = e >> 8, b = e & 255;
       const float4 v = *reinterpret_cast<const float4*>(compact + e * 4);
@@ -234,14 +246,14 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   __syncthreads();
 
   // ---- lookup phase ----
-  // lookup of byte value b in row r: [byteperm(word, hi, sel) + kLutImm + (r>>1)*65536 + (r&1)*128]
-  const uint32_t hi = (h << 16) | (uint32_t)(lane * 4);
+  // lookup of byte value b in row r: [byteperm(word, lane*4, sel) + kLutImm + (r>>1)*65536 + (r&1)*128]
+  const uint32_t hi = (uint32_t)(lane * 4);
   const uint32_t sel = 0x7604u | ((uint32_t)j << 4);
 
   // bias uses the all-ones entry (byte 255): sum of this lane's 8 inputs per row
-  float ones[kTileRows / RPG];
+  float ones[kGroups];
 #pragma unroll
-  for (int gi = 0; gi < kTileRows / RPG; gi++) {
+  for (int gi = 0; gi < kGroups; gi++) {
     float o = 0.f;
 #pragma unroll
     for (int r = gi * RPG; r < (gi + 1) * RPG; r++)
@@ -258,9 +270,9 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     __syncwarp();
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (active) {
-      const uint32_t buf = ring_quad + (uint32_t)((s % kBufs) * (kQuads * kStep));
+      const uint32_t buf = ring_quad + (uint32_t)((s % kBufs) * L::kBuf);
 #pragma unroll
-      for (int gi = 0; gi < kTileRows / RPG; gi++) {
+      for (int gi = 0; gi < kGroups; gi++) {
         float t[NB][4];
 #pragma unroll
         for (int rr = 0; rr < RPG; rr++) {
@@ -322,10 +334,10 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   if (tid == 0) {
     const unsigned total = gridDim.x * gridDim.y;
     const unsigned prev = atomicAdd(counter, 1u);
-    s_last = (prev == total - 1) ? 1u : 0u;
+    *s_last = (prev == total - 1) ? 1u : 0u;
   }
   __syncthreads();
-  if (s_last) {
+  if (*s_last) {
     __threadfence();
     for (int mm = tid; mm < M; mm += kThreads) {
       const float v = __ldcg(ws + mm);
@@ -349,43 +361,59 @@ struct LaunchArgs {
   int M, K, rows_per_group, cols_per_cta, nb_total;
 };
 
-template <int NB, int RPG, int kBufs>
+template <int TR, int NB, int RPG, int kBufs>
 int launch_one(const LaunchArgs& a, int b0, const __half* bias, int finalize) {
-  auto kern = lutgemm_kernel<NB, RPG, kBufs>;
-  constexpr size_t smem = smem_bytes<NB, RPG, kBufs>();
-  static_assert(smem <= 227 * 1024, "shared memory budget");
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  using L = Layout<TR, NB, RPG, kBufs>;
+  auto kern = lutgemm_kernel<TR, NB, RPG, kBufs>;
+  static_assert(L::kSmem <= L::kSmemLimit, "shared memory budget");
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kSmem);
   if (e != cudaSuccess) return cuda_status(e);
-  kern<<<a.grid, kThreads, smem, a.st>>>(a.bW, a.alpha, bias, a.x, a.out, a.ws, a.counter, a.M,
-                                         a.K, a.rows_per_group, a.cols_per_cta, a.nb_total, b0,
-                                         finalize);
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return cuda_status(e);
+  kern<<<a.grid, kThreads, L::kSmem, a.st>>>(a.bW, a.alpha, bias, a.x, a.out, a.ws, a.counter, a.M,
+                                             a.K, a.rows_per_group, a.cols_per_cta, a.nb_total, b0,
+                                             finalize);
   return launch_status();
 }
 
-template <int NB, int RPG>
+template <int TR, int NB, int RPG>
 int launch_sub(const LaunchArgs& a, int b0, const __half* bias, int finalize) {
-  return launch_one<NB, RPG, pick_bufs<NB, RPG>()>(a, b0, bias, finalize);
+  return launch_one<TR, NB, RPG, pick_bufs<TR, NB, RPG>()>(a, b0, bias, finalize);
 }
 
 // Bit planes are handled up to kMax at a time (what fits the shared-memory
 // ring); further planes go to follow-up launches that accumulate into the same
 // scratch row.  Only the first launch adds the bias term, only the last one
 // converts the scratch row.
-template <int RPG>
+template <int TR, int RPG>
 int launch_planes(const LaunchArgs& a) {
-  constexpr int kMax = RPG == 1 ? 3 : 4;
+  constexpr int kMax = (TR / RPG >= 2 && RPG == 1) ? 3 : 4;
   const int nb = a.nb_total;
   for (int b0 = 0; b0 < nb; b0 += kMax) {
     const int n = nb - b0 < kMax ? nb - b0 : kMax;
     const int last = (b0 + n == nb) ? 1 : 0;
     const __half* bias = b0 == 0 ? a.q_bias : nullptr;
     int st;
-    if (n == 1) st = launch_sub<1, RPG>(a, b0, bias, last);
-    else if (n == 2) st = launch_sub<2, RPG>(a, b0, bias, last);
-    else if (n == 3) st = launch_sub<3, RPG>(a, b0, bias, last);
-    else st = launch_sub<(kMax >= 4 ? 4 : 3), RPG>(a, b0, bias, last);
+    if (n == 1) st = launch_sub<TR, 1, RPG>(a, b0, bias, last);
+    else if (n == 2) st = launch_sub<TR, 2, RPG>(a, b0, bias, last);
+    else if (n == 3) st = launch_sub<TR, 3, RPG>(a, b0, bias, last);
+    else st = launch_sub<TR, (kMax >= 4 ? 4 : 3), RPG>(a, b0, bias, last);
     if (st != HQ_OK) return st;
   }
+  return HQ_OK;
+}
+
+// Shared memory the system reserves per CTA on the current device (the start
+// of a CTA's dynamic region when the kernel has no static shared memory).
+int reserved_smem_per_cta(int* out) {
+  int dev = 0, v = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e);
+  e = cudaDeviceGetAttribute(&v, cudaDevAttrReservedSharedMemoryPerBlock, dev);
+  if (e != cudaSuccess) return cuda_status(e);
+  *out = v;
   return HQ_OK;
 }
 
@@ -411,26 +439,32 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW, cons
       !aligned16(workspace))
     return HQ_ERR_MISALIGNED;
   const int rpg = group_size / 32;
-  int rpg_in_tile;
-  if (rpg % 4 == 0) rpg_in_tile = 4;
-  else if (rpg == 2) rpg_in_tile = 2;
-  else if (rpg == 1) rpg_in_tile = 1;
-  else return HQ_ERR_UNSUPPORTED;  // groups of 96, 160, ... inputs straddle tiles
+  // groups of 96, 160, ... inputs would straddle tiles
+  if (rpg != 1 && rpg % 2 != 0) return HQ_ERR_UNSUPPORTED;
+  int reserved = 0;
+  const int rst = reserved_smem_per_cta(&reserved);
+  if (rst != HQ_OK) return rst;
+  if (reserved < kDynBase || reserved > kDynBase + kSlack) return HQ_ERR_UNSUPPORTED;
 
-  const int tiles = (K / 32 + kTileRows - 1) / kTileRows;
+  // K tile: 128 inputs with one CTA per SM (the faster form on B200: 41 us
+  // against 54 us on a 12288 x 12288 3-plane matrix) wherever alpha groups do
+  // not straddle it; 64 inputs with two CTAs per SM for groups of 192, 320, ...
+  const int tile_rows = (rpg % 4 == 0 || rpg <= 2) ? 4 : 2;
+  const int ctas_per_sm = tile_rows == 2 ? 2 : 1;
+  const int tiles = (K / 32 + tile_rows - 1) / tile_rows;
   // columns per CTA: a multiple of 256 chosen so the grid is close to a
-  // multiple of the SM count with at least ~2 CTAs per SM when M allows.
-  const int sms = sm_count();
+  // multiple of the resident CTA slots while the table build stays amortised.
+  const int slots = sm_count() * ctas_per_sm;
   int best_cols = 256;
   double best_score = -1.0;
   const int max_chunks = (M + 255) / 256;
-  for (int chunk256 = 1; chunk256 <= max_chunks; chunk256++) {
-    const int mblocks = (max_chunks + chunk256 - 1) / chunk256;
-    const long ctas = (long)mblocks * tiles;
-    const long waves = (ctas + sms - 1) / sms;
+  for (int mb = 1; mb <= max_chunks; mb++) {
+    const int chunk256 = (max_chunks + mb - 1) / mb;  // balanced ranges
+    const long ctas = (long)((max_chunks + chunk256 - 1) / chunk256) * tiles;
+    const long waves = (ctas + slots - 1) / slots;
     // efficiency = useful lookups / (lookups + table build), times wave balance
     const double amort = (double)(chunk256 * 256) / (chunk256 * 256 + 700.0);
-    const double balance = (double)ctas / (double)(waves * sms);
+    const double balance = (double)ctas / (double)(waves * slots);
     const double score = amort * balance;
     if (score > best_score) { best_score = score; best_cols = chunk256 * 256; }
   }
@@ -451,9 +485,13 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW, cons
   a.rows_per_group = rpg;
   a.cols_per_cta = best_cols;
   a.nb_total = nb;
-  if (rpg_in_tile == 4) return launch_planes<4>(a);
-  if (rpg_in_tile == 2) return launch_planes<2>(a);
-  return launch_planes<1>(a);
+  if (tile_rows == 4) {
+    if (rpg % 4 == 0) return launch_planes<4, 4>(a);
+    if (rpg == 2) return launch_planes<4, 2>(a);
+    return launch_planes<4, 1>(a);
+  }
+  if (rpg % 2 == 0) return launch_planes<2, 2>(a);
+  return launch_planes<2, 1>(a);
 }
 
 // ---- entry point that allocates nothing ----------------------------------

@@ -235,7 +235,8 @@ def test_nf4_dequant_then_dense_matches_gemv(hq, oracle, dev):
 @pytest.mark.parametrize("M,K,nb,gs,bias", [
     (2048, 1024, 3, 128, True), (4096, 1024, 3, 128, False), (1024, 512, 4, 128, True),
     (512, 256, 8, 128, True), (260, 160, 3, 32, True), (1024, 256, 2, 64, True),
-    (12288, 12288, 3, 128, True), (256, 512, 1, 256, False), (64, 4096, 5, 512, True)])
+    (12288, 12288, 3, 128, True), (256, 512, 1, 256, False), (64, 4096, 5, 512, True),
+    (1024, 768, 3, 192, True), (516, 960, 5, 320, False)])  # groups of 192 / 320 inputs: 64-input tiles
 def test_lutgemm_nqmv(hq, oracle, dev, M, K, nb, gs, bias):
     import torch
     x, bW, alpha, qb = synth.lutgemm_case(M, K, nb, gs, seed=M + K + nb, bias=bias)
