@@ -39,6 +39,7 @@ import numpy as np
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+FALLBACK_BF16_TFLOPS = 1590.0
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -50,6 +51,18 @@ def measured_peak():
         except Exception:
             pass
     return FALLBACK_HBM_GBS, "fallback"
+
+
+def measured_tensor_peak():
+    """Dense bf16 cuBLAS throughput measured on this pool (burst figure: the
+    kernel is timed in a short graph, not inside a seconds-long step)."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_BF16_TFLOPS, "fallback"
 
 
 def ncu_traffic(workload: str):
@@ -119,14 +132,24 @@ def _host_case(name: str, seed: int):
                     bytes=K * 3 // 32 * N * 4 + 2 * (K // 128) * N * 2 + Mb * K * 2 + Mb * N * 2,
                     flops=2.0 * Mb * K * N,
                     desc=f"batched dequant-GEMM, 3-bit g128, X[{Mb}x{K}] x W[{K}x{N}] (Llama-3-70B MLP)")
+    if name == "qgemm_nf4":
+        Mb, K, N, bs = 64, 8192, 28672, 64
+        if os.environ.get("HQ_BENCH_QGEMM_SHAPE") == "down":
+            K, N = 28672, 8192
+        X, B, absmax, lut = synth.qgemm_nf4_case(Mb, K, N, bs, seed)
+        return dict(Mb=Mb, K=K, N=N, bs=bs, X=X, B=B, absmax=absmax, lut=lut,
+                    bytes=B.nbytes + absmax.nbytes + Mb * K * 2 + Mb * N * 2 + 64,
+                    flops=2.0 * Mb * K * N,
+                    desc=f"batched dequant-GEMM, NF4 blocksize 64, X[{Mb}x{K}] x W[{K}x{N}] "
+                         "(Llama-3-70B MLP)")
     raise SystemExit(f"unknown workload {name}")
 
 
 WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "bnb_quantize", "lutgemm",
-             "aqlm_1x16", "aqlm_2x8", "qgemm_q3"]
+             "aqlm_1x16", "aqlm_2x8", "qgemm_q3", "qgemm_nf4"]
 DTYPE = {"nf4_gemv": "f16", "nf4_dequant": "f16", "q3_gemv_f32": "f32", "q3_gemv_f16": "f16",
          "bnb_quantize": "u8", "lutgemm": "f16", "aqlm_1x16": "f16", "aqlm_2x8": "f16",
-         "qgemm_q3": "f16"}
+         "qgemm_q3": "f16", "qgemm_nf4": "f16"}
 
 
 class DeviceWorkload:
@@ -186,6 +209,12 @@ class DeviceWorkload:
             self.x = [t(c["X"]) for _ in range(R)]
             self.out = [torch.empty((c["Mb"], c["N"]), dtype=torch.float16, device=dev)
                         for _ in range(R)]
+        elif name == "qgemm_nf4":
+            self.B = [t(rot(c["B"], i)) for i in range(R)]
+            self.absmax, self.lut = t(c["absmax"]), t(c["lut"])
+            self.x = [t(c["X"]) for _ in range(R)]
+            self.out = [torch.empty((c["Mb"], c["N"]), dtype=torch.float16, device=dev)
+                        for _ in range(R)]
         elif name == "aqlm_2x8":
             self.codes = [t(rot(c["codes"], i)) for i in range(R)]
             self.cbs = t(c["cbs"])
@@ -219,6 +248,9 @@ class DeviceWorkload:
         elif n == "qgemm_q3":
             hq.qgemm_q3(self.x[i], self.mat[i], self.sc, self.z, c["N"], c["K"], 128,
                         out=self.out[i])
+        elif n == "qgemm_nf4":
+            hq.qgemm_nf4(self.x[i], self.B[i], self.absmax, self.lut, c["N"], c["K"], c["bs"], 0,
+                         out=self.out[i])
 
     # host <-> device traffic of one launch on the end-to-end path
     def host_io(self):
@@ -328,10 +360,29 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
         fn = lambda: O.aqlm_1x16_f32(c["codes"], c["x"], c["cb"], m, c["k"], [m, m, m, 1 << 30],
                                      65536)
         sample = "full mat-vec"
-    else:
+    elif name == "aqlm_2x8":
         m = c["m"]
         fn = lambda: O.aqlm_2x8_f64(c["codes"], c["x"], c["cbs"], m, c["k"])
         sample = "full mat-vec (fp64 oracle)"
+    elif name == "qgemm_q3":
+        cols = 128
+        mat = np.ascontiguousarray(O.q3_pack(c["codes"])[:, :cols])
+        sc, z = (np.ascontiguousarray(c[k][:, :cols]) for k in ("scales", "zeros"))
+        fn = lambda: O.gemm_f16_f64(c["X"], O.q3g_dequant_f16(mat, sc, z, c["K"], cols, 128))
+        sample = f"{cols} of {c['N']} output features (dequantise + fp64 product), one thread"
+        threads = 1
+        c = dict(c, bytes=c["bytes"] * cols / c["N"])
+    elif name == "qgemm_nf4":
+        cols = 128
+        B = c["B"][:cols * c["K"] // 2]
+        fn = lambda: O.gemm_f16_nk_f64(
+            c["X"], O.nf4_dequant_f16(B, c["absmax"], c["lut"], cols * c["K"], c["bs"],
+                                      0).reshape(cols, c["K"]))
+        sample = f"{cols} of {c['N']} output features (dequantise + fp64 product), one thread"
+        threads = 1
+        c = dict(c, bytes=c["bytes"] * cols / c["N"])
+    else:
+        raise SystemExit(f"no CPU baseline for {name}")
     fn()
     t0 = time.perf_counter(); reps = 0
     while True:
@@ -569,6 +620,16 @@ def main():
     if rank == 0:
         peak, peak_src = measured_peak()
         achieved = wl.bytes / (us_per_launch * 1e-6) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_source": f"of {peak_src}",
+                "traffic": ncu_traffic(args.workload), "same_size_pure_read_us": read_us}
+        if "flops" in wl.case:
+            # batch 64: 14.7 us of HBM time against 18.2 us of tensor time -> tensor bound
+            tpeak, tsrc = measured_tensor_peak()
+            tf = wl.case["flops"] / (us_per_launch * 1e-6) / 1e12
+            roof = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s",
+                    "frac": tf / tpeak, "peak_source": f"of {tsrc}",
+                    "traffic": ncu_traffic(args.workload), "hbm_frac": achieved / peak}
         line = {
             "metric": "effective_weight_bandwidth", "value": value, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -587,10 +648,7 @@ def main():
                                         if peer is not None else
                                         "NCCL all-gather of the slices after every layer"))},
             "us_per_gemv": us_per_launch,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_source": f"of {peak_src}",
-                         "traffic": ncu_traffic(args.workload),
-                         "same_size_pure_read_us": read_us},
+            "roofline": roof,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }
         if world == 1 and not args.no_cpu_baseline:

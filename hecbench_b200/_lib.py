@@ -38,6 +38,8 @@ SIGNATURES = {
     "hq_qgemm_workspace_bytes": (c_size_t, [c_int, c_int]),
     "hq_qgemm_q3_f16": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p, c_size_t, c_void_p,
                                                                c_void_p]),
+    "hq_qgemm_nf4_f16": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p,
+                                                                c_void_p]),
     "hq_aqlm_2x8_matvec": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p, c_void_p]),
 }
 

@@ -246,6 +246,15 @@ def code2x8_matvec(A, B, C_out, codebooks, prob_m: int, prob_k: int,
 _qgemm_ws = {}
 
 
+def _qgemm_workspace(lib, device, Mb: int, N: int):
+    key = (device, Mb, N)
+    ws = _qgemm_ws.get(key)
+    if ws is None:
+        ws = torch.zeros(lib.hq_qgemm_workspace_bytes(Mb, N), dtype=torch.uint8, device=device)
+        _qgemm_ws[key] = ws
+    return ws.data_ptr(), ws.numel()
+
+
 def qgemm_q3(X, mat, scales, zeros, N: int, K: int, group_size: int = 128,
              out: Optional[torch.Tensor] = None,
              status: Optional[torch.Tensor] = None, split_k: bool = True) -> torch.Tensor:
@@ -257,20 +266,34 @@ def qgemm_q3(X, mat, scales, zeros, N: int, K: int, group_size: int = 128,
     Mb = X.shape[0]
     if out is None:
         out = torch.empty((Mb, N), dtype=torch.float16, device=X.device)
-    ws_ptr, ws_bytes = 0, 0
-    if split_k:
-        key = (X.device, Mb, N)
-        ws = _qgemm_ws.get(key)
-        if ws is None:
-            ws = torch.zeros(lib.hq_qgemm_workspace_bytes(Mb, N), dtype=torch.uint8,
-                             device=X.device)
-            _qgemm_ws[key] = ws
-        ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
     args = (
         _dev(X, torch.float16, "X"), _dev(mat, torch.int32, "mat"),
         _dev(scales, torch.float16, "scales"), _dev(zeros, torch.float16, "zeros"),
-        _dev(out, torch.float16, "out"), Mb, N, K, group_size, ws_ptr, ws_bytes,
-        0 if status is None else _dev(status, torch.int32, "status"))
+        _dev(out, torch.float16, "out"), Mb, N, K, group_size)
+    ws_ptr, ws_bytes = _qgemm_workspace(lib, X.device, Mb, N) if split_k else (0, 0)
+    st = 0 if status is None else _dev(status, torch.int32, "status")
     with torch.cuda.device(X.device):
-        check("hq_qgemm_q3_f16", lib.hq_qgemm_q3_f16(*args, _stream()))
+        check("hq_qgemm_q3_f16", lib.hq_qgemm_q3_f16(*args, ws_ptr, ws_bytes, st, _stream()))
+    return out
+
+
+def qgemm_nf4(X, B, absmax, lut16, N: int, K: int, blocksize: int = 64, nibble_order: int = 0,
+              out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+              split_k: bool = True) -> torch.Tensor:
+    """Y[Mb][N] = X[Mb][K] @ W with W[k][n] the NF4 weight that dequantize_nf4
+    gives for element n*K + k of B (uint8[N*K/2], absmax per `blocksize`
+    elements); same conventions as gemv_nf4, same workspace and status rules as
+    qgemm_q3 (no counterpart in the reference tree)."""
+    lib = load_library()
+    Mb = X.shape[0]
+    if out is None:
+        out = torch.empty((Mb, N), dtype=torch.float16, device=X.device)
+    args = (
+        _dev(X, torch.float16, "X"), _dev(B, torch.uint8, "B"),
+        _dev(absmax, torch.float32, "absmax"), _dev(lut16, torch.float32, "lut16"),
+        _dev(out, torch.float16, "out"), Mb, N, K, blocksize, nibble_order)
+    ws_ptr, ws_bytes = _qgemm_workspace(lib, X.device, Mb, N) if split_k else (0, 0)
+    st = 0 if status is None else _dev(status, torch.int32, "status")
+    with torch.cuda.device(X.device):
+        check("hq_qgemm_nf4_f16", lib.hq_qgemm_nf4_f16(*args, ws_ptr, ws_bytes, st, _stream()))
     return out

@@ -1,10 +1,18 @@
-// Batched dequant-GEMM for the GPTQ 3-bit layout on the sm_100a tensor cores:
-//   Y[Mb][N] = X[Mb][K] * W[K][N],  W[k][n] = hfma(half(q[k][n]), scale[g][n], -zero[g][n])
-// X, Y, scale, zero are fp16, q is the packed 3-bit stream of quant3MatMul
-// (mat int32[K*3/32][N], 32 codes per 3 consecutive rows), g = k / group_size,
-// accumulation is fp32 in tensor memory.  No counterpart in the reference tree:
-// the dequant rule is the fp16 rule of quant3MatMul-cuda/kernels.h:121-122,137
-// with per-(group, column) parameters.
+// Batched dequant-GEMM on the sm_100a tensor cores, Y[Mb][N] = X[Mb][K] * W[K][N]
+// with fp16 X and Y and fp32 accumulation in tensor memory, for two packed
+// weight formats (no counterpart in the reference tree):
+//  * GPTQ 3-bit: W[k][n] = hfma(half(q[k][n]), scale[g][n], -zero[g][n]), q the
+//    packed 3-bit stream of quant3MatMul (mat int32[K*3/32][N], 32 codes per 3
+//    consecutive rows), g = k / group_size, fp16 scale / zero per (group,
+//    column): the fp16 rule of quant3MatMul-cuda/kernels.h:121-122,137;
+//  * NF4: W[k][n] = half(lut16[code[n*K + k]] * absmax[(n*K + k) / blocksize]),
+//    two 4-bit codes per byte in output-feature-major order B uint8[N][K/2]
+//    (even element in the high nibble unless the low-nibble-first flag is
+//    given): the dequantisation rule of hq_nf4_dequant_f16.
+// The description below is written for the 3-bit format; the NF4 form differs
+// only in the box the word warp fetches (128 rows x 32 bytes) and in the
+// unpack arithmetic (one fp32 table lookup and one multiply per code, packed to
+// half2 with round-to-nearest).
 //
 // The contraction is computed transposed so that the weight dimension fills
 // the 128 rows of a tcgen05.mma tile and the token batch is its N dimension:
@@ -54,14 +62,18 @@ constexpr int kTileN = 128;                 // output features per CTA (UMMA M)
 constexpr int kMaxTokens = 128;             // UMMA N upper bound handled here
 constexpr int kATile = kTileN * 128;        // bytes
 constexpr int kDeqLut = 64 * 128;           // 64 pair values x 32 lane copies x 4 B
-constexpr int kWordSlot = 6 * 512 + 2 * 256;  // 6 rows x 128 words, then 128 scales and 128 zeros
-constexpr int kWordRing = kWordAhead * kWordSlot;
+enum { kFmtQ3 = 0, kFmtNf4 = 1 };
+// bytes of one block's packed weights in the ring
+//   3-bit: 6 rows x 128 words, then 128 scales and 128 zeros;  NF4: 128 rows x 32 bytes
+template <int FMT>
+struct WordSlot { static constexpr int kBytes = FMT == kFmtQ3 ? 6 * 512 + 2 * 256 : 128 * 32; };
 constexpr int kProducerThreads = 256;
 constexpr int kThreads = 352;               // 8 unpack warps, MMA warp, two TMA warps
 constexpr uint32_t kSpinLimit = 1u << 20;   // bounded mbarrier polls
 
+template <int FMT>
 inline size_t qgemm_smem_bytes(int tokens_padded) {
-  return 1024 + (size_t)kStages * (kATile + tokens_padded * 128) + kWordRing + 512;
+  return 1024 + (size_t)kStages * (kATile + tokens_padded * 128) + kWordAhead * WordSlot<FMT>::kBytes + 512;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -150,7 +162,8 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// pair table: entry v (6 bits) = half2(v & 7, v >> 3), one copy per bank
+// lookup table with one copy per bank: [entry][lane].  3-bit: entry v (6 bits)
+// = half2(v & 7, v >> 3);  NF4: entry c (4 bits) = the fp32 level lut16[c]
 __shared__ __align__(16) uint32_t g_pair_lut[64 * 32];
 
 struct QgemmParams {
@@ -159,10 +172,15 @@ struct QgemmParams {
   unsigned* counters;
   int* status;
   int Mb, N, K, group_size, tokens_padded, ksplit;
+  // NF4 only (group_size is the absmax block size there)
+  const float* absmax;
+  const float* lut16;
+  int low_first;
 };
 
+template <int FMT>
 __global__ void __launch_bounds__(kThreads, 2)
-qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                 const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_z,
                 const QgemmParams p) {
   extern __shared__ unsigned char dsm_raw[];
@@ -170,6 +188,8 @@ qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   const uint32_t raw = smem_u32(dsm_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* sm = dsm_raw + (base - raw);
+  constexpr int kWordSlot = WordSlot<FMT>::kBytes;
+  constexpr int kWordRing = kWordAhead * kWordSlot;
   const int kBTile = p.tokens_padded * 128;
   const uint32_t a_tiles = base;
   const uint32_t b_tiles = base + kStages * kATile;
@@ -209,9 +229,13 @@ qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     mbar_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = tid; i < 64 * 32; i += kThreads) {
-    const int v = i >> 5;
-    g_pair_lut[i] = half2_as_u32(__halves2half2(__int2half_rn(v & 7), __int2half_rn(v >> 3)));
+  if (FMT == kFmtQ3) {
+    for (int i = tid; i < 64 * 32; i += kThreads) {
+      const int v = i >> 5;
+      g_pair_lut[i] = half2_as_u32(__halves2half2(__int2half_rn(v & 7), __int2half_rn(v >> 3)));
+    }
+  } else {
+    for (int i = tid; i < 16 * 32; i += kThreads) g_pair_lut[i] = __float_as_uint(p.lut16[i >> 5]);
   }
   if (warp == 8) {
     // 128 columns of tensor memory: accumulator D[128 lanes][tokens <= 128] fp32
@@ -245,65 +269,124 @@ qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
     uint32_t a_stage = (uint32_t)grp % kStages, a_parity = 1;  // parity meaning "stage released"
     uint32_t w_slot = (uint32_t)grp, w_parity = 0;
-    for (int i = grp; i < nloc; i += 2) {
-      if (!mbar_wait(wfull0 + 8 * w_slot, w_parity, ok)) ok = false;
-      uint32_t w[6];
-      uint16_t sc_bits, z_bits;
-      {
-        const uint32_t src = my_words + w_slot * kWordSlot;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+512];" : "=r"(w[1]) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+1024];" : "=r"(w[2]) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+1536];" : "=r"(w[3]) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+2048];" : "=r"(w[4]) : "r"(src));
-        asm volatile("ld.shared.u32 %0, [%1+2560];" : "=r"(w[5]) : "r"(src));
-        const uint32_t par = my_param + w_slot * kWordSlot;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc_bits) : "r"(par));
-        asm volatile("ld.shared.u16 %0, [%1+256];" : "=h"(z_bits) : "r"(par));
-      }
-      const __half2 sc2 = __half2half2(__ushort_as_half(sc_bits));
-      const __half2 nz2 = __half2half2(__hneg(__ushort_as_half(z_bits)));
-      uint32_t o[32];
-#pragma unroll
-      for (int hf = 0; hf < 2; hf++) {
-        const uint32_t w0 = w[3 * hf], w1 = w[3 * hf + 1], w2 = w[3 * hf + 2];
-        // sixteen 6-bit pair values of the 96-bit stream, as byte offsets (v << 7) | lane*4
-        uint32_t po[16];
-        po[0] = ((w0 << 7) & 0x1f80u) | lane4;
-        po[1] = ((w0 << 1) & 0x1f80u) | lane4;
-#pragma unroll
-        for (int q = 2; q < 5; q++) po[q] = ((w0 >> (6 * q - 7)) & 0x1f80u) | lane4;
-        po[5] = (__funnelshift_r(w0, w1, 23) & 0x1f80u) | lane4;
-        po[6] = ((w1 << 3) & 0x1f80u) | lane4;
-#pragma unroll
-        for (int q = 1; q < 4; q++) po[6 + q] = ((w1 >> (6 * q - 3)) & 0x1f80u) | lane4;
-        po[10] = (__funnelshift_r(w1, w2, 21) & 0x1f80u) | lane4;
-        po[11] = ((w2 << 5) & 0x1f80u) | lane4;
-#pragma unroll
-        for (int q = 1; q < 5; q++) po[11 + q] = ((w2 >> (6 * q - 5)) & 0x1f80u) | lane4;
-#pragma unroll
-        for (int e = 0; e < 16; e++) {
-          const uint32_t q2 = *reinterpret_cast<const uint32_t*>(lut + po[e]);
-          o[16 * hf + e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
+    if constexpr (FMT == kFmtQ3) {
+      for (int i = grp; i < nloc; i += 2) {
+        if (!mbar_wait(wfull0 + 8 * w_slot, w_parity, ok)) ok = false;
+        uint32_t w[6];
+        uint16_t sc_bits, z_bits;
+        {
+          const uint32_t src = my_words + w_slot * kWordSlot;
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(src));
+          asm volatile("ld.shared.u32 %0, [%1+512];" : "=r"(w[1]) : "r"(src));
+          asm volatile("ld.shared.u32 %0, [%1+1024];" : "=r"(w[2]) : "r"(src));
+          asm volatile("ld.shared.u32 %0, [%1+1536];" : "=r"(w[3]) : "r"(src));
+          asm volatile("ld.shared.u32 %0, [%1+2048];" : "=r"(w[4]) : "r"(src));
+          asm volatile("ld.shared.u32 %0, [%1+2560];" : "=r"(w[5]) : "r"(src));
+          const uint32_t par = my_param + w_slot * kWordSlot;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sc_bits) : "r"(par));
+          asm volatile("ld.shared.u16 %0, [%1+256];" : "=h"(z_bits) : "r"(par));
         }
+        const __half2 sc2 = __half2half2(__ushort_as_half(sc_bits));
+        const __half2 nz2 = __half2half2(__hneg(__ushort_as_half(z_bits)));
+        uint32_t o[32];
+  #pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          const uint32_t w0 = w[3 * hf], w1 = w[3 * hf + 1], w2 = w[3 * hf + 2];
+          // sixteen 6-bit pair values of the 96-bit stream, as byte offsets (v << 7) | lane*4
+          uint32_t po[16];
+          po[0] = ((w0 << 7) & 0x1f80u) | lane4;
+          po[1] = ((w0 << 1) & 0x1f80u) | lane4;
+  #pragma unroll
+          for (int q = 2; q < 5; q++) po[q] = ((w0 >> (6 * q - 7)) & 0x1f80u) | lane4;
+          po[5] = (__funnelshift_r(w0, w1, 23) & 0x1f80u) | lane4;
+          po[6] = ((w1 << 3) & 0x1f80u) | lane4;
+  #pragma unroll
+          for (int q = 1; q < 4; q++) po[6 + q] = ((w1 >> (6 * q - 3)) & 0x1f80u) | lane4;
+          po[10] = (__funnelshift_r(w1, w2, 21) & 0x1f80u) | lane4;
+          po[11] = ((w2 << 5) & 0x1f80u) | lane4;
+  #pragma unroll
+          for (int q = 1; q < 5; q++) po[11 + q] = ((w2 >> (6 * q - 5)) & 0x1f80u) | lane4;
+  #pragma unroll
+          for (int e = 0; e < 16; e++) {
+            const uint32_t q2 = *reinterpret_cast<const uint32_t*>(lut + po[e]);
+            o[16 * hf + e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
+          }
+        }
+        // the ring slot is released only now: the lookups above consumed the words,
+        // so the loads have certainly returned
+        mbar_arrive(wempty0 + 8 * w_slot);
+        w_slot += 2;
+        if (w_slot >= kWordAhead) { w_slot -= kWordAhead; w_parity ^= 1u; }
+        // the A tile of this stage must have been released by the tensor core
+        if (!mbar_wait(empty0 + 8 * a_stage, a_parity, ok)) ok = false;
+        const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
+  #pragma unroll
+        for (int c = 0; c < 8; c++)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + (((uint32_t)c ^ swz) * 16)),
+                       "r"(o[4 * c]), "r"(o[4 * c + 1]), "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
+                       : "memory");
+        fence_async_smem();
+        mbar_arrive(full0 + 8 * a_stage);
+        a_stage += 2;
+        if (a_stage >= kStages) { a_stage -= kStages; a_parity ^= 1u; }
       }
-      // the ring slot is released only now: the lookups above consumed the words,
-      // so the loads have certainly returned
-      mbar_arrive(wempty0 + 8 * w_slot);
-      w_slot += 2;
-      if (w_slot >= kWordAhead) { w_slot -= kWordAhead; w_parity ^= 1u; }
-      // the A tile of this stage must have been released by the tensor core
-      if (!mbar_wait(empty0 + 8 * a_stage, a_parity, ok)) ok = false;
-      const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
+    } else {
+      // NF4: the thread's 64 codes of a block are 32 consecutive bytes of its row;
+      // the block's absmax comes straight from global memory, one block ahead
+      const uint32_t my_bytes = word_ring + (uint32_t)(row * 32);
+      const float* am_row = p.absmax + ((size_t)(n0 + row) * p.K) / p.group_size;
+      const int am_shift = 31 - __clz(p.group_size / kBlockK);  // blocks per absmax = 2^am_shift
+      const bool am_pow2 = ((p.group_size / kBlockK) & (p.group_size / kBlockK - 1)) == 0;
+      auto am_index = [&](int kb) {
+        return am_pow2 ? (kb >> am_shift) : (kb * kBlockK) / p.group_size;
+      };
+      float am_next = grp < nloc ? __ldg(am_row + am_index(kb0 + grp)) : 0.f;
+      const bool low_first = p.low_first != 0;
+      for (int i = grp; i < nloc; i += 2) {
+        const float am = am_next;
+        if (i + 2 < nloc) am_next = __ldg(am_row + am_index(kb0 + i + 2));
+        if (!mbar_wait(wfull0 + 8 * w_slot, w_parity, ok)) ok = false;
+        uint32_t w[8];
+        {
+          const uint32_t src = my_bytes + w_slot * kWordSlot;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                       : "r"(src));
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+16];"
+                       : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                       : "r"(src));
+        }
+        uint32_t o[32];
 #pragma unroll
-      for (int c = 0; c < 8; c++)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + (((uint32_t)c ^ swz) * 16)),
-                     "r"(o[4 * c]), "r"(o[4 * c + 1]), "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
-                     : "memory");
-      fence_async_smem();
-      mbar_arrive(full0 + 8 * a_stage);
-      a_stage += 2;
-      if (a_stage >= kStages) { a_stage -= kStages; a_parity ^= 1u; }
+        for (int q = 0; q < 8; q++) {
+#pragma unroll
+          for (int t = 0; t < 4; t++) {
+            // byte t of word q: codes (high nibble, low nibble) as table offsets (c << 7) | lane*4
+            const uint32_t hi_off =
+                ((t == 0 ? (w[q] << 3) : (w[q] >> (8 * t - 3))) & 0x780u) | lane4;
+            const uint32_t lo_off =
+                ((t == 0 ? (w[q] << 7) : (w[q] >> (8 * t - 7))) & 0x780u) | lane4;
+            const float f_hi = __uint_as_float(*reinterpret_cast<const uint32_t*>(lut + hi_off)) * am;
+            const float f_lo = __uint_as_float(*reinterpret_cast<const uint32_t*>(lut + lo_off)) * am;
+            o[4 * q + t] = half2_as_u32(low_first ? __floats2half2_rn(f_lo, f_hi)
+                                                  : __floats2half2_rn(f_hi, f_lo));
+          }
+        }
+        mbar_arrive(wempty0 + 8 * w_slot);
+        w_slot += 2;
+        if (w_slot >= kWordAhead) { w_slot -= kWordAhead; w_parity ^= 1u; }
+        if (!mbar_wait(empty0 + 8 * a_stage, a_parity, ok)) ok = false;
+        const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + (((uint32_t)c ^ swz) * 16)),
+                       "r"(o[4 * c]), "r"(o[4 * c + 1]), "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
+                       : "memory");
+        fence_async_smem();
+        mbar_arrive(full0 + 8 * a_stage);
+        a_stage += 2;
+        if (a_stage >= kStages) { a_stage -= kStages; a_parity ^= 1u; }
+      }
     }
   } else if (warp == 8 && lane == 0) {
     // ------------------------------ MMA issuer ------------------------------
@@ -332,9 +415,13 @@ qgemm_q3_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       const int g = ((kb0 + i) * kBlockK) / p.group_size;
       const uint32_t dst = word_ring + slot * kWordSlot;
       mbar_expect_tx(wfull0 + 8 * slot, kWordSlot);
-      tma_load_2d(dst, &map_w, n0, 6 * (kb0 + i), wfull0 + 8 * slot);
-      tma_load_2d(dst + 6 * 512, &map_s, n0, g, wfull0 + 8 * slot);
-      tma_load_2d(dst + 6 * 512 + 256, &map_z, n0, g, wfull0 + 8 * slot);
+      if constexpr (FMT == kFmtQ3) {
+        tma_load_2d(dst, &map_w, n0, 6 * (kb0 + i), wfull0 + 8 * slot);
+        tma_load_2d(dst + 6 * 512, &map_s, n0, g, wfull0 + 8 * slot);
+        tma_load_2d(dst + 6 * 512 + 256, &map_z, n0, g, wfull0 + 8 * slot);
+      } else {
+        tma_load_2d(dst, &map_w, 32 * (kb0 + i), n0, wfull0 + 8 * slot);
+      }
       if (++slot == kWordAhead) { slot = 0; parity ^= 1u; }
     }
   } else if (warp == 10 && lane == 0) {
@@ -426,6 +513,69 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+
+// X[Mb][K] fp16: box = 64 inputs x tokens_padded rows, 128-byte swizzle; rows
+// beyond Mb are out of bounds and arrive as zeros
+int encode_x_map(EncodeTiledFn encode, CUtensorMap* map_x, const void* X_half, int Mb, int K) {
+  const int tokens_padded = (Mb + 15) / 16 * 16;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Mb};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)tokens_padded};
+  const cuuint32_t estr[2] = {1, 1};
+  if (encode(map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(X_half), dims, strides,
+             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return HQ_ERR_UNSUPPORTED;
+  return HQ_OK;
+}
+
+size_t qgemm_ws_bytes(int Mb, int N) {
+  return ((size_t)Mb * N * 4 + 255) / 256 * 256 + ((size_t)(N / kTileN + 1) * 4 + 255) / 256 * 256;
+}
+
+// K split: only with a workspace, and only when the tiles alone cannot fill
+// the CTA slots of the machine (two per SM)
+QgemmParams make_params(void* Y_half, int Mb, int N, int K, int group_size, void* workspace,
+                        size_t workspace_bytes, int* status_word) {
+  QgemmParams prm;
+  const int tiles = N / kTileN;
+  const int slots = 2 * sm_count();
+  int ksplit = 1;
+  if (workspace != nullptr && workspace_bytes >= qgemm_ws_bytes(Mb, N) && aligned16(workspace)) {
+    ksplit = slots / tiles;
+    const int nkb = K / kBlockK;
+    if (ksplit > nkb / 8) ksplit = nkb / 8;
+    if (ksplit < 1) ksplit = 1;
+  }
+  prm.Y = reinterpret_cast<__half*>(Y_half);
+  prm.ws = reinterpret_cast<float*>(workspace);
+  prm.counters = workspace ? reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
+                                                         ((size_t)Mb * N * 4 + 255) / 256 * 256)
+                           : nullptr;
+  prm.status = status_word;
+  prm.Mb = Mb;
+  prm.N = N;
+  prm.K = K;
+  prm.group_size = group_size;
+  prm.tokens_padded = (Mb + 15) / 16 * 16;
+  prm.ksplit = ksplit;
+  prm.absmax = nullptr;
+  prm.lut16 = nullptr;
+  prm.low_first = 0;
+  return prm;
+}
+
+template <int FMT>
+int launch_qgemm(const CUtensorMap& map_x, const CUtensorMap& map_w, const CUtensorMap& map_s,
+                 const CUtensorMap& map_z, const QgemmParams& prm, hq_stream_t stream) {
+  const size_t smem = qgemm_smem_bytes<FMT>(prm.tokens_padded);
+  cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return cuda_status(e);
+  qgemm_kernel<FMT><<<dim3(prm.N / kTileN, prm.ksplit), kThreads, smem, (cudaStream_t)stream>>>(
+      map_x, map_w, map_s, map_z, prm);
+  return launch_status();
+}
 }  // namespace
 }  // namespace hq
 
@@ -433,7 +583,7 @@ extern "C" {
 
 size_t hq_qgemm_workspace_bytes(int Mb, int N) {
   if (Mb <= 0 || N <= 0) return 0;
-  return ((size_t)Mb * N * 4 + 255) / 256 * 256 + ((size_t)(N / hq::kTileN + 1) * 4 + 255) / 256 * 256;
+  return hq::qgemm_ws_bytes(Mb, N);
 }
 
 int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_half,
@@ -445,41 +595,13 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
   if (Mb <= 0 || Mb > kMaxTokens || N <= 0 || K <= 0 || N % kTileN != 0 || K % kBlockK != 0)
     return HQ_ERR_BAD_SHAPE;
   if (group_size <= 0 || group_size % kBlockK != 0 || K % group_size != 0) return HQ_ERR_BAD_SHAPE;
-  if (!aligned16(X_half) || !aligned16(mat) || !aligned16(scales_half) || !aligned16(zeros_half) ||
-      (K % 8) != 0)
+  if (!aligned16(X_half) || !aligned16(mat) || !aligned16(scales_half) || !aligned16(zeros_half))
     return HQ_ERR_MISALIGNED;
-  const int tokens_padded = (Mb + 15) / 16 * 16;
-  const size_t smem = qgemm_smem_bytes(tokens_padded);
-  cudaError_t e = cudaFuncSetAttribute(qgemm_q3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem);
-  if (e != cudaSuccess) return cuda_status(e);
-  // K split: only with a workspace, and only when the tiles alone cannot fill
-  // the CTA slots of the machine (two per SM)
-  const int tiles = N / kTileN;
-  const int slots = 2 * sm_count();
-  int ksplit = 1;
-  if (workspace != nullptr && workspace_bytes >= hq_qgemm_workspace_bytes(Mb, N) &&
-      aligned16(workspace)) {
-    ksplit = slots / tiles;
-    const int nkb = K / kBlockK;
-    if (ksplit > nkb / 8) ksplit = nkb / 8;
-    if (ksplit < 1) ksplit = 1;
-  }
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return HQ_ERR_UNSUPPORTED;
-  CUtensorMap map_x, map_w;
-  {
-    // X[Mb][K] fp16: box = 64 inputs x tokens_padded rows, 128-byte swizzle; rows
-    // beyond Mb are out of bounds and arrive as zeros
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Mb};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)tokens_padded};
-    const cuuint32_t estr[2] = {1, 1};
-    if (encode(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(X_half), dims,
-               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return HQ_ERR_UNSUPPORTED;
-  }
+  CUtensorMap map_x, map_w, map_s, map_z;
+  int st = encode_x_map(encode, &map_x, X_half, Mb, K);
+  if (st != HQ_OK) return st;
   {
     // mat int32[K*3/32][N]: box = 128 columns x 6 rows (one block of 64 inputs)
     const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 32 * 3)};
@@ -491,7 +613,6 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return HQ_ERR_UNSUPPORTED;
   }
-  CUtensorMap map_s, map_z;
   for (int which = 0; which < 2; which++) {
     // scales / zeros fp16 [K/group_size][N]: box = 128 columns x 1 group
     const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / group_size)};
@@ -504,22 +625,42 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return HQ_ERR_UNSUPPORTED;
   }
-  QgemmParams prm;
-  prm.Y = reinterpret_cast<__half*>(Y_half);
-  prm.ws = reinterpret_cast<float*>(workspace);
-  prm.counters = workspace ? reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
-                                                         ((size_t)Mb * N * 4 + 255) / 256 * 256)
-                           : nullptr;
-  prm.status = status_word;
-  prm.Mb = Mb;
-  prm.N = N;
-  prm.K = K;
-  prm.group_size = group_size;
-  prm.tokens_padded = tokens_padded;
-  prm.ksplit = ksplit;
-  qgemm_q3_kernel<<<dim3(tiles, ksplit), kThreads, smem, (cudaStream_t)stream>>>(map_x, map_w, map_s,
-                                                                               map_z, prm);
-  return launch_status();
+  QgemmParams prm = make_params(Y_half, Mb, N, K, group_size, workspace, workspace_bytes, status_word);
+  return launch_qgemm<kFmtQ3>(map_x, map_w, map_s, map_z, prm, stream);
+}
+
+int hq_qgemm_nf4_f16(const void* X_half, const uint8_t* B, const float* absmax, const float* lut16,
+                     void* Y_half, int Mb, int N, int K, int blocksize, int flags, void* workspace,
+                     size_t workspace_bytes, int* status_word, hq_stream_t stream) {
+  using namespace hq;
+  if (!X_half || !B || !absmax || !lut16 || !Y_half) return HQ_ERR_NULL_POINTER;
+  if (Mb <= 0 || Mb > kMaxTokens || N <= 0 || K <= 0 || N % kTileN != 0 || K % kBlockK != 0)
+    return HQ_ERR_BAD_SHAPE;
+  // one absmax per (row, K block): blocks of 64 k inputs that never straddle a row
+  if (blocksize <= 0 || blocksize % kBlockK != 0 || K % blocksize != 0) return HQ_ERR_BAD_SHAPE;
+  if (!aligned16(X_half) || !aligned16(B) || ((uintptr_t)absmax & 3u) != 0)
+    return HQ_ERR_MISALIGNED;
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return HQ_ERR_UNSUPPORTED;
+  CUtensorMap map_x, map_w;
+  int st = encode_x_map(encode, &map_x, X_half, Mb, K);
+  if (st != HQ_OK) return st;
+  {
+    // B uint8[N][K/2]: box = 32 bytes (64 codes) x 128 rows
+    const cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kTileN};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(B), dims, strides, box,
+               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return HQ_ERR_UNSUPPORTED;
+  }
+  QgemmParams prm = make_params(Y_half, Mb, N, K, blocksize, workspace, workspace_bytes, status_word);
+  prm.absmax = absmax;
+  prm.lut16 = lut16;
+  prm.low_first = (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0;
+  return launch_qgemm<kFmtNf4>(map_x, map_w, map_w, map_w, prm, stream);
 }
 
 }  // extern "C"

@@ -63,6 +63,13 @@ def nf4_case(N: int, K: int, blocksize: int = 64, seed: int = 0):
     return A, B, absmax, nf4_levels(seed)
 
 
+def qgemm_nf4_case(Mb: int, K: int, N: int, blocksize: int = 64, seed: int = 0):
+    """Batched NF4 path: fp16 X~N(0,1) plus the weights of nf4_case(N, K)."""
+    _, B, absmax, lut16 = nf4_case(N, K, blocksize, seed)
+    X = _rng(seed, 55).standard_normal((Mb, K)).astype(np.float16)
+    return X, B, absmax, lut16
+
+
 def lutgemm_case(M: int, K: int, nb: int = 3, group_size: int = 128, seed: int = 0,
                  bias: bool = True):
     """LUT-GEMM: fp16 x~N(0,1), Bernoulli(1/2) sign planes uint32[K/32][nb][M],

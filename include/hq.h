@@ -218,6 +218,17 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
                     void* workspace, size_t workspace_bytes, int* status_word,
                     hq_stream_t stream);
 
+/* The same product with NF4 weights in the layout of hq_nf4_gemv_f16:
+ * B uint8[N][K/2] (output-feature-major, two codes per byte; flags as there),
+ * absmax float[N*K/blocksize], lut16 float[16];
+ * W[k][n] = half(lut16[code] * absmax[(n*K + k) / blocksize]) exactly as
+ * hq_nf4_dequant_f16 produces it.  No counterpart in the reference tree.
+ * 1 <= Mb <= 128, N % 128 == 0, blocksize % 64 == 0, K % blocksize == 0.
+ * workspace and status_word as for hq_qgemm_q3_f16. */
+int hq_qgemm_nf4_f16(const void* X_half, const uint8_t* B, const float* absmax, const float* lut16,
+                     void* Y_half, int Mb, int N, int K, int blocksize, int flags, void* workspace,
+                     size_t workspace_bytes, int* status_word, hq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,5 +1,6 @@
-"""Batched dequant-GEMM on the tensor cores (tcgen05 / tensor memory) against
-the oracle: bit-exact fp16 dequantised weights (oracle rule) times X in fp64.
+"""Batched dequant-GEMM on the tensor cores (tcgen05 / tensor memory), 3-bit
+and NF4 weights, against the oracle: bit-exact fp16 dequantised weights
+(oracle rule) times X in fp64.
 No reference implementation exists for this path (parity unpinned); tolerance
 1e-2 on |y - ref| / max(|ref|, rms(ref)) for the fp16 output."""
 import numpy as np
@@ -31,6 +32,43 @@ def _run(hq, oracle, dev, Mb, K, N, group, seed):
                                           (37, 256, 128, 128), (1, 128, 128, 64)])
 def test_qgemm_q3_small(hq, oracle, dev, Mb, K, N, group):
     assert _run(hq, oracle, dev, Mb, K, N, group, seed=Mb + K + N) < TOL_F16
+
+
+def _run_nf4(hq, oracle, dev, Mb, K, N, blocksize, low_first, seed):
+    import torch
+    X, B, absmax, lut16 = synth.qgemm_nf4_case(Mb, K, N, blocksize, seed)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    Y = hq.qgemm_nf4(to_dev(X, dev), to_dev(B, dev), to_dev(absmax, dev), to_dev(lut16, dev), N, K,
+                     blocksize, low_first, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded in-kernel wait ran out"
+    W16 = oracle.nf4_dequant_f16(B, absmax, lut16, N * K, blocksize, low_first).reshape(N, K)
+    ref = oracle.gemm_f16_nk_f64(X, W16)
+    return oracle.rel_err(Y.cpu().numpy().astype(np.float64), ref)
+
+
+@pytest.mark.parametrize("Mb,K,N,blocksize,low_first", [
+    (64, 256, 128, 64, 0), (16, 128, 256, 64, 1), (64, 1024, 512, 64, 0), (128, 512, 256, 128, 0),
+    (37, 768, 128, 256, 1), (1, 128, 128, 64, 0), (64, 4096, 1024, 64, 0), (32, 576, 384, 192, 0)])
+def test_qgemm_nf4_small(hq, oracle, dev, Mb, K, N, blocksize, low_first):
+    assert _run_nf4(hq, oracle, dev, Mb, K, N, blocksize, low_first, seed=Mb + K + N) < TOL_F16
+
+
+def test_qgemm_nf4_matches_dequant_then_gemm(hq, dev):
+    """Llama-2-7B MLP shape (11008 x 4096): the fused kernel against the library's
+    own NF4 dequantisation followed by a dense fp32 product in torch (checker only)."""
+    import torch
+    Mb, K, N = 64, 4096, 11008
+    X, B, absmax, lut16 = synth.qgemm_nf4_case(Mb, K, N, 64, 5)
+    dX, dB, dA, dL = (to_dev(a, dev) for a in (X, B, absmax, lut16))
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    Y = hq.qgemm_nf4(dX, dB, dA, dL, N, K, 64, 0, status=status)
+    W = hq.dequantize_nf4(dB, dA, dL, N * K, 64, 0).view(N, K)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = dX.float() @ W.float().t()
+    err = (Y.float() - ref).abs() / torch.maximum(ref.abs(), ref.pow(2).mean().sqrt())
+    assert float(err.max()) < TOL_F16
 
 
 def test_qgemm_q3_llama_shapes_property(hq, dev):
