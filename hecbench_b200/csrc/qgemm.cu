@@ -55,12 +55,12 @@
 namespace hq {
 namespace {
 
-constexpr int kStages = 3;
+constexpr int kStages = 4;                  // two per pipeline (unpack group + MMA issuer)
 constexpr int kWordAhead = 6;               // packed-word blocks in flight (shared-memory ring)
 constexpr int kBlockK = 64;                 // halves per smem row (128 bytes)
 constexpr int kTileN = 128;                 // output features per CTA (UMMA M)
 constexpr int kMaxTokens = 128;             // UMMA N upper bound handled here
-constexpr int kATile = kTileN * 128;        // bytes
+constexpr int kAColumns = kBlockK / 2;      // tensor-memory columns of one A stage (2 halves each)
 constexpr int kDeqLut = 64 * 128;           // 64 pair values x 32 lane copies x 4 B
 enum { kFmtQ3 = 0, kFmtNf4 = 1 };
 // bytes of one block's packed weights in the ring
@@ -68,12 +68,17 @@ enum { kFmtQ3 = 0, kFmtNf4 = 1 };
 template <int FMT>
 struct WordSlot { static constexpr int kBytes = FMT == kFmtQ3 ? 6 * 512 + 2 * 256 : 128 * 32; };
 constexpr int kProducerThreads = 256;
-constexpr int kThreads = 352;               // 8 unpack warps, MMA warp, two TMA warps
+constexpr int kThreads = 384;               // 8 unpack warps, MMA warp, two TMA warps, MMA warp
 constexpr uint32_t kSpinLimit = 1u << 20;   // bounded mbarrier polls
 
 template <int FMT>
 inline size_t qgemm_smem_bytes(int tokens_padded) {
-  return 1024 + (size_t)kStages * (kATile + tokens_padded * 128) + kWordAhead * WordSlot<FMT>::kBytes + 512;
+  const size_t need =
+      1024 + (size_t)kStages * (tokens_padded * 128) + kWordAhead * WordSlot<FMT>::kBytes + 512;
+  // The request also sets the number of CTAs per SM to what tensor memory holds:
+  // two CTAs of 256 columns up to 64 tokens, one CTA of 512 columns beyond.
+  const size_t floor_bytes = tokens_padded <= 64 ? 90 * 1024 : 120 * 1024;
+  return need > floor_bytes ? need : floor_bytes;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -146,6 +151,27 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0)
       : "memory");
 }
+// the same with the A operand in tensor memory (128 lanes x 8 columns of two halves per K = 16)
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0)
+      : "memory");
+}
+// 32 consecutive columns of the executing warp's 32 lanes, one lane per thread
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+      "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+      "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -191,23 +217,32 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
   constexpr int kWordSlot = WordSlot<FMT>::kBytes;
   constexpr int kWordRing = kWordAhead * kWordSlot;
   const int kBTile = p.tokens_padded * 128;
-  const uint32_t a_tiles = base;
-  const uint32_t b_tiles = base + kStages * kATile;
-  const uint32_t tiles_bytes = (uint32_t)(kStages * (kATile + kBTile));
+  const uint32_t b_tiles = base;
+  const uint32_t tiles_bytes = (uint32_t)(kStages * kBTile);
   const uint32_t word_ring = base + tiles_bytes;  // [kWordAhead][6 rows][128 columns] words
   const uint32_t bars = base + tiles_bytes + kWordRing;
   // barrier slots (8 bytes each)
-  const uint32_t full0 = bars;                          // A tile written (256 arrivals)
-  const uint32_t empty0 = full0 + 8 * kStages;          // stage released by the tensor core
-  const uint32_t xfull0 = empty0 + 8 * kStages;         // B tile landed (TMA bytes)
-  const uint32_t wfull0 = xfull0 + 8 * kStages;         // word box landed (TMA bytes)
-  const uint32_t wempty0 = wfull0 + 8 * kWordAhead;     // word box read by all 256 threads
-  const uint32_t accum_bar = wempty0 + 8 * kWordAhead;
+  // Pipeline j = unpack group j + MMA issuer j handles blocks j, j + 2, ... in
+  // its own two stages j and j + 2, so every stage barrier has one producer side
+  // and one consumer side that take its phases strictly in order.
+  // full[st]:  both operands of the stage are in place = one arrival per unpack
+  //            warp of the group (4) + the X warp's expect_tx arrival + the X
+  //            tile's bytes
+  // empty[st]: the issuer's instructions on the stage have completed
+  const uint32_t full0 = bars;
+  const uint32_t empty0 = full0 + 8 * kStages;
+  const uint32_t wfull0 = empty0 + 8 * kStages;         // word box landed (TMA bytes)
+  const uint32_t wempty0 = wfull0 + 8 * kWordAhead;     // word box read by the group's 4 warps
+  const uint32_t accum_bar = wempty0 + 8 * kWordAhead;  // both issuers committed their last block
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(
-      sm + tiles_bytes + kWordRing + 8 * (3 * kStages + 2 * kWordAhead + 1));
+      sm + tiles_bytes + kWordRing + 8 * (2 * kStages + 2 * kWordAhead + 1));
   __shared__ unsigned s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // tensor memory: two accumulators D[128 lanes][tokens] fp32 (one per MMA
+  // issuer), then kStages A tiles of 128 lanes x 32 columns (64 halves per row)
+  const uint32_t tmem_cols = p.tokens_padded <= 64 ? 256u : 512u;
+  const uint32_t a_col0 = 2u * (uint32_t)p.tokens_padded;
   const int n0 = blockIdx.x * kTileN;
   // K blocks of this CTA: split index blockIdx.y of p.ksplit
   const int nkb_total = p.K / kBlockK;
@@ -218,15 +253,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
 
   if (tid == 0) {
     for (int s = 0; s < kStages; s++) {
-      mbar_init(full0 + 8 * s, kProducerThreads / 2);
+      mbar_init(full0 + 8 * s, kProducerThreads / 64 + 1);
       mbar_init(empty0 + 8 * s, 1);
-      mbar_init(xfull0 + 8 * s, 1);
     }
     for (int s = 0; s < kWordAhead; s++) {
       mbar_init(wfull0 + 8 * s, 1);
-      mbar_init(wempty0 + 8 * s, kProducerThreads / 2);
+      mbar_init(wempty0 + 8 * s, kProducerThreads / 64);
     }
-    mbar_init(accum_bar, 1);
+    mbar_init(accum_bar, 2);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (FMT == kFmtQ3) {
@@ -238,10 +272,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     for (int i = tid; i < 16 * 32; i += kThreads) g_pair_lut[i] = __float_as_uint(p.lut16[i >> 5]);
   }
   if (warp == 8) {
-    // 128 columns of tensor memory: accumulator D[128 lanes][tokens <= 128] fp32
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"(128)
+                 "r"(tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -261,13 +294,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     const int grp = tid >> 7;       // blocks grp, grp + 2, ...
     const unsigned char* lut = reinterpret_cast<const unsigned char*>(g_pair_lut);
     const uint32_t lane4 = (uint32_t)lane * 4u;
-    const uint32_t a_row = a_tiles + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);
-    const uint32_t swz = (uint32_t)(row & 7);
+    // this warp's 32 lanes of tensor memory (lane = A row), first A column
+    const uint32_t a_lane = tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + a_col0;
     // word box: [6 rows][128 columns] words, then 128 scales, then 128 zeros
     const uint32_t my_words = word_ring + (uint32_t)(row * 4);
     const uint32_t my_param = word_ring + 6 * 512 + (uint32_t)(row * 2);
 
-    uint32_t a_stage = (uint32_t)grp % kStages, a_parity = 1;  // parity meaning "stage released"
+    // the group's m-th block uses stage grp + 2 * (m & 1) for the (m >> 1)-th time
+    uint32_t a_stage = (uint32_t)grp, a_use = 0;
     uint32_t w_slot = (uint32_t)grp, w_parity = 0;
     if constexpr (FMT == kFmtQ3) {
       for (int i = grp; i < nloc; i += 2) {
@@ -314,21 +348,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
         }
         // the ring slot is released only now: the lookups above consumed the words,
         // so the loads have certainly returned
-        mbar_arrive(wempty0 + 8 * w_slot);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(wempty0 + 8 * w_slot);
         w_slot += 2;
         if (w_slot >= kWordAhead) { w_slot -= kWordAhead; w_parity ^= 1u; }
         // the A tile of this stage must have been released by the tensor core
-        if (!mbar_wait(empty0 + 8 * a_stage, a_parity, ok)) ok = false;
-        const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
-  #pragma unroll
-        for (int c = 0; c < 8; c++)
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + (((uint32_t)c ^ swz) * 16)),
-                       "r"(o[4 * c]), "r"(o[4 * c + 1]), "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
-                       : "memory");
-        fence_async_smem();
-        mbar_arrive(full0 + 8 * a_stage);
+        if (a_use != 0 && !mbar_wait(empty0 + 8 * a_stage, (a_use - 1u) & 1u, ok)) ok = false;
+        tc_fence_after();  // orders the stores after the tensor core's reads of the stage
+        tmem_store_32(a_lane + a_stage * (uint32_t)kAColumns, o);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full0 + 8 * a_stage);
         a_stage += 2;
-        if (a_stage >= kStages) { a_stage -= kStages; a_parity ^= 1u; }
+        if (a_stage >= kStages) { a_stage -= kStages; a_use++; }
       }
     } else {
       // NF4: the thread's 64 codes of a block are 32 consecutive bytes of its row;
@@ -372,39 +405,46 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
                                                   : __floats2half2_rn(f_hi, f_lo));
           }
         }
-        mbar_arrive(wempty0 + 8 * w_slot);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(wempty0 + 8 * w_slot);
         w_slot += 2;
         if (w_slot >= kWordAhead) { w_slot -= kWordAhead; w_parity ^= 1u; }
-        if (!mbar_wait(empty0 + 8 * a_stage, a_parity, ok)) ok = false;
-        const uint32_t a_dst = a_row + a_stage * (uint32_t)kATile;
-#pragma unroll
-        for (int c = 0; c < 8; c++)
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + (((uint32_t)c ^ swz) * 16)),
-                       "r"(o[4 * c]), "r"(o[4 * c + 1]), "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
-                       : "memory");
-        fence_async_smem();
-        mbar_arrive(full0 + 8 * a_stage);
+        if (a_use != 0 && !mbar_wait(empty0 + 8 * a_stage, (a_use - 1u) & 1u, ok)) ok = false;
+        tc_fence_after();  // orders the stores after the tensor core's reads of the stage
+        tmem_store_32(a_lane + a_stage * (uint32_t)kAColumns, o);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full0 + 8 * a_stage);
         a_stage += 2;
-        if (a_stage >= kStages) { a_stage -= kStages; a_parity ^= 1u; }
+        if (a_stage >= kStages) { a_stage -= kStages; a_use++; }
       }
     }
-  } else if (warp == 8 && lane == 0) {
-    // ------------------------------ MMA issuer ------------------------------
+  } else if ((warp == 8 || warp == 11) && lane == 0) {
+    // ------------------------------ MMA issuers ------------------------------
+    // Issuer j takes blocks j, j + 2, ... (the blocks of unpack group j) and
+    // accumulates into its own tensor-memory columns, so that one issuer's
+    // barrier polls overlap the other's instructions; the epilogue adds the two.
     // instruction descriptor: D fp32, A/B fp16, both K-major, N = tokens_padded, M = 128
     const uint32_t idesc = (1u << 4) | ((uint32_t)(p.tokens_padded >> 3) << 17) |
                            ((uint32_t)(kTileN >> 4) << 24);
-    uint32_t st = 0, parity = 0;
-    for (int i = 0; i < nloc; i++) {
-      if (!mbar_wait(xfull0 + 8 * st, parity, ok)) ok = false;
-      if (!mbar_wait(full0 + 8 * st, parity, ok)) ok = false;
+    const int j = warp == 8 ? 0 : 1;
+    const uint32_t acc = tmem_d + (uint32_t)(j * p.tokens_padded);
+    uint32_t st = (uint32_t)j, use = 0;
+    uint32_t accumulate = 0;
+    for (int i = j; i < nloc; i += 2) {
+      if (!mbar_wait(full0 + 8 * st, use & 1u, ok)) ok = false;
       tc_fence_after();
-      const uint64_t adesc = smem_desc(a_tiles + st * kATile);
+      const uint32_t a_tmem = tmem_d + a_col0 + st * (uint32_t)kAColumns;
       const uint64_t bdesc = smem_desc(b_tiles + st * kBTile);
 #pragma unroll
-      for (int k = 0; k < kBlockK / 16; k++)
-        umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+      for (int k = 0; k < kBlockK / 16; k++) {
+        umma_f16_ts(acc, a_tmem + 8 * k, bdesc + 2 * k, idesc, accumulate);
+        accumulate = 1u;
+      }
       umma_commit(empty0 + 8 * st);
-      if (++st == kStages) { st = 0; parity ^= 1u; }
+      st += 2;
+      if (st >= kStages) { st -= kStages; use++; }
     }
     umma_commit(accum_bar);
   } else if (warp == 9 && lane == 0) {
@@ -426,12 +466,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     }
   } else if (warp == 10 && lane == 0) {
     // ------------------------------ X TMA ------------------------------
-    uint32_t st = 0, parity = 1;
+    uint32_t st = 0, use = 0;
     for (int i = 0; i < nloc; i++) {
-      if (!mbar_wait(empty0 + 8 * st, parity, ok)) ok = false;
-      mbar_expect_tx(xfull0 + 8 * st, (uint32_t)kBTile);
-      tma_load_2d(b_tiles + st * (uint32_t)kBTile, &map_x, (kb0 + i) * kBlockK, 0, xfull0 + 8 * st);
-      if (++st == kStages) { st = 0; parity ^= 1u; }
+      if (use != 0 && !mbar_wait(empty0 + 8 * st, (use - 1u) & 1u, ok)) ok = false;
+      const uint32_t bar = full0 + 8 * st;
+      mbar_expect_tx(bar, (uint32_t)kBTile);
+      tma_load_2d(b_tiles + st * (uint32_t)kBTile, &map_x, (kb0 + i) * kBlockK, 0, bar);
+      if (++st == kStages) { st = 0; use++; }
     }
   }
 
@@ -451,7 +492,23 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
             "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
             "=r"(r[14]), "=r"(r[15])
           : "r"(taddr + (uint32_t)j0));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (nloc > 1) {
+        // second issuer's partial sums (its columns are untouched when the CTA has one block)
+        uint32_t q[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]),
+              "=r"(q[7]), "=r"(q[8]), "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]),
+              "=r"(q[14]), "=r"(q[15])
+            : "r"(taddr + (uint32_t)(p.tokens_padded + j0)));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+      } else {
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
       if (p.ksplit == 1) {
 #pragma unroll
         for (int j = 0; j < 16; j++)
@@ -472,7 +529,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
   if (p.ksplit > 1) __threadfence();
   __syncthreads();
   if (warp == 8) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(128)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d),
+                 "r"(tmem_cols)
                  : "memory");
   }
   if (p.ksplit > 1) {
