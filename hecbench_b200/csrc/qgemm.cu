@@ -55,8 +55,9 @@
 namespace hq {
 namespace {
 
-constexpr int kStages = 4;                  // two per pipeline (unpack group + MMA issuer)
-constexpr int kWordAhead = 6;               // packed-word blocks in flight (shared-memory ring)
+constexpr int kStages = 4;                  // A tiles in tensor memory, two per pipeline
+constexpr int kXStages = 8;                 // X tiles in shared memory, four per pipeline
+constexpr int kWordAhead = 8;               // packed-word blocks in flight (shared-memory ring)
 constexpr int kBlockK = 64;                 // halves per smem row (128 bytes)
 constexpr int kTileN = 128;                 // output features per CTA (UMMA M)
 constexpr int kMaxTokens = 128;             // UMMA N upper bound handled here
@@ -68,13 +69,13 @@ enum { kFmtQ3 = 0, kFmtNf4 = 1 };
 template <int FMT>
 struct WordSlot { static constexpr int kBytes = FMT == kFmtQ3 ? 6 * 512 + 2 * 256 : 128 * 32; };
 constexpr int kProducerThreads = 256;
-constexpr int kThreads = 384;               // 8 unpack warps, MMA warp, two TMA warps, MMA warp
+constexpr int kThreads = 448;               // 8 unpack, MMA, 2 word TMA, MMA, 2 X TMA warps
 constexpr uint32_t kSpinLimit = 1u << 20;   // bounded mbarrier polls
 
 template <int FMT>
 inline size_t qgemm_smem_bytes(int tokens_padded) {
   const size_t need =
-      1024 + (size_t)kStages * (tokens_padded * 128) + kWordAhead * WordSlot<FMT>::kBytes + 512;
+      1024 + (size_t)kXStages * (tokens_padded * 128) + kWordAhead * WordSlot<FMT>::kBytes + 512;
   // The request also sets the number of CTAs per SM to what tensor memory holds:
   // two CTAs of 256 columns up to 64 tokens, one CTA of 512 columns beyond.
   const size_t floor_bytes = tokens_padded <= 64 ? 90 * 1024 : 120 * 1024;
@@ -218,24 +219,27 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
   constexpr int kWordRing = kWordAhead * kWordSlot;
   const int kBTile = p.tokens_padded * 128;
   const uint32_t b_tiles = base;
-  const uint32_t tiles_bytes = (uint32_t)(kStages * kBTile);
+  const uint32_t tiles_bytes = (uint32_t)(kXStages * kBTile);
   const uint32_t word_ring = base + tiles_bytes;  // [kWordAhead][6 rows][128 columns] words
   const uint32_t bars = base + tiles_bytes + kWordRing;
   // barrier slots (8 bytes each)
-  // Pipeline j = unpack group j + MMA issuer j handles blocks j, j + 2, ... in
-  // its own two stages j and j + 2, so every stage barrier has one producer side
-  // and one consumer side that take its phases strictly in order.
-  // full[st]:  both operands of the stage are in place = one arrival per unpack
-  //            warp of the group (4) + the X warp's expect_tx arrival + the X
-  //            tile's bytes
-  // empty[st]: the issuer's instructions on the stage have completed
+  // Pipeline j = unpack group j + MMA issuer j + two TMA warps handles blocks
+  // j, j + 2, ...; its m-th block uses A stage j + 2 * (m & 1) (tensor memory)
+  // and X stage j + 2 * (m & 3) (shared memory), so every barrier has one
+  // producer side and one consumer side that take its phases strictly in order.
+  // full[xs]:   both operands of the block are in place = one arrival per unpack
+  //             warp of the group (4) + the X warp's expect_tx arrival + the X
+  //             tile's bytes
+  // empty[st]:  the issuer's instructions that read A stage st have completed
+  // xempty[xs]: the issuer's instructions that read X stage xs have completed
   const uint32_t full0 = bars;
-  const uint32_t empty0 = full0 + 8 * kStages;
-  const uint32_t wfull0 = empty0 + 8 * kStages;         // word box landed (TMA bytes)
+  const uint32_t empty0 = full0 + 8 * kXStages;
+  const uint32_t xempty0 = empty0 + 8 * kStages;
+  const uint32_t wfull0 = xempty0 + 8 * kXStages;       // word box landed (TMA bytes)
   const uint32_t wempty0 = wfull0 + 8 * kWordAhead;     // word box read by the group's 4 warps
   const uint32_t accum_bar = wempty0 + 8 * kWordAhead;  // both issuers committed their last block
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(
-      sm + tiles_bytes + kWordRing + 8 * (2 * kStages + 2 * kWordAhead + 1));
+      sm + tiles_bytes + kWordRing + 8 * (2 * kXStages + kStages + 2 * kWordAhead + 1));
   __shared__ unsigned s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -252,10 +256,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
   bool ok = true;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; s++) {
+    for (int s = 0; s < kXStages; s++) {
       mbar_init(full0 + 8 * s, kProducerThreads / 64 + 1);
-      mbar_init(empty0 + 8 * s, 1);
+      mbar_init(xempty0 + 8 * s, 1);
     }
+    for (int s = 0; s < kStages; s++) mbar_init(empty0 + 8 * s, 1);
     for (int s = 0; s < kWordAhead; s++) {
       mbar_init(wfull0 + 8 * s, 1);
       mbar_init(wempty0 + 8 * s, kProducerThreads / 64);
@@ -301,7 +306,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     const uint32_t my_param = word_ring + 6 * 512 + (uint32_t)(row * 2);
 
     // the group's m-th block uses stage grp + 2 * (m & 1) for the (m >> 1)-th time
-    uint32_t a_stage = (uint32_t)grp, a_use = 0;
+    uint32_t a_stage = (uint32_t)grp, a_use = 0, x_stage = (uint32_t)grp;
     uint32_t w_slot = (uint32_t)grp, w_parity = 0;
     if constexpr (FMT == kFmtQ3) {
       for (int i = grp; i < nloc; i += 2) {
@@ -359,9 +364,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(full0 + 8 * a_stage);
+        if (lane == 0) mbar_arrive(full0 + 8 * x_stage);
         a_stage += 2;
         if (a_stage >= kStages) { a_stage -= kStages; a_use++; }
+        x_stage += 2;
+        if (x_stage >= kXStages) x_stage -= kXStages;
       }
     } else {
       // NF4: the thread's 64 codes of a block are 32 consecutive bytes of its row;
@@ -415,9 +422,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(full0 + 8 * a_stage);
+        if (lane == 0) mbar_arrive(full0 + 8 * x_stage);
         a_stage += 2;
         if (a_stage >= kStages) { a_stage -= kStages; a_use++; }
+        x_stage += 2;
+        if (x_stage >= kXStages) x_stage -= kXStages;
       }
     }
   } else if ((warp == 8 || warp == 11) && lane == 0) {
@@ -430,49 +439,62 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
                            ((uint32_t)(kTileN >> 4) << 24);
     const int j = warp == 8 ? 0 : 1;
     const uint32_t acc = tmem_d + (uint32_t)(j * p.tokens_padded);
-    uint32_t st = (uint32_t)j, use = 0;
+    uint32_t st = (uint32_t)j, xs = (uint32_t)j, xuse = 0;
     uint32_t accumulate = 0;
     for (int i = j; i < nloc; i += 2) {
-      if (!mbar_wait(full0 + 8 * st, use & 1u, ok)) ok = false;
+      if (!mbar_wait(full0 + 8 * xs, xuse & 1u, ok)) ok = false;
       tc_fence_after();
       const uint32_t a_tmem = tmem_d + a_col0 + st * (uint32_t)kAColumns;
-      const uint64_t bdesc = smem_desc(b_tiles + st * kBTile);
+      const uint64_t bdesc = smem_desc(b_tiles + xs * kBTile);
 #pragma unroll
       for (int k = 0; k < kBlockK / 16; k++) {
         umma_f16_ts(acc, a_tmem + 8 * k, bdesc + 2 * k, idesc, accumulate);
         accumulate = 1u;
       }
       umma_commit(empty0 + 8 * st);
+      umma_commit(xempty0 + 8 * xs);
       st += 2;
-      if (st >= kStages) { st -= kStages; use++; }
+      if (st >= kStages) st -= kStages;
+      xs += 2;
+      if (xs >= kXStages) { xs -= kXStages; xuse++; }
     }
     umma_commit(accum_bar);
-  } else if (warp == 9 && lane == 0) {
+  } else if ((warp == 9 || warp == 10) && lane < 3) {
     // ------------------------------ packed-word TMA ------------------------------
-    uint32_t slot = 0, parity = 1;  // first pass over the ring: slots are free
-    for (int i = 0; i < nloc; i++) {
-      if (!mbar_wait(wempty0 + 8 * slot, parity, ok)) ok = false;
-      const int g = ((kb0 + i) * kBlockK) / p.group_size;
-      const uint32_t dst = word_ring + slot * kWordSlot;
-      mbar_expect_tx(wfull0 + 8 * slot, kWordSlot);
-      if constexpr (FMT == kFmtQ3) {
-        tma_load_2d(dst, &map_w, n0, 6 * (kb0 + i), wfull0 + 8 * slot);
-        tma_load_2d(dst + 6 * 512, &map_s, n0, g, wfull0 + 8 * slot);
-        tma_load_2d(dst + 6 * 512 + 256, &map_z, n0, g, wfull0 + 8 * slot);
-      } else {
-        tma_load_2d(dst, &map_w, 32 * (kb0 + i), n0, wfull0 + 8 * slot);
+    // One warp per pipeline j: lane 0 waits for the slot and posts the byte
+    // count, then lanes 0-2 issue the loads side by side (3-bit: lane 0 the word
+    // box, lanes 1 and 2 the scales and zeros; NF4: lane 0 alone).
+    const int j = warp - 9;
+    uint32_t slot = (uint32_t)j, use = 0;
+    for (int i = j; i < nloc; i += 2) {
+      if (lane == 0) {
+        if (use != 0 && !mbar_wait(wempty0 + 8 * slot, (use - 1u) & 1u, ok)) ok = false;
+        mbar_expect_tx(wfull0 + 8 * slot, kWordSlot);
       }
-      if (++slot == kWordAhead) { slot = 0; parity ^= 1u; }
+      __syncwarp(0x7u);
+      const uint32_t dst = word_ring + slot * kWordSlot;
+      if constexpr (FMT == kFmtQ3) {
+        const int g = ((kb0 + i) * kBlockK) / p.group_size;
+        if (lane == 0) tma_load_2d(dst, &map_w, n0, 6 * (kb0 + i), wfull0 + 8 * slot);
+        else if (lane == 1) tma_load_2d(dst + 6 * 512, &map_s, n0, g, wfull0 + 8 * slot);
+        else tma_load_2d(dst + 6 * 512 + 256, &map_z, n0, g, wfull0 + 8 * slot);
+      } else {
+        if (lane == 0) tma_load_2d(dst, &map_w, 32 * (kb0 + i), n0, wfull0 + 8 * slot);
+      }
+      slot += 2;
+      if (slot >= kWordAhead) { slot -= kWordAhead; use++; }
     }
-  } else if (warp == 10 && lane == 0) {
+  } else if ((warp == 12 || warp == 13) && lane == 0) {
     // ------------------------------ X TMA ------------------------------
-    uint32_t st = 0, use = 0;
-    for (int i = 0; i < nloc; i++) {
-      if (use != 0 && !mbar_wait(empty0 + 8 * st, (use - 1u) & 1u, ok)) ok = false;
-      const uint32_t bar = full0 + 8 * st;
+    const int j = warp - 12;
+    uint32_t xs = (uint32_t)j, use = 0;
+    for (int i = j; i < nloc; i += 2) {
+      if (use != 0 && !mbar_wait(xempty0 + 8 * xs, (use - 1u) & 1u, ok)) ok = false;
+      const uint32_t bar = full0 + 8 * xs;
       mbar_expect_tx(bar, (uint32_t)kBTile);
-      tma_load_2d(b_tiles + st * (uint32_t)kBTile, &map_x, (kb0 + i) * kBlockK, 0, bar);
-      if (++st == kStages) { st = 0; use++; }
+      tma_load_2d(b_tiles + xs * (uint32_t)kBTile, &map_x, (kb0 + i) * kBlockK, 0, bar);
+      xs += 2;
+      if (xs >= kXStages) { xs -= kXStages; use++; }
     }
   }
 
