@@ -10,41 +10,49 @@
 //    (even element in the high nibble unless the low-nibble-first flag is
 //    given): the dequantisation rule of hq_nf4_dequant_f16.
 // The description below is written for the 3-bit format; the NF4 form differs
-// only in the box the word warp fetches (128 rows x 32 bytes) and in the
-// unpack arithmetic (one fp32 table lookup and one multiply per code, packed to
-// half2 with round-to-nearest).
+// only in the box the word warps fetch (128 rows x 32 bytes) and in the unpack
+// arithmetic (one fp32 table lookup and one multiply per code, packed to half2
+// with round-to-nearest).
 //
 // The contraction is computed transposed so that the weight dimension fills
 // the 128 rows of a tcgen05.mma tile and the token batch is its N dimension:
-//   D[128 n][Mb] += A[128 n][16 k] * B[16 k][Mb],  A = W^T (K-major), B = X^T (K-major)
-// One CTA owns 128 output features and a range of K blocks of 64 inputs:
-//   warp 9     (one lane) streams the packed words: one TMA box of 6 rows x 128
-//              columns per block into an 8-deep shared-memory ring;
-//   warp 10    (one lane) streams X: one TMA box of 64 inputs x all tokens per
-//              block straight into the stage's B tile in the 128-byte-swizzled
-//              K-major layout (rows beyond the token count are zero-filled by
-//              the TMA unit);
-//   warps 0-7  unpack: thread (row, half) owns one output feature and one
-//              group of 32 inputs of the block; it reads its three packed
-//              words from the ring, turns every 6-bit pair into half2(q0, q1)
-//              with one lookup in a bank-replicated shared table, applies
-//              hfma2 with the group's scale / -zero, and stores its 32 halves
-//              into the stage's A tile in the swizzled K-major layout; then
-//              fence.proxy.async + mbarrier arrive.  These threads have no
-//              asynchronous copies of their own in flight, so the fence only
-//              orders their four stores;
-//   warp 8     (one lane) waits for both tiles of the stage, issues four
-//              tcgen05.mma.cta_group::1.kind::f16 (K = 16 each) with shared
-//              memory descriptors, and commits them to the stage's "empty"
-//              mbarrier; after the last block it commits to the accumulator
-//              barrier;
-//   warps 0-7  epilogue: tcgen05.ld of the warp's 32 TMEM lanes, then either
-//              fp32 -> fp16 and a transposed store into Y, or (K split over
-//              several CTAs) fp32 reductions into a scratch matrix that the
-//              last CTA of the tile converts and re-zeroes.
-// Two CTAs share an SM (about 105 KiB of shared memory and 128 TMEM columns
-// each for up to 64 tokens), so one CTA's epilogue and ramp-up hide behind the
-// other's main loop.  No TMA load uses cluster multicast.
+//   D[128 n][Mb] += A[128 n][16 k] * B[16 k][Mb],  A = W^T, B = X^T (K-major)
+// with A in TENSOR MEMORY (the unpack warps write it there with tcgen05.st, so
+// the dequantised weights never pass through shared memory) and B = X in shared
+// memory.  One CTA (448 threads) owns 128 output features and a range of K
+// blocks of 64 inputs, and runs two independent pipelines j = 0, 1 over the
+// blocks j, j + 2, ...:
+//   warps 9, 10  packed-word TMA of pipeline 0 / 1: per block lane 0 waits for
+//              the ring slot and posts the byte count, lanes 0-2 issue the
+//              boxes (6 rows x 128 columns of words, 128 scales, 128 zeros)
+//              into the pipeline's slots of an 8-deep shared-memory ring;
+//   warps 12, 13 X TMA of pipeline 0 / 1 (one lane): one box of 64 inputs x all
+//              tokens per block into the pipeline's four X stages, in the
+//              128-byte-swizzled K-major layout (rows beyond the token count
+//              are zero-filled by the TMA unit);
+//   warps 0-3, 4-7  unpack group of pipeline 0 / 1: thread = one output feature
+//              = one tensor-memory lane; it reads its six packed words from the
+//              ring, turns every 6-bit pair into half2(q0, q1) with one lookup
+//              in a bank-replicated shared table, applies hfma2 with the
+//              group's scale / -zero, and writes its 64 halves as 32 columns of
+//              its lane of the pipeline's A stage (tcgen05.st 32x32b.x32), then
+//              tcgen05.wait::st, tcgen05.fence::before_thread_sync and one
+//              mbarrier arrival per warp;
+//   warps 8, 11  MMA issuer of pipeline 0 / 1 (one lane): waits for the block's
+//              "full" barrier (four unpack-warp arrivals + the X bytes), issues
+//              four tcgen05.mma.cta_group::1.kind::f16 (K = 16 each, A from
+//              tensor memory, B through a shared-memory descriptor) into the
+//              pipeline's OWN accumulator columns, and commits them to the
+//              "empty" barriers of the A stage and of the X stage;
+//   warps 0-7  epilogue: tcgen05.ld of both accumulators for the warp's 32
+//              lanes, their sum, then either fp32 -> fp16 and a transposed
+//              store into Y, or (K split over several CTAs) fp32 reductions
+//              into a scratch matrix that the last CTA of the tile converts
+//              and re-zeroes.
+// Tensor memory per CTA (up to 64 tokens): 2 x 64 accumulator columns + 4 A
+// stages x 32 columns = 256 of the SM's 512 columns, so two CTAs share an SM
+// (the shared-memory request is padded to keep it at two); beyond 64 tokens a
+// CTA takes all 512 columns.  No TMA load uses cluster multicast.
 // Every mbarrier wait is bounded: when the limit is hit the thread records a
 // status code, stops waiting and carries on, so the kernel always terminates
 // and frees its tensor memory; the host reads the status word.
