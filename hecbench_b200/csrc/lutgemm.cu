@@ -9,21 +9,25 @@
 //
 // Like the reference (mv_fp16.h:133-227) the +-sums over 8 inputs are looked up
 // by bit-plane byte in a table built from x, but:
-//  * a CTA of 512 threads owns a K tile of 128 inputs (4 packed rows) and a
-//    range of columns; lane (c,j) of a warp handles byte j of the words of
-//    columns 4c..4c+3 and reads replica c of table (row, j): the 16 tables are
-//    stored with one 256-byte line per (row pair, byte value) holding
+//  * a CTA of 512 threads owns a K tile of 128 inputs (4 packed rows; 64 inputs
+//    with two CTAs per SM for alpha groups of 192, 320, ... inputs) and a range
+//    of columns; lane (c,j) of a warp handles byte j of the words of columns
+//    4c..4c+3 and reads replica c of table (row, j): the 16 tables are stored
+//    with one 256-byte line per (row pair, byte value) holding
 //    [row parity][replica c][byte-lane j], so every lane of a warp reads its
-//    own bank - no lookup ever conflicts - and, the table block being aligned
-//    to 64 KiB in the shared window, the address of a lookup is ONE
-//    byte-permute of the packed word and a per-lane constant (the row is an
-//    immediate offset);
+//    own bank - no lookup ever conflicts - and, the table block sitting at a
+//    FIXED address of the shared window, the address of a lookup is ONE
+//    byte-permute of the packed word and a per-lane constant, plus an
+//    immediate offset that selects the row;
+//  * packed words, alphas and bias travel through a per-quad cp.async ring whose
+//    slots are an odd multiple of 16 bytes, so the eight quads of a warp fill
+//    and read their slots in eight different bank groups;
 //  * table entries and all sums are fp32 (the reference uses fp16 throughout
 //    and half2 atomics on the output);
 //  * the four lanes of a column quad are combined with two shuffles, each CTA
-//    adds its tile's partial sums to an fp32 scratch row with one coalesced
-//    reduction per 32 columns, and the last CTA to finish converts the scratch
-//    to fp16, stores the output and re-zeroes the scratch.
+//    adds its tile's partial sums to an fp32 scratch row with one 16-byte
+//    vector reduction per column quad, and the last CTA to finish converts the
+//    scratch to fp16, stores the output and re-zeroes the scratch.
 #include <mutex>
 
 #include "hq_common.cuh"
@@ -54,7 +58,10 @@ struct Layout {
   static constexpr int kWords = TR * NB;  // 16-byte word vectors per column step
   // bytes of one column step in a quad's ring: packed words, then per alpha
   // group NB alpha vectors and one bias vector of four halves each
-  static constexpr int kStep = (TR * NB * 16 + kGroups * (NB + 1) * 8 + 15) / 16 * 16;
+  // an odd multiple of 16 bytes: the eight quads of a warp then read and fill
+  // their slots in eight different 16-byte bank groups
+  static constexpr int kStepRaw = (TR * NB * 16 + kGroups * (NB + 1) * 8 + 15) / 16 * 16;
+  static constexpr int kStep = (kStepRaw / 16) % 2 == 0 ? kStepRaw + 16 : kStepRaw;
   static constexpr int kBuf = kQuads * kStep;
   static constexpr int kCompactWords = TR * 256 * 4;  // [row][byte value][j]
   static constexpr int kBuildBytes = kCompactWords * 4 + TR * 32 * 4 + 64;
@@ -76,6 +83,11 @@ constexpr int pick_bufs() {
 
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_v4_f32(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
 }
 template <int IMM>
 __device__ __forceinline__ float lds_f32_imm(uint32_t addr) {
@@ -322,8 +334,9 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
       acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
       acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 2);
     }
-    const float mine = j == 0 ? acc[0] : j == 1 ? acc[1] : j == 2 ? acc[2] : acc[3];
-    if (active) red_add_f32(ws + m + j, mine);  // lane (cq,j) -> column of this step + lane
+    // every lane of the quad now holds the four column sums: lane j == 0 adds
+    // them to the scratch row with one 16-byte reduction
+    if (active && j == 0) red_add_v4_f32(ws + m, acc[0], acc[1], acc[2], acc[3]);
   }
   cp_async_wait<0>();
 
