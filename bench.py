@@ -586,16 +586,54 @@ def main():
     if io is not None:
         hin, hout = io
         with torch.cuda.stream(stream):
-            def e2e_step():
+            # The R launches of a pass are independent requests (own input, weights
+            # and output), so they run as a few parallel chains: one request's copies
+            # overlap another's kernel, as in a serving loop with requests in flight.
+            chains = [torch.cuda.Stream() for _ in range(min(4, R))] if world == 1 else []
+
+            def e2e_one(i):
+                wl.x[i].copy_(hin[i], non_blocking=True)
+                layer(i)
+                if peer is not None:  # this rank's slice of the gathered vector
+                    c = wl.case
+                    hout[i].copy_(peer.slot(i)[rank * c["N"]:(rank + 1) * c["N"]],
+                                  non_blocking=True)
+                else:
+                    hout[i].copy_(wl.out[i], non_blocking=True)
+
+            def e2e_pass():
+                if not chains:
+                    for i in range(R):
+                        e2e_one(i)
+                    return
+                for cs in chains:
+                    cs.wait_stream(stream)
                 for i in range(R):
-                    wl.x[i].copy_(hin[i], non_blocking=True)
-                    layer(i)
-                    if peer is not None:  # this rank's slice of the gathered vector
-                        c = wl.case
-                        hout[i].copy_(peer.slot(i)[rank * c["N"]:(rank + 1) * c["N"]],
-                                      non_blocking=True)
-                    else:
-                        hout[i].copy_(wl.out[i], non_blocking=True)
+                    with torch.cuda.stream(chains[i % len(chains)]):
+                        e2e_one(i)
+                for cs in chains:
+                    stream.wait_stream(cs)
+            # the whole pass (pinned-host -> device copy, kernel, device -> pinned-host
+            # copy, per launch) as one CUDA graph, like the device-only leg
+            e2e_graph = None
+            e2e_pass()
+            stream.synchronize()
+            if graph is not None:
+                try:
+                    e2e_graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(e2e_graph, stream=stream):
+                        e2e_pass()
+                except Exception as exc:
+                    print(f"[bench] e2e graph capture failed ({exc}); running eagerly",
+                          file=sys.stderr)
+                    e2e_graph = None
+                    torch.cuda.synchronize()
+
+            def e2e_step():
+                if e2e_graph is not None:
+                    e2e_graph.replay()
+                else:
+                    e2e_pass()
             for _ in range(3):
                 e2e_step()
             barrier()
@@ -613,7 +651,9 @@ def main():
         e2e = {"value": total_bytes / (ems * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hin)),
                "d2h_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hout)),
-               "us_per_call": ems * 1e3 / launches}
+               "us_per_call": ems * 1e3 / launches,
+               "launch": ("cuda graph of R x (H2D copy, kernel, D2H copy)" if e2e_graph is not None
+                          else "eager") + (f", {len(chains)} requests in flight" if chains else "")}
 
     if peer is not None and int(peer.status.item()) != 0:
         raise SystemExit("a bounded gather wait ran out")
