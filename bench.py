@@ -145,6 +145,10 @@ def _host_case(name: str, seed: int):
     raise SystemExit(f"unknown workload {name}")
 
 
+# Weights are resident model state: the NF4 GEMV may fetch them while the preceding
+# launch of the stream is finishing (HQ_BENCH_NO_PDL=1 turns that off).
+PDL = os.environ.get("HQ_BENCH_NO_PDL") != "1"
+
 WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "bnb_quantize", "lutgemm",
              "aqlm_1x16", "aqlm_2x8", "qgemm_q3", "qgemm_nf4"]
 DTYPE = {"nf4_gemv": "f16", "nf4_dequant": "f16", "q3_gemv_f32": "f32", "q3_gemv_f16": "f16",
@@ -225,7 +229,7 @@ class DeviceWorkload:
         hq, c, n = self.hq, self.case, self.name
         if n == "nf4_gemv":
             hq.gemv_nf4(self.x[i], self.B[i], self.absmax[i], self.lut, c["N"], c["K"], c["bs"], 0,
-                        self.out[i])
+                        self.out[i], weights_resident=PDL)
         elif n == "nf4_dequant":
             hq.dequantize_nf4(self.B[i], self.absmax[i], self.lut, c["N"] * c["K"], c["bs"], 0,
                               self.W)
@@ -492,7 +496,7 @@ def main():
                 # ordinary GEMV into this rank's slice of its own gathered vector,
                 # then one small kernel: peer stores over NVLink, flags, bounded wait
                 hq.gemv_nf4(wl.x[i], wl.B[i], wl.absmax[i], wl.lut, c["N"], c["K"], c["bs"], 0,
-                            peer.local_slice(i))
+                            peer.local_slice(i), weights_resident=PDL)
                 peer.publish(i)
             return
         wl.launch(i)
@@ -679,7 +683,10 @@ def main():
                        "resident_weight_bytes_per_gpu": wl.bytes * R,
                        "l2": "inputs larger than L2 (replicas rotate, R x bytes >> 126 MB)",
                        "algorithmic_bytes_per_launch": wl.bytes,
-                       "launch": "cuda graph of R launches" if graph is not None else "eager",
+                       "launch": ("cuda graph of R launches" if graph is not None else "eager") +
+                                 ("; weights flagged resident: a launch fetches its weights while "
+                                  "the previous launch's tail drains (programmatic dependent launch)"
+                                  if PDL and args.workload == "nf4_gemv" else ""),
                        "parallelism": ("single GPU" if world == 1 else
                                        f"output features sharded over {world} GPUs, " +
                                        (f"gather '{args.gather}': slices stored into every GPU's "

@@ -12,6 +12,7 @@ GPU, but every compute call needs the built library and CUDA tensors.
 from ._lib import HqError, lib_path, load_library  # noqa: F401
 from .api import (  # noqa: F401
     NF4_HIGH_NIBBLE_FIRST,
+    NF4_WEIGHTS_RESIDENT,
     NF4_LOW_NIBBLE_FIRST,
     code1x16_matvec,
     code2x8_matvec,
@@ -32,5 +33,5 @@ __all__ = [
     "vecquant3matmul", "vecquant3matmul_faster", "vecquant3_dequant",
     "kQuantize", "dequantize_nf4", "gemv_nf4",
     "nQWeight_fp16", "matmul", "qgemm_q3", "qgemm_nf4", "code1x16_matvec", "code2x8_matvec",
-    "NF4_HIGH_NIBBLE_FIRST", "NF4_LOW_NIBBLE_FIRST",
+    "NF4_HIGH_NIBBLE_FIRST", "NF4_LOW_NIBBLE_FIRST", "NF4_WEIGHTS_RESIDENT",
 ]

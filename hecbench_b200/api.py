@@ -17,6 +17,7 @@ import torch
 from ._lib import check, load_library
 
 NF4_HIGH_NIBBLE_FIRST = 0
+NF4_WEIGHTS_RESIDENT = 2
 NF4_LOW_NIBBLE_FIRST = 1
 
 
@@ -117,16 +118,19 @@ def dequantize_nf4(B, absmax, lut16, n: int, blocksize: int = 64,
 
 def gemv_nf4(A, B, absmax, lut16, N: int, K: int, blocksize: int = 64,
              nibble_order: int = NF4_HIGH_NIBBLE_FIRST,
-             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None, weights_resident: bool = False) -> torch.Tensor:
     """NF4 4-bit GEMV (no counterpart in the reference tree):
-    out[n] = half(sum_k A[k] * lut16[code[n][k]] * absmax[(n*K+k)//blocksize])."""
+    out[n] = half(sum_k A[k] * lut16[code[n][k]] * absmax[(n*K+k)//blocksize]).
+    weights_resident: B, absmax and lut16 are not written by earlier work in the
+    stream, so the kernel may fetch them while the preceding kernel is finishing."""
     lib = load_library()
     if out is None:
         out = torch.empty(N, dtype=torch.float16, device=B.device)
     args = (
         _dev(A, torch.float16, "A"), _dev(B, torch.uint8, "B"),
         _dev(absmax, torch.float32, "absmax"), _dev(lut16, torch.float32, "lut16"),
-        _dev(out, torch.float16, "out"), N, K, blocksize, nibble_order)
+        _dev(out, torch.float16, "out"), N, K, blocksize,
+        nibble_order | (NF4_WEIGHTS_RESIDENT if weights_resident else 0))
     with torch.cuda.device(B.device):
         check("hq_nf4_gemv_f16", lib.hq_nf4_gemv_f16(*args, _stream()))
     return out

@@ -135,6 +135,7 @@ struct GemvParams {
   // flag has reached this rank's launch count, i.e. until the previous fused
   // gather - which produced the input of this layer - has landed everywhere
   const uint32_t* wait_flags;
+  int early_fetch;  // weights may be fetched before the preceding kernel in the stream has finished
   int* status;
 };
 
@@ -160,6 +161,11 @@ nf4_gemv_kernel(const GemvParams p) {
   // [pad up to shared address kLutImm] table rows (256 x 256 B: lane copies |
   // partial-sum slot) | [kStages][C][1024] uint4 | [kStages][C][1024] float
   if (smem_u32(dsm_raw) > (uint32_t)kLutImm) return;  // never on sm_100 (1 KiB reserved)
+  // Programmatic dependent launch: let the next kernel of the stream start its
+  // own prologue as soon as this grid is resident, and do not touch global
+  // memory that earlier work may still be writing before the wait below.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!p.early_fetch) asm volatile("griddepcontrol.wait;" ::: "memory");
   unsigned char* dsm = dsm_raw + (kLutImm - smem_u32(dsm_raw));
   const int S = ST > 0 ? ST : p.S;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -230,6 +236,9 @@ nf4_gemv_kernel(const GemvParams p) {
     row[entry & 1] = u4;
     row[(entry & 1) ^ 1] = u4;
   }
+  // the input vector (and, without early_fetch, everything) is read only after
+  // the preceding kernel has completed
+  if (p.early_fetch) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (p.wait_flags != nullptr) {
     if (tid < p.world) {
       const unsigned want = *reinterpret_cast<volatile unsigned*>(p.sync_words + 1);
@@ -559,6 +568,7 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   prm.gather_offset = gather_offset;
   prm.wait_flags = wait_flags;
   prm.status = status;
+  prm.early_fetch = (flags & HQ_NF4_WEIGHTS_RESIDENT) ? 1 : 0;
   cudaStream_t st = (cudaStream_t)stream;
 #define HQ_NF4_LAUNCH(CC, SS, AL)                                                               \
   {                                                                                             \
@@ -566,7 +576,18 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
     cudaError_t e =                                                                             \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
     if (e != cudaSuccess) return cuda_status(e);                                                \
-    kern<<<grid, kGemvThreads, smem, st>>>(prm);                                                \
+    cudaLaunchConfig_t cfg = {};                                                                \
+    cfg.gridDim = dim3(grid);                                                                   \
+    cfg.blockDim = dim3(kGemvThreads);                                                          \
+    cfg.dynamicSmemBytes = smem;                                                                \
+    cfg.stream = st;                                                                            \
+    cudaLaunchAttribute attr[1];                                                                \
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                            \
+    attr[0].val.programmaticStreamSerializationAllowed = 1;                                     \
+    cfg.attrs = attr;                                                                           \
+    cfg.numAttrs = 1;                                                                           \
+    e = cudaLaunchKernelEx(&cfg, kern, prm);                                                    \
+    if (e != cudaSuccess) return cuda_status(e);                                                \
   }
   if (C == 1 && S == 4 && aligned) HQ_NF4_LAUNCH(1, 4, true)
   else if (C == 1 && S == 8 && aligned) HQ_NF4_LAUNCH(1, 8, true)

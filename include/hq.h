@@ -83,6 +83,11 @@ int hq_bnb_quantize_u8(const float* code256, const float* A, uint8_t* out, size_
 /* flags for the NF4 entry points */
 #define HQ_NF4_HIGH_NIBBLE_FIRST 0 /* even element = high nibble (default) */
 #define HQ_NF4_LOW_NIBBLE_FIRST 1  /* even element = low nibble */
+/* hq_nf4_gemv_f16 only: B, absmax and lut16 are not written by earlier work in
+ * the stream (resident model weights), so the kernel may fetch them while the
+ * preceding kernel of the stream is still finishing (programmatic dependent
+ * launch); the input vector is always read after that kernel has completed. */
+#define HQ_NF4_WEIGHTS_RESIDENT 2
 
 /* NF4 blockwise dequantize (no counterpart in the reference tree):
  * out[e] = half_rn(lut16[code_e] * absmax[e / blocksize]), n elements, two

@@ -216,6 +216,52 @@ def test_nf4_gemv_and_dequant(hq, oracle, dev, N, K, bs, order):
     assert oracle.rel_err(_np(y).astype(np.float64), ref) < TOL_F16
 
 
+def test_nf4_gemv_chain_with_resident_weights(hq, dev):
+    """A chain of square layers in which every launch reads the previous
+    launch's output: with the weights flagged resident a launch may start
+    before its predecessor has finished, but must read its input only
+    afterwards.  Eager and graph-replayed chains must equal the plain chain
+    bit for bit."""
+    import torch
+    N = K = 4096
+    layers = 6
+    _, B0, absmax, lut = synth.nf4_case(N, K, 64, seed=9)
+    x0 = torch.from_numpy((np.random.default_rng(3).standard_normal(K) * 4).astype(np.float16)).to(dev)
+    Bs = [to_dev(np.roll(B0, 17 * i), dev) for i in range(layers)]
+    dabs, dlut = to_dev(absmax * 0.2, dev), to_dev(lut, dev)
+
+    def chain(flag):
+        bufs = [torch.empty(N, dtype=torch.float16, device=dev) for _ in range(layers)]
+        x = x0
+        for i in range(layers):
+            hq.gemv_nf4(x, Bs[i], dabs, dlut, N, K, 64, 0, bufs[i], weights_resident=flag)
+            x = bufs[i]
+        return bufs
+
+    plain = [b.clone() for b in chain(False)]
+    torch.cuda.synchronize()
+    assert float(plain[-1].float().abs().max()) > 0
+    for _ in range(5):
+        got = chain(True)
+        torch.cuda.synchronize()
+        for a, b in zip(plain, got):
+            assert torch.equal(a, b)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        chain(True)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            got = chain(True)
+        for _ in range(5):
+            for b in got:
+                b.zero_()
+            g.replay()
+            stream.synchronize()
+            for a, b in zip(plain, got):
+                assert torch.equal(a, b)
+
+
 def test_nf4_dequant_then_dense_matches_gemv(hq, oracle, dev):
     """Size-independent property at the full configuration: GEMV equals the
     dense product with the bit-exact dequantised weights."""
