@@ -28,6 +28,34 @@ inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Programmatic dependent launch.  A kernel calls pdl_launch_dependents() first
+// thing, so that the next kernel of the stream may become resident while this
+// grid is still running, and pdl_wait() before it touches global memory that
+// earlier work in the stream may still be writing (pdl_wait returns once every
+// preceding kernel has completed and its writes are visible; it returns at once
+// in a kernel that was launched the ordinary way).  launch_pdl() launches with
+// the attribute that allows the early start.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // Streaming 128-bit load that does not allocate in L1: packed weights are
 // read exactly once.
 __device__ __forceinline__ uint4 ldg_stream_u4(const void* p) {

@@ -43,6 +43,10 @@ __global__ void __launch_bounds__(kThreads)
 q3_gemv_kernel(const void* __restrict__ vec_, const int32_t* __restrict__ mat,
                float* __restrict__ mul, const float* __restrict__ scales,
                const float* __restrict__ zeros, int groups, int width, int groups_per_cta) {
+  // the next kernel of the stream may become resident while this grid runs;
+  // nothing is read or written before every earlier kernel has completed
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -280,9 +284,8 @@ int q3_gemv_launch(const void* vec, const int32_t* mat, float* mul, const float*
     if (e != cudaSuccess) return cuda_status(e);
   }
   dim3 grid(colblocks, ksplit);
-  kern<<<grid, kThreads, smem, (cudaStream_t)stream>>>(vec, mat, mul, scales, zeros, groups,
-                                                       width, gpc);
-  return launch_status();
+  return cuda_status(launch_pdl(kern, grid, dim3(kThreads), smem, (cudaStream_t)stream, vec, mat,
+                                mul, scales, zeros, groups, width, gpc));
 }
 
 template <bool F16OUT>
