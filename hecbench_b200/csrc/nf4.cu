@@ -429,6 +429,12 @@ gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
                       uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
                       int* status) {
   const int tid = threadIdx.x;
+  // Programmatic dependent launch: this CTA may become resident while the kernel
+  // that produces the slice is still draining, and the next kernel of the stream
+  // may start its own prologue while this one waits for the other ranks; the
+  // slice is read only after the producing kernel has completed.
+  pdl_launch_dependents();
+  pdl_wait();
   const __half* mine = peer_out[rank] + offset;
   const bool vec_ok = ((offset | (long long)n_slice) & 7) == 0;
   for (int r = 0; r < world; r++) {
@@ -478,10 +484,9 @@ int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
   using namespace hq;
   if (!peer_out_half || !peer_flags || !sync_words) return HQ_ERR_NULL_POINTER;
   if (world < 1 || world > 32 || rank < 0 || rank >= world || n_slice <= 0) return HQ_ERR_BAD_SHAPE;
-  gather_publish_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(
-      reinterpret_cast<__half* const*>(peer_out_half), offset, n_slice, peer_flags, sync_words,
-      world, rank, status);
-  return launch_status();
+  return cuda_status(launch_pdl(gather_publish_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream,
+                                reinterpret_cast<__half* const*>(peer_out_half), offset, n_slice,
+                                peer_flags, sync_words, world, rank, status));
 }
 
 int hq_gather_wait(const uint32_t* local_flags, const unsigned* sync_words, int world, int* status,
