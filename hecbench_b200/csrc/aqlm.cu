@@ -21,7 +21,12 @@ namespace hq {
 namespace {
 
 constexpr int kWarps1x16 = 8;
-constexpr int kRowsPerWarp = 4;
+// Rows per warp: 4 when that still gives every SM two CTAs, else 2 (a 4096-row
+// layer is latency-bound: more resident warps pay more than the per-CTA staging
+// of the inputs costs: 12.5 -> 11.0 us for 1x16, 11.5 -> 8.0 us for 2x8).
+inline int rows_per_warp_for(int prob_m, int warps) {
+  return prob_m / (warps * 4) >= 2 * sm_count() ? 4 : 2;
+}
 constexpr int kPad = 9;  // input slots per 8 groups (one pad slot: conflict-free 128-bit reads)
 
 __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
@@ -47,7 +52,8 @@ template <int VPL>
 __global__ void __launch_bounds__(kWarps1x16 * 32)
 aqlm_1x16_kernel(const uint4* __restrict__ codes, const uint4* __restrict__ x,
                  __half* __restrict__ out, const uint4* __restrict__ codebook, int prob_m,
-                 int prob_k, int4 cb_sizes, int cb_stride, const __half* __restrict__ scales) {
+                 int prob_k, int4 cb_sizes, int cb_stride, const __half* __restrict__ scales,
+                 int rows_per_warp) {
   extern __shared__ __align__(16) uint4 sh_x[];  // padded inputs: slot 9*(g/8) + g%8
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int groups = prob_k >> 3;    // 16-byte input groups
@@ -55,8 +61,8 @@ aqlm_1x16_kernel(const uint4* __restrict__ codes, const uint4* __restrict__ x,
   for (int g = tid; g < groups; g += blockDim.x) sh_x[kPad * (g >> 3) + (g & 7)] = x[g];
   __syncthreads();
 
-  const int row_begin = (blockIdx.x * kWarps1x16 + warp) * kRowsPerWarp;
-  for (int rr = 0; rr < kRowsPerWarp; rr++) {
+  const int row_begin = (blockIdx.x * kWarps1x16 + warp) * rows_per_warp;
+  for (int rr = 0; rr < rows_per_warp; rr++) {
     const int m = row_begin + rr;
     if (m >= prob_m) break;
     const uint4* cb = codebook;
@@ -97,12 +103,11 @@ aqlm_1x16_kernel(const uint4* __restrict__ codes, const uint4* __restrict__ x,
 }
 
 constexpr int kWarps2x8 = 8;
-constexpr int kRowsPerWarp2x8 = 4;
 
 __global__ void __launch_bounds__(kWarps2x8 * 32)
 aqlm_2x8_kernel(const uint4* __restrict__ codes, const uint4* __restrict__ x,
                 __half* __restrict__ out, const uint4* __restrict__ codebooks, int prob_m,
-                int prob_k, const __half* __restrict__ scales) {
+                int prob_k, const __half* __restrict__ scales, int rows_per_warp) {
   extern __shared__ __align__(16) uint4 smem4[];
   uint4* cbs = smem4;                  // [2][256][8 replicas]
   uint4* sh_x = smem4 + 2 * 256 * 8;   // padded inputs
@@ -115,8 +120,8 @@ aqlm_2x8_kernel(const uint4* __restrict__ codes, const uint4* __restrict__ x,
 
   const uint4* cb0 = cbs + (lane & 7);
   const uint4* cb1 = cbs + 256 * 8 + (lane & 7);
-  const int row_begin = (blockIdx.x * kWarps2x8 + warp) * kRowsPerWarp2x8;
-  for (int rr = 0; rr < kRowsPerWarp2x8; rr++) {
+  const int row_begin = (blockIdx.x * kWarps2x8 + warp) * rows_per_warp;
+  for (int rr = 0; rr < rows_per_warp; rr++) {
     const int m = row_begin + rr;
     if (m >= prob_m) break;
     const uint4* crow = codes + (size_t)m * vec_per_row;
@@ -167,7 +172,8 @@ int hq_aqlm_1x16_matvec(const void* codes, const void* x_half, void* out_half, c
   if (vpl > 4) return HQ_ERR_TOO_LARGE;  // prob_k <= 8192
   const int groups = prob_k / 8;
   const size_t smem = (size_t)kPad * ((groups + 7) / 8) * 16;
-  const int rows_per_cta = kWarps1x16 * kRowsPerWarp;
+  const int rows_per_warp = rows_per_warp_for(prob_m, kWarps1x16);
+  const int rows_per_cta = kWarps1x16 * rows_per_warp;
   const int grid = (prob_m + rows_per_cta - 1) / rows_per_cta;
   const int4 sizes = make_int4(cb_sizes[0], cb_sizes[1], cb_sizes[2], cb_sizes[3]);
   cudaStream_t st = (cudaStream_t)stream;
@@ -182,7 +188,8 @@ int hq_aqlm_1x16_matvec(const void* codes, const void* x_half, void* out_half, c
     kern<<<grid, kWarps1x16 * 32, smem, st>>>(                                               \
         reinterpret_cast<const uint4*>(codes), reinterpret_cast<const uint4*>(x_half),       \
         reinterpret_cast<__half*>(out_half), reinterpret_cast<const uint4*>(codebook),       \
-        prob_m, prob_k, sizes, cb_stride_int4, reinterpret_cast<const __half*>(scales_half)); \
+        prob_m, prob_k, sizes, cb_stride_int4, reinterpret_cast<const __half*>(scales_half), \
+        rows_per_warp);                                                                      \
   }
   switch (vpl) {
     case 1: HQ_AQLM_LAUNCH(1) break;
@@ -206,12 +213,13 @@ int hq_aqlm_2x8_matvec(const void* codes, const void* x_half, void* out_half, co
   cudaError_t e = cudaFuncSetAttribute(aqlm_2x8_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_status(e);
-  const int rows_per_cta = kWarps2x8 * kRowsPerWarp2x8;
+  const int rows_per_warp = rows_per_warp_for(prob_m, kWarps2x8);
+  const int rows_per_cta = kWarps2x8 * rows_per_warp;
   const int grid = (prob_m + rows_per_cta - 1) / rows_per_cta;
   aqlm_2x8_kernel<<<grid, kWarps2x8 * 32, smem, (cudaStream_t)stream>>>(
       reinterpret_cast<const uint4*>(codes), reinterpret_cast<const uint4*>(x_half),
       reinterpret_cast<__half*>(out_half), reinterpret_cast<const uint4*>(codebooks), prob_m,
-      prob_k, reinterpret_cast<const __half*>(scales_half));
+      prob_k, reinterpret_cast<const __half*>(scales_half), rows_per_warp);
   return launch_status();
 }
 
