@@ -10,9 +10,9 @@
 //    (even element in the high nibble unless the low-nibble-first flag is
 //    given): the dequantisation rule of hq_nf4_dequant_f16.
 // The description below is written for the 3-bit format; the NF4 form differs
-// only in the box the word warps fetch (128 rows x 32 bytes) and in the unpack
-// arithmetic (one fp32 table lookup and one multiply per code, packed to half2
-// with round-to-nearest).
+// only in the box the word warps fetch (128 rows x 32 bytes), in the unpack
+// arithmetic (one float2 table lookup per byte = two codes, one multiply per
+// code, packed to half2 with round-to-nearest) and in the ring depths.
 //
 // The contraction is computed transposed so that the weight dimension fills
 // the 128 rows of a tcgen05.mma tile and the token batch is its N dimension:
@@ -64,8 +64,6 @@ namespace hq {
 namespace {
 
 constexpr int kStages = 4;                  // A tiles in tensor memory, two per pipeline
-constexpr int kXStages = 8;                 // X tiles in shared memory, four per pipeline
-constexpr int kWordAhead = 8;               // packed-word blocks in flight (shared-memory ring)
 constexpr int kBlockK = 64;                 // halves per smem row (128 bytes)
 constexpr int kTileN = 128;                 // output features per CTA (UMMA M)
 constexpr int kMaxTokens = 128;             // UMMA N upper bound handled here
@@ -74,6 +72,17 @@ constexpr int kDeqLut = 64 * 128;           // 64 pair values x 32 lane copies x
 enum { kFmtQ3 = 0, kFmtNf4 = 1 };
 // bytes of one block's packed weights in the ring
 //   3-bit: 6 rows x 128 words, then 128 scales and 128 zeros;  NF4: 128 rows x 32 bytes
+// Per format: depth of the two shared-memory rings and size of the lookup table.
+// 3-bit: 8 X stages (four per pipeline), 8 word slots, table [64 pair values][32
+// lane copies] of half2.  NF4: 6 X stages, 6 word slots, table [256 byte
+// values][16 copies] of float2 (the two levels of the byte's codes), 32 KiB: the
+// shallower rings pay for it inside the same two-CTAs-per-SM budget.
+template <int FMT>
+struct Rings {
+  static constexpr int kXStages = FMT == 0 ? 8 : 6;
+  static constexpr int kWordAhead = FMT == 0 ? 8 : 6;
+  static constexpr int kLutWords = FMT == 0 ? 64 * 32 : 256 * 16 * 2;
+};
 template <int FMT>
 struct WordSlot { static constexpr int kBytes = FMT == kFmtQ3 ? 6 * 512 + 2 * 256 : 128 * 32; };
 constexpr int kProducerThreads = 256;
@@ -83,10 +92,12 @@ constexpr uint32_t kSpinLimit = 1u << 20;   // bounded mbarrier polls
 template <int FMT>
 inline size_t qgemm_smem_bytes(int tokens_padded) {
   const size_t need =
-      1024 + (size_t)kXStages * (tokens_padded * 128) + kWordAhead * WordSlot<FMT>::kBytes + 512;
+      1024 + (size_t)Rings<FMT>::kXStages * (tokens_padded * 128) +
+      Rings<FMT>::kWordAhead * WordSlot<FMT>::kBytes + 512;
   // The request also sets the number of CTAs per SM to what tensor memory holds:
   // two CTAs of 256 columns up to 64 tokens, one CTA of 512 columns beyond.
-  const size_t floor_bytes = tokens_padded <= 64 ? 90 * 1024 : 120 * 1024;
+  const size_t static_bytes = (size_t)Rings<FMT>::kLutWords * 4;
+  const size_t floor_bytes = (tokens_padded <= 64 ? 98 * 1024 : 128 * 1024) - static_bytes;
   return need > floor_bytes ? need : floor_bytes;
 }
 
@@ -197,9 +208,6 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// lookup table with one copy per bank: [entry][lane].  3-bit: entry v (6 bits)
-// = half2(v & 7, v >> 3);  NF4: entry c (4 bits) = the fp32 level lut16[c]
-__shared__ __align__(16) uint32_t g_pair_lut[64 * 32];
 
 struct QgemmParams {
   __half* Y;
@@ -224,7 +232,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* sm = dsm_raw + (base - raw);
   constexpr int kWordSlot = WordSlot<FMT>::kBytes;
+  constexpr int kXStages = Rings<FMT>::kXStages, kWordAhead = Rings<FMT>::kWordAhead;
   constexpr int kWordRing = kWordAhead * kWordSlot;
+  // lookup table.  3-bit: [pair value v (6 bits)][lane] = half2(v & 7, v >> 3), one
+  // copy per bank.  NF4: [byte value][copy c < 16] = float2(level of the first
+  // element, level of the second element): lane reads copy lane % 16, so the 16
+  // lanes of a half-warp read 16 different bank pairs whatever their bytes are.
+  __shared__ __align__(16) uint32_t lut_s[Rings<FMT>::kLutWords];
   const int kBTile = p.tokens_padded * 128;
   const uint32_t b_tiles = base;
   const uint32_t tiles_bytes = (uint32_t)(kXStages * kBTile);
@@ -279,10 +293,15 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
   if (FMT == kFmtQ3) {
     for (int i = tid; i < 64 * 32; i += kThreads) {
       const int v = i >> 5;
-      g_pair_lut[i] = half2_as_u32(__halves2half2(__int2half_rn(v & 7), __int2half_rn(v >> 3)));
+      lut_s[i] = half2_as_u32(__halves2half2(__int2half_rn(v & 7), __int2half_rn(v >> 3)));
     }
   } else {
-    for (int i = tid; i < 16 * 32; i += kThreads) g_pair_lut[i] = __float_as_uint(p.lut16[i >> 5]);
+    for (int i = tid; i < 256 * 16; i += kThreads) {
+      const int b = i >> 4, hi = b >> 4, lo = b & 15;
+      // even element = high nibble unless the low-nibble-first flag is given
+      lut_s[2 * i] = __float_as_uint(p.lut16[p.low_first ? lo : hi]);
+      lut_s[2 * i + 1] = __float_as_uint(p.lut16[p.low_first ? hi : lo]);
+    }
   }
   if (warp == 8) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -305,7 +324,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     // running counters and phase bits (no division, no modulo).
     const int row = tid & 127;      // output feature n0 + row, A-tile row
     const int grp = tid >> 7;       // blocks grp, grp + 2, ...
-    const unsigned char* lut = reinterpret_cast<const unsigned char*>(g_pair_lut);
+    const unsigned char* lut = reinterpret_cast<const unsigned char*>(lut_s);
+    const uint32_t lane8 = (uint32_t)(lane & 15) * 8u;  // NF4: this lane's copy of a table row
     const uint32_t lane4 = (uint32_t)lane * 4u;
     // this warp's 32 lanes of tensor memory (lane = A row), first A column
     const uint32_t a_lane = tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + a_col0;
@@ -389,7 +409,6 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
         return am_pow2 ? (kb >> am_shift) : (kb * kBlockK) / p.group_size;
       };
       float am_next = grp < nloc ? __ldg(am_row + am_index(kb0 + grp)) : 0.f;
-      const bool low_first = p.low_first != 0;
       for (int i = grp; i < nloc; i += 2) {
         const float am = am_next;
         if (i + 2 < nloc) am_next = __ldg(am_row + am_index(kb0 + i + 2));
@@ -409,15 +428,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
         for (int q = 0; q < 8; q++) {
 #pragma unroll
           for (int t = 0; t < 4; t++) {
-            // byte t of word q: codes (high nibble, low nibble) as table offsets (c << 7) | lane*4
-            const uint32_t hi_off =
-                ((t == 0 ? (w[q] << 3) : (w[q] >> (8 * t - 3))) & 0x780u) | lane4;
-            const uint32_t lo_off =
-                ((t == 0 ? (w[q] << 7) : (w[q] >> (8 * t - 7))) & 0x780u) | lane4;
-            const float f_hi = __uint_as_float(*reinterpret_cast<const uint32_t*>(lut + hi_off)) * am;
-            const float f_lo = __uint_as_float(*reinterpret_cast<const uint32_t*>(lut + lo_off)) * am;
-            o[4 * q + t] = half2_as_u32(low_first ? __floats2half2_rn(f_lo, f_hi)
-                                                  : __floats2half2_rn(f_hi, f_lo));
+            // byte t of word q -> table row offset (byte << 7) | copy
+            const uint32_t off =
+                ((t == 0 ? (w[q] << 7) : (w[q] >> (8 * t - 7))) & 0x7f80u) | lane8;
+            const float2 lv = *reinterpret_cast<const float2*>(lut + off);
+            o[4 * q + t] = half2_as_u32(__floats2half2_rn(lv.x * am, lv.y * am));
           }
         }
         __syncwarp();
