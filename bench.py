@@ -399,6 +399,20 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
             "sample": f"{sample}; {reps} repetitions in {el:.1f} s", "us_per_call": per * 1e6}
 
 
+def cpu_baseline_clean(name: str):
+    """cpu_baseline in a fresh interpreter (no CUDA context, no helper threads of
+    this process competing for the host cores), all host threads."""
+    env = dict(os.environ, OMP_NUM_THREADS=str(os.cpu_count() or 1))
+    code = ("import json, sys; sys.path.insert(0, %r); import bench; "
+            "print(json.dumps(bench.cpu_baseline(%r)))" % (str(ROOT), name))
+    try:
+        out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True,
+                             text=True, timeout=300, check=True).stdout
+        return json.loads(out.strip().splitlines()[-1])
+    except Exception:
+        return cpu_baseline(name)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -699,8 +713,7 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }
         if world == 1 and not args.no_cpu_baseline:
-            cb = cpu_baseline(args.workload)
-            line["cpu_baseline"] = cb
+            line["cpu_baseline"] = cpu_baseline_clean(args.workload)
         print(json.dumps(line), flush=True)
     if world > 1:
         # Tearing the NCCL communicator down after its collectives were captured in
