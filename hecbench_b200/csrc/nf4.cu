@@ -420,56 +420,57 @@ __global__ void gather_wait_kernel(const uint32_t* flags, const unsigned* sync_w
   else if (status != nullptr) atomicExch(status, 1);
 }
 
-// One CTA: copy this rank's finished slice (already in its own gathered vector)
-// into every peer's vector with 16-byte stores over NVLink, make the stores
-// visible system-wide, raise this rank's flag on every GPU, then wait (bounded)
-// until every rank's flag on this GPU has reached the same launch count.
-__global__ void __launch_bounds__(1024, 1)
+// One CTA per rank r of the node: CTA r copies this rank's finished slice
+// (already in its own gathered vector) into rank r's vector with 16-byte stores
+// over NVLink, makes the stores visible system-wide, raises this rank's flag on
+// GPU r, then waits (bounded) until rank r's flag on THIS GPU has reached the
+// same launch count.  The last CTA to finish advances the launch count.
+constexpr int kPublishThreads = 1024;
+__global__ void __launch_bounds__(kPublishThreads, 1)
 gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
                       uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
                       int* status) {
   const int tid = threadIdx.x;
-  // Programmatic dependent launch: this CTA may become resident while the kernel
+  const int r = blockIdx.x;
+  // Programmatic dependent launch: these CTAs may become resident while the kernel
   // that produces the slice is still draining, and the next kernel of the stream
-  // may start its own prologue while this one waits for the other ranks; the
-  // slice is read only after the producing kernel has completed.
+  // may start its own prologue while they wait for the other ranks; the slice is
+  // read only after the producing kernel has completed.
   pdl_launch_dependents();
   pdl_wait();
-  const __half* mine = peer_out[rank] + offset;
-  const bool vec_ok = ((offset | (long long)n_slice) & 7) == 0;
-  for (int r = 0; r < world; r++) {
-    if (r == rank) continue;
+  const unsigned epoch = *reinterpret_cast<volatile unsigned*>(sync_words + 1) + 1u;
+  if (r != rank) {
+    const __half* mine = peer_out[rank] + offset;
     __half* dst = peer_out[r] + offset;
+    const bool vec_ok = ((offset | (long long)n_slice) & 7) == 0;
     if (vec_ok) {
-      for (int i = tid; i < n_slice / 8; i += 1024)
+      for (int i = tid; i < n_slice / 8; i += kPublishThreads)
         reinterpret_cast<uint4*>(dst)[i] = __ldcg(reinterpret_cast<const uint4*>(mine) + i);
     } else {
-      for (int i = tid; i < n_slice; i += 1024)
+      for (int i = tid; i < n_slice; i += kPublishThreads)
         reinterpret_cast<unsigned short*>(dst)[i] =
             __ldcg(reinterpret_cast<const unsigned short*>(mine) + i);
     }
+    __threadfence_system();
   }
-  __threadfence_system();
   __syncthreads();
-  __shared__ unsigned s_epoch;
   if (tid == 0) {
-    const unsigned epoch = sync_words[1] + 1u;
-    sync_words[1] = epoch;
-    s_epoch = epoch;
-    for (int r = 0; r < world; r++)
-      *reinterpret_cast<volatile uint32_t*>(peer_flags[r] + rank) = epoch;
-  }
-  __syncthreads();
-  if (tid < world) {
-    const unsigned want = s_epoch;
-    const volatile uint32_t* f = peer_flags[rank] + tid;
+    *reinterpret_cast<volatile uint32_t*>(peer_flags[r] + rank) = epoch;
+    const volatile uint32_t* f = peer_flags[rank] + r;
     bool landed = false;
     for (unsigned spin = 0; spin < (1u << 22); spin++) {
-      if ((int)(*f - want) >= 0) { landed = true; break; }
+      if ((int)(*f - epoch) >= 0) { landed = true; break; }
       __nanosleep(32);
     }
     if (landed) __threadfence_system();
     else if (status != nullptr) atomicExch(status, 1);
+    // every CTA has read the old launch count before it gets here
+    __threadfence();
+    const unsigned prev = atomicAdd(sync_words, 1u);
+    if (prev == (unsigned)world - 1u) {
+      sync_words[1] = epoch;
+      sync_words[0] = 0u;
+    }
   }
 }
 
@@ -484,7 +485,8 @@ int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
   using namespace hq;
   if (!peer_out_half || !peer_flags || !sync_words) return HQ_ERR_NULL_POINTER;
   if (world < 1 || world > 32 || rank < 0 || rank >= world || n_slice <= 0) return HQ_ERR_BAD_SHAPE;
-  return cuda_status(launch_pdl(gather_publish_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream,
+  return cuda_status(launch_pdl(gather_publish_kernel, dim3(world), dim3(kPublishThreads), 0,
+                                (cudaStream_t)stream,
                                 reinterpret_cast<__half* const*>(peer_out_half), offset, n_slice,
                                 peer_flags, sync_words, world, rank, status));
 }
