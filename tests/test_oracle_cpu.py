@@ -217,3 +217,19 @@ def test_gemm_oracles(oracle):
     assert np.allclose(oracle.gemm_f16_f64(X, W), X.astype(np.float64) @ W.astype(np.float64))
     assert np.allclose(oracle.gemm_f16_nk_f64(X, np.ascontiguousarray(W.T)),
                        X.astype(np.float64) @ W.astype(np.float64))
+
+
+def test_batched_nf4_oracle_agrees_with_gemv_oracle(oracle):
+    """The batched path's checker (bit-exact dequantised weights, then an fp64
+    product) gives, row by row, what the mat-vec oracle gives for that input."""
+    from hecbench_b200 import synth
+    Mb, K, N, bs = 3, 256, 40, 64
+    X, B, absmax, lut = synth.qgemm_nf4_case(Mb, K, N, bs, seed=4)
+    for low_first in (0, 1):
+        W = oracle.nf4_dequant_f16(B, absmax, lut, N * K, bs, low_first).reshape(N, K)
+        Y = oracle.gemm_f16_nk_f64(X, W)
+        for j in range(Mb):
+            y = oracle.nf4_gemv_f64(X[j], B, absmax, lut, N, K, bs, low_first)
+            # the mat-vec oracle multiplies lut*absmax in fp64; the batched one rounds
+            # each weight to fp16 first, as the kernel under test does
+            assert np.allclose(Y[j], y, rtol=2e-3, atol=2e-3 * np.abs(y).max())
