@@ -16,7 +16,6 @@ SIGNATURES = {
     "hq_version": (c_int, []),
     "hq_status_string": (C.c_char_p, [c_int]),
     "hq_last_cuda_error": (c_int, []),
-    "hq_probe_stream_read": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p]),
     "hq_q3_gemv_f32": (c_int, [c_void_p] * 5 + [c_int, c_int, c_void_p]),
     "hq_q3_gemv_f16in": (c_int, [c_void_p] * 5 + [c_int, c_int, c_void_p]),
     "hq_q3_dequant_f32": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p]),
@@ -24,12 +23,14 @@ SIGNATURES = {
     "hq_bnb_quantize_u8": (c_int, [c_void_p] * 3 + [c_size_t, c_void_p]),
     "hq_nf4_dequant_f16": (c_int, [c_void_p] * 4 + [c_size_t, c_int, c_int, c_void_p]),
     "hq_nf4_gemv_f16": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p]),
-    "hq_nf4_gemv_f16_gather": (c_int, [c_void_p] * 4 + [c_int] * 4 + [c_void_p, C.c_longlong,
-                                                              c_void_p, c_void_p, c_int, c_int,
-                                                              c_void_p, c_void_p, c_void_p]),
+    "hq_nf4_gemv_f16_ll": (c_int, [c_void_p, c_void_p, C.c_longlong, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_int, c_int, c_int, c_void_p, C.c_longlong,
+                                   c_void_p, c_int, c_int, C.c_uint, c_void_p, c_void_p]),
+    "hq_ll_unpack": (c_int, [c_void_p, C.c_longlong, c_void_p, c_void_p, C.c_uint, c_void_p,
+                             c_void_p]),
     "hq_gather_publish": (c_int, [c_void_p, C.c_longlong, c_int, c_void_p, c_void_p, c_int, c_int,
-                                  c_void_p, c_void_p]),
-    "hq_gather_wait": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+                                  C.c_uint, c_void_p, c_void_p]),
+    "hq_gather_wait": (c_int, [c_void_p, c_void_p, c_int, C.c_uint, c_void_p, c_void_p]),
     "hq_lutgemm_workspace_bytes": (c_size_t, [c_int]),
     "hq_lutgemm_nqmv": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p, c_size_t, c_void_p]),
     "hq_lutgemm_nqmv_noalloc": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),

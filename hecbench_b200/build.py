@@ -1,7 +1,8 @@
 """In-tree build of libhq.so (the C-ABI launcher library) for sm_100a.
 
 `python -m hecbench_b200.build` compiles every .cu under csrc/ with nvcc
-(cross-compiles without a GPU) into hecbench_b200/libhq.so.  The objects are
+(cross-compiles without a GPU) into hecbench_b200/libhq.so, and the
+streaming-read probe of bench.py (csrc/probe/) into hecbench_b200/libhq_probe.so.  The objects are
 cached under hecbench_b200/build/ and rebuilt when a source or header is newer.
 """
 from __future__ import annotations
@@ -17,11 +18,14 @@ ROOT = PKG.parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libhq.so"
+PROBE_LIB = PKG / "libhq_probe.so"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
          f"-I{ROOT / 'include'}", f"-I{CSRC}"]
+# extra nvcc flags, e.g. HQ_NVCC_FLAGS="-DHQ_BOUNDS_CHECK" for the index-checked build
+FLAGS += os.environ.get("HQ_NVCC_FLAGS", "").split()
 
 
 def _newer(target: Path, deps) -> bool:
@@ -61,6 +65,13 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stderr}")
+    # measurement aid of bench.py, kept out of the product library
+    probe_src = CSRC / "probe" / "stream_read.cu"
+    if force or _newer(PROBE_LIB, [probe_src, *headers]):
+        cmd = [NVCC, *ARCH, *FLAGS, "-shared", str(probe_src), "-o", str(PROBE_LIB), "-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {probe_src.name}:\n{r.stderr}")
     return LIB
 
 

@@ -1,6 +1,8 @@
 // Shared helpers for the libhq kernels (sm_100a only).
 #pragma once
 
+#include <atomic>
+
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -27,6 +29,28 @@ inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// Shared memory the system reserves at the start of every CTA's window on the
+// current device (cached per device).
+int reserved_smem_per_block();
+
+// Raises the dynamic shared-memory limit of kernel Kern to `bytes` once per
+// device (and again only if a later call needs more): the attribute call costs
+// microseconds of host time, which an eager launch every few microseconds
+// cannot afford.  Safe from several host threads: the attribute is idempotent
+// and the record only ever grows.
+constexpr int kMaxDevices = 64;
+template <auto Kern>
+inline cudaError_t ensure_dynamic_smem(size_t bytes) {
+  static std::atomic<size_t> granted[kMaxDevices];  // zero-initialised, one array per kernel
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool tracked = dev >= 0 && dev < kMaxDevices;
+  if (tracked && granted[dev].load(std::memory_order_acquire) >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && tracked) granted[dev].store(bytes, std::memory_order_release);
+  return e;
+}
 
 // Programmatic dependent launch.  A kernel calls pdl_launch_dependents() first
 // thing, so that the next kernel of the stream may become resident while this

@@ -10,24 +10,30 @@
 // Like the reference (mv_fp16.h:133-227) the +-sums over 8 inputs are looked up
 // by bit-plane byte in a table built from x, but:
 //  * a CTA of 512 threads owns a K tile of 128 inputs (4 packed rows; 64 inputs
-//    with two CTAs per SM for alpha groups of 192, 320, ... inputs) and a range
-//    of columns; lane (c,j) of a warp handles byte j of the words of columns
-//    4c..4c+3 and reads replica c of table (row, j): the 16 tables are stored
-//    with one 256-byte line per (row pair, byte value) holding
-//    [row parity][replica c][byte-lane j], so every lane of a warp reads its
-//    own bank - no lookup ever conflicts - and, the table block sitting at a
-//    FIXED address of the shared window, the address of a lookup is ONE
-//    byte-permute of the packed word and a per-lane constant, plus an
-//    immediate offset that selects the row;
-//  * packed words, alphas and bias travel through a per-quad cp.async ring whose
-//    slots are an odd multiple of 16 bytes, so the eight quads of a warp fill
-//    and read their slots in eight different bank groups;
+//    for alpha groups of 192, 320, ... inputs) and a range of columns; lane
+//    (c,j) of a warp handles byte j of the words of columns 4c..4c+3 and reads
+//    replica c of table (row, j): the 16 tables are stored with one 256-byte
+//    line per (row pair, byte value) holding [row parity][replica c][byte-lane
+//    j], so every lane of a warp reads its own bank - no lookup ever conflicts
+//    - and, the table block sitting at a FIXED address of the shared window,
+//    the address of a lookup is ONE byte-permute of the packed word and a
+//    per-lane constant, plus an immediate offset that selects the row;
+//  * shared memory carries the lookups and nothing else: packed words, alphas
+//    and bias go from global memory straight into registers (128-bit streaming
+//    loads, the four lanes of a column quad reading the same 16 bytes), one
+//    column step ahead of their use, and the first step is requested before
+//    the tables are built;
+//  * before anything else a few threads ask the L2 for the CTA's whole
+//    footprint (bulk L2 prefetches of the TR*NB runs of packed words, line
+//    prefetches of the alpha / bias runs), so that the register loads of the
+//    lookup phase find their lines in L2 instead of waiting for HBM;
 //  * table entries and all sums are fp32 (the reference uses fp16 throughout
 //    and half2 atomics on the output);
 //  * the four lanes of a column quad are combined with two shuffles, each CTA
 //    adds its tile's partial sums to an fp32 scratch row with one 16-byte
-//    vector reduction per column quad, and the last CTA to finish converts the
-//    scratch to fp16, stores the output and re-zeroes the scratch.
+//    vector reduction per column quad, and the last CTA of each column range to
+//    finish converts that range of the scratch to fp16, stores the output and
+//    re-zeroes the scratch.
 #include <mutex>
 
 #include "hq_common.cuh"
@@ -37,53 +43,31 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
-constexpr int kQuads = kThreads / 4;
 // Shared-window address at which a CTA's dynamic region starts: the 1 KiB the
 // system reserves per CTA (the kernels have no static shared memory).  The
-// host checks the device attribute before launching and the kernel checks the
-// address itself; kSlack bytes of padding absorb a start up to kSlack later.
+// host checks the device attribute before launching; kSlack bytes of padding
+// absorb a start up to kSlack later.
 constexpr int kDynBase = 1024;
 constexpr int kSlack = 256;
+// completion counters at the end of the workspace: one per column range
+constexpr int kCounterWords = 64;
 
 // Compile-time layout of one variant.  TR: packed rows (32 inputs each) per K
-// tile, 4 with one CTA per SM or 2 with two CTAs per SM.  Dynamic shared memory:
-//   [flag 16 B][word ring, kBufs buffers][padding][tables TR/2 x 64 KiB]
+// tile.  Dynamic shared memory:
+//   [flag 16 B][build scratch: compact tables + inputs][padding][tables TR/2 x 64 KiB]
 // The tables start at the FIXED shared-window address kLutImm so that the
-// address of a lookup is a byte-permute plus an immediate.  The build scratch
-// (compact tables + inputs) aliases the last ring buffer, which is not written
-// before the tables are complete.
-template <int TR, int NB, int RPG, int kBufs>
+// address of a lookup is a byte-permute plus an immediate.
+template <int TR>
 struct Layout {
-  static constexpr int kGroups = TR / RPG;
-  static constexpr int kWords = TR * NB;  // 16-byte word vectors per column step
-  // bytes of one column step in a quad's ring: packed words, then per alpha
-  // group NB alpha vectors and one bias vector of four halves each
-  // an odd multiple of 16 bytes: the eight quads of a warp then read and fill
-  // their slots in eight different 16-byte bank groups
-  static constexpr int kStepRaw = (TR * NB * 16 + kGroups * (NB + 1) * 8 + 15) / 16 * 16;
-  static constexpr int kStep = (kStepRaw / 16) % 2 == 0 ? kStepRaw + 16 : kStepRaw;
-  static constexpr int kBuf = kQuads * kStep;
   static constexpr int kCompactWords = TR * 256 * 4;  // [row][byte value][j]
-  static constexpr int kBuildBytes = kCompactWords * 4 + TR * 32 * 4 + 64;
-  static constexpr int kRing = (kBufs - 1) * kBuf + (kBuf > kBuildBytes ? kBuf : kBuildBytes);
-  static constexpr int kRingOff = 16;
+  static constexpr int kBuildBytes = kCompactWords * 4 + TR * 32 * 4;
+  static constexpr int kFlagBytes = 16;
   static constexpr int kLutBytes = (TR / 2) * 65536;
-  static constexpr int kLutImm = (kDynBase + kSlack + kRingOff + kRing + 255) / 256 * 256;
+  static constexpr int kLutImm = (kDynBase + kSlack + kFlagBytes + kBuildBytes + 255) / 256 * 256;
   static constexpr int kSmem = kLutImm - kDynBase + kLutBytes;
-  static constexpr int kCtasPerSm = TR == 2 ? 2 : 1;
-  // an SM has 228 KiB; each resident CTA also takes the reserved 1 KiB
-  static constexpr int kSmemLimit = 228 * 1024 / kCtasPerSm - kDynBase;
-  static_assert(kStep % 16 == 0, "ring slots hold 16-byte asynchronous copies");
+  static_assert(kSmem <= 227 * 1024, "shared memory budget");
 };
-// deepest ring (3 or 2 column steps per quad) that fits
-template <int TR, int NB, int RPG>
-constexpr int pick_bufs() {
-  return Layout<TR, NB, RPG, 3>::kSmem <= Layout<TR, NB, RPG, 3>::kSmemLimit ? 3 : 2;
-}
 
-__device__ __forceinline__ void red_add_f32(float* addr, float v) {
-  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
-}
 __device__ __forceinline__ void red_add_v4_f32(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
                "f"(d)
@@ -91,127 +75,129 @@ __device__ __forceinline__ void red_add_v4_f32(float* addr, float a, float b, fl
 }
 template <int IMM>
 __device__ __forceinline__ float lds_f32_imm(uint32_t addr) {
-  // not volatile: the tables are constant once built, and every address depends
-  // on ring data that is read behind the proper barrier, so the scheduler is
-  // free to batch these loads
+  // not volatile: the tables are constant once built, so the scheduler is free
+  // to batch these loads
   float v;
   asm("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
   return v;
 }
-__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr));
-  return v;
+// Ask the L2 for `bytes` (a multiple of 16) at the 16-byte aligned address p.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+__device__ __forceinline__ void l2_prefetch_line(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
-__device__ __forceinline__ uint2 lds_u2(uint32_t addr) {
+__device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
   uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
   return v;
-}
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // One launch handles NB bit planes b0 .. b0+NB-1 of nb_total (more planes than
-// fit are split over launches that accumulate into the same scratch row; only
-// the last one converts it).  RPG: packed rows that share one alpha group
-// inside a tile.  kBufs: column steps resident in the word ring per quad
-// (kBufs - 1 in flight).  The word after the completion counter receives 1 if
-// the shared-memory layout does not fit where the CTA's dynamic region starts.
-template <int TR, int NB, int RPG, int kBufs>
-__global__ void __launch_bounds__(kThreads, (TR == 2 ? 2 : 1))
+// fit the register budget are split over launches that accumulate into the
+// same scratch row; only the last one converts it).  RPG: packed rows that
+// share one alpha group inside a tile.  counters: one completion counter per
+// column range (per_range != 0) or a single one.
+template <int TR, int NB, int RPG>
+__global__ void __launch_bounds__(kThreads, 1)
 lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha,
                const __half* __restrict__ q_bias, const __half* __restrict__ x,
-               __half* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ counter,
+               __half* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ counters,
                int M, int K, int rows_per_group, int cols_per_cta, int nb_total, int b0,
-               int finalize) {
-  using L = Layout<TR, NB, RPG, kBufs>;
-  constexpr int kWords = L::kWords, kStep = L::kStep, kGroups = L::kGroups;
-  constexpr int kItems = kGroups * (NB + 1);  // alpha / bias vectors per column step
+               int finalize, int per_range) {
+  using L = Layout<TR>;
+  constexpr int kGroups = TR / RPG;
   constexpr int kLutImm = L::kLutImm;
   extern __shared__ __align__(16) unsigned char dsm[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t dsm_addr = (uint32_t)__cvta_generic_to_shared(dsm);
-  if (dsm_addr < (uint32_t)kDynBase || dsm_addr > (uint32_t)(kDynBase + kSlack)) {
-    if (tid == 0) counter[1] = 1u;  // same decision in every CTA: nothing is computed
-    return;
-  }
+  // the host has checked where the dynamic region starts; never taken
+  if (dsm_addr < (uint32_t)kDynBase || dsm_addr > (uint32_t)(kDynBase + kSlack)) return;
   unsigned char* lut = dsm + ((uint32_t)kLutImm - dsm_addr);
-  unsigned char* ring = dsm + L::kRingOff;
   unsigned* s_last = reinterpret_cast<unsigned*>(dsm);
-  // ring layout: [buffer][quad][step bytes]; the build scratch aliases the last buffer
-  float* compact = reinterpret_cast<float*>(ring + (size_t)(kBufs - 1) * L::kBuf);
+  float* compact = reinterpret_cast<float*>(dsm + L::kFlagBytes);
   float* xs = compact + L::kCompactWords;  // the tile's inputs
   const int tile = blockIdx.y;
   const int row0 = tile * TR;  // first packed row of the tile
   const int total_rows = K >> 5;
   const int nrows = min(TR, total_rows - row0);
-
-  // ---- column steps of this warp and the quad's word ring ----
-  const int j = lane & 3;   // byte of the word this lane looks up
-  const int cq = lane >> 2; // column quad inside the 32-column step
   const int m_begin = blockIdx.x * cols_per_cta;
   const int m_end = min(M, m_begin + cols_per_cta);
-  const int m0 = m_begin + warp * 32 + cq * 4;  // step s handles columns m0 + s*kWarps*32 ..+3
-  const int nsteps = (m_end - (m_begin + warp * 32) + kWarps * 32 - 1) / (kWarps * 32);
-  const uint32_t ring_quad = dsm_addr + L::kRingOff + (uint32_t)((warp * 8 + cq) * kStep);
-  const uint32_t* src0 = bW + ((size_t)row0 * nb_total + b0) * M + m0;
   const int g0 = row0 / rows_per_group;  // alpha group of the tile's first row
-
-  // lane j of a quad copies word vectors j, j+4, ... of a step (rows past the end
-  // of K are skipped: their tables are all zero, so stale ring bytes are harmless)
-  auto issue = [&](int s) {
-    if (s < nsteps) {
-      const int m = m0 + s * (kWarps * 32);
-      if (m < m_end) {
-        const uint32_t dst = ring_quad + (uint32_t)((s % kBufs) * L::kBuf);
-        const uint32_t* src = src0 + (size_t)s * (kWarps * 32);
-        // alpha / bias vectors: item (group gi, plane b) with b == NB meaning the bias
-#pragma unroll
-        for (int t = 0; t < (kItems + 3) / 4; t++) {
-          const int it = j + 4 * t;
-          if (it < kItems) {
-            const int gi = it / (NB + 1), b = it - gi * (NB + 1);
-            const int g = g0 + gi;
-            if (gi * RPG < nrows) {
-              if (b < NB)
-                cp_async_8(dst + kWords * 16 + it * 8,
-                           alpha + ((size_t)g * nb_total + b0 + b) * M + m);
-              else if (q_bias != nullptr)
-                cp_async_8(dst + kWords * 16 + it * 8, q_bias + (size_t)g * M + m);
-            }
-          }
-        }
-#pragma unroll
-        for (int t = 0; t < (kWords + 3) / 4; t++) {
-          const int i = j + 4 * t;  // word vector (row i / NB, plane i % NB)
-          const int r = i / NB, b = i - r * NB;
-          if (i < kWords && r < nrows)
-            cp_async_16(dst + i * 16, src + (size_t)(r * nb_total + b) * M);
-        }
-      }
-    }
-    cp_async_commit();
-  };
-#pragma unroll
-  for (int s = 0; s < kBufs - 1; s++) issue(s);
 
   // ---- stage the tile's inputs (zero beyond K) ----
   if (tid < TR * 32) {
     const int k = row0 * 32 + tid;
     xs[tid] = (k < K) ? __half2float(x[k]) : 0.f;
+  }
+  // ---- ask the L2 for everything this CTA will read ----
+  {
+    const uint32_t run_bytes = (uint32_t)(m_end - m_begin) * 4u;  // multiple of 16: M % 4 == 0
+    if (tid < TR * NB) {
+      const int r = tid / NB, b = tid - r * NB;
+      if (r < nrows) {
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(
+            bW + ((size_t)(row0 + r) * nb_total + b0 + b) * M + m_begin);
+        for (uint32_t off = 0; off < run_bytes; off += 32768u)
+          l2_prefetch_bulk(src + off, min(32768u, run_bytes - off));
+      }
+    }
+    // alpha / bias runs, one 128-byte line per thread and turn
+    const int lines = ((m_end - m_begin) * 2 + 127) / 128;
+    for (int it = tid; it < kGroups * (NB + 1) * lines; it += kThreads) {
+      const int item = it / lines, ln = it - item * lines;
+      const int gi = item / (NB + 1), b = item - gi * (NB + 1);
+      if (gi * RPG < nrows) {
+        const int g = g0 + gi;
+        if (b < NB)
+          l2_prefetch_line(alpha + ((size_t)g * nb_total + b0 + b) * M + m_begin + ln * 64);
+        else if (q_bias != nullptr)
+          l2_prefetch_line(q_bias + (size_t)g * M + m_begin + ln * 64);
+      }
+    }
+  }
+
+  // ---- column steps of this warp: step s handles columns m0 + s*kWarps*32 ..+3 ----
+  const int j = lane & 3;   // byte of the word this lane looks up
+  const int cq = lane >> 2; // column quad inside the 32-column step
+  const int m0 = m_begin + warp * 32 + cq * 4;
+  const int nsteps = (m_end - (m_begin + warp * 32) + kWarps * 32 - 1) / (kWarps * 32);
+  const uint32_t* src0 = bW + ((size_t)row0 * nb_total + b0) * M + m0;
+
+  uint4 wv[TR][NB];
+  uint2 av[kGroups][NB + 1];
+#pragma unroll
+  for (int r = 0; r < TR; r++)
+#pragma unroll
+    for (int b = 0; b < NB; b++) wv[r][b] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int gi = 0; gi < kGroups; gi++)
+#pragma unroll
+    for (int b = 0; b <= NB; b++) av[gi][b] = make_uint2(0, 0);
+
+  // packed words of row r for the step whose first column (for this quad) is m
+  auto load_row = [&](int r, int m) {
+    if (r < nrows) {
+#pragma unroll
+      for (int b = 0; b < NB; b++)
+        wv[r][b] = ldg_stream_u4(src0 + (size_t)(r * nb_total + b) * M + (m - m0));
+    }
+  };
+  auto load_group = [&](int gi, int m) {
+    if (gi * RPG < nrows) {
+      const int g = g0 + gi;
+#pragma unroll
+      for (int b = 0; b < NB; b++)
+        av[gi][b] = ldg_nc_u2(alpha + ((size_t)g * nb_total + b0 + b) * M + m);
+      if (q_bias != nullptr) av[gi][NB] = ldg_nc_u2(q_bias + (size_t)g * M + m);
+    }
+  };
+  if (nsteps > 0 && m0 < m_end) {
+#pragma unroll
+    for (int r = 0; r < TR; r++) load_row(r, m0);
+#pragma unroll
+    for (int gi = 0; gi < kGroups; gi++) load_group(gi, m0);
   }
   __syncthreads();
 
@@ -275,14 +261,12 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   }
 
   for (int s = 0; s < nsteps; s++) {
-    issue(s + kBufs - 1);
     const int m = m0 + s * (kWarps * 32);
     const bool active = m < m_end;
-    cp_async_wait<kBufs - 1>();
-    __syncwarp();
+    const int m_next = m + kWarps * 32;
+    const bool next = (s + 1 < nsteps) && m_next < m_end;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (active) {
-      const uint32_t buf = ring_quad + (uint32_t)((s % kBufs) * L::kBuf);
 #pragma unroll
       for (int gi = 0; gi < kGroups; gi++) {
         float t[NB][4];
@@ -291,8 +275,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
           const int r = gi * RPG + rr;
 #pragma unroll
           for (int b = 0; b < NB; b++) {
-            const uint4 wv = lds_u4(buf + (uint32_t)((r * NB + b) * 16));
-            const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
+            const uint32_t w4[4] = {wv[r][b].x, wv[r][b].y, wv[r][b].z, wv[r][b].w};
 #pragma unroll
             for (int c = 0; c < 4; c++) {
               const uint32_t a = __byte_perm(w4[c], hi, sel);
@@ -304,30 +287,30 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
               t[b][c] = (rr == 0) ? v : t[b][c] + v;
             }
           }
+          if (next) load_row(r, m_next);  // the registers of this row are free again
         }
-        if (gi * RPG >= nrows) continue;  // rows past the end of K (no alpha was copied)
+        if (gi * RPG < nrows) {  // rows past the end of K have no alpha
 #pragma unroll
-        for (int b = 0; b < NB; b++) {
-          const uint2 avb = lds_u2(buf + (uint32_t)(kWords * 16 + (gi * (NB + 1) + b) * 8));
-          const float2 a01 = __half22float2(u32_as_half2(avb.x));
-          const float2 a23 = __half22float2(u32_as_half2(avb.y));
-          acc[0] = fmaf(a01.x, t[b][0], acc[0]);
-          acc[1] = fmaf(a01.y, t[b][1], acc[1]);
-          acc[2] = fmaf(a23.x, t[b][2], acc[2]);
-          acc[3] = fmaf(a23.y, t[b][3], acc[3]);
+          for (int b = 0; b < NB; b++) {
+            const float2 a01 = __half22float2(u32_as_half2(av[gi][b].x));
+            const float2 a23 = __half22float2(u32_as_half2(av[gi][b].y));
+            acc[0] = fmaf(a01.x, t[b][0], acc[0]);
+            acc[1] = fmaf(a01.y, t[b][1], acc[1]);
+            acc[2] = fmaf(a23.x, t[b][2], acc[2]);
+            acc[3] = fmaf(a23.y, t[b][3], acc[3]);
+          }
+          if (q_bias != nullptr) {
+            const float2 b01 = __half22float2(u32_as_half2(av[gi][NB].x));
+            const float2 b23 = __half22float2(u32_as_half2(av[gi][NB].y));
+            acc[0] = fmaf(b01.x, ones[gi], acc[0]);
+            acc[1] = fmaf(b01.y, ones[gi], acc[1]);
+            acc[2] = fmaf(b23.x, ones[gi], acc[2]);
+            acc[3] = fmaf(b23.y, ones[gi], acc[3]);
+          }
         }
-        if (q_bias != nullptr) {
-          const uint2 bvv = lds_u2(buf + (uint32_t)(kWords * 16 + (gi * (NB + 1) + NB) * 8));
-          const float2 b01 = __half22float2(u32_as_half2(bvv.x));
-          const float2 b23 = __half22float2(u32_as_half2(bvv.y));
-          acc[0] = fmaf(b01.x, ones[gi], acc[0]);
-          acc[1] = fmaf(b01.y, ones[gi], acc[1]);
-          acc[2] = fmaf(b23.x, ones[gi], acc[2]);
-          acc[3] = fmaf(b23.y, ones[gi], acc[3]);
-        }
+        if (next) load_group(gi, m_next);
       }
     }
-    __syncwarp();  // all lanes are done with this step's ring buffer
     // combine the four byte lanes of each column quad
 #pragma unroll
     for (int c = 0; c < 4; c++) {
@@ -338,26 +321,27 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     // them to the scratch row with one 16-byte reduction
     if (active && j == 0) red_add_v4_f32(ws + m, acc[0], acc[1], acc[2], acc[3]);
   }
-  cp_async_wait<0>();
 
-  // ---- last CTA converts the scratch row to fp16 and re-zeroes it ----
+  // ---- the last CTA of a column range converts it to fp16 and re-zeroes the scratch ----
   if (!finalize) return;
   __threadfence();
   __syncthreads();
   if (tid == 0) {
-    const unsigned total = gridDim.x * gridDim.y;
-    const unsigned prev = atomicAdd(counter, 1u);
+    const unsigned total = per_range ? gridDim.y : gridDim.x * gridDim.y;
+    const unsigned prev = atomicAdd(counters + (per_range ? blockIdx.x : 0), 1u);
     *s_last = (prev == total - 1) ? 1u : 0u;
   }
   __syncthreads();
   if (*s_last) {
     __threadfence();
-    for (int mm = tid; mm < M; mm += kThreads) {
-      const float v = __ldcg(ws + mm);
-      out[mm] = __float2half_rn(v);
-      ws[mm] = 0.f;
+    const int lo = per_range ? m_begin : 0, hi_m = per_range ? m_end : M;
+    for (int mm = lo + tid * 4; mm < hi_m; mm += kThreads * 4) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(ws + mm));
+      const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+      *reinterpret_cast<uint2*>(out + mm) = make_uint2(half2_as_u32(h01), half2_as_u32(h23));
+      *reinterpret_cast<float4*>(ws + mm) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (tid == 0) *counter = 0u;
+    if (tid == 0) counters[per_range ? blockIdx.x : 0] = 0u;
   }
 }
 
@@ -370,63 +354,57 @@ struct LaunchArgs {
   const __half* x;
   __half* out;
   float* ws;
-  unsigned* counter;
-  int M, K, rows_per_group, cols_per_cta, nb_total;
+  unsigned* counters;
+  int M, K, rows_per_group, cols_per_cta, nb_total, per_range;
 };
 
-template <int TR, int NB, int RPG, int kBufs>
+template <int TR, int NB, int RPG>
 int launch_one(const LaunchArgs& a, int b0, const __half* bias, int finalize) {
-  using L = Layout<TR, NB, RPG, kBufs>;
-  auto kern = lutgemm_kernel<TR, NB, RPG, kBufs>;
-  static_assert(L::kSmem <= L::kSmemLimit, "shared memory budget");
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kSmem);
+  using L = Layout<TR>;
+  constexpr auto kern = lutgemm_kernel<TR, NB, RPG>;
+  cudaError_t e = ensure_dynamic_smem<kern>(L::kSmem);
   if (e != cudaSuccess) return cuda_status(e);
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                           cudaSharedmemCarveoutMaxShared);
-  if (e != cudaSuccess) return cuda_status(e);
-  kern<<<a.grid, kThreads, L::kSmem, a.st>>>(a.bW, a.alpha, bias, a.x, a.out, a.ws, a.counter, a.M,
-                                             a.K, a.rows_per_group, a.cols_per_cta, a.nb_total, b0,
-                                             finalize);
+  kern<<<a.grid, kThreads, L::kSmem, a.st>>>(a.bW, a.alpha, bias, a.x, a.out, a.ws, a.counters,
+                                             a.M, a.K, a.rows_per_group, a.cols_per_cta,
+                                             a.nb_total, b0, finalize, a.per_range);
   return launch_status();
 }
 
-template <int TR, int NB, int RPG>
-int launch_sub(const LaunchArgs& a, int b0, const __half* bias, int finalize) {
-  return launch_one<TR, NB, RPG, pick_bufs<TR, NB, RPG>()>(a, b0, bias, finalize);
-}
-
-// Bit planes are handled up to kMax at a time (what fits the shared-memory
-// ring); further planes go to follow-up launches that accumulate into the same
-// scratch row.  Only the first launch adds the bias term, only the last one
-// converts the scratch row.
+// Bit planes are handled up to kMax at a time (what the register budget of the
+// one-step-ahead loads allows); further planes go to follow-up launches that
+// accumulate into the same scratch row.  Only the first launch adds the bias
+// term, only the last one converts the scratch row.
 template <int TR, int RPG>
 int launch_planes(const LaunchArgs& a) {
-  constexpr int kMax = (TR / RPG >= 2 && RPG == 1) ? 3 : 4;
+  constexpr int kMax = TR == 4 ? 3 : 4;
   const int nb = a.nb_total;
   for (int b0 = 0; b0 < nb; b0 += kMax) {
     const int n = nb - b0 < kMax ? nb - b0 : kMax;
     const int last = (b0 + n == nb) ? 1 : 0;
     const __half* bias = b0 == 0 ? a.q_bias : nullptr;
     int st;
-    if (n == 1) st = launch_sub<TR, 1, RPG>(a, b0, bias, last);
-    else if (n == 2) st = launch_sub<TR, 2, RPG>(a, b0, bias, last);
-    else if (n == 3) st = launch_sub<TR, 3, RPG>(a, b0, bias, last);
-    else st = launch_sub<TR, (kMax >= 4 ? 4 : 3), RPG>(a, b0, bias, last);
+    if (n == 1) st = launch_one<TR, 1, RPG>(a, b0, bias, last);
+    else if (n == 2) st = launch_one<TR, 2, RPG>(a, b0, bias, last);
+    else if (n == 3) st = launch_one<TR, 3, RPG>(a, b0, bias, last);
+    else st = launch_one<TR, (kMax >= 4 ? 4 : 3), RPG>(a, b0, bias, last);
     if (st != HQ_OK) return st;
   }
   return HQ_OK;
 }
 
-// Shared memory the system reserves per CTA on the current device (the start
-// of a CTA's dynamic region when the kernel has no static shared memory).
-int reserved_smem_per_cta(int* out) {
-  int dev = 0, v = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return cuda_status(e);
-  e = cudaDeviceGetAttribute(&v, cudaDevAttrReservedSharedMemoryPerBlock, dev);
-  if (e != cudaSuccess) return cuda_status(e);
-  *out = v;
+// Argument rules shared by both entry points; nothing is launched or touched
+// when they fail.
+int check_args(const void* out_half, const void* x_half, const uint32_t* bW, const void* alpha_half,
+               const void* q_bias_half, int M, int K, int nb, int group_size) {
+  if (!out_half || !x_half || !bW || !alpha_half) return HQ_ERR_NULL_POINTER;
+  if (M <= 0 || K <= 0 || M % 4 != 0 || K % 32 != 0 || nb < 1 || nb > 8) return HQ_ERR_BAD_SHAPE;
+  if (group_size <= 0 || group_size % 32 != 0 || K % group_size != 0) return HQ_ERR_BAD_SHAPE;
+  if (!aligned16(bW) || !aligned8(alpha_half) || (q_bias_half && !aligned8(q_bias_half)) ||
+      !aligned8(out_half))
+    return HQ_ERR_MISALIGNED;
+  const int rpg = group_size / 32;
+  // groups of 96, 160, ... inputs would straddle tiles
+  if (rpg != 1 && rpg % 2 != 0) return HQ_ERR_UNSUPPORTED;
   return HQ_OK;
 }
 
@@ -444,30 +422,21 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW, cons
                     const void* q_bias_half, int M, int K, int nb, int group_size, void* workspace,
                     size_t workspace_bytes, hq_stream_t stream) {
   using namespace hq;
-  if (!out_half || !x_half || !bW || !alpha_half) return HQ_ERR_NULL_POINTER;
-  if (M <= 0 || K <= 0 || M % 4 != 0 || K % 32 != 0 || nb < 1 || nb > 8) return HQ_ERR_BAD_SHAPE;
-  if (group_size <= 0 || group_size % 32 != 0 || K % group_size != 0) return HQ_ERR_BAD_SHAPE;
+  const int cst = check_args(out_half, x_half, bW, alpha_half, q_bias_half, M, K, nb, group_size);
+  if (cst != HQ_OK) return cst;
   if (!workspace || workspace_bytes < hq_lutgemm_workspace_bytes(M)) return HQ_ERR_WORKSPACE;
-  if (!aligned16(bW) || !aligned8(alpha_half) || (q_bias_half && !aligned8(q_bias_half)) ||
-      !aligned16(workspace))
-    return HQ_ERR_MISALIGNED;
+  if (!aligned16(workspace)) return HQ_ERR_MISALIGNED;
   const int rpg = group_size / 32;
-  // groups of 96, 160, ... inputs would straddle tiles
-  if (rpg != 1 && rpg % 2 != 0) return HQ_ERR_UNSUPPORTED;
-  int reserved = 0;
-  const int rst = reserved_smem_per_cta(&reserved);
-  if (rst != HQ_OK) return rst;
+  const int reserved = reserved_smem_per_block();
   if (reserved < kDynBase || reserved > kDynBase + kSlack) return HQ_ERR_UNSUPPORTED;
 
-  // K tile: 128 inputs with one CTA per SM (the faster form on B200: 41 us
-  // against 54 us on a 12288 x 12288 3-plane matrix) wherever alpha groups do
-  // not straddle it; 64 inputs with two CTAs per SM for groups of 192, 320, ...
+  // K tile: 128 inputs wherever alpha groups do not straddle it; 64 inputs for
+  // groups of 192, 320, ... inputs
   const int tile_rows = (rpg % 4 == 0 || rpg <= 2) ? 4 : 2;
-  const int ctas_per_sm = tile_rows == 2 ? 2 : 1;
   const int tiles = (K / 32 + tile_rows - 1) / tile_rows;
   // columns per CTA: a multiple of 256 chosen so the grid is close to a
-  // multiple of the resident CTA slots while the table build stays amortised.
-  const int slots = sm_count() * ctas_per_sm;
+  // multiple of the SM count while the table build stays amortised.
+  const int slots = sm_count();
   int best_cols = 256;
   double best_score = -1.0;
   const int max_chunks = (M + 255) / 256;
@@ -476,7 +445,7 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW, cons
     const long ctas = (long)((max_chunks + chunk256 - 1) / chunk256) * tiles;
     const long waves = (ctas + slots - 1) / slots;
     // efficiency = useful lookups / (lookups + table build), times wave balance
-    const double amort = (double)(chunk256 * 256) / (chunk256 * 256 + 700.0);
+    const double amort = (double)(chunk256 * 256) / (chunk256 * 256 + 2000.0);
     const double balance = (double)ctas / (double)(waves * slots);
     const double score = amort * balance;
     if (score > best_score) { best_score = score; best_cols = chunk256 * 256; }
@@ -491,13 +460,14 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW, cons
   a.x = reinterpret_cast<const __half*>(x_half);
   a.out = reinterpret_cast<__half*>(out_half);
   a.ws = reinterpret_cast<float*>(workspace);
-  a.counter = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
-                                          (hq_lutgemm_workspace_bytes(M) - 256));
+  a.counters = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
+                                           (hq_lutgemm_workspace_bytes(M) - 256));
   a.M = M;
   a.K = K;
   a.rows_per_group = rpg;
   a.cols_per_cta = best_cols;
   a.nb_total = nb;
+  a.per_range = mblocks <= kCounterWords ? 1 : 0;
   if (tile_rows == 4) {
     if (rpg % 4 == 0) return launch_planes<4, 4>(a);
     if (rpg == 2) return launch_planes<4, 2>(a);
@@ -519,7 +489,6 @@ namespace {
 // that loads the library holds these 257 KiB until the process exits.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[HQ_LUTGEMM_NOALLOC_MAX_M * 4 + 256];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_noalloc_mu;
 void* g_noalloc_ptr[kMaxDevices];  // device address of the array, per device; null = not set up
 
@@ -550,7 +519,9 @@ extern "C" int hq_lutgemm_nqmv_noalloc(void* out_half, const void* x_half, const
                                        int K, int nb, int group_size, hq_stream_t stream) {
   using namespace hq;
   if (M > HQ_LUTGEMM_NOALLOC_MAX_M) return HQ_ERR_TOO_LARGE;
-  if (M <= 0) return HQ_ERR_BAD_SHAPE;
+  // every argument rule is checked before the shared array is looked up or touched
+  const int cst = check_args(out_half, x_half, bW, alpha_half, q_bias_half, M, K, nb, group_size);
+  if (cst != HQ_OK) return cst;
   void* ws = nullptr;
   const int st = noalloc_scratch(&ws);
   if (st != HQ_OK) return st;

@@ -7,17 +7,22 @@
 //   dequant : out[e] = half_rn(lut16[code] * absmax[e/blocksize])   (bit exact)
 //   gemv    : out[n] = half_rn(sum_k A[k] * lut16[code[n][k]] * absmax[...])
 //
-// GEMV design (HBM-bound, 0.5 B of codes + 1/16 B of absmax per weight):
-//  * one persistent CTA of 1024 threads per SM; rows are dealt round-robin to
-//    CTAs and, inside a CTA, to groups of S warps; warp q of a group owns the
-//    K slice [q*1024*C, (q+1)*1024*C) of every row of its group, a lane reads
-//    16 bytes (32 codes) per chunk, so a warp streams 512 contiguous bytes;
-//  * packed codes and their absmax are staged through shared memory with
-//    per-lane asynchronous copies (cp.async), kStages rows deep: 128 KiB of
-//    weights are in flight per SM without holding a single register, which is
-//    what it takes to cover HBM latency at full bandwidth; each lane reads back
-//    only the slots it filled itself, so no barrier guards the ring; the first
-//    kStages rows are requested before the lookup table is built;
+// GEMV design (HBM-bound, 0.5 B of codes + 1/16 B of absmax per weight; the
+// second wall is instruction issue, so the kernel is built around the number
+// of instructions per weight):
+//  * one persistent CTA per SM; rows are dealt round-robin to CTAs and, inside
+//    a CTA, to groups of S warps; warp q of a group owns the K slice
+//    [q*1024*C, (q+1)*1024*C) of every row of its group; a lane reads C
+//    16-byte chunks (32 codes each) per row, and the 32 lanes of a warp read
+//    512 contiguous bytes per load instruction;
+//  * packed codes and absmax go from global memory straight into registers
+//    (128-bit streaming loads that bypass L1), D rows ahead of their use: the
+//    D*C outstanding 16-byte loads per thread are what covers the HBM
+//    latency, and nothing is staged through shared memory, whose bandwidth the
+//    table lookups need; optionally one lane per warp also asks the L2 for the
+//    warp's slice of the row PF rows ahead (a bulk L2 prefetch: one
+//    instruction for C*512 bytes), so that the register loads find their
+//    lines in L2;
 //  * the lane's slice of the input vector never changes, so it lives in
 //    registers for the whole kernel;
 //  * one byte = two codes = one shared-memory lookup into a 256-entry half2
@@ -26,14 +31,16 @@
 //    first 128 bytes), so the 32 random lookups of a warp never conflict and
 //    the table offset (b << 8) | lane*4 is ONE byte-permute of the packed word
 //    and the lane offset - no shift, no mask;
-//  * products are summed in half2 over the 32 weights of a chunk (two
-//    accumulators of 8 fused multiply-adds), then scaled by the chunk's fp32
+//  * products are summed in half2 over the 32 weights of a chunk (four
+//    accumulators of 4 fused multiply-adds), then scaled by the chunk's fp32
 //    absmax in fp32;
-//  * per-lane partial sums of a row go to shared memory (into the unused second
-//    128 bytes of the table rows); after kRound rows the
-//    S warps of the group meet at a named barrier and each finishes some of
-//    the rows (sum over the slices, warp-shuffle tree, one fp16 store).
+//  * per-lane partial sums of a row go to shared memory; after D rows the S
+//    warps of the group meet at a named barrier and each finishes some of the
+//    rows (sum over the slices, warp-shuffle tree, one fp16 store).  With
+//    S == 1 a warp finishes its rows alone and there is no barrier.
 #include <algorithm>
+#include <cstdlib>
+#include <mutex>
 
 #include "hq_common.cuh"
 
@@ -41,12 +48,9 @@ namespace hq {
 namespace {
 
 constexpr int kThreads = 256;        // dequant kernel
-constexpr int kGemvThreads = 1024;   // GEMV: one persistent CTA per SM
-constexpr int kGemvWarps = kGemvThreads / 32;
-constexpr int kStageChunks = 8;      // 16-byte chunks in flight per lane (shared-memory ring)
-constexpr int kRound = 4;            // rows between two group barriers
+constexpr unsigned kDefaultPolls = 1u << 21;  // about a second of polling with back-off
 
-constexpr int kLutBytes = 256 * 256;  // table rows interleaved with the partial-sum slots
+constexpr int kLutBytes = 256 * 256;  // 256 table rows of 256 bytes (first 128: lane copies)
 // The table sits at the fixed shared-window address kLutImm, so that a lookup
 // address is the byte-permute {0, 0, byte value, lane*4} plus an immediate.
 constexpr int kLutImm = 2048;
@@ -62,29 +66,21 @@ __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool pred) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %2, 0;\n"
-      " @p cp.async.cg.shared.global [%0], [%1], 16;\n}\n" ::"r"(dst), "l"(src), "r"((int)pred)
-      : "memory");
+
+// Ask the L2 for `bytes` (a multiple of 16) starting at the 16-byte aligned
+// address p; no data reaches the SM.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, bool pred) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %2, 0;\n"
-      " @p cp.async.ca.shared.global [%0], [%1], 4;\n}\n" ::"r"(dst), "l"(src), "r"((int)pred)
-      : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+__device__ __forceinline__ void l2_prefetch_line(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 // sum of the 32 products of one 16-byte chunk against 16 half2 inputs
 __device__ __forceinline__ float chunk_dot(const uint4& codes, const uint4 (&xp)[4],
                                            uint32_t lane4) {
   const uint32_t w[4] = {codes.x, codes.y, codes.z, codes.w};
-  __half2 a0 = __float2half2_rn(0.f), a1 = a0;
+  __half2 a0 = __float2half2_rn(0.f), a1 = a0, a2 = a0, a3 = a0;
 #pragma unroll
   for (int i = 0; i < 4; i++) {
     const uint32_t xw[4] = {xp[i].x, xp[i].y, xp[i].z, xp[i].w};
@@ -99,10 +95,10 @@ __device__ __forceinline__ float chunk_dot(const uint4& codes, const uint4 (&xp)
     const uint32_t l3 = lds_u32_imm<kLutImm>(o3);
     a0 = __hfma2(u32_as_half2(l0), u32_as_half2(xw[0]), a0);
     a1 = __hfma2(u32_as_half2(l1), u32_as_half2(xw[1]), a1);
-    a0 = __hfma2(u32_as_half2(l2), u32_as_half2(xw[2]), a0);
-    a1 = __hfma2(u32_as_half2(l3), u32_as_half2(xw[3]), a1);
+    a2 = __hfma2(u32_as_half2(l2), u32_as_half2(xw[2]), a2);
+    a3 = __hfma2(u32_as_half2(l3), u32_as_half2(xw[3]), a3);
   }
-  const float2 f = __half22float2(__hadd2(a0, a1));
+  const float2 f = __half22float2(__hadd2(__hadd2(a0, a1), __hadd2(a2, a3)));
   return f.x + f.y;
 }
 
@@ -124,48 +120,66 @@ struct GemvParams {
   int low_first;
   unsigned long long w_step;   // bytes between two rows of one group
   unsigned int a_step;         // absmax entries between two rows of one group (ALIGNED only)
-  // fused gather (null when unused): every result is also stored into the
-  // gathered vector of each GPU of the node at element gather_offset + n
-  __half* const* peer_out;
-  uint32_t* const* peer_flags;  // flags array of each rank; this rank writes word `rank`
-  unsigned* sync_words;         // local: [0] CTAs finished, [1] launches completed
+  // Low-latency gather (null when unused).  Output: every result is stored as
+  // one 8-byte packet {fp16 value, epoch} into element gather_offset + n of the
+  // packet vector of EVERY GPU of the node (peer_ll[r], peer-mapped memory).
+  // Input: the vector may itself be given as packets (A_ll, element k at
+  // A_ll[k * a_stride]); a packet counts once its epoch equals the epoch of the
+  // latest completed gather, which sync_words[1] holds.
+  uint2* const* peer_ll;
+  const uint2* A_ll;
+  long long a_stride;
+  unsigned* sync_words;         // local: [0] CTAs finished, [1] epoch of the latest completed gather
   int world, rank;
   long long gather_offset;
-  // optional: before the input vector is read, wait (bounded) until every rank's
-  // flag has reached this rank's launch count, i.e. until the previous fused
-  // gather - which produced the input of this layer - has landed everywhere
-  const uint32_t* wait_flags;
+  unsigned max_polls;           // limit of every wait for a packet, in polls
   int early_fetch;  // weights may be fetched before the preceding kernel in the stream has finished
   int* status;
 };
 
-// store one result locally and, for the fused gather, into every peer's vector
-__device__ __forceinline__ void store_result(const GemvParams& p, __half* local, long long n,
-                                             float v) {
-  const __half h = __float2half_rn(v);
-  if (p.peer_out == nullptr) *local = h;
-  else p.peer_out[p.rank][p.gather_offset + n] = h;  // own copy first; peers get it in bulk
+__device__ __forceinline__ uint2 ld_packet(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_packet(uint2* p, uint32_t value, uint32_t epoch) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(value), "r"(epoch)
+               : "memory");
+}
+// Waits (bounded) until the packet carries `epoch`; returns its value.  On
+// expiry *status becomes 1 and the stale value is returned: the kernel still
+// terminates, the host sees the status.
+__device__ __forceinline__ uint32_t wait_packet(const uint2* p, uint32_t epoch, unsigned max_polls,
+                                                int* status) {
+  uint2 v = ld_packet(p);
+  if (v.y == epoch) return v.x;
+  for (unsigned spin = 0; spin < max_polls; spin++) {
+    __nanosleep(20);
+    v = ld_packet(p);
+    if (v.y == epoch) return v.x;
+  }
+  if (status != nullptr) atomicExch(status, 1);
+  return v.x;
 }
 
-// C = chunks (32 codes) per lane per row; S warps share a row (ST > 0: compile
-// time, ST == 0: run time), G groups per CTA.  ALIGNED: every row starts on an
-// absmax block boundary and blocks are a power of two, so the absmax pointer
-// of a lane advances by a constant.  Every instruction of this kernel is
-// executed by 32 warps per SM, so per-thread setup is kept to a minimum:
-// nothing is divided on the device.
-template <int C, int ST, bool ALIGNED>
-__global__ void __launch_bounds__(kGemvThreads, 1)
+// C = chunks (32 codes) per lane per row; D = rows in flight per lane; S warps
+// share a row (ST > 0: compile time, ST == 0: run time), G groups per CTA;
+// PF = distance (rows) of the L2 prefetch, 0 = none.  ALIGNED: every row
+// starts on an absmax block boundary and blocks are a power of two, so the
+// absmax pointer of a lane advances by a constant.  Nothing is divided on the
+// device in the ALIGNED kernels.
+template <int C, int D, int ST, bool ALIGNED, int THREADS, int PF>
+__global__ void __launch_bounds__(THREADS, 1)
 nf4_gemv_kernel(const GemvParams p) {
-  constexpr int kStages = kStageChunks / C;  // rows in flight per lane
+  constexpr int W = THREADS / 32;
   extern __shared__ __align__(16) unsigned char dsm_raw[];
-  // [pad up to shared address kLutImm] table rows (256 x 256 B: lane copies |
-  // partial-sum slot) | [kStages][C][1024] uint4 | [kStages][C][1024] float
-  if (smem_u32(dsm_raw) > (uint32_t)kLutImm) return;  // never on sm_100 (1 KiB reserved)
+  // [pad up to shared address kLutImm] table rows (256 x 256 B) |
+  // partial sums [2][W * D][32] float
   // Programmatic dependent launch: let the next kernel of the stream start its
   // own prologue as soon as this grid is resident, and do not touch global
   // memory that earlier work may still be writing before the wait below.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (!p.early_fetch) asm volatile("griddepcontrol.wait;" ::: "memory");
+  pdl_launch_dependents();
+  if (!p.early_fetch) pdl_wait();
   unsigned char* dsm = dsm_raw + (kLutImm - smem_u32(dsm_raw));
   const int S = ST > 0 ? ST : p.S;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -177,10 +191,8 @@ nf4_gemv_kernel(const GemvParams p) {
   const int row_stride = gridDim.x * G;
   const int my_rows = g < G ? p.rows_base + (row_first < p.rows_rem ? 1 : 0) : 0;
 
-  // this lane's chunk columns; a lane beyond the row end copies nothing and
-  // sees zero scales in its (zero-filled) ring slots
-  const uint32_t ring_w0 = smem_u32(dsm + kLutBytes) + tid * 16;
-  const uint32_t ring_s0 = smem_u32(dsm + kLutBytes + kStageChunks * kGemvThreads * 16) + tid * 4;
+  // this lane's chunk columns; a lane beyond the row end loads nothing and
+  // keeps zero codes, scales and inputs
   const unsigned char* wp[C];
   const float* ap[C];
   bool live[C];
@@ -193,41 +205,62 @@ nf4_gemv_kernel(const GemvParams p) {
     wp[i] = p.B + (size_t)row_first * ((size_t)p.nchunks * 16) + (size_t)cc * 16;
     ci[i] = (uint32_t)row_first * (uint32_t)p.nchunks + (uint32_t)cc;
     ap[i] = p.absmax + (ALIGNED ? (ci[i] >> p.cpb_shift) : 0u);
-    if (!live[i]) {
-#pragma unroll
-      for (int st = 0; st < kStages; st++) {
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(
-                         ring_w0 + (uint32_t)((st * C + i) * kGemvThreads * 16)), "r"(0));
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(
-                         ring_s0 + (uint32_t)((st * C + i) * kGemvThreads * 4)), "r"(0));
-      }
-    }
   }
-  int to_issue = my_rows;  // rows not yet requested
+  uint4 cw[D][C];
+  float cs[D][C];
 
-#define HQ_NF4_ISSUE(STAGE)                                                                     \
+  // request row (loaded rows so far) into stage STAGE
+#define HQ_NF4_LOAD(STAGE)                                                                      \
   {                                                                                             \
-    const bool ok = to_issue > 0;                                                               \
     _Pragma("unroll") for (int i = 0; i < C; i++) {                                             \
       const float* a = ap[i];                                                                   \
       if (!ALIGNED)                                                                             \
         a = p.absmax + (p.cpb_shift >= 0 ? (ci[i] >> p.cpb_shift) : (ci[i] / (uint32_t)p.cpb)); \
-      cp_async_16(ring_w0 + (uint32_t)(((STAGE)*C + i) * kGemvThreads * 16), wp[i],             \
-                  ok && live[i]);                                                               \
-      cp_async_4(ring_s0 + (uint32_t)(((STAGE)*C + i) * kGemvThreads * 4), a, ok && live[i]);   \
+      if (live[i]) {                                                                            \
+        cw[STAGE][i] = ldg_stream_u4(wp[i]);                                                    \
+        cs[STAGE][i] = __ldg(a);                                                                \
+      }                                                                                         \
       wp[i] += p.w_step;                                                                        \
       if (ALIGNED) ap[i] += p.a_step;                                                           \
       else ci[i] += (uint32_t)row_stride * (uint32_t)p.nchunks;                                 \
     }                                                                                           \
-    cp_async_commit();                                                                          \
-    to_issue--;                                                                                 \
   }
 #pragma unroll
-  for (int st = 0; st < kStages; st++) HQ_NF4_ISSUE(st)
+  for (int d = 0; d < D; d++) {
+#pragma unroll
+    for (int i = 0; i < C; i++) {
+      cw[d][i] = make_uint4(0, 0, 0, 0);
+      cs[d][i] = 0.f;
+    }
+    if (d < my_rows) HQ_NF4_LOAD(d)
+  }
+  // L2 prefetch of this warp's slice of the rows D .. PF-1 (the steady state
+  // then asks for row j + PF while row j is computed)
+  const unsigned char* pfw = nullptr;
+  const float* pfa = nullptr;
+  const uint32_t pf_bytes =
+      (uint32_t)max(0, min(C * 512, (p.nchunks - q * C * 32) * 16));  // warp slice inside the row
+  if (PF > 0) {
+    // lane 0 prefetches codes, lane 1 the absmax line of the slice
+    pfw = p.B + (size_t)row_first * ((size_t)p.nchunks * 16) + (size_t)(q * C * 32) * 16;
+    if (ALIGNED)
+      pfa = p.absmax + (((uint32_t)row_first * (uint32_t)p.nchunks + (uint32_t)(q * C * 32)) >>
+                        p.cpb_shift);
+    pfw += (size_t)D * p.w_step;
+    if (ALIGNED) pfa += (size_t)D * p.a_step;
+    if (pf_bytes > 0) {
+      for (int j = D; j < PF && j < my_rows; j++) {
+        if (lane == 0) l2_prefetch_bulk(pfw, pf_bytes);
+        if (ALIGNED && lane == 1) l2_prefetch_line(pfa);
+        pfw += p.w_step;
+        if (ALIGNED) pfa += p.a_step;
+      }
+    }
+  }
 
-  // ---- prologue (overlaps the copies above): byte table, input slice ----
-  {
-    const int entry = tid >> 2, quarter = tid & 3;  // four threads per 128-byte table row
+  // ---- prologue (overlaps the loads above): byte table, input slice ----
+  for (int e4 = tid; e4 < 256 * 4; e4 += THREADS) {
+    const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
     const int hi = entry >> 4, lo = entry & 15;
     const int first = p.low_first ? lo : hi, second = p.low_first ? hi : lo;
     const uint32_t u = half2_as_u32(__floats2half2_rn(p.lut16[first], p.lut16[second]));
@@ -238,140 +271,125 @@ nf4_gemv_kernel(const GemvParams p) {
   }
   // the input vector (and, without early_fetch, everything) is read only after
   // the preceding kernel has completed
-  if (p.early_fetch) asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (p.wait_flags != nullptr) {
-    if (tid < p.world) {
-      const unsigned want = *reinterpret_cast<volatile unsigned*>(p.sync_words + 1);
-      const volatile uint32_t* f = p.wait_flags + tid;
-      bool landed = false;
-      for (unsigned spin = 0; spin < (1u << 20); spin++) {
-        if ((int)(*f - want) >= 0) { landed = true; break; }
-        __nanosleep(32);
-      }
-      if (landed) __threadfence_system();
-      else if (p.status != nullptr) atomicExch(p.status, 1);
-    }
+  if (p.early_fetch) pdl_wait();
+  // epoch of the latest completed gather: the input packets carry it, the
+  // output packets of this launch carry the next one
+  const uint32_t epoch_in =
+      p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
+  uint2* my_peer = nullptr;  // lane r stores the packets that go to rank r
+  if (p.peer_ll != nullptr && lane < p.world) my_peer = p.peer_ll[lane] + p.gather_offset;
+  const uint4* xsrc = reinterpret_cast<const uint4*>(p.A);
+  if (p.A_ll != nullptr) {
+    // the whole input arrives as packets: every thread waits for its share and
+    // leaves plain fp16 in shared memory
+    __half* xs = reinterpret_cast<__half*>(dsm + kLutBytes + (size_t)2 * W * D * 32 * sizeof(float));
+    for (int k = tid; k < p.nchunks * 32; k += THREADS)
+      xs[k] = __ushort_as_half((unsigned short)wait_packet(p.A_ll + (size_t)k * p.a_stride,
+                                                           epoch_in, p.max_polls, p.status));
     __syncthreads();
+    xsrc = reinterpret_cast<const uint4*>(xs);
   }
   uint4 xr[C][4];
 #pragma unroll
   for (int i = 0; i < C; i++) {
     const int c = (q * C + i) * 32 + lane;
-    const uint4* xp = reinterpret_cast<const uint4*>(p.A) + 4 * (live[i] ? c : 0);
+    const uint4* xp = xsrc + 4 * (live[i] ? c : 0);
 #pragma unroll
-    for (int t = 0; t < 4; t++) xr[i][t] = p.wait_flags ? __ldcg(xp + t) : __ldg(xp + t);
+    for (int t = 0; t < 4; t++) {
+      xr[i][t] = p.A_ll != nullptr ? xp[t] : __ldg(xp + t);
+      if (!live[i]) xr[i][t] = make_uint4(0, 0, 0, 0);
+    }
   }
   __syncthreads();
 
   const uint32_t lane4 = lane * 4;
-  __half* outp = p.out + row_first;  // row j of this group is outp[j * row_stride]
-  // partial-sum slot s (32 floats) lives in the second half of table row s
-  float* const part_lane = reinterpret_cast<float*>(dsm + 128) + lane;  // slot s: part_lane[s*64]
-  const uint4* ring_w = reinterpret_cast<const uint4*>(dsm + kLutBytes) + tid;
-  const float* ring_s =
-      reinterpret_cast<const float*>(dsm + kLutBytes + kStageChunks * kGemvThreads * 16) + tid;
+  // row j of this group is output element n_out + j * row_stride: stored as fp16
+  // (lane 0) or as one packet per GPU of the node (lane r -> rank r)
+  long long n_out = row_first;
+  auto store_result = [&](long long n, float v) {
+    const __half h = __float2half_rn(v);
+    if (p.peer_ll == nullptr) {
+      if (lane == 0) p.out[n] = h;
+    } else if (my_peer != nullptr) {
+      st_packet(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
+    }
+  };
+  // partial sums: [parity][g][d][t][lane]
+  float* const part = reinterpret_cast<float*>(dsm + kLutBytes) + (g * S * D) * 32 + lane;
+  int parity = 0;
 
-  int rows_left = my_rows;
-  const int slot_g = g * kRound * S;        // slots of this group: [parity][g][d][t]
-  const int slot_flip = G * kRound * S;
-  int parity = 0;                           // used only when a super-round is one round
-  constexpr int kRoundsPerPass = kStages / kRound;
-
-  // one round = kRound rows out of compile-time stages RR*kRound .. +kRound-1
-#define HQ_NF4_ROUND(RR)                                                                       \
-  {                                                                                            \
-    const int rows_in_round = min(kRound, rows_left);                                          \
-    const int slot0 = slot_g + ((kRoundsPerPass > 1 ? ((RR)&1) : parity) ? slot_flip : 0);      \
-    _Pragma("unroll") for (int d = 0; d < kRound; d++) {                                       \
-      cp_async_wait<kStages - 1>();                                                            \
-      if (d < rows_in_round) {                                                                 \
-        float acc = 0.f;                                                                       \
-        _Pragma("unroll") for (int i = 0; i < C; i++) acc =                                    \
-            fmaf(chunk_dot(ring_w[(((RR)*kRound + d) * C + i) * kGemvThreads], xr[i], lane4),       \
-                 ring_s[(((RR)*kRound + d) * C + i) * kGemvThreads], acc);                      \
-        if (S > 1) {                                                                           \
-          part_lane[(slot0 + d * S + q) * 64] = acc;                                           \
-        } else {                                                                               \
-          acc = warp_sum(acc);                                                                 \
-          if (lane == 0) store_result(p, outp, outp - p.out, acc);                             \
-          outp += row_stride;                                                                  \
-        }                                                                                      \
-      }                                                                                        \
-      HQ_NF4_ISSUE((RR)*kRound + d)                                                            \
-    }                                                                                          \
-    if (S > 1) {                                                                               \
-      group_barrier(1 + g, S * 32);                                                            \
-      for (int d = q; d < rows_in_round; d += S) {                                             \
-        float v = 0.f;                                                                         \
-        if (ST > 0) {                                                                          \
-          _Pragma("unroll") for (int t = 0; t < (ST > 0 ? ST : 1); t++) v +=                   \
-              part_lane[(slot0 + d * S + t) * 64];                                             \
-        } else {                                                                               \
-          for (int t = 0; t < S; t++) v += part_lane[(slot0 + d * S + t) * 64];                \
-        }                                                                                      \
-        v = warp_sum(v);                                                                       \
-        if (lane == 0)                                                                         \
-          store_result(p, outp + (size_t)d * row_stride, (outp - p.out) + (long long)d * row_stride, v); \
-      }                                                                                        \
-      outp += (size_t)kRound * row_stride;                                                     \
-    }                                                                                          \
-    parity ^= 1;                                                                               \
-    rows_left -= kRound;                                                                       \
-  }
-
-  while (rows_left > 0) {
-    HQ_NF4_ROUND(0)
-    if (kRoundsPerPass > 1) {
-      if (rows_left <= 0) break;
-      HQ_NF4_ROUND(1)
+  for (int j0 = 0; j0 < my_rows; j0 += D) {
+    const int rows_in_round = min(D, my_rows - j0);
+    float* const part_r = part + (parity ? W * D * 32 : 0);
+#pragma unroll
+    for (int d = 0; d < D; d++) {
+      if (d < rows_in_round) {
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < C; i++) acc = fmaf(chunk_dot(cw[d][i], xr[i], lane4), cs[d][i], acc);
+        if (j0 + d + D < my_rows) HQ_NF4_LOAD(d)
+        if (PF > 0) {
+          if (j0 + d + PF < my_rows && pf_bytes > 0) {
+            if (lane == 0) l2_prefetch_bulk(pfw, pf_bytes);
+            if (ALIGNED && lane == 1) l2_prefetch_line(pfa);
+            pfw += p.w_step;
+            if (ALIGNED) pfa += p.a_step;
+          }
+        }
+        if (S > 1) {
+          part_r[(d * S + q) * 32] = acc;
+        } else {
+          store_result(n_out, warp_sum(acc));
+          n_out += row_stride;
+        }
+      }
+    }
+    if (S > 1) {
+      group_barrier(1 + g, S * 32);
+      for (int d = q; d < rows_in_round; d += S) {
+        float v = 0.f;
+        if (ST > 0) {
+#pragma unroll
+          for (int t = 0; t < (ST > 0 ? ST : 1); t++) v += part_r[(d * S + t) * 32];
+        } else {
+          for (int t = 0; t < S; t++) v += part_r[(d * S + t) * 32];
+        }
+        store_result(n_out + (long long)d * row_stride, warp_sum(v));
+      }
+      n_out += (long long)D * row_stride;
+      parity ^= 1;
     }
   }
-#undef HQ_NF4_ROUND
-  cp_async_wait<0>();
-  if (p.peer_out != nullptr) {
-    // Fused gather epilogue: every CTA has stored its results into this GPU's own
-    // copy of the gathered vector; the last CTA of the grid to finish copies the
-    // whole slice to every peer with 16-byte stores over NVLink, makes them
-    // visible system-wide and then tells every peer, by one flag word per
-    // (receiver, sender), that this launch's slice has landed.
-    __shared__ unsigned s_last_cta;
-    __threadfence();
+#undef HQ_NF4_LOAD
+  if (p.peer_ll != nullptr) {
+    // the last CTA to finish records that this gather round is complete on the
+    // sending side (the packets validate themselves on the receiving side)
     __syncthreads();
     if (tid == 0) {
       const unsigned prev = atomicAdd(p.sync_words, 1u);
-      s_last_cta = (prev == gridDim.x - 1) ? 1u : 0u;
-    }
-    __syncthreads();
-    if (s_last_cta) {
-      __threadfence();
-      const int n_slice = p.rows_base * (int)(gridDim.x * p.G) + p.rows_rem;  // rows of this rank
-      const __half* mine = p.peer_out[p.rank] + p.gather_offset;
-      const bool vec_ok = ((p.gather_offset | (long long)n_slice) & 7) == 0;
-      for (int r = 0; r < p.world; r++) {
-        if (r == p.rank) continue;
-        __half* dst = p.peer_out[r] + p.gather_offset;
-        if (vec_ok) {
-          for (int i = tid; i < n_slice / 8; i += kGemvThreads)
-            reinterpret_cast<uint4*>(dst)[i] = __ldcg(reinterpret_cast<const uint4*>(mine) + i);
-        } else {
-          for (int i = tid; i < n_slice; i += kGemvThreads)
-            reinterpret_cast<unsigned short*>(dst)[i] =
-                __ldcg(reinterpret_cast<const unsigned short*>(mine) + i);
-        }
-      }
-      __threadfence_system();
-      __syncthreads();
-      if (tid == 0) {
+      if (prev == gridDim.x - 1) {
         p.sync_words[0] = 0u;
-        const unsigned epoch = p.sync_words[1] + 1u;
-        p.sync_words[1] = epoch;
-        __threadfence_system();
-        for (int r = 0; r < p.world; r++)
-          *reinterpret_cast<volatile uint32_t*>(p.peer_flags[r] + p.rank) = epoch;
+        *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) = epoch_in + 1u;
       }
     }
   }
-#undef HQ_NF4_ISSUE
+}
+
+// Plain fp16 copy of a packet vector: thread i waits (bounded) until packet i
+// carries the epoch of the latest completed gather (sync_words[1]; no check
+// when sync_words is null) and stores its value.
+__global__ void __launch_bounds__(256)
+ll_unpack_kernel(const uint2* __restrict__ ll, long long n, __half* __restrict__ out,
+                 const unsigned* sync_words, unsigned max_polls, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const bool check = sync_words != nullptr;
+  const uint32_t epoch = check ? *reinterpret_cast<const volatile unsigned*>(sync_words + 1) : 0u;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint32_t v = check ? wait_packet(ll + i, epoch, max_polls, status) : ld_packet(ll + i).x;
+    out[i] = __ushort_as_half((unsigned short)v);
+  }
 }
 
 // One thread: 4 bytes of codes (8 elements) -> 16 bytes of fp16.
@@ -405,13 +423,13 @@ nf4_dequant_kernel(const uint8_t* __restrict__ B, const float* __restrict__ absm
 // One warp: lane r waits (bounded) until rank r's flag has reached this rank's
 // own launch count, i.e. until rank r's slice of the latest gather has landed.
 __global__ void gather_wait_kernel(const uint32_t* flags, const unsigned* sync_words, int world,
-                                   int* status) {
+                                   unsigned max_polls, int* status) {
   const int r = threadIdx.x;
   if (r >= world) return;
   const unsigned want = sync_words[1];
   const volatile uint32_t* f = flags + r;
   bool ok = false;
-  for (unsigned spin = 0; spin < (1u << 22); spin++) {
+  for (unsigned spin = 0; spin < max_polls; spin++) {
     // flags only grow; "reached" is tested modulo 2^32
     if ((int)(*f - want) >= 0) { ok = true; break; }
     __nanosleep(64);
@@ -429,7 +447,7 @@ constexpr int kPublishThreads = 1024;
 __global__ void __launch_bounds__(kPublishThreads, 1)
 gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
                       uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
-                      int* status) {
+                      unsigned max_polls, int* status) {
   const int tid = threadIdx.x;
   const int r = blockIdx.x;
   // Programmatic dependent launch: these CTAs may become resident while the kernel
@@ -458,7 +476,7 @@ gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
     *reinterpret_cast<volatile uint32_t*>(peer_flags[r] + rank) = epoch;
     const volatile uint32_t* f = peer_flags[rank] + r;
     bool landed = false;
-    for (unsigned spin = 0; spin < (1u << 22); spin++) {
+    for (unsigned spin = 0; spin < max_polls; spin++) {
       if ((int)(*f - epoch) >= 0) { landed = true; break; }
       __nanosleep(32);
     }
@@ -477,27 +495,160 @@ gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
 }  // namespace
 }  // namespace hq
 
+namespace hq {
+namespace {
+
+template <int C, int D, int ST, bool AL, int THREADS, int PF>
+int launch_gemv(GemvParams& prm, int N, cudaStream_t st) {
+  constexpr int W = THREADS / 32;
+  const int S = prm.S;
+  int G = W / S;
+  if (S > 1 && G > 15) G = 15;  // named barriers 1..15
+  const int grid = std::min(sm_count(), (N + G - 1) / G);
+  prm.G = G;
+  prm.rows_base = N / (grid * G);
+  prm.rows_rem = N % (grid * G);
+  prm.w_step = (unsigned long long)grid * G * prm.nchunks * 16ull;
+  prm.a_step = AL ? (unsigned)(((unsigned long long)grid * G * prm.nchunks) >> prm.cpb_shift) : 0u;
+  // room for the pad that brings the table to shared address kLutImm wherever the
+  // dynamic region starts (at or below kLutImm)
+  size_t smem = (size_t)kLutImm + kLutBytes + (size_t)2 * W * D * 32 * sizeof(float);
+  if (prm.A_ll != nullptr) smem += (size_t)prm.nchunks * 32 * sizeof(__half);  // unpacked input
+  if (smem > 227 * 1024) return HQ_ERR_TOO_LARGE;
+  constexpr auto kern = nf4_gemv_kernel<C, D, ST, AL, THREADS, PF>;
+  cudaError_t e = ensure_dynamic_smem<kern>(smem);
+  if (e != cudaSuccess) return cuda_status(e);
+  return cuda_status(launch_pdl(kern, dim3(grid), dim3(THREADS), smem, st, prm));
+}
+
+}  // namespace
+}  // namespace hq
+
+// What the low-latency gather adds to a GEMV call (all null / zero without it).
+struct LlArgs {
+  const void* A_ll = nullptr;
+  long long a_stride = 1;
+  void* const* peer_ll = nullptr;
+  long long gather_offset = 0;
+  unsigned* sync_words = nullptr;
+  int world = 1, rank = 0;
+  unsigned max_polls = 0;
+  int* status = nullptr;
+};
+
+static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absmax,
+                         const float* lut16, void* out_half, int N, int K, int blocksize, int flags,
+                         const LlArgs& ll, hq_stream_t stream) {
+  using namespace hq;
+  if ((!A_half && !ll.A_ll) || !B || !absmax || !lut16 || (!out_half && !ll.peer_ll))
+    return HQ_ERR_NULL_POINTER;
+  if (N <= 0 || K <= 0 || K % 32 != 0 || blocksize <= 0 || blocksize % 32 != 0)
+    return HQ_ERR_BAD_SHAPE;
+  if (!aligned16(B) || (A_half && !aligned16(A_half)) || (ll.A_ll && !aligned8(ll.A_ll)))
+    return HQ_ERR_MISALIGNED;
+  if ((uint64_t)N * (uint64_t)(K / 32) > 0xffffffffull) return HQ_ERR_TOO_LARGE;
+  // the kernels address their table at a fixed shared-memory address, which the
+  // system-reserved part of the window (1 KiB on sm_100) must not overlap
+  if (reserved_smem_per_block() > kLutImm) return HQ_ERR_UNSUPPORTED;
+  const int nchunks = K / 32;
+  const int cols = (nchunks + 31) / 32;  // 1024-input slices per row
+  if (cols > 64) return HQ_ERR_TOO_LARGE;  // K > 65536
+  const int cpb = blocksize / 32;
+  int shift = -1;
+  if ((cpb & (cpb - 1)) == 0) {
+    shift = 0;
+    while ((1 << shift) < cpb) shift++;
+  }
+  const bool aligned = shift >= 0 && nchunks % cpb == 0;
+  GemvParams prm;
+  prm.A = reinterpret_cast<const __half*>(A_half);
+  prm.B = B;
+  prm.absmax = absmax;
+  prm.lut16 = lut16;
+  prm.out = reinterpret_cast<__half*>(out_half);
+  prm.nchunks = nchunks;
+  prm.cpb_shift = shift;
+  prm.cpb = cpb;
+  prm.low_first = (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0;
+  prm.peer_ll = reinterpret_cast<uint2* const*>(ll.peer_ll);
+  prm.A_ll = reinterpret_cast<const uint2*>(ll.A_ll);
+  prm.a_stride = ll.a_stride;
+  prm.sync_words = ll.sync_words;
+  prm.world = ll.world;
+  prm.rank = ll.rank;
+  prm.gather_offset = ll.gather_offset;
+  prm.max_polls = ll.max_polls ? ll.max_polls : kDefaultPolls;
+  prm.status = ll.status;
+  prm.early_fetch = (flags & HQ_NF4_WEIGHTS_RESIDENT) ? 1 : 0;
+  cudaStream_t st = (cudaStream_t)stream;
+#ifdef HQ_NF4_SWEEP
+#define HQ_NF4_SWEEP_LIST                                                                       \
+  V(0, 1, 4, 1024, 0) V(1, 1, 4, 1024, 8) V(2, 1, 6, 768, 0) V(3, 2, 4, 512, 0) V(4, 2, 6, 512, 0) \
+  V(5, 2, 4, 512, 8) V(6, 4, 2, 512, 8) V(7, 4, 3, 512, 0) V(8, 1, 4, 768, 8) V(9, 2, 3, 512, 8)  \
+  V(10, 1, 3, 1024, 8) V(11, 2, 5, 512, 0) V(12, 2, 2, 512, 8) V(13, 1, 8, 512, 0)                \
+  V(14, 1, 8, 768, 0) V(15, 2, 4, 512, 16) V(16, 1, 6, 768, 12) V(17, 1, 4, 1024, 16)
+  if (cols == 4 && aligned) {
+    const char* env = getenv("HQ_NF4_VARIANT");
+    const int v = env ? atoi(env) : -1;
+    switch (v) {
+#define V(ID, CC, DD, TT, PP) case ID: prm.S = 4 / CC; return launch_gemv<CC, DD, 4 / CC, true, TT, PP>(prm, N, st);
+      HQ_NF4_SWEEP_LIST
+#undef V
+      default: break;
+    }
+  }
+#endif
+  // Chunks per lane C and warps per row S = cols / C.  512 threads with up to
+  // 128 registers each hold C = 2 chunks of the input vector and D = 4 rows of
+  // packed weights in flight per lane.
+  if (aligned && cols == 4) { prm.S = 2; return launch_gemv<2, 4, 2, true, 512, 0>(prm, N, st); }
+  int C = cols <= 1 ? 1 : (cols <= 32 ? 2 : 4);
+  prm.S = (cols + C - 1) / C;
+  if (C == 1) return aligned ? launch_gemv<1, 4, 1, true, 512, 0>(prm, N, st)
+                             : launch_gemv<1, 4, 1, false, 512, 0>(prm, N, st);
+  if (C == 2) return aligned ? launch_gemv<2, 4, 0, true, 512, 0>(prm, N, st)
+                             : launch_gemv<2, 4, 0, false, 512, 0>(prm, N, st);
+  return aligned ? launch_gemv<4, 2, 0, true, 512, 0>(prm, N, st)
+                 : launch_gemv<4, 2, 0, false, 512, 0>(prm, N, st);
+}
+
 extern "C" {
 
 int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
                       uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
-                      int* status, hq_stream_t stream) {
+                      unsigned max_polls, int* status, hq_stream_t stream) {
   using namespace hq;
   if (!peer_out_half || !peer_flags || !sync_words) return HQ_ERR_NULL_POINTER;
   if (world < 1 || world > 32 || rank < 0 || rank >= world || n_slice <= 0) return HQ_ERR_BAD_SHAPE;
   return cuda_status(launch_pdl(gather_publish_kernel, dim3(world), dim3(kPublishThreads), 0,
                                 (cudaStream_t)stream,
                                 reinterpret_cast<__half* const*>(peer_out_half), offset, n_slice,
-                                peer_flags, sync_words, world, rank, status));
+                                peer_flags, sync_words, world, rank,
+                                max_polls ? max_polls : kDefaultPolls, status));
 }
 
-int hq_gather_wait(const uint32_t* local_flags, const unsigned* sync_words, int world, int* status,
-                   hq_stream_t stream) {
+int hq_gather_wait(const uint32_t* local_flags, const unsigned* sync_words, int world,
+                   unsigned max_polls, int* status, hq_stream_t stream) {
   using namespace hq;
   if (!local_flags || !sync_words) return HQ_ERR_NULL_POINTER;
   if (world < 1 || world > 32) return HQ_ERR_BAD_SHAPE;
-  gather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(local_flags, sync_words, world, status);
+  gather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(
+      local_flags, sync_words, world, max_polls ? max_polls : kDefaultPolls, status);
   return launch_status();
+}
+
+int hq_ll_unpack(const hq_ll_packet* ll, long long n, void* out_half, const unsigned* sync_words,
+                 unsigned max_polls, int* status, hq_stream_t stream) {
+  using namespace hq;
+  if (!ll || !out_half) return HQ_ERR_NULL_POINTER;
+  if (n <= 0) return HQ_ERR_BAD_SHAPE;
+  if (!aligned8(ll)) return HQ_ERR_MISALIGNED;
+  const long long want = (n + 255) / 256;
+  const int grid = (int)std::min<long long>(want, 4LL * sm_count());
+  return cuda_status(launch_pdl(ll_unpack_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream,
+                                reinterpret_cast<const uint2*>(ll), n,
+                                reinterpret_cast<__half*>(out_half), sync_words,
+                                max_polls ? max_polls : kDefaultPolls, status));
 }
 
 int hq_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut16, void* out_half,
@@ -517,113 +668,33 @@ int hq_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut16
   return launch_status();
 }
 
-static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absmax,
-                         const float* lut16, void* out_half, int N, int K, int blocksize, int flags,
-                         void* const* peer_out, uint32_t* const* peer_flags, unsigned* sync_words,
-                         int world, int rank, long long gather_offset, const uint32_t* wait_flags,
-                         int* status, hq_stream_t stream) {
-  using namespace hq;
-  if (!A_half || !B || !absmax || !lut16 || (!out_half && !peer_out)) return HQ_ERR_NULL_POINTER;
-  if (N <= 0 || K <= 0 || K % 32 != 0 || blocksize <= 0 || blocksize % 32 != 0 ||
-      false)
-    return HQ_ERR_BAD_SHAPE;
-  if (!aligned16(B) || !aligned16(A_half)) return HQ_ERR_MISALIGNED;
-  if ((uint64_t)N * (uint64_t)(K / 32) > 0xffffffffull) return HQ_ERR_TOO_LARGE;
-  const int nchunks = K / 32;
-  // warps per row S and chunks per lane C: C = 1 unless that needs more than 15
-  // named barriers (S = 2) or more warps than a CTA has.
-  const int cols = (nchunks + 31) / 32;  // 1024-input slices per row
-  int C = 1;
-  if (cols == 2 || cols > kGemvWarps) C = 2;
-  const int S = (cols + C - 1) / C;
-  if (S > kGemvWarps) return HQ_ERR_TOO_LARGE;  // K > 65536
-  int G = kGemvWarps / S;
-  if (S > 1 && G > 15) G = 15;
-  // room for the pad that brings the table to shared address kLutImm wherever the
-  // dynamic region starts (at or below kLutImm)
-  const size_t smem = (size_t)kLutImm + kLutBytes + (size_t)kStageChunks * kGemvThreads * 20;
-  const int sms = sm_count();
-  const int grid = std::min(sms, (N + G - 1) / G);
-  const int cpb = blocksize / 32;
-  int shift = -1;
-  if ((cpb & (cpb - 1)) == 0) {
-    shift = 0;
-    while ((1 << shift) < cpb) shift++;
-  }
-  const bool aligned = shift >= 0 && nchunks % cpb == 0;
-  GemvParams prm;
-  prm.A = reinterpret_cast<const __half*>(A_half);
-  prm.B = B;
-  prm.absmax = absmax;
-  prm.lut16 = lut16;
-  prm.out = reinterpret_cast<__half*>(out_half);
-  prm.nchunks = nchunks;
-  prm.S = S;
-  prm.G = G;
-  prm.rows_base = N / (grid * G);
-  prm.rows_rem = N % (grid * G);
-  prm.cpb_shift = shift;
-  prm.cpb = cpb;
-  prm.low_first = (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0;
-  prm.w_step = (unsigned long long)grid * G * nchunks * 16ull;
-  prm.a_step = aligned ? (unsigned)(((unsigned long long)grid * G * nchunks) >> shift) : 0u;
-  prm.peer_out = reinterpret_cast<__half* const*>(peer_out);
-  prm.peer_flags = peer_flags;
-  prm.sync_words = sync_words;
-  prm.world = world;
-  prm.rank = rank;
-  prm.gather_offset = gather_offset;
-  prm.wait_flags = wait_flags;
-  prm.status = status;
-  prm.early_fetch = (flags & HQ_NF4_WEIGHTS_RESIDENT) ? 1 : 0;
-  cudaStream_t st = (cudaStream_t)stream;
-#define HQ_NF4_LAUNCH(CC, SS, AL)                                                               \
-  {                                                                                             \
-    auto kern = nf4_gemv_kernel<CC, SS, AL>;                                                    \
-    cudaError_t e =                                                                             \
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    if (e != cudaSuccess) return cuda_status(e);                                                \
-    cudaLaunchConfig_t cfg = {};                                                                \
-    cfg.gridDim = dim3(grid);                                                                   \
-    cfg.blockDim = dim3(kGemvThreads);                                                          \
-    cfg.dynamicSmemBytes = smem;                                                                \
-    cfg.stream = st;                                                                            \
-    cudaLaunchAttribute attr[1];                                                                \
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                            \
-    attr[0].val.programmaticStreamSerializationAllowed = 1;                                     \
-    cfg.attrs = attr;                                                                           \
-    cfg.numAttrs = 1;                                                                           \
-    e = cudaLaunchKernelEx(&cfg, kern, prm);                                                    \
-    if (e != cudaSuccess) return cuda_status(e);                                                \
-  }
-  if (C == 1 && S == 4 && aligned) HQ_NF4_LAUNCH(1, 4, true)
-  else if (C == 1 && S == 8 && aligned) HQ_NF4_LAUNCH(1, 8, true)
-  else if (C == 1 && S == 1 && aligned) HQ_NF4_LAUNCH(1, 1, true)
-  else if (C == 1 && aligned) HQ_NF4_LAUNCH(1, 0, true)
-  else if (C == 1) HQ_NF4_LAUNCH(1, 0, false)
-  else if (S == 2 && aligned) HQ_NF4_LAUNCH(2, 2, true)
-  else if (aligned) HQ_NF4_LAUNCH(2, 0, true)
-  else HQ_NF4_LAUNCH(2, 0, false)
-#undef HQ_NF4_LAUNCH
-  return launch_status();
-}
-
 int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, const float* lut16,
                     void* out_half, int N, int K, int blocksize, int flags, hq_stream_t stream) {
-  return nf4_gemv_impl(A_half, B, absmax, lut16, out_half, N, K, blocksize, flags, nullptr, nullptr,
-                       nullptr, 1, 0, 0, nullptr, nullptr, stream);
+  return nf4_gemv_impl(A_half, B, absmax, lut16, out_half, N, K, blocksize, flags, LlArgs(),
+                       stream);
 }
 
-int hq_nf4_gemv_f16_gather(const void* A_half, const uint8_t* B, const float* absmax,
-                           const float* lut16, int N, int K, int blocksize, int flags,
-                           void* const* peer_out_half, long long gather_offset,
-                           uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
-                           const uint32_t* wait_flags, int* status, hq_stream_t stream) {
-  if (!peer_out_half || !peer_flags || !sync_words) return HQ_ERR_NULL_POINTER;
-  if (world < 1 || world > 32 || rank < 0 || rank >= world) return HQ_ERR_BAD_SHAPE;
-  return nf4_gemv_impl(A_half, B, absmax, lut16, nullptr, N, K, blocksize, flags, peer_out_half,
-                       peer_flags, sync_words, world, rank, gather_offset, wait_flags, status,
-                       stream);
+int hq_nf4_gemv_f16_ll(const void* A_half, const hq_ll_packet* A_ll, long long a_stride,
+                       const uint8_t* B, const float* absmax, const float* lut16, void* out_half,
+                       int N, int K, int blocksize, int flags, hq_ll_packet* const* peer_ll,
+                       long long gather_offset, unsigned* sync_words, int world, int rank,
+                       unsigned max_polls, int* status, hq_stream_t stream) {
+  if ((A_half != nullptr) == (A_ll != nullptr)) return HQ_ERR_NULL_POINTER;  // exactly one input
+  if ((out_half != nullptr) == (peer_ll != nullptr)) return HQ_ERR_NULL_POINTER;  // one output form
+  if (!sync_words) return HQ_ERR_NULL_POINTER;
+  if (world < 1 || world > 32 || rank < 0 || rank >= world || a_stride < 1)
+    return HQ_ERR_BAD_SHAPE;
+  LlArgs ll;
+  ll.A_ll = A_ll;
+  ll.a_stride = a_stride;
+  ll.peer_ll = reinterpret_cast<void* const*>(peer_ll);
+  ll.gather_offset = gather_offset;
+  ll.sync_words = sync_words;
+  ll.world = world;
+  ll.rank = rank;
+  ll.max_polls = max_polls;
+  ll.status = status;
+  return nf4_gemv_impl(A_half, B, absmax, lut16, out_half, N, K, blocksize, flags, ll, stream);
 }
 
 }  // extern "C"

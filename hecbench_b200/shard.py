@@ -84,82 +84,148 @@ def sharded_apply(local_fn: Callable[[], torch.Tensor], shard: FeatureShard, gro
     return gather_features(local_fn(), shard, group)
 
 
-class PeerGather:
-    """Buffers for the fused GEMV + all-gather: every rank's gathered vectors and
-    flag words live in peer-mapped ("symmetric") device memory, so the kernel of
-    one GPU stores its output slice directly into the vectors of all GPUs over
-    NVLink and announces it with one flag word per (receiver, sender).
+def _symmetric(nbytes: int, device, group):
+    """Zeroed peer-mapped buffer of nbytes on every rank; returns (tensor, [base pointers])."""
+    import torch.distributed._symmetric_memory as symm_mem
+    buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+    buf.zero_()
+    grp = group if group is not None else dist.group.WORLD
+    handle = symm_mem.rendezvous(buf, grp.group_name)
+    ptrs = [int(p) for p in handle.buffer_ptrs]
+    torch.cuda.synchronize(device)
+    dist.barrier(group=grp)
+    return buf, handle, ptrs
 
-    Layout of each rank's symmetric buffer: [256 bytes of flags][slots] with
-    slot = world * n_local fp16 values.  `sync` is a rank-local pair of words
-    (CTA counter, launch count) and `status` a rank-local error word.
+
+class PacketGather:
+    """Low-latency gather for the batch-1 path (hq_nf4_gemv_f16_ll): every rank's
+    gathered vectors live in peer-mapped ("symmetric") device memory as arrays of
+    8-byte packets {fp16 value, epoch}.  The GEMV of one GPU stores each finished
+    row straight into the packet vectors of all GPUs over NVLink, and the next
+    layer's GEMV reads its input from the packets, waiting (bounded) for each
+    until it carries the epoch of the round - no fence, no flag round trip, no
+    follow-up kernel.
+
+    `slots` packet vectors of world * n_local packets each; a chain of layers
+    must alternate between at least two of them, because a vector may be
+    rewritten as soon as the following round is complete on this rank.  `sync`
+    is the rank-local pair (CTA counter, epoch of the latest completed round),
+    `status` a rank-local word that becomes 1 if a bounded wait ran out.
     """
 
-    def __init__(self, shard: FeatureShard, slots: int, device, group=None):
-        import torch.distributed._symmetric_memory as symm_mem
-        self.shard, self.slots = shard, slots
+    def __init__(self, shard: FeatureShard, slots: int, device, group=None, max_polls: int = 0):
+        if slots < 2:
+            raise ValueError("a chain of gathers needs at least two packet vectors to alternate")
+        self.shard, self.slots, self.max_polls = shard, slots, max_polls
         self.slot_elems = shard.world * shard.n_local
-        nbytes = 256 + slots * self.slot_elems * 2
-        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
-        self.buf.zero_()
-        grp = group if group is not None else dist.group.WORLD
-        self.handle = symm_mem.rendezvous(self.buf, grp.group_name)
-        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.buf, self.handle, ptrs = _symmetric(slots * self.slot_elems * 8, device, group)
+        self._ptrs = ptrs
+        # device arrays of pointers to every rank's copy of slot i
+        self.peer_ll = [torch.tensor([p + i * self.slot_elems * 8 for p in ptrs], dtype=torch.int64,
+                                     device=device) for i in range(slots)]
+        self.sync = torch.zeros(2, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+
+    def packets(self, i: int) -> torch.Tensor:
+        """This rank's copy of packet vector i as int32 [n_total][2] (value, epoch)."""
+        off = i * self.slot_elems * 8
+        return self.buf[off:off + self.slot_elems * 8].view(torch.int32).view(-1, 2)
+
+    def gemv_nf4(self, i: int, A, B, absmax, lut16, K: int, blocksize: int = 64,
+                 nibble_order: int = 0, weights_resident: bool = False, a_slot=None,
+                 a_stride: int = 1, a_first: int = 0) -> None:
+        """NF4 GEMV of this rank's rows; results go as packets into vector i of
+        every rank.  Input: the plain fp16 tensor A, or (a_slot given) elements
+        a_first, a_first + a_stride, ... of this rank's copy of packet vector
+        a_slot - the gathered output of an earlier layer."""
+        from ._lib import check, load_library
+        lib = load_library()
+        sh = self.shard
+        flags = nibble_order | (2 if weights_resident else 0)
+        a_ll = 0
+        if a_slot is not None:
+            a_ll = self.buf.data_ptr() + (a_slot * self.slot_elems + a_first) * 8
+        check("hq_nf4_gemv_f16_ll", lib.hq_nf4_gemv_f16_ll(
+            0 if a_slot is not None else A.data_ptr(), a_ll, a_stride, B.data_ptr(),
+            absmax.data_ptr(), lut16.data_ptr(), 0, sh.n_local, K, blocksize, flags,
+            self.peer_ll[i].data_ptr(), sh.rank * sh.n_local, self.sync.data_ptr(), sh.world,
+            sh.rank, self.max_polls, self.status.data_ptr(),
+            torch.cuda.current_stream().cuda_stream))
+
+    def unpack(self, i: int, out: torch.Tensor | None = None, check_epoch: bool = True):
+        """Plain fp16 copy of gathered vector i; with check_epoch it waits (bounded)
+        until every packet carries the epoch of the latest completed round."""
+        from ._lib import check, load_library
+        if out is None:
+            out = torch.empty(self.slot_elems, dtype=torch.float16, device=self.buf.device)
+        check("hq_ll_unpack", load_library().hq_ll_unpack(
+            self.buf.data_ptr() + i * self.slot_elems * 8, self.slot_elems, out.data_ptr(),
+            self.sync.data_ptr() if check_epoch else 0, self.max_polls, self.status.data_ptr(),
+            torch.cuda.current_stream().cuda_stream))
+        return out
+
+
+class PeerGather:
+    """Copy + flag gather for larger slices and for any kernel of the family
+    (hq_gather_publish): an ordinary launch writes this rank's slice into its own
+    copy of the gathered buffer, then one small kernel copies the slice to every
+    peer with 16-byte stores over NVLink, fences, raises one flag word per
+    (receiver, sender) and waits (bounded) for the peers' slices of the round.
+
+    Layout of each rank's symmetric buffer: [256 bytes of flags][slots] with
+    slot = world * rows * n_local fp16 values laid out [world][rows][n_local]
+    (rows = 1 for a mat-vec, the batch for the batched product).  A chain of
+    rounds must alternate between at least two slots: a rank that has seen round
+    L complete may start storing round L + 1 while a slower rank still reads the
+    vector of round L - 1.
+    """
+
+    def __init__(self, shard: FeatureShard, slots: int, device, group=None, rows: int = 1,
+                 max_polls: int = 0):
+        if slots < 2:
+            raise ValueError("a chain of gathers needs at least two gathered vectors to alternate")
+        self.shard, self.slots, self.rows, self.max_polls = shard, slots, rows, max_polls
+        self.slice_elems = rows * shard.n_local
+        self.slot_elems = shard.world * self.slice_elems
+        self.buf, self.handle, ptrs = _symmetric(256 + slots * self.slot_elems * 2, device, group)
         # device arrays of pointers: flag arrays and data regions of every rank
         self.peer_flags = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self.peer_data = torch.tensor([p + 256 for p in ptrs], dtype=torch.int64, device=device)
         self.sync = torch.zeros(2, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
-        dist.barrier(group=grp)
 
     def slot(self, i: int) -> torch.Tensor:
-        """This rank's copy of gathered vector i (fp16 [world * n_local])."""
+        """This rank's copy of gathered buffer i: fp16 [world][rows][n_local]
+        (flattened to [world * n_local] when rows == 1)."""
         off = 256 + i * self.slot_elems * 2
-        return self.buf[off:off + self.slot_elems * 2].view(torch.float16)
-
-    def gemv_nf4(self, i: int, A, B, absmax, lut16, K: int, blocksize: int = 64,
-                 nibble_order: int = 0, wait: bool = True, wait_previous: bool = False) -> None:
-        """Fused NF4 GEMV of this rank's rows into gathered vector i of every rank.
-
-        wait: enqueue the bounded wait for THIS gather right after the kernel.
-        wait_previous: let the kernel wait, before it reads A, for the gather of
-        the previous fused call (a layer's input is the previous layer's gathered
-        output); the caller then only needs `wait_all()` after the last layer."""
-        from ._lib import check, load_library
-        lib = load_library()
-        sh = self.shard
-        stream = torch.cuda.current_stream().cuda_stream
-        off = i * self.slot_elems + sh.rank * sh.n_local
-        check("hq_nf4_gemv_f16_gather", lib.hq_nf4_gemv_f16_gather(
-            A.data_ptr(), B.data_ptr(), absmax.data_ptr(), lut16.data_ptr(), sh.n_local, K,
-            blocksize, nibble_order, self.peer_data.data_ptr(), off, self.peer_flags.data_ptr(),
-            self.sync.data_ptr(), sh.world, sh.rank,
-            self.buf.data_ptr() if wait_previous else 0, self.status.data_ptr(), stream))
-        if wait:
-            check("hq_gather_wait", lib.hq_gather_wait(
-                self.buf.data_ptr(), self.sync.data_ptr(), sh.world, self.status.data_ptr(),
-                stream))
-
-    def wait_all(self) -> None:
-        """Bounded wait until the slices of the latest fused call have landed here."""
-        from ._lib import check, load_library
-        check("hq_gather_wait", load_library().hq_gather_wait(
-            self.buf.data_ptr(), self.sync.data_ptr(), self.shard.world, self.status.data_ptr(),
-            torch.cuda.current_stream().cuda_stream))
+        t = self.buf[off:off + self.slot_elems * 2].view(torch.float16)
+        if self.rows == 1:
+            return t
+        return t.view(self.shard.world, self.rows, self.shard.n_local)
 
     def local_slice(self, i: int) -> torch.Tensor:
-        """This rank's own slice inside its copy of gathered vector i: an ordinary
+        """This rank's own slice inside its copy of gathered buffer i: an ordinary
         kernel writes its outputs here, then `publish(i)` sends them to the peers."""
         sh = self.shard
-        return self.slot(i)[sh.rank * sh.n_local:(sh.rank + 1) * sh.n_local]
+        if self.rows == 1:
+            return self.slot(i)[sh.rank * sh.n_local:(sh.rank + 1) * sh.n_local]
+        return self.slot(i)[sh.rank]
 
     def publish(self, i: int) -> None:
-        """Copy the local slice of vector i to all peers, flag it, and wait (bounded)
+        """Copy the local slice of buffer i to all peers, flag it, and wait (bounded)
         for the peers' slices of the same round."""
         from ._lib import check, load_library
         sh = self.shard
         check("hq_gather_publish", load_library().hq_gather_publish(
-            self.peer_data.data_ptr(), i * self.slot_elems + sh.rank * sh.n_local, sh.n_local,
-            self.peer_flags.data_ptr(), self.sync.data_ptr(), sh.world, sh.rank,
+            self.peer_data.data_ptr(), i * self.slot_elems + sh.rank * self.slice_elems,
+            self.slice_elems, self.peer_flags.data_ptr(), self.sync.data_ptr(), sh.world, sh.rank,
+            self.max_polls, self.status.data_ptr(), torch.cuda.current_stream().cuda_stream))
+
+    def wait_all(self) -> None:
+        """Bounded wait until the slices of the latest round have landed here."""
+        from ._lib import check, load_library
+        check("hq_gather_wait", load_library().hq_gather_wait(
+            self.buf.data_ptr(), self.sync.data_ptr(), self.shard.world, self.max_polls,
             self.status.data_ptr(), torch.cuda.current_stream().cuda_stream))

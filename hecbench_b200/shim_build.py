@@ -1,6 +1,7 @@
 """Builds the C++ host-side drop-ins against libhq.so when the HeCBench tree is
-present (REFERENCE_ROOT, default /root/reference); used by the GPU drop-in
-tests.  Outputs (binaries only) go to oracle/_ref/:
+present (the directory named by REFERENCE_ROOT, else a directory `reference`
+beside this repository); used by the GPU drop-in tests.  Outputs (binaries
+only) go to hecbench_b200/build/dropin/:
 
   dropin_quant3MatMul  reference main.cu + shim/quant3MatMul/kernels.h
   dropin_lutgemm       reference main.cu, nQWeight_fp16.cu + shim/lut-gemm/kernels.cu
@@ -22,11 +23,12 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 SHIM = PKG / "shim"
-OUT = ROOT / "oracle" / "_ref"
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+OUT = PKG / "build" / "dropin"
+REF = Path(os.environ["REFERENCE_ROOT"]) if os.environ.get("REFERENCE_ROOT") else \
+    ROOT.parent / "reference"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w",
-          f"-I{ROOT / 'include'}", f"-L{PKG}", "-lhq", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../hecbench_b200"]
+          f"-I{ROOT / 'include'}", f"-L{PKG}", "-lhq", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../.."]
 
 
 def _run(cmd, cwd=None):

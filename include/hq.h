@@ -40,13 +40,6 @@ const char* hq_status_string(int status);
 /* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
 int hq_last_cuda_error(void);
 
-/* Measurement aid (no counterpart in the reference): a kernel that reads
- * `bytes` bytes from src exactly once with 128-bit streaming loads and does
- * nothing else.  Timed like the real kernels it gives the ceiling a kernel of
- * that footprint can reach on this GPU, launch and ramp included.  sink is one
- * device word. */
-int hq_probe_stream_read(const void* src, size_t bytes, unsigned* sink, hq_stream_t stream);
-
 /* ---------------- GPTQ 3-bit GEMV (quant3MatMul) ---------------- */
 
 /* Replaces vecquant3matmul<float> (quant3MatMul-cuda/kernels.h:171-190).
@@ -104,41 +97,74 @@ int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax,
                     const float* lut16, void* out_half, int N, int K, int blocksize,
                     int flags, hq_stream_t stream);
 
-/* NF4 GEMV of one GPU's output-feature slice, fused with the all-gather of the
- * slices over NVLink (no counterpart in the reference tree).  Every GPU of the
- * node runs the same call on its own N rows; each result is stored straight
- * into the gathered vector of EVERY GPU (peer_out_half[r], r = 0..world-1,
- * device-resident array of pointers to peer-mapped memory) at element
- * gather_offset + n, n = 0..N-1 of this rank (normally gather_offset =
- * rank * N).  When the last CTA has finished, the kernel bumps this rank's
- * launch count (sync_words[1]; sync_words[0] is a CTA counter; both zero
- * before the first call) and writes it to word `rank` of every GPU's flag array
- * (peer_flags[r], `world` words each, zero before the first call).
- * hq_gather_wait, enqueued after the call on the same stream, returns once all
- * `world` flags of this GPU have reached this GPU's own launch count, i.e. once
- * every slice of that gather has landed; its wait is bounded and sets *status
- * (device int, nullable) to 1 if it runs out.  wait_flags (nullable; this
- * GPU's own flag array) makes the kernel itself perform that wait for the
- * PREVIOUS fused call before it reads A - the input of a layer is the gathered
- * output of the layer before - so that its weights already stream while the
- * last slices arrive; the wait is bounded and reports through *status.  Plain
- * peer stores and loads only: no NCCL, no multicast. */
-int hq_nf4_gemv_f16_gather(const void* A_half, const uint8_t* B, const float* absmax,
-                           const float* lut16, int N, int K, int blocksize, int flags,
-                           void* const* peer_out_half, long long gather_offset,
-                           uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
-                           const uint32_t* wait_flags, int* status, hq_stream_t stream);
-int hq_gather_wait(const uint32_t* local_flags, const unsigned* sync_words, int world, int* status,
-                   hq_stream_t stream);
-/* The gather as a kernel of its own, for a slice that an ordinary launch has
- * already written into this GPU's gathered vector (elements offset ..
- * offset + n_slice of peer_out_half[rank]): copies the slice to every peer over
- * NVLink, raises this rank's flag everywhere and waits (bounded, *status = 1 on
- * expiry) until all ranks' slices of the same round have landed here.  Same
- * buffers and conventions as hq_nf4_gemv_f16_gather. */
+/* ---------------- output-feature sharding over the GPUs of a node ----------------
+ *
+ * No counterpart in the reference tree (its only collective code is the NCCL
+ * all-reduce sample ccl-cuda/main.cu:83-117).  Every output feature of the
+ * family is independent, so a layer is split by output features: each GPU runs
+ * the ordinary kernel on its slice and the slices are gathered into a vector
+ * every GPU holds.  Two gathers are provided, both on peer-mapped device memory
+ * with plain peer stores (no NCCL, no multicast); every wait in them is bounded
+ * by a poll limit (max_polls, 0 = default of about a second) after which the
+ * kernel sets *status (device int, nullable) to 1 and returns.
+ *
+ * (1) Low-latency packets, for the batch-1 path where the gather is tens of
+ * kilobytes and latency is everything.  The gathered vector is an array of
+ * hq_ll_packet, one per element: the fp16 value and the number ("epoch") of the
+ * gather round that wrote it, written and read with single 8-byte accesses, so
+ * a reader that sees the expected epoch also sees the value - no fence, no flag
+ * round trip, no follow-up kernel.  The GEMV stores every result as a packet
+ * into the packet vector of EVERY GPU as soon as the row is finished, and the
+ * next layer's GEMV takes its input straight from the packets, waiting for
+ * each until it carries the epoch of the latest completed round.
+ * sync_words: two device words per GPU, zero before the first call: [0] a CTA
+ * counter, [1] the epoch of the latest round this GPU has completed sending.
+ * A call reads E = sync_words[1] when it starts, expects E in its input
+ * packets, writes E + 1 into its output packets and leaves sync_words[1] =
+ * E + 1.  All GPUs must issue the same sequence of calls.  Packet vectors must
+ * start zeroed.  A vector may be rewritten as soon as the NEXT round's packets
+ * are complete on this GPU, so a chain of layers must alternate between at
+ * least two packet vectors. */
+typedef struct hq_ll_packet {
+  uint32_t value; /* low 16 bits: the fp16 element */
+  uint32_t epoch; /* gather round that wrote it */
+} hq_ll_packet;
+
+/* hq_nf4_gemv_f16 with packet input and/or packet output.
+ * Input: exactly one of A_half (plain fp16[K]) and A_ll (packets; element k is
+ * A_ll[k * a_stride], a_stride >= 1; K <= 32768 in this form) is non-null.
+ * Output: exactly one of out_half (plain fp16[N]) and peer_ll is non-null;
+ * peer_ll is a device-resident array of `world` pointers, peer_ll[r] = packet
+ * vector of GPU r (peer-mapped), and result n goes to element gather_offset + n
+ * of each (normally gather_offset = rank * N). */
+int hq_nf4_gemv_f16_ll(const void* A_half, const hq_ll_packet* A_ll, long long a_stride,
+                       const uint8_t* B, const float* absmax, const float* lut16, void* out_half,
+                       int N, int K, int blocksize, int flags, hq_ll_packet* const* peer_ll,
+                       long long gather_offset, unsigned* sync_words, int world, int rank,
+                       unsigned max_polls, int* status, hq_stream_t stream);
+
+/* Plain fp16 copy of n packets: waits (bounded) for each until it carries
+ * sync_words[1], the epoch of the latest round completed on this GPU; with
+ * sync_words == NULL the values are copied unchecked. */
+int hq_ll_unpack(const hq_ll_packet* ll, long long n, void* out_half, const unsigned* sync_words,
+                 unsigned max_polls, int* status, hq_stream_t stream);
+
+/* (2) Copy + flag, for larger slices (the batched path) and for any kernel of
+ * the family: an ordinary launch writes its slice into this GPU's own gathered
+ * vector (elements offset .. offset + n_slice of peer_out_half[rank]);
+ * hq_gather_publish then copies the slice to every peer with 16-byte stores
+ * over NVLink, makes it visible system-wide, raises this rank's flag word on
+ * every GPU (peer_flags[r], `world` words each, zero before the first call)
+ * and waits until all ranks' slices of the same round have landed here.
+ * sync_words as above ([1] counts rounds).  hq_gather_wait is that wait alone.
+ * As with packets, a chain of rounds must alternate between at least two
+ * gathered vectors: a rank that has seen round L complete may start storing
+ * round L + 1 while a slower rank still reads round L - 1's vector. */
 int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
                       uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
-                      int* status, hq_stream_t stream);
+                      unsigned max_polls, int* status, hq_stream_t stream);
+int hq_gather_wait(const uint32_t* local_flags, const unsigned* sync_words, int world,
+                   unsigned max_polls, int* status, hq_stream_t stream);
 
 /* ---------------- LUT-GEMM binary-coding mat-vec (lut-gemm) ---------------- */
 
@@ -151,7 +177,8 @@ size_t hq_lutgemm_workspace_bytes(int M);
  * (lut-gemm-cuda/kernels.cu:22-31, mv_fp16.h:101-131,228-259) for one input
  * row.  bW uint32[K/32][nb][M], alpha half[K/group][nb][M], q_bias
  * half[K/group][M] or NULL, x half[K], out half[M] (overwritten).
- * K % 32 == 0, group_size % 32 == 0, M % 4 == 0, 1 <= nb <= 8. */
+ * K % 32 == 0, group_size % 32 == 0 (32, or an even multiple of 32), M % 4 == 0,
+ * 1 <= nb <= 8; bW 16-byte aligned, alpha, q_bias and out 8-byte aligned. */
 int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW,
                     const void* alpha_half, const void* q_bias_half, int M, int K, int nb,
                     int group_size, void* workspace, size_t workspace_bytes,

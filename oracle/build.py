@@ -3,10 +3,13 @@
   oracle/liboracle.so          plain-C restatement (hq_oracle.c), gcc -fopenmp
   oracle/_ref/libref_cpu.so    the reference's own CPU quantBnB code, g++
   oracle/_ref/libref_gpu.so    the reference's own CUDA kernels for sm_100a, nvcc
+  oracle/_ref/ref_gpu_bench    the same kernels plus ref_gpu_bench.cu: the timing
+                               program behind `bench.py --impl refgpu`
 
-The two _ref libraries are compiled from the reference sources where they lie
-(REFERENCE_ROOT, default /root/reference); they are only (re)built when that
-tree is present, and never needed by the shipped library.
+The _ref outputs are compiled from the reference sources where they lie: the
+HeCBench tree named by REFERENCE_ROOT, or else a directory `reference` beside
+this repository.  They are only (re)built when that tree is present, and never
+needed by the shipped library.
 """
 from __future__ import annotations
 
@@ -16,7 +19,8 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ["REFERENCE_ROOT"]) if os.environ.get("REFERENCE_ROOT") else \
+    HERE.parent.parent / "reference"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 
@@ -59,12 +63,7 @@ def build_ref_gpu(force: bool = False):
     out = HERE / "_ref" / "libref_gpu.so"
     if not (REF / "src" / "quant3MatMul-cuda" / "kernels.h").exists():
         return out if out.exists() else None
-    parts = {
-        "ref_gpu_q3.cu": ["quant3MatMul-cuda"],
-        "ref_gpu_bnb.cu": ["quantBnB-cuda"],
-        "ref_gpu_lut.cu": ["lut-gemm-cuda"],
-        "ref_gpu_aqlm.cu": ["quantAQLM-cuda"],
-    }
+    parts = REF_GPU_PARTS
     srcs = [HERE / p for p in parts]
     if not (force or _stale(out, srcs)):
         return out
@@ -81,8 +80,39 @@ def build_ref_gpu(force: bool = False):
     return out
 
 
+REF_GPU_PARTS = {
+    "ref_gpu_q3.cu": ["quant3MatMul-cuda"],
+    "ref_gpu_bnb.cu": ["quantBnB-cuda"],
+    "ref_gpu_lut.cu": ["lut-gemm-cuda"],
+    "ref_gpu_aqlm.cu": ["quantAQLM-cuda"],
+}
+
+
+def build_ref_gpu_bench(force: bool = False):
+    """The reference kernels again, with the default stream made per-thread so
+    that their launches can be captured in a CUDA graph, linked with the timing
+    program ref_gpu_bench.cu."""
+    out = HERE / "_ref" / "ref_gpu_bench"
+    if not (REF / "src" / "quant3MatMul-cuda" / "kernels.h").exists():
+        return out if out.exists() else None
+    srcs = [HERE / p for p in REF_GPU_PARTS] + [HERE / "ref_gpu_bench.cu"]
+    if not (force or _stale(out, srcs)):
+        return out
+    out.parent.mkdir(exist_ok=True)
+    common = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w",
+              "--default-stream", "per-thread"]
+    objs = []
+    for name, dirs in REF_GPU_PARTS.items():
+        obj = out.parent / (Path(name).stem + "_pt.o")
+        _run([*common, *[f"-I{REF / 'src' / d}" for d in dirs], "-c", HERE / name, "-o", obj])
+        objs.append(obj)
+    _run([*common, HERE / "ref_gpu_bench.cu", *objs, "-o", out, "-lcudart"])
+    return out
+
+
 def build_all(force: bool = False):
-    return build_oracle(force), build_ref_cpu(force), build_ref_gpu(force)
+    return (build_oracle(force), build_ref_cpu(force), build_ref_gpu(force),
+            build_ref_gpu_bench(force))
 
 
 if __name__ == "__main__":

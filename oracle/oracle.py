@@ -303,3 +303,31 @@ def rel_err(y, ref) -> float:
     den = np.maximum(np.abs(ref), rms)
     den[den == 0] = 1.0
     return float(np.max(np.abs(y - ref) / den))
+
+
+def rel_err_linf(y, ref, eps: float = 1e-3) -> float:
+    """max_i |y_i - ref_i| / max(|ref_i|, eps * max_j |ref_j|): the element-wise
+    relative error with only a small floor (eps of the largest output).  It is
+    reported beside rel_err; for outputs that are the small difference of large
+    terms it is dominated by cancellation, not by the kernel."""
+    y = np.asarray(y, dtype=np.float64).ravel()
+    ref = np.asarray(ref, dtype=np.float64).ravel()
+    if ref.size == 0:
+        return 0.0
+    den = np.maximum(np.abs(ref), eps * float(np.max(np.abs(ref))))
+    den[den == 0] = 1.0
+    return float(np.max(np.abs(y - ref) / den))
+
+
+def rel_err_above_floor(y, ref) -> float:
+    """Worst plain relative error |y_i - ref_i| / |ref_i| over the outputs whose
+    magnitude reaches the vector's RMS (the ones rel_err measures element-wise)."""
+    y = np.asarray(y, dtype=np.float64).ravel()
+    ref = np.asarray(ref, dtype=np.float64).ravel()
+    if ref.size == 0:
+        return 0.0
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    big = np.abs(ref) >= max(rms, np.finfo(np.float64).tiny)
+    if not np.any(big):
+        return 0.0
+    return float(np.max(np.abs(y[big] - ref[big]) / np.abs(ref[big])))

@@ -1,7 +1,7 @@
 """Generates tests/golden/bnb_golden.npz from the reference's own CPU code.
 
-Run in a container that has the HeCBench tree (REFERENCE_ROOT, default
-/root/reference): `python tests/golden/make_golden_cpu.py`.  It builds
+Run where the HeCBench tree is available (REFERENCE_ROOT, or a directory
+`reference` beside this repository): `python tests/golden/make_golden_cpu.py`.  It builds
 oracle/_ref/libref_cpu.so from quantBnB-omp/main.cpp and records
 
   code  the 256-entry table of quantBnB-cuda/code.h

@@ -58,6 +58,30 @@ def test_argument_errors_need_no_gpu(hq):
                                    0, None, None) == -1
 
 
+def test_gather_and_noalloc_argument_errors_need_no_gpu(hq):
+    lib = hq.load_library()
+    p = 64
+    # packet GEMV: exactly one input form, exactly one output form, sync words, rank < world
+    assert lib.hq_nf4_gemv_f16_ll(p, p, 1, p, p, p, p, 32, 64, 64, 0, 0, 0, p, 1, 0, 0, 0,
+                                  None) == -2
+    assert lib.hq_nf4_gemv_f16_ll(p, 0, 1, p, p, p, p, 32, 64, 64, 0, p, 0, p, 1, 0, 0, 0,
+                                  None) == -2
+    assert lib.hq_nf4_gemv_f16_ll(p, 0, 1, p, p, p, p, 32, 64, 64, 0, 0, 0, 0, 1, 0, 0, 0,
+                                  None) == -2
+    assert lib.hq_nf4_gemv_f16_ll(p, 0, 1, p, p, p, p, 32, 64, 64, 0, 0, 0, p, 2, 2, 0, 0,
+                                  None) == -1
+    assert lib.hq_gather_wait(p, p, 0, 0, 0, None) == -1
+    assert lib.hq_gather_publish(p, 0, 0, p, p, 1, 0, 0, 0, None) == -1
+    assert lib.hq_ll_unpack(p, 0, p, 0, 0, 0, None) == -1
+    # allocation-free LUT-GEMM: every argument rule is checked before the shared
+    # scratch array is looked up or touched (so no CUDA call is made here)
+    assert lib.hq_lutgemm_nqmv_noalloc(None, p, p, p, None, 256, 128, 3, 128, None) == -2
+    assert lib.hq_lutgemm_nqmv_noalloc(p, p, p, p, None, 258, 128, 3, 128, None) == -1
+    assert lib.hq_lutgemm_nqmv_noalloc(p, p, p, p, None, 256, 192, 3, 96, None) == -6
+    assert lib.hq_lutgemm_nqmv_noalloc(p, p, 8, p, None, 256, 128, 3, 128, None) == -3
+    assert lib.hq_lutgemm_nqmv_noalloc(p, p, p, p, None, 65536 + 4, 128, 3, 128, None) == -7
+
+
 def test_python_layer_rejects_cpu_tensors(hq):
     import torch
     t = torch.zeros(256)

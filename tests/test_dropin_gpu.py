@@ -10,7 +10,7 @@ from pathlib import Path
 import pytest
 
 pytestmark = pytest.mark.gpu
-BIN = Path(__file__).resolve().parent.parent / "oracle" / "_ref"
+BIN = Path(__file__).resolve().parent.parent / "hecbench_b200" / "build" / "dropin"
 
 
 def run(name, *args, timeout=600):

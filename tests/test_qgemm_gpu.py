@@ -71,26 +71,69 @@ def test_qgemm_nf4_matches_dequant_then_gemm(hq, dev):
     assert float(err.max()) < TOL_F16
 
 
-def test_qgemm_q3_llama_shapes_property(hq, dev):
-    """Full Llama-3-70B MLP shapes: compare with a dense fp32 product of the
-    dequantised weights computed by torch on the same GPU (checker only)."""
+LLAMA3_70B_MLP = [(8192, 28672), (28672, 8192)]  # (K, N): up/gate and down projections
+
+
+def _feature_subset(N, tiles=4, width=128):
+    """`tiles` whole 128-feature tiles spread over [0, N): first, last and evenly between."""
+    starts = np.unique(np.linspace(0, N - width, tiles).astype(np.int64) // width * width)
+    return np.concatenate([np.arange(s0, s0 + width) for s0 in starts])
+
+
+@pytest.mark.parametrize("K,N", LLAMA3_70B_MLP)
+def test_qgemm_q3_llama3_70b_mlp(hq, oracle, dev, K, N):
+    """Batch 64 at the full Llama-3-70B MLP shapes (the second one takes the K-split
+    path): 512 output features against the CPU oracle (bit-exact fp16 dequantised
+    weights times X in fp64), then every output against a dense fp32 product of
+    the dequantised weights computed by torch on the same GPU."""
     import torch
-    for (K, N) in [(8192, 28672), (28672, 8192)]:
-        Mb, group = 64, 128
-        g = torch.Generator(device="cpu").manual_seed(K)
-        codes = torch.randint(0, 8, (K, N), generator=g, dtype=torch.uint8)
-        mat = torch.from_numpy(synth.q3_pack(codes.numpy())).to(dev)
-        scales = (torch.rand(K // group, N, generator=g) * 0.009 + 0.001).half()
-        zeros = (scales.float() * torch.randint(0, 8, (K // group, N), generator=g)).half()
-        X = torch.randn(Mb, K, generator=g).half()
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
-        Y = hq.qgemm_q3(X.to(dev), mat, scales.to(dev), zeros.to(dev), N, K, group, status=status)
-        torch.cuda.synchronize()
-        assert int(status.item()) == 0
-        s = scales.to(dev).float().repeat_interleave(group, dim=0)
-        z = zeros.to(dev).float().repeat_interleave(group, dim=0)
-        W = (codes.to(dev).float() * s - z).half().float()
-        ref = X.to(dev).float() @ W
-        err = (Y.float() - ref).abs() / torch.maximum(ref.abs(), ref.pow(2).mean().sqrt())
-        assert float(err.max()) < TOL_F16
-        del W, s, z, ref
+    Mb, group = 64, 128
+    X, codes, scales, zeros = synth.qgemm_q3_case(Mb, K, N, group, seed=K % 97)
+    mat = synth.q3_pack(codes)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    dX, dS, dZ = to_dev(X, dev), to_dev(scales, dev), to_dev(zeros, dev)
+    Y = hq.qgemm_q3(dX, to_dev(mat, dev), dS, dZ, N, K, group, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded in-kernel wait ran out"
+    cols = _feature_subset(N)
+    W16 = oracle.q3g_dequant_f16(np.ascontiguousarray(mat[:, cols]),
+                                 np.ascontiguousarray(scales[:, cols]),
+                                 np.ascontiguousarray(zeros[:, cols]), K, cols.size, group)
+    ref = oracle.gemm_f16_f64(X, W16)
+    got = Y[:, torch.from_numpy(cols).to(dev)].cpu().numpy().astype(np.float64)
+    assert oracle.rel_err(got, ref) < TOL_F16
+    assert oracle.rel_err_above_floor(got, ref) < TOL_F16
+    s = dS.float().repeat_interleave(group, dim=0)
+    z = dZ.float().repeat_interleave(group, dim=0)
+    W = torch.addcmul(-z, torch.from_numpy(codes).to(dev).float(), s).half().float()
+    del s, z
+    full = dX.float() @ W
+    err = (Y.float() - full).abs() / torch.maximum(full.abs(), full.pow(2).mean().sqrt())
+    assert float(err.max()) < TOL_F16
+
+
+@pytest.mark.parametrize("K,N", LLAMA3_70B_MLP)
+def test_qgemm_nf4_llama3_70b_mlp(hq, oracle, dev, K, N):
+    """The NF4 operand at the same two shapes: 512 output features against the CPU
+    oracle, every output against the library's own bit-exact dequantisation
+    followed by a dense fp32 product in torch."""
+    import torch
+    Mb, bs = 64, 64
+    X, B, absmax, lut16 = synth.qgemm_nf4_case(Mb, K, N, bs, seed=K % 89)
+    dX, dB, dA, dL = (to_dev(a, dev) for a in (X, B, absmax, lut16))
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    Y = hq.qgemm_nf4(dX, dB, dA, dL, N, K, bs, 0, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded in-kernel wait ran out"
+    rows = _feature_subset(N)
+    Brows = np.ascontiguousarray(B.reshape(N, K // 2)[rows]).reshape(-1)
+    Arows = np.ascontiguousarray(absmax.reshape(N, K // bs)[rows]).reshape(-1)
+    W16 = oracle.nf4_dequant_f16(Brows, Arows, lut16, rows.size * K, bs, 0).reshape(rows.size, K)
+    ref = oracle.gemm_f16_nk_f64(X, W16)
+    got = Y[:, torch.from_numpy(rows).to(dev)].cpu().numpy().astype(np.float64)
+    assert oracle.rel_err(got, ref) < TOL_F16
+    assert oracle.rel_err_above_floor(got, ref) < TOL_F16
+    W = hq.dequantize_nf4(dB, dA, dL, N * K, bs, 0).view(N, K)
+    full = dX.float() @ W.float().t()
+    err = (Y.float() - full).abs() / torch.maximum(full.abs(), full.pow(2).mean().sqrt())
+    assert float(err.max()) < TOL_F16
