@@ -1,12 +1,14 @@
 #!/usr/bin/env python
 """Benchmark of the quantized mat-vec hot path on B200.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME]
+                  [--impl ours|reference|refgpu] [--scaling weak|strong] [--gather FORM]
 
-One "step" is one pass of the workload's kernel over R independent packed
-weight replicas (R layers of a decoder, back to back, as one CUDA graph); R is
-chosen so that R x bytes is several times the 126 MB L2, so every launch
-streams its weights from HBM.  Rank 0 prints ONE JSON line:
+One "step" is P passes of the workload's kernel over R independent packed
+weight replicas (R layers of a decoder, back to back, one CUDA graph per pass);
+R is chosen so that R x bytes is several times the 126 MB L2, so every launch
+streams its weights from HBM, and P so that a step lasts about 10 ms.  Rank 0
+prints ONE JSON line:
 
   value      effective weight GB/s over all ranks = algorithmic bytes / time,
              inputs resident in HBM, CUDA-event timed, max over ranks
@@ -15,17 +17,30 @@ streams its weights from HBM.  Rank 0 prints ONE JSON line:
              back (weights are model state and stay resident)
   roofline   achieved GB/s of the kernel (algorithmic bytes per launch / mean
              launch duration inside the timed region) against the measured HBM
-             copy bandwidth of MEASURED_PEAKS.json
+             copy bandwidth of MEASURED_PEAKS.json (and against the 8 TB/s
+             spec figure)
+  workloads  N = 1, headline workload only: every other workload of the family,
+             each timed the same way in a short loop, with the reference's own
+             CUDA kernel compiled for sm_100a beside it (`ref_kernel_us`, from
+             a separate process: `--impl refgpu`) and the CPU oracle time
   cpu_baseline  the CPU oracle port of the same workload timed on a bounded
              sample on this box's host cores (rank 0, N = 1 only)
 
+N > 1 (one process per GPU under torchrun): `--scaling weak` (default) gives
+every rank its own shard of a layer N times wider and gathers the output
+slices after every layer; `--scaling strong` (batched workloads) splits the
+one layer's output features over the ranks.  After the timed loops every rank
+checks its gathered results against the CPU oracle (`gather_check`).
+
 `--impl reference` times the reference algorithm's CPU implementation (the
 reference's own build for kQuantize, the oracle port otherwise) on the same
-workload with all host threads.
+workload with all host threads.  `--impl refgpu` times the reference's CUDA
+kernels (oracle/_ref/ref_gpu_bench).
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -41,28 +56,27 @@ sys.path.insert(0, str(ROOT))
 
 FALLBACK_BF16_TFLOPS = 1590.0
 FALLBACK_HBM_GBS = 6650.0
+SPEC_HBM_GBS = 8000.0
 
 
-def measured_peak():
+def _peak(key, fallback):
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+            return float(json.loads(p.read_text())[key]), "measured"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return fallback, "fallback"
+
+
+def measured_peak():
+    return _peak("hbm_gbs", FALLBACK_HBM_GBS)
 
 
 def measured_tensor_peak():
     """Dense bf16 cuBLAS throughput measured on this pool (burst figure: the
     kernel is timed in a short graph, not inside a seconds-long step)."""
-    p = ROOT / "MEASURED_PEAKS.json"
-    if p.exists():
-        try:
-            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
-        except Exception:
-            pass
-    return FALLBACK_BF16_TFLOPS, "fallback"
+    return _peak("bf16_tflops", FALLBACK_BF16_TFLOPS)
 
 
 def ncu_traffic(workload: str):
@@ -77,10 +91,10 @@ def ncu_traffic(workload: str):
 
 
 # --------------------------------------------------------------------------
-# workloads: name -> builder(seed) returning a dict of host arrays + metadata
+# workloads: name -> host arrays + metadata
 # --------------------------------------------------------------------------
 
-def _host_case(name: str, seed: int):
+def _host_case(name: str, seed: int, Mb: int = 64):
     from hecbench_b200 import synth
     if name == "nf4_gemv":
         N, K, bs = 11008, 4096, 64
@@ -94,12 +108,12 @@ def _host_case(name: str, seed: int):
         return dict(N=N, K=K, bs=bs, B=B, absmax=absmax, lut=lut,
                     bytes=B.nbytes + absmax.nbytes + N * K * 2,
                     desc="NF4 blockwise dequantize 11008x4096 -> fp16")
-    if name in ("q3_gemv_f32", "q3_gemv_f16"):
-        K, W = (4096, 4096)
-        if os.environ.get("HQ_BENCH_Q3_SHAPE") == "opt175b":
-            K, W = 49152, 12288
-        vec, codes, sc, z = synth.q3_case(K, W, seed)
-        return dict(K=K, W=W, vec=vec, codes=codes, sc=sc, z=z,
+    if name in ("q3_gemv_f32", "q3_gemv_f16", "q3_gemv_f32_opt175b", "q3_gemv_f16_opt175b"):
+        K, W = (49152, 12288) if name.endswith("opt175b") else (4096, 4096)
+        vec, _, sc, z = synth.q3_case(32, W, seed)
+        vec = synth._rng(seed, 2).standard_normal(K).astype(np.float32)
+        mat = synth.q3_words(K, W, seed)
+        return dict(K=K, W=W, vec=vec, mat=mat, sc=sc, z=z,
                     bytes=K * 3 // 32 * W * 4 + 3 * 4 * W + 4 * K,
                     desc=f"GPTQ 3-bit GEMV {K}x{W}")
     if name == "bnb_quantize":
@@ -116,26 +130,28 @@ def _host_case(name: str, seed: int):
         m = k = 4096
         codes, x, cb, scales = synth.aqlm_1x16_case(m, k, 1, seed)
         return dict(m=m, k=k, codes=codes, x=x, cb=cb, scales=scales,
-                    bytes=codes.nbytes + cb.nbytes + 3 * 8192,
+                    bytes=codes.nbytes + cb.nbytes + 3 * 8192, gather_bytes=m * k // 8 * 16,
                     desc="AQLM 1x16 mat-vec 4096x4096 (packed bytes; 16-byte gathers go through L2)")
     if name == "aqlm_2x8":
         m = k = 4096
         codes, x, cbs, scales = synth.aqlm_2x8_case(m, k, seed)
         return dict(m=m, k=k, codes=codes, x=x, cbs=cbs, scales=scales,
                     bytes=codes.nbytes + 4 * 8192, desc="AQLM 2x8 mat-vec 4096x4096")
-    if name == "qgemm_q3":
-        Mb, K, N = 64, 8192, 28672
-        if os.environ.get("HQ_BENCH_QGEMM_SHAPE") == "down":
-            K, N = 28672, 8192
-        X, codes, scales, zeros = synth.qgemm_q3_case(Mb, K, N, 128, seed)
-        return dict(Mb=Mb, K=K, N=N, X=X, codes=codes, scales=scales, zeros=zeros,
-                    bytes=K * 3 // 32 * N * 4 + 2 * (K // 128) * N * 2 + Mb * K * 2 + Mb * N * 2,
+    if name in ("qgemm_q3", "qgemm_q3_down"):
+        K, N = (28672, 8192) if name.endswith("down") else (8192, 28672)
+        G = K // 128
+        X = synth._rng(seed, 52).standard_normal((Mb, K)).astype(np.float16)
+        scales = synth._rng(seed, 53).uniform(0.001, 0.01, (G, N)).astype(np.float16)
+        zeros = (scales.astype(np.float32) *
+                 synth._rng(seed, 54).integers(0, 8, (G, N))).astype(np.float16)
+        mat = synth.q3_words(K, N, seed)
+        return dict(Mb=Mb, K=K, N=N, X=X, mat=mat, scales=scales, zeros=zeros,
+                    bytes=K * 3 // 32 * N * 4 + 2 * G * N * 2 + Mb * K * 2 + Mb * N * 2,
                     flops=2.0 * Mb * K * N,
                     desc=f"batched dequant-GEMM, 3-bit g128, X[{Mb}x{K}] x W[{K}x{N}] (Llama-3-70B MLP)")
-    if name == "qgemm_nf4":
-        Mb, K, N, bs = 64, 8192, 28672, 64
-        if os.environ.get("HQ_BENCH_QGEMM_SHAPE") == "down":
-            K, N = 28672, 8192
+    if name in ("qgemm_nf4", "qgemm_nf4_down"):
+        bs = 64
+        K, N = (28672, 8192) if name.endswith("down") else (8192, 28672)
         X, B, absmax, lut = synth.qgemm_nf4_case(Mb, K, N, bs, seed)
         return dict(Mb=Mb, K=K, N=N, bs=bs, X=X, B=B, absmax=absmax, lut=lut,
                     bytes=B.nbytes + absmax.nbytes + Mb * K * 2 + Mb * N * 2 + 64,
@@ -149,28 +165,35 @@ def _host_case(name: str, seed: int):
 # launch of the stream is finishing (HQ_BENCH_NO_PDL=1 turns that off).
 PDL = os.environ.get("HQ_BENCH_NO_PDL") != "1"
 
-WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "bnb_quantize", "lutgemm",
-             "aqlm_1x16", "aqlm_2x8", "qgemm_q3", "qgemm_nf4"]
-DTYPE = {"nf4_gemv": "f16", "nf4_dequant": "f16", "q3_gemv_f32": "f32", "q3_gemv_f16": "f16",
-         "bnb_quantize": "u8", "lutgemm": "f16", "aqlm_1x16": "f16", "aqlm_2x8": "f16",
-         "qgemm_q3": "f16", "qgemm_nf4": "f16"}
+WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "q3_gemv_f32_opt175b",
+             "q3_gemv_f16_opt175b", "bnb_quantize", "lutgemm", "aqlm_1x16", "aqlm_2x8",
+             "qgemm_q3", "qgemm_nf4", "qgemm_q3_down", "qgemm_nf4_down"]
+
+
+def dtype_of(name: str) -> str:
+    return "f32" if name.startswith("q3_gemv_f32") else ("u8" if name == "bnb_quantize" else "f16")
 
 
 class DeviceWorkload:
-    """R replicas of one workload on one GPU, launched through the C ABI."""
+    """R replicas of one workload on one GPU, launched through the C ABI.
+    `shard` (FeatureShard) keeps only this rank's output features of each
+    replica (strong scaling)."""
 
-    def __init__(self, name: str, dev, seed: int, target_bytes: float):
+    def __init__(self, name: str, dev, seed: int, target_bytes: float, Mb: int = 64, shard=None):
         import torch
         import hecbench_b200 as hq
-        self.hq, self.torch, self.name, self.dev = hq, torch, name, dev
-        c = _host_case(name, seed)
+        self.hq, self.torch, self.name, self.dev, self.shard = hq, torch, name, dev, shard
+        c = _host_case(name, seed, Mb)
         self.case = c
         self.bytes = int(c["bytes"])
-        self.R = max(2, int(np.ceil(target_bytes / self.bytes)))
+        local_bytes = self.bytes / (shard.world if shard else 1)
+        self.R = max(2, int(np.ceil(target_bytes / local_bytes)))
         t = lambda a: torch.from_numpy(np.ascontiguousarray(
             a.view(np.int32) if a.dtype == np.uint32 else a)).to(dev)
         R = self.R
         rot = lambda a, i: np.roll(a.reshape(-1), 4099 * i).reshape(a.shape) if i else a
+        rows = (lambda a: shard.rows(a)) if shard else (lambda a: a)
+        cols = (lambda a: shard.cols(a)) if shard else (lambda a: a)
         if name in ("nf4_gemv", "nf4_dequant"):
             self.B = [t(rot(c["B"], i)) for i in range(R)]
             self.absmax = [t(rot(c["absmax"], i)) for i in range(R)]
@@ -181,12 +204,10 @@ class DeviceWorkload:
             else:
                 self.W = torch.empty(c["N"] * c["K"], dtype=torch.float16, device=dev)
         elif name.startswith("q3_gemv"):
-            from hecbench_b200 import synth
-            mat = synth.q3_pack(c["codes"])
-            self.height = mat.shape[0]
-            self.mat = [t(rot(mat, i)) for i in range(R)]
+            self.height = c["mat"].shape[0]
+            self.mat = [t(rot(c["mat"], i)) for i in range(R)]
             self.sc, self.z = t(c["sc"]), t(c["z"])
-            v = c["vec"] if name == "q3_gemv_f32" else c["vec"].astype(np.float16)
+            v = c["vec"] if name.startswith("q3_gemv_f32") else c["vec"].astype(np.float16)
             self.x = [t(v) for _ in range(R)]
             self.out = [torch.zeros(c["W"], dtype=torch.float32, device=dev) for _ in range(R)]
         elif name == "bnb_quantize":
@@ -205,19 +226,21 @@ class DeviceWorkload:
             self.cb = t(c["cb"])
             self.x = [t(c["x"]) for _ in range(R)]
             self.out = [torch.empty(c["m"], dtype=torch.float16, device=dev) for _ in range(R)]
-        elif name == "qgemm_q3":
-            from hecbench_b200 import synth
-            mat = synth.q3_pack(c["codes"])
-            self.mat = [t(rot(mat, i)) for i in range(R)]
-            self.sc, self.z = t(c["scales"]), t(c["zeros"])
+        elif name.startswith("qgemm_q3"):
+            self.n_local = c["N"] // (shard.world if shard else 1)
+            self.mat = [t(cols(rot(c["mat"], i))) for i in range(R)]
+            self.sc, self.z = t(cols(c["scales"])), t(cols(c["zeros"]))
             self.x = [t(c["X"]) for _ in range(R)]
-            self.out = [torch.empty((c["Mb"], c["N"]), dtype=torch.float16, device=dev)
+            self.out = [torch.empty((c["Mb"], self.n_local), dtype=torch.float16, device=dev)
                         for _ in range(R)]
-        elif name == "qgemm_nf4":
-            self.B = [t(rot(c["B"], i)) for i in range(R)]
-            self.absmax, self.lut = t(c["absmax"]), t(c["lut"])
+        elif name.startswith("qgemm_nf4"):
+            self.n_local = c["N"] // (shard.world if shard else 1)
+            Bm = c["B"].reshape(c["N"], c["K"] // 2)
+            am = c["absmax"].reshape(c["N"], c["K"] // c["bs"])
+            self.B = [t(rows(rot(Bm, i)).reshape(-1)) for i in range(R)]
+            self.absmax, self.lut = t(rows(am).reshape(-1)), t(c["lut"])
             self.x = [t(c["X"]) for _ in range(R)]
-            self.out = [torch.empty((c["Mb"], c["N"]), dtype=torch.float16, device=dev)
+            self.out = [torch.empty((c["Mb"], self.n_local), dtype=torch.float16, device=dev)
                         for _ in range(R)]
         elif name == "aqlm_2x8":
             self.codes = [t(rot(c["codes"], i)) for i in range(R)]
@@ -225,18 +248,18 @@ class DeviceWorkload:
             self.x = [t(c["x"]) for _ in range(R)]
             self.out = [torch.empty(c["m"], dtype=torch.float16, device=dev) for _ in range(R)]
 
-    def launch(self, i: int):
+    def launch(self, i: int, out=None, pdl: bool = PDL):
         hq, c, n = self.hq, self.case, self.name
         if n == "nf4_gemv":
             hq.gemv_nf4(self.x[i], self.B[i], self.absmax[i], self.lut, c["N"], c["K"], c["bs"], 0,
-                        self.out[i], weights_resident=PDL)
+                        self.out[i] if out is None else out, weights_resident=pdl)
         elif n == "nf4_dequant":
             hq.dequantize_nf4(self.B[i], self.absmax[i], self.lut, c["N"] * c["K"], c["bs"], 0,
                               self.W)
-        elif n == "q3_gemv_f32":
+        elif n.startswith("q3_gemv_f32"):
             hq.vecquant3matmul(self.x[i], self.mat[i], self.out[i], self.sc, self.z, self.height,
                                c["W"])
-        elif n == "q3_gemv_f16":
+        elif n.startswith("q3_gemv_f16"):
             hq.vecquant3matmul_faster(self.x[i], self.mat[i], self.out[i], self.sc, self.z,
                                       self.height, c["W"])
         elif n == "bnb_quantize":
@@ -249,16 +272,16 @@ class DeviceWorkload:
                                [m, m, m, 1 << 30], 65536)
         elif n == "aqlm_2x8":
             hq.code2x8_matvec(self.codes[i], self.x[i], self.out[i], self.cbs, c["m"], c["k"])
-        elif n == "qgemm_q3":
-            hq.qgemm_q3(self.x[i], self.mat[i], self.sc, self.z, c["N"], c["K"], 128,
-                        out=self.out[i])
-        elif n == "qgemm_nf4":
-            hq.qgemm_nf4(self.x[i], self.B[i], self.absmax, self.lut, c["N"], c["K"], c["bs"], 0,
-                         out=self.out[i])
+        elif n.startswith("qgemm_q3"):
+            hq.qgemm_q3(self.x[i], self.mat[i], self.sc, self.z, self.n_local, c["K"], 128,
+                        out=self.out[i] if out is None else out)
+        elif n.startswith("qgemm_nf4"):
+            hq.qgemm_nf4(self.x[i], self.B[i], self.absmax, self.lut, self.n_local, c["K"], c["bs"],
+                         0, out=self.out[i] if out is None else out)
 
     # host <-> device traffic of one launch on the end-to-end path
     def host_io(self):
-        """(pinned host input, device input list, device output list) or None."""
+        """(pinned host inputs, pinned host outputs) or None."""
         torch = self.torch
         if not hasattr(self, "x") or not hasattr(self, "out"):
             return None
@@ -267,19 +290,24 @@ class DeviceWorkload:
         hout = [torch.empty_like(self.out[i], device="cpu").pin_memory() for i in range(self.R)]
         return hin, hout
 
+    def oracle_rows(self, i: int, x_half: np.ndarray, rows: int):
+        """fp64 oracle of the first `rows` outputs of replica i (NF4 GEMV only)."""
+        from oracle import oracle as O
+        c = self.case
+        B = self.B[i].cpu().numpy()[:rows * c["K"] // 2]
+        am = self.absmax[i].cpu().numpy()[:rows * c["K"] // c["bs"]]
+        return O.nf4_gemv_f64(x_half, B, am, c["lut"], rows, c["K"], c["bs"], 0)
+
     def check_one(self):
         """One replica against the CPU oracle (cheap sanity guard before timing)."""
         from oracle import oracle as O
-        c = self.case
         if self.name != "nf4_gemv":
             return None
         self.launch(0)
         self.torch.cuda.synchronize()
         y = self.out[0].cpu().numpy().astype(np.float64)
         rows = 512
-        ref = O.nf4_gemv_f64(c["A"], c["B"][:rows * c["K"] // 2], c["absmax"], c["lut"], rows,
-                             c["K"], c["bs"], 0)
-        return O.rel_err(y[:rows], ref)
+        return O.rel_err(y[:rows], self.oracle_rows(0, self.case["A"], rows))
 
 
 class ClockSampler:
@@ -328,6 +356,7 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
     sample of the workload, all host threads."""
     from oracle import oracle as O
     c = _host_case(name, 0)
+    full_bytes = float(c["bytes"])
     threads = O.num_threads()
     kind = "port"
     if name == "nf4_gemv":
@@ -338,10 +367,12 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
         fn = lambda: O.nf4_dequant_f16(c["B"], c["absmax"], c["lut"], c["N"] * c["K"], c["bs"], 0)
         sample = "full dequantize"
     elif name.startswith("q3_gemv"):
-        mat = O.q3_pack(c["codes"])
-        zero = np.zeros(c["W"], dtype=np.float32)
-        fn = lambda: O.q3_gemv_f32(c["vec"], mat, zero, c["sc"], c["z"])
-        sample = "full GEMV, reference fp32 order"
+        cols = min(c["W"], 4096)
+        mat = np.ascontiguousarray(c["mat"][:, :cols])
+        zero = np.zeros(cols, dtype=np.float32)
+        fn = lambda: O.q3_gemv_f32(c["vec"], mat, zero, c["sc"][:cols], c["z"][:cols])
+        sample = f"{cols} of {c['W']} output columns, reference fp32 order"
+        c = dict(c, bytes=c["bytes"] * cols / c["W"])
     elif name == "bnb_quantize":
         g = np.load(ROOT / "tests" / "golden" / "bnb_golden.npz")
         if O.ref_cpu() is not None:
@@ -368,22 +399,20 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
         m = c["m"]
         fn = lambda: O.aqlm_2x8_f64(c["codes"], c["x"], c["cbs"], m, c["k"])
         sample = "full mat-vec (fp64 oracle)"
-    elif name == "qgemm_q3":
+    elif name.startswith("qgemm_q3"):
         cols = 128
-        mat = np.ascontiguousarray(O.q3_pack(c["codes"])[:, :cols])
+        mat = np.ascontiguousarray(c["mat"][:, :cols])
         sc, z = (np.ascontiguousarray(c[k][:, :cols]) for k in ("scales", "zeros"))
         fn = lambda: O.gemm_f16_f64(c["X"], O.q3g_dequant_f16(mat, sc, z, c["K"], cols, 128))
-        sample = f"{cols} of {c['N']} output features (dequantise + fp64 product), one thread"
-        threads = 1
+        sample = f"{cols} of {c['N']} output features (dequantise + fp64 product)"
         c = dict(c, bytes=c["bytes"] * cols / c["N"])
-    elif name == "qgemm_nf4":
+    elif name.startswith("qgemm_nf4"):
         cols = 128
         B = c["B"][:cols * c["K"] // 2]
         fn = lambda: O.gemm_f16_nk_f64(
             c["X"], O.nf4_dequant_f16(B, c["absmax"], c["lut"], cols * c["K"], c["bs"],
                                       0).reshape(cols, c["K"]))
-        sample = f"{cols} of {c['N']} output features (dequantise + fp64 product), one thread"
-        threads = 1
+        sample = f"{cols} of {c['N']} output features (dequantise + fp64 product)"
         c = dict(c, bytes=c["bytes"] * cols / c["N"])
     else:
         raise SystemExit(f"no CPU baseline for {name}")
@@ -395,22 +424,41 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
         if el > budget_s or reps >= 20000:
             break
     per = el / reps
+    full_us = per * 1e6 * full_bytes / c["bytes"]  # a sampled time scaled to the whole call
     return {"value": c["bytes"] / per / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
-            "sample": f"{sample}; {reps} repetitions in {el:.1f} s", "us_per_call": per * 1e6}
+            "sample": f"{sample}; {reps} repetitions in {el:.1f} s", "us_per_call": per * 1e6,
+            "us_per_full_call": full_us}
 
 
-def cpu_baseline_clean(name: str):
+def _subprocess_json(code_or_cmd, env=None, timeout=600):
+    out = subprocess.run(code_or_cmd, env=env, capture_output=True, text=True, timeout=timeout,
+                         check=True).stdout
+    return json.loads(out.strip().splitlines()[-1])
+
+
+def cpu_baseline_clean(name: str, budget_s: float = 12.0):
     """cpu_baseline in a fresh interpreter (no CUDA context, no helper threads of
     this process competing for the host cores), all host threads."""
     env = dict(os.environ, OMP_NUM_THREADS=str(os.cpu_count() or 1))
     code = ("import json, sys; sys.path.insert(0, %r); import bench; "
-            "print(json.dumps(bench.cpu_baseline(%r)))" % (str(ROOT), name))
+            "print(json.dumps(bench.cpu_baseline(%r, %r)))" % (str(ROOT), name, budget_s))
     try:
-        out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True,
-                             text=True, timeout=300, check=True).stdout
-        return json.loads(out.strip().splitlines()[-1])
+        return _subprocess_json([sys.executable, "-c", code], env=env, timeout=300)
     except Exception:
-        return cpu_baseline(name)
+        return cpu_baseline(name, budget_s)
+
+
+def cpu_baselines_clean(names, budget_s: float):
+    """Short CPU-oracle timings of several workloads in ONE fresh interpreter."""
+    env = dict(os.environ, OMP_NUM_THREADS=str(os.cpu_count() or 1))
+    code = ("import json, sys; sys.path.insert(0, %r); import bench; "
+            "print(json.dumps({n: bench.cpu_baseline(n, %r) for n in %r}))"
+            % (str(ROOT), budget_s, list(names)))
+    try:
+        return _subprocess_json([sys.executable, "-c", code], env=env, timeout=600)
+    except Exception as exc:
+        print(f"[bench] CPU baselines of the workloads block failed: {exc}", file=sys.stderr)
+        return {}
 
 
 def run_reference(args):
@@ -436,7 +484,7 @@ def run_reference(args):
         "impl": "reference", "metric": "effective_weight_bandwidth", "value": v, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": el / max(1, args.steps) * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
+        "vs_baseline": None, "dtype": dtype_of(name), "data": "synthetic",
         "config": {"workload": c["desc"], "host_threads": last["cores"]},
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": last["cores"], "kind": last["kind"],
                          "sample": last["sample"]},
@@ -446,22 +494,124 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def ref_gpu_kernel_times(target_bytes: float):
+    """The reference's own CUDA kernels, compiled for sm_100a from their own
+    sources, timed by oracle/_ref/ref_gpu_bench in a process of its own (so that
+    this process never loads anything built from the reference)."""
+    exe = ROOT / "oracle" / "_ref" / "ref_gpu_bench"
+    if not exe.exists():
+        return {"unavailable": "oracle/_ref/ref_gpu_bench was not built (reference tree absent)"}
+    try:
+        return _subprocess_json([str(exe), str(target_bytes)], timeout=600)
+    except Exception as exc:
+        return {"unavailable": f"ref_gpu_bench failed: {exc}"}
+
+
+def run_refgpu(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    print(json.dumps({"impl": "refgpu", "unit": "us per launch",
+                      "protocol": "rotating replicas >> L2, CUDA graph, CUDA events",
+                      "ref_kernel_us": ref_gpu_kernel_times(args.replica_bytes)}), flush=True)
+
+
+def time_replicas(torch, stream, launch, R, replays, warm=3, graph=True):
+    """us per launch of `launch(i)`, i = 0..R-1 captured as one CUDA graph."""
+    with torch.cuda.stream(stream):
+        for i in range(R):
+            launch(i)
+        stream.synchronize()
+        g = None
+        if graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(R):
+                    launch(i)
+
+        def one():
+            if g is not None:
+                g.replay()
+            else:
+                for i in range(R):
+                    launch(i)
+        for _ in range(warm):
+            one()
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(replays):
+            one()
+        b.record(stream)
+        stream.synchronize()
+        return a.elapsed_time(b) * 1e3 / (replays * R)
+
+
+def roofline_of(case, us, name):
+    peak, peak_src = measured_peak()
+    achieved = case["bytes"] / (us * 1e-6) / 1e9
+    if "flops" in case:
+        # batch 64: 14.7 us of HBM time against 18.2 us of tensor time -> tensor bound
+        tpeak, tsrc = measured_tensor_peak()
+        tf = case["flops"] / (us * 1e-6) / 1e12
+        return {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s",
+                "frac": tf / tpeak, "peak_source": f"of {tsrc}", "traffic": ncu_traffic(name),
+                "hbm_frac": achieved / peak}
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "frac_of_spec_8tbs": achieved / SPEC_HBM_GBS,
+            "peak_source": f"of {peak_src}", "traffic": ncu_traffic(name)}
+
+
+def workloads_block(torch, dev, stream, target_bytes, skip):
+    """Every other workload of the family, each in a short graph loop."""
+    out = {}
+    plan = [(n, 64) for n in WORKLOADS if n != skip]
+    plan += [(n, mb) for n in ("qgemm_q3", "qgemm_nf4") for mb in (16, 32, 128)]
+    for name, mb in plan:
+        key = name if mb == 64 else f"{name}_m{mb}"
+        try:
+            wl = DeviceWorkload(name, dev, seed=1, target_bytes=target_bytes, Mb=mb)
+            est = time_replicas(torch, stream, wl.launch, wl.R, 2, warm=1)
+            replays = int(min(200, max(5, 40e3 / (est * wl.R))))  # about 40 ms
+            us = time_replicas(torch, stream, wl.launch, wl.R, replays)
+            roof = roofline_of(wl.case, us, name)
+            ent = {"us": us, "bound": roof["bound"], "frac": roof["frac"],
+                   "achieved": roof["achieved"], "unit": roof["unit"], "replicas": wl.R,
+                   "bytes": wl.bytes, "desc": wl.case["desc"]}
+            if "gather_bytes" in wl.case:
+                ent["gather_gbs"] = wl.case["gather_bytes"] / (us * 1e-6) / 1e9
+            out[key] = ent
+            del wl
+        except Exception as exc:
+            out[key] = {"error": str(exc)[:200]}
+        torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "refgpu"])
     ap.add_argument("--workload", default="nf4_gemv", choices=WORKLOADS)
     ap.add_argument("--replica-bytes", type=float, default=640e6,
                     help="bytes of packed weights resident per GPU (>> L2)")
+    ap.add_argument("--passes", type=int, default=0,
+                    help="graph replays per step (0: as many as make a step last about 10 ms)")
+    ap.add_argument("--batch", type=int, default=64, help="tokens of the batched workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="skip the block that times every other workload and the reference kernels")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly (for profilers)")
-    ap.add_argument("--gather", default="publish", choices=["publish", "fused", "nccl"],
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1: every rank its own shard of an N-times wider layer (weak), or "
+                         "the one layer's output features split over the ranks (strong)")
+    ap.add_argument("--gather", default=None, choices=["packets", "publish", "nccl"],
                     help="N > 1: how the output slices of a layer are gathered")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "refgpu":
+        return run_refgpu(args)
 
     import torch
     import torch.distributed as dist
@@ -478,50 +628,86 @@ def main():
         import datetime
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     hq.load_library()
+    name = args.workload
+    batched = name.startswith("qgemm")
+    strong = world > 1 and args.scaling == "strong"
+    if strong and not batched:
+        raise SystemExit("--scaling strong is wired for the batched workloads (qgemm_*)")
+    gather = args.gather or ("packets" if name == "nf4_gemv" else "publish")
+    if gather == "packets" and name != "nf4_gemv":
+        raise SystemExit("--gather packets is the NF4 GEMV's low-latency form")
+    if world > 1 and not (batched or name == "nf4_gemv"):
+        raise SystemExit("N > 1 is wired for nf4_gemv and the batched workloads")
 
-    wl = DeviceWorkload(args.workload, dev, seed=rank, target_bytes=args.replica_bytes)
-    R = wl.R
+    from hecbench_b200.shard import FeatureShard, PacketGather, PeerGather
+    shard = None
+    if strong:
+        n_total = 8192 if name.endswith("down") else 28672
+        shard = FeatureShard(rank, world, n_total, multiple=128)
+    # weak scaling: every rank holds a different layer shard (seed = rank); strong:
+    # all ranks cut their slice out of the same layer (seed 0)
+    wl = DeviceWorkload(name, dev, seed=0 if strong else rank, target_bytes=args.replica_bytes,
+                        Mb=args.batch, shard=shard)
+    R, c = wl.R, wl.case
     err = wl.check_one()
     if err is not None and err > 1e-2:
         raise SystemExit(f"parity guard failed before timing: rel err {err}")
 
-    # N > 1: every rank holds its output-feature shard of each of the R layers
-    # (weak scaling: the layer grows with N) and the slices of every layer are
-    # all-gathered over NCCL right after its kernel, as a decoder needs them.
+    # ---- N > 1: gathered outputs ------------------------------------------------
+    packets = peer = None
     gathered = None
-    peer = None
-    if world > 1 and args.workload == "nf4_gemv" and args.gather in ("publish", "fused"):
-        # fused GEMV + gather: the kernel stores its slice into every GPU's
-        # gathered vector over NVLink and flags it; a bounded wait follows
-        from hecbench_b200.shard import FeatureShard, PeerGather
-        c = wl.case
-        peer = PeerGather(FeatureShard(rank, world, world * c["N"]), slots=R, device=dev)
-    elif world > 1 and hasattr(wl, "out"):
-        gathered = [torch.empty(world * wl.out[i].numel(), dtype=wl.out[i].dtype, device=dev)
-                    for i in range(R)]
+    stride = 1
+    if world > 1:
+        if strong:
+            gshard = shard
+            rows_out = c["Mb"]
+        else:
+            n_loc = wl.out[0].shape[-1] if hasattr(wl, "out") else 0
+            gshard = FeatureShard(rank, world, world * n_loc)
+            rows_out = c.get("Mb", 1)
+        if gather == "packets":
+            packets = PacketGather(gshard, slots=R, device=dev)
+            stride = (world * c["N"]) // c["K"]
+        elif gather == "publish" and hasattr(wl, "out"):
+            peer = PeerGather(gshard, slots=R, device=dev, rows=rows_out)
+        elif hasattr(wl, "out"):
+            gathered = [torch.empty(world * wl.out[i].numel(), dtype=wl.out[i].dtype, device=dev)
+                        for i in range(R)]
 
     def layer(i):
-        if peer is not None:
-            c = wl.case
-            if args.gather == "fused":
-                # the GEMV's last CTA sends the slice itself; bounded wait after it
-                peer.gemv_nf4(i, wl.x[i], wl.B[i], wl.absmax[i], wl.lut, c["K"], c["bs"])
+        if packets is not None:
+            # every finished row goes as a packet into all GPUs' vector i; layer i > 0
+            # takes its input from the packets of layer i - 1 (every stride-th element
+            # of the gathered output), as the next layer of a decoder would
+            if i == 0:
+                packets.gemv_nf4(0, wl.x[0], wl.B[0], wl.absmax[0], wl.lut, c["K"], c["bs"],
+                                 weights_resident=PDL)
             else:
-                # ordinary GEMV into this rank's slice of its own gathered vector,
-                # then one small kernel: peer stores over NVLink, flags, bounded wait
-                hq.gemv_nf4(wl.x[i], wl.B[i], wl.absmax[i], wl.lut, c["N"], c["K"], c["bs"], 0,
-                            peer.local_slice(i), weights_resident=PDL)
-                peer.publish(i)
+                packets.gemv_nf4(i, None, wl.B[i], wl.absmax[i], wl.lut, c["K"], c["bs"],
+                                 weights_resident=PDL, a_slot=i - 1, a_stride=stride)
+            return
+        if peer is not None:
+            # ordinary kernel into this rank's slice of its own gathered buffer, then
+            # one small kernel: peer stores over NVLink, flags, bounded wait
+            wl.launch(i, out=peer.local_slice(i))
+            peer.publish(i)
             return
         wl.launch(i)
         if gathered is not None:
             dist.all_gather_into_tensor(gathered[i], wl.out[i].view(-1))
+
+    def finish_pass():
+        if packets is not None:  # the last layer's gather is waited for explicitly
+            packets.unpack(R - 1, out=pk_plain)
+    pk_plain = (torch.empty(packets.slot_elems, dtype=torch.float16, device=dev)
+                if packets is not None else None)
 
     stream = torch.cuda.Stream()
     graph = None
     with torch.cuda.stream(stream):
         for i in range(R):
             layer(i)
+        finish_pass()
         stream.synchronize()
         if not args.no_graph:
             try:
@@ -529,22 +715,43 @@ def main():
                 with torch.cuda.graph(graph, stream=stream):
                     for i in range(R):
                         layer(i)
+                    finish_pass()
             except Exception as exc:  # NCCL capture not available: launch eagerly
                 print(f"[bench] graph capture failed ({exc}); running eagerly", file=sys.stderr)
                 graph = None
                 torch.cuda.synchronize()
 
-    def step():
+    def one_pass():
         if graph is not None:
             graph.replay()
         else:
             for i in range(R):
                 layer(i)
+            finish_pass()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # passes per step: a step lasts about 10 ms, so that 20 steps give the clock
+    # sampler (20 ms period) ten samples or more
+    with torch.cuda.stream(stream):
+        one_pass(); stream.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            one_pass()
+        stream.synchronize()
+        est_pass_ms = (time.perf_counter() - t0) / 3 * 1e3
+    passes = args.passes or int(min(4096, max(1, round(10.0 / max(est_pass_ms, 1e-3)))))
+    if world > 1:
+        tp = torch.tensor([passes], device=dev)
+        dist.broadcast(tp, 0)
+        passes = int(tp.item())
+
+    def step():
+        for _ in range(passes):
+            one_pass()
 
     sampler = ClockSampler(local) if rank == 0 else None
     with torch.cuda.stream(stream):
@@ -566,39 +773,36 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms = float(tt.item())
 
-    # ceiling of a kernel with this footprint: pure streaming read of the same
-    # number of bytes per launch over the same rotating buffers, same graph setup
-    read_us = None
-    if args.workload == "nf4_gemv" and world == 1:
-        lib = hq.load_library()
-        sink = torch.zeros(1, dtype=torch.int32, device=dev)
-        nbytes = wl.B[0].numel()
-        with torch.cuda.stream(stream):
-            def reads():
-                for i in range(R):
-                    lib.hq_probe_stream_read(wl.B[i].data_ptr(), nbytes, sink.data_ptr(),
-                                             torch.cuda.current_stream().cuda_stream)
-            reads()
-            stream.synchronize()
-            rg = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(rg, stream=stream):
-                reads()
-            for _ in range(3):
-                rg.replay()
-            ra = torch.cuda.Event(enable_timing=True); rb = torch.cuda.Event(enable_timing=True)
-            ra.record(stream)
-            for _ in range(min(args.steps, 100)):
-                rg.replay()
-            rb.record(stream)
-            stream.synchronize()
-            read_us = ra.elapsed_time(rb) * 1e3 / (R * min(args.steps, 100))
-
-    launches = R * args.steps
+    launches = R * passes * args.steps
     us_per_launch = ms * 1e3 / launches
-    total_bytes = wl.bytes * launches * world
+    # weak: every rank streams a whole case per launch; strong: the ranks share one
+    total_bytes = wl.bytes * launches * (1 if strong else world)
     value = total_bytes / (ms * 1e-3) / 1e9
 
-    # ---- end to end: host activations in, host results out, every launch ----
+    # ---- N > 1: the gathered results of this program against the CPU oracle --------
+    gather_check = None
+    if world > 1 and (packets is not None or peer is not None or gathered is not None):
+        gather_check = check_gather(torch, dist, wl, packets, peer, gathered, rank, world, stride,
+                                    strong, shard)
+
+    # ---- N = 1 extras: isolated launches, pure-read ceiling -----------------------
+    read_us = no_pdl_us = None
+    if name == "nf4_gemv" and world == 1:
+        no_pdl_us = time_replicas(torch, stream, lambda i: wl.launch(i, pdl=False), R, 50)
+        probe = ROOT / "hecbench_b200" / "libhq_probe.so"
+        if probe.exists():
+            plib = ctypes.CDLL(str(probe))
+            plib.hq_probe_stream_read.argtypes = [ctypes.c_void_p, ctypes.c_size_t,
+                                                  ctypes.c_void_p, ctypes.c_void_p]
+            sink = torch.zeros(1, dtype=torch.int32, device=dev)
+            nbytes = wl.B[0].numel()
+            read_us = time_replicas(
+                torch, stream,
+                lambda i: plib.hq_probe_stream_read(wl.B[i].data_ptr(), nbytes, sink.data_ptr(),
+                                                    torch.cuda.current_stream().cuda_stream),
+                R, 50)
+
+    # ---- end to end: host activations in, host results out, every launch ----------
     e2e = None
     io = wl.host_io()
     if io is not None:
@@ -610,12 +814,13 @@ def main():
             chains = [torch.cuda.Stream() for _ in range(min(4, R))] if world == 1 else []
 
             def e2e_one(i):
-                wl.x[i].copy_(hin[i], non_blocking=True)
+                if packets is None or i == 0:
+                    wl.x[i].copy_(hin[i], non_blocking=True)
                 layer(i)
-                if peer is not None:  # this rank's slice of the gathered vector
-                    c = wl.case
-                    hout[i].copy_(peer.slot(i)[rank * c["N"]:(rank + 1) * c["N"]],
-                                  non_blocking=True)
+                if packets is not None:
+                    return
+                if peer is not None:  # this rank's slice of the gathered buffer
+                    hout[i].copy_(peer.local_slice(i), non_blocking=True)
                 else:
                     hout[i].copy_(wl.out[i], non_blocking=True)
 
@@ -623,6 +828,11 @@ def main():
                 if not chains:
                     for i in range(R):
                         e2e_one(i)
+                    if packets is not None:
+                        # the chain's result: this rank's slice of the last gathered vector
+                        finish_pass()
+                        hout[R - 1].copy_(pk_plain[rank * c["N"]:(rank + 1) * c["N"]],
+                                          non_blocking=True)
                     return
                 for cs in chains:
                     cs.wait_stream(stream)
@@ -648,10 +858,11 @@ def main():
                     torch.cuda.synchronize()
 
             def e2e_step():
-                if e2e_graph is not None:
-                    e2e_graph.replay()
-                else:
-                    e2e_pass()
+                for _ in range(passes):
+                    if e2e_graph is not None:
+                        e2e_graph.replay()
+                    else:
+                        e2e_pass()
             for _ in range(3):
                 e2e_step()
             barrier()
@@ -662,58 +873,105 @@ def main():
             b.record(stream)
             barrier()
             ems = a.elapsed_time(b)
+            # latency of ONE request alone: copy in, kernel, copy out, wait
+            single_us = None
+            if world == 1:
+                lat = []
+                for k in range(60):
+                    i = k % R
+                    stream.synchronize()
+                    t0 = time.perf_counter()
+                    e2e_one(i)
+                    stream.synchronize()
+                    lat.append((time.perf_counter() - t0) * 1e6)
+                single_us = float(np.median(lat[10:]))
         if world > 1:
             tt = torch.tensor([ems], device=dev)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             ems = float(tt.item())
+        n_in = R if packets is None else 1
+        n_out = R if packets is None else 1
         e2e = {"value": total_bytes / (ems * 1e-3) / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hin)),
-               "d2h_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hout)),
+               "h2d_bytes_per_step": int(passes * sum(h.numel() * h.element_size()
+                                                      for h in hin[:n_in])),
+               "d2h_bytes_per_step": int(passes * sum(h.numel() * h.element_size()
+                                                      for h in hout[:n_out])),
                "us_per_call": ems * 1e3 / launches,
+               "single_request_latency_us": single_us,
                "launch": ("cuda graph of R x (H2D copy, kernel, D2H copy)" if e2e_graph is not None
-                          else "eager") + (f", {len(chains)} requests in flight" if chains else "")}
+                          else "eager") + (f", {len(chains)} requests in flight" if chains else
+                                           (", one chain of R dependent layers: input of layer 0 "
+                                            "from the host, last gathered slice back to the host"
+                                            if packets is not None else ""))}
 
-    if peer is not None and int(peer.status.item()) != 0:
+    status_bad = any(g is not None and int(g.status.item()) != 0 for g in (packets, peer))
+    if status_bad:
         raise SystemExit("a bounded gather wait ran out")
+    ok = gather_check is None or gather_check["ranks_ok"] == world
     if rank == 0:
-        peak, peak_src = measured_peak()
-        achieved = wl.bytes / (us_per_launch * 1e-6) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_source": f"of {peak_src}",
-                "traffic": ncu_traffic(args.workload), "same_size_pure_read_us": read_us}
-        if "flops" in wl.case:
-            # batch 64: 14.7 us of HBM time against 18.2 us of tensor time -> tensor bound
-            tpeak, tsrc = measured_tensor_peak()
-            tf = wl.case["flops"] / (us_per_launch * 1e-6) / 1e12
-            roof = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s",
-                    "frac": tf / tpeak, "peak_source": f"of {tsrc}",
-                    "traffic": ncu_traffic(args.workload), "hbm_frac": achieved / peak}
+        roof = roofline_of(c, us_per_launch, name)
+        if strong:  # per-GPU kernel works on 1/world of the layer
+            roof["note"] = "per-GPU share of the layer; achieved is the whole job's rate"
+        if read_us is not None:
+            roof["same_size_pure_read_us"] = read_us
+        par = "single GPU"
+        if world > 1:
+            how = {"packets": "every finished row stored as an 8-byte {value, epoch} packet into "
+                              "every GPU's vector over NVLink by the GEMV itself; the next layer "
+                              "reads its input from the packets (bounded waits)",
+                   "publish": "slices copied into every GPU's gathered buffer by our own kernel "
+                              "(peer stores over NVLink + flags), bounded wait after every layer",
+                   "nccl": "NCCL all-gather of the slices after every layer"}[gather]
+            par = (f"output features sharded over {world} GPUs ({args.scaling} scaling), "
+                   f"gather '{gather}': {how}")
         line = {
             "metric": "effective_weight_bandwidth", "value": value, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": DTYPE[args.workload], "data": "synthetic",
-            "config": {"workload": wl.case["desc"], "replicas_per_gpu": R,
-                       "resident_weight_bytes_per_gpu": wl.bytes * R,
+            "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if strong else "weak",
+            "vs_baseline": None, "dtype": dtype_of(name), "data": "synthetic",
+            "config": {"workload": c["desc"], "replicas_per_gpu": R,
+                       "passes_per_step": passes, "launches_per_step": R * passes,
+                       "resident_weight_bytes_per_gpu": int(wl.bytes * R /
+                                                            (world if strong else 1)),
                        "l2": "inputs larger than L2 (replicas rotate, R x bytes >> 126 MB)",
                        "algorithmic_bytes_per_launch": wl.bytes,
                        "launch": ("cuda graph of R launches" if graph is not None else "eager") +
                                  ("; weights flagged resident: a launch fetches its weights while "
                                   "the previous launch's tail drains (programmatic dependent launch)"
-                                  if PDL and args.workload == "nf4_gemv" else ""),
-                       "parallelism": ("single GPU" if world == 1 else
-                                       f"output features sharded over {world} GPUs, " +
-                                       (f"gather '{args.gather}': slices stored into every GPU's "
-                                        "gathered vector by our own kernel (peer stores over "
-                                        "NVLink + flags), bounded wait after every layer"
-                                        if peer is not None else
-                                        "NCCL all-gather of the slices after every layer"))},
+                                  if PDL and name == "nf4_gemv" else ""),
+                       "parallelism": par},
             "us_per_gemv": us_per_launch,
             "roofline": roof,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }
+        if no_pdl_us is not None:
+            line["value_no_pdl"] = wl.bytes / (no_pdl_us * 1e-6) / 1e9
+            line["us_per_gemv_no_pdl"] = no_pdl_us
+            line["roofline"]["frac_no_pdl"] = line["value_no_pdl"] / roof["peak"]
+        if gather_check is not None:
+            line["gather_check"] = gather_check
+        if world == 1 and name == "nf4_gemv" and not args.no_workloads:
+            del wl
+            torch.cuda.empty_cache()
+            block = workloads_block(torch, dev, stream, args.replica_bytes, skip=name)
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+            ref = ref_gpu_kernel_times(args.replica_bytes)
+            for k, v in ref.items():
+                if k in block and isinstance(v, dict):
+                    block[k]["ref_kernel_us"] = v.get("us")
+                    block[k]["ref_kernel_launch"] = v.get("launch")
+            if "unavailable" in ref:
+                line["ref_kernel"] = ref
+            if not args.no_cpu_baseline:
+                cpu = cpu_baselines_clean([n for n in WORKLOADS if n != name and n in block], 1.5)
+                for k, v in cpu.items():
+                    block[k]["cpu_baseline_us"] = v.get("us_per_full_call")
+                    block[k]["cpu_cores"] = v.get("cores")
+            line["workloads"] = block
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline_clean(args.workload)
+            line["cpu_baseline"] = cpu_baseline_clean(name)
         print(json.dumps(line), flush=True)
     if world > 1:
         # Tearing the NCCL communicator down after its collectives were captured in
@@ -723,7 +981,82 @@ def main():
         torch.cuda.synchronize()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(0 if ok else 1)
+
+
+def check_gather(torch, dist, wl, packets, peer, gathered, rank, world, stride, strong, shard):
+    """Replica 0 and replica R-1 of this rank's gathered results against the CPU
+    oracle of the whole (world x wider, or sharded) layer.  For the oracle every
+    rank contributes the first rows of its weights of those two replicas."""
+    from oracle import oracle as O
+    c, R, name = wl.case, wl.R, wl.name
+    dev = wl.dev
+    worst = 0.0
+    rows = 128
+
+    def allgather_np(t):
+        out = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(out, t.contiguous())
+        return [o.cpu().numpy() for o in out]
+
+    for i in sorted({0, R - 1}):
+        if name == "nf4_gemv":
+            n_loc = c["N"]
+            if packets is not None:
+                got = packets.unpack(i, check_epoch=False).cpu().numpy()
+                if i == 0:
+                    x = None
+                else:
+                    prev = packets.unpack(i - 1, check_epoch=False).cpu().numpy()
+                    x = np.ascontiguousarray(prev[::stride][:c["K"]])
+            else:
+                got = (peer.slot(i) if peer is not None else gathered[i]).cpu().numpy()
+                x = None
+            # weak scaling: rank r computed its slice from ITS input vector (and table)
+            xs = allgather_np(wl.x[i])
+            luts = allgather_np(wl.lut)
+            Bs = allgather_np(wl.B[i][:rows * c["K"] // 2])
+            As = allgather_np(wl.absmax[i][:rows * c["K"] // c["bs"]])
+            for r in range(world):
+                xr = xs[r] if (x is None or i == 0) else x
+                ref = O.nf4_gemv_f64(xr, Bs[r], As[r], luts[r], rows, c["K"], c["bs"], 0)
+                worst = max(worst, O.rel_err(
+                    got[r * n_loc:r * n_loc + rows].astype(np.float64), ref))
+        elif name.startswith("qgemm"):
+            Mb, K = c["Mb"], c["K"]
+            n_loc = wl.n_local
+            if peer is not None:
+                got = peer.slot(i).cpu().numpy()  # [G][Mb][n_loc]
+            else:
+                got = gathered[i].view(world, Mb, n_loc).cpu().numpy()
+            Xs = allgather_np(wl.x[i])
+            if name.startswith("qgemm_q3"):
+                mats = allgather_np(wl.mat[i][:, :rows])
+                scs = allgather_np(wl.sc[:, :rows]); zs = allgather_np(wl.z[:, :rows])
+                for r in range(world):
+                    W16 = O.q3g_dequant_f16(np.ascontiguousarray(mats[r]),
+                                            np.ascontiguousarray(scs[r]),
+                                            np.ascontiguousarray(zs[r]), K, rows, 128)
+                    ref = O.gemm_f16_f64(Xs[r], W16)
+                    worst = max(worst, O.rel_err(got[r][:, :rows].astype(np.float64), ref))
+            else:
+                Bs = allgather_np(wl.B[i][:rows * K // 2])
+                As = allgather_np(wl.absmax[:rows * K // c["bs"]])
+                luts = allgather_np(wl.lut)
+                for r in range(world):
+                    W16 = O.nf4_dequant_f16(Bs[r], As[r], luts[r], rows * K, c["bs"],
+                                            0).reshape(rows, K)
+                    ref = O.gemm_f16_nk_f64(Xs[r], W16)
+                    worst = max(worst, O.rel_err(got[r][:, :rows].astype(np.float64), ref))
+        else:
+            return None
+    ok = torch.tensor([1 if worst < 1e-2 else 0], device=dev)
+    dist.all_reduce(ok)
+    w = torch.tensor([worst], device=dev)
+    dist.all_reduce(w, op=dist.ReduceOp.MAX)
+    return {"max_rel_err": float(w.item()), "ranks_ok": int(ok.item()),
+            "checked": f"replicas 0 and {R - 1}, first {rows} output features of every rank's "
+                       "slice, on every rank's own gathered copy, against the fp64 CPU oracle"}
 
 
 if __name__ == "__main__":

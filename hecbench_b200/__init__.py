@@ -23,6 +23,7 @@ from .api import (  # noqa: F401
     nQWeight_fp16,
     qgemm_q3,
     qgemm_nf4,
+    qgemm_reset_workspaces,
     vecquant3_dequant,
     vecquant3matmul,
     vecquant3matmul_faster,
@@ -32,6 +33,6 @@ __all__ = [
     "HqError", "lib_path", "load_library",
     "vecquant3matmul", "vecquant3matmul_faster", "vecquant3_dequant",
     "kQuantize", "dequantize_nf4", "gemv_nf4",
-    "nQWeight_fp16", "matmul", "qgemm_q3", "qgemm_nf4", "code1x16_matvec", "code2x8_matvec",
+    "nQWeight_fp16", "matmul", "qgemm_q3", "qgemm_nf4", "qgemm_reset_workspaces", "code1x16_matvec", "code2x8_matvec",
     "NF4_HIGH_NIBBLE_FIRST", "NF4_LOW_NIBBLE_FIRST", "NF4_WEIGHTS_RESIDENT",
 ]

@@ -251,7 +251,10 @@ _qgemm_ws = {}
 
 
 def _qgemm_workspace(lib, device, Mb: int, N: int):
-    key = (device, Mb, N)
+    """Zero-initialised split-K scratch, one per (device, stream, Mb, N): calls on
+    different streams may overlap on the GPU and must not share the fp32 partial
+    sums and tile counters."""
+    key = (device, _stream(), Mb, N)
     ws = _qgemm_ws.get(key)
     if ws is None:
         ws = torch.zeros(lib.hq_qgemm_workspace_bytes(Mb, N), dtype=torch.uint8, device=device)
@@ -259,13 +262,23 @@ def _qgemm_workspace(lib, device, Mb: int, N: int):
     return ws.data_ptr(), ws.numel()
 
 
+def qgemm_reset_workspaces() -> None:
+    """Re-zero every cached split-K scratch on its device.  Call this after a
+    batched product reported status 1 (a bounded in-kernel wait ran out): such a
+    call may leave partial sums and tile counters behind, and the kernels rely on
+    finding the scratch zero."""
+    for ws in _qgemm_ws.values():
+        ws.zero_()
+
+
 def qgemm_q3(X, mat, scales, zeros, N: int, K: int, group_size: int = 128,
              out: Optional[torch.Tensor] = None,
              status: Optional[torch.Tensor] = None, split_k: bool = True) -> torch.Tensor:
     """Y[Mb][N] = X[Mb][K] @ dequant(mat) for the GPTQ 3-bit layout with per-group
     fp16 scales / zeros [K/group_size][N] (no counterpart in the reference tree).
-    `status` (int32[1], optional) receives 1 if a bounded in-kernel wait ran out.
-    With split_k a zero-initialised scratch matrix is kept per (device, Mb, N)."""
+    `status` (int32[1], optional) receives 1 if a bounded in-kernel wait ran out;
+    call qgemm_reset_workspaces() before the next product in that case.
+    With split_k a zero-initialised scratch matrix is kept per (device, stream, Mb, N)."""
     lib = load_library()
     Mb = X.shape[0]
     if out is None:

@@ -179,10 +179,9 @@ int hq_aqlm_1x16_matvec(const void* codes, const void* x_half, void* out_half, c
   cudaStream_t st = (cudaStream_t)stream;
 #define HQ_AQLM_LAUNCH(VPL)                                                                  \
   {                                                                                          \
-    auto kern = aqlm_1x16_kernel<VPL>;                                                       \
+    constexpr auto kern = aqlm_1x16_kernel<VPL>;                                             \
     if (smem > 48 * 1024) {                                                                  \
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                           (int)smem);                                       \
+      cudaError_t e = ensure_dynamic_smem<kern>(smem);                                       \
       if (e != cudaSuccess) return cuda_status(e);                                           \
     }                                                                                        \
     kern<<<grid, kWarps1x16 * 32, smem, st>>>(                                               \

@@ -6,12 +6,25 @@
 // The same sequence of fp32 compares is executed here, so the result is
 // bit-exact for ANY table (sorted or not, NaN inputs included).
 //
-// Design.  5 bytes per element of HBM traffic; the search is 7 dependent
-// table reads per element, so shared-memory bandwidth is the second wall.  The
-// table is replicated once per bank (table[entry][lane]) so every lookup of a
-// warp is conflict-free whatever the 32 pivots are, and the first two levels
-// (pivots 127, 63/191) come from registers.  Each thread quantizes four
-// consecutive elements (one 16-byte load, one 4-byte store).
+// Design.  5 bytes per element of HBM traffic; the search is a chain of
+// dependent table reads per element, so instruction issue and shared-memory
+// bandwidth are the second wall.  The table is replicated once per bank
+// (table[entry][lane]) so every lookup of a warp is conflict-free whatever the
+// 32 pivots are, and the first two levels (pivots 127, 63/191) come from
+// registers.  Each thread quantizes four consecutive elements (one 16-byte
+// load, one 4-byte store).
+//
+// Only the pivot is tracked through the search.  The reference also carries
+// (lower_pivot, lower) and (upper_pivot, upper), the last pivots at which the
+// compare went up resp. down, but with strides 64, 32, .., 1 these are
+// functions of the final pivot P alone: after the last "down" at pivot p with
+// stride s every later step goes up, so P = p - s + (s - 1) = p - 1, i.e.
+// upper_pivot = P + 1 (and P = 254, upper_pivot = 255 when no step went down);
+// symmetrically lower_pivot = P - 1, or 0 when no step went up (then P = 0).
+// `upper` and `lower` are the table entries at those indices - for any table,
+// sorted or not, because the argument is about indices only.  So the final
+// test reads ONE neighbour, code[P + 1] or code[max(P - 1, 0)], and the result
+// is the one the reference's compare sequence gives, NaN inputs included.
 #include "hq_common.cuh"
 
 namespace hq {
@@ -19,30 +32,25 @@ namespace {
 
 constexpr int kThreads = 256;
 
-__device__ __forceinline__ uint32_t quantize_one(const float* __restrict__ tab_lane, float x,
-                                                 float c127, float c63, float c191, float c0,
-                                                 float c255) {
-  // tab_lane points at table[0][lane]; entry p is tab_lane[p * 32].
-  int pivot, upper_pivot = 255, lower_pivot = 0;
-  float lower = -1.0f, upper = 1.0f, val;
-  // step i = 64 (val = code[127])
-  if (x > c127) { lower_pivot = 127; lower = c127; pivot = 191; val = c191; }
-  else          { upper_pivot = 127; upper = c127; pivot = 63;  val = c63; }
+// tab_lane points at table[0][lane]; entry p is at byte offset p * 128.
+__device__ __forceinline__ uint32_t quantize_one(const unsigned char* __restrict__ tab_lane,
+                                                 float x, float c127, float c63, float c191) {
+  // step i = 64 (val = code[127]): decided from registers
+  const bool up0 = x > c127;
+  float val = up0 ? c191 : c63;
+  int off = up0 ? 191 * 128 : 63 * 128;  // byte offset of the pivot's table row
 #pragma unroll
   for (int i = 32; i > 0; i >>= 1) {
-    if (x > val) { lower_pivot = pivot; lower = val; pivot += i; }
-    else         { upper_pivot = pivot; upper = val; pivot -= i; }
-    val = tab_lane[pivot * 32];
+    off += (x > val) ? i * 128 : -i * 128;
+    val = *reinterpret_cast<const float*>(tab_lane + off);
   }
-  if (upper_pivot == 255) upper = c255;
-  if (lower_pivot == 0) lower = c0;
-  if (x > val) {
-    const float midpoint = (upper + val) * 0.5f;
-    return x > midpoint ? upper_pivot : pivot;
-  } else {
-    const float midpoint = (lower + val) * 0.5f;
-    return x < midpoint ? lower_pivot : pivot;
-  }
+  // off / 128 is the final pivot P, val = code[P]
+  const bool gt = x > val;
+  const int nb_off = max(off + (gt ? 128 : -128), 0);
+  const float nb = *reinterpret_cast<const float*>(tab_lane + nb_off);
+  const float midpoint = (nb + val) * 0.5f;
+  const bool step = gt ? (x > midpoint) : (x < midpoint);
+  return (uint32_t)(step ? nb_off : off) >> 7;
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -60,9 +68,9 @@ bnb_quantize_kernel(const float* __restrict__ code, const float* __restrict__ A,
     for (int q = 0; q < 8; q++) row[(q + tid) & 7] = v4;  // rotate to spread banks
   }
   __syncthreads();
-  const float* tab_lane = table + lane;
-  const float c127 = tab_lane[127 * 32], c63 = tab_lane[63 * 32], c191 = tab_lane[191 * 32];
-  const float c0 = tab_lane[0], c255 = tab_lane[255 * 32];
+  const unsigned char* tab_lane = reinterpret_cast<const unsigned char*>(table + lane);
+  const float c127 = table[127 * 32 + lane], c63 = table[63 * 32 + lane],
+              c191 = table[191 * 32 + lane];
 
   const size_t nvec = n >> 2;
   const size_t stride = (size_t)gridDim.x * kThreads;
@@ -71,20 +79,20 @@ bnb_quantize_kernel(const float* __restrict__ code, const float* __restrict__ A,
   if (vec_ok) {
     for (size_t v = (size_t)blockIdx.x * kThreads + tid; v < nvec; v += stride) {
       uint4 raw = ldg_stream_u4(A + 4 * v);
-      uint32_t q0 = quantize_one(tab_lane, __uint_as_float(raw.x), c127, c63, c191, c0, c255);
-      uint32_t q1 = quantize_one(tab_lane, __uint_as_float(raw.y), c127, c63, c191, c0, c255);
-      uint32_t q2 = quantize_one(tab_lane, __uint_as_float(raw.z), c127, c63, c191, c0, c255);
-      uint32_t q3 = quantize_one(tab_lane, __uint_as_float(raw.w), c127, c63, c191, c0, c255);
+      uint32_t q0 = quantize_one(tab_lane, __uint_as_float(raw.x), c127, c63, c191);
+      uint32_t q1 = quantize_one(tab_lane, __uint_as_float(raw.y), c127, c63, c191);
+      uint32_t q2 = quantize_one(tab_lane, __uint_as_float(raw.z), c127, c63, c191);
+      uint32_t q3 = quantize_one(tab_lane, __uint_as_float(raw.w), c127, c63, c191);
       reinterpret_cast<uint32_t*>(out)[v] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
     }
     // tail (n % 4 elements)
     if (blockIdx.x == 0 && tid < (int)(n & 3)) {
       const size_t i = (nvec << 2) + tid;
-      out[i] = (uint8_t)quantize_one(tab_lane, A[i], c127, c63, c191, c0, c255);
+      out[i] = (uint8_t)quantize_one(tab_lane, A[i], c127, c63, c191);
     }
   } else {
     for (size_t i = (size_t)blockIdx.x * kThreads + tid; i < n; i += stride)
-      out[i] = (uint8_t)quantize_one(tab_lane, A[i], c127, c63, c191, c0, c255);
+      out[i] = (uint8_t)quantize_one(tab_lane, A[i], c127, c63, c191);
   }
 }
 
@@ -98,17 +106,9 @@ extern "C" int hq_bnb_quantize_u8(const float* code256, const float* A, uint8_t*
   if (n == 0) return HQ_OK;
   if (!aligned4(A) || !aligned4(code256)) return HQ_ERR_MISALIGNED;
   const size_t smem = 256 * 32 * sizeof(float);
-  static thread_local int configured_device = -1;
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
+  constexpr auto kern = bnb_quantize_kernel;
+  const cudaError_t e = ensure_dynamic_smem<kern>(smem);
   if (e != cudaSuccess) return cuda_status(e);
-  if (configured_device != dev) {
-    // the attribute is per function per device; setting it again is harmless
-    e = cudaFuncSetAttribute(bnb_quantize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem);
-    if (e != cudaSuccess) return cuda_status(e);
-    configured_device = dev;
-  }
   const size_t want = (n / 4 + kThreads - 1) / kThreads;
   const size_t cap = (size_t)sm_count() * 6;
   const unsigned grid = (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));

@@ -672,8 +672,8 @@ template <int FMT>
 int launch_qgemm(const CUtensorMap& map_x, const CUtensorMap& map_w, const CUtensorMap& map_s,
                  const CUtensorMap& map_z, const QgemmParams& prm, hq_stream_t stream) {
   const size_t smem = qgemm_smem_bytes<FMT>(prm.tokens_padded);
-  cudaError_t e = cudaFuncSetAttribute(qgemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem);
+  constexpr auto kern = qgemm_kernel<FMT>;
+  cudaError_t e = ensure_dynamic_smem<kern>(smem);
   if (e != cudaSuccess) return cuda_status(e);
   qgemm_kernel<FMT><<<dim3(prm.N / kTileN, prm.ksplit), kThreads, smem, (cudaStream_t)stream>>>(
       map_x, map_w, map_s, map_z, prm);

@@ -43,6 +43,15 @@ def q3_pack(codes: np.ndarray) -> np.ndarray:
     return w.astype(np.uint32).view(np.int32).reshape(K // 32 * 3, width)
 
 
+def q3_words(K: int, width: int, seed: int = 0) -> np.ndarray:
+    """Packed quant3MatMul words int32[K*3/32][width] drawn directly: 32 uniform
+    3-bit codes fill 96 bits exactly, so uniform codes and uniform words are the
+    same distribution.  For large shapes where the unpacked codes are not needed."""
+    assert K % 32 == 0
+    w = _rng(seed, 5).integers(0, 2**32, size=(K // 32 * 3, width), dtype=np.uint32)
+    return w.view(np.int32)
+
+
 def nf4_levels(seed: int = 0) -> np.ndarray:
     """A 16-entry sorted level table in [-1, 1] with exact -1, 0 and 1 (the
     shape of a normal-float table; the values are seeded, not a published

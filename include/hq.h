@@ -242,8 +242,14 @@ int hq_aqlm_2x8_matvec(const void* codes, const void* x_half, void* out_half,
  * N % 128 == 0, K % group_size == 0, group_size % 64 == 0.  workspace
  * (nullable) is zero-initialised device scratch of hq_qgemm_workspace_bytes
  * bytes that lets the kernel split K over several CTAs when N alone gives too
- * few tiles to fill the GPU; every call leaves it zero.  status_word (device
- * int, nullable) is set to 1 if a bounded in-kernel wait ran out. */
+ * few tiles to fill the GPU; every call that ends with status 0 leaves it
+ * zero.  Two rules follow: (1) one workspace serves one stream - calls that may
+ * overlap on the GPU (different streams, several host threads) need a
+ * workspace each, or they race on the partial sums and tile counters and give
+ * wrong results without any error; (2) after a call that set the status word
+ * the workspace may hold partial sums and counters: clear it (cudaMemsetAsync
+ * on the same stream) before it is used again.  status_word (device int,
+ * nullable) is set to 1 if a bounded in-kernel wait ran out. */
 size_t hq_qgemm_workspace_bytes(int Mb, int N);
 int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_half,
                     const void* zeros_half, void* Y_half, int Mb, int N, int K, int group_size,

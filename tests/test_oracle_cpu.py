@@ -233,3 +233,41 @@ def test_batched_nf4_oracle_agrees_with_gemv_oracle(oracle):
             # the mat-vec oracle multiplies lut*absmax in fp64; the batched one rounds
             # each weight to fp16 first, as the kernel under test does
             assert np.allclose(Y[j], y, rtol=2e-3, atol=2e-3 * np.abs(y).max())
+
+
+def test_bnb_pivot_only_rule_equals_dquantize(oracle):
+    """The GPU kernel tracks only the pivot through the search and derives the
+    bracket from the final pivot P (upper_pivot = P + 1, lower_pivot = max(P - 1, 0)).
+    This numpy restatement of that rule must agree with the restated dQuantize<0>
+    (quantBnB-cuda/main.cu:13-66) for ANY table - sorted, unsorted, with NaN
+    entries - and any input, and with the reference-generated golden file."""
+    def pivot_only(code, A):
+        x = A.astype(np.float32)
+        with np.errstate(invalid="ignore", over="ignore"):
+            P = np.where(x > code[127], 191, 63)
+            val = code[P]
+            i = 32
+            while i > 0:
+                P = P + np.where(x > val, i, -i)
+                val = code[P]
+                i >>= 1
+            gt = x > val
+            nb = np.maximum(P + np.where(gt, 1, -1), 0)
+            mid = (code[nb] + val) * np.float32(0.5)
+            return np.where(np.where(gt, x > mid, x < mid), nb, P).astype(np.uint8)
+
+    g = np.load(GOLDEN / "bnb_golden.npz")
+    assert np.array_equal(pivot_only(g["code"], g["A"]), g["out"])
+    rng = np.random.default_rng(1)
+    for t in range(8):
+        code = rng.standard_normal(256).astype(np.float32)
+        if t % 3 == 0:
+            code = np.sort(code)
+        if t % 4 == 1:
+            code[rng.integers(0, 256, 5)] = np.nan
+        A = (rng.standard_normal(50000) * 2).astype(np.float32)
+        A[:50] = np.nan
+        A[50:100] = np.inf
+        A[100:150] = -np.inf
+        A[200:456] = code
+        assert np.array_equal(pivot_only(code, A), oracle.bnb_quantize(code, A)), t
