@@ -41,6 +41,10 @@ SIGNATURES = {
                                                                c_void_p]),
     "hq_qgemm_nf4_f16": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p,
                                                                 c_void_p]),
+    "hq_vllm_static_scaled_int8_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, C.c_float,
+                                                 C.c_int32, c_void_p]),
+    "hq_vllm_dynamic_scaled_int8_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int,
+                                                  c_void_p, c_void_p, c_void_p]),
     "hq_aqlm_2x8_matvec": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p, c_void_p]),
 }
 

@@ -137,6 +137,57 @@ def gemv_nf4(A, B, absmax, lut16, N: int, K: int, blocksize: int = 64,
 
 
 # --------------------------------------------------------------------------
+# quantVLLM: per-token int8 activation quantization
+# --------------------------------------------------------------------------
+
+_VLLM_DTYPE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def _vllm_input(input, hidden_size: int, num_tokens: int) -> int:
+    if not isinstance(input, torch.Tensor) or not input.is_cuda:
+        raise TypeError("input: must be a CUDA tensor (there is no CPU path)")
+    if input.dtype not in _VLLM_DTYPE:
+        raise TypeError(f"input: expected float16, bfloat16 or float32, got {input.dtype}")
+    if not input.is_contiguous() or input.numel() != hidden_size * num_tokens:
+        raise TypeError("input: must be contiguous [num_tokens][hidden_size]")
+    return _VLLM_DTYPE[input.dtype]
+
+
+def static_scaled_int8_quant(output, input, hidden_size: int, num_tokens: int, scale: float,
+                             azp: int = 0) -> None:
+    """static_scaled_int8_quant<scalar_t>(output, input, hidden_size, num_tokens,
+    scale, azp) (quantVLLM-cuda/main.cu:137-153): azp == 0 selects the form
+    without zero point, as in the reference."""
+    lib = load_library()
+    code = _vllm_input(input, hidden_size, num_tokens)
+    if output.numel() != input.numel():
+        raise ValueError("output and input differ in size")
+    with torch.cuda.device(input.device):
+        check("hq_vllm_static_scaled_int8_quant", lib.hq_vllm_static_scaled_int8_quant(
+            _dev(output, torch.int8, "output"), input.data_ptr(), code, hidden_size, num_tokens,
+            float(scale), int(azp), _stream()))
+
+
+def dynamic_scaled_int8_quant(output, input, hidden_size: int, num_tokens: int, scales,
+                              azp=None) -> None:
+    """dynamic_scaled_int8_quant<scalar_t>(output, input, hidden_size, num_tokens,
+    scales, azp) (quantVLLM-cuda/main.cu:155-172): scales float32[num_tokens]
+    and, when azp (int32[num_tokens]) is given, the per-token zero points are
+    written too."""
+    lib = load_library()
+    code = _vllm_input(input, hidden_size, num_tokens)
+    if output.numel() != input.numel() or scales.numel() < num_tokens:
+        raise ValueError("output / scales are too small")
+    if azp is not None and azp.numel() < num_tokens:
+        raise ValueError("azp is too small")
+    with torch.cuda.device(input.device):
+        check("hq_vllm_dynamic_scaled_int8_quant", lib.hq_vllm_dynamic_scaled_int8_quant(
+            _dev(output, torch.int8, "output"), input.data_ptr(), code, hidden_size, num_tokens,
+            _dev(scales, torch.float32, "scales"),
+            0 if azp is None else _dev(azp, torch.int32, "azp"), _stream()))
+
+
+# --------------------------------------------------------------------------
 # lut-gemm
 # --------------------------------------------------------------------------
 

@@ -7,6 +7,7 @@ only) go to hecbench_b200/build/dropin/:
   dropin_lutgemm       reference main.cu, nQWeight_fp16.cu + shim/lut-gemm/kernels.cu
   dropin_quantBnB      shim/quantBnB/main.cu (reference code.h on the include path)
   dropin_quantAQLM     shim/quantAQLM/main.cu
+  dropin_quantVLLM     shim/quantVLLM/main.cu (reference reference.h, utils.h on the include path)
 
 The reference sources are compiled from where they lie; for quant3MatMul the
 driver is copied into a temporary directory first, because `#include
@@ -81,6 +82,13 @@ def build(force: bool = False):
     drv = SHIM / "quantAQLM" / "main.cu"
     if stale(tgt, [drv]):
         _run([NVCC, *COMMON, drv, "-o", tgt])
+    built.append(tgt)
+
+    tgt = OUT / "dropin_quantVLLM"
+    drv = SHIM / "quantVLLM" / "main.cu"
+    if stale(tgt, [drv]):
+        _run([NVCC, *COMMON, "--expt-relaxed-constexpr", f"-I{src / 'quantVLLM-cuda'}", drv,
+              "-o", tgt])
     built.append(tgt)
     return built
 

@@ -232,6 +232,34 @@ int hq_aqlm_2x8_matvec(const void* codes, const void* x_half, void* out_half,
                        const void* codebooks, int prob_m, int prob_k, const void* scales_half,
                        hq_stream_t stream);
 
+/* ---------------- per-token int8 activation quantization (quantVLLM) ---------------- */
+
+/* input element types of the hq_vllm_* entries */
+#define HQ_DTYPE_F16 0
+#define HQ_DTYPE_BF16 1
+#define HQ_DTYPE_F32 2
+
+/* Replaces static_scaled_int8_quant<scalar_t>(output, input, hidden_size,
+ * num_tokens, scale, azp) (quantVLLM-cuda/main.cu:137-153) and its kernels
+ * (main.cu:12-46): out[t][i] = sat8(rint(x[t][i] / scale)) when azp == 0, else
+ * sat8(sat32(rint(x / scale)) + azp).  input is [num_tokens][hidden_size] of
+ * the given element type, out int8 of the same shape.  Byte exact against the
+ * reference's host functions (reference.h:1-31). */
+int hq_vllm_static_scaled_int8_quant(int8_t* out, const void* input, int dtype, int hidden_size,
+                                     int num_tokens, float scale, int32_t azp,
+                                     hq_stream_t stream);
+
+/* Replaces dynamic_scaled_int8_quant<scalar_t>(output, input, hidden_size,
+ * num_tokens, scales, azp) (quantVLLM-cuda/main.cu:155-172) and its kernels
+ * (main.cu:48-134): per token row, scales[t] = absmax / 127 and out =
+ * sat8(rint(x * (127 / absmax))) when azp == NULL; else scales[t] = (max -
+ * min) / 255, azp[t] = rint(-128 - min / scales[t]) and out = sat8(sat32(rint(x
+ * / scales[t])) + azp[t]), the running maximum starting at FLT_MIN as in the
+ * reference.  Byte exact against reference.h:33-93. */
+int hq_vllm_dynamic_scaled_int8_quant(int8_t* out, const void* input, int dtype, int hidden_size,
+                                      int num_tokens, float* scales, int32_t* azp,
+                                      hq_stream_t stream);
+
 /* ---------------- batched dequant-GEMM (tensor cores) ---------------- */
 
 /* Y[Mb][N] = X[Mb][K] * W[K][N] with W the GPTQ 3-bit layout of quant3MatMul

@@ -47,15 +47,24 @@ def build_oracle(force: bool = False) -> Path:
 
 
 def build_ref_cpu(force: bool = False):
+    """The reference's CPU code of the path: quantBnB-omp/main.cpp and the host
+    reference loops of quantVLLM-cuda/reference.h."""
     out = HERE / "_ref" / "libref_cpu.so"
     if not (REF / "src" / "quantBnB-omp" / "main.cpp").exists():
         return out if out.exists() else None
-    src = HERE / "ref_cpu.cpp"
-    if force or _stale(out, [src]):
+    # each harness sees only its own benchmark's directory (both have a utils.h)
+    parts = {"ref_cpu.cpp": ["quantBnB-omp", "quantBnB-cuda"], "ref_cpu_vllm.cpp": ["quantVLLM-cuda"]}
+    if force or _stale(out, [HERE / p for p in parts]):
         out.parent.mkdir(exist_ok=True)
-        _run(["g++", "-O3", "-std=c++17", "-pthread", "-fPIC", "-shared", "-w",
-              f"-I{REF / 'src' / 'quantBnB-omp'}", f"-I{REF / 'src' / 'quantBnB-cuda'}",
-              src, "-o", out])
+        cuda_inc = Path(NVCC).resolve().parent.parent / "include"
+        objs = []
+        for name, dirs in parts.items():
+            obj = out.parent / (Path(name).stem + ".o")
+            _run(["g++", "-O2", "-std=c++17", "-pthread", "-fPIC", "-w", "-fno-fast-math",
+                  "-ffp-contract=off", *[f"-I{REF / 'src' / d}" for d in dirs], f"-I{cuda_inc}",
+                  "-c", HERE / name, "-o", obj])
+            objs.append(obj)
+        _run(["g++", "-shared", "-pthread", *objs, "-o", out])
     return out
 
 

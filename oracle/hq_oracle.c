@@ -23,6 +23,7 @@
  * Every function cites the reference file:line it follows (paths relative to
  * the HeCBench source tree).
  */
+#include <float.h>
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -631,4 +632,95 @@ int orc_num_threads(void) {
 #else
   return 1;
 #endif
+}
+
+/* ------------------------------------------------------------------------
+ * Per-token int8 activation quantization (quantVLLM).  Restates the host
+ * reference loops of quantVLLM-cuda/reference.h:1-93 with the helpers of
+ * quantVLLM-cuda/utils.h:9-63 (float_to_int8_rn, float_to_int32_rn,
+ * int32_to_int8); the CUDA kernels of main.cu:12-134 compute the same values
+ * and the reference driver compares the two with memcmp (main.cu:222-267).
+ * dtype: 0 = fp16, 1 = bf16, 2 = fp32 input.  Conversions of NaN to an integer,
+ * undefined in the host reference, give 0 here (what the device gives).
+ * ------------------------------------------------------------------------ */
+static inline float vllm_in(const void* in, int dtype, size_t i) {
+  if (dtype == 0) return orc_h2f(((const uint16_t*)in)[i]);
+  if (dtype == 1) {
+    union { uint32_t u; float f; } v;
+    v.u = (uint32_t)((const uint16_t*)in)[i] << 16;
+    return v.f;
+  }
+  return ((const float*)in)[i];
+}
+/* utils.h:9-28 */
+static inline int8_t vllm_f2i8_rn(float x) {
+  float dst = nearbyintf(x);
+  if (dst != dst) return 0;
+  dst = dst < -128.0f ? -128.0f : (127.0f < dst ? 127.0f : dst);
+  return (int8_t)dst;
+}
+/* utils.h:30-53 */
+static inline int32_t vllm_f2i32_rn(float x) {
+  float dst = nearbyintf(x);
+  if (dst != dst) return 0;
+  if (dst >= 2147483648.0f) return INT32_MAX;
+  if (dst <= -2147483648.0f) return INT32_MIN;
+  return (int32_t)dst;
+}
+/* utils.h:55-63 */
+static inline int8_t vllm_i32_to_i8(int32_t x) {
+  return (int8_t)(x < -128 ? -128 : (127 < x ? 127 : x));
+}
+
+/* reference.h:1-31: azp == 0 selects the form without zero point, as the
+ * launcher does (main.cu:147-152) */
+void orc_vllm_static_quant(const void* in, int dtype, int8_t* out, float scale, int32_t azp,
+                           long long num_tokens, int hidden) {
+#pragma omp parallel for
+  for (long long t = 0; t < num_tokens; t++)
+    for (int i = 0; i < hidden; i++) {
+      size_t idx = (size_t)t * hidden + i;
+      float val = vllm_in(in, dtype, idx);
+      if (azp == 0) out[idx] = vllm_f2i8_rn(val / scale);
+      else out[idx] = vllm_i32_to_i8((int32_t)((uint32_t)vllm_f2i32_rn(val / scale) + (uint32_t)azp));
+    }
+}
+
+/* reference.h:33-58 (azp_out == NULL) and :60-93 */
+void orc_vllm_dynamic_quant(const void* in, int dtype, int8_t* out, float* scale_out,
+                            int32_t* azp_out, long long num_tokens, int hidden) {
+#pragma omp parallel for
+  for (long long t = 0; t < num_tokens; t++) {
+    size_t row = (size_t)t * hidden;
+    if (azp_out == NULL) {
+      float absmax_val = 0.0f;
+      for (int i = 0; i < hidden; i++) {
+        float val = vllm_in(in, dtype, row + i);
+        val = val > 0.0f ? val : -val;
+        absmax_val = val > absmax_val ? val : absmax_val;
+      }
+      scale_out[t] = absmax_val / 127.0f;
+      float tmp_scale = 127.0f / absmax_val;
+      for (int i = 0; i < hidden; i++)
+        out[row + i] = vllm_f2i8_rn(vllm_in(in, dtype, row + i) * tmp_scale);
+    } else {
+      /* the reference starts the maximum at the smallest positive normal float */
+      float max_val = FLT_MIN, min_val = FLT_MAX;
+      for (int i = 0; i < hidden; i++) {
+        float val = vllm_in(in, dtype, row + i);
+        max_val = max_val < val ? val : max_val;
+        min_val = val < min_val ? val : min_val;
+      }
+      float scale_val = (max_val - min_val) / 255.0f;
+      float azp_float = nearbyintf(-128.0f - min_val / scale_val);
+      int32_t azp_val = azp_float != azp_float ? 0 : (int32_t)azp_float;
+      scale_out[t] = scale_val;
+      azp_out[t] = azp_val;
+      for (int i = 0; i < hidden; i++) {
+        float val = vllm_in(in, dtype, row + i);
+        out[row + i] =
+            vllm_i32_to_i8((int32_t)((uint32_t)vllm_f2i32_rn(val / scale_val) + (uint32_t)azp_val));
+      }
+    }
+  }
 }

@@ -152,6 +152,63 @@ def ref_bnb_quantize(A, threads: int = 0):
     return out
 
 
+# ---------------- quantVLLM: per-token int8 activation quantization ----------------
+
+VLLM_DTYPES = {"float16": 0, "bfloat16": 1, "float32": 2}
+
+
+def _vllm_in(x, dtype: str):
+    """fp16 arrays travel as float16, bf16 as uint16 bit patterns, fp32 as float32."""
+    code = VLLM_DTYPES[dtype]
+    want = {0: np.float16, 1: np.uint16, 2: np.float32}[code]
+    x = np.ascontiguousarray(x)
+    assert x.dtype == want and x.ndim == 2, (x.dtype, want)
+    return x, code
+
+
+def _vllm_static(fn, x, dtype, scale, azp):
+    x, code = _vllm_in(x, dtype)
+    out = np.empty(x.shape, dtype=np.int8)
+    fn(_ptr(x), C.c_int(code), _ptr(out), C.c_float(scale), C.c_int32(azp),
+       C.c_longlong(x.shape[0]), C.c_int(x.shape[1]))
+    return out
+
+
+def _vllm_dynamic(fn, x, dtype, with_azp):
+    x, code = _vllm_in(x, dtype)
+    out = np.empty(x.shape, dtype=np.int8)
+    scale = np.empty(x.shape[0], dtype=np.float32)
+    azp = np.empty(x.shape[0], dtype=np.int32) if with_azp else None
+    fn(_ptr(x), C.c_int(code), _ptr(out), _ptr(scale), _ptr(azp) if with_azp else None,
+       C.c_longlong(x.shape[0]), C.c_int(x.shape[1]))
+    return out, scale, azp
+
+
+def vllm_static_quant(x, dtype: str, scale: float, azp: int = 0) -> np.ndarray:
+    """static_scaled_int8_quant (quantVLLM-cuda/reference.h:1-31); azp == 0 = no zero point."""
+    return _vllm_static(lib().orc_vllm_static_quant, x, dtype, scale, azp)
+
+
+def vllm_dynamic_quant(x, dtype: str, with_azp: bool = False):
+    """dynamic_scaled_int8_quant (reference.h:33-93): (int8 out, fp32 scale per token,
+    int32 azp per token or None)."""
+    return _vllm_dynamic(lib().orc_vllm_dynamic_quant, x, dtype, with_azp)
+
+
+def ref_vllm_static_quant(x, dtype: str, scale: float, azp: int = 0):
+    r = ref_cpu()
+    if r is None or not hasattr(r, "ref_vllm_static_quant"):
+        return None
+    return _vllm_static(r.ref_vllm_static_quant, x, dtype, scale, azp)
+
+
+def ref_vllm_dynamic_quant(x, dtype: str, with_azp: bool = False):
+    r = ref_cpu()
+    if r is None or not hasattr(r, "ref_vllm_dynamic_quant"):
+        return None
+    return _vllm_dynamic(r.ref_vllm_dynamic_quant, x, dtype, with_azp)
+
+
 # ---------------- nf4 ----------------
 
 def nf4_dequant_f16(B, absmax, lut16, n, blocksize=64, low_first=0) -> np.ndarray:

@@ -46,3 +46,10 @@ def test_quantaqlm_driver_passes():
     out = run("dropin_quantAQLM")
     assert out.count("kernel execution time") == 4
     assert out.strip().splitlines()[-1] == "PASS", out
+
+
+def test_quantvllm_driver_passes():
+    """The reference run's own shape (4096 tokens x 5137), fewer repetitions."""
+    out = run("dropin_quantVLLM", 4096, 5137, 20)
+    assert out.count("Average execution time of") == 12
+    assert out.count("PASS") == 3 and "FAIL" not in out, out

@@ -271,3 +271,23 @@ def test_bnb_pivot_only_rule_equals_dquantize(oracle):
         A[100:150] = -np.inf
         A[200:456] = code
         assert np.array_equal(pivot_only(code, A), oracle.bnb_quantize(code, A)), t
+
+
+VLLM_DTYPES = ["float16", "bfloat16", "float32"]
+
+
+@pytest.mark.parametrize("dtype", VLLM_DTYPES)
+def test_vllm_quant_oracle_matches_reference_golden(oracle, dtype):
+    """The C restatement of quantVLLM-cuda/reference.h against the golden file
+    produced by the reference's own host functions (tests/golden/make_golden_vllm.py)."""
+    g = np.load(GOLDEN / "vllm_golden.npz")
+    x = g[f"x_{dtype}"]
+    assert np.array_equal(oracle.vllm_static_quant(x, dtype, 0.1, 0), g[f"static_{dtype}"])
+    assert np.array_equal(oracle.vllm_static_quant(x, dtype, 0.1, 54), g[f"static_azp_{dtype}"])
+    q, s, _ = oracle.vllm_dynamic_quant(x, dtype, False)
+    assert np.array_equal(q, g[f"dyn_{dtype}"])
+    assert np.array_equal(s.view(np.uint32), g[f"dyn_scale_{dtype}"].view(np.uint32))
+    q, s, z = oracle.vllm_dynamic_quant(x, dtype, True)
+    assert np.array_equal(q, g[f"dynazp_{dtype}"])
+    assert np.array_equal(s.view(np.uint32), g[f"dynazp_scale_{dtype}"].view(np.uint32))
+    assert np.array_equal(z, g[f"dynazp_azp_{dtype}"])
