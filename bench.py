@@ -137,6 +137,12 @@ def _host_case(name: str, seed: int, Mb: int = 64):
         codes, x, cbs, scales = synth.aqlm_2x8_case(m, k, seed)
         return dict(m=m, k=k, codes=codes, x=x, cbs=cbs, scales=scales,
                     bytes=codes.nbytes + 4 * 8192, desc="AQLM 2x8 mat-vec 4096x4096")
+    if name in ("vllm_static_f16", "vllm_dynamic_f16", "vllm_dynamic_azp_f16"):
+        tokens, hidden = 4096, 5137  # the reference's own run (quantVLLM-cuda/Makefile:57)
+        x = (synth._rng(seed, 60).integers(0, 1000, (tokens, hidden)) - 300).astype(np.float16)
+        return dict(tokens=tokens, hidden=hidden, x=x, bytes=tokens * hidden * 3 + tokens * 8,
+                    desc=f"per-token int8 activation quantization {tokens}x{hidden} fp16 "
+                         f"({name[5:-4].replace('_', ' ')})")
     if name in ("qgemm_q3", "qgemm_q3_down"):
         K, N = (28672, 8192) if name.endswith("down") else (8192, 28672)
         G = K // 128
@@ -167,10 +173,13 @@ PDL = os.environ.get("HQ_BENCH_NO_PDL") != "1"
 
 WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "q3_gemv_f32_opt175b",
              "q3_gemv_f16_opt175b", "bnb_quantize", "lutgemm", "aqlm_1x16", "aqlm_2x8",
-             "qgemm_q3", "qgemm_nf4", "qgemm_q3_down", "qgemm_nf4_down"]
+             "qgemm_q3", "qgemm_nf4", "qgemm_q3_down", "qgemm_nf4_down",
+             "vllm_static_f16", "vllm_dynamic_f16", "vllm_dynamic_azp_f16"]
 
 
 def dtype_of(name: str) -> str:
+    if name.startswith("vllm"):
+        return "i8"
     return "f32" if name.startswith("q3_gemv_f32") else ("u8" if name == "bnb_quantize" else "f16")
 
 
@@ -242,6 +251,11 @@ class DeviceWorkload:
             self.x = [t(c["X"]) for _ in range(R)]
             self.out = [torch.empty((c["Mb"], self.n_local), dtype=torch.float16, device=dev)
                         for _ in range(R)]
+        elif name.startswith("vllm"):
+            self.xin = [t(rot(c["x"], i)) for i in range(R)]
+            self.q = torch.empty((c["tokens"], c["hidden"]), dtype=torch.int8, device=dev)
+            self.scales = torch.empty(c["tokens"], dtype=torch.float32, device=dev)
+            self.azp = torch.empty(c["tokens"], dtype=torch.int32, device=dev)
         elif name == "aqlm_2x8":
             self.codes = [t(rot(c["codes"], i)) for i in range(R)]
             self.cbs = t(c["cbs"])
@@ -272,6 +286,11 @@ class DeviceWorkload:
                                [m, m, m, 1 << 30], 65536)
         elif n == "aqlm_2x8":
             hq.code2x8_matvec(self.codes[i], self.x[i], self.out[i], self.cbs, c["m"], c["k"])
+        elif n == "vllm_static_f16":
+            hq.static_scaled_int8_quant(self.q, self.xin[i], c["hidden"], c["tokens"], 0.1, 0)
+        elif n.startswith("vllm_dynamic"):
+            hq.dynamic_scaled_int8_quant(self.q, self.xin[i], c["hidden"], c["tokens"],
+                                         self.scales, self.azp if "azp" in n else None)
         elif n.startswith("qgemm_q3"):
             hq.qgemm_q3(self.x[i], self.mat[i], self.sc, self.z, self.n_local, c["K"], 128,
                         out=self.out[i] if out is None else out)
@@ -399,6 +418,12 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
         m = c["m"]
         fn = lambda: O.aqlm_2x8_f64(c["codes"], c["x"], c["cbs"], m, c["k"])
         sample = "full mat-vec (fp64 oracle)"
+    elif name.startswith("vllm"):
+        if name == "vllm_static_f16":
+            fn = lambda: O.vllm_static_quant(c["x"], "float16", 0.1, 0)
+        else:
+            fn = lambda: O.vllm_dynamic_quant(c["x"], "float16", "azp" in name)
+        sample = "full tensor"
     elif name.startswith("qgemm_q3"):
         cols = 128
         mat = np.ascontiguousarray(c["mat"][:, :cols])

@@ -31,6 +31,19 @@ SIGNATURES = {
     "hq_gather_publish": (c_int, [c_void_p, C.c_longlong, c_int, c_void_p, c_void_p, c_int, c_int,
                                   C.c_uint, c_void_p, c_void_p]),
     "hq_gather_wait": (c_int, [c_void_p, c_void_p, c_int, C.c_uint, c_void_p, c_void_p]),
+    "hq_shard_layout": (c_int, [c_int, c_int, C.c_longlong, c_int, c_int, c_int, c_void_p, c_void_p,
+                                c_void_p]),
+    "hq_shard_create": (c_int, [c_void_p, c_void_p, c_int, C.c_longlong, c_int, c_int, c_int]),
+    "hq_shard_destroy": (None, [c_void_p]),
+    "hq_shard_stream": (c_void_p, [c_void_p, c_int]),
+    "hq_shard_nf4_gemv": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, C.c_longlong, c_void_p,
+                                  c_void_p, c_void_p, c_int, c_int, c_int]),
+    "hq_shard_unpack": (c_int, [c_void_p, c_int, c_int, c_void_p]),
+    "hq_shard_local_slice": (c_void_p, [c_void_p, c_int, c_int]),
+    "hq_shard_publish": (c_int, [c_void_p, c_int, c_int]),
+    "hq_shard_allgather_nccl": (c_int, [c_void_p, c_int]),
+    "hq_shard_gathered": (c_void_p, [c_void_p, c_int, c_int]),
+    "hq_shard_status": (c_int, [c_void_p, c_int, c_void_p]),
     "hq_lutgemm_workspace_bytes": (c_size_t, [c_int]),
     "hq_lutgemm_nqmv": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p, c_size_t, c_void_p]),
     "hq_lutgemm_nqmv_noalloc": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),

@@ -61,7 +61,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
 
     objs = [OBJ / (s.stem + ".o") for s in sources]
     if force or jobs or _newer(LIB, objs):
-        cmd = [NVCC, *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
+        cmd = [NVCC, *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stderr}")

@@ -55,6 +55,7 @@ const char* hq_status_string(int status) {
     case HQ_ERR_WORKSPACE: return "workspace missing or too small";
     case HQ_ERR_UNSUPPORTED: return "unsupported configuration";
     case HQ_ERR_TOO_LARGE: return "size beyond supported maximum";
+    case HQ_ERR_NCCL: return "NCCL call failed";
     default: return "unknown status";
   }
 }

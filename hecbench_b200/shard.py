@@ -216,11 +216,15 @@ class PeerGather:
     def publish(self, i: int) -> None:
         """Copy the local slice of buffer i to all peers, flag it, and wait (bounded)
         for the peers' slices of the same round."""
+        import ctypes
         from ._lib import check, load_library
         sh = self.shard
-        check("hq_gather_publish", load_library().hq_gather_publish(
-            self.peer_data.data_ptr(), i * self.slot_elems + sh.rank * self.slice_elems,
-            self.slice_elems, self.peer_flags.data_ptr(), self.sync.data_ptr(), sh.world, sh.rank,
+        lib = load_library()
+        first = ctypes.c_longlong()  # index arithmetic shared with the C hosts (hq_shard_layout)
+        check("hq_shard_layout", lib.hq_shard_layout(sh.world, self.rows, sh.n_local, self.slots,
+                                                     sh.rank, i, None, ctypes.byref(first), None))
+        check("hq_gather_publish", lib.hq_gather_publish(
+            self.peer_data.data_ptr(), first.value, self.slice_elems, self.peer_flags.data_ptr(), self.sync.data_ptr(), sh.world, sh.rank,
             self.max_polls, self.status.data_ptr(), torch.cuda.current_stream().cuda_stream))
 
     def wait_all(self) -> None:

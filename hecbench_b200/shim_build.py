@@ -8,6 +8,7 @@ only) go to hecbench_b200/build/dropin/:
   dropin_quantBnB      shim/quantBnB/main.cu (reference code.h on the include path)
   dropin_quantAQLM     shim/quantAQLM/main.cu
   dropin_quantVLLM     shim/quantVLLM/main.cu (reference reference.h, utils.h on the include path)
+  shard_demo           shim/shard/main.cu: one-process host of the hq_shard_* context
 
 The reference sources are compiled from where they lie; for quant3MatMul the
 driver is copied into a temporary directory first, because `#include
@@ -39,10 +40,9 @@ def _run(cmd, cwd=None):
 
 
 def build(force: bool = False):
-    """Returns the list of binaries built (empty when the reference tree is absent)."""
+    """Returns the list of binaries built (only shard_demo when the reference
+    tree is absent)."""
     src = REF / "src"
-    if not (src / "quant3MatMul-cuda" / "main.cu").exists():
-        return []
     OUT.mkdir(parents=True, exist_ok=True)
     lib = PKG / "libhq.so"
     built = []
@@ -52,6 +52,15 @@ def build(force: bool = False):
             return True
         t = target.stat().st_mtime
         return any(Path(d).exists() and Path(d).stat().st_mtime > t for d in [lib, *deps])
+
+    # our own multi-GPU host for the hq_shard_* context (no reference source involved)
+    tgt = OUT / "shard_demo"
+    drv = SHIM / "shard" / "main.cu"
+    if stale(tgt, [drv]):
+        _run([NVCC, *COMMON, drv, "-o", tgt])
+    built.append(tgt)
+    if not (src / "quant3MatMul-cuda" / "main.cu").exists():
+        return built
 
     # quant3MatMul: reference driver + our kernels.h
     tgt = OUT / "dropin_quant3MatMul"

@@ -32,7 +32,8 @@ enum {
   HQ_ERR_CUDA = -4,        /* a CUDA runtime call failed (see hq_last_cuda_error) */
   HQ_ERR_WORKSPACE = -5,   /* workspace missing or too small */
   HQ_ERR_UNSUPPORTED = -6, /* valid arguments the kernels do not cover */
-  HQ_ERR_TOO_LARGE = -7    /* size beyond a documented fixed maximum */
+  HQ_ERR_TOO_LARGE = -7,   /* size beyond a documented fixed maximum */
+  HQ_ERR_NCCL = -8         /* an NCCL call failed (the communicators were aborted) */
 };
 
 int hq_version(void);
@@ -165,6 +166,55 @@ int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
                       unsigned max_polls, int* status, hq_stream_t stream);
 int hq_gather_wait(const uint32_t* local_flags, const unsigned* sync_words, int world,
                    unsigned max_polls, int* status, hq_stream_t stream);
+
+/* (3) A context for hosts that drive all GPUs of the node from ONE process
+ * (C or C++ drivers; the Python layer runs one process per GPU instead and
+ * keeps its buffers in torch symmetric memory).  hq_shard_create enables peer
+ * access between the listed devices and allocates, per rank, a stream, `slots`
+ * gathered buffers in both forms above (packet vectors for rows == 1; fp16
+ * buffers [world][rows][n_local] with their flag words), the device-resident
+ * pointer tables, the sync words and a status word; with HQ_SHARD_NCCL it also
+ * loads libnccl.so.2 and creates one communicator per device (the sequence of
+ * ccl-cuda/main.cu:83-91).  n_local = output features per rank, rows = 1 for a
+ * mat-vec or the token batch for the batched product, slots >= 2.  The
+ * per-rank calls are asynchronous on that rank's stream (hq_shard_stream) and
+ * may be issued for rank 0 .. world-1 in turn from one host thread: a rank
+ * that waits for another's data polls with a bound of about a second.
+ *   hq_shard_nf4_gemv      NF4 GEMV of the rank's n_local rows with packet
+ *                          output into buffer `slot` of every rank; input
+ *                          A_half, or (A_half == NULL) elements 0, a_stride,
+ *                          2*a_stride, ... of the rank's own packet vector a_slot
+ *   hq_shard_unpack        plain fp16 copy of the rank's packet vector `slot`
+ *   hq_shard_local_slice   where an ordinary kernel on that rank's stream
+ *                          writes its slice [rows][n_local] of buffer `slot`
+ *   hq_shard_publish       copy + flag gather of that slice
+ *   hq_shard_allgather_nccl  the same gather by ncclAllGather, one grouped call
+ *                          for all ranks (ccl-cuda/main.cu:112-117); on failure
+ *                          the communicators are aborted (ncclCommAbort) and
+ *                          HQ_ERR_NCCL is returned
+ *   hq_shard_gathered      the rank's copy of gathered buffer `slot`
+ *   hq_shard_status        synchronises the rank's stream and returns its
+ *                          status word (1 = a bounded wait ran out)
+ * hq_shard_layout is the index arithmetic alone (no CUDA call): first packet
+ * of a rank's results and first fp16 element of its slice, counted from the
+ * start of the rank's packet resp. fp16 region, and elements per buffer. */
+#define HQ_SHARD_NCCL 1
+typedef struct hq_shard_ctx hq_shard_ctx;
+int hq_shard_layout(int world, int rows, long long n_local, int slots, int rank, int slot,
+                    long long* packet_index, long long* slice_index, long long* slot_elems);
+int hq_shard_create(hq_shard_ctx** ctx, const int* devices, int world, long long n_local, int rows,
+                    int slots, int flags);
+void hq_shard_destroy(hq_shard_ctx* ctx);
+hq_stream_t hq_shard_stream(hq_shard_ctx* ctx, int rank);
+int hq_shard_nf4_gemv(hq_shard_ctx* ctx, int rank, int slot, const void* A_half, int a_slot,
+                      long long a_stride, const uint8_t* B, const float* absmax,
+                      const float* lut16, int K, int blocksize, int flags);
+int hq_shard_unpack(hq_shard_ctx* ctx, int rank, int slot, void* out_half);
+void* hq_shard_local_slice(hq_shard_ctx* ctx, int rank, int slot);
+int hq_shard_publish(hq_shard_ctx* ctx, int rank, int slot);
+int hq_shard_allgather_nccl(hq_shard_ctx* ctx, int slot);
+const void* hq_shard_gathered(hq_shard_ctx* ctx, int rank, int slot);
+int hq_shard_status(hq_shard_ctx* ctx, int rank, int* status_out);
 
 /* ---------------- LUT-GEMM binary-coding mat-vec (lut-gemm) ---------------- */
 

@@ -82,6 +82,37 @@ def test_gather_and_noalloc_argument_errors_need_no_gpu(hq):
     assert lib.hq_lutgemm_nqmv_noalloc(p, p, p, p, None, 65536 + 4, 128, 3, 128, None) == -7
 
 
+def test_shard_layout_arithmetic_and_argument_errors(hq):
+    """Index arithmetic of the sharding context (no CUDA call) and the argument
+    checks of hq_shard_create that come before any CUDA call."""
+    lib = hq.load_library()
+    pk, sl, per = (ctypes.c_longlong() for _ in range(3))
+    ref = ctypes.byref
+    # mat-vec: 4 ranks x 1376 features, 3 slots
+    assert lib.hq_shard_layout(4, 1, 1376, 3, 2, 1, ref(pk), ref(sl), ref(per)) == 0
+    assert per.value == 4 * 1376
+    assert pk.value == 1 * 4 * 1376 + 2 * 1376
+    assert sl.value == pk.value
+    # batched: [world][rows][n_local] per slot
+    assert lib.hq_shard_layout(8, 64, 3584, 2, 5, 1, ref(pk), ref(sl), ref(per)) == 0
+    assert per.value == 8 * 64 * 3584
+    assert sl.value == per.value + 5 * 64 * 3584
+    for r in range(8):  # slices tile a slot exactly, in rank order
+        lib.hq_shard_layout(8, 64, 3584, 2, r, 0, None, ref(sl), None)
+        assert sl.value == r * 64 * 3584
+    assert lib.hq_shard_layout(0, 1, 8, 2, 0, 0, None, None, None) == -1
+    assert lib.hq_shard_layout(4, 1, 8, 2, 4, 0, None, None, None) == -1
+    assert lib.hq_shard_layout(4, 1, 8, 2, 0, 2, None, None, None) == -1
+    ctx = ctypes.c_void_p()
+    devs = (ctypes.c_int * 2)(0, 1)
+    assert lib.hq_shard_create(None, devs, 2, 128, 1, 2, 0) == -2
+    assert lib.hq_shard_create(ref(ctx), devs, 0, 128, 1, 2, 0) == -1
+    assert lib.hq_shard_create(ref(ctx), devs, 2, 128, 1, 1, 0) == -1  # fewer than two slots
+    assert lib.hq_shard_publish(None, 0, 0) == -1
+    assert lib.hq_shard_stream(None, 0) is None
+    lib.hq_shard_destroy(None)
+
+
 def test_python_layer_rejects_cpu_tensors(hq):
     import torch
     t = torch.zeros(256)
