@@ -16,6 +16,7 @@ SIGNATURES = {
     "hq_version": (c_int, []),
     "hq_status_string": (C.c_char_p, [c_int]),
     "hq_last_cuda_error": (c_int, []),
+    "hq_bounds_check_report": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int]),
     "hq_q3_gemv_f32": (c_int, [c_void_p] * 5 + [c_int, c_int, c_void_p]),
     "hq_q3_gemv_f16in": (c_int, [c_void_p] * 5 + [c_int, c_int, c_void_p]),
     "hq_q3_dequant_f32": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p]),
@@ -72,6 +73,20 @@ class HqError(RuntimeError):
 
 def lib_path() -> Path:
     return _LIB_PATH
+
+
+def load_checked_library():
+    """A separate handle on libhq_checked.so (the -DHQ_BOUNDS_CHECK build), with
+    the same prototypes; None when it was not built."""
+    path = _PKG / "libhq_checked.so"
+    if not path.exists():
+        return None
+    lib = C.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
 
 
 def load_library():

@@ -19,6 +19,7 @@ CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libhq.so"
 PROBE_LIB = PKG / "libhq_probe.so"
+CHECKED_LIB = PKG / "libhq_checked.so"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -75,5 +76,26 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB
 
 
+def build_checked(force: bool = False) -> Path:
+    """The same sources with -DHQ_BOUNDS_CHECK into hecbench_b200/libhq_checked.so:
+    every global access of the instrumented kernels is tested against its
+    buffer's extent, violations are recorded and skipped (never trapped), and
+    hq_bounds_check_report returns them.  The GPU tests run their small parity
+    cases through this library as well."""
+    global OBJ, LIB, PROBE_LIB, FLAGS
+    saved = (OBJ, LIB, PROBE_LIB, FLAGS)
+    try:
+        OBJ = PKG / "build" / "checked"
+        OBJ.parent.mkdir(exist_ok=True)
+        LIB = CHECKED_LIB
+        PROBE_LIB = OBJ / "probe_unused.so"
+        FLAGS = FLAGS + ["-DHQ_BOUNDS_CHECK"]
+        return build(force=force)
+    finally:
+        OBJ, LIB, PROBE_LIB, FLAGS = saved
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    if "--checked" in sys.argv:
+        print(build_checked(force="-f" in sys.argv))

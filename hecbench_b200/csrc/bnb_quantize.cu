@@ -78,6 +78,9 @@ bnb_quantize_kernel(const float* __restrict__ code, const float* __restrict__ A,
                       (reinterpret_cast<uintptr_t>(out) & 3u) == 0;
   if (vec_ok) {
     for (size_t v = (size_t)blockIdx.x * kThreads + tid; v < nvec; v += stride) {
+      if (!HQ_IN_BOUNDS(A + 4 * v, 16, A, n * 4, 301) ||
+          !HQ_IN_BOUNDS(reinterpret_cast<uint32_t*>(out) + v, 4, out, n, 302))
+        continue;
       uint4 raw = ldg_stream_u4(A + 4 * v);
       uint32_t q0 = quantize_one(tab_lane, __uint_as_float(raw.x), c127, c63, c191);
       uint32_t q1 = quantize_one(tab_lane, __uint_as_float(raw.y), c127, c63, c191);

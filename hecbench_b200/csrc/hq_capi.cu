@@ -1,5 +1,7 @@
 // Library-wide pieces of the C ABI: version, status strings, per-thread error
 // record and the cached SM count.
+#include <vector>
+
 #include "hq_common.cuh"
 
 namespace hq {
@@ -23,6 +25,16 @@ int sm_count() {
   return cached;
 }
 
+#ifdef HQ_BOUNDS_CHECK
+namespace {
+std::vector<BoundsAccess>& bounds_accessors() {
+  static std::vector<BoundsAccess> v;
+  return v;
+}
+}  // namespace
+void register_bounds_access(BoundsAccess fn) { bounds_accessors().push_back(fn); }
+#endif
+
 int reserved_smem_per_block() {
   static thread_local int cached_dev = -1;
   static thread_local int cached = 1024;
@@ -44,6 +56,35 @@ extern "C" {
 int hq_version(void) { return 100; }
 
 int hq_last_cuda_error(void) { return hq::last_cuda_error_ref(); }
+
+int hq_bounds_check_report(unsigned* violations, unsigned* site, unsigned long long* offset,
+                           unsigned long long* extent, int reset) {
+#ifdef HQ_BOUNDS_CHECK
+  unsigned total = 0, first_site = 0;
+  unsigned long long first_off = 0, first_ext = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return hq::cuda_status(e);
+  for (hq::BoundsAccess fn : hq::bounds_accessors()) {
+    hq::BoundsRecord r;
+    e = fn(&r, reset != 0);
+    if (e != cudaSuccess) return hq::cuda_status(e);
+    if (r.violations != 0 && total == 0) {
+      first_site = r.site;
+      first_off = r.offset;
+      first_ext = r.extent;
+    }
+    total += r.violations;
+  }
+  if (violations) *violations = total;
+  if (site) *site = first_site;
+  if (offset) *offset = first_off;
+  if (extent) *extent = first_ext;
+  return HQ_OK;
+#else
+  (void)violations; (void)site; (void)offset; (void)extent; (void)reset;
+  return HQ_ERR_UNSUPPORTED;  // this library was built without -DHQ_BOUNDS_CHECK
+#endif
+}
 
 const char* hq_status_string(int status) {
   switch (status) {

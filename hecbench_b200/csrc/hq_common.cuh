@@ -80,6 +80,50 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// ---- index-checked build (-DHQ_BOUNDS_CHECK) --------------------------------
+// compute-sanitizer may be unavailable where this library is developed, so the
+// kernels carry their own bounds checks, compiled in only with
+// -DHQ_BOUNDS_CHECK: every global access of an instrumented kernel is tested
+// against the extent of its buffer; a violation is RECORDED (count, first
+// site, first offset) and the access is SKIPPED - nothing traps, the kernel
+// runs to its end, and hq_bounds_check_report returns what was seen.  Each
+// translation unit has its own record; hq_capi.cu adds them up.
+struct BoundsRecord {
+  unsigned violations;
+  unsigned site;                // first violating access: 100 * file + access number
+  unsigned long long offset;    // its byte offset from the buffer's base (wraps if below)
+  unsigned long long extent;    // the buffer's size in bytes
+};
+#ifdef HQ_BOUNDS_CHECK
+static __device__ BoundsRecord g_bounds_rec;
+using BoundsAccess = cudaError_t (*)(BoundsRecord*, bool reset);
+void register_bounds_access(BoundsAccess fn);  // hq_capi.cu
+static cudaError_t bounds_access_this_tu(BoundsRecord* out, bool reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_bounds_rec, sizeof(BoundsRecord));
+  if (e == cudaSuccess && reset) {
+    const BoundsRecord zero = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(g_bounds_rec, &zero, sizeof(BoundsRecord));
+  }
+  return e;
+}
+static const int g_bounds_registered = (register_bounds_access(bounds_access_this_tu), 0);
+__device__ __forceinline__ bool in_bounds(const void* p, size_t bytes, const void* base,
+                                          size_t extent, unsigned site) {
+  const unsigned long long off = (unsigned long long)((const char*)p - (const char*)base);
+  if (off <= extent && bytes <= extent - off) return true;
+  if (atomicAdd(&g_bounds_rec.violations, 1u) == 0u) {
+    g_bounds_rec.site = site;
+    g_bounds_rec.offset = off;
+    g_bounds_rec.extent = extent;
+  }
+  return false;
+}
+#define HQ_IN_BOUNDS(p, bytes, base, extent, site) \
+  hq::in_bounds((p), (size_t)(bytes), (base), (size_t)(extent), (site))
+#else
+#define HQ_IN_BOUNDS(p, bytes, base, extent, site) true
+#endif
+
 // Streaming 128-bit load that does not allocate in L1: packed weights are
 // read exactly once.
 __device__ __forceinline__ uint4 ldg_stream_u4(const void* p) {

@@ -129,7 +129,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   // ---- stage the tile's inputs (zero beyond K) ----
   if (tid < TR * 32) {
     const int k = row0 * 32 + tid;
-    xs[tid] = (k < K) ? __half2float(x[k]) : 0.f;
+    xs[tid] = (k < K && HQ_IN_BOUNDS(x + k, 2, x, (size_t)K * 2, 206)) ? __half2float(x[k]) : 0.f;
   }
   // ---- ask the L2 for everything this CTA will read ----
   {
@@ -177,20 +177,29 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     for (int b = 0; b <= NB; b++) av[gi][b] = make_uint2(0, 0);
 
   // packed words of row r for the step whose first column (for this quad) is m
+  // extents of the caller's buffers, used only by the index-checked build
+  const size_t bw_bytes = (size_t)total_rows * nb_total * M * 4;
+  const size_t alpha_bytes = (size_t)(total_rows / rows_per_group) * nb_total * M * 2;
+  const size_t bias_bytes = (size_t)(total_rows / rows_per_group) * M * 2;
   auto load_row = [&](int r, int m) {
     if (r < nrows) {
 #pragma unroll
-      for (int b = 0; b < NB; b++)
-        wv[r][b] = ldg_stream_u4(src0 + (size_t)(r * nb_total + b) * M + (m - m0));
+      for (int b = 0; b < NB; b++) {
+        const uint32_t* src = src0 + (size_t)(r * nb_total + b) * M + (m - m0);
+        if (HQ_IN_BOUNDS(src, 16, bW, bw_bytes, 201)) wv[r][b] = ldg_stream_u4(src);
+      }
     }
   };
   auto load_group = [&](int gi, int m) {
     if (gi * RPG < nrows) {
       const int g = g0 + gi;
 #pragma unroll
-      for (int b = 0; b < NB; b++)
-        av[gi][b] = ldg_nc_u2(alpha + ((size_t)g * nb_total + b0 + b) * M + m);
-      if (q_bias != nullptr) av[gi][NB] = ldg_nc_u2(q_bias + (size_t)g * M + m);
+      for (int b = 0; b < NB; b++) {
+        const __half* src = alpha + ((size_t)g * nb_total + b0 + b) * M + m;
+        if (HQ_IN_BOUNDS(src, 8, alpha, alpha_bytes, 202)) av[gi][b] = ldg_nc_u2(src);
+      }
+      if (q_bias != nullptr && HQ_IN_BOUNDS(q_bias + (size_t)g * M + m, 8, q_bias, bias_bytes, 203))
+        av[gi][NB] = ldg_nc_u2(q_bias + (size_t)g * M + m);
     }
   };
   if (nsteps > 0 && m0 < m_end) {
@@ -319,7 +328,8 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     }
     // every lane of the quad now holds the four column sums: lane j == 0 adds
     // them to the scratch row with one 16-byte reduction
-    if (active && j == 0) red_add_v4_f32(ws + m, acc[0], acc[1], acc[2], acc[3]);
+    if (active && j == 0 && HQ_IN_BOUNDS(ws + m, 16, ws, (size_t)M * 4, 204))
+      red_add_v4_f32(ws + m, acc[0], acc[1], acc[2], acc[3]);
   }
 
   // ---- the last CTA of a column range converts it to fp16 and re-zeroes the scratch ----
@@ -336,6 +346,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     __threadfence();
     const int lo = per_range ? m_begin : 0, hi_m = per_range ? m_end : M;
     for (int mm = lo + tid * 4; mm < hi_m; mm += kThreads * 4) {
+      if (!HQ_IN_BOUNDS(out + mm, 8, out, (size_t)M * 2, 205)) continue;
       const float4 v = __ldcg(reinterpret_cast<const float4*>(ws + mm));
       const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
       *reinterpret_cast<uint2*>(out + mm) = make_uint2(half2_as_u32(h01), half2_as_u32(h23));

@@ -133,6 +133,8 @@ struct GemvParams {
   int world, rank;
   long long gather_offset;
   unsigned max_polls;           // limit of every wait for a packet, in polls
+  // buffer extents in bytes, used only by the index-checked build
+  unsigned long long b_bytes, absmax_bytes, a_bytes, out_bytes;
   int early_fetch;  // weights may be fetched before the preceding kernel in the stream has finished
   int* status;
 };
@@ -216,7 +218,8 @@ nf4_gemv_kernel(const GemvParams p) {
       const float* a = ap[i];                                                                   \
       if (!ALIGNED)                                                                             \
         a = p.absmax + (p.cpb_shift >= 0 ? (ci[i] >> p.cpb_shift) : (ci[i] / (uint32_t)p.cpb)); \
-      if (live[i]) {                                                                            \
+      if (live[i] && HQ_IN_BOUNDS(wp[i], 16, p.B, p.b_bytes, 101) &&                            \
+          HQ_IN_BOUNDS(a, 4, p.absmax, p.absmax_bytes, 102)) {                                  \
         cw[STAGE][i] = ldg_stream_u4(wp[i]);                                                    \
         cs[STAGE][i] = __ldg(a);                                                                \
       }                                                                                         \
@@ -296,7 +299,9 @@ nf4_gemv_kernel(const GemvParams p) {
     const uint4* xp = xsrc + 4 * (live[i] ? c : 0);
 #pragma unroll
     for (int t = 0; t < 4; t++) {
-      xr[i][t] = p.A_ll != nullptr ? xp[t] : __ldg(xp + t);
+      if (p.A_ll != nullptr) xr[i][t] = xp[t];
+      else if (HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 103)) xr[i][t] = __ldg(xp + t);
+      else xr[i][t] = make_uint4(0, 0, 0, 0);
       if (!live[i]) xr[i][t] = make_uint4(0, 0, 0, 0);
     }
   }
@@ -309,7 +314,7 @@ nf4_gemv_kernel(const GemvParams p) {
   auto store_result = [&](long long n, float v) {
     const __half h = __float2half_rn(v);
     if (p.peer_ll == nullptr) {
-      if (lane == 0) p.out[n] = h;
+      if (lane == 0 && HQ_IN_BOUNDS(p.out + n, 2, p.out, p.out_bytes, 104)) p.out[n] = h;
     } else if (my_peer != nullptr) {
       st_packet(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
     }
@@ -404,6 +409,11 @@ nf4_dequant_kernel(const uint8_t* __restrict__ B, const float* __restrict__ absm
   const float* lut_lane = lut + lane;
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t w = (size_t)blockIdx.x * kThreads + tid; w < nwords; w += stride) {
+    if (!HQ_IN_BOUNDS(reinterpret_cast<const uint32_t*>(B) + w, 4, B, nwords * 4, 111) ||
+        !HQ_IN_BOUNDS(absmax + w / (size_t)words_per_block, 4, absmax,
+                      ((nwords + words_per_block - 1) / words_per_block) * 4, 112) ||
+        !HQ_IN_BOUNDS(reinterpret_cast<uint4*>(out) + w, 16, out, nwords * 16, 113))
+      continue;
     const uint32_t codes = ldg_stream_u32(reinterpret_cast<const uint32_t*>(B) + w);
     const float s = __ldg(absmax + w / (size_t)words_per_block);
     uint32_t o[4];
@@ -580,6 +590,10 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   prm.max_polls = ll.max_polls ? ll.max_polls : kDefaultPolls;
   prm.status = ll.status;
   prm.early_fetch = (flags & HQ_NF4_WEIGHTS_RESIDENT) ? 1 : 0;
+  prm.b_bytes = (unsigned long long)N * (K / 2);
+  prm.absmax_bytes = ((unsigned long long)N * K + blocksize - 1) / blocksize * 4ull;
+  prm.a_bytes = (unsigned long long)K * 2;
+  prm.out_bytes = (unsigned long long)N * 2;
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef HQ_NF4_SWEEP
 #define HQ_NF4_SWEEP_LIST                                                                       \

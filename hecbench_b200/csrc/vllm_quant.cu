@@ -67,6 +67,10 @@ vllm_static_kernel(const T* __restrict__ in, int8_t* __restrict__ out, size_t n,
   const size_t stride = (size_t)gridDim.x * kThreads;
   const size_t nvec = vec_ok ? n / 16 : 0;
   for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < nvec; v += stride) {
+    if (!HQ_IN_BOUNDS(reinterpret_cast<const uint4*>(in) + v * kLoads, 16 * kLoads, in,
+                      n * sizeof(T), 401) ||
+        !HQ_IN_BOUNDS(reinterpret_cast<uint4*>(out) + v, 16, out, n, 402))
+      continue;
     uint4 raw[kLoads];
 #pragma unroll
     for (int l = 0; l < kLoads; l++)
@@ -128,7 +132,9 @@ vllm_dynamic_kernel(const T* __restrict__ in, int8_t* __restrict__ out,
 #pragma unroll
       for (int j = 0; j < EPT; j++) {
         const int i = tid + j * kThreads;
-        v[j] = i < hidden ? to_float<T>(row[i]) : (AZP ? FLT_MIN : 0.f);
+        v[j] = (i < hidden && HQ_IN_BOUNDS(row + i, sizeof(T), in,
+                                           (size_t)num_tokens * hidden * sizeof(T), 403))
+                   ? to_float<T>(row[i]) : (AZP ? FLT_MIN : 0.f);
       }
 #pragma unroll
       for (int j = 0; j < EPT; j++) {
@@ -165,7 +171,7 @@ vllm_dynamic_kernel(const T* __restrict__ in, int8_t* __restrict__ out,
 #pragma unroll
       for (int j = 0; j < EPT; j++) {
         const int i = tid + j * kThreads;
-        if (i < hidden)
+        if (i < hidden && HQ_IN_BOUNDS(orow + i, 1, out, (size_t)num_tokens * hidden, 404))
           orow[i] = (int8_t)(AZP ? f2i8_azp(__fdiv_rn(v[j], scale), azp)
                                  : f2i8_rn(__fmul_rn(v[j], mul)));
       }

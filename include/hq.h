@@ -41,6 +41,18 @@ const char* hq_status_string(int status);
 /* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
 int hq_last_cuda_error(void);
 
+/* Index-checked build.  A library compiled with -DHQ_BOUNDS_CHECK tests every
+ * global access of its instrumented kernels (NF4 GEMV and dequantize, LUT-GEMM,
+ * kQuantize, the int8 activation quantization) against the extent of the
+ * buffer the caller described; a violation is recorded and the access skipped,
+ * nothing traps.  This call synchronises the current device and returns the
+ * number of violations seen since the last reset, with the first one's site
+ * (100 * file + access number), byte offset and buffer extent.  An ordinary
+ * build returns HQ_ERR_UNSUPPORTED.  No counterpart in the reference (its own
+ * guards are commented out, quant3MatMul-cuda/kernels.h:25,41). */
+int hq_bounds_check_report(unsigned* violations, unsigned* site, unsigned long long* offset,
+                           unsigned long long* extent, int reset);
+
 /* ---------------- GPTQ 3-bit GEMV (quant3MatMul) ---------------- */
 
 /* Replaces vecquant3matmul<float> (quant3MatMul-cuda/kernels.h:171-190).
