@@ -5,8 +5,11 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
+import os
+
 _PKG = Path(__file__).resolve().parent
-_LIB_PATH = _PKG / "libhq.so"
+# HQ_LIBRARY selects another build of the same library (e.g. libhq_checked.so)
+_LIB_PATH = Path(os.environ["HQ_LIBRARY"]) if os.environ.get("HQ_LIBRARY") else _PKG / "libhq.so"
 _lib = None
 
 c_void_p, c_int, c_size_t = C.c_void_p, C.c_int, C.c_size_t

@@ -132,6 +132,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     xs[tid] = (k < K && HQ_IN_BOUNDS(x + k, 2, x, (size_t)K * 2, 206)) ? __half2float(x[k]) : 0.f;
   }
   // ---- ask the L2 for everything this CTA will read ----
+#ifndef HQ_LUT_NO_L2_PREFETCH
   {
     const uint32_t run_bytes = (uint32_t)(m_end - m_begin) * 4u;  // multiple of 16: M % 4 == 0
     if (tid < TR * NB) {
@@ -158,6 +159,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     }
   }
 
+#endif
   // ---- column steps of this warp: step s handles columns m0 + s*kWarps*32 ..+3 ----
   const int j = lane & 3;   // byte of the word this lane looks up
   const int cq = lane >> 2; // column quad inside the 32-column step

@@ -137,7 +137,22 @@ struct GemvParams {
   unsigned long long b_bytes, absmax_bytes, a_bytes, out_bytes;
   int early_fetch;  // weights may be fetched before the preceding kernel in the stream has finished
   int* status;
+#ifdef HQ_NF4_TRACE
+  unsigned long long* trace;  // development: [CTA][16] globaltimer stamps
+#endif
 };
+
+#ifdef HQ_NF4_TRACE
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define HQ_STAMP(i) \
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 16 + (i)] = gtime();
+#else
+#define HQ_STAMP(i)
+#endif
 
 __device__ __forceinline__ uint2 ld_packet(const uint2* p) {
   uint2 v;
@@ -180,6 +195,7 @@ nf4_gemv_kernel(const GemvParams p) {
   // Programmatic dependent launch: let the next kernel of the stream start its
   // own prologue as soon as this grid is resident, and do not touch global
   // memory that earlier work may still be writing before the wait below.
+  HQ_STAMP(0)
   pdl_launch_dependents();
   if (!p.early_fetch) pdl_wait();
   unsigned char* dsm = dsm_raw + (kLutImm - smem_u32(dsm_raw));
@@ -261,6 +277,7 @@ nf4_gemv_kernel(const GemvParams p) {
     }
   }
 
+  HQ_STAMP(1)
   // ---- prologue (overlaps the loads above): byte table, input slice ----
   for (int e4 = tid; e4 < 256 * 4; e4 += THREADS) {
     const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
@@ -274,7 +291,9 @@ nf4_gemv_kernel(const GemvParams p) {
   }
   // the input vector (and, without early_fetch, everything) is read only after
   // the preceding kernel has completed
+  HQ_STAMP(2)
   if (p.early_fetch) pdl_wait();
+  HQ_STAMP(3)
   // epoch of the latest completed gather: the input packets carry it, the
   // output packets of this launch carry the next one
   const uint32_t epoch_in =
@@ -307,6 +326,7 @@ nf4_gemv_kernel(const GemvParams p) {
   }
   __syncthreads();
 
+  HQ_STAMP(4)
   const uint32_t lane4 = lane * 4;
   // row j of this group is output element n_out + j * row_stride: stored as fp16
   // (lane 0) or as one packet per GPU of the node (lane r -> rank r)
@@ -364,7 +384,9 @@ nf4_gemv_kernel(const GemvParams p) {
       n_out += (long long)D * row_stride;
       parity ^= 1;
     }
+    HQ_STAMP(5 + min(j0 / D, 9))
   }
+  HQ_STAMP(15)
 #undef HQ_NF4_LOAD
   if (p.peer_ll != nullptr) {
     // the last CTA to finish records that this gather round is complete on the
@@ -594,6 +616,12 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   prm.absmax_bytes = ((unsigned long long)N * K + blocksize - 1) / blocksize * 4ull;
   prm.a_bytes = (unsigned long long)K * 2;
   prm.out_bytes = (unsigned long long)N * 2;
+#ifdef HQ_NF4_TRACE
+  {
+    const char* tp = getenv("HQ_NF4_TRACE_PTR");
+    prm.trace = tp ? reinterpret_cast<unsigned long long*>(strtoull(tp, nullptr, 0)) : nullptr;
+  }
+#endif
   cudaStream_t st = (cudaStream_t)stream;
 #ifdef HQ_NF4_SWEEP
 #define HQ_NF4_SWEEP_LIST                                                                       \

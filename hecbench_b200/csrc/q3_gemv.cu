@@ -28,6 +28,12 @@ constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 constexpr int kColsPerCta = 128;  // 32 lanes x 4 columns
 constexpr int kF16Words = 20;     // 18 half2 input pairs per group + 2 pad (16-byte rows)
+constexpr int kPrefetchAhead = 4; // turns (of kWarps groups) between an L2 prefetch and its use
+
+// Ask the L2 for `bytes` (a multiple of 16) at the 16-byte aligned address p.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 
 __device__ __forceinline__ float pow2f(int e) { return __int_as_float((e + 127) << 23); }
 
@@ -124,8 +130,27 @@ q3_gemv_kernel(const void* __restrict__ vec_, const int32_t* __restrict__ mat,
     n1 = ldg_stream_u4(p + width);
     n2 = ldg_stream_u4(p + 2 * (size_t)width);
   }
+  // lanes 0-2 also ask the L2 for the warp's 512-byte run of each of the three
+  // packed rows kPrefetchAhead turns ahead, so that the register loads (one
+  // turn ahead) find their lines in L2 instead of waiting for HBM
+  const int warp_col0 = blockIdx.x * kColsPerCta;
+  const uint32_t run_bytes = (uint32_t)min(kColsPerCta, max(0, width - warp_col0)) * 4u;
+  const int32_t* pf_base = mat + (size_t)g0 * 3 * width + warp_col0 + (size_t)lane * width;
+#ifdef HQ_Q3_NO_L2_PREFETCH
+  const bool pf_on = false;
+#else
+  const bool pf_on = true;
+#endif
+  if (pf_on && lane < 3 && run_bytes > 0) {
+#pragma unroll
+    for (int a = 1; a < kPrefetchAhead; a++)
+      if (warp + a * kWarps < ng)
+        l2_prefetch_bulk(pf_base + (size_t)(warp + a * kWarps) * 3 * width, run_bytes);
+  }
   for (int gi = warp; gi < ng; gi += kWarps) {
     const uint4 u0 = n0, u1 = n1, u2 = n2;
+    if (pf_on && lane < 3 && run_bytes > 0 && gi + kPrefetchAhead * kWarps < ng)
+      l2_prefetch_bulk(pf_base + (size_t)(gi + kPrefetchAhead * kWarps) * 3 * width, run_bytes);
     if (active && gi + kWarps < ng) {
       const int32_t* p = base + (size_t)(gi + kWarps) * 3 * width;
       n0 = ldg_stream_u4(p);
@@ -265,22 +290,33 @@ int q3_gemv_launch(const void* vec, const int32_t* mat, float* mul, const float*
   if (!aligned4(vec) || !aligned4(mul)) return HQ_ERR_MISALIGNED;
   const int groups = height / 3;
   const int colblocks = (width + kColsPerCta - 1) / kColsPerCta;
-  // K split: enough CTAs to fill the machine several times over, a slice of at
-  // most 256 groups (8192 inputs) so the pre-scaled inputs fit shared memory.
+  // K split: a slice of at most 256 groups (8192 inputs) so the pre-scaled inputs
+  // fit shared memory, at least one group per warp, and - among the splits that
+  // give every SM several CTAs - the one whose grid fills whole waves of the
+  // resident CTA slots best (a grid of 2.1 waves runs as long as one of 3).
   const int sms = sm_count();
-  int ksplit = (8 * sms + colblocks - 1) / colblocks;
-  ksplit = max(ksplit, (groups + 255) / 256);
-  ksplit = min(ksplit, (groups + kWarps - 1) / kWarps);
-  ksplit = max(ksplit, 1);
+  const int slots = sms * (F16IN ? 4 : 3);  // resident CTAs at 59 / 74 registers per thread
+  const int k_lo = max(1, (groups + 255) / 256);
+  const int k_hi = max(k_lo, min((groups + kWarps - 1) / kWarps, (16 * sms + colblocks - 1) / colblocks));
+  int ksplit = k_lo;
+  double best = -1.0;
+  for (int k = k_lo; k <= k_hi; k++) {
+    const int g = (groups + k - 1) / k;
+    const int kk = (groups + g - 1) / g;
+    const long ctas = (long)colblocks * kk;
+    const long waves = (ctas + slots - 1) / slots;
+    // whole waves, enough CTAs to fill the slots, prologue amortised over the slice
+    const double score = (double)ctas / (double)(waves * slots) * ((double)g / (g + 6.0));
+    if (score > best + 1e-9) { best = score; ksplit = kk; }
+  }
   int gpc = (groups + ksplit - 1) / ksplit;
   ksplit = (groups + gpc - 1) / gpc;
   const int xp_words = F16IN ? kF16Words : 32;
   size_t smem = (size_t)gpc * xp_words * 4 + (size_t)((gpc + 3) & ~3) * 4 +
                 (size_t)kWarps * kColsPerCta * 4 + 16;
-  auto kern = q3_gemv_kernel<F16IN>;
+  constexpr auto kern = q3_gemv_kernel<F16IN>;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = ensure_dynamic_smem<kern>(smem);
     if (e != cudaSuccess) return cuda_status(e);
   }
   dim3 grid(colblocks, ksplit);

@@ -209,6 +209,30 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 
+// Codes 2e and 2e+1 of a 96-bit stream (three words) as half2(q, q') without a
+// table: the two 16-bit windows that hold the fields are brought into the
+// halves of one register by a byte permute (a field at bit o <= 7 of a window
+// lies inside the 10 mantissa bits of a half), everything but the fields is
+// masked off and the exponent of 2^(10 - o) is OR-ed in, so each half reads
+// 2^(10 - o) + q exactly; subtracting 2^(10 - o) leaves q.  With e a constant
+// after unrolling every selector, mask and constant folds: PRMT + LOP3 + HADD2.
+#ifndef HQ_QGEMM_ARITH
+#define HQ_QGEMM_ARITH 0
+#endif
+__device__ __forceinline__ uint32_t q3_pair_half2(const uint32_t (&w)[3], int e) {
+  const int b0 = 6 * e, b1 = b0 + 3;
+  const int B0 = b0 >> 3, o0 = b0 & 7, B1 = b1 >> 3, o1 = b1 & 7;
+  const int a = B0 >> 2;  // first word involved
+  const int n0 = B0 - 4 * a, n1 = (B0 + 1 < 11 ? B0 + 1 : 11) - 4 * a;
+  const int n2 = B1 - 4 * a, n3 = (B1 + 1 < 11 ? B1 + 1 : 11) - 4 * a;
+  const uint32_t sel = (uint32_t)(n0 | (n1 << 4) | (n2 << 8) | (n3 << 12));
+  const uint32_t mask = (7u << o0) | (7u << (16 + o1));
+  const uint32_t expo = ((uint32_t)(25 - o0) << 10) | ((uint32_t)(25 - o1) << 26);
+  const uint32_t r = __byte_perm(w[a], w[a + 1 < 3 ? a + 1 : a], sel);
+  const uint32_t v = (r & mask) | expo;
+  return half2_as_u32(__hsub2(u32_as_half2(v), u32_as_half2(expo)));
+}
+
 struct QgemmParams {
   __half* Y;
   float* ws;            // fp32 [Mb][N] scratch + per-tile counters, used when ksplit > 1
@@ -356,6 +380,16 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
         const __half2 sc2 = __half2half2(__ushort_as_half(sc_bits));
         const __half2 nz2 = __half2half2(__hneg(__ushort_as_half(z_bits)));
         uint32_t o[32];
+#if HQ_QGEMM_ARITH
+  #pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          const uint32_t w3[3] = {w[3 * hf], w[3 * hf + 1], w[3 * hf + 2]};
+  #pragma unroll
+          for (int e = 0; e < 16; e++)
+            o[16 * hf + e] =
+                half2_as_u32(__hfma2(u32_as_half2(q3_pair_half2(w3, e)), sc2, nz2));
+        }
+#else
   #pragma unroll
         for (int hf = 0; hf < 2; hf++) {
           const uint32_t w0 = w[3 * hf], w1 = w[3 * hf + 1], w2 = w[3 * hf + 2];
@@ -379,6 +413,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
             o[16 * hf + e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
           }
         }
+#endif
         // the ring slot is released only now: the lookups above consumed the words,
         // so the loads have certainly returned
         __syncwarp();

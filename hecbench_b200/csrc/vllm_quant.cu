@@ -20,10 +20,11 @@
 //    registers (up to 32 elements per thread), reduced with warp shuffles and
 //    one shared-memory exchange, and quantized from the registers - the
 //    reference reads every row twice.  Rows are contiguous but start at any
-//    element (the reference's own run uses hidden_size = 5137), so a thread
-//    takes elements t, t + 256, ... with 2/4-byte loads and 1-byte stores: a
-//    warp still touches 64/128 and 32 contiguous bytes per instruction, and
-//    all loads of a row are in flight together.
+//    element (the reference's own run uses hidden_size = 5137), so the CTA
+//    works on the aligned 16-byte chunks that overlap its row and masks the
+//    neighbours' elements: full-width loads and 8-byte stores at any row
+//    offset, all loads of a row in flight together.  An element-wise form
+//    covers unaligned buffers and rows beyond the register cache.
 #include <cuda_bf16.h>
 
 #include <cfloat>
@@ -114,7 +115,101 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
 }
 
 // ---- dynamic forms: one CTA per token row (rows dealt round-robin) ----
-// EPT: elements per thread kept in registers; EPT == 0 re-reads the row.
+// Vector form.  The tensor is viewed as aligned 16-byte chunks (EPC = 8 or 4
+// elements); the CTA of row t takes the chunks that overlap [t*hidden,
+// (t+1)*hidden) - a chunk on a row boundary is read by both rows' CTAs and each
+// masks the elements of the other row.  A thread keeps CPT chunks in registers
+// (chunks tid, tid + 256, ...), so the row is read once, with full-width
+// loads whatever the row's starting address is.  The eight (four) results of a
+// chunk inside the row leave as one 8-byte (4-byte) store; a boundary chunk
+// stores its in-row bytes one by one.
+template <typename T, bool AZP, int CPT>
+__global__ void __launch_bounds__(kThreads)
+vllm_dynamic_vec_kernel(const T* __restrict__ in, int8_t* __restrict__ out,
+                        float* __restrict__ scale_out, int* __restrict__ azp_out, int num_tokens,
+                        int hidden) {
+  constexpr int EPC = 16 / sizeof(T);
+  __shared__ float sh[kWarps];
+  const int tid = threadIdx.x;
+  const size_t total = (size_t)num_tokens * hidden;
+  for (int t = blockIdx.x; t < num_tokens; t += gridDim.x) {
+    const size_t e0 = (size_t)t * hidden, e1 = e0 + hidden;  // the row's elements, flat
+    const size_t c0 = e0 / EPC;                               // first chunk that overlaps it
+    float v[CPT][EPC];
+    float mx = AZP ? FLT_MIN : 0.f, mn = FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < CPT; j++) {
+      const size_t c = c0 + tid + (size_t)j * kThreads;
+      const size_t first = c * EPC;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      // the last chunk of the tensor may be partial: it is fetched element-wise
+      if (first < e1) {
+        if (first + EPC <= total) {
+          if (HQ_IN_BOUNDS(reinterpret_cast<const uint4*>(in) + c, 16, in, total * sizeof(T), 403))
+            raw = ldg_stream_u4(reinterpret_cast<const uint4*>(in) + c);
+        } else {
+          T* r = reinterpret_cast<T*>(&raw);
+          for (int k = 0; k < EPC; k++)
+            if (first + k < total) r[k] = in[first + k];
+        }
+      }
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int k = 0; k < EPC; k++) {
+        const bool mine = first + k >= e0 && first + k < e1;
+        const float x = to_float<T>(e[k]);
+        v[j][k] = x;
+        if (AZP) {
+          mx = fmaxf(mx, mine ? x : FLT_MIN);
+          mn = fminf(mn, mine ? x : FLT_MAX);
+        } else {
+          mx = fmaxf(mx, mine ? fabsf(x) : 0.f);
+        }
+      }
+    }
+    mx = block_reduce(mx, true, sh);
+    float scale, mul = 0.f;
+    int azp = 0;
+    if (AZP) {
+      mn = block_reduce(mn, false, sh);
+      scale = __fdiv_rn(__fsub_rn(mx, mn), 255.0f);
+      azp = __float2int_rz(rintf(__fsub_rn(-128.0f, __fdiv_rn(mn, scale))));
+    } else {
+      scale = __fdiv_rn(mx, 127.0f);
+      mul = __fdiv_rn(127.0f, mx);
+    }
+    if (tid == 0) {
+      scale_out[t] = scale;
+      if (AZP) azp_out[t] = azp;
+    }
+#pragma unroll
+    for (int j = 0; j < CPT; j++) {
+      const size_t first = (c0 + tid + (size_t)j * kThreads) * EPC;
+      if (first >= e1) continue;
+      uint32_t q[EPC / 4] = {};
+#pragma unroll
+      for (int k = 0; k < EPC; k++) {
+        const int r = AZP ? f2i8_azp(__fdiv_rn(v[j][k], scale), azp) : f2i8_rn(__fmul_rn(v[j][k], mul));
+        q[k / 4] |= (uint32_t)(r & 0xff) << (8 * (k & 3));
+      }
+      if (first >= e0 && first + EPC <= e1) {  // wholly inside the row: one aligned store
+        if (HQ_IN_BOUNDS(out + first, EPC, out, total, 404)) {
+          if (EPC == 8) *reinterpret_cast<uint2*>(out + first) = make_uint2(q[0], q[EPC / 4 - 1]);
+          else *reinterpret_cast<uint32_t*>(out + first) = q[0];
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPC; k++)
+          if (first + k >= e0 && first + k < e1)
+            out[first + k] = (int8_t)((q[k / 4] >> (8 * (k & 3))) & 0xff);
+      }
+    }
+  }
+}
+
+// Element-wise form for buffers that are not 16 / 8-byte aligned and for rows
+// longer than the register cache.  EPT: elements per thread kept in registers;
+// EPT == 0 re-reads the row.
 template <typename T, bool AZP, int EPT>
 __global__ void __launch_bounds__(kThreads)
 vllm_dynamic_kernel(const T* __restrict__ in, int8_t* __restrict__ out,
@@ -132,9 +227,7 @@ vllm_dynamic_kernel(const T* __restrict__ in, int8_t* __restrict__ out,
 #pragma unroll
       for (int j = 0; j < EPT; j++) {
         const int i = tid + j * kThreads;
-        v[j] = (i < hidden && HQ_IN_BOUNDS(row + i, sizeof(T), in,
-                                           (size_t)num_tokens * hidden * sizeof(T), 403))
-                   ? to_float<T>(row[i]) : (AZP ? FLT_MIN : 0.f);
+        v[j] = i < hidden ? to_float<T>(row[i]) : (AZP ? FLT_MIN : 0.f);
       }
 #pragma unroll
       for (int j = 0; j < EPT; j++) {
@@ -171,7 +264,7 @@ vllm_dynamic_kernel(const T* __restrict__ in, int8_t* __restrict__ out,
 #pragma unroll
       for (int j = 0; j < EPT; j++) {
         const int i = tid + j * kThreads;
-        if (i < hidden && HQ_IN_BOUNDS(orow + i, 1, out, (size_t)num_tokens * hidden, 404))
+        if (i < hidden)
           orow[i] = (int8_t)(AZP ? f2i8_azp(__fdiv_rn(v[j], scale), azp)
                                  : f2i8_rn(__fmul_rn(v[j], mul)));
       }
@@ -202,7 +295,19 @@ template <typename T, bool AZP>
 int dynamic_launch_ept(int8_t* out, const T* x, float* scales, int* azp, int tokens, int hidden,
                        cudaStream_t st) {
   const unsigned grid = (unsigned)std::min(tokens, sm_count() * 32);
-  if (hidden <= 8 * kThreads)
+  constexpr int EPC = 16 / sizeof(T);
+  // chunks a row can overlap: its elements plus one partial chunk at either end
+  const long chunks = ((long)hidden + EPC - 1) / EPC + 1;
+  const bool vec_ok = aligned16(x) && aligned8(out);
+  if (vec_ok && chunks <= 1L * kThreads)
+    vllm_dynamic_vec_kernel<T, AZP, 1><<<grid, kThreads, 0, st>>>(x, out, scales, azp, tokens, hidden);
+  else if (vec_ok && chunks <= 2L * kThreads)
+    vllm_dynamic_vec_kernel<T, AZP, 2><<<grid, kThreads, 0, st>>>(x, out, scales, azp, tokens, hidden);
+  else if (vec_ok && chunks <= 4L * kThreads)
+    vllm_dynamic_vec_kernel<T, AZP, 4><<<grid, kThreads, 0, st>>>(x, out, scales, azp, tokens, hidden);
+  else if (vec_ok && sizeof(T) == 4 && chunks <= 8L * kThreads)
+    vllm_dynamic_vec_kernel<T, AZP, 8><<<grid, kThreads, 0, st>>>(x, out, scales, azp, tokens, hidden);
+  else if (hidden <= 8 * kThreads)
     vllm_dynamic_kernel<T, AZP, 8><<<grid, kThreads, 0, st>>>(x, out, scales, azp, tokens, hidden);
   else if (hidden <= 16 * kThreads)
     vllm_dynamic_kernel<T, AZP, 16><<<grid, kThreads, 0, st>>>(x, out, scales, azp, tokens, hidden);
