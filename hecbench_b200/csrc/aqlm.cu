@@ -47,57 +47,73 @@ __device__ __forceinline__ float dot8_ref_order(const uint4& a, const uint4& b) 
   return __half2float(__low2half(r)) + __half2float(__high2half(r));
 }
 
-// VPL = 16-byte code vectors per lane per row (prob_k / 64 / 32 rounded up).
-template <int VPL>
+// VPL = 16-byte code vectors per lane per row (prob_k / 64 / 32 rounded up),
+// RPW = rows per warp.  The dependent chain code -> codebook row -> FMA is what
+// bounds this kernel, so everything that does not depend on the input vector
+// is issued first: the code vectors of ALL rows of the warp, then the gathers
+// of the first vector, and only then the CTA stages the inputs in shared
+// memory; afterwards the gathers of vector u + 1 are in flight while vector u
+// is multiplied.  The arithmetic (and its order) is the reference's.
+template <int VPL, int RPW>
 __global__ void __launch_bounds__(kWarps1x16 * 32)
 aqlm_1x16_kernel(const uint4* __restrict__ codes, const uint4* __restrict__ x,
                  __half* __restrict__ out, const uint4* __restrict__ codebook, int prob_m,
-                 int prob_k, int4 cb_sizes, int cb_stride, const __half* __restrict__ scales,
-                 int rows_per_warp) {
+                 int prob_k, int4 cb_sizes, int cb_stride, const __half* __restrict__ scales) {
   extern __shared__ __align__(16) uint4 sh_x[];  // padded inputs: slot 9*(g/8) + g%8
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int groups = prob_k >> 3;    // 16-byte input groups
   const int vec_per_row = prob_k >> 6;
-  for (int g = tid; g < groups; g += blockDim.x) sh_x[kPad * (g >> 3) + (g & 7)] = x[g];
-  __syncthreads();
+  const int row_begin = (blockIdx.x * kWarps1x16 + warp) * RPW;
+  constexpr int kUnits = RPW * VPL;  // unit u = (row u / VPL, vector u % VPL)
 
-  const int row_begin = (blockIdx.x * kWarps1x16 + warp) * rows_per_warp;
-  for (int rr = 0; rr < rows_per_warp; rr++) {
-    const int m = row_begin + rr;
-    if (m >= prob_m) break;
+  uint4 cv[kUnits];
+#pragma unroll
+  for (int u = 0; u < kUnits; u++) {
+    const int m = row_begin + u / VPL, idx = lane + 32 * (u % VPL);
+    cv[u] = (m < prob_m && idx < vec_per_row)
+                ? ldg_stream_u4(codes + (size_t)m * vec_per_row + idx)
+                : make_uint4(0, 0, 0, 0);
+  }
+  auto book = [&](int m) {
     const uint4* cb = codebook;
     if (m >= cb_sizes.x) cb += cb_stride;
     if (m >= cb_sizes.y) cb += cb_stride;
     if (m >= cb_sizes.z) cb += cb_stride;
-    const uint4* crow = codes + (size_t)m * vec_per_row;
+    return cb;
+  };
+  auto gather = [&](int u, uint4 (&rows)[8]) {
+    const int m = row_begin + u / VPL, idx = lane + 32 * (u % VPL);
+    if (m < prob_m && idx < vec_per_row) {
+      const uint4* cb = book(m);
+      const uint32_t cw[4] = {cv[u].x, cv[u].y, cv[u].z, cv[u].w};
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        rows[i] = ldg_nc_u4(cb + ((cw[i >> 1] >> (16 * (i & 1))) & 0xffffu));
+    }
+  };
+  uint4 rows[2][8];
+  gather(0, rows[0]);
 
-    uint4 cv[VPL];
+  for (int g = tid; g < groups; g += blockDim.x) sh_x[kPad * (g >> 3) + (g & 7)] = x[g];
+  __syncthreads();
+
+  float res = 0.f;
 #pragma unroll
-    for (int v = 0; v < VPL; v++) {
-      const int idx = lane + 32 * v;
-      cv[v] = (idx < vec_per_row) ? ldg_stream_u4(crow + idx) : make_uint4(0, 0, 0, 0);
+  for (int u = 0; u < kUnits; u++) {
+    if (u + 1 < kUnits) gather(u + 1, rows[(u + 1) & 1]);
+    const int m = row_begin + u / VPL, idx = lane + 32 * (u % VPL);
+    if (m < prob_m && idx < vec_per_row) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) res += dot8_ref_order(rows[u & 1][i], sh_x[kPad * idx + i]);
     }
-    float res = 0.f;
+    if (u % VPL == VPL - 1) {  // the row is complete
 #pragma unroll
-    for (int v = 0; v < VPL; v++) {
-      const int idx = lane + 32 * v;
-      if (idx < vec_per_row) {
-        const uint32_t cw[4] = {cv[v].x, cv[v].y, cv[v].z, cv[v].w};
-        uint4 rows[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const uint32_t code = (cw[i >> 1] >> (16 * (i & 1))) & 0xffffu;
-          rows[i] = ldg_nc_u4(cb + code);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) res += dot8_ref_order(rows[i], sh_x[kPad * idx + i]);
+      for (int o = 16; o > 0; o >>= 1) res += __shfl_down_sync(0xffffffffu, res, o);
+      if (lane == 0 && m < prob_m) {
+        if (scales != nullptr) res *= __half2float(scales[m]);
+        out[m] = __float2half(res);
       }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) res += __shfl_down_sync(0xffffffffu, res, o);
-    if (lane == 0) {
-      if (scales != nullptr) res *= __half2float(scales[m]);
-      out[m] = __float2half(res);
+      res = 0.f;
     }
   }
 }
@@ -177,9 +193,9 @@ int hq_aqlm_1x16_matvec(const void* codes, const void* x_half, void* out_half, c
   const int grid = (prob_m + rows_per_cta - 1) / rows_per_cta;
   const int4 sizes = make_int4(cb_sizes[0], cb_sizes[1], cb_sizes[2], cb_sizes[3]);
   cudaStream_t st = (cudaStream_t)stream;
-#define HQ_AQLM_LAUNCH(VPL)                                                                  \
+#define HQ_AQLM_LAUNCH(VPL, RPW)                                                             \
   {                                                                                          \
-    constexpr auto kern = aqlm_1x16_kernel<VPL>;                                             \
+    constexpr auto kern = aqlm_1x16_kernel<VPL, RPW>;                                        \
     if (smem > 48 * 1024) {                                                                  \
       cudaError_t e = ensure_dynamic_smem<kern>(smem);                                       \
       if (e != cudaSuccess) return cuda_status(e);                                           \
@@ -187,15 +203,18 @@ int hq_aqlm_1x16_matvec(const void* codes, const void* x_half, void* out_half, c
     kern<<<grid, kWarps1x16 * 32, smem, st>>>(                                               \
         reinterpret_cast<const uint4*>(codes), reinterpret_cast<const uint4*>(x_half),       \
         reinterpret_cast<__half*>(out_half), reinterpret_cast<const uint4*>(codebook),       \
-        prob_m, prob_k, sizes, cb_stride_int4, reinterpret_cast<const __half*>(scales_half), \
-        rows_per_warp);                                                                      \
+        prob_m, prob_k, sizes, cb_stride_int4, reinterpret_cast<const __half*>(scales_half)); \
   }
+#define HQ_AQLM_ROWS(VPL)                                \
+  if (rows_per_warp == 4) HQ_AQLM_LAUNCH(VPL, 4)         \
+  else HQ_AQLM_LAUNCH(VPL, 2)
   switch (vpl) {
-    case 1: HQ_AQLM_LAUNCH(1) break;
-    case 2: HQ_AQLM_LAUNCH(2) break;
-    case 3: HQ_AQLM_LAUNCH(3) break;
-    default: HQ_AQLM_LAUNCH(4) break;
+    case 1: HQ_AQLM_ROWS(1) break;
+    case 2: HQ_AQLM_ROWS(2) break;
+    case 3: HQ_AQLM_ROWS(3) break;
+    default: HQ_AQLM_ROWS(4) break;
   }
+#undef HQ_AQLM_ROWS
 #undef HQ_AQLM_LAUNCH
   return launch_status();
 }
@@ -209,8 +228,8 @@ int hq_aqlm_2x8_matvec(const void* codes, const void* x_half, void* out_half, co
   const int groups = prob_k / 8;
   const size_t smem = (size_t)2 * 256 * 8 * 16 + (size_t)kPad * ((groups + 7) / 8) * 16;
   if (smem > 220 * 1024) return HQ_ERR_TOO_LARGE;
-  cudaError_t e = cudaFuncSetAttribute(aqlm_2x8_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  constexpr auto kern2x8 = aqlm_2x8_kernel;
+  cudaError_t e = ensure_dynamic_smem<kern2x8>(smem);
   if (e != cudaSuccess) return cuda_status(e);
   const int rows_per_warp = rows_per_warp_for(prob_m, kWarps2x8);
   const int rows_per_cta = kWarps2x8 * rows_per_warp;

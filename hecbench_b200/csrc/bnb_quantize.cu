@@ -25,6 +25,12 @@
 // sorted or not, because the argument is about indices only.  So the final
 // test reads ONE neighbour, code[P + 1] or code[max(P - 1, 0)], and the result
 // is the one the reference's compare sequence gives, NaN inputs included.
+//
+// The integer side of the search runs on the half-rate integer pipe, which is
+// what bounds the kernel once the loads are covered, so a level costs one
+// compare, ONE predicated add and one table read: only the "went up" strides
+// are accumulated, and the constant rest of the pivot's address is an
+// immediate of the shared-memory load.
 #include "hq_common.cuh"
 
 namespace hq {
@@ -32,31 +38,53 @@ namespace {
 
 constexpr int kThreads = 256;
 
-// tab_lane points at table[0][lane]; entry p is at byte offset p * 128.
-__device__ __forceinline__ uint32_t quantize_one(const unsigned char* __restrict__ tab_lane,
-                                                 float x, float c127, float c63, float c191) {
+template <int IMM>
+__device__ __forceinline__ float lds_f32_imm(uint32_t addr) {
+  // not volatile: the table is constant after the barrier that follows its set-up
+  float v;
+  asm("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
+  return v;
+}
+
+// One search level with stride D (in table rows of 128 bytes): a compare, one
+// predicated add and the next pivot's value.  With acc = lane address + (sum of
+// 2*d*128 over the levels that went up), the pivot after this level is at
+// acc + (D - 1) * 128, and the constant part rides in the load's immediate.
+template <int D>
+__device__ __forceinline__ void search_level(uint32_t& acc, float& val, float x) {
+  if (x > val) acc += 2u * D * 128u;
+  val = lds_f32_imm<(D - 1) * 128>(acc);
+}
+
+// lane_addr: shared-window address of table[0][lane]; entry p is at lane_addr +
+// p * 128, and the row before entry 0 holds a copy of entry 0 (so that the
+// "lower neighbour" of pivot 0 can be read without a clamp on the address).
+__device__ __forceinline__ uint32_t quantize_one(uint32_t lane_addr, float x, float c127, float c63,
+                                                 float c191) {
   // step i = 64 (val = code[127]): decided from registers
   const bool up0 = x > c127;
   float val = up0 ? c191 : c63;
-  int off = up0 ? 191 * 128 : 63 * 128;  // byte offset of the pivot's table row
-#pragma unroll
-  for (int i = 32; i > 0; i >>= 1) {
-    off += (x > val) ? i * 128 : -i * 128;
-    val = *reinterpret_cast<const float*>(tab_lane + off);
-  }
-  // off / 128 is the final pivot P, val = code[P]
+  uint32_t acc = lane_addr + (up0 ? 128u * 128u : 0u);
+  search_level<32>(acc, val, x);
+  search_level<16>(acc, val, x);
+  search_level<8>(acc, val, x);
+  search_level<4>(acc, val, x);
+  search_level<2>(acc, val, x);
+  search_level<1>(acc, val, x);
+  // (acc - lane_addr) / 128 is the final pivot P, val = code[P]
   const bool gt = x > val;
-  const int nb_off = max(off + (gt ? 128 : -128), 0);
-  const float nb = *reinterpret_cast<const float*>(tab_lane + nb_off);
+  const float nb = gt ? lds_f32_imm<128>(acc) : lds_f32_imm<-128>(acc);
   const float midpoint = (nb + val) * 0.5f;
   const bool step = gt ? (x > midpoint) : (x < midpoint);
-  return (uint32_t)(step ? nb_off : off) >> 7;
+  const int P = (int)((acc - lane_addr) >> 7);
+  return (uint32_t)(step ? (gt ? P + 1 : max(P - 1, 0)) : P);
 }
 
 __global__ void __launch_bounds__(kThreads)
 bnb_quantize_kernel(const float* __restrict__ code, const float* __restrict__ A,
                     uint8_t* __restrict__ out, size_t n) {
-  extern __shared__ __align__(16) float table[];  // [256][32]
+  extern __shared__ __align__(16) float table_raw[];  // one guard row, then [256][32]
+  float* table = table_raw + 32;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   {
@@ -66,9 +94,10 @@ bnb_quantize_kernel(const float* __restrict__ code, const float* __restrict__ A,
     float4* row = reinterpret_cast<float4*>(table + tid * 32);
 #pragma unroll
     for (int q = 0; q < 8; q++) row[(q + tid) & 7] = v4;  // rotate to spread banks
+    if (tid < 32) table_raw[tid] = code[0];  // the guard row in front of entry 0
   }
   __syncthreads();
-  const unsigned char* tab_lane = reinterpret_cast<const unsigned char*>(table + lane);
+  const uint32_t tab_lane = (uint32_t)__cvta_generic_to_shared(table + lane);
   const float c127 = table[127 * 32 + lane], c63 = table[63 * 32 + lane],
               c191 = table[191 * 32 + lane];
 
@@ -108,7 +137,7 @@ extern "C" int hq_bnb_quantize_u8(const float* code256, const float* A, uint8_t*
   if (!code256 || (n && (!A || !out))) return HQ_ERR_NULL_POINTER;
   if (n == 0) return HQ_OK;
   if (!aligned4(A) || !aligned4(code256)) return HQ_ERR_MISALIGNED;
-  const size_t smem = 256 * 32 * sizeof(float);
+  const size_t smem = 257 * 32 * sizeof(float);  // guard row + table
   constexpr auto kern = bnb_quantize_kernel;
   const cudaError_t e = ensure_dynamic_smem<kern>(smem);
   if (e != cudaSuccess) return cuda_status(e);

@@ -23,10 +23,6 @@
 //    loads, the four lanes of a column quad reading the same 16 bytes), one
 //    column step ahead of their use, and the first step is requested before
 //    the tables are built;
-//  * before anything else a few threads ask the L2 for the CTA's whole
-//    footprint (bulk L2 prefetches of the TR*NB runs of packed words, line
-//    prefetches of the alpha / bias runs), so that the register loads of the
-//    lookup phase find their lines in L2 instead of waiting for HBM;
 //  * table entries and all sums are fp32 (the reference uses fp16 throughout
 //    and half2 atomics on the output);
 //  * the four lanes of a column quad are combined with two shuffles, each CTA
@@ -34,6 +30,8 @@
 //    vector reduction per column quad, and the last CTA of each column range to
 //    finish converts that range of the scratch to fp16, stores the output and
 //    re-zeroes the scratch.
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "hq_common.cuh"
@@ -41,8 +39,9 @@
 namespace hq {
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = kThreads / 32;
+// CTA shapes: 512 threads with a 128-input tile (one CTA per SM), or 256 threads
+// with a 64-input tile and two CTAs per SM - the two then run out of phase, one
+// streaming packed words while the other builds its tables.
 // Shared-window address at which a CTA's dynamic region starts: the 1 KiB the
 // system reserves per CTA (the kernels have no static shared memory).  The
 // host checks the device attribute before launching; kSlack bytes of padding
@@ -81,13 +80,6 @@ __device__ __forceinline__ float lds_f32_imm(uint32_t addr) {
   asm("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
   return v;
 }
-// Ask the L2 for `bytes` (a multiple of 16) at the 16-byte aligned address p.
-__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void l2_prefetch_line(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-}
 __device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
   uint2 v;
   asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
@@ -99,14 +91,15 @@ __device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
 // same scratch row; only the last one converts it).  RPG: packed rows that
 // share one alpha group inside a tile.  counters: one completion counter per
 // column range (per_range != 0) or a single one.
-template <int TR, int NB, int RPG>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int TR, int NB, int RPG, int kThreads>
+__global__ void __launch_bounds__(kThreads, (kThreads == 256 ? 2 : 1))
 lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha,
                const __half* __restrict__ q_bias, const __half* __restrict__ x,
                __half* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ counters,
                int M, int K, int rows_per_group, int cols_per_cta, int nb_total, int b0,
                int finalize, int per_range) {
   using L = Layout<TR>;
+  constexpr int kWarps = kThreads / 32;
   constexpr int kGroups = TR / RPG;
   constexpr int kLutImm = L::kLutImm;
   extern __shared__ __align__(16) unsigned char dsm[];
@@ -131,35 +124,6 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
     const int k = row0 * 32 + tid;
     xs[tid] = (k < K && HQ_IN_BOUNDS(x + k, 2, x, (size_t)K * 2, 206)) ? __half2float(x[k]) : 0.f;
   }
-  // ---- ask the L2 for everything this CTA will read ----
-#ifndef HQ_LUT_NO_L2_PREFETCH
-  {
-    const uint32_t run_bytes = (uint32_t)(m_end - m_begin) * 4u;  // multiple of 16: M % 4 == 0
-    if (tid < TR * NB) {
-      const int r = tid / NB, b = tid - r * NB;
-      if (r < nrows) {
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(
-            bW + ((size_t)(row0 + r) * nb_total + b0 + b) * M + m_begin);
-        for (uint32_t off = 0; off < run_bytes; off += 32768u)
-          l2_prefetch_bulk(src + off, min(32768u, run_bytes - off));
-      }
-    }
-    // alpha / bias runs, one 128-byte line per thread and turn
-    const int lines = ((m_end - m_begin) * 2 + 127) / 128;
-    for (int it = tid; it < kGroups * (NB + 1) * lines; it += kThreads) {
-      const int item = it / lines, ln = it - item * lines;
-      const int gi = item / (NB + 1), b = item - gi * (NB + 1);
-      if (gi * RPG < nrows) {
-        const int g = g0 + gi;
-        if (b < NB)
-          l2_prefetch_line(alpha + ((size_t)g * nb_total + b0 + b) * M + m_begin + ln * 64);
-        else if (q_bias != nullptr)
-          l2_prefetch_line(q_bias + (size_t)g * M + m_begin + ln * 64);
-      }
-    }
-  }
-
-#endif
   // ---- column steps of this warp: step s handles columns m0 + s*kWarps*32 ..+3 ----
   const int j = lane & 3;   // byte of the word this lane looks up
   const int cq = lane >> 2; // column quad inside the 32-column step
@@ -183,6 +147,7 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   const size_t bw_bytes = (size_t)total_rows * nb_total * M * 4;
   const size_t alpha_bytes = (size_t)(total_rows / rows_per_group) * nb_total * M * 2;
   const size_t bias_bytes = (size_t)(total_rows / rows_per_group) * M * 2;
+  (void)bw_bytes; (void)alpha_bytes; (void)bias_bytes;
   auto load_row = [&](int r, int m) {
     if (r < nrows) {
 #pragma unroll
@@ -212,15 +177,17 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   }
   __syncthreads();
 
-  // ---- phase A: thread = (byte value, TR/2 rows); signed sums of 8 inputs ----
+  // ---- phase A: thread = (byte value, some of the rows); signed sums of 8 inputs ----
   {
+    constexpr int kRowSets = kThreads / 256;      // threads per byte value
+    constexpr int kRowsEach = TR / kRowSets;      // rows per thread
     const int bv = tid & 255, rp = tid >> 8;
     uint32_t sgn[8];
 #pragma unroll
     for (int t = 0; t < 8; t++) sgn[t] = ((bv >> t) & 1) ? 0u : 0x80000000u;
 #pragma unroll
-    for (int rr = 0; rr < TR / 2; rr++) {
-      const int r = rp * (TR / 2) + rr;
+    for (int rr = 0; rr < kRowsEach; rr++) {
+      const int r = rp * kRowsEach + rr;
       float v[4];
 #pragma unroll
       for (int jj = 0; jj < 4; jj++) {
@@ -358,6 +325,301 @@ lutgemm_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha
   }
 }
 
+// ---- bulk-copy form ---------------------------------------------------------
+// The register form above keeps one column step of packed words in flight per
+// warp, about 29 KB per SM, and waits out the HBM latency at every step.  This
+// form asks the copy engine for the CTA's WHOLE column range right at the
+// start: a CTA owns a 64-input K tile (two packed rows, 64 KB of tables) and up
+// to kMaxStages steps of 512 columns.  Each of the 2*NB packed-word runs, NB
+// alpha runs and the bias run of that range is contiguous in global memory and
+// is fetched by TWO large bulk copies (cp.async.bulk, global -> shared), one
+// per half of the range, each half completing on its own mbarrier - few large
+// copies is what the copy engine is good at.  All copies are in flight while
+// the tables are built, HBM streams without gaps, the first half is looked up
+// while the second one lands, and the lookup phase reads its operands with
+// quad-broadcast shared-memory loads (one wavefront per load).  Needs M % 8 == 0, alpha groups
+// of a multiple of 64 inputs and 16-byte aligned alpha / bias (the alpha runs
+// are copied in 16-byte units); other shapes take the register form.
+constexpr int kBulkThreads = 512;
+constexpr int kBulkWarps = kBulkThreads / 32;
+constexpr int kBulkCols = kBulkWarps * 32;  // columns per step
+constexpr int kMaxStages = 8;
+constexpr uint32_t kMbarSpins = 1u << 22;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kMbarSpins; i++) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+
+// Shared memory: [flag 16 B][mbarriers 8 x 8 B][build scratch][padding][tables 64 KiB at
+// kLutImm][2*NB word runs of the column range][NB alpha runs][bias run]
+struct BulkLayout {
+  static constexpr int kCompactWords = 2 * 256 * 4;
+  static constexpr int kBuildBytes = kCompactWords * 4 + 2 * 32 * 4;
+  static constexpr int kHeadBytes = 16 + kMaxStages * 8;
+  static constexpr int kLutBytes = 65536;
+  static constexpr int kLutImm = (kDynBase + kSlack + kHeadBytes + kBuildBytes + 255) / 256 * 256;
+  static constexpr int kStage0 = kLutImm + kLutBytes;  // shared-window address of stage 0
+};
+template <int NB>
+struct BulkStage {
+  static constexpr int kBytes = 2 * NB * kBulkCols * 4 + (NB + 1) * kBulkCols * 2;
+};
+
+template <int NB>
+__global__ void __launch_bounds__(kBulkThreads, 1)
+lutgemm_bulk_kernel(const uint32_t* __restrict__ bW, const __half* __restrict__ alpha,
+                    const __half* __restrict__ q_bias, const __half* __restrict__ x,
+                    __half* __restrict__ out, float* __restrict__ ws,
+                    unsigned* __restrict__ counters, int M, int K, int rows_per_group,
+                    int cols_per_cta, int nb_total, int b0, int finalize, int per_range) {
+  using L = BulkLayout;
+  constexpr int kLutImm = L::kLutImm;
+  extern __shared__ __align__(16) unsigned char dsm[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t dsm_addr = (uint32_t)__cvta_generic_to_shared(dsm);
+  // the host has checked where the dynamic region starts; never taken
+  if (dsm_addr < (uint32_t)kDynBase || dsm_addr > (uint32_t)(kDynBase + kSlack)) return;
+  unsigned char* base0 = dsm - dsm_addr;  // generic address of shared-window address 0
+  unsigned char* lut = base0 + kLutImm;
+  unsigned* s_last = reinterpret_cast<unsigned*>(dsm);
+  const uint32_t bars = dsm_addr + 16;
+  float* compact = reinterpret_cast<float*>(dsm + L::kHeadBytes);
+  float* xs = compact + L::kCompactWords;
+  const int row0 = blockIdx.y * 2;  // first packed row of the tile
+  const int total_rows = K >> 5;
+  const int nrows = min(2, total_rows - row0);
+  const int m_begin = blockIdx.x * cols_per_cta;
+  const int m_end = min(M, m_begin + cols_per_cta);
+  const int nsteps = (m_end - m_begin + kBulkCols - 1) / kBulkCols;
+  const int g = row0 / rows_per_group;  // the tile's alpha group
+
+  if (tid < 64) {
+    const int k = row0 * 32 + tid;
+    xs[tid] = (k < K) ? __half2float(x[k]) : 0.f;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kMaxStages; s++) mbar_init(bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // ---- request the whole column range: warp h asks for half h of every run ----
+  const int steps_half = (nsteps + 1) / 2;            // steps in the first half
+  const uint32_t range_cols = (uint32_t)cols_per_cta;  // run pitch in shared memory (columns)
+  const uint32_t alpha_off = 2u * NB * range_cols * 4u;
+  if (warp < 2 && warp * steps_half < nsteps) {
+    const int h = warp;
+    const int m = m_begin + h * steps_half * kBulkCols;
+    const int m_hi = h == 0 ? min(m_end, m_begin + steps_half * kBulkCols) : m_end;
+    const uint32_t cols = (uint32_t)(m_hi - m);  // multiple of 8
+    const uint32_t stage = (uint32_t)L::kStage0;
+    const uint32_t col0 = (uint32_t)(m - m_begin);
+    const uint32_t bar = bars + 8 * h;
+    const bool bias_on = q_bias != nullptr;
+    // this lane's copy: packed words of (row r, plane b), alpha of plane b, or the bias
+    const void* src = nullptr;
+    uint32_t dst = 0, bytes = 0;
+    if (lane < 2 * NB) {
+      const int r = lane / NB, b = lane - r * NB;
+      if (r < nrows) {
+        src = bW + ((size_t)(row0 + r) * nb_total + b0 + b) * M + m;
+        dst = stage + ((uint32_t)lane * range_cols + col0) * 4u;
+        bytes = cols * 4u;
+      }
+    } else if (lane < 3 * NB) {
+      const int b = lane - 2 * NB;
+      src = alpha + ((size_t)g * nb_total + b0 + b) * M + m;
+      dst = stage + alpha_off + ((uint32_t)b * range_cols + col0) * 2u;
+      bytes = cols * 2u;
+    } else if (lane == 3 * NB && bias_on) {
+      src = q_bias + (size_t)g * M + m;
+      dst = stage + alpha_off + ((uint32_t)NB * range_cols + col0) * 2u;
+      bytes = cols * 2u;
+    }
+#ifdef HQ_BOUNDS_CHECK
+    {
+      // a copy that leaves its buffer is recorded and the whole stage is skipped
+      const size_t groups = (size_t)(total_rows / rows_per_group);
+      bool fine = true;
+      if (bytes != 0) {
+        if (lane < 2 * NB) fine = HQ_IN_BOUNDS(src, bytes, bW, (size_t)total_rows * nb_total * M * 4, 211);
+        else if (lane < 3 * NB) fine = HQ_IN_BOUNDS(src, bytes, alpha, groups * nb_total * M * 2, 212);
+        else fine = HQ_IN_BOUNDS(src, bytes, q_bias, groups * M * 2, 213);
+      }
+      if (__ballot_sync(0xffffffffu, !fine) != 0u) bytes = 0;
+    }
+#endif
+    uint32_t total = bytes;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    if (lane == 0) mbar_expect_tx(bar, total);
+    __syncwarp();
+    if (bytes != 0) bulk_load(dst, src, bytes, bar);
+  }
+
+  // ---- phase A: thread = (byte value, row); signed sums of 8 inputs ----
+  {
+    const int bv = tid & 255, r = tid >> 8;
+    uint32_t sgn[8];
+#pragma unroll
+    for (int t = 0; t < 8; t++) sgn[t] = ((bv >> t) & 1) ? 0u : 0x80000000u;
+    float v[4];
+#pragma unroll
+    for (int jj = 0; jj < 4; jj++) {
+      const float4 xa = *reinterpret_cast<const float4*>(xs + r * 32 + jj * 8);
+      const float4 xb = *reinterpret_cast<const float4*>(xs + r * 32 + jj * 8 + 4);
+      const float s0 = __uint_as_float(__float_as_uint(xa.x) ^ sgn[0]) +
+                       __uint_as_float(__float_as_uint(xa.y) ^ sgn[1]);
+      const float s1 = __uint_as_float(__float_as_uint(xa.z) ^ sgn[2]) +
+                       __uint_as_float(__float_as_uint(xa.w) ^ sgn[3]);
+      const float s2 = __uint_as_float(__float_as_uint(xb.x) ^ sgn[4]) +
+                       __uint_as_float(__float_as_uint(xb.y) ^ sgn[5]);
+      const float s3 = __uint_as_float(__float_as_uint(xb.z) ^ sgn[6]) +
+                       __uint_as_float(__float_as_uint(xb.w) ^ sgn[7]);
+      v[jj] = (s0 + s1) + (s2 + s3);
+    }
+    *reinterpret_cast<float4*>(compact + (r * 256 + bv) * 4) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+  __syncthreads();
+  // ---- phase B: replicate each (row, byte) entry 8 times into its table line ----
+  // line (byte b) at lut + b*256; inside: [row parity][c][j] floats
+  {
+    const int c = lane & 7, bl = lane >> 3;
+#pragma unroll 4
+    for (int it = 0; it < 2 * 256 / (kBulkWarps * 4); it++) {
+      const int e = (it * kBulkWarps + warp) * 4 + bl;  // row*256 + byte
+      const int r = e >> 8, b = e & 255;
+      const float4 v = *reinterpret_cast<const float4*>(compact + e * 4);
+      *reinterpret_cast<float4*>(lut + b * 256 + (r & 1) * 128 + c * 16) = v;
+    }
+  }
+  __syncthreads();
+
+  // ---- lookup phase ----
+  const int j = lane & 3;   // byte of the word this lane looks up
+  const int cq = lane >> 2; // column quad inside the warp's 32 columns
+  const uint32_t hi = (uint32_t)(lane * 4);
+  const uint32_t sel = 0x7604u | ((uint32_t)j << 4);
+  // bias uses the all-ones entry (byte 255): sum of this lane's 8 inputs per row
+  const float ones = *reinterpret_cast<const float*>(lut + 255 * 256 + lane * 4) +
+                     *reinterpret_cast<const float*>(lut + 255 * 256 + 128 + lane * 4);
+  const uint32_t col_off = (uint32_t)(warp * 32 + cq * 4);  // column inside the step
+  bool ok = true;
+  for (int s = 0; s < nsteps; s++) {
+    const int m = m_begin + s * kBulkCols + (int)col_off;
+    if (ok && !mbar_wait(bars + 8 * (s >= steps_half ? 1 : 0), 0)) ok = false;
+    const bool active = m < m_end;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) {
+      const uint32_t stage = (uint32_t)L::kStage0;
+      const uint32_t col = (uint32_t)(s * kBulkCols) + col_off;  // column inside the range
+      float t[NB][4];
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+          // rows past the end of K were not copied: their tables are zero, any word will do
+          const uint4 wv = lds_u4(stage + ((uint32_t)(r * NB + b) * range_cols + col) * 4u);
+          const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            const uint32_t a = __byte_perm(w4[c], hi, sel);
+            const float v = r == 0 ? lds_f32_imm<kLutImm>(a) : lds_f32_imm<kLutImm + 128>(a);
+            t[b][c] = (r == 0) ? v : t[b][c] + v;
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < NB; b++) {
+        const uint2 av = lds_u2(stage + alpha_off + ((uint32_t)b * range_cols + col) * 2u);
+        const float2 a01 = __half22float2(u32_as_half2(av.x));
+        const float2 a23 = __half22float2(u32_as_half2(av.y));
+        acc[0] = fmaf(a01.x, t[b][0], acc[0]);
+        acc[1] = fmaf(a01.y, t[b][1], acc[1]);
+        acc[2] = fmaf(a23.x, t[b][2], acc[2]);
+        acc[3] = fmaf(a23.y, t[b][3], acc[3]);
+      }
+      if (q_bias != nullptr) {
+        const uint2 bv = lds_u2(stage + alpha_off + ((uint32_t)NB * range_cols + col) * 2u);
+        const float2 b01 = __half22float2(u32_as_half2(bv.x));
+        const float2 b23 = __half22float2(u32_as_half2(bv.y));
+        acc[0] = fmaf(b01.x, ones, acc[0]);
+        acc[1] = fmaf(b01.y, ones, acc[1]);
+        acc[2] = fmaf(b23.x, ones, acc[2]);
+        acc[3] = fmaf(b23.y, ones, acc[3]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
+      acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 2);
+    }
+    if (active && j == 0 && HQ_IN_BOUNDS(ws + m, 16, ws, (size_t)M * 4, 214))
+      red_add_v4_f32(ws + m, acc[0], acc[1], acc[2], acc[3]);
+  }
+  // a wait that ran out: word kCounterWords - 1 of the counter block tells the host
+  if (!ok && lane == 0) atomicExch(counters + (kCounterWords - 1), 1u);
+
+  // ---- the last CTA of a column range converts it to fp16 and re-zeroes the scratch ----
+  if (!finalize) return;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned total = per_range ? gridDim.y : gridDim.x * gridDim.y;
+    const unsigned prev = atomicAdd(counters + (per_range ? blockIdx.x : 0), 1u);
+    *s_last = (prev == total - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (*s_last) {
+    __threadfence();
+    const int lo = per_range ? m_begin : 0, hi_m = per_range ? m_end : M;
+    for (int mm = lo + tid * 4; mm < hi_m; mm += kBulkThreads * 4) {
+      if (!HQ_IN_BOUNDS(out + mm, 8, out, (size_t)M * 2, 215)) continue;
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(ws + mm));
+      const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+      *reinterpret_cast<uint2*>(out + mm) = make_uint2(half2_as_u32(h01), half2_as_u32(h23));
+      *reinterpret_cast<float4*>(ws + mm) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (tid == 0) counters[per_range ? blockIdx.x : 0] = 0u;
+  }
+}
+
 struct LaunchArgs {
   dim3 grid;
   cudaStream_t st;
@@ -374,7 +636,8 @@ struct LaunchArgs {
 template <int TR, int NB, int RPG>
 int launch_one(const LaunchArgs& a, int b0, const __half* bias, int finalize) {
   using L = Layout<TR>;
-  constexpr auto kern = lutgemm_kernel<TR, NB, RPG>;
+  constexpr int kThreads = TR == 4 ? 512 : 256;
+  constexpr auto kern = lutgemm_kernel<TR, NB, RPG, kThreads>;
   cudaError_t e = ensure_dynamic_smem<kern>(L::kSmem);
   if (e != cudaSuccess) return cuda_status(e);
   kern<<<a.grid, kThreads, L::kSmem, a.st>>>(a.bW, a.alpha, bias, a.x, a.out, a.ws, a.counters,
@@ -400,6 +663,43 @@ int launch_planes(const LaunchArgs& a) {
     else if (n == 2) st = launch_one<TR, 2, RPG>(a, b0, bias, last);
     else if (n == 3) st = launch_one<TR, 3, RPG>(a, b0, bias, last);
     else st = launch_one<TR, (kMax >= 4 ? 4 : 3), RPG>(a, b0, bias, last);
+    if (st != HQ_OK) return st;
+  }
+  return HQ_OK;
+}
+
+template <int NB>
+int launch_bulk_one(const LaunchArgs& a, int b0, const __half* bias, int finalize) {
+  constexpr auto kern = lutgemm_bulk_kernel<NB>;
+  const int stages = (a.cols_per_cta + kBulkCols - 1) / kBulkCols;
+  const size_t smem = (size_t)BulkLayout::kStage0 - kDynBase + (size_t)stages * BulkStage<NB>::kBytes;
+  cudaError_t e = ensure_dynamic_smem<kern>(smem);
+  if (e != cudaSuccess) return cuda_status(e);
+  kern<<<a.grid, kBulkThreads, smem, a.st>>>(a.bW, a.alpha, bias, a.x, a.out, a.ws, a.counters, a.M,
+                                             a.K, a.rows_per_group, a.cols_per_cta, a.nb_total, b0,
+                                             finalize, a.per_range);
+  return launch_status();
+}
+
+// stages of 512 columns that fit beside the tables for NB planes per launch
+inline int bulk_max_stages(int nb) {
+  const int stage = 2 * nb * kBulkCols * 4 + (nb + 1) * kBulkCols * 2;
+  const int room = 227 * 1024 - (BulkLayout::kStage0 - kDynBase);
+  return std::min(kMaxStages, room / stage);
+}
+
+// Planes in groups of up to 3 per launch (what leaves room for 8 stages)
+int launch_bulk_planes(const LaunchArgs& a) {
+  constexpr int kMax = 3;
+  const int nb = a.nb_total;
+  for (int b0 = 0; b0 < nb; b0 += kMax) {
+    const int n = nb - b0 < kMax ? nb - b0 : kMax;
+    const int last = (b0 + n == nb) ? 1 : 0;
+    const __half* bias = b0 == 0 ? a.q_bias : nullptr;
+    int st;
+    if (n == 1) st = launch_bulk_one<1>(a, b0, bias, last);
+    else if (n == 2) st = launch_bulk_one<2>(a, b0, bias, last);
+    else st = launch_bulk_one<3>(a, b0, bias, last);
     if (st != HQ_OK) return st;
   }
   return HQ_OK;
@@ -443,13 +743,43 @@ int hq_lutgemm_nqmv(void* out_half, const void* x_half, const uint32_t* bW, cons
   const int reserved = reserved_smem_per_block();
   if (reserved < kDynBase || reserved > kDynBase + kSlack) return HQ_ERR_UNSUPPORTED;
 
+  // Bulk-copy form: 64-input tiles, the whole column range of a CTA requested up front.
+  if (M % 8 == 0 && rpg % 2 == 0 && aligned16(alpha_half) &&
+      (!q_bias_half || aligned16(q_bias_half)) && !getenv("HQ_LUT_NO_BULK")) {
+    const int tiles2 = (K / 32 + 1) / 2;
+    const int max_cols = bulk_max_stages(std::min(nb, 3)) * kBulkCols;
+    // balanced column ranges of at most max_cols columns, multiples of 512
+    const int steps_total = (M + kBulkCols - 1) / kBulkCols;
+    const int ranges = (steps_total * kBulkCols + max_cols - 1) / max_cols;
+    const int steps_per_range = (steps_total + ranges - 1) / ranges;
+    LaunchArgs a;
+    a.cols_per_cta = steps_per_range * kBulkCols;
+    const int mblocks = (M + a.cols_per_cta - 1) / a.cols_per_cta;
+    a.grid = dim3(mblocks, tiles2);
+    a.st = (cudaStream_t)stream;
+    a.bW = bW;
+    a.alpha = reinterpret_cast<const __half*>(alpha_half);
+    a.q_bias = reinterpret_cast<const __half*>(q_bias_half);
+    a.x = reinterpret_cast<const __half*>(x_half);
+    a.out = reinterpret_cast<__half*>(out_half);
+    a.ws = reinterpret_cast<float*>(workspace);
+    a.counters = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
+                                             (hq_lutgemm_workspace_bytes(M) - 256));
+    a.M = M;
+    a.K = K;
+    a.rows_per_group = rpg;
+    a.nb_total = nb;
+    a.per_range = mblocks <= kCounterWords - 1 ? 1 : 0;
+    return launch_bulk_planes(a);
+  }
   // K tile: 128 inputs wherever alpha groups do not straddle it; 64 inputs for
   // groups of 192, 320, ... inputs
-  const int tile_rows = (rpg % 4 == 0 || rpg <= 2) ? 4 : 2;
+  int tile_rows = (rpg % 4 == 0 || rpg <= 2) ? 4 : 2;
+  if (getenv("HQ_LUT_TILE64") && rpg != 1 && rpg % 2 == 0) tile_rows = 2;  // development switch
   const int tiles = (K / 32 + tile_rows - 1) / tile_rows;
   // columns per CTA: a multiple of 256 chosen so the grid is close to a
-  // multiple of the SM count while the table build stays amortised.
-  const int slots = sm_count();
+  // multiple of the resident CTA slots while the table build stays amortised.
+  const int slots = sm_count() * (tile_rows == 2 ? 2 : 1);
   int best_cols = 256;
   double best_score = -1.0;
   const int max_chunks = (M + 255) / 256;

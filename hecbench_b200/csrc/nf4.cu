@@ -402,6 +402,211 @@ nf4_gemv_kernel(const GemvParams p) {
   }
 }
 
+// ---- bulk-copy form (rows of up to 4096 inputs) -------------------------------
+// A CTA owns a CONTIGUOUS range of rows and moves it through shared memory in
+// chunks of 16 rows (one row per warp): one bulk copy (cp.async.bulk, global ->
+// shared, completing on the chunk's mbarrier) for the chunk's 32 KB of packed
+// codes and one for its absmax run.  Few large copies is what the copy engine
+// is good at; with four chunk slots nearly a CTA's whole share of an
+// 11008 x 4096 layer (170 KB) is requested in the first microsecond, HBM
+// streams without gaps while the table is built and the input vector is
+// fetched, and no load instruction, address update or register is spent on
+// weights in the loop.  One warp owns a whole row (C = K / 1024 chunks per
+// lane), so a row ends with a shuffle tree and one store: no partial sums, no
+// barrier between warps.  A slot is refilled once all 16 warps have released
+// it.  Every mbarrier wait is bounded.
+constexpr int kTmaThreads = 512;
+constexpr int kTmaWarps = kTmaThreads / 32;   // = rows per chunk
+constexpr int kChunkSlots = 4;
+constexpr uint32_t kMbarSpins = 1u << 22;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// bounded wait for the phase with the given parity; false when the limit was hit
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kMbarSpins; i++) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// bulk copy global -> this CTA's shared memory; bytes a multiple of 16, both
+// addresses 16-byte aligned; completes on the mbarrier
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// C = chunks (32 codes) per lane = K / 1024.
+template <int C>
+__global__ void __launch_bounds__(kTmaThreads, 1)
+nf4_gemv_bulk_kernel(const GemvParams p, int rows_total) {
+  extern __shared__ __align__(16) unsigned char dsm_raw[];
+  // [pad up to shared address kLutImm] table rows (256 x 256 B) |
+  // chunk slots [kChunkSlots][16 rows of codes | 16 absmax runs] |
+  // mbarriers full[kChunkSlots], empty[kChunkSlots] | unpacked input (packet input only)
+  HQ_STAMP(0)
+  pdl_launch_dependents();
+  if (!p.early_fetch) pdl_wait();
+  unsigned char* dsm = dsm_raw + (kLutImm - smem_u32(dsm_raw));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t row_bytes = (uint32_t)p.nchunks * 16u;
+  const uint32_t am_bytes = ((uint32_t)p.nchunks >> p.cpb_shift) * 4u;
+  const uint32_t slot_bytes = (row_bytes + am_bytes) * kTmaWarps;
+  const uint32_t slots0 = smem_u32(dsm) + kLutBytes;
+  const uint32_t full0 = slots0 + kChunkSlots * slot_bytes;
+  const uint32_t empty0 = full0 + 8 * kChunkSlots;
+
+  // rows of this CTA: a contiguous, balanced range
+  const long long r0 = ((long long)rows_total * blockIdx.x) / gridDim.x;
+  const long long r1 = ((long long)rows_total * (blockIdx.x + 1)) / gridDim.x;
+  const int nrows = (int)(r1 - r0);
+  const int nchunk = (nrows + kTmaWarps - 1) / kTmaWarps;
+  // chunk c (rows r0 + 16c ..) into slot c % kChunkSlots; issued by one thread
+  auto request = [&](int c) {
+    const long long n = r0 + (long long)c * kTmaWarps;
+    const uint32_t rows = (uint32_t)min((long long)kTmaWarps, r1 - n);
+    const int s = c % kChunkSlots;
+    const uint32_t dst = slots0 + (uint32_t)s * slot_bytes, bar = full0 + 8u * s;
+    const unsigned char* src = p.B + (size_t)n * row_bytes;
+    const float* am = p.absmax + (((size_t)n * p.nchunks) >> p.cpb_shift);
+    if (HQ_IN_BOUNDS(src, rows * row_bytes, p.B, p.b_bytes, 121) &&
+        HQ_IN_BOUNDS(am, rows * am_bytes, p.absmax, p.absmax_bytes, 122)) {
+      mbar_expect_tx(bar, rows * (row_bytes + am_bytes));
+      bulk_load(dst, src, rows * row_bytes, bar);
+      bulk_load(dst + kTmaWarps * row_bytes, am, rows * am_bytes, bar);
+    } else {
+      mbar_expect_tx(bar, 0);  // checked build: the chunk is skipped, the waiters still pass
+    }
+  };
+  if (tid == 0) {
+    for (int s = 0; s < kChunkSlots; s++) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, kTmaWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int c = 0; c < nchunk && c < kChunkSlots; c++) request(c);
+  }
+  HQ_STAMP(1)
+
+  // ---- byte table (overlaps the copies) ----
+  for (int e4 = tid; e4 < 256 * 4; e4 += kTmaThreads) {
+    const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
+    const int hi = entry >> 4, lo = entry & 15;
+    const int first = p.low_first ? lo : hi, second = p.low_first ? hi : lo;
+    const uint32_t u = half2_as_u32(__floats2half2_rn(p.lut16[first], p.lut16[second]));
+    const uint4 u4 = make_uint4(u, u, u, u);
+    uint4* row = reinterpret_cast<uint4*>(dsm + (size_t)entry * 256 + quarter * 32);
+    row[entry & 1] = u4;
+    row[(entry & 1) ^ 1] = u4;
+  }
+  HQ_STAMP(2)
+  if (p.early_fetch) pdl_wait();
+  HQ_STAMP(3)
+  const uint32_t epoch_in =
+      p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
+  uint2* my_peer = nullptr;  // lane r stores the packets that go to rank r
+  if (p.peer_ll != nullptr && lane < p.world) my_peer = p.peer_ll[lane] + p.gather_offset;
+  const uint4* xsrc = reinterpret_cast<const uint4*>(p.A);
+  if (p.A_ll != nullptr) {
+    __half* xs = reinterpret_cast<__half*>(dsm + kLutBytes + (size_t)kChunkSlots * slot_bytes +
+                                           (size_t)16 * kChunkSlots);
+    for (int k = tid; k < p.nchunks * 32; k += kTmaThreads)
+      xs[k] = __ushort_as_half((unsigned short)wait_packet(p.A_ll + (size_t)k * p.a_stride,
+                                                           epoch_in, p.max_polls, p.status));
+    __syncthreads();
+    xsrc = reinterpret_cast<const uint4*>(xs);
+  }
+  uint4 xr[C][4];
+#pragma unroll
+  for (int i = 0; i < C; i++) {
+    const uint4* xp = xsrc + 4 * (i * 32 + lane);
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      if (p.A_ll != nullptr) xr[i][t] = xp[t];
+      else if (HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 123)) xr[i][t] = __ldg(xp + t);
+      else xr[i][t] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  __syncthreads();  // the table is complete, the barriers are initialised
+  HQ_STAMP(4)
+
+  const uint32_t lane4 = lane * 4;
+  bool ok = true;
+  for (int c = 0; c < nchunk; c++) {
+    const int s = c % kChunkSlots;
+    const uint32_t use = (uint32_t)(c / kChunkSlots);
+    const long long n = r0 + (long long)c * kTmaWarps + warp;
+    if (ok && !mbar_wait(full0 + 8u * s, use & 1u)) ok = false;
+    if (n < r1) {
+      const uint32_t codes = slots0 + (uint32_t)s * slot_bytes + (uint32_t)warp * row_bytes;
+      const uint32_t scales =
+          slots0 + (uint32_t)s * slot_bytes + kTmaWarps * row_bytes + (uint32_t)warp * am_bytes;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < C; i++) {
+        const int ch = i * 32 + lane;
+        uint4 cw;
+        float cs;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(cw.x), "=r"(cw.y), "=r"(cw.z), "=r"(cw.w)
+                     : "r"(codes + (uint32_t)ch * 16u));
+        asm volatile("ld.shared.f32 %0, [%1];"
+                     : "=f"(cs)
+                     : "r"(scales + ((uint32_t)ch >> p.cpb_shift) * 4u));
+        acc = fmaf(chunk_dot(cw, xr[i], lane4), cs, acc);
+      }
+      acc = warp_sum(acc);  // every lane's sum has arrived: the warp has read its row
+      const __half h = __float2half_rn(acc);
+      if (p.peer_ll == nullptr) {
+        if (lane == 0 && HQ_IN_BOUNDS(p.out + n, 2, p.out, p.out_bytes, 124)) p.out[n] = h;
+      } else if (my_peer != nullptr) {
+        st_packet(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
+      }
+    }
+    // release the slot; one thread refills it once all 16 warps have released it
+    if (c + kChunkSlots < nchunk) {
+      if (lane == 0) mbar_arrive(empty0 + 8u * s);
+      if (tid == 0) {
+        if (ok && !mbar_wait(empty0 + 8u * s, use & 1u)) ok = false;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        request(c + kChunkSlots);
+      }
+    }
+    HQ_STAMP(5 + min(c, 9))
+  }
+  if (!ok && p.status != nullptr && lane == 0) atomicExch(p.status, 1);
+  HQ_STAMP(15)
+  if (p.peer_ll != nullptr) {
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned prev = atomicAdd(p.sync_words, 1u);
+      if (prev == gridDim.x - 1) {
+        p.sync_words[0] = 0u;
+        *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) = epoch_in + 1u;
+      }
+    }
+  }
+}
+
 // Plain fp16 copy of a packet vector: thread i waits (bounded) until packet i
 // carries the epoch of the latest completed gather (sync_words[1]; no check
 // when sync_words is null) and stores its value.
@@ -419,25 +624,33 @@ ll_unpack_kernel(const uint2* __restrict__ ll, long long n, __half* __restrict__
   }
 }
 
-// One thread: 4 bytes of codes (8 elements) -> 16 bytes of fp16.
+// One thread and turn: 4 bytes of codes (8 elements) -> 16 bytes of fp16, two
+// turns in flight per thread.  SHIFT >= 0: words per absmax block is a power of
+// two (a shift instead of a division); the output is written with streaming
+// stores (it is 3.5x the size of everything that is read and not read again
+// here).
+__device__ __forceinline__ void st_stream_u4(void* p, const uint4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+template <bool POW2>
 __global__ void __launch_bounds__(kThreads)
 nf4_dequant_kernel(const uint8_t* __restrict__ B, const float* __restrict__ absmax,
                    const float* __restrict__ lut16, __half* __restrict__ out, size_t nwords,
-                   int words_per_block, int low_first) {
+                   int words_per_block, int shift, int low_first) {
   __shared__ float lut[16 * 32];  // [code][lane]
   const int tid = threadIdx.x, lane = tid & 31;
   for (int i = tid; i < 16 * 32; i += kThreads) lut[i] = lut16[i >> 5];
   __syncthreads();
   const float* lut_lane = lut + lane;
   const size_t stride = (size_t)gridDim.x * kThreads;
-  for (size_t w = (size_t)blockIdx.x * kThreads + tid; w < nwords; w += stride) {
-    if (!HQ_IN_BOUNDS(reinterpret_cast<const uint32_t*>(B) + w, 4, B, nwords * 4, 111) ||
-        !HQ_IN_BOUNDS(absmax + w / (size_t)words_per_block, 4, absmax,
-                      ((nwords + words_per_block - 1) / words_per_block) * 4, 112) ||
-        !HQ_IN_BOUNDS(reinterpret_cast<uint4*>(out) + w, 16, out, nwords * 16, 113))
-      continue;
-    const uint32_t codes = ldg_stream_u32(reinterpret_cast<const uint32_t*>(B) + w);
-    const float s = __ldg(absmax + w / (size_t)words_per_block);
+  auto block_of = [&](size_t w) -> size_t {
+    if (POW2) return w >> shift;
+    return nwords <= 0xffffffffull ? (size_t)((uint32_t)w / (uint32_t)words_per_block)
+                                   : w / (size_t)words_per_block;
+  };
+  auto convert = [&](uint32_t codes, float s) {
     uint32_t o[4];
 #pragma unroll
     for (int b = 0; b < 4; b++) {
@@ -448,7 +661,23 @@ nf4_dequant_kernel(const uint8_t* __restrict__ B, const float* __restrict__ absm
       const float v1 = __fmul_rn(lut_lane[second * 32], s);
       o[b] = half2_as_u32(__floats2half2_rn(v0, v1));
     }
-    reinterpret_cast<uint4*>(out)[w] = make_uint4(o[0], o[1], o[2], o[3]);
+    return make_uint4(o[0], o[1], o[2], o[3]);
+  };
+  const size_t nblocks = (nwords + words_per_block - 1) / words_per_block;
+  (void)nblocks;
+  for (size_t w = (size_t)blockIdx.x * kThreads + tid; w < nwords; w += 2 * stride) {
+    const size_t w2 = w + stride;
+    const bool two = w2 < nwords;
+    if (!HQ_IN_BOUNDS(reinterpret_cast<const uint32_t*>(B) + w, 4, B, nwords * 4, 111) ||
+        !HQ_IN_BOUNDS(absmax + block_of(w), 4, absmax, nblocks * 4, 112) ||
+        !HQ_IN_BOUNDS(reinterpret_cast<uint4*>(out) + w, 16, out, nwords * 16, 113))
+      continue;
+    const uint32_t c0 = ldg_stream_u32(reinterpret_cast<const uint32_t*>(B) + w);
+    const uint32_t c1 = two ? ldg_stream_u32(reinterpret_cast<const uint32_t*>(B) + w2) : 0u;
+    const float s0 = __ldg(absmax + block_of(w));
+    const float s1 = two ? __ldg(absmax + block_of(w2)) : 0.f;
+    st_stream_u4(reinterpret_cast<uint4*>(out) + w, convert(c0, s0));
+    if (two) st_stream_u4(reinterpret_cast<uint4*>(out) + w2, convert(c1, s1));
   }
 }
 
@@ -568,6 +797,25 @@ struct LlArgs {
   int* status = nullptr;
 };
 
+namespace hq {
+namespace {
+template <int C>
+int launch_gemv_bulk(GemvParams& prm, int N, cudaStream_t st) {
+  const uint32_t slot_bytes =
+      ((uint32_t)prm.nchunks * 16u + ((uint32_t)prm.nchunks >> prm.cpb_shift) * 4u) * kTmaWarps;
+  const size_t smem = (size_t)kLutImm + kLutBytes + (size_t)kChunkSlots * slot_bytes +
+                      (size_t)16 * kChunkSlots +
+                      (prm.A_ll != nullptr ? (size_t)prm.nchunks * 32 * sizeof(__half) : 0);
+  if (smem > 227 * 1024) return HQ_ERR_UNSUPPORTED;
+  const int grid = std::min(sm_count(), (N + kTmaWarps - 1) / kTmaWarps);
+  constexpr auto kern = nf4_gemv_bulk_kernel<C>;
+  cudaError_t e = ensure_dynamic_smem<kern>(smem);
+  if (e != cudaSuccess) return cuda_status(e);
+  return cuda_status(launch_pdl(kern, dim3(grid), dim3(kTmaThreads), smem, st, prm, N));
+}
+}  // namespace
+}  // namespace hq
+
 static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absmax,
                          const float* lut16, void* out_half, int N, int K, int blocksize, int flags,
                          const LlArgs& ll, hq_stream_t stream) {
@@ -640,6 +888,19 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
     }
   }
 #endif
+  // Rows of 1024 .. 4096 inputs whose codes and absmax runs start on 16-byte
+  // boundaries take the bulk-copy form (one warp per row).
+  if (aligned && nchunks % 32 == 0 && cols <= 4 && aligned16(absmax) &&
+      ((nchunks >> shift) * 4) % 16 == 0 && !getenv("HQ_NF4_NO_BULK")) {
+    int rc;
+    switch (cols) {
+      case 1: rc = launch_gemv_bulk<1>(prm, N, st); break;
+      case 2: rc = launch_gemv_bulk<2>(prm, N, st); break;
+      case 3: rc = launch_gemv_bulk<3>(prm, N, st); break;
+      default: rc = launch_gemv_bulk<4>(prm, N, st); break;
+    }
+    if (rc != HQ_ERR_UNSUPPORTED) return rc;
+  }
   // Chunks per lane C and warps per row S = cols / C.  512 threads with up to
   // 128 registers each hold C = 2 chunks of the input vector and D = 4 rows of
   // packed weights in flight per lane.
@@ -704,9 +965,19 @@ int hq_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut16
   const size_t want = (nwords + kThreads - 1) / kThreads;
   const size_t cap = (size_t)sm_count() * 16;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
-  nf4_dequant_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(
-      B, absmax, lut16, reinterpret_cast<__half*>(out_half), nwords, blocksize / 8,
-      (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0);
+  const int wpb = blocksize / 8;
+  int shift = -1;
+  if ((wpb & (wpb - 1)) == 0) {
+    shift = 0;
+    while ((1 << shift) < wpb) shift++;
+  }
+  const int low = (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0;
+  if (shift >= 0)
+    nf4_dequant_kernel<true><<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        B, absmax, lut16, reinterpret_cast<__half*>(out_half), nwords, wpb, shift, low);
+  else
+    nf4_dequant_kernel<false><<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        B, absmax, lut16, reinterpret_cast<__half*>(out_half), nwords, wpb, 0, low);
   return launch_status();
 }
 

@@ -28,12 +28,6 @@ constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 constexpr int kColsPerCta = 128;  // 32 lanes x 4 columns
 constexpr int kF16Words = 20;     // 18 half2 input pairs per group + 2 pad (16-byte rows)
-constexpr int kPrefetchAhead = 4; // turns (of kWarps groups) between an L2 prefetch and its use
-
-// Ask the L2 for `bytes` (a multiple of 16) at the 16-byte aligned address p.
-__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
 
 __device__ __forceinline__ float pow2f(int e) { return __int_as_float((e + 127) << 23); }
 
@@ -130,27 +124,8 @@ q3_gemv_kernel(const void* __restrict__ vec_, const int32_t* __restrict__ mat,
     n1 = ldg_stream_u4(p + width);
     n2 = ldg_stream_u4(p + 2 * (size_t)width);
   }
-  // lanes 0-2 also ask the L2 for the warp's 512-byte run of each of the three
-  // packed rows kPrefetchAhead turns ahead, so that the register loads (one
-  // turn ahead) find their lines in L2 instead of waiting for HBM
-  const int warp_col0 = blockIdx.x * kColsPerCta;
-  const uint32_t run_bytes = (uint32_t)min(kColsPerCta, max(0, width - warp_col0)) * 4u;
-  const int32_t* pf_base = mat + (size_t)g0 * 3 * width + warp_col0 + (size_t)lane * width;
-#ifdef HQ_Q3_NO_L2_PREFETCH
-  const bool pf_on = false;
-#else
-  const bool pf_on = true;
-#endif
-  if (pf_on && lane < 3 && run_bytes > 0) {
-#pragma unroll
-    for (int a = 1; a < kPrefetchAhead; a++)
-      if (warp + a * kWarps < ng)
-        l2_prefetch_bulk(pf_base + (size_t)(warp + a * kWarps) * 3 * width, run_bytes);
-  }
   for (int gi = warp; gi < ng; gi += kWarps) {
     const uint4 u0 = n0, u1 = n1, u2 = n2;
-    if (pf_on && lane < 3 && run_bytes > 0 && gi + kPrefetchAhead * kWarps < ng)
-      l2_prefetch_bulk(pf_base + (size_t)(gi + kPrefetchAhead * kWarps) * 3 * width, run_bytes);
     if (active && gi + kWarps < ng) {
       const int32_t* p = base + (size_t)(gi + kWarps) * 3 * width;
       n0 = ldg_stream_u4(p);

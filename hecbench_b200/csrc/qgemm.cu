@@ -58,6 +58,8 @@
 // and frees its tensor memory; the host reads the status word.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "hq_common.cuh"
 
 namespace hq {
@@ -209,35 +211,14 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 
-// Codes 2e and 2e+1 of a 96-bit stream (three words) as half2(q, q') without a
-// table: the two 16-bit windows that hold the fields are brought into the
-// halves of one register by a byte permute (a field at bit o <= 7 of a window
-// lies inside the 10 mantissa bits of a half), everything but the fields is
-// masked off and the exponent of 2^(10 - o) is OR-ed in, so each half reads
-// 2^(10 - o) + q exactly; subtracting 2^(10 - o) leaves q.  With e a constant
-// after unrolling every selector, mask and constant folds: PRMT + LOP3 + HADD2.
-#ifndef HQ_QGEMM_ARITH
-#define HQ_QGEMM_ARITH 0
-#endif
-__device__ __forceinline__ uint32_t q3_pair_half2(const uint32_t (&w)[3], int e) {
-  const int b0 = 6 * e, b1 = b0 + 3;
-  const int B0 = b0 >> 3, o0 = b0 & 7, B1 = b1 >> 3, o1 = b1 & 7;
-  const int a = B0 >> 2;  // first word involved
-  const int n0 = B0 - 4 * a, n1 = (B0 + 1 < 11 ? B0 + 1 : 11) - 4 * a;
-  const int n2 = B1 - 4 * a, n3 = (B1 + 1 < 11 ? B1 + 1 : 11) - 4 * a;
-  const uint32_t sel = (uint32_t)(n0 | (n1 << 4) | (n2 << 8) | (n3 << 12));
-  const uint32_t mask = (7u << o0) | (7u << (16 + o1));
-  const uint32_t expo = ((uint32_t)(25 - o0) << 10) | ((uint32_t)(25 - o1) << 26);
-  const uint32_t r = __byte_perm(w[a], w[a + 1 < 3 ? a + 1 : a], sel);
-  const uint32_t v = (r & mask) | expo;
-  return half2_as_u32(__hsub2(u32_as_half2(v), u32_as_half2(expo)));
-}
-
 struct QgemmParams {
   __half* Y;
   float* ws;            // fp32 [Mb][N] scratch + per-tile counters, used when ksplit > 1
   unsigned* counters;
   int* status;
+#ifdef HQ_QGEMM_TRACE
+  long long* trace;  // development: [CTA][4 roles][8] accumulated clock cycles
+#endif
   int Mb, N, K, group_size, tokens_padded, ksplit;
   // NF4 only (group_size is the absmax block size there)
   const float* absmax;
@@ -300,6 +281,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
   const int kb1 = (int)(((long long)nkb_total * (blockIdx.y + 1)) / p.ksplit);
   const int nloc = kb1 - kb0;
   bool ok = true;
+#ifdef HQ_QGEMM_TRACE
+  long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long tmark = clock64();
+#define HQ_TR(i) { const long long now_ = clock64(); tr[i] += now_ - tmark; tmark = now_; }
+#else
+#define HQ_TR(i)
+#endif
 
   if (tid == 0) {
     for (int s = 0; s < kXStages; s++) {
@@ -361,8 +349,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     uint32_t a_stage = (uint32_t)grp, a_use = 0, x_stage = (uint32_t)grp;
     uint32_t w_slot = (uint32_t)grp, w_parity = 0;
     if constexpr (FMT == kFmtQ3) {
+      HQ_TR(0)
       for (int i = grp; i < nloc; i += 2) {
         if (!mbar_wait(wfull0 + 8 * w_slot, w_parity, ok)) ok = false;
+        HQ_TR(1)
         uint32_t w[6];
         uint16_t sc_bits, z_bits;
         {
@@ -380,16 +370,6 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
         const __half2 sc2 = __half2half2(__ushort_as_half(sc_bits));
         const __half2 nz2 = __half2half2(__hneg(__ushort_as_half(z_bits)));
         uint32_t o[32];
-#if HQ_QGEMM_ARITH
-  #pragma unroll
-        for (int hf = 0; hf < 2; hf++) {
-          const uint32_t w3[3] = {w[3 * hf], w[3 * hf + 1], w[3 * hf + 2]};
-  #pragma unroll
-          for (int e = 0; e < 16; e++)
-            o[16 * hf + e] =
-                half2_as_u32(__hfma2(u32_as_half2(q3_pair_half2(w3, e)), sc2, nz2));
-        }
-#else
   #pragma unroll
         for (int hf = 0; hf < 2; hf++) {
           const uint32_t w0 = w[3 * hf], w1 = w[3 * hf + 1], w2 = w[3 * hf + 2];
@@ -413,21 +393,23 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
             o[16 * hf + e] = half2_as_u32(__hfma2(u32_as_half2(q2), sc2, nz2));
           }
         }
-#endif
         // the ring slot is released only now: the lookups above consumed the words,
         // so the loads have certainly returned
         __syncwarp();
         if (lane == 0) mbar_arrive(wempty0 + 8 * w_slot);
         w_slot += 2;
         if (w_slot >= kWordAhead) { w_slot -= kWordAhead; w_parity ^= 1u; }
+        HQ_TR(2)
         // the A tile of this stage must have been released by the tensor core
         if (a_use != 0 && !mbar_wait(empty0 + 8 * a_stage, (a_use - 1u) & 1u, ok)) ok = false;
+        HQ_TR(3)
         tc_fence_after();  // orders the stores after the tensor core's reads of the stage
         tmem_store_32(a_lane + a_stage * (uint32_t)kAColumns, o);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(full0 + 8 * x_stage);
+        HQ_TR(4)
         a_stage += 2;
         if (a_stage >= kStages) { a_stage -= kStages; a_use++; }
         x_stage += 2;
@@ -499,8 +481,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     const uint32_t acc = tmem_d + (uint32_t)(j * p.tokens_padded);
     uint32_t st = (uint32_t)j, xs = (uint32_t)j, xuse = 0;
     uint32_t accumulate = 0;
+    HQ_TR(0)
     for (int i = j; i < nloc; i += 2) {
       if (!mbar_wait(full0 + 8 * xs, xuse & 1u, ok)) ok = false;
+      HQ_TR(1)
       tc_fence_after();
       const uint32_t a_tmem = tmem_d + a_col0 + st * (uint32_t)kAColumns;
       const uint64_t bdesc = smem_desc(b_tiles + xs * kBTile);
@@ -511,6 +495,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
       }
       umma_commit(empty0 + 8 * st);
       umma_commit(xempty0 + 8 * xs);
+      HQ_TR(2)
       st += 2;
       if (st >= kStages) st -= kStages;
       xs += 2;
@@ -556,6 +541,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     }
   }
 
+#ifdef HQ_QGEMM_TRACE
+  if (p.trace != nullptr) {
+    int role = -1;
+    if (tid == 0) role = 0;            // unpack group 0
+    else if (tid == 128) role = 1;     // unpack group 1
+    else if (warp == 8 && lane == 0) role = 2;   // MMA issuer 0
+    else if (warp == 11 && lane == 0) role = 3;  // MMA issuer 1
+    if (role >= 0) {
+      HQ_TR(5)
+      for (int k = 0; k < 8; k++)
+        p.trace[((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 4 + role) * 8 + k] = tr[k];
+    }
+  }
+#endif
   if (warp < 8) {
     // ------------------------------ epilogue ------------------------------
     if (!mbar_wait(accum_bar, 0, ok)) ok = false;
@@ -700,6 +699,12 @@ QgemmParams make_params(void* Y_half, int Mb, int N, int K, int group_size, void
   prm.absmax = nullptr;
   prm.lut16 = nullptr;
   prm.low_first = 0;
+#ifdef HQ_QGEMM_TRACE
+  {
+    const char* tp = getenv("HQ_QGEMM_TRACE_PTR");
+    prm.trace = tp ? reinterpret_cast<long long*>(strtoull(tp, nullptr, 0)) : nullptr;
+  }
+#endif
   return prm;
 }
 

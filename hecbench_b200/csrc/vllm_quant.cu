@@ -154,16 +154,28 @@ vllm_dynamic_vec_kernel(const T* __restrict__ in, int8_t* __restrict__ out,
         }
       }
       const T* e = reinterpret_cast<const T*>(&raw);
+      // position of the chunk's first element inside the row (-EPC < lo < hidden)
+      const int lo = first < e1 ? (int)((long long)first - (long long)e0) : hidden;
+      if (lo >= 0 && lo + EPC <= hidden) {  // wholly inside the row: no masks
 #pragma unroll
-      for (int k = 0; k < EPC; k++) {
-        const bool mine = first + k >= e0 && first + k < e1;
-        const float x = to_float<T>(e[k]);
-        v[j][k] = x;
-        if (AZP) {
-          mx = fmaxf(mx, mine ? x : FLT_MIN);
-          mn = fminf(mn, mine ? x : FLT_MAX);
-        } else {
-          mx = fmaxf(mx, mine ? fabsf(x) : 0.f);
+        for (int k = 0; k < EPC; k++) {
+          const float x = to_float<T>(e[k]);
+          v[j][k] = x;
+          if (AZP) { mx = fmaxf(mx, x); mn = fminf(mn, x); }
+          else mx = fmaxf(mx, fabsf(x));
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPC; k++) {
+          const bool mine = (unsigned)(lo + k) < (unsigned)hidden;
+          const float x = to_float<T>(e[k]);
+          v[j][k] = x;
+          if (AZP) {
+            mx = fmaxf(mx, mine ? x : FLT_MIN);
+            mn = fminf(mn, mine ? x : FLT_MAX);
+          } else {
+            mx = fmaxf(mx, mine ? fabsf(x) : 0.f);
+          }
         }
       }
     }

@@ -201,8 +201,16 @@ def test_bnb_against_reference_kernel(hq, oracle, dev):
 
 # ------------------------------------------------------------------ nf4
 
-@pytest.mark.parametrize("N,K,bs,order", [(64, 256, 64, 0), (11008, 4096, 64, 0), (37, 1024, 64, 1),
-                                          (5, 4096, 128, 0), (130, 96, 32, 1), (16, 8192, 64, 0)])
+@pytest.mark.parametrize("N,K,bs,order", [
+    (64, 256, 64, 0), (11008, 4096, 64, 0), (37, 1024, 64, 1), (5, 4096, 128, 0),
+    (130, 96, 32, 1), (16, 8192, 64, 0),
+    # rows of 1024 .. 4096 inputs take the bulk-copy kernel: one row, fewer rows than
+    # CTAs, one more than the CTA count, several slot reuses per warp, every K / 1024,
+    # large and small blocks, low-nibble-first
+    (1, 4096, 64, 0), (149, 2048, 64, 1), (2369, 3072, 64, 0), (40000, 1024, 256, 0),
+    (24000, 4096, 1024, 1), (300, 4096, 32, 0),
+    # shapes that must fall back to the register-pipeline kernel
+    (33, 1056, 32, 0), (9, 12288, 64, 0), (3, 33792, 64, 1)])
 def test_nf4_gemv_and_dequant(hq, oracle, dev, N, K, bs, order):
     import torch
     A, B, absmax, lut = synth.nf4_case(N, K, bs, seed=N + K)
