@@ -19,10 +19,8 @@
 //    (128-bit streaming loads that bypass L1), D rows ahead of their use: the
 //    D*C outstanding 16-byte loads per thread are what covers the HBM
 //    latency, and nothing is staged through shared memory, whose bandwidth the
-//    table lookups need; optionally one lane per warp also asks the L2 for the
-//    warp's slice of the row PF rows ahead (a bulk L2 prefetch: one
-//    instruction for C*512 bytes), so that the register loads find their
-//    lines in L2;
+//    table lookups need (asking the L2 for rows further ahead with bulk
+//    prefetches was measured and made the kernel slower);
 //  * the lane's slice of the input vector never changes, so it lives in
 //    registers for the whole kernel;
 //  * one byte = two codes = one shared-memory lookup into a 256-entry half2
@@ -65,15 +63,6 @@ __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-// Ask the L2 for `bytes` (a multiple of 16) starting at the 16-byte aligned
-// address p; no data reaches the SM.
-__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void l2_prefetch_line(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 // sum of the 32 products of one 16-byte chunk against 16 half2 inputs
@@ -181,11 +170,11 @@ __device__ __forceinline__ uint32_t wait_packet(const uint2* p, uint32_t epoch, 
 
 // C = chunks (32 codes) per lane per row; D = rows in flight per lane; S warps
 // share a row (ST > 0: compile time, ST == 0: run time), G groups per CTA;
-// PF = distance (rows) of the L2 prefetch, 0 = none.  ALIGNED: every row
+// ALIGNED: every row
 // starts on an absmax block boundary and blocks are a power of two, so the
 // absmax pointer of a lane advances by a constant.  Nothing is divided on the
 // device in the ALIGNED kernels.
-template <int C, int D, int ST, bool ALIGNED, int THREADS, int PF>
+template <int C, int D, int ST, bool ALIGNED, int THREADS>
 __global__ void __launch_bounds__(THREADS, 1)
 nf4_gemv_kernel(const GemvParams p) {
   constexpr int W = THREADS / 32;
@@ -253,30 +242,6 @@ nf4_gemv_kernel(const GemvParams p) {
     }
     if (d < my_rows) HQ_NF4_LOAD(d)
   }
-  // L2 prefetch of this warp's slice of the rows D .. PF-1 (the steady state
-  // then asks for row j + PF while row j is computed)
-  const unsigned char* pfw = nullptr;
-  const float* pfa = nullptr;
-  const uint32_t pf_bytes =
-      (uint32_t)max(0, min(C * 512, (p.nchunks - q * C * 32) * 16));  // warp slice inside the row
-  if (PF > 0) {
-    // lane 0 prefetches codes, lane 1 the absmax line of the slice
-    pfw = p.B + (size_t)row_first * ((size_t)p.nchunks * 16) + (size_t)(q * C * 32) * 16;
-    if (ALIGNED)
-      pfa = p.absmax + (((uint32_t)row_first * (uint32_t)p.nchunks + (uint32_t)(q * C * 32)) >>
-                        p.cpb_shift);
-    pfw += (size_t)D * p.w_step;
-    if (ALIGNED) pfa += (size_t)D * p.a_step;
-    if (pf_bytes > 0) {
-      for (int j = D; j < PF && j < my_rows; j++) {
-        if (lane == 0) l2_prefetch_bulk(pfw, pf_bytes);
-        if (ALIGNED && lane == 1) l2_prefetch_line(pfa);
-        pfw += p.w_step;
-        if (ALIGNED) pfa += p.a_step;
-      }
-    }
-  }
-
   HQ_STAMP(1)
   // ---- prologue (overlaps the loads above): byte table, input slice ----
   for (int e4 = tid; e4 < 256 * 4; e4 += THREADS) {
@@ -353,14 +318,6 @@ nf4_gemv_kernel(const GemvParams p) {
 #pragma unroll
         for (int i = 0; i < C; i++) acc = fmaf(chunk_dot(cw[d][i], xr[i], lane4), cs[d][i], acc);
         if (j0 + d + D < my_rows) HQ_NF4_LOAD(d)
-        if (PF > 0) {
-          if (j0 + d + PF < my_rows && pf_bytes > 0) {
-            if (lane == 0) l2_prefetch_bulk(pfw, pf_bytes);
-            if (ALIGNED && lane == 1) l2_prefetch_line(pfa);
-            pfw += p.w_step;
-            if (ALIGNED) pfa += p.a_step;
-          }
-        }
         if (S > 1) {
           part_r[(d * S + q) * 32] = acc;
         } else {
@@ -759,7 +716,7 @@ gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
 namespace hq {
 namespace {
 
-template <int C, int D, int ST, bool AL, int THREADS, int PF>
+template <int C, int D, int ST, bool AL, int THREADS>
 int launch_gemv(GemvParams& prm, int N, cudaStream_t st) {
   constexpr int W = THREADS / 32;
   const int S = prm.S;
@@ -776,7 +733,7 @@ int launch_gemv(GemvParams& prm, int N, cudaStream_t st) {
   size_t smem = (size_t)kLutImm + kLutBytes + (size_t)2 * W * D * 32 * sizeof(float);
   if (prm.A_ll != nullptr) smem += (size_t)prm.nchunks * 32 * sizeof(__half);  // unpacked input
   if (smem > 227 * 1024) return HQ_ERR_TOO_LARGE;
-  constexpr auto kern = nf4_gemv_kernel<C, D, ST, AL, THREADS, PF>;
+  constexpr auto kern = nf4_gemv_kernel<C, D, ST, AL, THREADS>;
   cudaError_t e = ensure_dynamic_smem<kern>(smem);
   if (e != cudaSuccess) return cuda_status(e);
   return cuda_status(launch_pdl(kern, dim3(grid), dim3(THREADS), smem, st, prm));
@@ -871,27 +828,12 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   }
 #endif
   cudaStream_t st = (cudaStream_t)stream;
-#ifdef HQ_NF4_SWEEP
-#define HQ_NF4_SWEEP_LIST                                                                       \
-  V(0, 1, 4, 1024, 0) V(1, 1, 4, 1024, 8) V(2, 1, 6, 768, 0) V(3, 2, 4, 512, 0) V(4, 2, 6, 512, 0) \
-  V(5, 2, 4, 512, 8) V(6, 4, 2, 512, 8) V(7, 4, 3, 512, 0) V(8, 1, 4, 768, 8) V(9, 2, 3, 512, 8)  \
-  V(10, 1, 3, 1024, 8) V(11, 2, 5, 512, 0) V(12, 2, 2, 512, 8) V(13, 1, 8, 512, 0)                \
-  V(14, 1, 8, 768, 0) V(15, 2, 4, 512, 16) V(16, 1, 6, 768, 12) V(17, 1, 4, 1024, 16)
-  if (cols == 4 && aligned) {
-    const char* env = getenv("HQ_NF4_VARIANT");
-    const int v = env ? atoi(env) : -1;
-    switch (v) {
-#define V(ID, CC, DD, TT, PP) case ID: prm.S = 4 / CC; return launch_gemv<CC, DD, 4 / CC, true, TT, PP>(prm, N, st);
-      HQ_NF4_SWEEP_LIST
-#undef V
-      default: break;
-    }
-  }
-#endif
-  // Rows of 1024 .. 4096 inputs whose codes and absmax runs start on 16-byte
-  // boundaries take the bulk-copy form (one warp per row).
-  if (aligned && nchunks % 32 == 0 && cols <= 4 && aligned16(absmax) &&
-      ((nchunks >> shift) * 4) % 16 == 0 && !getenv("HQ_NF4_NO_BULK")) {
+  // The bulk-copy form is opt-in (environment HQ_NF4_BULK=1): on B200 it measured
+  // 10.1 us against 7.8 us for the register pipeline on an 11008 x 4096 layer.
+  // It takes rows of 1024 .. 4096 inputs whose codes and absmax runs start on
+  // 16-byte boundaries (one warp per row).
+  if (env_flag("HQ_NF4_BULK") && aligned && nchunks % 32 == 0 && cols <= 4 && aligned16(absmax) &&
+      ((nchunks >> shift) * 4) % 16 == 0) {
     int rc;
     switch (cols) {
       case 1: rc = launch_gemv_bulk<1>(prm, N, st); break;
@@ -904,15 +846,15 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   // Chunks per lane C and warps per row S = cols / C.  512 threads with up to
   // 128 registers each hold C = 2 chunks of the input vector and D = 4 rows of
   // packed weights in flight per lane.
-  if (aligned && cols == 4) { prm.S = 2; return launch_gemv<2, 4, 2, true, 512, 0>(prm, N, st); }
+  if (aligned && cols == 4) { prm.S = 2; return launch_gemv<2, 4, 2, true, 512>(prm, N, st); }
   int C = cols <= 1 ? 1 : (cols <= 32 ? 2 : 4);
   prm.S = (cols + C - 1) / C;
-  if (C == 1) return aligned ? launch_gemv<1, 4, 1, true, 512, 0>(prm, N, st)
-                             : launch_gemv<1, 4, 1, false, 512, 0>(prm, N, st);
-  if (C == 2) return aligned ? launch_gemv<2, 4, 0, true, 512, 0>(prm, N, st)
-                             : launch_gemv<2, 4, 0, false, 512, 0>(prm, N, st);
-  return aligned ? launch_gemv<4, 2, 0, true, 512, 0>(prm, N, st)
-                 : launch_gemv<4, 2, 0, false, 512, 0>(prm, N, st);
+  if (C == 1) return aligned ? launch_gemv<1, 4, 1, true, 512>(prm, N, st)
+                             : launch_gemv<1, 4, 1, false, 512>(prm, N, st);
+  if (C == 2) return aligned ? launch_gemv<2, 4, 0, true, 512>(prm, N, st)
+                             : launch_gemv<2, 4, 0, false, 512>(prm, N, st);
+  return aligned ? launch_gemv<4, 2, 0, true, 512>(prm, N, st)
+                 : launch_gemv<4, 2, 0, false, 512>(prm, N, st);
 }
 
 extern "C" {

@@ -204,15 +204,21 @@ def test_bnb_against_reference_kernel(hq, oracle, dev):
 @pytest.mark.parametrize("N,K,bs,order", [
     (64, 256, 64, 0), (11008, 4096, 64, 0), (37, 1024, 64, 1), (5, 4096, 128, 0),
     (130, 96, 32, 1), (16, 8192, 64, 0),
-    # rows of 1024 .. 4096 inputs take the bulk-copy kernel: one row, fewer rows than
-    # CTAs, one more than the CTA count, several slot reuses per warp, every K / 1024,
-    # large and small blocks, low-nibble-first
+    # one row, fewer rows than CTAs, one more than the CTA count, every K / 1024, large
+    # and small blocks, low-nibble-first
     (1, 4096, 64, 0), (149, 2048, 64, 1), (2369, 3072, 64, 0), (40000, 1024, 256, 0),
     (24000, 4096, 1024, 1), (300, 4096, 32, 0),
-    # shapes that must fall back to the register-pipeline kernel
+    # ragged rows, long rows
     (33, 1056, 32, 0), (9, 12288, 64, 0), (3, 33792, 64, 1)])
-def test_nf4_gemv_and_dequant(hq, oracle, dev, N, K, bs, order):
+@pytest.mark.parametrize("form", ["register", "bulk"])
+def test_nf4_gemv_and_dequant(hq, oracle, dev, monkeypatch, N, K, bs, order, form):
+    """form "bulk": the opt-in bulk-copy GEMV (rows of 1024 .. 4096 inputs; every
+    other shape must still fall back to the register pipeline)."""
     import torch
+    if form == "bulk":
+        monkeypatch.setenv("HQ_NF4_BULK", "1")
+    else:
+        monkeypatch.delenv("HQ_NF4_BULK", raising=False)
     A, B, absmax, lut = synth.nf4_case(N, K, bs, seed=N + K)
     dA = to_dev(A.view(np.uint16), dev).view(torch.float16)
     dB, dabs, dlut = to_dev(B, dev), to_dev(absmax, dev), to_dev(lut, dev)
@@ -291,8 +297,14 @@ def test_nf4_dequant_then_dense_matches_gemv(hq, oracle, dev):
     (512, 256, 8, 128, True), (260, 160, 3, 32, True), (1024, 256, 2, 64, True),
     (12288, 12288, 3, 128, True), (256, 512, 1, 256, False), (64, 4096, 5, 512, True),
     (1024, 768, 3, 192, True), (516, 960, 5, 320, False)])  # groups of 192 / 320 inputs: 64-input tiles
-def test_lutgemm_nqmv(hq, oracle, dev, M, K, nb, gs, bias):
+@pytest.mark.parametrize("form", ["register", "bulk"])
+def test_lutgemm_nqmv(hq, oracle, dev, monkeypatch, M, K, nb, gs, bias, form):
+    """form "bulk": the opt-in bulk-copy kernel (shapes it does not take fall back)."""
     import torch
+    if form == "bulk":
+        monkeypatch.setenv("HQ_LUT_BULK", "1")
+    else:
+        monkeypatch.delenv("HQ_LUT_BULK", raising=False)
     x, bW, alpha, qb = synth.lutgemm_case(M, K, nb, gs, seed=M + K + nb, bias=bias)
     w = hq.nQWeight_fp16()
     w.parsing(bW, alpha.astype(np.float32), K, M, nb, False, K // gs,
