@@ -262,7 +262,7 @@ class DeviceWorkload:
             self.x = [t(c["x"]) for _ in range(R)]
             self.out = [torch.empty(c["m"], dtype=torch.float16, device=dev) for _ in range(R)]
 
-    def launch(self, i: int, out=None, pdl: bool = PDL):
+    def launch(self, i: int, out=None, pdl: bool = PDL, peers=None):
         hq, c, n = self.hq, self.case, self.name
         if n == "nf4_gemv":
             hq.gemv_nf4(self.x[i], self.B[i], self.absmax[i], self.lut, c["N"], c["K"], c["bs"], 0,
@@ -293,10 +293,10 @@ class DeviceWorkload:
                                          self.scales, self.azp if "azp" in n else None)
         elif n.startswith("qgemm_q3"):
             hq.qgemm_q3(self.x[i], self.mat[i], self.sc, self.z, self.n_local, c["K"], 128,
-                        out=self.out[i] if out is None else out)
+                        out=self.out[i] if out is None else out, peers=peers)
         elif n.startswith("qgemm_nf4"):
             hq.qgemm_nf4(self.x[i], self.B[i], self.absmax, self.lut, self.n_local, c["K"], c["bs"],
-                         0, out=self.out[i] if out is None else out)
+                         0, out=self.out[i] if out is None else out, peers=peers)
 
     # host <-> device traffic of one launch on the end-to-end path
     def host_io(self):
@@ -630,7 +630,7 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="N > 1: every rank its own shard of an N-times wider layer (weak), or "
                          "the one layer's output features split over the ranks (strong)")
-    ap.add_argument("--gather", default=None, choices=["packets", "publish", "nccl"],
+    ap.add_argument("--gather", default=None, choices=["packets", "fused", "publish", "nccl"],
                     help="N > 1: how the output slices of a layer are gathered")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -658,9 +658,12 @@ def main():
     strong = world > 1 and args.scaling == "strong"
     if strong and not batched:
         raise SystemExit("--scaling strong is wired for the batched workloads (qgemm_*)")
-    gather = args.gather or ("packets" if name == "nf4_gemv" else "publish")
+    gather = args.gather or ("packets" if name == "nf4_gemv" else "fused" if batched else "publish")
     if gather == "packets" and name != "nf4_gemv":
         raise SystemExit("--gather packets is the NF4 GEMV's low-latency form")
+    if gather == "fused" and not batched:
+        raise SystemExit("--gather fused is the batched product's form (tiles stored to all GPUs "
+                         "by the epilogue)")
     if world > 1 and not (batched or name == "nf4_gemv"):
         raise SystemExit("N > 1 is wired for nf4_gemv and the batched workloads")
 
@@ -693,7 +696,7 @@ def main():
         if gather == "packets":
             packets = PacketGather(gshard, slots=R, device=dev)
             stride = (world * c["N"]) // c["K"]
-        elif gather == "publish" and hasattr(wl, "out"):
+        elif gather in ("publish", "fused") and hasattr(wl, "out"):
             peer = PeerGather(gshard, slots=R, device=dev, rows=rows_out)
         elif hasattr(wl, "out"):
             gathered = [torch.empty(world * wl.out[i].numel(), dtype=wl.out[i].dtype, device=dev)
@@ -711,9 +714,15 @@ def main():
                 packets.gemv_nf4(i, None, wl.B[i], wl.absmax[i], wl.lut, c["K"], c["bs"],
                                  weights_resident=PDL, a_slot=i - 1, a_stride=stride)
             return
+        if peer is not None and gather == "fused":
+            # the product's epilogue stores every finished tile into the slice of all
+            # GPUs; one small kernel then raises the flags and waits (bounded)
+            wl.launch(i, peers=peer.peers(i))
+            peer.publish(i, stored=True)
+            return
         if peer is not None:
             # ordinary kernel into this rank's slice of its own gathered buffer, then
-            # one small kernel: peer stores over NVLink, flags, bounded wait
+            # one kernel: peer stores over NVLink, flags, bounded wait
             wl.launch(i, out=peer.local_slice(i))
             peer.publish(i)
             return
@@ -944,6 +953,9 @@ def main():
             how = {"packets": "every finished row stored as an 8-byte {value, epoch} packet into "
                               "every GPU's vector over NVLink by the GEMV itself; the next layer "
                               "reads its input from the packets (bounded waits)",
+                   "fused": "every finished 128-feature tile stored into every GPU's gathered "
+                            "buffer over NVLink by the product's own epilogue; a one-CTA kernel "
+                            "raises the flags and waits (bounded) after every layer",
                    "publish": "slices copied into every GPU's gathered buffer by our own kernel "
                               "(peer stores over NVLink + flags), bounded wait after every layer",
                    "nccl": "NCCL all-gather of the slices after every layer"}[gather]

@@ -58,6 +58,10 @@ SIGNATURES = {
                                                                c_void_p]),
     "hq_qgemm_nf4_f16": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p, c_size_t, c_void_p,
                                                                 c_void_p]),
+    "hq_qgemm_q3_f16_peers": (c_int, [c_void_p] * 5 + [C.c_longlong] + [c_int] * 5 +
+                              [c_void_p, c_size_t, c_void_p, c_void_p]),
+    "hq_qgemm_nf4_f16_peers": (c_int, [c_void_p] * 5 + [C.c_longlong] + [c_int] * 6 +
+                               [c_void_p, c_size_t, c_void_p, c_void_p]),
     "hq_vllm_static_scaled_int8_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, C.c_float,
                                                  C.c_int32, c_void_p]),
     "hq_vllm_dynamic_scaled_int8_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int,

@@ -324,44 +324,62 @@ def qgemm_reset_workspaces() -> None:
 
 def qgemm_q3(X, mat, scales, zeros, N: int, K: int, group_size: int = 128,
              out: Optional[torch.Tensor] = None,
-             status: Optional[torch.Tensor] = None, split_k: bool = True) -> torch.Tensor:
+             status: Optional[torch.Tensor] = None, split_k: bool = True,
+             peers=None) -> Optional[torch.Tensor]:
     """Y[Mb][N] = X[Mb][K] @ dequant(mat) for the GPTQ 3-bit layout with per-group
     fp16 scales / zeros [K/group_size][N] (no counterpart in the reference tree).
     `status` (int32[1], optional) receives 1 if a bounded in-kernel wait ran out;
     call qgemm_reset_workspaces() before the next product in that case.
-    With split_k a zero-initialised scratch matrix is kept per (device, stream, Mb, N)."""
+    With split_k a zero-initialised scratch matrix is kept per (device, stream, Mb, N).
+    peers = (pointer_table, offset_elements, world): store every finished tile into
+    the output slice of every GPU of the node instead of `out` (hq_qgemm_q3_f16_peers);
+    returns None in that form."""
     lib = load_library()
     Mb = X.shape[0]
-    if out is None:
-        out = torch.empty((Mb, N), dtype=torch.float16, device=X.device)
-    args = (
+    head = (
         _dev(X, torch.float16, "X"), _dev(mat, torch.int32, "mat"),
-        _dev(scales, torch.float16, "scales"), _dev(zeros, torch.float16, "zeros"),
-        _dev(out, torch.float16, "out"), Mb, N, K, group_size)
+        _dev(scales, torch.float16, "scales"), _dev(zeros, torch.float16, "zeros"))
     ws_ptr, ws_bytes = _qgemm_workspace(lib, X.device, Mb, N) if split_k else (0, 0)
     st = 0 if status is None else _dev(status, torch.int32, "status")
     with torch.cuda.device(X.device):
-        check("hq_qgemm_q3_f16", lib.hq_qgemm_q3_f16(*args, ws_ptr, ws_bytes, st, _stream()))
+        if peers is not None:
+            table, offset, world = peers
+            check("hq_qgemm_q3_f16_peers", lib.hq_qgemm_q3_f16_peers(
+                *head, int(table), int(offset), int(world), Mb, N, K, group_size, ws_ptr, ws_bytes,
+                st, _stream()))
+            return None
+        if out is None:
+            out = torch.empty((Mb, N), dtype=torch.float16, device=X.device)
+        check("hq_qgemm_q3_f16", lib.hq_qgemm_q3_f16(
+            *head, _dev(out, torch.float16, "out"), Mb, N, K, group_size, ws_ptr, ws_bytes, st,
+            _stream()))
     return out
 
 
 def qgemm_nf4(X, B, absmax, lut16, N: int, K: int, blocksize: int = 64, nibble_order: int = 0,
               out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-              split_k: bool = True) -> torch.Tensor:
+              split_k: bool = True, peers=None) -> Optional[torch.Tensor]:
     """Y[Mb][N] = X[Mb][K] @ W with W[k][n] the NF4 weight that dequantize_nf4
     gives for element n*K + k of B (uint8[N*K/2], absmax per `blocksize`
-    elements); same conventions as gemv_nf4, same workspace and status rules as
-    qgemm_q3 (no counterpart in the reference tree)."""
+    elements); same conventions as gemv_nf4, same workspace, status and `peers`
+    rules as qgemm_q3 (no counterpart in the reference tree)."""
     lib = load_library()
     Mb = X.shape[0]
-    if out is None:
-        out = torch.empty((Mb, N), dtype=torch.float16, device=X.device)
-    args = (
+    head = (
         _dev(X, torch.float16, "X"), _dev(B, torch.uint8, "B"),
-        _dev(absmax, torch.float32, "absmax"), _dev(lut16, torch.float32, "lut16"),
-        _dev(out, torch.float16, "out"), Mb, N, K, blocksize, nibble_order)
+        _dev(absmax, torch.float32, "absmax"), _dev(lut16, torch.float32, "lut16"))
     ws_ptr, ws_bytes = _qgemm_workspace(lib, X.device, Mb, N) if split_k else (0, 0)
     st = 0 if status is None else _dev(status, torch.int32, "status")
     with torch.cuda.device(X.device):
-        check("hq_qgemm_nf4_f16", lib.hq_qgemm_nf4_f16(*args, ws_ptr, ws_bytes, st, _stream()))
+        if peers is not None:
+            table, offset, world = peers
+            check("hq_qgemm_nf4_f16_peers", lib.hq_qgemm_nf4_f16_peers(
+                *head, int(table), int(offset), int(world), Mb, N, K, blocksize, nibble_order,
+                ws_ptr, ws_bytes, st, _stream()))
+            return None
+        if out is None:
+            out = torch.empty((Mb, N), dtype=torch.float16, device=X.device)
+        check("hq_qgemm_nf4_f16", lib.hq_qgemm_nf4_f16(
+            *head, _dev(out, torch.float16, "out"), Mb, N, K, blocksize, nibble_order, ws_ptr,
+            ws_bytes, st, _stream()))
     return out

@@ -168,6 +168,34 @@ __device__ __forceinline__ uint32_t wait_packet(const uint2* p, uint32_t epoch, 
   return v.x;
 }
 
+// The input vector given as packets -> plain fp16 in shared memory.  The loads of
+// a batch are all issued before the first is examined (examined one at a time, a
+// thread's packets cost one L2 round trip each: 8 x 0.5 us at K = 4096); only a
+// packet that does not carry the epoch yet is polled.
+template <int THREADS>
+__device__ __forceinline__ void stage_packets(__half* xs, const uint2* ll, long long stride, int n,
+                                              uint32_t epoch, unsigned max_polls, int* status,
+                                              int tid) {
+  constexpr int kBatch = 8;
+  for (int k0 = tid; k0 < n; k0 += THREADS * kBatch) {
+    uint2 v[kBatch];
+#pragma unroll
+    for (int b = 0; b < kBatch; b++) {
+      const int k = k0 + b * THREADS;
+      v[b] = k < n ? ld_packet(ll + (size_t)k * stride) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; b++) {
+      const int k = k0 + b * THREADS;
+      if (k < n) {
+        const uint32_t val =
+            v[b].y == epoch ? v[b].x : wait_packet(ll + (size_t)k * stride, epoch, max_polls, status);
+        xs[k] = __ushort_as_half((unsigned short)val);
+      }
+    }
+  }
+}
+
 // C = chunks (32 codes) per lane per row; D = rows in flight per lane; S warps
 // share a row (ST > 0: compile time, ST == 0: run time), G groups per CTA;
 // ALIGNED: every row
@@ -197,6 +225,23 @@ nf4_gemv_kernel(const GemvParams p) {
   const int row_first = blockIdx.x + gridDim.x * g;
   const int row_stride = gridDim.x * G;
   const int my_rows = g < G ? p.rows_base + (row_first < p.rows_rem ? 1 : 0) : 0;
+
+  // The 16 levels first: the table build must not queue behind the weight loads
+  // below.  (The levels count as weights: read before the wait with early_fetch.)
+  constexpr int kTabTurns = (256 * 4 + THREADS - 1) / THREADS;
+  float lv_first[kTabTurns], lv_second[kTabTurns];
+#pragma unroll
+  for (int t = 0; t < kTabTurns; t++) {
+    const int entry = ((tid + t * THREADS) >> 2) & 255;
+    const int hi = entry >> 4, lo = entry & 15;
+    lv_first[t] = p.lut16[p.low_first ? lo : hi];
+    lv_second[t] = p.lut16[p.low_first ? hi : lo];
+  }
+  // ... and a hint to the L2 for the lines of the input vector, which may only be
+  // READ after the wait (a prefetch moves no data to the SM)
+  if (p.early_fetch && p.A != nullptr)
+    for (int line = tid; line * 128 < p.nchunks * 64; line += THREADS)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.A) + line * 128));
 
   // this lane's chunk columns; a lane beyond the row end loads nothing and
   // keeps zero codes, scales and inputs
@@ -244,15 +289,17 @@ nf4_gemv_kernel(const GemvParams p) {
   }
   HQ_STAMP(1)
   // ---- prologue (overlaps the loads above): byte table, input slice ----
-  for (int e4 = tid; e4 < 256 * 4; e4 += THREADS) {
-    const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
-    const int hi = entry >> 4, lo = entry & 15;
-    const int first = p.low_first ? lo : hi, second = p.low_first ? hi : lo;
-    const uint32_t u = half2_as_u32(__floats2half2_rn(p.lut16[first], p.lut16[second]));
-    const uint4 u4 = make_uint4(u, u, u, u);
-    uint4* row = reinterpret_cast<uint4*>(dsm + (size_t)entry * 256 + quarter * 32);
-    row[entry & 1] = u4;
-    row[(entry & 1) ^ 1] = u4;
+#pragma unroll
+  for (int t = 0; t < kTabTurns; t++) {
+    const int e4 = tid + t * THREADS;
+    if (e4 < 256 * 4) {
+      const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
+      const uint32_t u = half2_as_u32(__floats2half2_rn(lv_first[t], lv_second[t]));
+      const uint4 u4 = make_uint4(u, u, u, u);
+      uint4* row = reinterpret_cast<uint4*>(dsm + (size_t)entry * 256 + quarter * 32);
+      row[entry & 1] = u4;
+      row[(entry & 1) ^ 1] = u4;
+    }
   }
   // the input vector (and, without early_fetch, everything) is read only after
   // the preceding kernel has completed
@@ -270,9 +317,8 @@ nf4_gemv_kernel(const GemvParams p) {
     // the whole input arrives as packets: every thread waits for its share and
     // leaves plain fp16 in shared memory
     __half* xs = reinterpret_cast<__half*>(dsm + kLutBytes + (size_t)2 * W * D * 32 * sizeof(float));
-    for (int k = tid; k < p.nchunks * 32; k += THREADS)
-      xs[k] = __ushort_as_half((unsigned short)wait_packet(p.A_ll + (size_t)k * p.a_stride,
-                                                           epoch_in, p.max_polls, p.status));
+    stage_packets<THREADS>(xs, p.A_ll, p.a_stride, p.nchunks * 32, epoch_in, p.max_polls, p.status,
+                           tid);
     __syncthreads();
     xsrc = reinterpret_cast<const uint4*>(xs);
   }
@@ -361,20 +407,25 @@ nf4_gemv_kernel(const GemvParams p) {
 
 // ---- bulk-copy form (rows of up to 4096 inputs) -------------------------------
 // A CTA owns a CONTIGUOUS range of rows and moves it through shared memory in
-// chunks of 16 rows (one row per warp): one bulk copy (cp.async.bulk, global ->
-// shared, completing on the chunk's mbarrier) for the chunk's 32 KB of packed
-// codes and one for its absmax run.  Few large copies is what the copy engine
-// is good at; with four chunk slots nearly a CTA's whole share of an
-// 11008 x 4096 layer (170 KB) is requested in the first microsecond, HBM
-// streams without gaps while the table is built and the input vector is
-// fetched, and no load instruction, address update or register is spent on
-// weights in the loop.  One warp owns a whole row (C = K / 1024 chunks per
+// chunks of 16 rows (one row per compute warp): one bulk copy (cp.async.bulk,
+// global -> shared, completing on the chunk's mbarrier) for the chunk's packed
+// codes and one for its absmax run, into one of four chunk slots.  A seventeenth
+// warp does nothing but issue these copies.  It keeps at most kCopiesInFlight
+// chunks outstanding and issues the next one when the oldest has LANDED (not
+// when a slot has been consumed): requested all at once, the copies of a CTA
+// are served side by side and the first chunk arrives with the last; paced by
+// arrival they land in order at the full rate, and by the time the input vector
+// is there most of the CTA's share of an 11008 x 4096 layer sits in shared
+// memory.  No load instruction, address update or register is spent on weights
+// in the compute warps.  One warp owns a whole row (C = K / 1024 chunks per
 // lane), so a row ends with a shuffle tree and one store: no partial sums, no
-// barrier between warps.  A slot is refilled once all 16 warps have released
-// it.  Every mbarrier wait is bounded.
-constexpr int kTmaThreads = 512;
-constexpr int kTmaWarps = kTmaThreads / 32;   // = rows per chunk
+// barrier between warps.  A slot is refilled once all 16 compute warps have
+// released it.  Every mbarrier wait is bounded.
+constexpr int kTmaWarps = 16;                      // compute warps = rows per chunk
+constexpr int kTmaCompute = kTmaWarps * 32;        // compute threads
+constexpr int kTmaThreads = kTmaCompute + 32;      // + the copy warp
 constexpr int kChunkSlots = 4;
+constexpr int kCopiesInFlight = 2;
 constexpr uint32_t kMbarSpins = 1u << 22;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -454,111 +505,142 @@ nf4_gemv_bulk_kernel(const GemvParams p, int rows_total) {
       mbar_expect_tx(bar, 0);  // checked build: the chunk is skipped, the waiters still pass
     }
   };
-  if (tid == 0) {
+  const bool copy_thread = tid == kTmaCompute;
+  int issued = 0;
+  if (copy_thread) {
     for (int s = 0; s < kChunkSlots; s++) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, kTmaWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    for (int c = 0; c < nchunk && c < kChunkSlots; c++) request(c);
+    for (; issued < nchunk && issued < kCopiesInFlight; issued++) request(issued);
   }
   HQ_STAMP(1)
+  __syncthreads();  // the barriers are initialised for everybody
 
-  // ---- byte table (overlaps the copies) ----
-  for (int e4 = tid; e4 < 256 * 4; e4 += kTmaThreads) {
-    const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
-    const int hi = entry >> 4, lo = entry & 15;
-    const int first = p.low_first ? lo : hi, second = p.low_first ? hi : lo;
-    const uint32_t u = half2_as_u32(__floats2half2_rn(p.lut16[first], p.lut16[second]));
-    const uint4 u4 = make_uint4(u, u, u, u);
-    uint4* row = reinterpret_cast<uint4*>(dsm + (size_t)entry * 256 + quarter * 32);
-    row[entry & 1] = u4;
-    row[(entry & 1) ^ 1] = u4;
-  }
-  HQ_STAMP(2)
-  if (p.early_fetch) pdl_wait();
-  HQ_STAMP(3)
-  const uint32_t epoch_in =
-      p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
-  uint2* my_peer = nullptr;  // lane r stores the packets that go to rank r
-  if (p.peer_ll != nullptr && lane < p.world) my_peer = p.peer_ll[lane] + p.gather_offset;
-  const uint4* xsrc = reinterpret_cast<const uint4*>(p.A);
-  if (p.A_ll != nullptr) {
-    __half* xs = reinterpret_cast<__half*>(dsm + kLutBytes + (size_t)kChunkSlots * slot_bytes +
-                                           (size_t)16 * kChunkSlots);
-    for (int k = tid; k < p.nchunks * 32; k += kTmaThreads)
-      xs[k] = __ushort_as_half((unsigned short)wait_packet(p.A_ll + (size_t)k * p.a_stride,
-                                                           epoch_in, p.max_polls, p.status));
-    __syncthreads();
-    xsrc = reinterpret_cast<const uint4*>(xs);
-  }
-  uint4 xr[C][4];
-#pragma unroll
-  for (int i = 0; i < C; i++) {
-    const uint4* xp = xsrc + 4 * (i * 32 + lane);
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-      if (p.A_ll != nullptr) xr[i][t] = xp[t];
-      else if (HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 123)) xr[i][t] = __ldg(xp + t);
-      else xr[i][t] = make_uint4(0, 0, 0, 0);
-    }
-  }
-  __syncthreads();  // the table is complete, the barriers are initialised
-  HQ_STAMP(4)
-
-  const uint32_t lane4 = lane * 4;
-  bool ok = true;
-  for (int c = 0; c < nchunk; c++) {
-    const int s = c % kChunkSlots;
-    const uint32_t use = (uint32_t)(c / kChunkSlots);
-    const long long n = r0 + (long long)c * kTmaWarps + warp;
-    if (ok && !mbar_wait(full0 + 8u * s, use & 1u)) ok = false;
-    if (n < r1) {
-      const uint32_t codes = slots0 + (uint32_t)s * slot_bytes + (uint32_t)warp * row_bytes;
-      const uint32_t scales =
-          slots0 + (uint32_t)s * slot_bytes + kTmaWarps * row_bytes + (uint32_t)warp * am_bytes;
-      float acc = 0.f;
-#pragma unroll
-      for (int i = 0; i < C; i++) {
-        const int ch = i * 32 + lane;
-        uint4 cw;
-        float cs;
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(cw.x), "=r"(cw.y), "=r"(cw.z), "=r"(cw.w)
-                     : "r"(codes + (uint32_t)ch * 16u));
-        asm volatile("ld.shared.f32 %0, [%1];"
-                     : "=f"(cs)
-                     : "r"(scales + ((uint32_t)ch >> p.cpb_shift) * 4u));
-        acc = fmaf(chunk_dot(cw, xr[i], lane4), cs, acc);
+  if (warp == kTmaWarps) {
+    // ---- the copy warp: one thread paces the remaining chunks ----
+    if (copy_thread) {
+      bool ok = true;
+      int landed = 0;
+      while (ok && issued < nchunk) {
+        // the oldest outstanding chunk has landed ...
+        if (!mbar_wait(full0 + 8u * (landed % kChunkSlots), (uint32_t)(landed / kChunkSlots) & 1u)) {
+          ok = false;
+          break;
+        }
+        landed++;
+        // ... and the slot of the next one is free (its previous chunk consumed)
+        const int s = issued % kChunkSlots;
+        if (issued >= kChunkSlots) {
+          if (!mbar_wait(empty0 + 8u * s, (uint32_t)(issued / kChunkSlots - 1) & 1u)) {
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        request(issued);
+        issued++;
       }
-      acc = warp_sum(acc);  // every lane's sum has arrived: the warp has read its row
-      const __half h = __float2half_rn(acc);
-      if (p.peer_ll == nullptr) {
-        if (lane == 0 && HQ_IN_BOUNDS(p.out + n, 2, p.out, p.out_bytes, 124)) p.out[n] = h;
-      } else if (my_peer != nullptr) {
-        st_packet(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
+      if (!ok && p.status != nullptr) atomicExch(p.status, 1);
+    }
+  } else {
+    // ---- byte table (overlaps the copies) ----
+    constexpr int kTabTurns = (256 * 4 + kTmaCompute - 1) / kTmaCompute;
+#pragma unroll
+    for (int t = 0; t < kTabTurns; t++) {
+      const int e4 = tid + t * kTmaCompute;
+      if (e4 < 256 * 4) {
+        const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
+        const int hi = entry >> 4, lo = entry & 15;
+        const int first = p.low_first ? lo : hi, second = p.low_first ? hi : lo;
+        const uint32_t u = half2_as_u32(__floats2half2_rn(p.lut16[first], p.lut16[second]));
+        const uint4 u4 = make_uint4(u, u, u, u);
+        uint4* row = reinterpret_cast<uint4*>(dsm + (size_t)entry * 256 + quarter * 32);
+        row[entry & 1] = u4;
+        row[(entry & 1) ^ 1] = u4;
       }
     }
-    // release the slot; one thread refills it once all 16 warps have released it
-    if (c + kChunkSlots < nchunk) {
-      if (lane == 0) mbar_arrive(empty0 + 8u * s);
+    if (p.early_fetch && p.A != nullptr)
+      for (int line = tid; line * 128 < p.nchunks * 64; line += kTmaCompute)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.A) + line * 128));
+    HQ_STAMP(2)
+    if (p.early_fetch) pdl_wait();
+    HQ_STAMP(3)
+    const uint32_t epoch_in =
+        p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
+    uint2* my_peer = nullptr;  // lane r stores the packets that go to rank r
+    if (p.peer_ll != nullptr && lane < p.world) my_peer = p.peer_ll[lane] + p.gather_offset;
+    const uint4* xsrc = reinterpret_cast<const uint4*>(p.A);
+    if (p.A_ll != nullptr) {
+      __half* xs = reinterpret_cast<__half*>(dsm + kLutBytes + (size_t)kChunkSlots * slot_bytes +
+                                             (size_t)16 * kChunkSlots);
+      stage_packets<kTmaCompute>(xs, p.A_ll, p.a_stride, p.nchunks * 32, epoch_in, p.max_polls,
+                                 p.status, tid);
+      group_barrier(1, kTmaCompute);
+      xsrc = reinterpret_cast<const uint4*>(xs);
+    }
+    uint4 xr[C][4];
+#pragma unroll
+    for (int i = 0; i < C; i++) {
+      const uint4* xp = xsrc + 4 * (i * 32 + lane);
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        if (p.A_ll != nullptr) xr[i][t] = xp[t];
+        else if (HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 123)) xr[i][t] = __ldg(xp + t);
+        else xr[i][t] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    group_barrier(1, kTmaCompute);  // the table is complete
+    HQ_STAMP(4)
+
+    const uint32_t lane4 = lane * 4;
+    bool ok = true;
+    for (int c = 0; c < nchunk; c++) {
+      const int s = c % kChunkSlots;
+      const uint32_t use = (uint32_t)(c / kChunkSlots);
+      const long long n = r0 + (long long)c * kTmaWarps + warp;
+      if (ok && !mbar_wait(full0 + 8u * s, use & 1u)) ok = false;
+      if (n < r1) {
+        const uint32_t codes = slots0 + (uint32_t)s * slot_bytes + (uint32_t)warp * row_bytes;
+        const uint32_t scales =
+            slots0 + (uint32_t)s * slot_bytes + kTmaWarps * row_bytes + (uint32_t)warp * am_bytes;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < C; i++) {
+          const int ch = i * 32 + lane;
+          uint4 cw;
+          float cs;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(cw.x), "=r"(cw.y), "=r"(cw.z), "=r"(cw.w)
+                       : "r"(codes + (uint32_t)ch * 16u));
+          asm volatile("ld.shared.f32 %0, [%1];"
+                       : "=f"(cs)
+                       : "r"(scales + ((uint32_t)ch >> p.cpb_shift) * 4u));
+          acc = fmaf(chunk_dot(cw, xr[i], lane4), cs, acc);
+        }
+        acc = warp_sum(acc);  // every lane's sum has arrived: the warp has read its row
+        const __half h = __float2half_rn(acc);
+        if (p.peer_ll == nullptr) {
+          if (lane == 0 && HQ_IN_BOUNDS(p.out + n, 2, p.out, p.out_bytes, 124)) p.out[n] = h;
+        } else if (my_peer != nullptr) {
+          st_packet(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
+        }
+      }
+      // release the slot: the copy warp refills it once all 16 warps have released it
+      if (c + kChunkSlots < nchunk && lane == 0) mbar_arrive(empty0 + 8u * s);
+      HQ_STAMP(5 + min(c, 9))
+    }
+    if (!ok && p.status != nullptr && lane == 0) atomicExch(p.status, 1);
+    HQ_STAMP(15)
+    if (p.peer_ll != nullptr) {
+      group_barrier(1, kTmaCompute);
       if (tid == 0) {
-        if (ok && !mbar_wait(empty0 + 8u * s, use & 1u)) ok = false;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        request(c + kChunkSlots);
-      }
-    }
-    HQ_STAMP(5 + min(c, 9))
-  }
-  if (!ok && p.status != nullptr && lane == 0) atomicExch(p.status, 1);
-  HQ_STAMP(15)
-  if (p.peer_ll != nullptr) {
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned prev = atomicAdd(p.sync_words, 1u);
-      if (prev == gridDim.x - 1) {
-        p.sync_words[0] = 0u;
-        *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) = epoch_in + 1u;
+        const unsigned prev = atomicAdd(p.sync_words, 1u);
+        if (prev == gridDim.x - 1) {
+          p.sync_words[0] = 0u;
+          *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) = epoch_in + 1u;
+        }
       }
     }
   }
@@ -574,10 +656,24 @@ ll_unpack_kernel(const uint2* __restrict__ ll, long long n, __half* __restrict__
   pdl_wait();
   const bool check = sync_words != nullptr;
   const uint32_t epoch = check ? *reinterpret_cast<const volatile unsigned*>(sync_words + 1) : 0u;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
-    const uint32_t v = check ? wait_packet(ll + i, epoch, max_polls, status) : ld_packet(ll + i).x;
-    out[i] = __ushort_as_half((unsigned short)v);
+  // four packets per thread and turn, loaded before the first is examined
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n; i0 += 4 * step) {
+    uint2 v[4];
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+      const long long i = i0 + b * step;
+      v[b] = i < n ? ld_packet(ll + i) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+      const long long i = i0 + b * step;
+      if (i < n) {
+        const uint32_t val =
+            (!check || v[b].y == epoch) ? v[b].x : wait_packet(ll + i, epoch, max_polls, status);
+        out[i] = __ushort_as_half((unsigned short)val);
+      }
+    }
   }
 }
 
@@ -656,18 +752,21 @@ __global__ void gather_wait_kernel(const uint32_t* flags, const unsigned* sync_w
   else if (status != nullptr) atomicExch(status, 1);
 }
 
-// One CTA per rank r of the node: CTA r copies this rank's finished slice
-// (already in its own gathered vector) into rank r's vector with 16-byte stores
-// over NVLink, makes the stores visible system-wide, raises this rank's flag on
-// GPU r, then waits (bounded) until rank r's flag on THIS GPU has reached the
-// same launch count.  The last CTA to finish advances the launch count.
+// Copies this rank's finished slice (already in its own gathered vector) into
+// every peer's vector with 16-byte stores over NVLink, the (peer, piece) pairs
+// spread over the CTAs of the grid; the CTA that finishes last raises this
+// rank's flag on every GPU, waits (bounded) until every rank's flag on THIS GPU
+// has reached the same launch count and advances the launch count.  With an
+// empty slice (the producing kernel stored to the peers itself) only the
+// signalling remains.
 constexpr int kPublishThreads = 1024;
+constexpr int kPublishPiece = kPublishThreads * 16;  // bytes one CTA moves per sweep
 __global__ void __launch_bounds__(kPublishThreads, 1)
 gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
                       uint32_t* const* peer_flags, unsigned* sync_words, int world, int rank,
                       unsigned max_polls, int* status) {
+  __shared__ unsigned s_last;
   const int tid = threadIdx.x;
-  const int r = blockIdx.x;
   // Programmatic dependent launch: these CTAs may become resident while the kernel
   // that produces the slice is still draining, and the next kernel of the stream
   // may start its own prologue while they wait for the other ranks; the slice is
@@ -675,38 +774,57 @@ gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
   pdl_launch_dependents();
   pdl_wait();
   const unsigned epoch = *reinterpret_cast<volatile unsigned*>(sync_words + 1) + 1u;
-  if (r != rank) {
-    const __half* mine = peer_out[rank] + offset;
+  // work items = (peer, 16 KB piece of the slice), dealt round-robin to the CTAs;
+  // consecutive items go to different peers so that all links carry data at once
+  const long long bytes = (long long)n_slice * 2;
+  const int pieces = (int)((bytes + kPublishPiece - 1) / kPublishPiece);
+  const int peers = world - 1;
+  const bool vec_ok = ((offset | (long long)n_slice) & 7) == 0;
+  const __half* mine = peer_out[rank] + offset;
+  for (int item = blockIdx.x; item < pieces * peers; item += gridDim.x) {
+    const int piece = item / peers, pr = item - piece * peers;
+    const int r = pr + (pr >= rank ? 1 : 0);
     __half* dst = peer_out[r] + offset;
-    const bool vec_ok = ((offset | (long long)n_slice) & 7) == 0;
     if (vec_ok) {
-      for (int i = tid; i < n_slice / 8; i += kPublishThreads)
+      const int i = piece * kPublishThreads + tid;
+      if (i < n_slice / 8)
         reinterpret_cast<uint4*>(dst)[i] = __ldcg(reinterpret_cast<const uint4*>(mine) + i);
     } else {
-      for (int i = tid; i < n_slice; i += kPublishThreads)
+      const int i0 = piece * (kPublishPiece / 2);
+      for (int i = i0 + tid; i < min(i0 + kPublishPiece / 2, n_slice); i += kPublishThreads)
         reinterpret_cast<unsigned short*>(dst)[i] =
             __ldcg(reinterpret_cast<const unsigned short*>(mine) + i);
     }
-    __threadfence_system();
   }
+  // every CTA makes its own stores visible system-wide before it is counted; the
+  // CTA that is counted last raises the flags, so a flag is ordered after the
+  // stores of ALL CTAs (fence - atomic - fence)
+  __threadfence_system();
   __syncthreads();
   if (tid == 0) {
-    *reinterpret_cast<volatile uint32_t*>(peer_flags[r] + rank) = epoch;
-    const volatile uint32_t* f = peer_flags[rank] + r;
-    bool landed = false;
+    const unsigned prev = atomicAdd(sync_words, 1u);
+    s_last = prev == gridDim.x - 1u ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last == 0u) return;
+  __threadfence_system();
+  bool landed = true;
+  if (tid < world) {
+    // thread r: this rank's flag on GPU r, then rank r's flag here
+    *reinterpret_cast<volatile uint32_t*>(peer_flags[tid] + rank) = epoch;
+    const volatile uint32_t* f = peer_flags[rank] + tid;
+    landed = false;
     for (unsigned spin = 0; spin < max_polls; spin++) {
       if ((int)(*f - epoch) >= 0) { landed = true; break; }
       __nanosleep(32);
     }
     if (landed) __threadfence_system();
     else if (status != nullptr) atomicExch(status, 1);
-    // every CTA has read the old launch count before it gets here
-    __threadfence();
-    const unsigned prev = atomicAdd(sync_words, 1u);
-    if (prev == (unsigned)world - 1u) {
-      sync_words[1] = epoch;
-      sync_words[0] = 0u;
-    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    sync_words[0] = 0u;
+    *reinterpret_cast<volatile unsigned*>(sync_words + 1) = epoch;
   }
 }
 
@@ -864,8 +982,12 @@ int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
                       unsigned max_polls, int* status, hq_stream_t stream) {
   using namespace hq;
   if (!peer_out_half || !peer_flags || !sync_words) return HQ_ERR_NULL_POINTER;
-  if (world < 1 || world > 32 || rank < 0 || rank >= world || n_slice <= 0) return HQ_ERR_BAD_SHAPE;
-  return cuda_status(launch_pdl(gather_publish_kernel, dim3(world), dim3(kPublishThreads), 0,
+  if (world < 1 || world > 32 || rank < 0 || rank >= world || n_slice < 0) return HQ_ERR_BAD_SHAPE;
+  // one CTA per (peer, 16 KB piece) up to the number of SMs; n_slice == 0: the
+  // producing kernel has stored the slice to the peers itself, only signal and wait
+  const long long pieces = ((long long)n_slice * 2 + kPublishPiece - 1) / kPublishPiece;
+  const int grid = (int)std::max<long long>(1, std::min<long long>(pieces * (world - 1), sm_count()));
+  return cuda_status(launch_pdl(gather_publish_kernel, dim3(grid), dim3(kPublishThreads), 0,
                                 (cudaStream_t)stream,
                                 reinterpret_cast<__half* const*>(peer_out_half), offset, n_slice,
                                 peer_flags, sync_words, world, rank,

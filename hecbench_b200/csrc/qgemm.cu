@@ -70,7 +70,6 @@ constexpr int kBlockK = 64;                 // halves per smem row (128 bytes)
 constexpr int kTileN = 128;                 // output features per CTA (UMMA M)
 constexpr int kMaxTokens = 128;             // UMMA N upper bound handled here
 constexpr int kAColumns = kBlockK / 2;      // tensor-memory columns of one A stage (2 halves each)
-constexpr int kDeqLut = 64 * 128;           // 64 pair values x 32 lane copies x 4 B
 enum { kFmtQ3 = 0, kFmtNf4 = 1 };
 // bytes of one block's packed weights in the ring
 //   3-bit: 6 rows x 128 words, then 128 scales and 128 zeros;  NF4: 128 rows x 32 bytes
@@ -142,9 +141,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void fence_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -165,15 +161,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
   return d;
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                         uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0)
-      : "memory");
-}
-// the same with the A operand in tensor memory (128 lanes x 8 columns of two halves per K = 16)
+// tcgen05.mma, A operand in tensor memory (128 lanes x 8 columns of two halves per K = 16)
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
                                             uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -199,20 +187,16 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 
 
 struct QgemmParams {
   __half* Y;
+  // Sharded layers: when peer_Y is non-null the tile is stored, as soon as it is
+  // finished, into the output slice of EVERY GPU of the node (peer_Y[r] + y_offset,
+  // peer-mapped memory, the local GPU included) instead of Y.
+  __half* const* peer_Y;
+  long long y_offset;
+  int world;
   float* ws;            // fp32 [Mb][N] scratch + per-tile counters, used when ksplit > 1
   unsigned* counters;
   int* status;
@@ -225,6 +209,13 @@ struct QgemmParams {
   const float* lut16;
   int low_first;
 };
+
+// output slice of this launch on GPU g (the table is constant during the launch)
+__device__ __forceinline__ __half* peer_slice(const QgemmParams& p, int g) {
+  return reinterpret_cast<__half*>(
+             __ldg(reinterpret_cast<const unsigned long long*>(p.peer_Y) + g)) +
+         p.y_offset;
+}
 
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -588,11 +579,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
       } else {
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
-      if (p.ksplit == 1) {
+      if (p.ksplit == 1 && p.peer_Y == nullptr) {
 #pragma unroll
         for (int j = 0; j < 16; j++)
           if (j0 + j < p.Mb)
             p.Y[(size_t)(j0 + j) * p.N + n] = __float2half_rn(__uint_as_float(r[j]));
+      } else if (p.ksplit == 1) {
+        // 32 lanes = 32 consecutive features: 64 contiguous bytes per store and GPU
+        for (int g = 0; g < p.world; g++) {
+          __half* Yg = peer_slice(p, g);
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            if (j0 + j < p.Mb)
+              Yg[(size_t)(j0 + j) * p.N + n] = __float2half_rn(__uint_as_float(r[j]));
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < 16; j++)
@@ -624,7 +624,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
       for (int idx = tid; idx < p.Mb * kTileN; idx += kThreads) {
         const int j = idx / kTileN, c = idx - j * kTileN;
         float* w = p.ws + (size_t)j * p.N + n0 + c;
-        p.Y[(size_t)j * p.N + n0 + c] = __float2half_rn(__ldcg(w));
+        const __half h = __float2half_rn(__ldcg(w));
+        if (p.peer_Y == nullptr) {
+          p.Y[(size_t)j * p.N + n0 + c] = h;
+        } else {
+          for (int g = 0; g < p.world; g++)
+            peer_slice(p, g)[(size_t)j * p.N + n0 + c] = h;
+        }
         *w = 0.f;
       }
       if (tid == 0) p.counters[blockIdx.x] = 0u;
@@ -685,6 +691,9 @@ QgemmParams make_params(void* Y_half, int Mb, int N, int K, int group_size, void
     if (ksplit < 1) ksplit = 1;
   }
   prm.Y = reinterpret_cast<__half*>(Y_half);
+  prm.peer_Y = nullptr;
+  prm.y_offset = 0;
+  prm.world = 1;
   prm.ws = reinterpret_cast<float*>(workspace);
   prm.counters = workspace ? reinterpret_cast<unsigned*>(reinterpret_cast<char*>(workspace) +
                                                          ((size_t)Mb * N * 4 + 255) / 256 * 256)
@@ -722,19 +731,21 @@ int launch_qgemm(const CUtensorMap& map_x, const CUtensorMap& map_w, const CUten
 }  // namespace
 }  // namespace hq
 
-extern "C" {
+// Where a sharded launch stores its tiles (all null / 1 without sharding).
+struct PeerOut {
+  void* const* peer_Y = nullptr;
+  long long y_offset = 0;
+  int world = 1;
+};
 
-size_t hq_qgemm_workspace_bytes(int Mb, int N) {
-  if (Mb <= 0 || N <= 0) return 0;
-  return hq::qgemm_ws_bytes(Mb, N);
-}
-
-int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_half,
-                    const void* zeros_half, void* Y_half, int Mb, int N, int K, int group_size,
-                    void* workspace, size_t workspace_bytes, int* status_word,
-                    hq_stream_t stream) {
+static int qgemm_q3_impl(const void* X_half, const int32_t* mat, const void* scales_half,
+                         const void* zeros_half, void* Y_half, const PeerOut& po, int Mb, int N,
+                         int K, int group_size, void* workspace, size_t workspace_bytes,
+                         int* status_word, hq_stream_t stream) {
   using namespace hq;
-  if (!X_half || !mat || !scales_half || !zeros_half || !Y_half) return HQ_ERR_NULL_POINTER;
+  if (!X_half || !mat || !scales_half || !zeros_half || (!Y_half && !po.peer_Y))
+    return HQ_ERR_NULL_POINTER;
+  if (po.peer_Y && (po.world < 1 || po.world > 32 || po.y_offset < 0)) return HQ_ERR_BAD_SHAPE;
   if (Mb <= 0 || Mb > kMaxTokens || N <= 0 || K <= 0 || N % kTileN != 0 || K % kBlockK != 0)
     return HQ_ERR_BAD_SHAPE;
   if (group_size <= 0 || group_size % kBlockK != 0 || K % group_size != 0) return HQ_ERR_BAD_SHAPE;
@@ -769,14 +780,19 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
       return HQ_ERR_UNSUPPORTED;
   }
   QgemmParams prm = make_params(Y_half, Mb, N, K, group_size, workspace, workspace_bytes, status_word);
+  prm.peer_Y = reinterpret_cast<__half* const*>(po.peer_Y);
+  prm.y_offset = po.y_offset;
+  prm.world = po.world;
   return launch_qgemm<kFmtQ3>(map_x, map_w, map_s, map_z, prm, stream);
 }
 
-int hq_qgemm_nf4_f16(const void* X_half, const uint8_t* B, const float* absmax, const float* lut16,
-                     void* Y_half, int Mb, int N, int K, int blocksize, int flags, void* workspace,
-                     size_t workspace_bytes, int* status_word, hq_stream_t stream) {
+static int qgemm_nf4_impl(const void* X_half, const uint8_t* B, const float* absmax,
+                          const float* lut16, void* Y_half, const PeerOut& po, int Mb, int N, int K,
+                          int blocksize, int flags, void* workspace, size_t workspace_bytes,
+                          int* status_word, hq_stream_t stream) {
   using namespace hq;
-  if (!X_half || !B || !absmax || !lut16 || !Y_half) return HQ_ERR_NULL_POINTER;
+  if (!X_half || !B || !absmax || !lut16 || (!Y_half && !po.peer_Y)) return HQ_ERR_NULL_POINTER;
+  if (po.peer_Y && (po.world < 1 || po.world > 32 || po.y_offset < 0)) return HQ_ERR_BAD_SHAPE;
   if (Mb <= 0 || Mb > kMaxTokens || N <= 0 || K <= 0 || N % kTileN != 0 || K % kBlockK != 0)
     return HQ_ERR_BAD_SHAPE;
   // one absmax per (row, K block): blocks of 64 k inputs that never straddle a row
@@ -803,7 +819,61 @@ int hq_qgemm_nf4_f16(const void* X_half, const uint8_t* B, const float* absmax, 
   prm.absmax = absmax;
   prm.lut16 = lut16;
   prm.low_first = (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0;
+  prm.peer_Y = reinterpret_cast<__half* const*>(po.peer_Y);
+  prm.y_offset = po.y_offset;
+  prm.world = po.world;
   return launch_qgemm<kFmtNf4>(map_x, map_w, map_w, map_w, prm, stream);
+}
+
+extern "C" {
+
+size_t hq_qgemm_workspace_bytes(int Mb, int N) {
+  if (Mb <= 0 || N <= 0) return 0;
+  return hq::qgemm_ws_bytes(Mb, N);
+}
+
+int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_half,
+                    const void* zeros_half, void* Y_half, int Mb, int N, int K, int group_size,
+                    void* workspace, size_t workspace_bytes, int* status_word,
+                    hq_stream_t stream) {
+  if (!Y_half) return HQ_ERR_NULL_POINTER;
+  return qgemm_q3_impl(X_half, mat, scales_half, zeros_half, Y_half, PeerOut(), Mb, N, K,
+                       group_size, workspace, workspace_bytes, status_word, stream);
+}
+
+int hq_qgemm_q3_f16_peers(const void* X_half, const int32_t* mat, const void* scales_half,
+                          const void* zeros_half, void* const* peer_Y_half, long long y_offset,
+                          int world, int Mb, int N, int K, int group_size, void* workspace,
+                          size_t workspace_bytes, int* status_word, hq_stream_t stream) {
+  if (!peer_Y_half) return HQ_ERR_NULL_POINTER;
+  PeerOut po;
+  po.peer_Y = peer_Y_half;
+  po.y_offset = y_offset;
+  po.world = world;
+  return qgemm_q3_impl(X_half, mat, scales_half, zeros_half, nullptr, po, Mb, N, K, group_size,
+                       workspace, workspace_bytes, status_word, stream);
+}
+
+int hq_qgemm_nf4_f16(const void* X_half, const uint8_t* B, const float* absmax, const float* lut16,
+                     void* Y_half, int Mb, int N, int K, int blocksize, int flags, void* workspace,
+                     size_t workspace_bytes, int* status_word, hq_stream_t stream) {
+  if (!Y_half) return HQ_ERR_NULL_POINTER;
+  return qgemm_nf4_impl(X_half, B, absmax, lut16, Y_half, PeerOut(), Mb, N, K, blocksize, flags,
+                        workspace, workspace_bytes, status_word, stream);
+}
+
+int hq_qgemm_nf4_f16_peers(const void* X_half, const uint8_t* B, const float* absmax,
+                           const float* lut16, void* const* peer_Y_half, long long y_offset,
+                           int world, int Mb, int N, int K, int blocksize, int flags,
+                           void* workspace, size_t workspace_bytes, int* status_word,
+                           hq_stream_t stream) {
+  if (!peer_Y_half) return HQ_ERR_NULL_POINTER;
+  PeerOut po;
+  po.peer_Y = peer_Y_half;
+  po.y_offset = y_offset;
+  po.world = world;
+  return qgemm_nf4_impl(X_half, B, absmax, lut16, nullptr, po, Mb, N, K, blocksize, flags,
+                        workspace, workspace_bytes, status_word, stream);
 }
 
 }  // extern "C"

@@ -213,18 +213,32 @@ class PeerGather:
             return self.slot(i)[sh.rank * sh.n_local:(sh.rank + 1) * sh.n_local]
         return self.slot(i)[sh.rank]
 
-    def publish(self, i: int) -> None:
-        """Copy the local slice of buffer i to all peers, flag it, and wait (bounded)
-        for the peers' slices of the same round."""
+    def _slice_offset(self, i: int) -> int:
+        """Element offset of this rank's slice of buffer i inside every rank's data
+        region (index arithmetic shared with the C hosts: hq_shard_layout)."""
         import ctypes
         from ._lib import check, load_library
         sh = self.shard
-        lib = load_library()
-        first = ctypes.c_longlong()  # index arithmetic shared with the C hosts (hq_shard_layout)
-        check("hq_shard_layout", lib.hq_shard_layout(sh.world, self.rows, sh.n_local, self.slots,
-                                                     sh.rank, i, None, ctypes.byref(first), None))
-        check("hq_gather_publish", lib.hq_gather_publish(
-            self.peer_data.data_ptr(), first.value, self.slice_elems, self.peer_flags.data_ptr(), self.sync.data_ptr(), sh.world, sh.rank,
+        first = ctypes.c_longlong()
+        check("hq_shard_layout", load_library().hq_shard_layout(
+            sh.world, self.rows, sh.n_local, self.slots, sh.rank, i, None, ctypes.byref(first), None))
+        return first.value
+
+    def peers(self, i: int):
+        """(pointer table, element offset, world) of this rank's slice of buffer i on
+        every GPU: the `peers` argument of qgemm_q3 / qgemm_nf4, whose epilogue then
+        stores each finished tile to all GPUs; follow with publish(i, stored=True)."""
+        return (self.peer_data.data_ptr(), self._slice_offset(i), self.shard.world)
+
+    def publish(self, i: int, stored: bool = False) -> None:
+        """Copy the local slice of buffer i to all peers, flag it, and wait (bounded)
+        for the peers' slices of the same round.  stored=True: the producing kernel
+        has stored the slice to the peers itself; only flag and wait."""
+        from ._lib import check, load_library
+        sh = self.shard
+        check("hq_gather_publish", load_library().hq_gather_publish(
+            self.peer_data.data_ptr(), self._slice_offset(i), 0 if stored else self.slice_elems,
+            self.peer_flags.data_ptr(), self.sync.data_ptr(), sh.world, sh.rank,
             self.max_polls, self.status.data_ptr(), torch.cuda.current_stream().cuda_stream))
 
     def wait_all(self) -> None:

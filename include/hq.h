@@ -166,9 +166,12 @@ int hq_ll_unpack(const hq_ll_packet* ll, long long n, void* out_half, const unsi
  * the family: an ordinary launch writes its slice into this GPU's own gathered
  * vector (elements offset .. offset + n_slice of peer_out_half[rank]);
  * hq_gather_publish then copies the slice to every peer with 16-byte stores
- * over NVLink, makes it visible system-wide, raises this rank's flag word on
- * every GPU (peer_flags[r], `world` words each, zero before the first call)
+ * over NVLink (the copy is spread over as many CTAs as the slice has 16 KB
+ * pieces per peer), makes it visible system-wide, raises this rank's flag word
+ * on every GPU (peer_flags[r], `world` words each, zero before the first call)
  * and waits until all ranks' slices of the same round have landed here.
+ * n_slice = 0: the producing kernel stored the slice to the peers itself
+ * (hq_qgemm_*_peers); only the flags and the wait remain.
  * sync_words as above ([1] counts rounds).  hq_gather_wait is that wait alone.
  * As with packets, a chain of rounds must alternate between at least two
  * gathered vectors: a rank that has seen round L complete may start storing
@@ -356,6 +359,25 @@ int hq_qgemm_q3_f16(const void* X_half, const int32_t* mat, const void* scales_h
 int hq_qgemm_nf4_f16(const void* X_half, const uint8_t* B, const float* absmax, const float* lut16,
                      void* Y_half, int Mb, int N, int K, int blocksize, int flags, void* workspace,
                      size_t workspace_bytes, int* status_word, hq_stream_t stream);
+
+/* Sharded layers: the same two products with the gather fused into the
+ * epilogue.  Every finished 128-feature tile is stored straight into the output
+ * slice of EVERY GPU of the node: element (t, n) goes to peer_Y_half[r][y_offset
+ * + t * N + n] for r = 0 .. world - 1 (peer-mapped buffers, this GPU's own
+ * among them; peer_Y_half is a device-resident pointer table as for
+ * hq_gather_publish), so the transfer over NVLink runs tile by tile beside the
+ * remaining tiles' math and no copy kernel follows.  The stores are complete
+ * when the launch is; hq_gather_publish with n_slice = 0 on the same stream
+ * then raises the flags and waits for the other ranks. */
+int hq_qgemm_q3_f16_peers(const void* X_half, const int32_t* mat, const void* scales_half,
+                          const void* zeros_half, void* const* peer_Y_half, long long y_offset,
+                          int world, int Mb, int N, int K, int group_size, void* workspace,
+                          size_t workspace_bytes, int* status_word, hq_stream_t stream);
+int hq_qgemm_nf4_f16_peers(const void* X_half, const uint8_t* B, const float* absmax,
+                           const float* lut16, void* const* peer_Y_half, long long y_offset,
+                           int world, int Mb, int N, int K, int blocksize, int flags,
+                           void* workspace, size_t workspace_bytes, int* status_word,
+                           hq_stream_t stream);
 
 #ifdef __cplusplus
 }

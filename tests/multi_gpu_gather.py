@@ -136,6 +136,39 @@ def main():
     torch.cuda.synchronize()
     report["qgemm nf4 publish"] = O.rel_err(
         f64(pq.slot(0).permute(1, 0, 2).reshape(Mb, Ng)), ref_nf4)
+
+    # fused form: the product's epilogue stores every tile into all GPUs' buffers and
+    # publish only signals; the buffers are cleared first so that nothing stale passes
+    def clear_slots():
+        torch.cuda.synchronize(); dist.barrier()
+        for i in range(2):
+            pq.slot(i).zero_()
+        torch.cuda.synchronize(); dist.barrier()
+    clear_slots()
+    for it in range(4):
+        i = it % 2
+        hq.qgemm_q3(*args_q3, status=stq, peers=pq.peers(i))
+        pq.publish(i, stored=True)
+    torch.cuda.synchronize()
+    report["qgemm q3 fused"] = max(
+        O.rel_err(f64(pq.slot(i).permute(1, 0, 2).reshape(Mb, Ng)), ref_q3) for i in range(2))
+    clear_slots()
+    hq.qgemm_nf4(*args_nf4, status=stq, peers=pq.peers(1))
+    pq.publish(1, stored=True)
+    torch.cuda.synchronize()
+    report["qgemm nf4 fused"] = O.rel_err(
+        f64(pq.slot(1).permute(1, 0, 2).reshape(Mb, Ng)), ref_nf4)
+    # fused with the K split (narrow shard, workspace in use) and a ragged batch
+    clear_slots()
+    Xr = dX[:37].contiguous()
+    hq.qgemm_q3(Xr, *args_q3[1:], status=stq, peers=pq.peers(0))
+    pq.publish(0, stored=True)
+    torch.cuda.synchronize()
+    got = pq.slot(0)[:, :37, :]  # rows 37 .. 63 of every slice stay zero
+    report["qgemm q3 fused ragged"] = O.rel_err(
+        f64(got.permute(1, 0, 2).reshape(37, Ng)), ref_q3[:37])
+    if float(pq.slot(0)[:, 37:, :].abs().max()) != 0.0:
+        status |= 2
     status |= int(pq.status.item()) | int(stq.item())
 
     ok = status == 0 and all(v < 1e-2 for v in report.values())

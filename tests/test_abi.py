@@ -71,7 +71,17 @@ def test_gather_and_noalloc_argument_errors_need_no_gpu(hq):
     assert lib.hq_nf4_gemv_f16_ll(p, 0, 1, p, p, p, p, 32, 64, 64, 0, 0, 0, p, 2, 2, 0, 0,
                                   None) == -1
     assert lib.hq_gather_wait(p, p, 0, 0, 0, None) == -1
-    assert lib.hq_gather_publish(p, 0, 0, p, p, 1, 0, 0, 0, None) == -1
+    assert lib.hq_gather_publish(p, 0, -1, p, p, 1, 0, 0, 0, None) == -1
+    assert lib.hq_gather_publish(p, 0, 64, p, p, 2, 2, 0, 0, None) == -1
+    # batched product with the gather in its epilogue: pointer table, 1 <= world <= 32
+    assert lib.hq_qgemm_q3_f16_peers(p, p, p, p, 0, 0, 2, 64, 128, 128, 128, None, 0, None,
+                                     None) == -2
+    assert lib.hq_qgemm_q3_f16_peers(p, p, p, p, p, 0, 0, 64, 128, 128, 128, None, 0, None,
+                                     None) == -1
+    assert lib.hq_qgemm_nf4_f16_peers(p, p, p, p, p, -8, 2, 64, 128, 128, 64, 0, None, 0, None,
+                                      None) == -1
+    assert lib.hq_qgemm_nf4_f16_peers(p, p, p, p, 0, 0, 2, 64, 128, 128, 64, 0, None, 0, None,
+                                      None) == -2
     assert lib.hq_ll_unpack(p, 0, p, 0, 0, 0, None) == -1
     # allocation-free LUT-GEMM: every argument rule is checked before the shared
     # scratch array is looked up or touched (so no CUDA call is made here)

@@ -167,3 +167,73 @@ def test_gather_publish_single_rank(hq, dev):
         assert sync.cpu().tolist() == [0, rnd + 1]
         assert int(flags[0].item()) == rnd + 1
     assert torch.equal(data, want)
+
+
+@pytest.mark.parametrize("n,offset", [(100_000, 8), (24_000, 0), (1001, 3), (0, 0)])
+def test_gather_publish_spreads_the_copy_over_ctas(hq, dev, n, offset):
+    """world = 3, rank 1, with the two "peers" as further buffers of this GPU and
+    their flags raised by the host beforehand, so the launch waits for no other
+    kernel: the slice (several 16 KB pieces per peer, i.e. several CTAs; an
+    unaligned one; an empty one = signal only) must arrive in both peer buffers,
+    nothing outside it may change, and the flags and the round counter advance."""
+    import torch
+    lib = hq.load_library()
+    total = offset + n + 64
+    bufs = [torch.full((total,), float(r + 1), dtype=torch.float16, device=dev) for r in range(3)]
+    bufs[1][offset:offset + n] = torch.arange(n, device=dev).remainder(2039).to(torch.float16)
+    want = bufs[1][offset:offset + n].clone()
+    flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(3)]
+    flags[1][0] = 1  # ranks 0 and 2 have "already published" round 1 here
+    flags[1][2] = 1
+    peer_out = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+    peer_flags = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
+    sync = torch.zeros(2, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    assert lib.hq_gather_publish(peer_out.data_ptr(), offset, n, peer_flags.data_ptr(),
+                                 sync.data_ptr(), 3, 1, 0, status.data_ptr(), _stream()) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert sync.cpu().tolist() == [0, 1]
+    for r in (0, 2):
+        assert int(flags[r][1].item()) == 1            # this rank's flag on GPU r
+        if n:
+            assert torch.equal(bufs[r][offset:offset + n], want)
+        assert bool((bufs[r][:offset] == r + 1).all()) and bool((bufs[r][offset + n:] == r + 1).all())
+    assert int(flags[1][1].item()) == 1
+
+
+@pytest.mark.parametrize("fmt", ["q3", "nf4"])
+@pytest.mark.parametrize("Mb,N,K", [(64, 512, 1024), (37, 256, 4096)])
+def test_qgemm_peer_epilogue_equals_plain(hq, dev, fmt, Mb, N, K):
+    """The sharded form of the batched product (tiles stored to every GPU's slice by
+    the epilogue) with two local buffers standing in for two GPUs: both must hold
+    the plain product, at the given offset, and nothing around it changes; the
+    narrow shape runs with the K split."""
+    import torch
+    offset = 128
+    if fmt == "q3":
+        X, codes, scales, zeros = synth.qgemm_q3_case(Mb, K, N, 128, seed=N + K)
+        args = (to_dev(X, dev), to_dev(synth.q3_pack(codes), dev), to_dev(scales, dev),
+                to_dev(zeros, dev), N, K, 128)
+        fn = hq.qgemm_q3
+    else:
+        X, B, absmax, lut = synth.qgemm_nf4_case(Mb, K, N, 64, seed=N + K)
+        args = (to_dev(X, dev), to_dev(B, dev), to_dev(absmax, dev), to_dev(lut, dev), N, K, 64, 0)
+        fn = hq.qgemm_nf4
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    plain = fn(*args, status=status)
+    bufs = [torch.full((offset + Mb * N + 64,), 3.0, dtype=torch.float16, device=dev) for _ in range(2)]
+    table = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+    assert fn(*args, status=status, peers=(table.data_ptr(), offset, 2)) is None
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    got = [b[offset:offset + Mb * N].view(Mb, N) for b in bufs]
+    assert torch.equal(got[0], got[1])
+    if N >= 512:
+        assert torch.equal(got[0], plain)
+    else:
+        # K split: the partial sums meet in fp32 atomics, whose order differs from
+        # launch to launch, so two launches agree only to fp32 rounding
+        assert torch.allclose(got[0].float(), plain.float(), rtol=2e-3, atol=2e-3)
+    for b in bufs:
+        assert bool((b[:offset] == 3).all()) and bool((b[offset + Mb * N:] == 3).all())
