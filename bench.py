@@ -819,6 +819,14 @@ def main():
         gather_check = check_gather(torch, dist, wl, packets, peer, gathered, rank, world, stride,
                                     strong, shard)
 
+    # ---- N > 1: this rank's kernel alone (no gather), max over ranks -----------------
+    kernel_only_us = None
+    if world > 1 and hasattr(wl, "out"):
+        k_us = time_replicas(torch, stream, lambda i: wl.launch(i), R, 20)
+        tk = torch.tensor([k_us], device=dev)
+        dist.all_reduce(tk, op=dist.ReduceOp.MAX)
+        kernel_only_us = float(tk.item())
+
     # ---- N = 1 extras: isolated launches, pure-read ceiling -----------------------
     read_us = no_pdl_us = None
     if name == "nf4_gemv" and world == 1:
@@ -988,6 +996,8 @@ def main():
             line["roofline"]["frac_no_pdl"] = line["value_no_pdl"] / roof["peak"]
         if gather_check is not None:
             line["gather_check"] = gather_check
+        if kernel_only_us is not None:
+            line["kernel_only_us_per_layer"] = kernel_only_us
         if world == 1 and name == "nf4_gemv" and not args.no_workloads:
             del wl
             torch.cuda.empty_cache()

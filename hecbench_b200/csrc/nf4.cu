@@ -828,6 +828,55 @@ gather_publish_kernel(__half* const* peer_out, long long offset, int n_slice,
   }
 }
 
+// Small slices (a mat-vec's output): one CTA per rank r of the node copies the
+// whole slice to GPU r, makes it visible, raises this rank's flag there and
+// waits for rank r's flag here - no counter between the copy and the flag, which
+// is what the latency of a 20 KB gather is made of.  The last CTA to finish
+// advances the launch count.
+__global__ void __launch_bounds__(kPublishThreads, 1)
+gather_publish_small_kernel(__half* const* peer_out, long long offset, int n_slice,
+                            uint32_t* const* peer_flags, unsigned* sync_words, int world,
+                            int rank, unsigned max_polls, int* status) {
+  const int tid = threadIdx.x;
+  const int r = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned epoch = *reinterpret_cast<volatile unsigned*>(sync_words + 1) + 1u;
+  if (r != rank) {
+    const __half* mine = peer_out[rank] + offset;
+    __half* dst = peer_out[r] + offset;
+    const bool vec_ok = ((offset | (long long)n_slice) & 7) == 0;
+    if (vec_ok) {
+      for (int i = tid; i < n_slice / 8; i += kPublishThreads)
+        reinterpret_cast<uint4*>(dst)[i] = __ldcg(reinterpret_cast<const uint4*>(mine) + i);
+    } else {
+      for (int i = tid; i < n_slice; i += kPublishThreads)
+        reinterpret_cast<unsigned short*>(dst)[i] =
+            __ldcg(reinterpret_cast<const unsigned short*>(mine) + i);
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    *reinterpret_cast<volatile uint32_t*>(peer_flags[r] + rank) = epoch;
+    const volatile uint32_t* f = peer_flags[rank] + r;
+    bool landed = false;
+    for (unsigned spin = 0; spin < max_polls; spin++) {
+      if ((int)(*f - epoch) >= 0) { landed = true; break; }
+      __nanosleep(32);
+    }
+    if (landed) __threadfence_system();
+    else if (status != nullptr) atomicExch(status, 1);
+    // every CTA has read the old launch count before it gets here
+    __threadfence();
+    const unsigned prev = atomicAdd(sync_words, 1u);
+    if (prev == (unsigned)world - 1u) {
+      sync_words[1] = epoch;
+      sync_words[0] = 0u;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace hq
 
@@ -983,9 +1032,16 @@ int hq_gather_publish(void* const* peer_out_half, long long offset, int n_slice,
   using namespace hq;
   if (!peer_out_half || !peer_flags || !sync_words) return HQ_ERR_NULL_POINTER;
   if (world < 1 || world > 32 || rank < 0 || rank >= world || n_slice < 0) return HQ_ERR_BAD_SHAPE;
-  // one CTA per (peer, 16 KB piece) up to the number of SMs; n_slice == 0: the
-  // producing kernel has stored the slice to the peers itself, only signal and wait
+  // n_slice == 0: the producing kernel has stored the slice to the peers itself,
+  // only signal and wait.  Larger slices: one CTA per (peer, 16 KB piece) up to the
+  // number of SMs.
   const long long pieces = ((long long)n_slice * 2 + kPublishPiece - 1) / kPublishPiece;
+  if (pieces <= 4)  // up to 64 KB per peer: one CTA per peer, flag straight after the copy
+    return cuda_status(launch_pdl(gather_publish_small_kernel, dim3(world), dim3(kPublishThreads),
+                                  0, (cudaStream_t)stream,
+                                  reinterpret_cast<__half* const*>(peer_out_half), offset, n_slice,
+                                  peer_flags, sync_words, world, rank,
+                                  max_polls ? max_polls : kDefaultPolls, status));
   const int grid = (int)std::max<long long>(1, std::min<long long>(pieces * (world - 1), sm_count()));
   return cuda_status(launch_pdl(gather_publish_kernel, dim3(grid), dim3(kPublishThreads), 0,
                                 (cudaStream_t)stream,

@@ -621,17 +621,41 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
     __syncthreads();
     if (s_last) {
       __threadfence();
-      for (int idx = tid; idx < p.Mb * kTileN; idx += kThreads) {
-        const int j = idx / kTileN, c = idx - j * kTileN;
-        float* w = p.ws + (size_t)j * p.N + n0 + c;
-        const __half h = __float2half_rn(__ldcg(w));
-        if (p.peer_Y == nullptr) {
-          p.Y[(size_t)j * p.N + n0 + c] = h;
-        } else {
-          for (int g = 0; g < p.world; g++)
-            peer_slice(p, g)[(size_t)j * p.N + n0 + c] = h;
+      // Mb x 32 groups of four features; five groups per thread and turn, all loads
+      // of a turn issued before the first is used (one L2 round trip per turn
+      // instead of one per element)
+      constexpr int kTurn = 5;
+      const int groups = p.Mb * (kTileN / 4);
+      for (int g0 = tid; g0 < groups; g0 += kThreads * kTurn) {
+        float4 v[kTurn];
+#pragma unroll
+        for (int u = 0; u < kTurn; u++) {
+          const int gi = g0 + u * kThreads;
+          if (gi < groups) {
+            const int j = gi / (kTileN / 4), c = (gi - j * (kTileN / 4)) * 4;
+            v[u] = __ldcg(reinterpret_cast<const float4*>(p.ws + (size_t)j * p.N + n0 + c));
+          }
         }
-        *w = 0.f;
+#pragma unroll
+        for (int u = 0; u < kTurn; u++) {
+          const int gi = g0 + u * kThreads;
+          if (gi < groups) {
+            const int j = gi / (kTileN / 4), c = (gi - j * (kTileN / 4)) * 4;
+            const size_t at = (size_t)j * p.N + n0 + c;
+            const __half2 lo = __floats2half2_rn(v[u].x, v[u].y), hi = __floats2half2_rn(v[u].z, v[u].w);
+            const uint2 packed = make_uint2(half2_as_u32(lo), half2_as_u32(hi));
+            for (int g = 0; g < (p.peer_Y == nullptr ? 1 : p.world); g++) {
+              __half* Yg = p.peer_Y == nullptr ? p.Y : peer_slice(p, g);
+              if ((reinterpret_cast<uintptr_t>(Yg + at) & 7u) == 0) {
+                *reinterpret_cast<uint2*>(Yg + at) = packed;
+              } else {
+                Yg[at] = __low2half(lo); Yg[at + 1] = __high2half(lo);
+                Yg[at + 2] = __low2half(hi); Yg[at + 3] = __high2half(hi);
+              }
+            }
+            *reinterpret_cast<float4*>(p.ws + at) = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
       }
       if (tid == 0) p.counters[blockIdx.x] = 0u;
     }
