@@ -71,13 +71,17 @@ __device__ __forceinline__ uint32_t quantize_one(uint32_t lane_addr, float x, fl
   search_level<4>(acc, val, x);
   search_level<2>(acc, val, x);
   search_level<1>(acc, val, x);
-  // (acc - lane_addr) / 128 is the final pivot P, val = code[P]
+  // (acc - lane_addr) / 128 is the final pivot P, val = code[P].  The neighbour is
+  // one row up or down: ONE load from a selected address (two loads under a
+  // condition compile to a branch), and the answer is the row of the pivot or of
+  // the neighbour - the guard row in front of entry 0 stands for "stay at 0".
   const bool gt = x > val;
-  const float nb = gt ? lds_f32_imm<128>(acc) : lds_f32_imm<-128>(acc);
+  const uint32_t nb_addr = gt ? acc + 128u : acc - 128u;
+  const float nb = lds_f32_imm<0>(nb_addr);
   const float midpoint = (nb + val) * 0.5f;
   const bool step = gt ? (x > midpoint) : (x < midpoint);
-  const int P = (int)((acc - lane_addr) >> 7);
-  return (uint32_t)(step ? (gt ? P + 1 : max(P - 1, 0)) : P);
+  const int row = (int)((step ? nb_addr : acc) - lane_addr) >> 7;  // -1 for the guard row
+  return (uint32_t)max(row, 0);
 }
 
 __global__ void __launch_bounds__(kThreads)
