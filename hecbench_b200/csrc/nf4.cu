@@ -65,6 +65,22 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// Loads that keep their place in the program order among the other ordered
+// loads (asm volatile): the prologue depends on WHICH request reaches the memory
+// system first.
+__device__ __forceinline__ float ldg_ordered_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ldg_ordered_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
 // sum of the 32 products of one 16-byte chunk against 16 half2 inputs
 __device__ __forceinline__ float chunk_dot(const uint4& codes, const uint4 (&xp)[4],
                                            uint32_t lane4) {
@@ -228,21 +244,16 @@ nf4_gemv_kernel(const GemvParams p) {
 
   // The 16 levels first: the table build must not queue behind the weight loads
   // below.  (The levels count as weights: read before the wait with early_fetch.)
+  // (ordered loads: the compiler must not sink them below the weight loads)
   constexpr int kTabTurns = (256 * 4 + THREADS - 1) / THREADS;
   float lv_first[kTabTurns], lv_second[kTabTurns];
 #pragma unroll
   for (int t = 0; t < kTabTurns; t++) {
     const int entry = ((tid + t * THREADS) >> 2) & 255;
     const int hi = entry >> 4, lo = entry & 15;
-    lv_first[t] = p.lut16[p.low_first ? lo : hi];
-    lv_second[t] = p.lut16[p.low_first ? hi : lo];
+    lv_first[t] = ldg_ordered_f32(p.lut16 + (p.low_first ? lo : hi));
+    lv_second[t] = ldg_ordered_f32(p.lut16 + (p.low_first ? hi : lo));
   }
-  // ... and a hint to the L2 for the lines of the input vector, which may only be
-  // READ after the wait (a prefetch moves no data to the SM)
-  if (p.early_fetch && p.A != nullptr)
-    for (int line = tid; line * 128 < p.nchunks * 64; line += THREADS)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.A) + line * 128));
-
   // this lane's chunk columns; a lane beyond the row end loads nothing and
   // keeps zero codes, scales and inputs
   const unsigned char* wp[C];
@@ -278,6 +289,12 @@ nf4_gemv_kernel(const GemvParams p) {
       else ci[i] += (uint32_t)row_stride * (uint32_t)p.nchunks;                                 \
     }                                                                                           \
   }
+  // Order of the prologue.  With early_fetch: the first kEarly rows of weights,
+  // then the wait for the preceding kernel, then the INPUT VECTOR, then the other
+  // rows, then the table.  The vector is requested before the bulk of the weights
+  // on purpose: behind D rows per lane (9.5 MB over the whole GPU) its 8 KB took
+  // 1.5 us to come back, and nothing can be computed without it.
+  constexpr int kEarly = D / 2;
 #pragma unroll
   for (int d = 0; d < D; d++) {
 #pragma unroll
@@ -285,10 +302,36 @@ nf4_gemv_kernel(const GemvParams p) {
       cw[d][i] = make_uint4(0, 0, 0, 0);
       cs[d][i] = 0.f;
     }
-    if (d < my_rows) HQ_NF4_LOAD(d)
+    if (p.early_fetch && d < kEarly && d < my_rows) HQ_NF4_LOAD(d)
   }
   HQ_STAMP(1)
-  // ---- prologue (overlaps the loads above): byte table, input slice ----
+  // the input vector (and, without early_fetch, everything) is read only after
+  // the preceding kernel has completed
+  if (p.early_fetch) pdl_wait();
+  HQ_STAMP(2)
+  // epoch of the latest completed gather: the input packets carry it, the
+  // output packets of this launch carry the next one
+  const uint32_t epoch_in =
+      p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
+  uint2* my_peer = nullptr;  // lane r stores the packets that go to rank r
+  if (p.peer_ll != nullptr && lane < p.world) my_peer = p.peer_ll[lane] + p.gather_offset;
+  uint4 xr[C][4];
+  if (p.A_ll == nullptr) {
+#pragma unroll
+    for (int i = 0; i < C; i++) {
+      const int c = (q * C + i) * 32 + lane;
+      const uint4* xp = reinterpret_cast<const uint4*>(p.A) + 4 * (live[i] ? c : 0);
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        if (live[i] && HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 103)) xr[i][t] = ldg_ordered_u4(xp + t);
+        else xr[i][t] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+#pragma unroll
+  for (int d = 0; d < D; d++)
+    if (!(p.early_fetch && d < kEarly) && d < my_rows) HQ_NF4_LOAD(d)
+  // ---- byte table ----
 #pragma unroll
   for (int t = 0; t < kTabTurns; t++) {
     const int e4 = tid + t * THREADS;
@@ -301,18 +344,7 @@ nf4_gemv_kernel(const GemvParams p) {
       row[(entry & 1) ^ 1] = u4;
     }
   }
-  // the input vector (and, without early_fetch, everything) is read only after
-  // the preceding kernel has completed
-  HQ_STAMP(2)
-  if (p.early_fetch) pdl_wait();
   HQ_STAMP(3)
-  // epoch of the latest completed gather: the input packets carry it, the
-  // output packets of this launch carry the next one
-  const uint32_t epoch_in =
-      p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
-  uint2* my_peer = nullptr;  // lane r stores the packets that go to rank r
-  if (p.peer_ll != nullptr && lane < p.world) my_peer = p.peer_ll[lane] + p.gather_offset;
-  const uint4* xsrc = reinterpret_cast<const uint4*>(p.A);
   if (p.A_ll != nullptr) {
     // the whole input arrives as packets: every thread waits for its share and
     // leaves plain fp16 in shared memory
@@ -320,19 +352,12 @@ nf4_gemv_kernel(const GemvParams p) {
     stage_packets<THREADS>(xs, p.A_ll, p.a_stride, p.nchunks * 32, epoch_in, p.max_polls, p.status,
                            tid);
     __syncthreads();
-    xsrc = reinterpret_cast<const uint4*>(xs);
-  }
-  uint4 xr[C][4];
 #pragma unroll
-  for (int i = 0; i < C; i++) {
-    const int c = (q * C + i) * 32 + lane;
-    const uint4* xp = xsrc + 4 * (live[i] ? c : 0);
+    for (int i = 0; i < C; i++) {
+      const int c = (q * C + i) * 32 + lane;
+      const uint4* xp = reinterpret_cast<const uint4*>(xs) + 4 * (live[i] ? c : 0);
 #pragma unroll
-    for (int t = 0; t < 4; t++) {
-      if (p.A_ll != nullptr) xr[i][t] = xp[t];
-      else if (HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 103)) xr[i][t] = __ldg(xp + t);
-      else xr[i][t] = make_uint4(0, 0, 0, 0);
-      if (!live[i]) xr[i][t] = make_uint4(0, 0, 0, 0);
+      for (int t = 0; t < 4; t++) xr[i][t] = live[i] ? xp[t] : make_uint4(0, 0, 0, 0);
     }
   }
   __syncthreads();
