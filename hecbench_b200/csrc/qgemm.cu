@@ -585,14 +585,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
           if (j0 + j < p.Mb)
             p.Y[(size_t)(j0 + j) * p.N + n] = __float2half_rn(__uint_as_float(r[j]));
       } else if (p.ksplit == 1) {
-        // 32 lanes = 32 consecutive features: 64 contiguous bytes per store and GPU
-        for (int g = 0; g < p.world; g++) {
-          __half* Yg = peer_slice(p, g);
+        // sharded form: the tile is collected in shared memory as fp16 [token][128
+        // features] (the X stages are free: every MMA has completed) and leaves in
+        // whole 256-byte rows below
+        __half* tile = reinterpret_cast<__half*>(sm);
 #pragma unroll
-          for (int j = 0; j < 16; j++)
-            if (j0 + j < p.Mb)
-              Yg[(size_t)(j0 + j) * p.N + n] = __float2half_rn(__uint_as_float(r[j]));
-        }
+        for (int j = 0; j < 16; j++)
+          tile[(j0 + j) * kTileN + (warp & 3) * 32 + lane] = __float2half_rn(__uint_as_float(r[j]));
       } else {
 #pragma unroll
         for (int j = 0; j < 16; j++)
@@ -600,6 +599,29 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
             asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p.ws + (size_t)(j0 + j) * p.N + n),
                          "f"(__uint_as_float(r[j]))
                          : "memory");
+      }
+    }
+  }
+  if (warp < 8 && p.ksplit == 1 && p.peer_Y != nullptr) {
+    // 16 threads x 16 bytes = one token row of the tile; every row goes to the
+    // output slice of every GPU of the node as one 256-byte run (over NVLink for
+    // the peers)
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const __half* tile = reinterpret_cast<const __half*>(sm);
+    const int e = tid, c8 = (e & 15) * 8;
+    for (int g = 0; g < p.world; g++) {
+      __half* Yg = peer_slice(p, g);
+      const bool vec = (reinterpret_cast<uintptr_t>(Yg) & 15u) == 0;
+      for (int t = e >> 4; t < p.Mb; t += 16) {
+        const uint4 v = *reinterpret_cast<const uint4*>(tile + t * kTileN + c8);
+        __half* dst = Yg + (size_t)t * p.N + n0 + c8;
+        if (vec) {
+          *reinterpret_cast<uint4*>(dst) = v;
+        } else {
+          const __half* h = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+          for (int k = 0; k < 8; k++) dst[k] = h[k];
+        }
       }
     }
   }
