@@ -217,7 +217,9 @@ __device__ __forceinline__ __half* peer_slice(const QgemmParams& p, int g) {
          p.y_offset;
 }
 
-template <int FMT>
+// PEERS: the sharded form (tiles stored to every GPU's slice); a separate
+// instantiation so that the plain form carries none of it.
+template <int FMT, bool PEERS>
 __global__ void __launch_bounds__(kThreads, 2)
 qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                 const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_z,
@@ -579,7 +581,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
       } else {
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
-      if (p.ksplit == 1 && p.peer_Y == nullptr) {
+      if (p.ksplit == 1 && !PEERS) {
 #pragma unroll
         for (int j = 0; j < 16; j++)
           if (j0 + j < p.Mb)
@@ -602,7 +604,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
       }
     }
   }
-  if (warp < 8 && p.ksplit == 1 && p.peer_Y != nullptr) {
+  if (PEERS && warp < 8 && p.ksplit == 1) {
     // 16 threads x 16 bytes = one token row of the tile; every row goes to the
     // output slice of every GPU of the node as one 256-byte run (over NVLink for
     // the peers)
@@ -666,8 +668,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ 
             const size_t at = (size_t)j * p.N + n0 + c;
             const __half2 lo = __floats2half2_rn(v[u].x, v[u].y), hi = __floats2half2_rn(v[u].z, v[u].w);
             const uint2 packed = make_uint2(half2_as_u32(lo), half2_as_u32(hi));
-            for (int g = 0; g < (p.peer_Y == nullptr ? 1 : p.world); g++) {
-              __half* Yg = p.peer_Y == nullptr ? p.Y : peer_slice(p, g);
+            for (int g = 0; g < (PEERS ? p.world : 1); g++) {
+              __half* Yg = PEERS ? peer_slice(p, g) : p.Y;
               if ((reinterpret_cast<uintptr_t>(Yg + at) & 7u) == 0) {
                 *reinterpret_cast<uint2*>(Yg + at) = packed;
               } else {
@@ -767,11 +769,18 @@ template <int FMT>
 int launch_qgemm(const CUtensorMap& map_x, const CUtensorMap& map_w, const CUtensorMap& map_s,
                  const CUtensorMap& map_z, const QgemmParams& prm, hq_stream_t stream) {
   const size_t smem = qgemm_smem_bytes<FMT>(prm.tokens_padded);
-  constexpr auto kern = qgemm_kernel<FMT>;
-  cudaError_t e = ensure_dynamic_smem<kern>(smem);
-  if (e != cudaSuccess) return cuda_status(e);
-  qgemm_kernel<FMT><<<dim3(prm.N / kTileN, prm.ksplit), kThreads, smem, (cudaStream_t)stream>>>(
-      map_x, map_w, map_s, map_z, prm);
+  const dim3 grid(prm.N / kTileN, prm.ksplit);
+  if (prm.peer_Y != nullptr) {
+    constexpr auto kern = qgemm_kernel<FMT, true>;
+    cudaError_t e = ensure_dynamic_smem<kern>(smem);
+    if (e != cudaSuccess) return cuda_status(e);
+    kern<<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_x, map_w, map_s, map_z, prm);
+  } else {
+    constexpr auto kern = qgemm_kernel<FMT, false>;
+    cudaError_t e = ensure_dynamic_smem<kern>(smem);
+    if (e != cudaSuccess) return cuda_status(e);
+    kern<<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_x, map_w, map_s, map_z, prm);
+  }
   return launch_status();
 }
 }  // namespace
