@@ -80,8 +80,14 @@ enum { kFmtQ3 = 0, kFmtNf4 = 1 };
 // shallower rings pay for it inside the same two-CTAs-per-SM budget.
 template <int FMT>
 struct Rings {
-  static constexpr int kXStages = FMT == 0 ? 8 : 6;
-  static constexpr int kWordAhead = FMT == 0 ? 8 : 6;
+#ifndef HQ_RING_X_Q3  // ring depths (even: half per pipeline); overridable for sweeps
+#define HQ_RING_X_Q3 8
+#define HQ_RING_W_Q3 8
+#define HQ_RING_X_NF4 6
+#define HQ_RING_W_NF4 6
+#endif
+  static constexpr int kXStages = FMT == 0 ? HQ_RING_X_Q3 : HQ_RING_X_NF4;
+  static constexpr int kWordAhead = FMT == 0 ? HQ_RING_W_Q3 : HQ_RING_W_NF4;
   static constexpr int kLutWords = FMT == 0 ? 64 * 32 : 256 * 16 * 2;
 };
 template <int FMT>
