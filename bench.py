@@ -143,6 +143,13 @@ def _host_case(name: str, seed: int, Mb: int = 64):
         return dict(tokens=tokens, hidden=hidden, x=x, bytes=tokens * hidden * 3 + tokens * 8,
                     desc=f"per-token int8 activation quantization {tokens}x{hidden} fp16 "
                          f"({name[5:-4].replace('_', ' ')})")
+    if name in ("gemv_int8", "gemv_int4"):
+        size = 8192  # square, as in the reference driver (its default 512 is 256 KB: all launch)
+        bits = 8 if name == "gemv_int8" else 4
+        mat, vec = synth.gemv_uniform_case(size, size, bits, seed)
+        return dict(size=size, bits=bits, mat=mat, vec=vec, scale=0.0625, zp=0.01,
+                    bytes=mat.nbytes + 4 * size,
+                    desc=f"uniform int{bits} weight-only GEMV {size}x{size} (gemv-cuda), fp16 in/out")
     if name in ("qgemm_q3", "qgemm_q3_down"):
         K, N = (28672, 8192) if name.endswith("down") else (8192, 28672)
         G = K // 128
@@ -174,7 +181,8 @@ PDL = os.environ.get("HQ_BENCH_NO_PDL") != "1"
 WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "q3_gemv_f32_opt175b",
              "q3_gemv_f16_opt175b", "bnb_quantize", "lutgemm", "aqlm_1x16", "aqlm_2x8",
              "qgemm_q3", "qgemm_nf4", "qgemm_q3_down", "qgemm_nf4_down",
-             "vllm_static_f16", "vllm_dynamic_f16", "vllm_dynamic_azp_f16"]
+             "vllm_static_f16", "vllm_dynamic_f16", "vllm_dynamic_azp_f16",
+             "gemv_int8", "gemv_int4"]
 
 
 def dtype_of(name: str) -> str:
@@ -251,6 +259,10 @@ class DeviceWorkload:
             self.x = [t(c["X"]) for _ in range(R)]
             self.out = [torch.empty((c["Mb"], self.n_local), dtype=torch.float16, device=dev)
                         for _ in range(R)]
+        elif name.startswith("gemv_int"):
+            self.mat = [t(rot(c["mat"], i)) for i in range(R)]
+            self.x = [t(c["vec"]) for _ in range(R)]
+            self.out = [torch.empty(c["size"], dtype=torch.float16, device=dev) for _ in range(R)]
         elif name.startswith("vllm"):
             self.xin = [t(rot(c["x"], i)) for i in range(R)]
             self.q = torch.empty((c["tokens"], c["hidden"]), dtype=torch.int8, device=dev)
@@ -286,6 +298,10 @@ class DeviceWorkload:
                                [m, m, m, 1 << 30], 65536)
         elif n == "aqlm_2x8":
             hq.code2x8_matvec(self.codes[i], self.x[i], self.out[i], self.cbs, c["m"], c["k"])
+        elif n == "gemv_int8":
+            hq.gemv_int8_quantized(self.mat[i], self.x[i], c["scale"], c["zp"], out=self.out[i])
+        elif n == "gemv_int4":
+            hq.gemv_int4_quantized(self.mat[i], self.x[i], c["scale"], c["zp"], out=self.out[i])
         elif n == "vllm_static_f16":
             hq.static_scaled_int8_quant(self.q, self.xin[i], c["hidden"], c["tokens"], 0.1, 0)
         elif n.startswith("vllm_dynamic"):
@@ -417,6 +433,9 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
     elif name == "aqlm_2x8":
         m = c["m"]
         fn = lambda: O.aqlm_2x8_f64(c["codes"], c["x"], c["cbs"], m, c["k"])
+        sample = "full mat-vec (fp64 oracle)"
+    elif name.startswith("gemv_int"):
+        fn = lambda: O.gemv_uniform_f64(c["mat"], c["vec"], c["bits"], c["scale"], c["zp"])
         sample = "full mat-vec (fp64 oracle)"
     elif name.startswith("vllm"):
         if name == "vllm_static_f16":

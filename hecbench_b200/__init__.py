@@ -5,7 +5,8 @@ The compute lives in libhq.so (hand-written CUDA, C ABI declared in
 include/hq.h).  This package is the thin Python host layer over it: it mirrors
 the reference launchers (`vecquant3matmul`, `vecquant3matmul_faster`,
 `kQuantize`, `matmul` + `nQWeight_fp16`, `code1x16_matvec`,
-`static_scaled_int8_quant`, `dynamic_scaled_int8_quant`) on torch CUDA
+`static_scaled_int8_quant`, `dynamic_scaled_int8_quant`, the `gemv` int8 / int4
+kernels) on torch CUDA
 tensors and adds the pieces the reference names but does not contain (NF4
 dequantize / GEMV, AQLM 2x8).  There is no CPU path: importing works without a
 GPU, but every compute call needs the built library and CUDA tensors.
@@ -19,6 +20,9 @@ from .api import (  # noqa: F401
     code2x8_matvec,
     dequantize_nf4,
     dynamic_scaled_int8_quant,
+    gemv_fp16,
+    gemv_int4_quantized,
+    gemv_int8_quantized,
     gemv_nf4,
     kQuantize,
     matmul,
@@ -38,5 +42,6 @@ __all__ = [
     "kQuantize", "dequantize_nf4", "gemv_nf4",
     "nQWeight_fp16", "matmul", "qgemm_q3", "qgemm_nf4", "qgemm_reset_workspaces", "code1x16_matvec", "code2x8_matvec",
     "static_scaled_int8_quant", "dynamic_scaled_int8_quant",
+    "gemv_fp16", "gemv_int8_quantized", "gemv_int4_quantized",
     "NF4_HIGH_NIBBLE_FIRST", "NF4_LOW_NIBBLE_FIRST", "NF4_WEIGHTS_RESIDENT",
 ]

@@ -66,6 +66,9 @@ SIGNATURES = {
                                                  C.c_int32, c_void_p]),
     "hq_vllm_dynamic_scaled_int8_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int,
                                                   c_void_p, c_void_p, c_void_p]),
+    "hq_gemv_f16": (c_int, [c_void_p] * 3 + [c_int, c_int, c_void_p]),
+    "hq_gemv_int8_f16": (c_int, [c_void_p] * 3 + [c_int, c_int, C.c_float, C.c_float, c_void_p]),
+    "hq_gemv_int4_f16": (c_int, [c_void_p] * 3 + [c_int, c_int, C.c_float, C.c_float, c_void_p]),
     "hq_aqlm_2x8_matvec": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p, c_void_p]),
 }
 

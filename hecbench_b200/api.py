@@ -188,6 +188,61 @@ def dynamic_scaled_int8_quant(output, input, hidden_size: int, num_tokens: int, 
 
 
 # --------------------------------------------------------------------------
+# gemv: uniform int8 / int4 weight-only mat-vec
+# --------------------------------------------------------------------------
+
+def _gemv_out(mat, vec, n: int, out):
+    rows = mat.shape[0]
+    if vec.numel() != n:
+        raise ValueError(f"vec has {vec.numel()} elements, a row of mat {n}")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.float16, device=mat.device)
+    elif out.numel() < rows:
+        raise ValueError("out is too small")
+    return rows, out
+
+
+def gemv_fp16(mat, vec, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """gemv_fp16 behind solve_gemv_with_params (gemv-cuda/kernels.h:64-123,
+    gemv.cu:61-81): mat fp16 [rows][n], vec fp16 [n] -> fp16 [rows]."""
+    n = mat.shape[1]
+    rows, out = _gemv_out(mat, vec, n, out)
+    with torch.cuda.device(mat.device):
+        check("hq_gemv_f16", load_library().hq_gemv_f16(
+            _dev(mat, torch.float16, "mat"), _dev(vec, torch.float16, "vec"),
+            _dev(out, torch.float16, "out"), rows, n, _stream()))
+    return out
+
+
+def gemv_int8_quantized(mat, vec, scale: float, zero_point: float,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """gemv_quantized_int8 behind solve_gemv_int8_quantized_with_params
+    (gemv-cuda/kernels.h:127-200, gemv.cu:38-59): mat int8 [rows][n]; scale and
+    zero_point are rounded to fp16 as the reference launcher does."""
+    n = mat.shape[1]
+    rows, out = _gemv_out(mat, vec, n, out)
+    with torch.cuda.device(mat.device):
+        check("hq_gemv_int8_f16", load_library().hq_gemv_int8_f16(
+            _dev(mat, torch.int8, "mat"), _dev(vec, torch.float16, "vec"),
+            _dev(out, torch.float16, "out"), rows, n, float(scale), float(zero_point), _stream()))
+    return out
+
+
+def gemv_int4_quantized(mat, vec, scale: float, zero_point: float,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """gemv_quantized_int4 behind solve_gemv_int4_quantized_with_params
+    (gemv-cuda/kernels.h:205-307, gemv.cu:15-36): mat uint8 [rows][n/2], element
+    2j in the low nibble of byte j (uint4_2, kernels.h:9-32)."""
+    n = 2 * mat.shape[1]
+    rows, out = _gemv_out(mat, vec, n, out)
+    with torch.cuda.device(mat.device):
+        check("hq_gemv_int4_f16", load_library().hq_gemv_int4_f16(
+            _dev(mat, torch.uint8, "mat"), _dev(vec, torch.float16, "vec"),
+            _dev(out, torch.float16, "out"), rows, n, float(scale), float(zero_point), _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------
 # lut-gemm
 # --------------------------------------------------------------------------
 

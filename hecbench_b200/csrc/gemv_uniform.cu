@@ -1,0 +1,243 @@
+// Uniformly quantized weight-only mat-vec (gemv-cuda) for sm_100a: fp16, int8
+// and packed int4 weights with ONE scale and zero point per tensor.
+//
+// Reference semantics (gemv-cuda/kernels.h:64-123 fp16, :127-200 int8, :205-307
+// int4; launchers gemv.cu:15-81): mat is row-major [rows][n] (int4: n/2 bytes
+// per row, element 2j in the LOW nibble of byte j, 2j+1 in the high nibble);
+// scale and zero point are rounded to fp16 by the launcher and used as fp32;
+//   res[row] = half( scale * sum_j float(vec[j]) * (float(w[row][j]) - zero_point) )
+// with fp32 accumulation.  Here the affine part is factored,
+//   scale * ( sum_j w*x  -  zero_point * sum_j x ),
+// the products are formed in fp16 pairs (an integer weight is exact in fp16)
+// and summed in fp32 every 32 (int8, fp16) or 64 (int4) weights per lane.
+//
+// Design.  HBM-bound (2, 1 or 0.5 bytes per weight).  Two 512-thread CTAs per
+// SM; the input vector is staged once per CTA in shared memory (fp16) and its
+// sum reduced there; a warp owns whole rows (row = warp, warp + #warps, ...)
+// and streams them with 128-bit loads that bypass L1, four loads (64 bytes per
+// lane) in flight.
+//  * int8 -> fp16: one XOR flips the sign bits of four bytes (b + 128), a byte
+//    permute places two of them under the exponent byte 0x64 (1024 + b + 128,
+//    exact), one half2 subtract of 1152 leaves the integers, one half2 fma
+//    multiplies with the inputs: 7 instructions per 4 weights.
+//  * int4: byte -> half2(low nibble, high nibble) through a 256-row table held
+//    once per bank (row stride 256 bytes at a fixed shared address, so the
+//    lookup address is one byte permute plus an immediate), one half2 fma per
+//    byte: 3 instructions per 2 weights.
+#include <algorithm>
+
+#include "hq_common.cuh"
+
+namespace hq {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+constexpr int kInFlight = 4;            // 16-byte loads per lane in flight
+constexpr int kLutImm = 2048;           // shared-window address of the int4 table
+constexpr int kLutBytes = 256 * 256;    // 256 rows of 256 bytes (first 128: one copy per bank)
+
+template <int IMM>
+__device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
+  uint32_t v;  // not volatile: the table is constant after the prologue barrier
+  asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+  return v;
+}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ float sum4(__half2 a0, __half2 a1, __half2 a2, __half2 a3) {
+  const float2 f = __half22float2(__hadd2(__hadd2(a0, a1), __hadd2(a2, a3)));
+  return f.x + f.y;
+}
+
+// 16 bytes of weights against the matching inputs -> fp32 partial sum.
+// BITS = 16: 8 halves x 8 inputs; 8: 16 int8 x 16 inputs; 4: 32 nibbles x 32 inputs.
+// xs points at the chunk's first 16-byte piece of inputs; its further pieces
+// follow at a distance of `pitch` pieces (the inputs are stored piece-major so
+// that the 32 lanes of a warp, which hold consecutive chunks, read consecutive
+// 16-byte words: chunk-major, a chunk's 32 or 64 bytes apart, they would meet in
+// the same banks two or four at a time).
+template <int BITS>
+__device__ __forceinline__ float chunk_dot(const uint4& w, const uint4* xs, int pitch,
+                                           uint32_t lane4) {
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+  __half2 a0 = __float2half2_rn(0.f), a1 = a0, a2 = a0, a3 = a0;
+  if (BITS == 16) {
+    const uint4 x = xs[0];
+    a0 = __hmul2(u32_as_half2(ww[0]), u32_as_half2(x.x));
+    a1 = __hmul2(u32_as_half2(ww[1]), u32_as_half2(x.y));
+    a2 = __hmul2(u32_as_half2(ww[2]), u32_as_half2(x.z));
+    a3 = __hmul2(u32_as_half2(ww[3]), u32_as_half2(x.w));
+    // one product per accumulator: summed in fp32 right away
+    const float2 f0 = __half22float2(a0), f1 = __half22float2(a1), f2 = __half22float2(a2),
+                 f3 = __half22float2(a3);
+    return ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+  } else if (BITS == 8) {
+    const uint4 xa = xs[0], xb = xs[pitch];
+    const uint32_t x2[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+    const __half2 off = __float2half2_rn(1152.f);  // 1024 (exponent byte) + 128 (sign flip)
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t t = ww[i] ^ 0x80808080u;
+      const __half2 lo = __hsub2(u32_as_half2(__byte_perm(t, 0x64646464u, 0x4140)), off);
+      const __half2 hi = __hsub2(u32_as_half2(__byte_perm(t, 0x64646464u, 0x4342)), off);
+      if (i & 1) {
+        a2 = __hfma2(lo, u32_as_half2(x2[2 * i]), a2);
+        a3 = __hfma2(hi, u32_as_half2(x2[2 * i + 1]), a3);
+      } else {
+        a0 = __hfma2(lo, u32_as_half2(x2[2 * i]), a0);
+        a1 = __hfma2(hi, u32_as_half2(x2[2 * i + 1]), a1);
+      }
+    }
+    return sum4(a0, a1, a2, a3);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint4 x = xs[i * pitch];
+      // byte k of the word -> (byte << 8) | lane*4: bytes {lane4.0, w.k, 0, 0}
+      const uint32_t l0 = lds_u32_imm<kLutImm>(__byte_perm(ww[i], lane4, 0x7604));
+      const uint32_t l1 = lds_u32_imm<kLutImm>(__byte_perm(ww[i], lane4, 0x7614));
+      const uint32_t l2 = lds_u32_imm<kLutImm>(__byte_perm(ww[i], lane4, 0x7624));
+      const uint32_t l3 = lds_u32_imm<kLutImm>(__byte_perm(ww[i], lane4, 0x7634));
+      a0 = __hfma2(u32_as_half2(l0), u32_as_half2(x.x), a0);
+      a1 = __hfma2(u32_as_half2(l1), u32_as_half2(x.y), a1);
+      a2 = __hfma2(u32_as_half2(l2), u32_as_half2(x.z), a2);
+      a3 = __hfma2(u32_as_half2(l3), u32_as_half2(x.w), a3);
+    }
+    return sum4(a0, a1, a2, a3);
+  }
+}
+
+// n: inputs per row; row_bytes = n * BITS / 8 (a multiple of 16).
+template <int BITS>
+__global__ void __launch_bounds__(kThreads, 2)
+gemv_uniform_kernel(const unsigned char* __restrict__ mat, const __half* __restrict__ vec,
+                    __half* __restrict__ res, int rows, int n, float scale, float zero_point) {
+  extern __shared__ __align__(16) unsigned char dsm_raw[];
+  // int4: [pad up to shared address kLutImm] table | inputs;  else: inputs
+  __shared__ float s_part[kWarps];
+  unsigned char* dsm = dsm_raw;
+  if (BITS == 4) dsm = dsm_raw + (kLutImm - smem_u32(dsm_raw)) + kLutBytes;
+  __half* xs = reinterpret_cast<__half*>(dsm);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kPieces = 16 / BITS == 0 ? 1 : 16 / BITS;  // 16-byte pieces of inputs per chunk
+  const size_t row_bytes = (size_t)n * BITS / 8;
+  const int chunks = (int)(row_bytes / 16);   // 16-byte chunks per row
+
+  // Programmatic dependent launch: the next kernel of the stream may become
+  // resident while this grid drains; the table (no global memory involved) is
+  // built before the wait, everything that earlier work may have produced - the
+  // input vector - is read after it, and nothing is written before it.
+  pdl_launch_dependents();
+  if (BITS == 4) {
+    // byte b -> half2(low nibble, high nibble): element 2j sits in the low nibble
+    unsigned char* lut = dsm - kLutBytes;
+    for (int e4 = tid; e4 < 256 * 4; e4 += kThreads) {
+      const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
+      const uint32_t u = half2_as_u32(
+          __halves2half2(__int2half_rn(entry & 15), __int2half_rn(entry >> 4)));
+      const uint4 u4 = make_uint4(u, u, u, u);
+      uint4* row = reinterpret_cast<uint4*>(lut + (size_t)entry * 256 + quarter * 32);
+      row[0] = u4;
+      row[1] = u4;
+    }
+  }
+  pdl_wait();
+  // ---- prologue: inputs to shared memory (piece-major) and their sum ----
+  float part = 0.f;
+  for (int i = tid; i < n / 8; i += kThreads) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (HQ_IN_BOUNDS(reinterpret_cast<const uint4*>(vec) + i, 16, vec, (size_t)n * 2, 401))
+      v = __ldg(reinterpret_cast<const uint4*>(vec) + i);
+    // 16-byte piece p of chunk c goes to [p][c]
+    reinterpret_cast<uint4*>(xs)[(i % kPieces) * chunks + i / kPieces] = v;
+    const float2 f0 = __half22float2(u32_as_half2(v.x)), f1 = __half22float2(u32_as_half2(v.y)),
+                 f2 = __half22float2(u32_as_half2(v.z)), f3 = __half22float2(u32_as_half2(v.w));
+    part += ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+  }
+  part = warp_sum(part);
+  if (lane == 0) s_part[warp] = part;
+  __syncthreads();
+  float sumx = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; w++) sumx += s_part[w];
+
+  // ---- rows of this warp ----
+  const uint32_t lane4 = (uint32_t)lane * 4u;
+  const int warps_total = gridDim.x * kWarps;
+  for (long long row = (long long)blockIdx.x * kWarps + warp; row < rows; row += warps_total) {
+    const unsigned char* src = mat + (size_t)row * row_bytes;
+    float acc = 0.f;
+    for (int c0 = lane; c0 < chunks; c0 += 32 * kInFlight) {
+      uint4 w[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; u++) {
+        const int c = c0 + 32 * u;
+        w[u] = make_uint4(0, 0, 0, 0);
+        if (c < chunks && HQ_IN_BOUNDS(src + (size_t)c * 16, 16, mat, (size_t)rows * row_bytes, 402))
+          w[u] = ldg_stream_u4(src + (size_t)c * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < kInFlight; u++) {
+        const int c = c0 + 32 * u;
+        if (c < chunks)
+          acc += chunk_dot<BITS>(w[u], reinterpret_cast<const uint4*>(xs) + c, chunks, lane4);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0 && HQ_IN_BOUNDS(res + row, 2, res, (size_t)rows * 2, 403)) {
+      const float v = BITS == 16 ? acc : scale * (acc - zero_point * sumx);
+      res[row] = __float2half_rn(v);
+    }
+  }
+}
+
+template <int BITS>
+int launch(const void* mat, const void* vec_half, void* res_half, int rows, int n, float scale,
+           float zero_point, hq_stream_t stream) {
+  if (!mat || !vec_half || !res_half) return HQ_ERR_NULL_POINTER;
+  // a row is a whole number of 16-byte chunks and the inputs a whole number of
+  // 16-byte groups: n a multiple of 8 (fp16), 16 (int8), 32 (int4)
+  if (rows <= 0 || n <= 0 || n % (128 / BITS) != 0) return HQ_ERR_BAD_SHAPE;
+  if (!aligned16(mat) || !aligned16(vec_half)) return HQ_ERR_MISALIGNED;
+  size_t smem = (size_t)n * 2;
+  if (BITS == 4) {
+    if (reserved_smem_per_block() > kLutImm) return HQ_ERR_UNSUPPORTED;
+    smem += (size_t)kLutImm + kLutBytes;
+  }
+  if (smem > 226 * 1024) return HQ_ERR_TOO_LARGE;  // beyond 113 KiB only one CTA fits an SM
+  constexpr auto kern = gemv_uniform_kernel<BITS>;
+  const cudaError_t e = ensure_dynamic_smem<kern>(smem);
+  if (e != cudaSuccess) return cuda_status(e);
+  // the launcher of the reference rounds both parameters to fp16 (gemv.cu:21-22)
+  const float s = __half2float(__float2half_rn(scale));
+  const float z = __half2float(__float2half_rn(zero_point));
+  const int grid = std::min(2 * sm_count(), (rows + kWarps - 1) / kWarps);
+  return cuda_status(launch_pdl(kern, dim3(grid), dim3(kThreads), smem, (cudaStream_t)stream,
+                                reinterpret_cast<const unsigned char*>(mat),
+                                reinterpret_cast<const __half*>(vec_half),
+                                reinterpret_cast<__half*>(res_half), rows, n, s, z));
+}
+
+}  // namespace
+}  // namespace hq
+
+extern "C" {
+
+int hq_gemv_f16(const void* mat_half, const void* vec_half, void* res_half, int rows, int n,
+                hq_stream_t stream) {
+  return hq::launch<16>(mat_half, vec_half, res_half, rows, n, 1.f, 0.f, stream);
+}
+
+int hq_gemv_int8_f16(const int8_t* mat, const void* vec_half, void* res_half, int rows, int n,
+                     float scale, float zero_point, hq_stream_t stream) {
+  return hq::launch<8>(mat, vec_half, res_half, rows, n, scale, zero_point, stream);
+}
+
+int hq_gemv_int4_f16(const uint8_t* mat, const void* vec_half, void* res_half, int rows, int n,
+                     float scale, float zero_point, hq_stream_t stream) {
+  return hq::launch<4>(mat, vec_half, res_half, rows, n, scale, zero_point, stream);
+}
+
+}  // extern "C"

@@ -8,6 +8,7 @@ only) go to hecbench_b200/build/dropin/:
   dropin_quantBnB      shim/quantBnB/main.cu (reference code.h on the include path)
   dropin_quantAQLM     shim/quantAQLM/main.cu
   dropin_quantVLLM     shim/quantVLLM/main.cu (reference reference.h, utils.h on the include path)
+  dropin_gemv          reference main.cu + shim/gemv/gemv.cu (reference kernels.h, simple_tensor.h on the include path)
   shard_demo           shim/shard/main.cu: one-process host of the hq_shard_* context
 
 The reference sources are compiled from where they lie; for quant3MatMul the
@@ -98,6 +99,14 @@ def build(force: bool = False):
     if stale(tgt, [drv]):
         _run([NVCC, *COMMON, "--expt-relaxed-constexpr", f"-I{src / 'quantVLLM-cuda'}", drv,
               "-o", tgt])
+    built.append(tgt)
+
+    # gemv: reference driver (option parsing) + our gemv.cu in place of the reference's
+    tgt = OUT / "dropin_gemv"
+    shim_cu = SHIM / "gemv" / "gemv.cu"
+    if stale(tgt, [shim_cu]):
+        d = src / "gemv-cuda"
+        _run([NVCC, *COMMON, f"-I{d}", d / "main.cu", shim_cu, "-o", tgt])
     built.append(tgt)
     return built
 

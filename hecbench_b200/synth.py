@@ -72,6 +72,19 @@ def nf4_case(N: int, K: int, blocksize: int = 64, seed: int = 0):
     return A, B, absmax, nf4_levels(seed)
 
 
+def gemv_uniform_case(rows: int, n: int, bits: int, seed: int = 0):
+    """gemv-cuda's inputs (simple_tensor.h:63-87): fp16 vec~U(0,1); mat int8
+    uniform over -128..127, or two uniform 4-bit codes per byte, or fp16~U(0,1)."""
+    vec = _rng(seed, 71).uniform(0.0, 1.0, n).astype(np.float16)
+    if bits == 8:
+        mat = _rng(seed, 72).integers(-128, 128, size=(rows, n), dtype=np.int8)
+    elif bits == 4:
+        mat = _rng(seed, 73).integers(0, 256, size=(rows, n // 2), dtype=np.uint8)
+    else:
+        mat = _rng(seed, 74).uniform(0.0, 1.0, (rows, n)).astype(np.float16)
+    return mat, vec
+
+
 def qgemm_nf4_case(Mb: int, K: int, N: int, blocksize: int = 64, seed: int = 0):
     """Batched NF4 path: fp16 X~N(0,1) plus the weights of nf4_case(N, K)."""
     _, B, absmax, lut16 = nf4_case(N, K, blocksize, seed)

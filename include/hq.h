@@ -325,6 +325,31 @@ int hq_vllm_dynamic_scaled_int8_quant(int8_t* out, const void* input, int dtype,
                                       int num_tokens, float* scales, int32_t* azp,
                                       hq_stream_t stream);
 
+/* ---------------- gemv: uniform int8 / int4 weight-only mat-vec ---------------- */
+
+/* gemv_quantized_int8 / gemv_quantized_int4 / gemv_fp16 of src/gemv-cuda
+ * (kernels.h:127-200, :205-307, :64-123; launchers gemv.cu:15-36, :38-59,
+ * :61-81).  mat is row-major [rows][n]: int8 values, or for int4 n/2 bytes
+ * per row with element 2j in the LOW nibble of byte j and 2j+1 in the high
+ * nibble (uint4_2::getX / getY, kernels.h:17-23), or fp16.  One scale and one
+ * zero point per tensor, rounded to fp16 as the reference launchers do
+ * (gemv.cu:21-22, :44-45):
+ *   res[row] = half( half(scale) * sum_j vec[j] * (w[row][j] - half(zero_point)) )
+ * with fp32 accumulation across 32- or 64-weight partial sums formed in fp16.
+ * The reference drivers use square matrices (rows == n == size); here rows and
+ * n are independent.  n must be a multiple of 8 (fp16), 16 (int8) or 32 (int4);
+ * mat and vec 16-byte aligned; n <= 114688 (fp16, int8) or 81920 (int4), else
+ * HQ_ERR_TOO_LARGE (the inputs are staged in shared memory; beyond half of those
+ * lengths only one CTA fits an SM).  The grid and block shapes of the reference launchers
+ * (block_dim_x, block_dim_y, num_per_thread) are tuning knobs of its kernels
+ * and have no counterpart here. */
+int hq_gemv_f16(const void* mat_half, const void* vec_half, void* res_half, int rows, int n,
+                hq_stream_t stream);
+int hq_gemv_int8_f16(const int8_t* mat, const void* vec_half, void* res_half, int rows, int n,
+                     float scale, float zero_point, hq_stream_t stream);
+int hq_gemv_int4_f16(const uint8_t* mat, const void* vec_half, void* res_half, int rows, int n,
+                     float scale, float zero_point, hq_stream_t stream);
+
 /* ---------------- batched dequant-GEMM (tensor cores) ---------------- */
 
 /* Y[Mb][N] = X[Mb][K] * W[K][N] with W the GPTQ 3-bit layout of quant3MatMul

@@ -94,6 +94,7 @@ REF_GPU_PARTS = {
     "ref_gpu_bnb.cu": ["quantBnB-cuda"],
     "ref_gpu_lut.cu": ["lut-gemm-cuda"],
     "ref_gpu_aqlm.cu": ["quantAQLM-cuda"],
+    "ref_gpu_gemv.cu": ["gemv-cuda"],
 }
 
 

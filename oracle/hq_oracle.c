@@ -626,6 +626,39 @@ void orc_q3g_dequant_f16(const int32_t* mat, const uint16_t* scales, const uint1
   }
 }
 
+/* ------------------------------------------------------------------------
+ * gemv: uniform int8 / int4 weight-only mat-vec.  Restates the device-side
+ * checks of gemv-cuda/gemv.cu:98-114 (int8) and :116-141 (int4) - the only
+ * statement of the expected result in the reference: the weight is dequantised
+ * in fp32 as (float(w) - float(zero_point_half)) * float(scale_half) - with the
+ * accumulation carried in fp64 here.  bits = 16 (fp16 matrix, gemv.cu:83-96),
+ * 8 (int8) or 4 (two codes per byte, element 2j in the low nibble:
+ * kernels.h:17-23).  scale and zero_point arrive as fp16 bit patterns, which
+ * is what the reference launchers make of their float arguments
+ * (gemv.cu:21-22).
+ * ------------------------------------------------------------------------ */
+void orc_gemv_uniform_f64(const void* mat, const uint16_t* vec, double* out, int rows, int n,
+                          int bits, uint16_t scale_h, uint16_t zero_h) {
+  const float scale = orc_h2f(scale_h), zp = orc_h2f(zero_h);
+#pragma omp parallel for
+  for (int r = 0; r < rows; r++) {
+    double acc = 0.0;
+    for (int j = 0; j < n; j++) {
+      float w;
+      if (bits == 16) {
+        w = orc_h2f(((const uint16_t*)mat)[(size_t)r * n + j]);
+      } else if (bits == 8) {
+        w = ((float)((const int8_t*)mat)[(size_t)r * n + j] - zp) * scale;
+      } else {
+        const uint8_t b = ((const uint8_t*)mat)[(size_t)r * (n / 2) + j / 2];
+        w = ((float)((j & 1) ? (b >> 4) : (b & 15)) - zp) * scale;
+      }
+      acc += (double)w * (double)orc_h2f(vec[j]);
+    }
+    out[r] = acc;
+  }
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -237,6 +237,25 @@ def nf4_gemv_f32(A, B, absmax, lut16, N, K, blocksize=64, low_first=0) -> np.nda
     return out.view(np.float16)
 
 
+# ---------------- gemv (uniform int8 / int4) ----------------
+
+def gemv_uniform_f64(mat, vec, bits: int, scale: float = 1.0, zero_point: float = 0.0) -> np.ndarray:
+    """fp64 truth of gemv-cuda's kernels: mat fp16 [rows][n] (bits 16), int8
+    [rows][n] (bits 8) or uint8 [rows][n/2] (bits 4); scale and zero point are
+    rounded to fp16 first, as the reference launchers do."""
+    dt = {16: np.uint16, 8: np.int8, 4: np.uint8}[bits]
+    mat = _c(mat.view(np.uint16) if mat.dtype == np.float16 else mat, dt)
+    rows = mat.shape[0]
+    n = mat.shape[1] * (2 if bits == 4 else 1)
+    vec = _c(vec, np.uint16)
+    out = np.empty(rows, dtype=np.float64)
+    sh = int(np.float16(scale).view(np.uint16))
+    zh = int(np.float16(zero_point).view(np.uint16))
+    lib().orc_gemv_uniform_f64(_ptr(mat), _ptr(vec), _ptr(out), C.c_int(rows), C.c_int(n),
+                               C.c_int(bits), C.c_uint16(sh), C.c_uint16(zh))
+    return out
+
+
 # ---------------- lut-gemm ----------------
 
 def lutgemm_dequant_f32(bW, alpha, q_bias, M, K, nb, group_size) -> np.ndarray:

@@ -32,6 +32,10 @@ void ref_lutgemm_matmul(void* output, void* input, unsigned int* bW, void* alpha
                         int M, int K, int nb, int num_groups);
 void ref_aqlm_1x16(const void* A, const void* B, void* C, const void* codebook, int prob_m,
                    int prob_k, const int* sizes, int codebook_stride);
+void ref_gemv_int8(int8_t* mat, void* vec_half, void* res_half, unsigned size, float scale_f,
+                   float zero_point_f, unsigned bx, unsigned by);
+void ref_gemv_int4(uint8_t* mat, void* vec_half, void* res_half, unsigned size, float scale_f,
+                   float zero_point_f, unsigned bx, unsigned by);
 }
 
 #define CK(x)                                                                          \
@@ -214,6 +218,28 @@ int main(int argc, char** argv) {
     emit("aqlm_1x16", time_launches(R, 20, [&](int i) {
            ref_aqlm_1x16(codes[i], x, out, cb, m, k, sizes, 65536);
          }));
+    free_all();
+  }
+  for (int bits = 8; bits >= 4; bits -= 4) {
+    // gemv, square 8192 x 8192; block shapes: the driver's default 32 x 4
+    // (gemv-cuda/main.cu:33-34) and 256 x 4 (both satisfy the launchers' asserts);
+    // the faster of the two is reported
+    const unsigned size = 8192;
+    const size_t bytes = (size_t)size * size * bits / 8;
+    const int R = replicas_for((double)bytes, target);
+    std::vector<void*> mats(R);
+    for (int i = 0; i < R; i++) mats[i] = filled(bytes / 4, 0, 0, 0, 500 + 10 * bits + i);
+    __half* x = (__half*)filled(size, 2, 0.f, 1.f, 11);
+    __half* out = (__half*)dmalloc((size_t)size * 2);
+    Result best{1e30, false, R};
+    for (unsigned bx : {32u, 256u}) {
+      const Result r = time_launches(R, 20, [&](int i) {
+        if (bits == 8) ref_gemv_int8((int8_t*)mats[i], x, out, size, 0.0625f, 0.01f, bx, 4);
+        else ref_gemv_int4((uint8_t*)mats[i], x, out, size, 0.0625f, 0.01f, bx, 4);
+      });
+      if (r.us < best.us) best = r;
+    }
+    emit(bits == 8 ? "gemv_int8" : "gemv_int4", best);
     free_all();
   }
   printf("}\n");

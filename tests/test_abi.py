@@ -92,6 +92,18 @@ def test_gather_and_noalloc_argument_errors_need_no_gpu(hq):
     assert lib.hq_lutgemm_nqmv_noalloc(p, p, p, p, None, 65536 + 4, 128, 3, 128, None) == -7
 
 
+def test_gemv_uniform_argument_errors_need_no_gpu(hq):
+    lib = hq.load_library()
+    p = 64
+    assert lib.hq_gemv_int8_f16(None, p, p, 16, 16, 1.0, 0.0, None) == -2
+    assert lib.hq_gemv_int4_f16(p, None, p, 16, 32, 1.0, 0.0, None) == -2
+    assert lib.hq_gemv_f16(p, p, None, 16, 8, None) == -2
+    assert lib.hq_gemv_int8_f16(p, p, p, 16, 24, 1.0, 0.0, None) == -1   # n % 16
+    assert lib.hq_gemv_int4_f16(p, p, p, 16, 16, 1.0, 0.0, None) == -1   # n % 32
+    assert lib.hq_gemv_f16(p, p, p, 0, 8, None) == -1
+    assert lib.hq_gemv_int8_f16(p + 8, p, p, 16, 16, 1.0, 0.0, None) == -3
+
+
 def test_shard_layout_arithmetic_and_argument_errors(hq):
     """Index arithmetic of the sharding context (no CUDA call) and the argument
     checks of hq_shard_create that come before any CUDA call."""

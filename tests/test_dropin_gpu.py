@@ -3,6 +3,7 @@ compiled unmodified against this library's shim headers / objects, and the two
 replacement drivers (quantBnB, quantAQLM), run on the GPU and judged by the
 drivers' own PASS / FAIL lines.  The binaries are built where the HeCBench tree
 is available (hecbench_b200/shim_build.py) and travel as build outputs."""
+import math
 import re
 import subprocess
 from pathlib import Path
@@ -53,3 +54,26 @@ def test_quantvllm_driver_passes():
     out = run("dropin_quantVLLM", 4096, 5137, 20)
     assert out.count("Average execution time of") == 12
     assert out.count("PASS") == 3 and "FAIL" not in out, out
+
+
+@pytest.mark.parametrize("size", [512, 4096])
+def test_gemv_reference_driver_runs_clean(size):
+    """The reference's own main.cu (option parsing, prints) linked with this
+    library's gemv.cu: both quantized sections run and the device-side check
+    (one '!!!' line per element outside 0.125 * n / 512) reports nothing but
+    fp16 output rounding.  512 is the driver's default size (main.cu:31)."""
+    out = run("dropin_gemv", "-s", size, "-i", 10)
+    assert f"size={size}, iter=10" in out
+    assert "GEMV int8 quantized..." in out and "GEMV int4 quantized..." in out
+    assert out.count("Average kernel execution time") == 2
+    assert out.count("Check correctness on the device") == 2
+    assert "status" not in out, out
+    # The reference's check allows 0.125 * n / 512 absolute, less than half an fp16
+    # spacing of the largest results (its tensors are all drawn from the same
+    # generator state, so row 0 correlates with the input vector and is large): a
+    # correctly rounded fp16 result can be reported.  Every reported element must
+    # be explained by that rounding alone.
+    for m in re.finditer(r"!!!\[idx=(\d+)\] (\S+) != (\S+), diff=(\S+)", out):
+        want, diff = float(m.group(3)), float(m.group(4))
+        half_spacing = 2.0 ** (math.floor(math.log2(abs(want))) - 10) / 2
+        assert abs(diff) <= half_spacing * 1.001, m.group(0)

@@ -291,3 +291,26 @@ def test_vllm_quant_oracle_matches_reference_golden(oracle, dtype):
     assert np.array_equal(q, g[f"dynazp_{dtype}"])
     assert np.array_equal(s.view(np.uint32), g[f"dynazp_scale_{dtype}"].view(np.uint32))
     assert np.array_equal(z, g[f"dynazp_azp_{dtype}"])
+
+
+def test_gemv_uniform_oracle_against_numpy(oracle):
+    """The C restatement of gemv-cuda's device-side checks (gemv.cu:83-141)
+    against the same arithmetic written in numpy: fp32 dequantisation with the
+    fp16-rounded scale and zero point, element 2j in the low nibble."""
+    from hecbench_b200 import synth
+    for bits in (8, 4, 16):
+        mat, vec = synth.gemv_uniform_case(33, 96, bits, seed=bits)
+        y = oracle.gemv_uniform_f64(mat, vec, bits, 0.0625, 0.01)
+        s = np.float32(np.float16(0.0625))
+        z = np.float32(np.float16(0.01))
+        if bits == 8:
+            w = (mat.astype(np.float32) - z) * s
+        elif bits == 4:
+            w = np.empty((33, 96), np.float32)
+            w[:, 0::2] = mat & 15
+            w[:, 1::2] = mat >> 4
+            w = (w - z) * s
+        else:
+            w = mat.astype(np.float32)
+        assert np.array_equal(y, w.astype(np.float64) @ vec.astype(np.float64)) or \
+            np.allclose(y, w.astype(np.float64) @ vec.astype(np.float64), rtol=1e-13, atol=0)
