@@ -13,8 +13,9 @@
 //
 // Design.  HBM-bound (2, 1 or 0.5 bytes per weight).  Two 512-thread CTAs per
 // SM; the input vector is staged once per CTA in shared memory (fp16) and its
-// sum reduced there; a warp owns whole rows (row = warp, warp + #warps, ...)
-// and streams them with 128-bit loads that bypass L1, four loads (64 bytes per
+// sum reduced there; a warp owns whole rows, two adjacent ones at a time (a
+// piece of the input vector read from shared memory then serves both), and
+// streams them with 128-bit loads that bypass L1, eight loads (128 bytes per
 // lane) in flight.
 //  * int8 -> fp16: one XOR flips the sign bits of four bytes (b + 128), a byte
 //    permute places two of them under the exponent byte 0x64 (1024 + b + 128,
@@ -33,7 +34,8 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
-constexpr int kInFlight = 4;            // 16-byte loads per lane in flight
+constexpr int kInFlight = 8;            // 16-byte loads per lane in flight
+constexpr int kRows = 2;                // adjacent rows a warp works on at a time
 constexpr int kLutImm = 2048;           // shared-window address of the int4 table
 constexpr int kLutBytes = 256 * 256;    // 256 rows of 256 bytes (first 128: one copy per bank)
 
@@ -51,61 +53,74 @@ __device__ __forceinline__ float sum4(__half2 a0, __half2 a1, __half2 a2, __half
   return f.x + f.y;
 }
 
-// 16 bytes of weights against the matching inputs -> fp32 partial sum.
+// 16 bytes of weights of each of R rows against the matching inputs, added to
+// the rows' fp32 sums; the inputs are read once for the R rows.
 // BITS = 16: 8 halves x 8 inputs; 8: 16 int8 x 16 inputs; 4: 32 nibbles x 32 inputs.
 // xs points at the chunk's first 16-byte piece of inputs; its further pieces
 // follow at a distance of `pitch` pieces (the inputs are stored piece-major so
 // that the 32 lanes of a warp, which hold consecutive chunks, read consecutive
 // 16-byte words: chunk-major, a chunk's 32 or 64 bytes apart, they would meet in
 // the same banks two or four at a time).
-template <int BITS>
-__device__ __forceinline__ float chunk_dot(const uint4& w, const uint4* xs, int pitch,
-                                           uint32_t lane4) {
-  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-  __half2 a0 = __float2half2_rn(0.f), a1 = a0, a2 = a0, a3 = a0;
+template <int BITS, int R>
+__device__ __forceinline__ void chunk_dot(const uint4 (&w)[R], const uint4* xs, int pitch,
+                                          uint32_t lane4, float (&acc)[R]) {
   if (BITS == 16) {
     const uint4 x = xs[0];
-    a0 = __hmul2(u32_as_half2(ww[0]), u32_as_half2(x.x));
-    a1 = __hmul2(u32_as_half2(ww[1]), u32_as_half2(x.y));
-    a2 = __hmul2(u32_as_half2(ww[2]), u32_as_half2(x.z));
-    a3 = __hmul2(u32_as_half2(ww[3]), u32_as_half2(x.w));
-    // one product per accumulator: summed in fp32 right away
-    const float2 f0 = __half22float2(a0), f1 = __half22float2(a1), f2 = __half22float2(a2),
-                 f3 = __half22float2(a3);
-    return ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      // one product per accumulator: summed in fp32 right away
+      const float2 f0 = __half22float2(__hmul2(u32_as_half2(w[r].x), u32_as_half2(x.x))),
+                   f1 = __half22float2(__hmul2(u32_as_half2(w[r].y), u32_as_half2(x.y))),
+                   f2 = __half22float2(__hmul2(u32_as_half2(w[r].z), u32_as_half2(x.z))),
+                   f3 = __half22float2(__hmul2(u32_as_half2(w[r].w), u32_as_half2(x.w)));
+      acc[r] += ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+    }
   } else if (BITS == 8) {
     const uint4 xa = xs[0], xb = xs[pitch];
     const uint32_t x2[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
     const __half2 off = __float2half2_rn(1152.f);  // 1024 (exponent byte) + 128 (sign flip)
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const uint32_t t = ww[i] ^ 0x80808080u;
-      const __half2 lo = __hsub2(u32_as_half2(__byte_perm(t, 0x64646464u, 0x4140)), off);
-      const __half2 hi = __hsub2(u32_as_half2(__byte_perm(t, 0x64646464u, 0x4342)), off);
-      if (i & 1) {
-        a2 = __hfma2(lo, u32_as_half2(x2[2 * i]), a2);
-        a3 = __hfma2(hi, u32_as_half2(x2[2 * i + 1]), a3);
-      } else {
-        a0 = __hfma2(lo, u32_as_half2(x2[2 * i]), a0);
-        a1 = __hfma2(hi, u32_as_half2(x2[2 * i + 1]), a1);
+    for (int r = 0; r < R; r++) {
+      const uint32_t ww[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
+      __half2 a0 = __float2half2_rn(0.f), a1 = a0, a2 = a0, a3 = a0;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint32_t t = ww[i] ^ 0x80808080u;
+        const __half2 lo = __hsub2(u32_as_half2(__byte_perm(t, 0x64646464u, 0x4140)), off);
+        const __half2 hi = __hsub2(u32_as_half2(__byte_perm(t, 0x64646464u, 0x4342)), off);
+        if (i & 1) {
+          a2 = __hfma2(lo, u32_as_half2(x2[2 * i]), a2);
+          a3 = __hfma2(hi, u32_as_half2(x2[2 * i + 1]), a3);
+        } else {
+          a0 = __hfma2(lo, u32_as_half2(x2[2 * i]), a0);
+          a1 = __hfma2(hi, u32_as_half2(x2[2 * i + 1]), a1);
+        }
       }
+      acc[r] += sum4(a0, a1, a2, a3);
     }
-    return sum4(a0, a1, a2, a3);
   } else {
+    __half2 a[R][4];
+#pragma unroll
+    for (int r = 0; r < R; r++) a[r][0] = a[r][1] = a[r][2] = a[r][3] = __float2half2_rn(0.f);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       const uint4 x = xs[i * pitch];
-      // byte k of the word -> (byte << 8) | lane*4: bytes {lane4.0, w.k, 0, 0}
-      const uint32_t l0 = lds_u32_imm<kLutImm>(__byte_perm(ww[i], lane4, 0x7604));
-      const uint32_t l1 = lds_u32_imm<kLutImm>(__byte_perm(ww[i], lane4, 0x7614));
-      const uint32_t l2 = lds_u32_imm<kLutImm>(__byte_perm(ww[i], lane4, 0x7624));
-      const uint32_t l3 = lds_u32_imm<kLutImm>(__byte_perm(ww[i], lane4, 0x7634));
-      a0 = __hfma2(u32_as_half2(l0), u32_as_half2(x.x), a0);
-      a1 = __hfma2(u32_as_half2(l1), u32_as_half2(x.y), a1);
-      a2 = __hfma2(u32_as_half2(l2), u32_as_half2(x.z), a2);
-      a3 = __hfma2(u32_as_half2(l3), u32_as_half2(x.w), a3);
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        const uint32_t wi = i == 0 ? w[r].x : i == 1 ? w[r].y : i == 2 ? w[r].z : w[r].w;
+        // byte k of the word -> (byte << 8) | lane*4: bytes {lane4.0, w.k, 0, 0}
+        const uint32_t l0 = lds_u32_imm<kLutImm>(__byte_perm(wi, lane4, 0x7604));
+        const uint32_t l1 = lds_u32_imm<kLutImm>(__byte_perm(wi, lane4, 0x7614));
+        const uint32_t l2 = lds_u32_imm<kLutImm>(__byte_perm(wi, lane4, 0x7624));
+        const uint32_t l3 = lds_u32_imm<kLutImm>(__byte_perm(wi, lane4, 0x7634));
+        a[r][0] = __hfma2(u32_as_half2(l0), u32_as_half2(x.x), a[r][0]);
+        a[r][1] = __hfma2(u32_as_half2(l1), u32_as_half2(x.y), a[r][1]);
+        a[r][2] = __hfma2(u32_as_half2(l2), u32_as_half2(x.z), a[r][2]);
+        a[r][3] = __hfma2(u32_as_half2(l3), u32_as_half2(x.w), a[r][3]);
+      }
     }
-    return sum4(a0, a1, a2, a3);
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] += sum4(a[r][0], a[r][1], a[r][2], a[r][3]);
   }
 }
 
@@ -163,32 +178,44 @@ gemv_uniform_kernel(const unsigned char* __restrict__ mat, const __half* __restr
 #pragma unroll
   for (int w = 0; w < kWarps; w++) sumx += s_part[w];
 
-  // ---- rows of this warp ----
+  // ---- rows of this warp: kRows adjacent rows at a time, so that a piece of the
+  // input vector read from shared memory serves kRows rows ----
   const uint32_t lane4 = (uint32_t)lane * 4u;
   const int warps_total = gridDim.x * kWarps;
-  for (long long row = (long long)blockIdx.x * kWarps + warp; row < rows; row += warps_total) {
-    const unsigned char* src = mat + (size_t)row * row_bytes;
-    float acc = 0.f;
-    for (int c0 = lane; c0 < chunks; c0 += 32 * kInFlight) {
-      uint4 w[kInFlight];
+  constexpr int kPerRow = kInFlight / kRows;  // loads per row and batch
+  const size_t mat_bytes = (size_t)rows * row_bytes;
+  (void)mat_bytes;
+  for (long long row0 = ((long long)blockIdx.x * kWarps + warp) * kRows; row0 < rows;
+       row0 += (long long)warps_total * kRows) {
+    const unsigned char* src = mat + (size_t)row0 * row_bytes;
+    float acc[kRows];
 #pragma unroll
-      for (int u = 0; u < kInFlight; u++) {
+    for (int r = 0; r < kRows; r++) acc[r] = 0.f;
+    for (int c0 = lane; c0 < chunks; c0 += 32 * kPerRow) {
+      uint4 w[kPerRow][kRows];
+#pragma unroll
+      for (int u = 0; u < kPerRow; u++) {
         const int c = c0 + 32 * u;
-        w[u] = make_uint4(0, 0, 0, 0);
-        if (c < chunks && HQ_IN_BOUNDS(src + (size_t)c * 16, 16, mat, (size_t)rows * row_bytes, 402))
-          w[u] = ldg_stream_u4(src + (size_t)c * 16);
+#pragma unroll
+        for (int r = 0; r < kRows; r++) {
+          const unsigned char* at = src + (size_t)r * row_bytes + (size_t)c * 16;
+          w[u][r] = make_uint4(0, 0, 0, 0);  // a row past the end contributes zeros
+          if (c < chunks && row0 + r < rows && HQ_IN_BOUNDS(at, 16, mat, mat_bytes, 402))
+            w[u][r] = ldg_stream_u4(at);
+        }
       }
 #pragma unroll
-      for (int u = 0; u < kInFlight; u++) {
+      for (int u = 0; u < kPerRow; u++) {
         const int c = c0 + 32 * u;
         if (c < chunks)
-          acc += chunk_dot<BITS>(w[u], reinterpret_cast<const uint4*>(xs) + c, chunks, lane4);
+          chunk_dot<BITS, kRows>(w[u], reinterpret_cast<const uint4*>(xs) + c, chunks, lane4, acc);
       }
     }
-    acc = warp_sum(acc);
-    if (lane == 0 && HQ_IN_BOUNDS(res + row, 2, res, (size_t)rows * 2, 403)) {
-      const float v = BITS == 16 ? acc : scale * (acc - zero_point * sumx);
-      res[row] = __float2half_rn(v);
+#pragma unroll
+    for (int r = 0; r < kRows; r++) {
+      const float total = warp_sum(acc[r]);
+      if (lane == 0 && row0 + r < rows && HQ_IN_BOUNDS(res + row0 + r, 2, res, (size_t)rows * 2, 403))
+        res[row0 + r] = __float2half_rn(BITS == 16 ? total : scale * (total - zero_point * sumx));
     }
   }
 }
@@ -213,7 +240,7 @@ int launch(const void* mat, const void* vec_half, void* res_half, int rows, int 
   // the launcher of the reference rounds both parameters to fp16 (gemv.cu:21-22)
   const float s = __half2float(__float2half_rn(scale));
   const float z = __half2float(__float2half_rn(zero_point));
-  const int grid = std::min(2 * sm_count(), (rows + kWarps - 1) / kWarps);
+  const int grid = std::min(2 * sm_count(), (rows + kWarps * kRows - 1) / (kWarps * kRows));
   return cuda_status(launch_pdl(kern, dim3(grid), dim3(kThreads), smem, (cudaStream_t)stream,
                                 reinterpret_cast<const unsigned char*>(mat),
                                 reinterpret_cast<const __half*>(vec_half),
