@@ -150,6 +150,26 @@ def _host_case(name: str, seed: int, Mb: int = 64):
         return dict(size=size, bits=bits, mat=mat, vec=vec, scale=0.0625, zp=0.01,
                     bytes=mat.nbytes + 4 * size,
                     desc=f"uniform int{bits} weight-only GEMV {size}x{size} (gemv-cuda), fp16 in/out")
+    if name in ("fused_nf4_swiglu", "fused_int8_swiglu", "fused_int4_swiglu"):
+        # entry of a Llama-3-8B MLP at batch 1: RMSNorm(4096) -> interleaved up/gate
+        # rows [2 * 14336][4096] -> SwiGLU, one launch
+        n, rows_out = 4096, 14336
+        rng = synth._rng(seed, 70)
+        x = (rng.standard_normal(n) * 2).astype(np.float16)
+        gamma = rng.uniform(0.5, 1.5, n).astype(np.float16)
+        fmt = name.split("_")[1]
+        if fmt == "nf4":
+            _, B, absmax, lut = synth.nf4_case(2 * rows_out, n, 64, seed)
+            extra = dict(mat=B.reshape(2 * rows_out, n // 2), absmax=absmax, lut=lut)
+            nbytes = B.nbytes + absmax.nbytes + 64
+        else:
+            mat, _ = synth.gemv_uniform_case(2 * rows_out, n, int(fmt[3:]), seed)
+            extra = dict(mat=mat, scale=0.02, zp=0.5)
+            nbytes = mat.nbytes
+        return dict(n=n, rows_out=rows_out, fmt=fmt, x=x, gamma=gamma, **extra,
+                    bytes=nbytes + 4 * n + 2 * rows_out,
+                    desc=f"RMSNorm -> {fmt} up/gate mat-vec [{2 * rows_out}x{n}] -> SwiGLU, one "
+                         "launch (Llama-3-8B MLP entry, batch 1)")
     if name in ("qgemm_q3", "qgemm_q3_down"):
         K, N = (28672, 8192) if name.endswith("down") else (8192, 28672)
         G = K // 128
@@ -182,7 +202,8 @@ WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "q3_gemv_f
              "q3_gemv_f16_opt175b", "bnb_quantize", "lutgemm", "aqlm_1x16", "aqlm_2x8",
              "qgemm_q3", "qgemm_nf4", "qgemm_q3_down", "qgemm_nf4_down",
              "vllm_static_f16", "vllm_dynamic_f16", "vllm_dynamic_azp_f16",
-             "gemv_int8", "gemv_int4"]
+             "gemv_int8", "gemv_int4", "fused_nf4_swiglu", "fused_int8_swiglu",
+             "fused_int4_swiglu"]
 
 
 def dtype_of(name: str) -> str:
@@ -263,6 +284,15 @@ class DeviceWorkload:
             self.mat = [t(rot(c["mat"], i)) for i in range(R)]
             self.x = [t(c["vec"]) for _ in range(R)]
             self.out = [torch.empty(c["size"], dtype=torch.float16, device=dev) for _ in range(R)]
+        elif name.startswith("fused_"):
+            self.mat = [t(rot(c["mat"], i)) for i in range(R)]
+            self.gamma = t(c["gamma"])
+            if c["fmt"] == "nf4":
+                self.absmax = [t(rot(c["absmax"], i)) for i in range(R)]
+                self.lut = t(c["lut"])
+            self.x = [t(c["x"]) for _ in range(R)]
+            self.out = [torch.empty(c["rows_out"], dtype=torch.float16, device=dev)
+                        for _ in range(R)]
         elif name.startswith("vllm"):
             self.xin = [t(rot(c["x"], i)) for i in range(R)]
             self.q = torch.empty((c["tokens"], c["hidden"]), dtype=torch.int8, device=dev)
@@ -302,6 +332,13 @@ class DeviceWorkload:
             hq.gemv_int8_quantized(self.mat[i], self.x[i], c["scale"], c["zp"], out=self.out[i])
         elif n == "gemv_int4":
             hq.gemv_int4_quantized(self.mat[i], self.x[i], c["scale"], c["zp"], out=self.out[i])
+        elif n.startswith("fused_"):
+            kw = (dict(absmax=self.absmax[i], lut16=self.lut, blocksize=64) if c["fmt"] == "nf4"
+                  else dict(scale=c["scale"], zero_point=c["zp"]))
+            if c["fmt"] == "nf4":
+                kw["weights_resident"] = pdl
+            hq.gemv_fused(c["fmt"], self.x[i], self.mat[i], c["rows_out"], gamma=self.gamma,
+                          eps=1e-5, act=hq.ACT_SWIGLU, out=self.out[i], **kw)
         elif n == "vllm_static_f16":
             hq.static_scaled_int8_quant(self.q, self.xin[i], c["hidden"], c["tokens"], 0.1, 0)
         elif n.startswith("vllm_dynamic"):
@@ -313,6 +350,23 @@ class DeviceWorkload:
         elif n.startswith("qgemm_nf4"):
             hq.qgemm_nf4(self.x[i], self.B[i], self.absmax, self.lut, self.n_local, c["K"], c["bs"],
                          0, out=self.out[i] if out is None else out, peers=peers)
+
+    def launch_unfused(self, i: int, pdl: bool = PDL):
+        """The fused workloads as three launches: torch's RMSNorm, the library's plain
+        mat-vec over all 2 * rows_out rows, torch's SiLU-and-multiply of the pairs."""
+        hq, c, F = self.hq, self.case, self.torch.nn.functional
+        xn = F.rms_norm(self.x[i], (c["n"],), self.gamma, 1e-5)
+        rows = 2 * c["rows_out"]
+        if not hasattr(self, "pairs"):
+            self.pairs = self.torch.empty(rows, dtype=self.torch.float16, device=self.dev)
+        if c["fmt"] == "nf4":
+            hq.gemv_nf4(xn, self.mat[i], self.absmax[i], self.lut, rows, c["n"], 64, 0, self.pairs,
+                        weights_resident=pdl)
+        elif c["fmt"] == "int8":
+            hq.gemv_int8_quantized(self.mat[i], xn, c["scale"], c["zp"], out=self.pairs)
+        else:
+            hq.gemv_int4_quantized(self.mat[i], xn, c["scale"], c["zp"], out=self.pairs)
+        self.torch.mul(F.silu(self.pairs[1::2]), self.pairs[0::2], out=self.out[i])
 
     # host <-> device traffic of one launch on the end-to-end path
     def host_io(self):
@@ -847,7 +901,9 @@ def main():
         kernel_only_us = float(tk.item())
 
     # ---- N = 1 extras: isolated launches, pure-read ceiling -----------------------
-    read_us = no_pdl_us = None
+    read_us = no_pdl_us = unfused_us = None
+    if name.startswith("fused_") and world == 1:
+        unfused_us = time_replicas(torch, stream, wl.launch_unfused, R, 20)
     if name == "nf4_gemv" and world == 1:
         no_pdl_us = time_replicas(torch, stream, lambda i: wl.launch(i, pdl=False), R, 50)
         probe = ROOT / "hecbench_b200" / "libhq_probe.so"
@@ -1003,7 +1059,7 @@ def main():
                        "launch": ("cuda graph of R launches" if graph is not None else "eager") +
                                  ("; weights flagged resident: a launch fetches its weights while "
                                   "the previous launch's tail drains (programmatic dependent launch)"
-                                  if PDL and name == "nf4_gemv" else ""),
+                                  if PDL and name in ("nf4_gemv", "fused_nf4_swiglu") else ""),
                        "parallelism": par},
             "us_per_gemv": us_per_launch,
             "roofline": roof,
@@ -1013,6 +1069,8 @@ def main():
             line["value_no_pdl"] = wl.bytes / (no_pdl_us * 1e-6) / 1e9
             line["us_per_gemv_no_pdl"] = no_pdl_us
             line["roofline"]["frac_no_pdl"] = line["value_no_pdl"] / roof["peak"]
+        if unfused_us is not None:
+            line["us_as_three_launches"] = unfused_us  # torch rms_norm, plain mat-vec, torch silu * mul
         if gather_check is not None:
             line["gather_check"] = gather_check
         if kernel_only_us is not None:

@@ -20,7 +20,11 @@ from .api import (  # noqa: F401
     code2x8_matvec,
     dequantize_nf4,
     dynamic_scaled_int8_quant,
+    ACT_GEGLU,
+    ACT_NONE,
+    ACT_SWIGLU,
     gemv_fp16,
+    gemv_fused,
     gemv_int4_quantized,
     gemv_int8_quantized,
     gemv_nf4,
@@ -43,5 +47,6 @@ __all__ = [
     "nQWeight_fp16", "matmul", "qgemm_q3", "qgemm_nf4", "qgemm_reset_workspaces", "code1x16_matvec", "code2x8_matvec",
     "static_scaled_int8_quant", "dynamic_scaled_int8_quant",
     "gemv_fp16", "gemv_int8_quantized", "gemv_int4_quantized",
+    "gemv_fused", "ACT_NONE", "ACT_SWIGLU", "ACT_GEGLU",
     "NF4_HIGH_NIBBLE_FIRST", "NF4_LOW_NIBBLE_FIRST", "NF4_WEIGHTS_RESIDENT",
 ]

@@ -69,6 +69,14 @@ SIGNATURES = {
     "hq_gemv_f16": (c_int, [c_void_p] * 3 + [c_int, c_int, c_void_p]),
     "hq_gemv_int8_f16": (c_int, [c_void_p] * 3 + [c_int, c_int, C.c_float, C.c_float, c_void_p]),
     "hq_gemv_int4_f16": (c_int, [c_void_p] * 3 + [c_int, c_int, C.c_float, C.c_float, c_void_p]),
+    "hq_gemv_fused_f16": (c_int, [c_void_p, c_void_p, C.c_float, c_void_p, c_void_p] +
+                          [c_int] * 3 + [c_void_p]),
+    "hq_gemv_fused_int8_f16": (c_int, [c_void_p, c_void_p, C.c_float, c_void_p, c_void_p, c_int,
+                                       c_int, C.c_float, C.c_float, c_int, c_void_p]),
+    "hq_gemv_fused_int4_f16": (c_int, [c_void_p, c_void_p, C.c_float, c_void_p, c_void_p, c_int,
+                                       c_int, C.c_float, C.c_float, c_int, c_void_p]),
+    "hq_gemv_fused_nf4_f16": (c_int, [c_void_p, c_void_p, C.c_float] + [c_void_p] * 4 +
+                              [c_int] * 5 + [c_void_p]),
     "hq_aqlm_2x8_matvec": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p, c_void_p]),
 }
 

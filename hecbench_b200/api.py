@@ -243,6 +243,57 @@ def gemv_int4_quantized(mat, vec, scale: float, zero_point: float,
 
 
 # --------------------------------------------------------------------------
+# RMSNorm -> mat-vec -> gated activation, fused
+# --------------------------------------------------------------------------
+
+ACT_NONE, ACT_SWIGLU, ACT_GEGLU = 0, 1, 2
+
+
+def gemv_fused(fmt: str, x, mat, rows_out: int, *, gamma=None, eps: float = 1e-5, act: int = ACT_NONE,
+               scale: float = 1.0, zero_point: float = 0.0, absmax=None, lut16=None,
+               blocksize: int = 64, nibble_order: int = 0, weights_resident: bool = False,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One launch for the entry of a decode-time MLP: RMSNorm of x (skipped when
+    gamma is None; rmsnorm-cuda/reference.h:4-25), the weight-only mat-vec in
+    format fmt ("f16", "int8", "int4", "nf4"; layouts and parameters as gemv_fp16,
+    gemv_int8_quantized, gemv_int4_quantized, gemv_nf4) and, with act = ACT_SWIGLU
+    or ACT_GEGLU, the gated activation of row pairs: mat then has 2 * rows_out
+    rows, row 2m the value row and row 2m + 1 the gate row of output m
+    (geglu-cuda/reference.h:8-16, swish-cuda/reference.h:4).  weights_resident
+    (NF4): as in gemv_nf4, the weights may be fetched while the preceding kernel
+    of the stream drains."""
+    lib = load_library()
+    n = x.numel()
+    if out is None:
+        out = torch.empty(rows_out, dtype=torch.float16, device=x.device)
+    xp = _dev(x, torch.float16, "x")
+    gp = 0 if gamma is None else _dev(gamma, torch.float16, "gamma")
+    op = _dev(out, torch.float16, "out")
+    with torch.cuda.device(x.device):
+        if fmt == "f16":
+            st = lib.hq_gemv_fused_f16(xp, gp, float(eps), _dev(mat, torch.float16, "mat"), op,
+                                       rows_out, n, act, _stream())
+        elif fmt == "int8":
+            st = lib.hq_gemv_fused_int8_f16(xp, gp, float(eps), _dev(mat, torch.int8, "mat"), op,
+                                            rows_out, n, float(scale), float(zero_point), act,
+                                            _stream())
+        elif fmt == "int4":
+            st = lib.hq_gemv_fused_int4_f16(xp, gp, float(eps), _dev(mat, torch.uint8, "mat"), op,
+                                            rows_out, n, float(scale), float(zero_point), act,
+                                            _stream())
+        elif fmt == "nf4":
+            st = lib.hq_gemv_fused_nf4_f16(xp, gp, float(eps), _dev(mat, torch.uint8, "mat"),
+                                           _dev(absmax, torch.float32, "absmax"),
+                                           _dev(lut16, torch.float32, "lut16"), op, rows_out, n,
+                                           blocksize, nibble_order | (2 if weights_resident else 0),
+                                           act, _stream())
+        else:
+            raise ValueError(f"unknown format {fmt!r}")
+        check("hq_gemv_fused_" + fmt, st)
+    return out
+
+
+# --------------------------------------------------------------------------
 # lut-gemm
 # --------------------------------------------------------------------------
 

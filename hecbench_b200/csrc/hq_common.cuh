@@ -165,6 +165,13 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Gate of a gated linear unit, fp32: HQ_ACT_SWIGLU g * sigmoid(g)
+// (swish-cuda/reference.h:4), else HQ_ACT_GEGLU 0.5 g (1 + erf(g / sqrt 2))
+// (geglu-cuda/reference.h:1-5).
+__device__ __forceinline__ float gate_act(float g, int act) {
+  if (act == HQ_ACT_SWIGLU) return g / (1.f + expf(-g));
+  return 0.5f * g * (1.f + erff(g * 0.70710678118654752440f));
+}
 __device__ __forceinline__ __half2 u32_as_half2(uint32_t u) {
   return *reinterpret_cast<__half2*>(&u);
 }

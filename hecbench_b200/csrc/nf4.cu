@@ -81,6 +81,16 @@ __device__ __forceinline__ uint4 ldg_ordered_u4(const void* p) {
   return v;
 }
 
+// 16-byte asynchronous copy global -> shared (no register holds the data)
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
 // sum of the 32 products of one 16-byte chunk against 16 half2 inputs
 __device__ __forceinline__ float chunk_dot(const uint4& codes, const uint4 (&xp)[4],
                                            uint32_t lane4) {
@@ -142,6 +152,17 @@ struct GemvParams {
   unsigned long long b_bytes, absmax_bytes, a_bytes, out_bytes;
   int early_fetch;  // weights may be fetched before the preceding kernel in the stream has finished
   int* status;
+  // Fused forms (FUSE kernels only).  gamma != null: the input vector is RMS-
+  // normalised and scaled by gamma first.  act != 0: the rows come in pairs
+  // (value row 2m, gate row 2m + 1), a group walks pairs instead of rows and
+  // output m = value * gate_act(gate).  w_step / a_step then are the distance
+  // from a value row to its gate row, the _odd ones from a gate row to the next
+  // pair's value row.
+  const __half* gamma;
+  float eps;
+  int act;
+  unsigned long long w_step_odd;
+  unsigned int a_step_odd;
 #ifdef HQ_NF4_TRACE
   unsigned long long* trace;  // development: [CTA][16] globaltimer stamps
 #endif
@@ -218,10 +239,16 @@ __device__ __forceinline__ void stage_packets(__half* xs, const uint2* ll, long 
 // starts on an absmax block boundary and blocks are a power of two, so the
 // absmax pointer of a lane advances by a constant.  Nothing is divided on the
 // device in the ALIGNED kernels.
-template <int C, int D, int ST, bool ALIGNED, int THREADS>
+//
+// FUSE: RMSNorm of the input vector before the product and / or a gated
+// activation of row pairs after it (rmsnorm-cuda/reference.h:4-25,
+// geglu-cuda/reference.h:8-16), see GemvParams; plain fp16 input and output only.
+template <int C, int D, int ST, bool ALIGNED, int THREADS, bool FUSE>
 __global__ void __launch_bounds__(THREADS, 1)
 nf4_gemv_kernel(const GemvParams p) {
   constexpr int W = THREADS / 32;
+  static_assert(D % 2 == 0, "a value row and its gate row sit in adjacent stages");
+  __shared__ float s_sq[W];  // FUSE: sum of squares of each warp's inputs
   extern __shared__ __align__(16) unsigned char dsm_raw[];
   // [pad up to shared address kLutImm] table rows (256 x 256 B) |
   // partial sums [2][W * D][32] float
@@ -238,9 +265,13 @@ nf4_gemv_kernel(const GemvParams p) {
   const int G = p.G;
 
   // rows of this group: n = blockIdx.x + gridDim.x * (g + G * j), j < my_rows
-  const int row_first = blockIdx.x + gridDim.x * g;
+  // (paired: the same walk over pairs; matrix rows 2n and 2n + 1 of each)
+  const bool paired = FUSE && p.act != 0;
+  const int unit_first = blockIdx.x + gridDim.x * g;
   const int row_stride = gridDim.x * G;
-  const int my_rows = g < G ? p.rows_base + (row_first < p.rows_rem ? 1 : 0) : 0;
+  const int my_units = g < G ? p.rows_base + (unit_first < p.rows_rem ? 1 : 0) : 0;
+  const int row_first = paired ? 2 * unit_first : unit_first;
+  const int my_rows = paired ? 2 * my_units : my_units;
 
   // The 16 levels first: the table build must not queue behind the weight loads
   // below.  (The levels count as weights: read before the wait with early_fetch.)
@@ -284,9 +315,11 @@ nf4_gemv_kernel(const GemvParams p) {
         cw[STAGE][i] = ldg_stream_u4(wp[i]);                                                    \
         cs[STAGE][i] = __ldg(a);                                                                \
       }                                                                                         \
-      wp[i] += p.w_step;                                                                        \
-      if (ALIGNED) ap[i] += p.a_step;                                                           \
-      else ci[i] += (uint32_t)row_stride * (uint32_t)p.nchunks;                                 \
+      const bool odd = FUSE && (((STAGE) & 1) != 0);                                            \
+      wp[i] += odd ? p.w_step_odd : p.w_step;                                                   \
+      if (ALIGNED) ap[i] += odd ? p.a_step_odd : p.a_step;                                      \
+      else ci[i] += (uint32_t)(!paired ? row_stride : (odd ? 2 * row_stride - 1 : 1)) *         \
+                    (uint32_t)p.nchunks;                                                        \
     }                                                                                           \
   }
   // Order of the prologue.  With early_fetch: the first kEarly rows of weights,
@@ -328,6 +361,15 @@ nf4_gemv_kernel(const GemvParams p) {
       }
     }
   }
+  // FUSE: gamma goes to shared memory by asynchronous copies (no registers are
+  // held for it while the weights are requested)
+  __half* const gs = reinterpret_cast<__half*>(dsm + kLutBytes + (size_t)2 * W * D * 32 * sizeof(float));
+  if (FUSE && p.gamma != nullptr) {
+    for (int i = tid; i < p.nchunks * 4; i += THREADS)
+      if (HQ_IN_BOUNDS(reinterpret_cast<const uint4*>(p.gamma) + i, 16, p.gamma, p.a_bytes, 105))
+        cp_async_16(reinterpret_cast<uint4*>(gs) + i, reinterpret_cast<const uint4*>(p.gamma) + i);
+    cp_async_commit();
+  }
 #pragma unroll
   for (int d = 0; d < D; d++)
     if (!(p.early_fetch && d < kEarly) && d < my_rows) HQ_NF4_LOAD(d)
@@ -360,13 +402,55 @@ nf4_gemv_kernel(const GemvParams p) {
       for (int t = 0; t < 4; t++) xr[i][t] = live[i] ? xp[t] : make_uint4(0, 0, 0, 0);
     }
   }
+  if (FUSE && p.gamma != nullptr) {
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < C; i++)
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        const uint32_t h[4] = {xr[i][t].x, xr[i][t].y, xr[i][t].z, xr[i][t].w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const float2 f = __half22float2(u32_as_half2(h[k]));
+          sq = fmaf(f.x, f.x, fmaf(f.y, f.y, sq));
+        }
+      }
+    sq = warp_sum(sq);
+    if (lane == 0) s_sq[warp] = sq;
+    cp_async_wait_all();
+  }
   __syncthreads();
+  if (FUSE && p.gamma != nullptr) {
+    // the S warps of a group hold the whole vector between them
+    float tot = 0.f;
+    for (int t = 0; t < S; t++) tot += s_sq[g * S + t];
+    const float norm = rsqrtf(tot / (float)(p.nchunks * 32) + p.eps);
+#pragma unroll
+    for (int i = 0; i < C; i++) {
+      const int c = (q * C + i) * 32 + lane;
+      const uint4* gp = reinterpret_cast<const uint4*>(gs) + 4 * (live[i] ? c : 0);
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        const uint4 gv = gp[t];
+        uint32_t h[4] = {xr[i][t].x, xr[i][t].y, xr[i][t].z, xr[i][t].w};
+        const uint32_t gh[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const float2 f = __half22float2(u32_as_half2(h[k]));
+          const float2 w = __half22float2(u32_as_half2(gh[k]));
+          h[k] = half2_as_u32(__floats2half2_rn(f.x * norm * w.x, f.y * norm * w.y));
+        }
+        if (live[i]) xr[i][t] = make_uint4(h[0], h[1], h[2], h[3]);
+      }
+    }
+  }
 
   HQ_STAMP(4)
   const uint32_t lane4 = lane * 4;
   // row j of this group is output element n_out + j * row_stride: stored as fp16
   // (lane 0) or as one packet per GPU of the node (lane r -> rank r)
-  long long n_out = row_first;
+  long long n_out = unit_first;
+  float held = 0.f;  // paired, one warp per row: the value row's sum until its gate row is done
   auto store_result = [&](long long n, float v) {
     const __half h = __float2half_rn(v);
     if (p.peer_ll == nullptr) {
@@ -391,13 +475,33 @@ nf4_gemv_kernel(const GemvParams p) {
         if (j0 + d + D < my_rows) HQ_NF4_LOAD(d)
         if (S > 1) {
           part_r[(d * S + q) * 32] = acc;
+        } else if (paired) {
+          const float total = warp_sum(acc);
+          if (d & 1) {
+            store_result(n_out, held * gate_act(total, p.act));
+            n_out += row_stride;
+          } else {
+            held = total;
+          }
         } else {
           store_result(n_out, warp_sum(acc));
           n_out += row_stride;
         }
       }
     }
-    if (S > 1) {
+    if (S > 1 && paired) {
+      group_barrier(1 + g, S * 32);
+      for (int pr = q; 2 * pr < rows_in_round; pr += S) {
+        float v = 0.f, gt = 0.f;
+        for (int t = 0; t < S; t++) {
+          v += part_r[(2 * pr * S + t) * 32];
+          gt += part_r[((2 * pr + 1) * S + t) * 32];
+        }
+        store_result(n_out + (long long)pr * row_stride, warp_sum(v) * gate_act(warp_sum(gt), p.act));
+      }
+      n_out += (long long)(D / 2) * row_stride;
+      parity ^= 1;
+    } else if (S > 1) {
       group_barrier(1 + g, S * 32);
       for (int d = q; d < rows_in_round; d += S) {
         float v = 0.f;
@@ -908,7 +1012,8 @@ gather_publish_small_kernel(__half* const* peer_out, long long offset, int n_sli
 namespace hq {
 namespace {
 
-template <int C, int D, int ST, bool AL, int THREADS>
+// N: rows of the matrix, or (FUSE with a gated activation) pairs of rows
+template <int C, int D, int ST, bool AL, int THREADS, bool FUSE>
 int launch_gemv(GemvParams& prm, int N, cudaStream_t st) {
   constexpr int W = THREADS / 32;
   const int S = prm.S;
@@ -918,14 +1023,24 @@ int launch_gemv(GemvParams& prm, int N, cudaStream_t st) {
   prm.G = G;
   prm.rows_base = N / (grid * G);
   prm.rows_rem = N % (grid * G);
-  prm.w_step = (unsigned long long)grid * G * prm.nchunks * 16ull;
-  prm.a_step = AL ? (unsigned)(((unsigned long long)grid * G * prm.nchunks) >> prm.cpb_shift) : 0u;
+  // rows from one row of a group to its next one, even and odd stages
+  unsigned long long step = (unsigned long long)grid * G, step_odd = step;
+  if (FUSE && prm.act != 0) {
+    step = 1;
+    step_odd = 2ull * grid * G - 1;
+  }
+  prm.w_step = step * prm.nchunks * 16ull;
+  prm.w_step_odd = step_odd * prm.nchunks * 16ull;
+  prm.a_step = AL ? (unsigned)((step * prm.nchunks) >> prm.cpb_shift) : 0u;
+  prm.a_step_odd = AL ? (unsigned)((step_odd * prm.nchunks) >> prm.cpb_shift) : 0u;
   // room for the pad that brings the table to shared address kLutImm wherever the
   // dynamic region starts (at or below kLutImm)
   size_t smem = (size_t)kLutImm + kLutBytes + (size_t)2 * W * D * 32 * sizeof(float);
-  if (prm.A_ll != nullptr) smem += (size_t)prm.nchunks * 32 * sizeof(__half);  // unpacked input
+  // unpacked input (packets) or gamma (FUSE)
+  if (prm.A_ll != nullptr || (FUSE && prm.gamma != nullptr))
+    smem += (size_t)prm.nchunks * 32 * sizeof(__half);
   if (smem > 227 * 1024) return HQ_ERR_TOO_LARGE;
-  constexpr auto kern = nf4_gemv_kernel<C, D, ST, AL, THREADS>;
+  constexpr auto kern = nf4_gemv_kernel<C, D, ST, AL, THREADS, FUSE>;
   cudaError_t e = ensure_dynamic_smem<kern>(smem);
   if (e != cudaSuccess) return cuda_status(e);
   return cuda_status(launch_pdl(kern, dim3(grid), dim3(THREADS), smem, st, prm));
@@ -965,9 +1080,16 @@ int launch_gemv_bulk(GemvParams& prm, int N, cudaStream_t st) {
 }  // namespace
 }  // namespace hq
 
+// What the fused forms add (see GemvParams): N stays the number of matrix rows.
+struct FuseArgs {
+  const void* gamma = nullptr;
+  float eps = 0.f;
+  int act = HQ_ACT_NONE;
+};
+
 static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absmax,
                          const float* lut16, void* out_half, int N, int K, int blocksize, int flags,
-                         const LlArgs& ll, hq_stream_t stream) {
+                         const LlArgs& ll, hq_stream_t stream, const FuseArgs* fuse = nullptr) {
   using namespace hq;
   if ((!A_half && !ll.A_ll) || !B || !absmax || !lut16 || (!out_half && !ll.peer_ll))
     return HQ_ERR_NULL_POINTER;
@@ -1013,6 +1135,23 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   prm.absmax_bytes = ((unsigned long long)N * K + blocksize - 1) / blocksize * 4ull;
   prm.a_bytes = (unsigned long long)K * 2;
   prm.out_bytes = (unsigned long long)N * 2;
+  prm.gamma = nullptr;
+  prm.eps = 0.f;
+  prm.act = HQ_ACT_NONE;
+  int units = N;  // what a group of warps walks: rows, or value / gate pairs
+  if (fuse != nullptr) {
+    if (fuse->act != HQ_ACT_NONE && fuse->act != HQ_ACT_SWIGLU && fuse->act != HQ_ACT_GEGLU)
+      return HQ_ERR_BAD_SHAPE;
+    if (fuse->gamma && !aligned16(fuse->gamma)) return HQ_ERR_MISALIGNED;
+    if (fuse->act != HQ_ACT_NONE) {
+      if (N % 2 != 0) return HQ_ERR_BAD_SHAPE;
+      units = N / 2;
+      prm.out_bytes = (unsigned long long)units * 2;
+    }
+    prm.gamma = reinterpret_cast<const __half*>(fuse->gamma);
+    prm.eps = fuse->eps;
+    prm.act = fuse->act;
+  }
 #ifdef HQ_NF4_TRACE
   {
     const char* tp = getenv("HQ_NF4_TRACE_PTR");
@@ -1024,7 +1163,7 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   // 10.1 us against 7.8 us for the register pipeline on an 11008 x 4096 layer.
   // It takes rows of 1024 .. 4096 inputs whose codes and absmax runs start on
   // 16-byte boundaries (one warp per row).
-  if (env_flag("HQ_NF4_BULK") && aligned && nchunks % 32 == 0 && cols <= 4 && aligned16(absmax) &&
+  if (fuse == nullptr && env_flag("HQ_NF4_BULK") && aligned && nchunks % 32 == 0 && cols <= 4 && aligned16(absmax) &&
       ((nchunks >> shift) * 4) % 16 == 0) {
     int rc;
     switch (cols) {
@@ -1038,15 +1177,16 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   // Chunks per lane C and warps per row S = cols / C.  512 threads with up to
   // 128 registers each hold C = 2 chunks of the input vector and D = 4 rows of
   // packed weights in flight per lane.
-  if (aligned && cols == 4) { prm.S = 2; return launch_gemv<2, 4, 2, true, 512>(prm, N, st); }
+#define HQ_NF4_GO(C_, D_, ST_, AL_)                                        \
+  (fuse != nullptr ? launch_gemv<C_, D_, ST_, AL_, 512, true>(prm, units, st) \
+                   : launch_gemv<C_, D_, ST_, AL_, 512, false>(prm, units, st))
+  if (aligned && cols == 4) { prm.S = 2; return HQ_NF4_GO(2, 4, 2, true); }
   int C = cols <= 1 ? 1 : (cols <= 32 ? 2 : 4);
   prm.S = (cols + C - 1) / C;
-  if (C == 1) return aligned ? launch_gemv<1, 4, 1, true, 512>(prm, N, st)
-                             : launch_gemv<1, 4, 1, false, 512>(prm, N, st);
-  if (C == 2) return aligned ? launch_gemv<2, 4, 0, true, 512>(prm, N, st)
-                             : launch_gemv<2, 4, 0, false, 512>(prm, N, st);
-  return aligned ? launch_gemv<4, 2, 0, true, 512>(prm, N, st)
-                 : launch_gemv<4, 2, 0, false, 512>(prm, N, st);
+  if (C == 1) return aligned ? HQ_NF4_GO(1, 4, 1, true) : HQ_NF4_GO(1, 4, 1, false);
+  if (C == 2) return aligned ? HQ_NF4_GO(2, 4, 0, true) : HQ_NF4_GO(2, 4, 0, false);
+  return aligned ? HQ_NF4_GO(4, 2, 0, true) : HQ_NF4_GO(4, 2, 0, false);
+#undef HQ_NF4_GO
 }
 
 extern "C" {
@@ -1130,6 +1270,19 @@ int hq_nf4_gemv_f16(const void* A_half, const uint8_t* B, const float* absmax, c
                     void* out_half, int N, int K, int blocksize, int flags, hq_stream_t stream) {
   return nf4_gemv_impl(A_half, B, absmax, lut16, out_half, N, K, blocksize, flags, LlArgs(),
                        stream);
+}
+
+int hq_gemv_fused_nf4_f16(const void* x_half, const void* gamma_half, float eps, const uint8_t* B,
+                          const float* absmax, const float* lut16, void* out_half, int rows_out,
+                          int n, int blocksize, int flags, int act, hq_stream_t stream) {
+  if (rows_out <= 0 || rows_out > (1 << 30)) return HQ_ERR_BAD_SHAPE;
+  FuseArgs fuse;
+  fuse.gamma = gamma_half;
+  fuse.eps = eps;
+  fuse.act = act;
+  const int rows = act != HQ_ACT_NONE ? 2 * rows_out : rows_out;
+  return nf4_gemv_impl(x_half, B, absmax, lut16, out_half, rows, n, blocksize, flags, LlArgs(),
+                       stream, &fuse);
 }
 
 int hq_nf4_gemv_f16_ll(const void* A_half, const hq_ll_packet* A_ll, long long a_stride,

@@ -350,6 +350,41 @@ int hq_gemv_int8_f16(const int8_t* mat, const void* vec_half, void* res_half, in
 int hq_gemv_int4_f16(const uint8_t* mat, const void* vec_half, void* res_half, int rows, int n,
                      float scale, float zero_point, hq_stream_t stream);
 
+/* ---------------- RMSNorm -> mat-vec -> gated activation, fused ---------------- */
+
+/* The entry of a decode-time MLP in one launch: RMSNorm of the input vector
+ * (src/rmsnorm-cuda/reference.h:4-25: xn[k] = x[k] * rsqrt(mean(x^2) + eps) *
+ * gamma[k], computed in fp32 and rounded to fp16; gamma_half == NULL skips it),
+ * the weight-only mat-vec in one of the four formats above, and the gated
+ * activation of row pairs.  With act != HQ_ACT_NONE the matrix has 2 * rows_out
+ * rows: row 2m is the value row and row 2m + 1 the gate row of output m (the
+ * x / gate order of src/geglu-cuda/reference.h:8-16, per output feature) and
+ *   out[m] = v * g / (1 + exp(-g))                  HQ_ACT_SWIGLU (src/swish-cuda/reference.h:4)
+ *   out[m] = v * 0.5 * g * (1 + erf(g / sqrt(2)))   HQ_ACT_GEGLU  (src/geglu-cuda/reference.h:1-5)
+ * in fp32, rounded to fp16 once; with HQ_ACT_NONE the matrix has rows_out rows
+ * and the call is the plain mat-vec of the normalised vector.  Layouts, scale /
+ * zero point / absmax / level-table rules, alignment and length limits are those
+ * of hq_gemv_f16, hq_gemv_int8_f16, hq_gemv_int4_f16 and hq_nf4_gemv_f16 (NF4:
+ * B is the row-major matrix of 2 * rows_out (or rows_out) rows of n codes, n
+ * takes the place of K, flags are HQ_NF4_LOW_NIBBLE_FIRST and
+ * HQ_NF4_WEIGHTS_RESIDENT).
+ * No counterpart in the reference tree, which has the three steps as separate
+ * benchmarks. */
+#define HQ_ACT_NONE 0
+#define HQ_ACT_SWIGLU 1
+#define HQ_ACT_GEGLU 2
+int hq_gemv_fused_f16(const void* x_half, const void* gamma_half, float eps, const void* mat_half,
+                      void* out_half, int rows_out, int n, int act, hq_stream_t stream);
+int hq_gemv_fused_int8_f16(const void* x_half, const void* gamma_half, float eps, const int8_t* mat,
+                           void* out_half, int rows_out, int n, float scale, float zero_point,
+                           int act, hq_stream_t stream);
+int hq_gemv_fused_int4_f16(const void* x_half, const void* gamma_half, float eps,
+                           const uint8_t* mat, void* out_half, int rows_out, int n, float scale,
+                           float zero_point, int act, hq_stream_t stream);
+int hq_gemv_fused_nf4_f16(const void* x_half, const void* gamma_half, float eps, const uint8_t* B,
+                          const float* absmax, const float* lut16, void* out_half, int rows_out,
+                          int n, int blocksize, int flags, int act, hq_stream_t stream);
+
 /* ---------------- batched dequant-GEMM (tensor cores) ---------------- */
 
 /* Y[Mb][N] = X[Mb][K] * W[K][N] with W the GPTQ 3-bit layout of quant3MatMul

@@ -47,13 +47,15 @@ def build_oracle(force: bool = False) -> Path:
 
 
 def build_ref_cpu(force: bool = False):
-    """The reference's CPU code of the path: quantBnB-omp/main.cpp and the host
-    reference loops of quantVLLM-cuda/reference.h."""
+    """The reference's CPU code of the path: quantBnB-omp/main.cpp, the host
+    reference loops of quantVLLM-cuda/reference.h, and those of rmsnorm-cuda,
+    geglu-cuda and swish-cuda (the operators fused around the mat-vec)."""
     out = HERE / "_ref" / "libref_cpu.so"
     if not (REF / "src" / "quantBnB-omp" / "main.cpp").exists():
         return out if out.exists() else None
     # each harness sees only its own benchmark's directory (both have a utils.h)
-    parts = {"ref_cpu.cpp": ["quantBnB-omp", "quantBnB-cuda"], "ref_cpu_vllm.cpp": ["quantVLLM-cuda"]}
+    parts = {"ref_cpu.cpp": ["quantBnB-omp", "quantBnB-cuda"], "ref_cpu_vllm.cpp": ["quantVLLM-cuda"],
+             "ref_cpu_fused.cpp": ["."]}  # rmsnorm-cuda, geglu-cuda, swish-cuda by path
     if force or _stale(out, [HERE / p for p in parts]):
         out.parent.mkdir(exist_ok=True)
         cuda_inc = Path(NVCC).resolve().parent.parent / "include"

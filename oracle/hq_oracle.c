@@ -659,6 +659,64 @@ void orc_gemv_uniform_f64(const void* mat, const uint16_t* vec, double* out, int
   }
 }
 
+/* ------------------------------------------------------------------------
+ * RMSNorm -> weight-only mat-vec -> gated activation, in fp64.  Restates
+ * rmsnorm-cuda/reference.h:4-25 (xn = x * 1/sqrt(mean(x^2) + eps) * gamma; no
+ * rounding of xn here), the mat-vec of the format (fmt 16 / 8 / 4 as
+ * orc_gemv_uniform_f64, fmt 40 = NF4 as orc_nf4_gemv_f64) and, for act != 0,
+ * the pairing of geglu-cuda/reference.h:8-16 per output feature (row 2m the
+ * value, row 2m + 1 the gate) with act 1: v * g / (1 + exp(-g))
+ * (swish-cuda/reference.h:4), act 2: v * 0.5 * g * (1 + erf(g / sqrt 2))
+ * (geglu-cuda/reference.h:1-5).  gamma == NULL: no normalisation.
+ * ------------------------------------------------------------------------ */
+void orc_gemv_fused_f64(int fmt, const void* mat, const float* absmax, const float* lut16,
+                        int low_first, int blocksize, const uint16_t* x, const uint16_t* gamma,
+                        double eps, double* out, int rows_out, int n, int act, uint16_t scale_h,
+                        uint16_t zero_h) {
+  double* xn = (double*)malloc((size_t)n * sizeof(double));
+  double ms = 0.0;
+  for (int k = 0; k < n; k++) {
+    const double v = (double)orc_h2f(x[k]);
+    ms += v * v;
+  }
+  const double s = gamma ? 1.0 / sqrt(ms / n + eps) : 1.0;
+  for (int k = 0; k < n; k++)
+    xn[k] = (double)orc_h2f(x[k]) * s * (gamma ? (double)orc_h2f(gamma[k]) : 1.0);
+  const float scale = orc_h2f(scale_h), zp = orc_h2f(zero_h);
+  const int rows_mat = act ? 2 * rows_out : rows_out;
+  double* y = (double*)malloc((size_t)rows_mat * sizeof(double));
+#pragma omp parallel for
+  for (int r = 0; r < rows_mat; r++) {
+    double acc = 0.0;
+    for (int j = 0; j < n; j++) {
+      float w;
+      if (fmt == 16) {
+        w = orc_h2f(((const uint16_t*)mat)[(size_t)r * n + j]);
+      } else if (fmt == 8) {
+        w = ((float)((const int8_t*)mat)[(size_t)r * n + j] - zp) * scale;
+      } else if (fmt == 4) {
+        const uint8_t b = ((const uint8_t*)mat)[(size_t)r * (n / 2) + j / 2];
+        w = ((float)((j & 1) ? (b >> 4) : (b & 15)) - zp) * scale;
+      } else {
+        const size_t e = (size_t)r * n + j;
+        w = lut16[nf4_code((const uint8_t*)mat, e, low_first)] * absmax[e / (size_t)blocksize];
+      }
+      acc += (double)w * xn[j];
+    }
+    y[r] = acc;
+  }
+  for (int m = 0; m < rows_out; m++) {
+    if (!act) {
+      out[m] = y[m];
+    } else {
+      const double v = y[2 * m], g = y[2 * m + 1];
+      out[m] = act == 1 ? v * g / (1.0 + exp(-g)) : v * 0.5 * g * (1.0 + erf(g * 0.70710678118654752440));
+    }
+  }
+  free(y);
+  free(xn);
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -256,6 +256,63 @@ def gemv_uniform_f64(mat, vec, bits: int, scale: float = 1.0, zero_point: float 
     return out
 
 
+def gemv_fused_f64(fmt: str, mat, x, gamma, eps: float, rows_out: int, act: int = 0, scale: float = 1.0,
+                   zero_point: float = 0.0, absmax=None, lut16=None, blocksize: int = 64,
+                   low_first: int = 0) -> np.ndarray:
+    """fp64 truth of RMSNorm -> mat-vec -> gated activation (rmsnorm-cuda,
+    geglu-cuda and swish-cuda host references around the format's mat-vec).
+    fmt: "f16", "int8", "int4" or "nf4"; gamma None = no normalisation; act 0
+    none, 1 SwiGLU, 2 GeGLU (then mat has 2 * rows_out rows, value / gate
+    interleaved)."""
+    code = {"f16": 16, "int8": 8, "int4": 4, "nf4": 40}[fmt]
+    dt = {16: np.uint16, 8: np.int8, 4: np.uint8, 40: np.uint8}[code]
+    mat = _c(mat.view(np.uint16) if mat.dtype == np.float16 else mat, dt)
+    x = _c(x, np.uint16)
+    n = x.size
+    out = np.empty(rows_out, dtype=np.float64)
+    g = None if gamma is None else _c(gamma, np.uint16)
+    am = None if absmax is None else _c(absmax, np.float32)
+    lt = None if lut16 is None else _c(lut16, np.float32)
+    sh = int(np.float16(scale).view(np.uint16))
+    zh = int(np.float16(zero_point).view(np.uint16))
+    lib().orc_gemv_fused_f64(C.c_int(code), _ptr(mat), None if am is None else _ptr(am),
+                             None if lt is None else _ptr(lt), C.c_int(low_first),
+                             C.c_int(blocksize), _ptr(x), None if g is None else _ptr(g),
+                             C.c_double(eps), _ptr(out), C.c_int(rows_out), C.c_int(n),
+                             C.c_int(act), C.c_uint16(sh), C.c_uint16(zh))
+    return out
+
+
+def ref_fused_f32(W, x, gamma, rows_out: int, act: int):
+    """RMSNorm -> W @ xn -> gated activation where the three operators are the
+    reference's own host checks (oracle/_ref: rmsnorm_forward_cpu, geglu_reference,
+    swish reference; eps fixed at 1e-5) and only the product between them is numpy
+    (fp64, rounded to fp32).  W: dequantized fp32 weights [rows][n].  None if the
+    reference build is absent."""
+    r = ref_cpu()
+    if r is None or not hasattr(r, "ref_rmsnorm_f32"):
+        return None
+    W = np.asarray(W, dtype=np.float32)
+    xf = _c(np.asarray(x, dtype=np.float32), np.float32)
+    n = xf.size
+    xn = xf
+    if gamma is not None:
+        g = _c(np.asarray(gamma, dtype=np.float32), np.float32)
+        xn = np.empty(n, dtype=np.float32)
+        r.ref_rmsnorm_f32(_ptr(xn), _ptr(xf), _ptr(g), C.c_int64(1), C.c_int64(n))
+    y = _c((W.astype(np.float64) @ xn.astype(np.float64)).astype(np.float32), np.float32)
+    if act == 0:
+        return y
+    out = np.empty(rows_out, dtype=np.float32)
+    if act == 2:
+        r.ref_geglu_f32(_ptr(out), _ptr(y), C.c_int(rows_out), C.c_int(1))
+        return out
+    gate = _c(y[1::2], np.float32)
+    sw = np.empty(rows_out, dtype=np.float32)
+    r.ref_swish_f32(_ptr(gate), _ptr(sw), C.c_int(rows_out))
+    return y[0::2] * sw
+
+
 # ---------------- lut-gemm ----------------
 
 def lutgemm_dequant_f32(bW, alpha, q_bias, M, K, nb, group_size) -> np.ndarray:

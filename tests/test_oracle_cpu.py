@@ -314,3 +314,60 @@ def test_gemv_uniform_oracle_against_numpy(oracle):
             w = mat.astype(np.float32)
         assert np.array_equal(y, w.astype(np.float64) @ vec.astype(np.float64)) or \
             np.allclose(y, w.astype(np.float64) @ vec.astype(np.float64), rtol=1e-13, atol=0)
+
+
+def _fused_dequant(fmt, mat, kw, rows, n):
+    """fp32 weights of a fused-case matrix, in numpy."""
+    if fmt == "f16":
+        return mat.astype(np.float32)
+    if fmt == "nf4":
+        codes = np.empty(rows * n, np.uint8)
+        flat = mat.reshape(-1)
+        codes[0::2], codes[1::2] = flat >> 4, flat & 15   # element 2j in the high nibble
+        return (kw["lut16"][codes] * np.repeat(kw["absmax"], kw["blocksize"])).reshape(rows, n)
+    s, z = np.float32(np.float16(kw["scale"])), np.float32(np.float16(kw["zero_point"]))
+    if fmt == "int8":
+        return (mat.astype(np.float32) - z) * s
+    w = np.empty((rows, n), np.float32)
+    w[:, 0::2], w[:, 1::2] = mat & 15, mat >> 4
+    return (w - z) * s
+
+
+@pytest.mark.parametrize("fmt", ["f16", "int8", "int4", "nf4"])
+@pytest.mark.parametrize("act", [0, 1, 2])
+@pytest.mark.parametrize("norm", [True, False])
+def test_gemv_fused_oracle_against_reference_operators(oracle, fmt, act, norm):
+    """The C restatement of RMSNorm -> mat-vec -> SwiGLU / GeGLU (fp64) against
+    (a) the same arithmetic in numpy fp64 and (b) the reference's own host checks
+    of the three operators (rmsnorm-cuda, geglu-cuda, swish-cuda; fp32) around a
+    numpy product, when the reference build is present."""
+    from math import erf
+    from hecbench_b200 import synth
+    rows_out, n = 24, 128
+    rows = rows_out * (2 if act else 1)
+    rng = np.random.default_rng(11 + act)
+    x = rng.standard_normal(n).astype(np.float16)
+    gamma = rng.uniform(0.5, 1.5, n).astype(np.float16) if norm else None
+    kw = {}
+    if fmt == "nf4":
+        _, B, absmax, lut = synth.nf4_case(rows, n, 64, 5)
+        mat, kw = B.reshape(rows, n // 2), dict(absmax=absmax, lut16=lut, blocksize=64)
+    else:
+        mat, _ = synth.gemv_uniform_case(rows, n, {"f16": 16, "int8": 8, "int4": 4}[fmt], 5)
+        if fmt != "f16":
+            kw = dict(scale=0.05, zero_point=3.5)
+    y = oracle.gemv_fused_f64(fmt, mat, x, gamma, 1e-5, rows_out, act, **kw)
+    W = _fused_dequant(fmt, mat, kw, rows, n)
+    xd = x.astype(np.float64)
+    if norm:
+        xd = xd / np.sqrt(np.mean(xd * xd) + 1e-5) * gamma.astype(np.float64)
+    t = W.astype(np.float64) @ xd
+    if act == 1:
+        t = t[0::2] * t[1::2] / (1.0 + np.exp(-t[1::2]))
+    elif act == 2:
+        t = t[0::2] * 0.5 * t[1::2] * (1.0 + np.array([erf(g / np.sqrt(2.0)) for g in t[1::2]]))
+    assert np.allclose(y, t, rtol=1e-12, atol=1e-12)
+    ref = oracle.ref_fused_f32(W, x, gamma, rows_out, act)
+    if ref is None:
+        pytest.skip("reference host operators not built")
+    assert np.allclose(y, ref.astype(np.float64), rtol=2e-5, atol=2e-5 * np.abs(y).max())
