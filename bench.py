@@ -170,6 +170,27 @@ def _host_case(name: str, seed: int, Mb: int = 64):
                     bytes=nbytes + 4 * n + 2 * rows_out,
                     desc=f"RMSNorm -> {fmt} up/gate mat-vec [{2 * rows_out}x{n}] -> SwiGLU, one "
                          "launch (Llama-3-8B MLP entry, batch 1)")
+    if name in ("mxfp4_qdq_f16", "mxfp4_quantize_f16"):
+        numel = 1 << 26  # 128 MB of fp16 per launch (the reference's own run has 2^29 elements)
+        x = (synth._rng(seed, 80).standard_normal(numel, dtype=np.float32) * 3).astype(np.float16)
+        pack = name == "mxfp4_quantize_f16"
+        return dict(numel=numel, x=x, pack=pack,
+                    bytes=numel * 2 + (numel // 2 + numel // 32 if pack else numel * 2),
+                    desc=f"MXFP4 {'packer' if pack else 'quantize-dequantize'} of {numel} fp16 values "
+                         "(mxfp4-cuda)")
+    if name == "nf4_quantize":
+        N, K, bs = 11008, 4096, 64
+        W = (synth._rng(seed, 83).standard_normal(N * K, dtype=np.float32) * 0.02).astype(np.float16)
+        return dict(n=N * K, bs=bs, W=W, lut=synth.nf4_levels(seed),
+                    bytes=N * K * 2 + N * K // 2 + N * K // bs * 4,
+                    desc="blockwise 4-bit quantizer, 11008x4096 fp16 weights, blocksize 64")
+    if name == "zero_point":
+        size = 1 << 24  # the reference's own run has 10^7 channels
+        lo = synth._rng(seed, 81).uniform(-1, 1, size).astype(np.float32)
+        hi = synth._rng(seed, 82).uniform(-1, 1, size).astype(np.float32)
+        return dict(size=size, lo=lo, hi=hi, bytes=size * 16,
+                    desc=f"scale / zero point of {size} channels from min / max, int8 symmetric "
+                         "(zeropoint-cuda)")
     if name in ("qgemm_q3", "qgemm_q3_down"):
         K, N = (28672, 8192) if name.endswith("down") else (8192, 28672)
         G = K // 128
@@ -203,12 +224,17 @@ WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "q3_gemv_f
              "qgemm_q3", "qgemm_nf4", "qgemm_q3_down", "qgemm_nf4_down",
              "vllm_static_f16", "vllm_dynamic_f16", "vllm_dynamic_azp_f16",
              "gemv_int8", "gemv_int4", "fused_nf4_swiglu", "fused_int8_swiglu",
-             "fused_int4_swiglu"]
+             "fused_int4_swiglu", "mxfp4_qdq_f16", "mxfp4_quantize_f16", "zero_point",
+             "nf4_quantize"]
 
 
 def dtype_of(name: str) -> str:
     if name.startswith("vllm"):
         return "i8"
+    if name.startswith("mxfp4"):
+        return "fp4"
+    if name == "zero_point":
+        return "f64"
     return "f32" if name.startswith("q3_gemv_f32") else ("u8" if name == "bnb_quantize" else "f16")
 
 
@@ -293,6 +319,21 @@ class DeviceWorkload:
             self.x = [t(c["x"]) for _ in range(R)]
             self.out = [torch.empty(c["rows_out"], dtype=torch.float16, device=dev)
                         for _ in range(R)]
+        elif name.startswith("mxfp4"):
+            self.xin = [t(rot(c["x"], i)) for i in range(R)]
+            self.y = torch.empty(c["numel"], dtype=torch.float16, device=dev)
+            self.codes = torch.empty(c["numel"] // 2, dtype=torch.uint8, device=dev)
+            self.scales8 = torch.empty(c["numel"] // 32, dtype=torch.uint8, device=dev)
+        elif name == "nf4_quantize":
+            self.W = [t(rot(c["W"], i)) for i in range(R)]
+            self.lut = t(c["lut"])
+            self.B = torch.empty(c["n"] // 2, dtype=torch.uint8, device=dev)
+            self.absmax = torch.empty(c["n"] // c["bs"], dtype=torch.float32, device=dev)
+        elif name == "zero_point":
+            self.lo = [t(rot(c["lo"], i)) for i in range(R)]
+            self.hi = [t(rot(c["hi"], i)) for i in range(R)]
+            self.sc = torch.empty(c["size"], dtype=torch.float32, device=dev)
+            self.zp = torch.empty(c["size"], dtype=torch.int32, device=dev)
         elif name.startswith("vllm"):
             self.xin = [t(rot(c["x"], i)) for i in range(R)]
             self.q = torch.empty((c["tokens"], c["hidden"]), dtype=torch.int8, device=dev)
@@ -339,6 +380,14 @@ class DeviceWorkload:
                 kw["weights_resident"] = pdl
             hq.gemv_fused(c["fmt"], self.x[i], self.mat[i], c["rows_out"], gamma=self.gamma,
                           eps=1e-5, act=hq.ACT_SWIGLU, out=self.out[i], **kw)
+        elif n == "mxfp4_qdq_f16":
+            hq.mxfp4(self.y, self.xin[i], c["numel"])
+        elif n == "mxfp4_quantize_f16":
+            hq.mxfp4_quantize(self.xin[i], self.codes, self.scales8)
+        elif n == "nf4_quantize":
+            hq.quantize_nf4(self.W[i], self.lut, c["bs"], 0, self.B, self.absmax)
+        elif n == "zero_point":
+            hq.zero_point(self.lo[i], self.hi[i], -127, 127, c["size"], True, self.sc, self.zp)
         elif n == "vllm_static_f16":
             hq.static_scaled_int8_quant(self.q, self.xin[i], c["hidden"], c["tokens"], 0.1, 0)
         elif n.startswith("vllm_dynamic"):

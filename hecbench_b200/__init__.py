@@ -25,6 +25,11 @@ from .api import (  # noqa: F401
     ACT_SWIGLU,
     gemv_fp16,
     gemv_fused,
+    mxfp4,
+    mxfp4_dequantize,
+    mxfp4_quantize,
+    quantize_nf4,
+    zero_point,
     gemv_int4_quantized,
     gemv_int8_quantized,
     gemv_nf4,
@@ -48,5 +53,6 @@ __all__ = [
     "static_scaled_int8_quant", "dynamic_scaled_int8_quant",
     "gemv_fp16", "gemv_int8_quantized", "gemv_int4_quantized",
     "gemv_fused", "ACT_NONE", "ACT_SWIGLU", "ACT_GEGLU",
+    "zero_point", "mxfp4", "mxfp4_quantize", "mxfp4_dequantize", "quantize_nf4",
     "NF4_HIGH_NIBBLE_FIRST", "NF4_LOW_NIBBLE_FIRST", "NF4_WEIGHTS_RESIDENT",
 ]

@@ -77,6 +77,13 @@ SIGNATURES = {
                                        c_int, C.c_float, C.c_float, c_int, c_void_p]),
     "hq_gemv_fused_nf4_f16": (c_int, [c_void_p, c_void_p, C.c_float] + [c_void_p] * 4 +
                               [c_int] * 5 + [c_void_p]),
+    "hq_zero_point": (c_int, [c_void_p, c_void_p, C.c_int32, C.c_int32, c_int, c_int, c_void_p,
+                              c_void_p, c_void_p]),
+    "hq_nf4_quantize": (c_int, [c_void_p, c_int, c_size_t, c_int, c_void_p, c_int, c_void_p,
+                                c_void_p, c_void_p]),
+    "hq_mxfp4_qdq": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "hq_mxfp4_quantize": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "hq_mxfp4_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "hq_aqlm_2x8_matvec": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p, c_void_p]),
 }
 

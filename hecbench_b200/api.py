@@ -243,6 +243,104 @@ def gemv_int4_quantized(mat, vec, scale: float, zero_point: float,
 
 
 # --------------------------------------------------------------------------
+# quantization parameters and packers
+# --------------------------------------------------------------------------
+
+def zero_point(x_min, x_max, qmin: int, qmax: int, size: int, preserve_sparsity: bool, scale,
+               zero_point_out) -> None:
+    """zero_point<<<...>>>(x_min, x_max, qmin, qmax, size, preserve_sparsity, scale,
+    zero_point) (zeropoint-cuda/main.cu:10-18): fp32 scale and int32 zero point of
+    every channel from its minimum and maximum."""
+    lib = load_library()
+    if min(x_min.numel(), x_max.numel(), scale.numel(), zero_point_out.numel()) < size:
+        raise ValueError("a tensor is shorter than size")
+    with torch.cuda.device(x_min.device):
+        check("hq_zero_point", lib.hq_zero_point(
+            _dev(x_min, torch.float32, "x_min"), _dev(x_max, torch.float32, "x_max"), int(qmin),
+            int(qmax), int(size), int(bool(preserve_sparsity)), _dev(scale, torch.float32, "scale"),
+            _dev(zero_point_out, torch.int32, "zero_point"), _stream()))
+
+
+def quantize_nf4(W, lut16, blocksize: int = 64, nibble_order: int = NF4_HIGH_NIBBLE_FIRST,
+                 B=None, absmax=None):
+    """Blockwise 4-bit quantizer (the inverse of dequantize_nf4; no counterpart in
+    the reference tree): W float16 / bfloat16 / float32 -> (B uint8[n / 2], absmax
+    float32[n / blocksize]); code = the nearest of the 16 ascending levels lut16 to
+    w / absmax, a tie going to the lower level."""
+    lib = load_library()
+    code = _VLLM_DTYPE.get(W.dtype)
+    if code is None:
+        raise TypeError("W must be float16, bfloat16 or float32")
+    if not W.is_cuda or not W.is_contiguous():
+        raise ValueError("W must be a contiguous CUDA tensor")
+    n = W.numel()
+    if B is None:
+        B = torch.empty(n // 2, dtype=torch.uint8, device=W.device)
+    if absmax is None:
+        absmax = torch.empty(n // blocksize, dtype=torch.float32, device=W.device)
+    with torch.cuda.device(W.device):
+        check("hq_nf4_quantize", lib.hq_nf4_quantize(
+            W.data_ptr(), code, n, blocksize, _dev(lut16, torch.float32, "lut16"), nibble_order,
+            _dev(B, torch.uint8, "B"), _dev(absmax, torch.float32, "absmax"), _stream()))
+    return B, absmax
+
+
+_MX_DTYPE = {torch.float16: 0, torch.bfloat16: 1}
+
+
+def _mx_code(t) -> int:
+    if t.dtype not in _MX_DTYPE:
+        raise TypeError("MXFP4 takes float16 or bfloat16 tensors")
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError("tensors must be contiguous CUDA tensors")
+    return _MX_DTYPE[t.dtype]
+
+
+def mxfp4(y, a, numel: int) -> None:
+    """mxfp4<T>(y, a, numel, ...) (mxfp4-cuda/main.cu:152-176, without its timing
+    loop): y = a quantized to MXFP4 and back, groups of 32, T = float16 or
+    bfloat16."""
+    lib = load_library()
+    code = _mx_code(a)
+    if y.dtype != a.dtype or min(y.numel(), a.numel()) < numel:
+        raise ValueError("y and a must have the same type and numel elements")
+    with torch.cuda.device(a.device):
+        check("hq_mxfp4_qdq", lib.hq_mxfp4_qdq(a.data_ptr(), y.data_ptr(), int(numel), code,
+                                               _stream()))
+
+
+def mxfp4_quantize(a, codes=None, scales=None):
+    """Packed MXFP4 of a float16 / bfloat16 tensor: (codes uint8[numel / 2], element
+    2j in the low nibble; scales uint8[numel / 32], E8M0)."""
+    lib = load_library()
+    code = _mx_code(a)
+    n = a.numel()
+    if codes is None:
+        codes = torch.empty(n // 2, dtype=torch.uint8, device=a.device)
+    if scales is None:
+        scales = torch.empty(n // 32, dtype=torch.uint8, device=a.device)
+    with torch.cuda.device(a.device):
+        check("hq_mxfp4_quantize", lib.hq_mxfp4_quantize(
+            a.data_ptr(), _dev(codes, torch.uint8, "codes"), _dev(scales, torch.uint8, "scales"),
+            n, code, _stream()))
+    return codes, scales
+
+
+def mxfp4_dequantize(codes, scales, dtype=torch.float16, out=None):
+    """Values of a packed MXFP4 tensor in float16 or bfloat16."""
+    lib = load_library()
+    n = codes.numel() * 2
+    if out is None:
+        out = torch.empty(n, dtype=dtype, device=codes.device)
+    code = _mx_code(out)
+    with torch.cuda.device(codes.device):
+        check("hq_mxfp4_dequantize", lib.hq_mxfp4_dequantize(
+            _dev(codes, torch.uint8, "codes"), _dev(scales, torch.uint8, "scales"), out.data_ptr(),
+            n, code, _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------
 # RMSNorm -> mat-vec -> gated activation, fused
 # --------------------------------------------------------------------------
 

@@ -385,6 +385,55 @@ int hq_gemv_fused_nf4_f16(const void* x_half, const void* gamma_half, float eps,
                           const float* absmax, const float* lut16, void* out_half, int rows_out,
                           int n, int blocksize, int flags, int act, hq_stream_t stream);
 
+/* ---------------- quantization parameters and packers ---------------- */
+
+/* Scale and zero point of an affine integer quantization from per-channel minima
+ * and maxima: replaces the kernel zero_point of src/zeropoint-cuda/main.cu:10-80
+ * (same argument order; host check src/zeropoint-cuda/reference.h:1-71).  Bit for
+ * bit the reference's results, including its mixed fp32 / fp64 arithmetic: with
+ * preserve_sparsity and min < 0 < max the range is made symmetric first and the
+ * zero point is (qmin + qmax) / 2; the range is widened to contain 0; scale =
+ * (max - min) / (qmax - qmin), or 0.1 where that is 0 or its reciprocal
+ * overflows; the zero point is clamped to [qmin, qmax] and rounded to nearest,
+ * ties to even.  size >= 0, qmax > qmin. */
+int hq_zero_point(const float* x_min, const float* x_max, int32_t qmin, int32_t qmax, int size,
+                  int preserve_sparsity, float* scale, int32_t* zero_point, hq_stream_t stream);
+
+/* Blockwise 4-bit quantizer: produces what hq_nf4_dequant_f16 / hq_nf4_gemv_f16 /
+ * hq_qgemm_nf4_f16 consume.  W: n weights of type dtype (HQ_DTYPE_F16, _BF16 or
+ * _F32); absmax[b] = max |w| over block b of blocksize weights; x = fp32(w) * (1 /
+ * absmax[b]) (0 for a block of zeros); code = how many of the 15 midpoints
+ * (lut16[j] + lut16[j+1]) / 2, formed in fp32 from the 16 ascending levels, are
+ * < x: the nearest level, a tie going to the lower one.  B gets two codes per
+ * byte in the nibble order of flags (HQ_NF4_*_NIBBLE_FIRST).  blocksize a power
+ * of two in 32 .. 4096, n % blocksize == 0, W 16-byte aligned, B 4-byte aligned.
+ * No counterpart in the reference tree (src/quantBnB-cuda/main.cu:13-85 is the
+ * 8-bit whole-tensor quantizer, hq_bnb_quantize_u8 here). */
+int hq_nf4_quantize(const void* W, int dtype, size_t n, int blocksize, const float* lut16,
+                    int flags, uint8_t* B, float* absmax, hq_stream_t stream);
+
+/* MXFP4 (32 consecutive elements share a power-of-two scale, each element is a
+ * 4-bit e2m1 float with values 0, .5, 1, 1.5, 2, 3, 4, 6 and a sign).
+ * hq_mxfp4_qdq replaces qdq_mxfp4_kernel of src/mxfp4-cuda/main.cu:112-150 (out =
+ * the quantized values in the input type; dtype HQ_DTYPE_F16 or HQ_DTYPE_BF16):
+ * per group k = floor(log2(max |x|, rounded up to the next power of two from
+ * 1.75 * 2^e)) - 2, clamped to [-127, 127]; x / 2^k is rounded to the nearest grid
+ * value, ties to the even mantissa, magnitudes above 6 saturate; out = that *
+ * 2^k.  Same bits as the reference kernel for every group whose maximum is
+ * finite and, after that rounding, a normal number of the type; a group with a
+ * smaller maximum (the reference takes the logarithm of zero there) uses the
+ * smallest k the reference can produce, so a group of zeros gives zeros.
+ * hq_mxfp4_quantize writes the packed form instead - codes: one byte per two
+ * elements, element 2j in the low nibble, nibble = sign << 3 | index into the
+ * grid; scales_e8m0: one byte k + 127 per group - and hq_mxfp4_dequantize turns
+ * it back into values (= what hq_mxfp4_qdq gives).  numel % 32 == 0; in / out
+ * 16-byte aligned, codes 4-byte aligned.  No packed form exists in the reference. */
+int hq_mxfp4_qdq(const void* in, void* out, size_t numel, int dtype, hq_stream_t stream);
+int hq_mxfp4_quantize(const void* in, uint8_t* codes, uint8_t* scales_e8m0, size_t numel, int dtype,
+                      hq_stream_t stream);
+int hq_mxfp4_dequantize(const uint8_t* codes, const uint8_t* scales_e8m0, void* out, size_t numel,
+                        int dtype, hq_stream_t stream);
+
 /* ---------------- batched dequant-GEMM (tensor cores) ---------------- */
 
 /* Y[Mb][N] = X[Mb][K] * W[K][N] with W the GPTQ 3-bit layout of quant3MatMul

@@ -49,13 +49,15 @@ def build_oracle(force: bool = False) -> Path:
 def build_ref_cpu(force: bool = False):
     """The reference's CPU code of the path: quantBnB-omp/main.cpp, the host
     reference loops of quantVLLM-cuda/reference.h, and those of rmsnorm-cuda,
-    geglu-cuda and swish-cuda (the operators fused around the mat-vec)."""
+    geglu-cuda and swish-cuda (the operators fused around the mat-vec) and of
+    zeropoint-cuda."""
     out = HERE / "_ref" / "libref_cpu.so"
     if not (REF / "src" / "quantBnB-omp" / "main.cpp").exists():
         return out if out.exists() else None
     # each harness sees only its own benchmark's directory (both have a utils.h)
     parts = {"ref_cpu.cpp": ["quantBnB-omp", "quantBnB-cuda"], "ref_cpu_vllm.cpp": ["quantVLLM-cuda"],
-             "ref_cpu_fused.cpp": ["."]}  # rmsnorm-cuda, geglu-cuda, swish-cuda by path
+             "ref_cpu_fused.cpp": ["."],  # rmsnorm-cuda, geglu-cuda, swish-cuda by path
+             "ref_cpu_zeropoint.cpp": ["zeropoint-cuda"]}
     if force or _stale(out, [HERE / p for p in parts]):
         out.parent.mkdir(exist_ok=True)
         cuda_inc = Path(NVCC).resolve().parent.parent / "include"
@@ -97,6 +99,8 @@ REF_GPU_PARTS = {
     "ref_gpu_lut.cu": ["lut-gemm-cuda"],
     "ref_gpu_aqlm.cu": ["quantAQLM-cuda"],
     "ref_gpu_gemv.cu": ["gemv-cuda"],
+    "ref_gpu_mxfp4.cu": ["mxfp4-cuda"],
+    "ref_gpu_zeropoint.cu": ["zeropoint-cuda"],
 }
 
 

@@ -320,6 +320,35 @@ void orc_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut
     out[e] = orc_f2h(lut16[nf4_code(B, e, low_first)] * absmax[e / (size_t)blocksize]);
 }
 
+/* Blockwise 4-bit quantizer, the inverse of the dequantisation above (no
+ * counterpart in the reference tree): absmax[b] = max |w| over the block, x = w *
+ * (1 / absmax[b]) in fp32 (0 for a block of zeros), code = how many of the 15
+ * midpoints (lut16[j] + lut16[j+1]) / 2 (fp32) are < x - the nearest level, a tie
+ * going to the lower one.  w: the weights widened to fp32 (exact for fp16 / bf16). */
+void orc_nf4_quantize(const float* w, size_t n, int blocksize, const float* lut16, int low_first,
+                      uint8_t* B, float* absmax) {
+  float mid[15];
+  for (int j = 0; j < 15; j++) mid[j] = 0.5f * (lut16[j] + lut16[j + 1]);
+  for (size_t i = 0; i < n / 2; i++) B[i] = 0;
+  for (size_t b = 0; b < n / (size_t)blocksize; b++) {
+    float m = 0.f;
+    for (int j = 0; j < blocksize; j++) {
+      const float a = fabsf(w[b * blocksize + j]);
+      if (a > m) m = a;
+    }
+    absmax[b] = m;
+    const float inv = m > 0.f ? 1.f / m : 0.f;
+    for (int j = 0; j < blocksize; j++) {
+      const size_t e = b * blocksize + j;
+      const float x = w[e] * inv;
+      unsigned code = 0;
+      for (int k = 0; k < 15; k++) code += x > mid[k];
+      const int low = ((e & 1) != 0) ^ (low_first != 0);
+      B[e >> 1] |= (uint8_t)(low ? code : code << 4);
+    }
+  }
+}
+
 /* fp64 truth of the 4-bit GEMV: out[n] = sum_k A[k] * (lut16[c]*absmax) with
  * the weight taken as the exact fp32 product (not rounded to fp16). */
 void orc_nf4_gemv_f64(const uint16_t* A, const uint8_t* B, const float* absmax,
@@ -715,6 +744,167 @@ void orc_gemv_fused_f64(int fmt, const void* mat, const float* absmax, const flo
   }
   free(y);
   free(xn);
+}
+
+/* ------------------------------------------------------------------------
+ * MXFP4 quantize-dequantize (mxfp4-cuda/main.cu:112-150) and its packed form.
+ * T is fp16 (bf16 = 0) or bf16 (bf16 = 1), passed as 16-bit patterns.
+ * ------------------------------------------------------------------------ */
+static inline float orc_bf2f(uint16_t b) {
+  union { uint32_t u; float f; } v;
+  v.u = (uint32_t)b << 16;
+  return v.f;
+}
+static inline uint16_t orc_f2bf(float f) { /* round to nearest even */
+  union { uint32_t u; float f; } v;
+  v.f = f;
+  if ((v.u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((v.u >> 16) | 0x40u);
+  return (uint16_t)((v.u + 0x7fffu + ((v.u >> 16) & 1u)) >> 16);
+}
+static inline float mx_t2f(uint16_t b, int bf16) { return bf16 ? orc_bf2f(b) : orc_h2f(b); }
+static inline uint16_t mx_d2t(double d, int bf16) { return bf16 ? orc_f2bf((float)d) : orc_d2h(d); }
+
+/* One value of T, already divided by the group's scale, rounded to the e2m1
+ * grid and returned in T's encoding: the bit procedure of fp16_to_fp4_simulate
+ * (main.cu:21-109) - E exponent bits, M mantissa bits, bias B.  The rounding
+ * looks at the mantissa bits e2m1 drops (one more per binade below e2m1's
+ * smallest normal, the lowest exponent bit standing in for the implicit one),
+ * goes to the nearer neighbour and on a tie to the even mantissa; results are
+ * clamped to the binades 2^-1 .. 2^2 and magnitudes beyond 6 become 6. */
+static uint16_t mx_round_e2m1(uint16_t bits, int E, int M, int B) {
+  const int exp = (bits >> M) & ((1 << E) - 1);
+  const int sign = (bits >> (M + E)) & 1;
+  const int top = (bits >> (M - 1)) & 1; /* the one mantissa bit e2m1 keeps */
+  const int e4 = exp - B + 1;            /* exponent in e2m1's bias (main.cu:32-33) */
+  const int below = e4 <= 0 ? 1 - e4 : 0;
+  int cut = M - 1 + below;               /* bits the rounding discards (main.cu:39) */
+  if (cut > 16) cut = 16;
+  const uint32_t tail = (bits & ((1u << (M + 1)) - 1u)) & ((1u << cut) - 1u);
+  const uint32_t half = 1u << (cut - 1);
+  int new_exp, new_man;
+  if (tail < half) { /* towards zero (main.cu:68-69) */
+    new_exp = exp;
+    new_man = e4 > 0 ? top : 0;
+  } else if (tail > half) { /* away from zero (main.cu:82-83) */
+    new_exp = exp + ((e4 <= 0 || top) ? 1 : 0);
+    new_man = (e4 > 0 && !top) ? 1 : 0;
+  } else { /* tie: to the even mantissa; .25 goes to 0 (main.cu:93) */
+    new_exp = exp > B - 2 ? exp + top : 0;
+    new_man = 0;
+  }
+  if (new_exp > B + 2 && new_man == 0) new_man = 1; /* main.cu:101 */
+  if (new_exp < B - 2) new_exp = 0;                 /* main.cu:104 */
+  else if (new_exp > B + 2) new_exp = B + 2;
+  return (uint16_t)((sign << 15) | (new_exp << M) | (new_man << (M - 1)));
+}
+
+/* exponent k of the scale of one group from its largest magnitude (T's bits):
+ * mantissa rounded up from 1.75 by adding a quarter of the mantissa range to the
+ * bits and keeping the exponent field (main.cu:127-129), floor(log2) - 2,
+ * clamped to E8M0's range (main.cu:131-135).  A field of 0 (a zero or small
+ * denormal maximum, for which the reference takes log2 of zero) counts as 1,
+ * the smallest field the reference's expression is defined for. */
+static int mx_scale_exponent(uint16_t max_bits, int bf16) {
+  const int M = bf16 ? 7 : 10, B = bf16 ? 127 : 15;
+  int field = (int)(((uint32_t)max_bits + (1u << (M - 2))) >> M);
+  if (field < 1) field = 1;
+  int k = field - B - 2;
+  if (k < -127) k = -127;
+  if (k > 127) k = 127;
+  return k;
+}
+/* the same from T's own bits, as the reference does it; -1000 where the
+ * reference's expression is undefined (log2 of zero) */
+int orc_mxfp4_scale_exponent_ref(uint16_t max_bits, int bf16) {
+  const int M = bf16 ? 7 : 10, E = bf16 ? 8 : 5, B = bf16 ? 127 : 15;
+  const uint32_t r = ((uint32_t)max_bits + (1u << (M - 2))) & (((1u << (E + 1)) - 1u) << M);
+  const int exp = (int)(r >> M) & ((1 << E) - 1);
+  if (exp == 0) return -1000;
+  int k = exp - B - 2;
+  if (k > 127) k = 127;
+  if (k < -127) k = -127;
+  return k;
+}
+int orc_mxfp4_scale_exponent(uint16_t max_bits, int bf16) { return mx_scale_exponent(max_bits, bf16); }
+
+/* out (T) = quantize-dequantize of in; codes / scales (nullable): the packed
+ * form, element 2j in the low nibble, nibble = sign << 3 | grid index, scale
+ * byte = k + 127. */
+void orc_mxfp4(const uint16_t* in, uint16_t* out, uint8_t* codes, uint8_t* scales, size_t numel,
+               int bf16) {
+  const int M = bf16 ? 7 : 10, E = bf16 ? 8 : 5, B = bf16 ? 127 : 15;
+#pragma omp parallel for
+  for (long long g = 0; g < (long long)(numel / 32); g++) {
+    const uint16_t* x = in + (size_t)g * 32;
+    uint16_t mx = 0;
+    for (int j = 0; j < 32; j++) {
+      const uint16_t a = x[j] & 0x7fffu;
+      if (a > mx) mx = a;
+    }
+    const int k = mx_scale_exponent(mx, bf16);
+    if (scales) scales[g] = (uint8_t)(k + 127);
+    for (int j = 0; j < 32; j++) {
+      /* x / scale in T (exact, or a denormal of T, which rounds to 0 below) */
+      const uint16_t a = mx_d2t(ldexp((double)mx_t2f(x[j], bf16), -k), bf16);
+      const uint16_t q = mx_round_e2m1(a, E, M, B);
+      if (out) out[(size_t)g * 32 + j] = mx_d2t(ldexp((double)mx_t2f(q, bf16), k), bf16);
+      if (codes) {
+        const float mag = fabsf(mx_t2f(q, bf16));
+        const int idx = mag < 2.f ? (int)(mag * 2.f) : (mag < 4.f ? (int)mag + 2 : (int)(mag / 2.f) + 4);
+        const uint8_t nib = (uint8_t)(((q >> 15) << 3) | idx);
+        uint8_t* c = codes + ((size_t)g * 32 + j) / 2;
+        if (j & 1) *c = (uint8_t)((*c & 0x0f) | (nib << 4));
+        else *c = (uint8_t)((*c & 0xf0) | nib);
+      }
+    }
+  }
+}
+
+/* packed form -> T */
+void orc_mxfp4_dequant(const uint8_t* codes, const uint8_t* scales, uint16_t* out, size_t numel,
+                       int bf16) {
+  static const float grid[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  for (size_t i = 0; i < numel; i++) {
+    const uint8_t nib = (i & 1) ? (codes[i / 2] >> 4) : (codes[i / 2] & 15);
+    const double v = ldexp((double)grid[nib & 7], (int)scales[i / 32] - 127);
+    out[i] = mx_d2t((nib & 8) ? -v : v, bf16);
+  }
+}
+
+/* ------------------------------------------------------------------------
+ * Scale and zero point per channel from its minimum and maximum: restates
+ * zeropoint-cuda/reference.h:1-71 (the kernel main.cu:10-80 is the same
+ * arithmetic).  The mixed fp32 / fp64 arithmetic is the reference's.
+ * ------------------------------------------------------------------------ */
+void orc_zero_point(const float* x_min, const float* x_max, int32_t qmin, int32_t qmax, int size,
+                    int preserve_sparsity, float* scale, int32_t* zero_point) {
+  const int span = qmax - qmin;
+  const int sym_lo = -(span / 2 + 1), sym_hi = span / 2;
+  for (int i = 0; i < size; i++) {
+    float lo = x_min[i], hi = x_max[i];
+    if (preserve_sparsity && lo < 0 && hi > 0) { /* reference.h:15-22 */
+      const float a = fabsf(lo / (float)sym_lo), b = fabsf(hi / (float)sym_hi);
+      const double m = (double)(a > b ? a : b);
+      lo = (float)(m * (double)sym_lo);
+      hi = (float)(m * (double)sym_hi);
+    }
+    if (!(lo < 0.f)) lo = 0.f; /* reference.h:27-28: the range contains 0 */
+    if (!(hi > 0.f)) hi = 0.f;
+    float sc = (float)(((double)hi - (double)lo) / (double)span); /* reference.h:29 */
+    if (sc == 0.f || isinf(1.f / sc)) sc = 0.1f;                  /* reference.h:33-35 */
+    const double s = (double)sc;
+    const double from_lo = (double)qmin - (double)lo / s, from_hi = (double)qmax - (double)hi / s;
+    const double err_lo = (double)abs(qmin) + fabs((double)lo / s);
+    const double err_hi = (double)abs(qmax) + fabs((double)hi / s);
+    double z = err_lo < err_hi ? from_lo : from_hi; /* reference.h:37-46 */
+    if (preserve_sparsity && lo < 0 && hi > 0) z = (double)(qmin + qmax) / 2.0; /* :52-54 */
+    int32_t nudged;
+    if (z < (double)qmin) nudged = qmin;
+    else if (z > (double)qmax) nudged = qmax;
+    else nudged = (int32_t)nearbyint(z); /* reference.h:60-67 */
+    scale[i] = sc;
+    zero_point[i] = nudged;
+  }
 }
 
 int orc_num_threads(void) {

@@ -313,6 +313,77 @@ def ref_fused_f32(W, x, gamma, rows_out: int, act: int):
     return y[0::2] * sw
 
 
+def nf4_quantize(w, blocksize: int, lut16, low_first: int = 0):
+    """(codes uint8[n / 2], absmax fp32[n / blocksize]) of fp32-widened weights."""
+    w = _c(np.asarray(w, dtype=np.float32).reshape(-1), np.float32)
+    lut16 = _c(lut16, np.float32)
+    B = np.empty(w.size // 2, dtype=np.uint8)
+    absmax = np.empty(w.size // blocksize, dtype=np.float32)
+    lib().orc_nf4_quantize(_ptr(w), C.c_size_t(w.size), C.c_int(blocksize), _ptr(lut16),
+                           C.c_int(low_first), _ptr(B), _ptr(absmax))
+    return B, absmax
+
+
+# ---------------- zero point ----------------
+
+def _zero_point(fn, x_min, x_max, qmin, qmax, preserve_sparsity):
+    x_min, x_max = _c(x_min, np.float32), _c(x_max, np.float32)
+    scale = np.empty(x_min.size, dtype=np.float32)
+    zp = np.empty(x_min.size, dtype=np.int32)
+    fn(_ptr(x_min), _ptr(x_max), C.c_int32(qmin), C.c_int32(qmax), C.c_int(x_min.size),
+       C.c_int(int(preserve_sparsity)), _ptr(scale), _ptr(zp))
+    return scale, zp
+
+
+def zero_point(x_min, x_max, qmin: int, qmax: int, preserve_sparsity: bool):
+    """(scale fp32, zero point int32) per channel: the C restatement."""
+    return _zero_point(lib().orc_zero_point, x_min, x_max, qmin, qmax, preserve_sparsity)
+
+
+def ref_zero_point(x_min, x_max, qmin: int, qmax: int, preserve_sparsity: bool):
+    """The same from the reference's own host function (None if it was never built)."""
+    r = ref_cpu()
+    if r is None or not hasattr(r, "ref_zero_point"):
+        return None
+    return _zero_point(r.ref_zero_point, x_min, x_max, qmin, qmax, preserve_sparsity)
+
+
+# ---------------- MXFP4 ----------------
+
+def mxfp4_qdq(x_bits, bf16: bool = False) -> np.ndarray:
+    """Quantize-dequantize of 16-bit patterns of fp16 (or bf16) values, groups of 32."""
+    x = _c(x_bits, np.uint16).reshape(-1)
+    out = np.empty_like(x)
+    lib().orc_mxfp4(_ptr(x), _ptr(out), None, None, C.c_size_t(x.size), C.c_int(int(bf16)))
+    return out
+
+
+def mxfp4_quantize(x_bits, bf16: bool = False):
+    """(codes uint8[n/2], scales uint8[n/32]) of the packed form."""
+    x = _c(x_bits, np.uint16).reshape(-1)
+    codes = np.zeros(x.size // 2, dtype=np.uint8)
+    scales = np.zeros(x.size // 32, dtype=np.uint8)
+    lib().orc_mxfp4(_ptr(x), None, _ptr(codes), _ptr(scales), C.c_size_t(x.size),
+                    C.c_int(int(bf16)))
+    return codes, scales
+
+
+def mxfp4_dequantize(codes, scales, bf16: bool = False) -> np.ndarray:
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint8)
+    out = np.empty(codes.size * 2, dtype=np.uint16)
+    lib().orc_mxfp4_dequant(_ptr(codes), _ptr(scales), _ptr(out), C.c_size_t(out.size),
+                            C.c_int(int(bf16)))
+    return out
+
+
+def mxfp4_scale_exponents(max_bits: int, bf16: bool = False):
+    """(exponent used here, exponent by the reference's expression or None where
+    that is undefined)."""
+    ours = int(lib().orc_mxfp4_scale_exponent(C.c_uint16(max_bits), C.c_int(int(bf16))))
+    ref = int(lib().orc_mxfp4_scale_exponent_ref(C.c_uint16(max_bits), C.c_int(int(bf16))))
+    return ours, (None if ref == -1000 else ref)
+
+
 # ---------------- lut-gemm ----------------
 
 def lutgemm_dequant_f32(bW, alpha, q_bias, M, K, nb, group_size) -> np.ndarray:

@@ -36,6 +36,9 @@ void ref_gemv_int8(int8_t* mat, void* vec_half, void* res_half, unsigned size, f
                    float zero_point_f, unsigned bx, unsigned by);
 void ref_gemv_int4(uint8_t* mat, void* vec_half, void* res_half, unsigned size, float scale_f,
                    float zero_point_f, unsigned bx, unsigned by);
+int ref_mxfp4_qdq(const void* in, void* out, int numel, int bf16);
+int ref_zero_point_gpu(const float* x_min, const float* x_max, int32_t qmin, int32_t qmax, int size,
+                       int preserve_sparsity, float* scale, int32_t* zp);
 }
 
 #define CK(x)                                                                          \
@@ -240,6 +243,30 @@ int main(int argc, char** argv) {
       if (r.us < best.us) best = r;
     }
     emit(bits == 8 ? "gemv_int8" : "gemv_int4", best);
+    free_all();
+  }
+  {  // MXFP4 quantize-dequantize, 2^26 fp16 values per launch (128 MB in, 128 MB out)
+    const int numel = 1 << 26;
+    const int R = replicas_for((double)numel * 2, target);
+    std::vector<void*> xs(R);
+    for (int i = 0; i < R; i++) xs[i] = filled(numel, 2, -6.f, 6.f, 600 + i);
+    void* out = dmalloc((size_t)numel * 2);
+    emit("mxfp4_qdq_f16", time_launches(R, 20, [&](int i) { ref_mxfp4_qdq(xs[i], out, numel, 0); }));
+    free_all();
+  }
+  {  // zero point, 2^24 channels (the driver's own run has 10^7, zeropoint-cuda/Makefile:56)
+    const int size = 1 << 24;
+    const int R = replicas_for((double)size * 8, target);
+    std::vector<void*> lo(R), hi(R);
+    for (int i = 0; i < R; i++) {
+      lo[i] = filled(size, 1, -1.f, 1.f, 700 + i);
+      hi[i] = filled(size, 1, -1.f, 1.f, 800 + i);
+    }
+    float* sc = (float*)dmalloc((size_t)size * 4);
+    int32_t* zp = (int32_t*)dmalloc((size_t)size * 4);
+    emit("zero_point", time_launches(R, 20, [&](int i) {
+           ref_zero_point_gpu((float*)lo[i], (float*)hi[i], -127, 127, size, 1, sc, zp);
+         }));
     free_all();
   }
   printf("}\n");

@@ -371,3 +371,141 @@ def test_gemv_fused_oracle_against_reference_operators(oracle, fmt, act, norm):
     if ref is None:
         pytest.skip("reference host operators not built")
     assert np.allclose(y, ref.astype(np.float64), rtol=2e-5, atol=2e-5 * np.abs(y).max())
+
+
+# ---------------- MXFP4 ----------------
+
+# the values the reference driver draws from (mxfp4-cuda/main.cu:178-182) and what
+# its own check expects of each (verify.h:3-85) when the group's scale is 1
+MXFP4_KNOWN = {0.0: 0.0, 0.5: 0.5, 1.0: 1.0, 1.5: 1.5, 2.0: 2.0, 3.0: 3.0, 4.0: 4.0,
+               0.25: 0.0, 0.75: 1.0, 1.25: 1.0, 1.75: 2.0, 2.5: 2.0, 3.5: 4.0, 5.0: 4.0,
+               0.1: 0.0, 0.3: 0.5, 0.4: 0.5, 0.6: 0.5, 0.9: 1.0}
+
+
+def mxfp4_driver_case(numel: int, seed: int, dtype):
+    """Inputs drawn like the reference driver's (main.cu:184-190): every group of 32
+    holds values of the list above, either sign, and one +-6 that fixes its scale at 1."""
+    rng = np.random.default_rng(seed)
+    vals = np.array(list(MXFP4_KNOWN) + [-v for v in MXFP4_KNOWN if v != 0.0] + [-0.0])
+    x = rng.choice(vals, size=numel).reshape(-1, 32)
+    pos = rng.integers(0, 32, size=x.shape[0])
+    x[np.arange(x.shape[0]), pos] = np.where(pos < 16, 6.0, -6.0)
+    return x.reshape(-1).astype(dtype)
+
+
+def _bf16_bits(x32: np.ndarray) -> np.ndarray:
+    u = x32.astype(np.float32).view(np.uint32)
+    return ((u + 0x7fff + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def _bf16_vals(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_mxfp4_oracle_known_answers(oracle, bf16):
+    x = mxfp4_driver_case(32 * 4096, 3, np.float32)
+    bits = _bf16_bits(x) if bf16 else x.astype(np.float16).view(np.uint16)
+    xin = _bf16_vals(bits) if bf16 else bits.view(np.float16).astype(np.float32)
+    y_bits = oracle.mxfp4_qdq(bits, bf16)
+    y = _bf16_vals(y_bits) if bf16 else y_bits.view(np.float16).astype(np.float32)
+    # expectations are keyed by the value as T holds it (0.1, 0.3 ... are inexact)
+    conv = (lambda v: float(_bf16_vals(_bf16_bits(np.array([v], np.float32)))[0])) if bf16 else \
+        (lambda v: float(np.float16(v)))
+    want = {conv(k): v for k, v in MXFP4_KNOWN.items()}
+    want[conv(6.0)] = 6.0
+    exp = np.array([np.copysign(want[abs(float(v))], v) for v in xin], dtype=np.float32)
+    assert np.array_equal(y, exp)
+    assert np.array_equal(np.signbit(y), np.signbit(xin))
+    # the packed form decodes to the same values, scale byte 127 (2^0) everywhere
+    codes, scales = oracle.mxfp4_quantize(bits, bf16)
+    assert np.all(scales == 127)
+    assert np.array_equal(oracle.mxfp4_dequantize(codes, scales, bf16), y_bits)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_mxfp4_scale_exponent_is_the_references_where_that_is_defined(oracle, bf16):
+    """floor(log2(rounded maximum)) - 2 from the fp32 form of the maximum equals
+    the reference's expression on T's own bits for every finite maximum whose
+    rounded value is a normal number of T."""
+    top = 0x7f80 if bf16 else 0x7c00
+    defined = 0
+    for bits in range(0, top, 7 if bf16 else 3):
+        ours, ref = oracle.mxfp4_scale_exponents(bits, bf16)
+        if ref is not None:
+            defined += 1
+            assert ours == ref, hex(bits)
+    assert defined > 1000
+
+
+def test_mxfp4_oracle_random_groups(oracle):
+    """Scaled groups: the result is the nearest grid value times the scale, ties
+    to the even mantissa, computed here in numpy on exact binary fractions."""
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal(32 * 2048) * np.repeat(2.0 ** rng.integers(-8, 9, 2048), 32))
+    x = x.astype(np.float16)
+    y = oracle.mxfp4_qdq(x.view(np.uint16)).view(np.float16).astype(np.float64)
+    g = x.astype(np.float64).reshape(-1, 32)
+    m = np.abs(g).max(axis=1)
+    e = np.floor(np.log2(m))
+    e = np.where(m / 2.0 ** e >= 1.75, e + 1, e)
+    s = 2.0 ** (e - 2)
+    a = np.abs(g) / s[:, None]
+    step = np.where(a < 2, 0.5, np.where(a < 4, 1.0, 2.0))
+    q = np.minimum(np.round(a / step) * step, 6.0)   # np.round: ties to even
+    assert np.array_equal(y.reshape(-1, 32), np.copysign(q * s[:, None], g))
+
+
+# ---------------- zero point ----------------
+
+ZP_CONFIGS = [(-127, 127), (-128, 127), (0, 255), (0, 15), (-8, 7)]
+
+
+@pytest.mark.parametrize("qmin,qmax", ZP_CONFIGS)
+@pytest.mark.parametrize("preserve", [0, 1])
+def test_zero_point_oracle_matches_reference_golden(oracle, qmin, qmax, preserve):
+    """The C restatement against vectors recorded from the reference's own host
+    function (zeropoint-cuda/reference.h): scales bit for bit, zero points equal."""
+    g = np.load(GOLDEN / "zeropoint_golden.npz")
+    scale, zp = oracle.zero_point(g["x_min"], g["x_max"], qmin, qmax, bool(preserve))
+    assert np.array_equal(scale.view(np.uint32), g[f"scale_{qmin}_{qmax}_{preserve}"].view(np.uint32))
+    assert np.array_equal(zp, g[f"zp_{qmin}_{qmax}_{preserve}"])
+    ref = oracle.ref_zero_point(g["x_min"], g["x_max"], qmin, qmax, bool(preserve))
+    if ref is not None:  # the reference build itself, where it is present
+        assert np.array_equal(ref[0].view(np.uint32), scale.view(np.uint32))
+        assert np.array_equal(ref[1], zp)
+
+
+# ---------------- blockwise 4-bit quantizer ----------------
+
+def spaced_levels(seed: int) -> np.ndarray:
+    """16 ascending levels from -1 to 1, neighbours at least 0.05 apart (so that an
+    fp16 rounding of level * absmax cannot cross a midpoint)."""
+    rng = np.random.default_rng(seed)
+    gaps = 0.05 + rng.uniform(0, 1, 15)
+    lv = np.concatenate([[0.0], np.cumsum(gaps)])
+    return (lv / lv[-1] * 2 - 1).astype(np.float32)
+
+
+def test_nf4_quantize_oracle_against_numpy(oracle):
+    rng = np.random.default_rng(2)
+    lut = spaced_levels(1)
+    w = (rng.standard_normal(64 * 300) * np.repeat(10.0 ** rng.integers(-3, 3, 300), 64)).astype(np.float32)
+    w[128:192] = 0.0
+    mids = (0.5 * (lut[:-1] + lut[1:])).astype(np.float32)
+    w[200] = 0.0
+    for order in (0, 1):
+        B, absmax = oracle.nf4_quantize(w, 64, lut, order)
+        g = w.reshape(-1, 64)
+        m = np.abs(g).max(axis=1)
+        assert np.array_equal(absmax, m)
+        inv = np.where(m > 0, np.float32(1) / np.where(m > 0, m, 1), 0).astype(np.float32)
+        x = (g * inv[:, None]).astype(np.float32)
+        codes = (x[..., None] > mids).sum(axis=-1).astype(np.uint8).reshape(-1)
+        first, second = (codes[0::2], codes[1::2])
+        want = (second << 4 | first) if order else (first << 4 | second)
+        assert np.array_equal(B, want)
+        # dequantising and quantising again returns the same codes
+        deq = oracle.nf4_dequant_f16(B, absmax, lut, w.size, 64, order).astype(np.float32)
+        B2, _ = oracle.nf4_quantize(deq, 64, lut, order)
+        assert np.array_equal(B2, B)
