@@ -31,6 +31,8 @@
 // per-halfword unsigned integer maximum of the magnitudes (three SIMD
 // instructions per thread) and two quad shuffles; rounding to the grid is one
 // add and one subtract of a magic constant chosen by the magnitude's binade.
+// The fp16 packer does this in half2 arithmetic and reads the 3-bit grid index
+// straight out of the sum's mantissa (pack8_half).
 #include <cuda_bf16.h>
 
 #include <algorithm>
@@ -86,6 +88,39 @@ __device__ __forceinline__ uint32_t grid_index(float q) {
   return (uint32_t)max((int)(b >> 22) - 252, (int)min(b, 1u));
 }
 
+// The packer for fp16 inputs, two elements per instruction in half2 arithmetic.
+// |x| / 2^k is two exact multiplications (2^-k alone can leave fp16's range);
+// adding 768, 1538 or 3080 - by the binade of the scaled magnitude - rounds to the
+// grid's step there (.5, 1, 2), ties to even, and the offsets 0, 2 and 8 folded
+// into those constants make the low three mantissa bits of the sum the grid
+// index itself: 768 + r has mantissa 512 + 2r, 1538 + r has 514 + r, 3080 + r has
+// 516 + r / 2.  Returns the four bytes of 8 elements.
+__device__ __forceinline__ uint32_t pack8_half(const uint4& v, int k) {
+  const int k1 = k >> 1, k2 = k - k1;  // both in [-8, 7]
+  const uint32_t b1 = (uint32_t)(15 - k1) << 10, b2 = (uint32_t)(15 - k2) << 10;
+  const __half2 s1 = u32_as_half2(b1 | (b1 << 16)), s2 = u32_as_half2(b2 | (b2 << 16));
+  const __half2 six = __float2half2_rn(6.f), k1024 = __float2half2_rn(1024.f),
+                k512 = __float2half2_rn(512.f), m2047 = __float2half2_rn(-2047.f),
+                c0 = __float2half2_rn(768.f),
+                d1 = __float2half2_rn(770.f), d2 = __float2half2_rn(1542.f);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t m[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    __half2 a = __hmul2(__hmul2(u32_as_half2(w[j] & 0x7fff7fffu), s1), s2);
+    a = __hmin2(a, six);
+    // 1 from 2 (from 4) on, else 0: a saturating fused multiply-add on the
+    // fp16 pipe, exact at the boundary (fp16 neighbours of 2 and 4 are 2^-10 and
+    // 2^-9 below them)
+    const __half2 ge2 = __hfma2_sat(a, k1024, m2047), ge4 = __hfma2_sat(a, k512, m2047);
+    __half2 c = __hfma2(ge2, d1, c0);   // 768, or 1538 from 2 on
+    c = __hfma2(ge4, d2, c);            // 3080 from 4 on
+    const uint32_t n = (half2_as_u32(__hadd2(a, c)) & 0x00070007u) | ((w[j] >> 12) & 0x00080008u);
+    m[j] = n | (n >> 12);  // byte 0: element 2j in the low nibble, 2j + 1 in the high one
+  }
+  return __byte_perm(__byte_perm(m[0], m[1], 0x0040), __byte_perm(m[2], m[3], 0x0040), 0x5410);
+}
+
 // the group maximum of the magnitudes as 16 bits of T: this thread's 8 elements,
 // then the quad
 __device__ __forceinline__ uint32_t quad_max(const uint4& v) {
@@ -124,8 +159,10 @@ mxfp4_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, uint32_t* __
       const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
       uint32_t o[4];
       uint32_t packed = 0;
+      if (MODE == 1 && !BF16) packed = pack8_half(v[u], k);
 #pragma unroll
       for (int j = 0; j < 4; j++) {
+        if (MODE == 1 && !BF16) break;
         const float2 f = to_float2<BF16>(w[j]);
         const float q0 = to_grid(fabsf(f.x) * inv), q1 = to_grid(fabsf(f.y) * inv);
         if (MODE == 0) {

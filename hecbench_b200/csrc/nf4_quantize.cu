@@ -4,7 +4,7 @@
 // reference tree has no blockwise 4-bit quantizer (its quantBnB benchmark is the
 // 8-bit, whole-tensor kQuantize), so the rule is stated here:
 //   absmax[b] = max |w| over block b (fp32)
-//   x         = fp32(w) * (1 / absmax[b])          (0 for a block of zeros)
+//   x         = fp32(w) * (1 / absmax[b])          (0 where absmax is 0, denormal or infinite)
 //   code      = number of the 15 midpoints m_j = (lut16[j] + lut16[j+1]) / 2 (fp32)
 //               that are < x: the nearest level, a tie going to the lower one
 // with lut16 the 16 ascending levels, and two codes per byte in the nibble order
@@ -31,13 +31,9 @@ namespace hq {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kUnroll = 4;           // 8-weight vectors per thread in flight
 constexpr int kCells = 66;          // cell c covers [(c - 33) / 32, (c - 32) / 32)
 constexpr int kCellStride = 256;    // bytes between cells: 32 lanes x 8 bytes
-
-struct QuantTable {
-  float mid[15];
-  bool dense;  // two midpoints share a cell: the table cannot be used
-};
 
 // loads 8 consecutive weights as fp32
 template <int DTYPE>
@@ -79,6 +75,12 @@ __device__ __forceinline__ float max_abs8(const float (&w)[8]) {
   return m;
 }
 
+// 1 / absmax, or 0 where that is not a finite number (absmax zero, denormal,
+// infinite): such a block quantizes to the code of 0
+__device__ __forceinline__ float block_inverse(float m) {
+  return (m >= 1.17549435e-38f && m <= 3.40282347e38f) ? 1.f / m : 0.f;
+}
+
 // codes of 8 weights scaled by inv, packed into one word (byte j = elements 2j, 2j + 1)
 template <bool DENSE>
 __device__ __forceinline__ uint32_t encode8(const float (&w)[8], float inv, const unsigned char* cells,
@@ -93,9 +95,10 @@ __device__ __forceinline__ uint32_t encode8(const float (&w)[8], float inv, cons
 #pragma unroll
       for (int k = 0; k < 15; k++) code += x > mids[k] ? 1u : 0u;
     } else {
-      // x * 32 is exact, so is the cell
-      const uint32_t cell = min((uint32_t)(__float2int_rd(x * 32.f) + 33), (uint32_t)(kCells - 1));
-      const float2 e = *reinterpret_cast<const float2*>(cells + cell * kCellStride + lane * 8);
+      // x * 32 is exact, so is the cell.  |x| <= 1 + 2^-23 or x is not a number
+      // (which converts to 0): floor(x * 32) lies in -33 .. 32 without a clamp
+      const int cell = __float2int_rd(x * 32.f);
+      const float2 e = *reinterpret_cast<const float2*>(cells + (cell + 33) * kCellStride + lane * 8);
       code = __float_as_uint(e.x) + (x > e.y ? 1u : 0u);
     }
     const bool high = ((j & 1) == 0) != low_first;  // even element: high nibble by default
@@ -141,25 +144,32 @@ nf4_quantize_kernel(const void* __restrict__ W, size_t nvec, int blocksize,
     // lane of its block: the lanes of a block are inside or outside together
     const size_t stride = (size_t)gridDim.x * kThreads;
     const size_t first = (size_t)blockIdx.x * kThreads + tid;
-    const size_t rounds = (nvec + stride - 1) / stride;
+    const size_t rounds = (nvec + stride * kUnroll - 1) / (stride * kUnroll);
     for (size_t r = 0; r < rounds; r++) {
-      const size_t v = first + r * stride;
-      float w[8];
-      if (v < nvec) load8<DTYPE>(W, v, nvec, w);
-      else {
+      float w[kUnroll][8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) w[j] = 0.f;
+      for (int u = 0; u < kUnroll; u++) {  // all loads of the round before any arithmetic
+        const size_t v = first + (r * kUnroll + u) * stride;
+        if (v < nvec) load8<DTYPE>(W, v, nvec, w[u]);
+        else {
+#pragma unroll
+          for (int j = 0; j < 8; j++) w[u][j] = 0.f;
+        }
       }
-      float m = max_abs8(w);
 #pragma unroll
-      for (int d = 1; d < LPB; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-      const float inv = m > 0.f ? 1.f / m : 0.f;
-      const uint32_t word = dense ? encode8<true>(w, inv, s_cells, s_mid, lane, lf)
-                                  : encode8<false>(w, inv, s_cells, s_mid, lane, lf);
-      if (v >= nvec) continue;
-      if (HQ_IN_BOUNDS(B + v, 4, B, nvec * 4, 803)) B[v] = word;
-      if ((v % LPB) == 0 && HQ_IN_BOUNDS(absmax + v / LPB, 4, absmax, nvec / LPB * 4, 804))
-        absmax[v / LPB] = m;
+      for (int u = 0; u < kUnroll; u++) {
+        const size_t v = first + (r * kUnroll + u) * stride;
+        float m = max_abs8(w[u]);
+#pragma unroll
+        for (int d = 1; d < LPB; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+        const float inv = block_inverse(m);
+        const uint32_t word = dense ? encode8<true>(w[u], inv, s_cells, s_mid, lane, lf)
+                                    : encode8<false>(w[u], inv, s_cells, s_mid, lane, lf);
+        if (v >= nvec) continue;
+        if (HQ_IN_BOUNDS(B + v, 4, B, nvec * 4, 803)) B[v] = word;
+        if ((v % LPB) == 0 && HQ_IN_BOUNDS(absmax + v / LPB, 4, absmax, nvec / LPB * 4, 804))
+          absmax[v / LPB] = m;
+      }
     }
   } else {
     const int vpb = blocksize / 8;  // vectors per block, a multiple of 32
@@ -174,7 +184,7 @@ nf4_quantize_kernel(const void* __restrict__ W, size_t nvec, int blocksize,
       }
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-      const float inv = m > 0.f ? 1.f / m : 0.f;
+      const float inv = block_inverse(m);
       for (int i = lane; i < vpb; i += 32) {
         float w[8];
         const size_t v = b * vpb + i;

@@ -402,7 +402,7 @@ int hq_zero_point(const float* x_min, const float* x_max, int32_t qmin, int32_t 
 /* Blockwise 4-bit quantizer: produces what hq_nf4_dequant_f16 / hq_nf4_gemv_f16 /
  * hq_qgemm_nf4_f16 consume.  W: n weights of type dtype (HQ_DTYPE_F16, _BF16 or
  * _F32); absmax[b] = max |w| over block b of blocksize weights; x = fp32(w) * (1 /
- * absmax[b]) (0 for a block of zeros); code = how many of the 15 midpoints
+ * absmax[b]) (0 where absmax is zero, denormal or infinite); code = how many of the 15 midpoints
  * (lut16[j] + lut16[j+1]) / 2, formed in fp32 from the 16 ascending levels, are
  * < x: the nearest level, a tie going to the lower one.  B gets two codes per
  * byte in the nibble order of flags (HQ_NF4_*_NIBBLE_FIRST).  blocksize a power

@@ -322,9 +322,10 @@ void orc_nf4_dequant_f16(const uint8_t* B, const float* absmax, const float* lut
 
 /* Blockwise 4-bit quantizer, the inverse of the dequantisation above (no
  * counterpart in the reference tree): absmax[b] = max |w| over the block, x = w *
- * (1 / absmax[b]) in fp32 (0 for a block of zeros), code = how many of the 15
- * midpoints (lut16[j] + lut16[j+1]) / 2 (fp32) are < x - the nearest level, a tie
- * going to the lower one.  w: the weights widened to fp32 (exact for fp16 / bf16). */
+ * (1 / absmax[b]) in fp32 (0 where absmax is zero, denormal or infinite), code =
+ * how many of the 15 midpoints (lut16[j] + lut16[j+1]) / 2 (fp32) are < x - the
+ * nearest level, a tie going to the lower one.  w: the weights widened to fp32
+ * (exact for fp16 / bf16). */
 void orc_nf4_quantize(const float* w, size_t n, int blocksize, const float* lut16, int low_first,
                       uint8_t* B, float* absmax) {
   float mid[15];
@@ -337,7 +338,7 @@ void orc_nf4_quantize(const float* w, size_t n, int blocksize, const float* lut1
       if (a > m) m = a;
     }
     absmax[b] = m;
-    const float inv = m > 0.f ? 1.f / m : 0.f;
+    const float inv = (m >= FLT_MIN && m <= FLT_MAX) ? 1.f / m : 0.f;
     for (int j = 0; j < blocksize; j++) {
       const size_t e = b * blocksize + j;
       const float x = w[e] * inv;

@@ -108,6 +108,7 @@ def _weights(n_blocks, bs, seed, dtype):
     w = rng.standard_normal(n_blocks * bs) * np.repeat(10.0 ** rng.integers(-3, 3, n_blocks), bs)
     w = w.astype(np.float32)
     w[bs:2 * bs] = 0.0                                           # a block of zeros
+    w[2 * bs:3 * bs] *= np.float32(1e-42) / np.abs(w[2 * bs:3 * bs]).max()   # a denormal absmax (fp32)
     if dtype == "float16":
         return w.astype(np.float16).astype(np.float32)
     if dtype == "bfloat16":
