@@ -261,6 +261,35 @@ def zero_point(x_min, x_max, qmin: int, qmax: int, size: int, preserve_sparsity:
             _dev(zero_point_out, torch.int32, "zero_point"), _stream()))
 
 
+def quantize_q3(W, mat=None, scales=None, zeros=None):
+    """Round-to-nearest 3-bit quantizer and packer (per-column min / max, the layout
+    of quant3MatMul-cuda/kernels.h:41-87; no counterpart in the reference tree):
+    W[K][N] float16 / bfloat16 / float32 -> (mat int32[K*3/32][N], scales float32[N],
+    zeros float32[N]) as vecquant3matmul consumes them."""
+    lib = load_library()
+    code = _VLLM_DTYPE.get(W.dtype)
+    if code is None:
+        raise TypeError("W must be float16, bfloat16 or float32")
+    if W.dim() != 2 or not W.is_cuda or not W.is_contiguous():
+        raise ValueError("W must be a contiguous 2-D CUDA tensor")
+    K, N = W.shape
+    dev = W.device
+    if mat is None:
+        mat = torch.empty((K * 3 // 32, N), dtype=torch.int32, device=dev)
+    if scales is None:
+        scales = torch.empty(N, dtype=torch.float32, device=dev)
+    if zeros is None:
+        zeros = torch.empty(N, dtype=torch.float32, device=dev)
+    nbytes = int(lib.hq_q3_quantize_workspace_bytes(N))
+    ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check("hq_q3_quantize", lib.hq_q3_quantize(
+            W.data_ptr(), code, K, N, _dev(mat, torch.int32, "mat"),
+            _dev(scales, torch.float32, "scales"), _dev(zeros, torch.float32, "zeros"),
+            ws.data_ptr(), nbytes, _stream()))
+    return mat, scales, zeros
+
+
 def quantize_nf4(W, lut16, blocksize: int = 64, nibble_order: int = NF4_HIGH_NIBBLE_FIRST,
                  B=None, absmax=None):
     """Blockwise 4-bit quantizer (the inverse of dequantize_nf4; no counterpart in

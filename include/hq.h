@@ -399,6 +399,21 @@ int hq_gemv_fused_nf4_f16(const void* x_half, const void* gamma_half, float eps,
 int hq_zero_point(const float* x_min, const float* x_max, int32_t qmin, int32_t qmax, int size,
                   int preserve_sparsity, float* scale, int32_t* zero_point, hq_stream_t stream);
 
+/* Round-to-nearest 3-bit quantizer and packer: produces what hq_q3_gemv_f32 /
+ * hq_q3_gemv_f16in consume (the layout of src/quant3MatMul-cuda/kernels.h:41-87;
+ * the reference tree holds only that consumer).  W: K x N weights, row-major, of
+ * type dtype (HQ_DTYPE_F16, _BF16, _F32).  Per column c, in fp32: lo = min(column,
+ * 0), hi = max(column, 0) (-1 and 1 if both are 0); scale = (hi - lo) / 7; z =
+ * rint(-lo / scale); code = clamp(rint(w / scale) + z, 0, 7), roundings to
+ * nearest, ties to even - GPTQ's min / max quantizer without its error search;
+ * scales[c] = scale, zeros[c] = scale * z.  mat: int32[K * 3 / 32][N].  workspace:
+ * hq_q3_quantize_workspace_bytes(N) bytes of device scratch (contents
+ * irrelevant).  K % 32 == 0, N % 8 == 0, W / mat / scales / zeros 16-byte
+ * aligned. */
+size_t hq_q3_quantize_workspace_bytes(int N);
+int hq_q3_quantize(const void* W, int dtype, int K, int N, int32_t* mat, float* scales,
+                   float* zeros, void* workspace, size_t workspace_bytes, hq_stream_t stream);
+
 /* Blockwise 4-bit quantizer: produces what hq_nf4_dequant_f16 / hq_nf4_gemv_f16 /
  * hq_qgemm_nf4_f16 consume.  W: n weights of type dtype (HQ_DTYPE_F16, _BF16 or
  * _F32); absmax[b] = max |w| over block b of blocksize weights; x = fp32(w) * (1 /

@@ -150,6 +150,42 @@ void orc_q3_pack(const uint8_t* codes, int32_t* mat, int K, int width) {
     }
 }
 
+/* Round-to-nearest 3-bit quantizer, W[K][width] fp32 (widened weights) -> the
+ * packed matrix, scales and zeros of the 3-bit mat-vec.  No counterpart in the
+ * reference tree (it holds only the consumer, quant3MatMul-cuda/kernels.h); the
+ * rule is GPTQ's per-column min / max quantizer without its error search:
+ * lo = min(column, 0), hi = max(column, 0) (-1, 1 if both are 0); scale = (hi -
+ * lo) / 7; z = rint(-lo / scale); q = clamp(rint(w / scale) + z, 0, 7), all fp32;
+ * scales[c] = scale, zeros[c] = scale * z. */
+void orc_q3_quantize(const float* W, int K, int width, int32_t* mat, float* scales, float* zeros) {
+  uint8_t* codes = (uint8_t*)malloc((size_t)K * width);
+#pragma omp parallel for
+  for (int c = 0; c < width; c++) {
+    float lo = 0.f, hi = 0.f;
+    for (int k = 0; k < K; k++) {
+      const float w = W[(size_t)k * width + c];
+      if (w < lo) lo = w;
+      if (w > hi) hi = w;
+    }
+    if (lo == 0.f && hi == 0.f) {
+      lo = -1.f;
+      hi = 1.f;
+    }
+    const float scale = (hi - lo) / 7.f;
+    const float z = rintf(-lo / scale);
+    scales[c] = scale;
+    zeros[c] = scale * z;
+    for (int k = 0; k < K; k++) {
+      float q = rintf(W[(size_t)k * width + c] / scale) + z;
+      if (q < 0.f) q = 0.f;
+      if (q > 7.f) q = 7.f;
+      codes[(size_t)k * width + c] = (uint8_t)q;
+    }
+  }
+  orc_q3_pack(codes, mat, K, width);
+  free(codes);
+}
+
 void orc_q3_unpack(const int32_t* mat, uint8_t* codes, int height, int width) {
   int groups = height / 3;
   for (int r = 0; r < groups; r++)

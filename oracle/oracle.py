@@ -313,6 +313,17 @@ def ref_fused_f32(W, x, gamma, rows_out: int, act: int):
     return y[0::2] * sw
 
 
+def q3_quantize(W):
+    """(mat int32[K*3/32][N], scales fp32[N], zeros fp32[N]) of fp32-widened W[K][N]."""
+    W = _c(np.asarray(W, dtype=np.float32), np.float32)
+    K, N = W.shape
+    mat = np.empty((K * 3 // 32, N), dtype=np.int32)
+    scales = np.empty(N, dtype=np.float32)
+    zeros = np.empty(N, dtype=np.float32)
+    lib().orc_q3_quantize(_ptr(W), C.c_int(K), C.c_int(N), _ptr(mat), _ptr(scales), _ptr(zeros))
+    return mat, scales, zeros
+
+
 def nf4_quantize(w, blocksize: int, lut16, low_first: int = 0):
     """(codes uint8[n / 2], absmax fp32[n / blocksize]) of fp32-widened weights."""
     w = _c(np.asarray(w, dtype=np.float32).reshape(-1), np.float32)

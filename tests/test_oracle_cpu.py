@@ -509,3 +509,23 @@ def test_nf4_quantize_oracle_against_numpy(oracle):
         deq = oracle.nf4_dequant_f16(B, absmax, lut, w.size, 64, order).astype(np.float32)
         B2, _ = oracle.nf4_quantize(deq, 64, lut, order)
         assert np.array_equal(B2, B)
+
+
+def test_q3_quantize_oracle_against_numpy(oracle):
+    """The C restatement of the per-column min / max 3-bit quantizer against numpy,
+    and its packed matrix through the unpacker and the dequantiser."""
+    rng = np.random.default_rng(8)
+    K, N = 96, 40
+    W = (rng.standard_normal((K, N)) * rng.uniform(0.01, 2, N)).astype(np.float32)
+    W[:, 0] = 0.0
+    W[:, 1] = np.abs(W[:, 1]) + 0.5
+    mat, scales, zeros = oracle.q3_quantize(W)
+    lo, hi = np.minimum(W.min(axis=0), 0), np.maximum(W.max(axis=0), 0)
+    lo[0], hi[0] = -1.0, 1.0
+    sc = ((hi - lo) / np.float32(7)).astype(np.float32)
+    z = np.rint((-lo / sc).astype(np.float32))
+    q = np.clip(np.rint((W / sc).astype(np.float32)) + z, 0, 7).astype(np.uint8)
+    assert np.array_equal(scales, sc) and np.array_equal(zeros, (sc * z).astype(np.float32))
+    assert np.array_equal(oracle.q3_unpack(mat), q)
+    Wq = oracle.q3_dequant_f32(mat, scales, zeros)
+    assert np.all(np.abs(Wq - W) <= sc / 2 * (1 + 1e-5) + 1e-7)

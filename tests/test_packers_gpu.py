@@ -101,6 +101,97 @@ def test_zero_point_argument_errors(hq, dev):
     assert lib.hq_zero_point(None, None, -127, 127, 0, 1, None, None, None) == 0
 
 
+# ---------------- 3-bit quantizer and packer ----------------
+
+def _q3_weights(K, N, seed, dtype):
+    rng = np.random.default_rng(seed)
+    W = (rng.standard_normal((K, N)) * rng.uniform(0.01, 2.0, N)).astype(np.float32)
+    W[:, 0] = 0.0                                  # a column of zeros
+    W[:, 1] = np.abs(W[:, 1]) + 0.5                # positive only
+    W[:, 2] = -np.abs(W[:, 2]) - 0.5               # negative only
+    W[:, 3] = 0.25                                 # constant
+    if dtype == "float16":
+        return W.astype(np.float16).astype(np.float32)
+    if dtype == "bfloat16":
+        return _bf16_vals(_bf16_bits(W)).reshape(K, N)
+    return W
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16", "float32"])
+@pytest.mark.parametrize("K,N", [(32, 8), (96, 264), (4096, 4096), (1024, 136), (64, 12288)])
+def test_q3_quantize_against_oracle(hq, oracle, dev, dtype, K, N):
+    """Packed matrix, scales and zeros bit for bit: shapes that leave column tiles and
+    K slices ragged, columns of one sign, of zeros, of one value."""
+    W = _q3_weights(K, N, K + N, dtype)
+    mat, scales, zeros = hq.quantize_q3(_to_torch(W, dtype, dev))
+    om, osc, oz = oracle.q3_quantize(W)
+    assert np.array_equal(scales.cpu().numpy().view(np.uint32), osc.view(np.uint32))
+    assert np.array_equal(zeros.cpu().numpy().view(np.uint32), oz.view(np.uint32))
+    assert np.array_equal(mat.cpu().numpy(), om)
+
+
+def test_q3_quantize_ties_and_mat_vec(hq, oracle, dev):
+    """Weights exactly half way between two codes (ties go to the even code), and
+    the quantized layer through the 3-bit mat-vec against the mat-vec of its own
+    dequantised weights."""
+    import torch
+    K, N = 2048, 512
+    rng = np.random.default_rng(4)
+    # scale 0.5 per column: lo = -1.5, hi = 2 -> codes at -1.5, -1, ..., 2; ties at +-.25 steps
+    W = (rng.integers(-6, 9, (K, N)) * 0.25).astype(np.float32)
+    W[0], W[1] = -1.5, 2.0
+    mat, scales, zeros = hq.quantize_q3(to_dev(W, dev))
+    om, osc, oz = oracle.q3_quantize(W)
+    assert np.array_equal(mat.cpu().numpy(), om)
+    assert np.array_equal(scales.cpu().numpy(), osc) and np.array_equal(zeros.cpu().numpy(), oz)
+    Wq = oracle.q3_dequant_f32(om, osc, oz)
+    assert np.abs(Wq - W).max() <= 0.25 + 1e-6
+    x = rng.standard_normal(K).astype(np.float32)
+    y = torch.zeros(N, dtype=torch.float32, device=dev)
+    hq.vecquant3matmul(to_dev(x, dev), mat, y, scales, zeros, K * 3 // 32, N)
+    ref = x.astype(np.float64) @ Wq.astype(np.float64)
+    assert oracle.rel_err(y.cpu().numpy().astype(np.float64), ref) < 1e-3
+
+
+def test_q3_quantize_layer_size_properties(hq, dev):
+    """12288 x 12288 fp16 weights: every dequantised weight within half a step of
+    the original, steps = (max - min) / 7 of the column range widened to hold 0."""
+    import torch
+    K = N = 12288
+    g = torch.Generator(device=dev).manual_seed(11)
+    W = torch.empty((K, N), dtype=torch.float16, device=dev).normal_(0, 0.02, generator=g)
+    mat, scales, zeros = hq.quantize_q3(W)
+    lo = W.float().amin(dim=0).clamp(max=0)
+    hi = W.float().amax(dim=0).clamp(min=0)
+    assert np.array_equal(scales.cpu().numpy(), (hi - lo).cpu().numpy() / np.float32(7))
+    lib = hq.load_library()
+    Wq = torch.empty((K, N), dtype=torch.float32, device=dev)
+    assert lib.hq_q3_dequant_f32(mat.data_ptr(), scales.data_ptr(), zeros.data_ptr(), Wq.data_ptr(),
+                                 K * 3 // 32, N, None) == 0
+    err = (Wq - W.float()).abs() / scales
+    assert float(err.max()) <= 0.5 + 1e-3
+    del Wq, err
+
+
+def test_q3_quantize_argument_errors(hq, dev):
+    import torch
+    lib = hq.load_library()
+    w = torch.zeros(64 * 16, dtype=torch.float16, device=dev)
+    m = torch.zeros(6 * 16, dtype=torch.int32, device=dev)
+    f = torch.zeros(16, dtype=torch.float32, device=dev)
+    ws = torch.zeros(128, dtype=torch.uint8, device=dev)
+    p = lambda t: t.data_ptr()
+    assert lib.hq_q3_quantize_workspace_bytes(16) == 128
+    assert lib.hq_q3_quantize(p(w), 0, 48, 16, p(m), p(f), p(f), p(ws), 128, None) == -1
+    assert lib.hq_q3_quantize(p(w), 0, 64, 12, p(m), p(f), p(f), p(ws), 128, None) == -1
+    assert lib.hq_q3_quantize(None, 0, 64, 16, p(m), p(f), p(f), p(ws), 128, None) == -2
+    assert lib.hq_q3_quantize(p(w), 0, 64, 16, p(m), p(f), p(f), p(ws), 64, None) == -5
+    assert lib.hq_q3_quantize(p(w), 0, 64, 16, p(m), p(f), p(f), None, 0, None) == -5
+    assert lib.hq_q3_quantize(p(w), 7, 64, 16, p(m), p(f), p(f), p(ws), 128, None) == -6
+    assert lib.hq_q3_quantize(p(w) + 2, 0, 32, 16, p(m), p(f), p(f), p(ws), 128, None) == -3
+    torch.cuda.synchronize()
+
+
 # ---------------- blockwise 4-bit quantizer ----------------
 
 def _weights(n_blocks, bs, seed, dtype):
