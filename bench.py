@@ -178,9 +178,14 @@ def _host_case(name: str, seed: int, Mb: int = 64):
                     bytes=numel * 2 + (numel // 2 + numel // 32 if pack else numel * 2),
                     desc=f"MXFP4 {'packer' if pack else 'quantize-dequantize'} of {numel} fp16 values "
                          "(mxfp4-cuda)")
-    if name == "q3_quantize":
-        K, N = 12288, 12288  # one square projection of the 175B-class layer of the mat-vec workload
+    if name in ("q3_quantize", "bcq_quantize"):
+        K, N = 12288, 12288  # the LUT-GEMM workload's layer; one square projection of the 3-bit one
         W = (synth._rng(seed, 84).standard_normal((K, N), dtype=np.float32) * 0.02).astype(np.float16)
+        if name == "bcq_quantize":
+            return dict(K=K, N=N, W=W,
+                        bytes=K * N * 2 + K // 32 * 3 * N * 4 + K // 128 * 4 * N * 2,
+                        desc=f"greedy binary-coding quantizer, {K}x{N} fp16 weights, 3 planes, "
+                             "groups of 128")
         return dict(K=K, N=N, W=W, bytes=2 * K * N * 2 + K * 3 // 32 * N * 4 + 8 * N,
                     desc=f"3-bit round-to-nearest quantizer and packer, {K}x{N} fp16 weights "
                          "(two passes over the weights)")
@@ -231,7 +236,7 @@ WORKLOADS = ["nf4_gemv", "nf4_dequant", "q3_gemv_f32", "q3_gemv_f16", "q3_gemv_f
              "vllm_static_f16", "vllm_dynamic_f16", "vllm_dynamic_azp_f16",
              "gemv_int8", "gemv_int4", "fused_nf4_swiglu", "fused_int8_swiglu",
              "fused_int4_swiglu", "mxfp4_qdq_f16", "mxfp4_quantize_f16", "zero_point",
-             "nf4_quantize", "q3_quantize"]
+             "nf4_quantize", "q3_quantize", "bcq_quantize"]
 
 
 def dtype_of(name: str) -> str:
@@ -330,6 +335,8 @@ class DeviceWorkload:
             self.y = torch.empty(c["numel"], dtype=torch.float16, device=dev)
             self.codes = torch.empty(c["numel"] // 2, dtype=torch.uint8, device=dev)
             self.scales8 = torch.empty(c["numel"] // 32, dtype=torch.uint8, device=dev)
+        elif name == "bcq_quantize":
+            self.W = [t(rot(c["W"], i)) for i in range(R)]
         elif name == "q3_quantize":
             self.W = [t(rot(c["W"], i)) for i in range(R)]
             self.mat3 = torch.empty((c["K"] * 3 // 32, c["N"]), dtype=torch.int32, device=dev)
@@ -395,6 +402,8 @@ class DeviceWorkload:
             hq.mxfp4(self.y, self.xin[i], c["numel"])
         elif n == "mxfp4_quantize_f16":
             hq.mxfp4_quantize(self.xin[i], self.codes, self.scales8)
+        elif n == "bcq_quantize":
+            hq.quantize_bcq(self.W[i], 3, 128, True)
         elif n == "q3_quantize":
             hq.quantize_q3(self.W[i], self.mat3, self.sc3, self.z3)
         elif n == "nf4_quantize":

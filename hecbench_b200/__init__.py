@@ -28,6 +28,7 @@ from .api import (  # noqa: F401
     mxfp4,
     mxfp4_dequantize,
     mxfp4_quantize,
+    quantize_bcq,
     quantize_nf4,
     quantize_q3,
     zero_point,
@@ -54,6 +55,6 @@ __all__ = [
     "static_scaled_int8_quant", "dynamic_scaled_int8_quant",
     "gemv_fp16", "gemv_int8_quantized", "gemv_int4_quantized",
     "gemv_fused", "ACT_NONE", "ACT_SWIGLU", "ACT_GEGLU",
-    "zero_point", "mxfp4", "mxfp4_quantize", "mxfp4_dequantize", "quantize_nf4", "quantize_q3",
+    "zero_point", "mxfp4", "mxfp4_quantize", "mxfp4_dequantize", "quantize_nf4", "quantize_bcq", "quantize_q3",
     "NF4_HIGH_NIBBLE_FIRST", "NF4_LOW_NIBBLE_FIRST", "NF4_WEIGHTS_RESIDENT",
 ]

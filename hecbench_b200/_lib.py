@@ -82,6 +82,8 @@ SIGNATURES = {
     "hq_q3_quantize_workspace_bytes": (c_size_t, [c_int]),
     "hq_q3_quantize": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_size_t, c_void_p]),
+    "hq_lutgemm_quantize": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                    c_void_p, c_void_p, c_void_p]),
     "hq_nf4_quantize": (c_int, [c_void_p, c_int, c_size_t, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p]),
     "hq_mxfp4_qdq": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_void_p]),

@@ -290,6 +290,30 @@ def quantize_q3(W, mat=None, scales=None, zeros=None):
     return mat, scales, zeros
 
 
+def quantize_bcq(W, nb: int = 3, group_size: int = 128, bias: bool = True):
+    """Greedy binary-coding quantizer (no counterpart in the reference tree): W[K][M]
+    float16 / bfloat16 / float32 -> (bW int32[K/32][nb][M] sign planes, alpha
+    float16[K/group_size][nb][M], q_bias float16[K/group_size][M] or None), the
+    arrays nQWeight_fp16 takes."""
+    lib = load_library()
+    code = _VLLM_DTYPE.get(W.dtype)
+    if code is None:
+        raise TypeError("W must be float16, bfloat16 or float32")
+    if W.dim() != 2 or not W.is_cuda or not W.is_contiguous():
+        raise ValueError("W must be a contiguous 2-D CUDA tensor")
+    K, M = W.shape
+    dev = W.device
+    G = K // group_size
+    bW = torch.empty((K // 32, nb, M), dtype=torch.int32, device=dev)
+    alpha = torch.empty((G, nb, M), dtype=torch.float16, device=dev)
+    qb = torch.empty((G, M), dtype=torch.float16, device=dev) if bias else None
+    with torch.cuda.device(dev):
+        check("hq_lutgemm_quantize", lib.hq_lutgemm_quantize(
+            W.data_ptr(), code, K, M, nb, group_size, bW.data_ptr(), alpha.data_ptr(),
+            qb.data_ptr() if bias else None, _stream()))
+    return bW, alpha, qb
+
+
 def quantize_nf4(W, lut16, blocksize: int = 64, nibble_order: int = NF4_HIGH_NIBBLE_FIRST,
                  B=None, absmax=None):
     """Blockwise 4-bit quantizer (the inverse of dequantize_nf4; no counterpart in

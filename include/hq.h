@@ -414,6 +414,20 @@ size_t hq_q3_quantize_workspace_bytes(int N);
 int hq_q3_quantize(const void* W, int dtype, int K, int N, int32_t* mat, float* scales,
                    float* zeros, void* workspace, size_t workspace_bytes, hq_stream_t stream);
 
+/* Greedy binary-coding quantizer: produces what hq_lutgemm_nqmv consumes (the
+ * layouts of src/lut-gemm-cuda/main.cu:27-30,118-134; the reference tree holds only
+ * that consumer).  W: K x M weights, row-major (input k, output m), of type dtype.
+ * Per output m and group of group_size consecutive inputs, in fp32 with sums
+ * taken in ascending k: q_bias = half(mean) (q_bias_half == NULL: no offsets, the
+ * mean stays in the residual); r = w - q_bias; for each of the nb planes alpha =
+ * half(mean |r|), bit = (r >= 0), r -= +-alpha (the rounded value).  bW:
+ * uint32[K / 32][nb][M], bit t of a word = input 32 * row + t; alpha_half:
+ * half[K / group_size][nb][M]; q_bias_half: half[K / group_size][M].
+ * 1 <= nb <= 8, group_size % 32 == 0 (at most 448 for the shared-memory tile),
+ * K % group_size == 0, M % 8 == 0, W 16-byte aligned. */
+int hq_lutgemm_quantize(const void* W, int dtype, int K, int M, int nb, int group_size,
+                        uint32_t* bW, void* alpha_half, void* q_bias_half, hq_stream_t stream);
+
 /* Blockwise 4-bit quantizer: produces what hq_nf4_dequant_f16 / hq_nf4_gemv_f16 /
  * hq_qgemm_nf4_f16 consume.  W: n weights of type dtype (HQ_DTYPE_F16, _BF16 or
  * _F32); absmax[b] = max |w| over block b of blocksize weights; x = fp32(w) * (1 /

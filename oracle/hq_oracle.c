@@ -464,6 +464,46 @@ void orc_lutgemm_dequant_f32(const uint32_t* bW, const uint16_t* alpha,
   }
 }
 
+/* Greedy binary-coding quantizer, W[K][M] fp32 (widened weights) -> the layouts
+ * above.  No counterpart in the reference tree (it holds only the consumer).  Per
+ * column and group, fp32, sums in ascending k: q_bias = half(mean) (when asked
+ * for); r = w - q_bias; per plane alpha = half(mean |r|), bit = r >= 0, r -=
+ * +-alpha (the rounded value). */
+void orc_lutgemm_quantize(const float* W, int K, int M, int nb, int group_size, uint32_t* bW,
+                          uint16_t* alpha, uint16_t* q_bias) {
+  const int G = K / group_size;
+  memset(bW, 0, (size_t)(K / 32) * nb * M * sizeof(uint32_t));
+#pragma omp parallel for
+  for (int m = 0; m < M; m++) {
+    float* r = (float*)malloc((size_t)group_size * sizeof(float));
+    for (int g = 0; g < G; g++) {
+      for (int k = 0; k < group_size; k++) r[k] = W[(size_t)(g * group_size + k) * M + m];
+      if (q_bias) {
+        float s = 0.f;
+        for (int k = 0; k < group_size; k++) s += r[k];
+        const uint16_t bh = orc_f2h(s / (float)group_size);
+        q_bias[(size_t)g * M + m] = bh;
+        const float bias = orc_h2f(bh);
+        for (int k = 0; k < group_size; k++) r[k] = r[k] - bias;
+      }
+      for (int b = 0; b < nb; b++) {
+        float s = 0.f;
+        for (int k = 0; k < group_size; k++) s += fabsf(r[k]);
+        const uint16_t ah = orc_f2h(s / (float)group_size);
+        alpha[((size_t)g * nb + b) * M + m] = ah;
+        const float a = orc_h2f(ah);
+        for (int k = 0; k < group_size; k++) {
+          const int up = r[k] >= 0.f;
+          const int kk = g * group_size + k;
+          if (up) bW[((size_t)(kk >> 5) * nb + b) * M + m] |= 1u << (kk & 31);
+          r[k] = r[k] - (up ? a : -a);
+        }
+      }
+    }
+    free(r);
+  }
+}
+
 void orc_lutgemm_gemv_f64(const uint16_t* x, const uint32_t* bW, const uint16_t* alpha,
                           const uint16_t* q_bias, double* out, int M, int K, int nb,
                           int group_size) {

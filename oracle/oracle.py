@@ -407,6 +407,20 @@ def lutgemm_dequant_f32(bW, alpha, q_bias, M, K, nb, group_size) -> np.ndarray:
     return W
 
 
+def lutgemm_quantize(W, nb: int, group_size: int, bias: bool = True):
+    """(bW uint32[K/32][nb][M], alpha fp16[G][nb][M], q_bias fp16[G][M] or None) of
+    fp32-widened W[K][M]."""
+    W = _c(np.asarray(W, dtype=np.float32), np.float32)
+    K, M = W.shape
+    G = K // group_size
+    bW = np.empty((K // 32, nb, M), dtype=np.uint32)
+    alpha = np.empty((G, nb, M), dtype=np.uint16)
+    qb = np.empty((G, M), dtype=np.uint16) if bias else None
+    lib().orc_lutgemm_quantize(_ptr(W), C.c_int(K), C.c_int(M), C.c_int(nb), C.c_int(group_size),
+                               _ptr(bW), _ptr(alpha), _ptr(qb) if bias else None)
+    return bW, alpha.view(np.float16), (qb.view(np.float16) if bias else None)
+
+
 def lutgemm_gemv_f64(x, bW, alpha, q_bias, M, K, nb, group_size) -> np.ndarray:
     x, bW, alpha = _c(x, np.uint16), _c(bW, np.uint32), _c(alpha, np.uint16)
     qb = None if q_bias is None else _c(q_bias, np.uint16)

@@ -192,6 +192,74 @@ def test_q3_quantize_argument_errors(hq, dev):
     torch.cuda.synchronize()
 
 
+# ---------------- greedy binary-coding quantizer ----------------
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16", "float32"])
+@pytest.mark.parametrize("K,M,nb,gs,bias", [(128, 128, 3, 128, True), (256, 136, 4, 64, True),
+                                            (512, 1024, 1, 32, False), (1024, 264, 3, 256, False),
+                                            (384, 8, 8, 128, True)])
+def test_bcq_quantize_against_oracle(hq, oracle, dev, dtype, K, M, nb, gs, bias):
+    """Sign planes, scales and offsets bit for bit; columns of zeros and of one value
+    (zero residuals: the bit of a zero is 1)."""
+    rng = np.random.default_rng(K + M + nb)
+    W = (rng.standard_normal((K, M)) * 0.05).astype(np.float32)
+    W[:, 0] = 0.0
+    W[:, 1] = 0.125
+    if dtype == "float16":
+        W = W.astype(np.float16).astype(np.float32)
+    elif dtype == "bfloat16":
+        W = _bf16_vals(_bf16_bits(W)).reshape(K, M)
+    bW, alpha, qb = hq.quantize_bcq(_to_torch(W, dtype, dev), nb, gs, bias)
+    obW, oal, oqb = oracle.lutgemm_quantize(W, nb, gs, bias)
+    assert np.array_equal(bW.cpu().numpy().view(np.uint32), obW)
+    assert np.array_equal(alpha.cpu().numpy().view(np.uint16), oal.view(np.uint16))
+    if bias:
+        assert np.array_equal(qb.cpu().numpy().view(np.uint16), oqb.view(np.uint16))
+
+
+def test_bcq_quantize_error_shrinks_and_feeds_the_mat_vec(hq, oracle, dev):
+    """More planes, smaller error; and the quantized layer through the LUT-GEMM
+    mat-vec equals the mat-vec of its own dequantised weights."""
+    import torch
+    K = M = 1024
+    rng = np.random.default_rng(6)
+    W = (rng.standard_normal((K, M)) * 0.03).astype(np.float16)
+    x = rng.standard_normal(K).astype(np.float16)
+    dW = to_dev(W.view(np.uint16).view(np.int16), dev).view(torch.float16)
+    errs = []
+    for nb in (1, 2, 3, 4):
+        bW, alpha, qb = hq.quantize_bcq(dW, nb, 128, True)
+        Wq = oracle.lutgemm_dequant_f32(bW.cpu().numpy().view(np.uint32),
+                                        alpha.cpu().numpy(), qb.cpu().numpy(), M, K, nb, 128)
+        errs.append(float(np.sqrt(np.mean((Wq - W.astype(np.float32)) ** 2))))
+        if nb == 3:
+            w = hq.nQWeight_fp16(bW.cpu().numpy().view(np.uint32), alpha.cpu().numpy().astype(np.float32),
+                                 K, M, nb, False, K // 128, qb.cpu().numpy().astype(np.float32),
+                                 device=dev)
+            y = torch.empty(M, dtype=torch.float16, device=dev)
+            hq.matmul(y, to_dev(x.view(np.uint16).view(np.int16), dev).view(torch.float16), w)
+            ref = x.astype(np.float64) @ Wq.astype(np.float64)
+            assert oracle.rel_err(y.cpu().numpy().astype(np.float64), ref) < 1e-2
+    assert errs[0] > errs[1] > errs[2] > errs[3]
+    assert errs[2] < 0.25 * 0.03      # three planes leave under a quarter of the spread
+
+
+def test_bcq_quantize_argument_errors(hq, dev):
+    import torch
+    lib = hq.load_library()
+    w = torch.zeros(128 * 16, dtype=torch.float16, device=dev)
+    b = torch.zeros(4 * 3 * 16, dtype=torch.int32, device=dev)
+    a = torch.zeros(3 * 16, dtype=torch.float16, device=dev)
+    p = lambda t: t.data_ptr()
+    assert lib.hq_lutgemm_quantize(p(w), 0, 128, 16, 3, 48, p(b), p(a), None, None) == -1
+    assert lib.hq_lutgemm_quantize(p(w), 0, 128, 12, 3, 128, p(b), p(a), None, None) == -1
+    assert lib.hq_lutgemm_quantize(p(w), 0, 128, 16, 9, 128, p(b), p(a), None, None) == -1
+    assert lib.hq_lutgemm_quantize(p(w), 0, 128, 16, 3, 128, None, p(a), None, None) == -2
+    assert lib.hq_lutgemm_quantize(p(w), 5, 128, 16, 3, 128, p(b), p(a), None, None) == -6
+    assert lib.hq_lutgemm_quantize(p(w), 0, 1024, 16, 3, 512, p(b), p(a), None, None) == -6
+    torch.cuda.synchronize()
+
+
 # ---------------- blockwise 4-bit quantizer ----------------
 
 def _weights(n_blocks, bs, seed, dtype):
