@@ -9,6 +9,8 @@ only) go to hecbench_b200/build/dropin/:
   dropin_quantAQLM     shim/quantAQLM/main.cu
   dropin_quantVLLM     shim/quantVLLM/main.cu (reference reference.h, utils.h on the include path)
   dropin_gemv          reference main.cu + shim/gemv/gemv.cu (reference kernels.h, simple_tensor.h on the include path)
+  dropin_zeropoint     shim/zeropoint/main.cu (reference reference.h on the include path)
+  dropin_mxfp4         shim/mxfp4/main.cu (reference verify.h on the include path)
   shard_demo           shim/shard/main.cu: one-process host of the hq_shard_* context
 
 The reference sources are compiled from where they lie; for quant3MatMul the
@@ -108,6 +110,13 @@ def build(force: bool = False):
         d = src / "gemv-cuda"
         _run([NVCC, *COMMON, f"-I{d}", d / "main.cu", shim_cu, "-o", tgt])
     built.append(tgt)
+
+    for name, extra in (("zeropoint", []), ("mxfp4", ["--expt-relaxed-constexpr"])):
+        tgt = OUT / f"dropin_{name}"
+        drv = SHIM / name / "main.cu"
+        if stale(tgt, [drv]):
+            _run([NVCC, *COMMON, *extra, f"-I{src / (name + '-cuda')}", drv, "-o", tgt])
+        built.append(tgt)
     return built
 
 

@@ -56,6 +56,23 @@ def test_quantvllm_driver_passes():
     assert out.count("PASS") == 3 and "FAIL" not in out, out
 
 
+def test_zeropoint_driver_passes():
+    """The reference run's own size (10^7 channels, zeropoint-cuda/Makefile), fewer
+    repetitions: the driver's comparison with the reference's host function."""
+    out = run("dropin_zeropoint", 10000000, 20)
+    assert "Average execution time of zero-point kernel" in out
+    assert out.count("PASS") == 1 and "FAIL" not in out and "status" not in out, out
+
+
+def test_mxfp4_driver_passes():
+    """fp16 and bf16 sections with the reference's own verify.h; 2^24 elements (the
+    reference run has 2^29)."""
+    out = run("dropin_mxfp4", 1 << 24, 20)
+    assert "Simulate conversion between FP16 and FP4" in out
+    assert "Simulate conversion between BF16 and FP4" in out
+    assert out.count("PASS") == 2 and "FAIL" not in out and "status" not in out, out
+
+
 @pytest.mark.parametrize("size", [512, 4096])
 def test_gemv_reference_driver_runs_clean(size):
     """The reference's own main.cu (option parsing, prints) linked with this
