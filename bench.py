@@ -583,6 +583,45 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
                                       0).reshape(cols, c["K"]))
         sample = f"{cols} of {c['N']} output features (dequantise + fp64 product)"
         c = dict(c, bytes=c["bytes"] * cols / c["N"])
+    elif name.startswith("fused_"):
+        rows = 1024  # output pairs of the sample
+        kw = (dict(absmax=c["absmax"][:2 * rows * c["n"] // 64], lut16=c["lut"], blocksize=64)
+              if c["fmt"] == "nf4" else dict(scale=c["scale"], zero_point=c["zp"]))
+        mat = np.ascontiguousarray(c["mat"][:2 * rows])
+        fn = lambda: O.gemv_fused_f64(c["fmt"], mat, c["x"], c["gamma"], 1e-5, rows, 1, **kw)
+        sample = f"{rows} of {c['rows_out']} outputs (fp64 oracle)"
+        c = dict(c, bytes=c["bytes"] * rows / c["rows_out"])
+    elif name.startswith("mxfp4"):
+        n = 1 << 22
+        xs = np.ascontiguousarray(c["x"][:n]).view(np.uint16)
+        fn = (lambda: O.mxfp4_quantize(xs)) if c["pack"] else (lambda: O.mxfp4_qdq(xs))
+        sample = f"{n} of {c['numel']} values"
+        c = dict(c, bytes=c["bytes"] * n / c["numel"])
+    elif name == "zero_point":
+        n = 1 << 22
+        lo, hi = np.ascontiguousarray(c["lo"][:n]), np.ascontiguousarray(c["hi"][:n])
+        if O.ref_zero_point(lo[:8], hi[:8], -127, 127, True) is not None:
+            kind, threads = "reference", 1
+            fn = lambda: O.ref_zero_point(lo, hi, -127, 127, True)
+        else:
+            threads = 1
+            fn = lambda: O.zero_point(lo, hi, -127, 127, True)
+        sample = f"{n} of {c['size']} channels, one thread (the host function is serial)"
+        c = dict(c, bytes=c["bytes"] * n / c["size"])
+    elif name == "nf4_quantize":
+        n = c["n"] // 8
+        w = c["W"][:n].astype(np.float32)
+        threads = 1
+        fn = lambda: O.nf4_quantize(w, c["bs"], c["lut"], 0)
+        sample = f"{n} of {c['n']} weights, one thread"
+        c = dict(c, bytes=c["bytes"] / 8)
+    elif name in ("q3_quantize", "bcq_quantize"):
+        cols = 512
+        w = np.ascontiguousarray(c["W"][:, :cols]).astype(np.float32)
+        fn = (lambda: O.q3_quantize(w)) if name == "q3_quantize" else \
+            (lambda: O.lutgemm_quantize(w, 3, 128, True))
+        sample = f"{cols} of {c['N']} output columns"
+        c = dict(c, bytes=c["bytes"] * cols / c["N"])
     else:
         raise SystemExit(f"no CPU baseline for {name}")
     fn()
