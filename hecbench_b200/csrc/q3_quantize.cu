@@ -20,8 +20,9 @@
 //  2. quantize and pack: a warp owns 32 rows x 128 columns, a lane 4 columns; the
 //     quotient by the column's scale is a product with the correctly rounded
 //     reciprocal and one fused residual correction (the correctly rounded
-//     quotient); 8 rows at a time become 24 bits that are merged into the three
-//     words of the group; one 128-bit store per word row.
+//     quotient), its rounding to an integer one addition of 1.5 * 2^23; 8 rows at
+//     a time become 24 bits that are merged into the three words of the group;
+//     one 128-bit store per word row.
 #include <cuda_bf16.h>
 
 #include <algorithm>
@@ -143,7 +144,9 @@ q3_minmax_kernel(const void* __restrict__ W, int K, int N, int rows_per_cta,
 }
 
 struct ColumnParams {
-  float scale, rcp, zero_int;
+  float scale, rcp, zero;  // zero: the integer zero point as rint left it (a zero keeps its sign)
+  int zero_int;
+  bool plain;  // the scale is too small or too large for the corrected product: divide
 };
 __device__ __forceinline__ ColumnParams column_params(float lo, float hi) {
   lo = fminf(lo, 0.f);
@@ -155,27 +158,111 @@ __device__ __forceinline__ ColumnParams column_params(float lo, float hi) {
   ColumnParams p;
   p.scale = (hi - lo) / 7.f;
   p.rcp = 1.f / p.scale;
-  p.zero_int = rintf(-lo / p.scale);
+  p.zero = rintf(-lo / p.scale);
+  p.zero_int = (int)p.zero;
+  p.plain = !(p.scale >= 0x1p-60f && p.scale <= 0x1p60f);
   return p;
 }
-// w / scale, correctly rounded: q' = q + (w - q * scale) * RN(1 / scale)
-__device__ __forceinline__ float quotient(float w, const ColumnParams& p) {
-  if (!(fabsf(w) >= 0x1p-60f && fabsf(w) <= 0x1p100f && p.scale >= 0x1p-60f && p.scale <= 0x1p60f))
-    return w / p.scale;  // the residual could underflow or overflow: divide
-  const float q = w * p.rcp;
-  return fmaf(fmaf(-q, p.scale, w), p.rcp, q);
+// clamp(rint(w / scale) + z, 0, 7).  The quotient is the corrected product q' = q +
+// (w - q * scale) * RN(1 / scale), i.e. the correctly rounded w / scale: every
+// weight of the column lies within 7 scales of zero, so nothing overflows, and
+// where the residual would underflow (|w| below 2^-87 with a scale of at least
+// 2^-60) the quotient is below 2^-27 and rounds to 0 whatever its last bit.  The
+// rounding to an integer is the addition of 1.5 * 2^23, which leaves rint(q) in
+// the low mantissa bits.
+template <bool PLAIN>
+__device__ __forceinline__ uint32_t code_of(float w, const ColumnParams& p) {
+  float q;
+  if (PLAIN) {
+    q = w / p.scale;
+  } else {
+    q = w * p.rcp;
+    q = fmaf(fmaf(-q, p.scale, w), p.rcp, q);
+  }
+  const int r = __float_as_int(q + 12582912.f) - 0x4b400000 + p.zero_int;
+  return (uint32_t)min(max(r, 0), 7);
 }
 
-// pass 2: a warp packs rows 32 g .. 32 g + 31 of 128 columns
+// four adjacent weights as they lie in memory, and as fp32
+template <int DTYPE>
+struct Raw4 {
+  uint4 v;  // fp32: all of it; 16-bit types: x and y
+};
+template <int DTYPE>
+__device__ __forceinline__ Raw4<DTYPE> load_raw4(const void* W, size_t e, size_t total) {
+  Raw4<DTYPE> r;
+  r.v = make_uint4(0, 0, 0, 0);
+  if (DTYPE == HQ_DTYPE_F32) {
+    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(W) + e);
+    if (HQ_IN_BOUNDS(p, 16, W, total * 4, 901)) r.v = ldg_stream_u4(p);
+  } else {
+    const unsigned short* p = reinterpret_cast<const unsigned short*>(W) + e;
+    if (HQ_IN_BOUNDS(p, 8, W, total * 2, 903)) {
+      const uint2 a = ldg_stream_u2(p);
+      r.v.x = a.x;
+      r.v.y = a.y;
+    }
+  }
+  return r;
+}
+template <int DTYPE>
+__device__ __forceinline__ void widen4(const Raw4<DTYPE>& r, float (&w)[4]) {
+  if (DTYPE == HQ_DTYPE_F32) {
+    w[0] = __uint_as_float(r.v.x); w[1] = __uint_as_float(r.v.y);
+    w[2] = __uint_as_float(r.v.z); w[3] = __uint_as_float(r.v.w);
+  } else if (DTYPE == HQ_DTYPE_BF16) {
+    w[0] = __uint_as_float(r.v.x << 16); w[1] = __uint_as_float(r.v.x & 0xffff0000u);
+    w[2] = __uint_as_float(r.v.y << 16); w[3] = __uint_as_float(r.v.y & 0xffff0000u);
+  } else {
+    const float2 a = __half22float2(u32_as_half2(r.v.x)), b = __half22float2(u32_as_half2(r.v.y));
+    w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
+  }
+}
+
+// the codes of RB rows x 4 columns (rows b0 .. b0 + RB - 1 of the group) merged
+// into the columns' 96 bits
+template <int DTYPE, int RB, bool PLAIN>
+__device__ __forceinline__ void pack_rows(const Raw4<DTYPE> (&raw)[RB], int b0, const ColumnParams (&cp)[4],
+                                          unsigned long long (&low)[4], uint32_t (&high)[4]) {
+#pragma unroll
+  for (int sb = 0; sb < RB / 8; sb++) {  // 8 rows = 24 bits at bit 24 b
+    uint32_t v[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      float w[4];
+      widen4<DTYPE>(raw[sb * 8 + r], w);
+#pragma unroll
+      for (int c = 0; c < 4; c++) v[c] |= code_of<PLAIN>(w[c], cp[c]) << (3 * r);
+    }
+    const int b = b0 / 8 + sb;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      if (b < 2) low[c] |= (unsigned long long)v[c] << (24 * b);
+      if (b == 2) {
+        low[c] |= (unsigned long long)v[c] << 48;
+        high[c] |= v[c] >> 16;
+      }
+      if (b == 3) high[c] |= v[c] << 8;
+    }
+  }
+}
+
+// pass 2: a warp packs rows 32 g .. 32 g + 31 of 128 columns.  16-bit inputs: all
+// 32 rows of the lane's four columns are requested before the first is used
+// (256 bytes per lane in flight); fp32 inputs: 8 rows at a time.
 template <int DTYPE>
 __global__ void __launch_bounds__(kThreads)
 q3_pack_kernel(const void* __restrict__ W, int K, int N, const uint32_t* __restrict__ keys,
                int32_t* __restrict__ mat, float* __restrict__ scales, float* __restrict__ zeros) {
+  constexpr int RB = DTYPE == HQ_DTYPE_F32 ? 8 : 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = blockIdx.x * 128 + lane * 4;
   const int g = blockIdx.y * kWarps + warp;  // K group of this warp
   if (col >= N || g * 32 >= K) return;
   const size_t total = (size_t)K * N;
+  Raw4<DTYPE> raw[RB];
+#pragma unroll
+  for (int r = 0; r < RB; r++) raw[r] = load_raw4<DTYPE>(W, (size_t)(g * 32 + r) * N + col, total);
   ColumnParams cp[4];
 #pragma unroll
   for (int c = 0; c < 4; c++)
@@ -186,32 +273,21 @@ q3_pack_kernel(const void* __restrict__ W, int K, int N, const uint32_t* __restr
           make_float4(cp[0].scale, cp[1].scale, cp[2].scale, cp[3].scale);
     if (HQ_IN_BOUNDS(zeros + col, 16, zeros, (size_t)N * 4, 907))
       *reinterpret_cast<float4*>(zeros + col) =
-          make_float4(cp[0].scale * cp[0].zero_int, cp[1].scale * cp[1].zero_int,
-                      cp[2].scale * cp[2].zero_int, cp[3].scale * cp[3].zero_int);
+          make_float4(cp[0].scale * cp[0].zero, cp[1].scale * cp[1].zero, cp[2].scale * cp[2].zero,
+                      cp[3].scale * cp[3].zero);
   }
+  const bool plain = cp[0].plain || cp[1].plain || cp[2].plain || cp[3].plain;
   unsigned long long low[4] = {0, 0, 0, 0};  // bits 0 .. 63 of each column's 96
   uint32_t high[4] = {0, 0, 0, 0};           // bits 64 .. 95
 #pragma unroll
-  for (int b = 0; b < 4; b++) {  // 8 rows = 24 bits at bit 24 b
-    float w[8][4];
+  for (int b0 = 0; b0 < 32; b0 += RB) {
+    if (b0 > 0) {
 #pragma unroll
-    for (int r = 0; r < 8; r++)
-      load_cols<DTYPE, 4>(W, (size_t)(g * 32 + b * 8 + r) * N + col, total, w[r]);
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-      uint32_t v = 0;
-#pragma unroll
-      for (int r = 0; r < 8; r++) {
-        const float q = fminf(fmaxf(rintf(quotient(w[r][c], cp[c])) + cp[c].zero_int, 0.f), 7.f);
-        v |= (uint32_t)q << (3 * r);
-      }
-      if (b < 2) low[c] |= (unsigned long long)v << (24 * b);
-      if (b == 2) {
-        low[c] |= (unsigned long long)v << 48;
-        high[c] |= v >> 16;
-      }
-      if (b == 3) high[c] |= v << 8;
+      for (int r = 0; r < RB; r++)
+        raw[r] = load_raw4<DTYPE>(W, (size_t)(g * 32 + b0 + r) * N + col, total);
     }
+    if (plain) pack_rows<DTYPE, RB, true>(raw, b0, cp, low, high);
+    else pack_rows<DTYPE, RB, false>(raw, b0, cp, low, high);
   }
   int32_t* out = mat + (size_t)(3 * g) * N + col;
   const size_t mat_bytes = (size_t)(K / 32) * 3 * N * 4;

@@ -417,14 +417,15 @@ int hq_q3_quantize(const void* W, int dtype, int K, int N, int32_t* mat, float* 
 /* Greedy binary-coding quantizer: produces what hq_lutgemm_nqmv consumes (the
  * layouts of src/lut-gemm-cuda/main.cu:27-30,118-134; the reference tree holds only
  * that consumer).  W: K x M weights, row-major (input k, output m), of type dtype.
- * Per output m and group of group_size consecutive inputs, in fp32 with sums
- * taken in ascending k: q_bias = half(mean) (q_bias_half == NULL: no offsets, the
+ * Per output m and group of group_size consecutive inputs, in fp32 (a sum over a
+ * group = one sum per 32 consecutive inputs, ascending, those partial sums added
+ * in ascending order): q_bias = half(mean) (q_bias_half == NULL: no offsets, the
  * mean stays in the residual); r = w - q_bias; for each of the nb planes alpha =
  * half(mean |r|), bit = (r >= 0), r -= +-alpha (the rounded value).  bW:
  * uint32[K / 32][nb][M], bit t of a word = input 32 * row + t; alpha_half:
  * half[K / group_size][nb][M]; q_bias_half: half[K / group_size][M].
- * 1 <= nb <= 8, group_size % 32 == 0 (at most 448 for the shared-memory tile),
- * K % group_size == 0, M % 8 == 0, W 16-byte aligned. */
+ * 1 <= nb <= 8, group_size % 32 == 0 and at most 512, K % group_size == 0,
+ * M % 8 == 0, W and bW 16-byte aligned. */
 int hq_lutgemm_quantize(const void* W, int dtype, int K, int M, int nb, int group_size,
                         uint32_t* bW, void* alpha_half, void* q_bias_half, hq_stream_t stream);
 

@@ -466,9 +466,19 @@ void orc_lutgemm_dequant_f32(const uint32_t* bW, const uint16_t* alpha,
 
 /* Greedy binary-coding quantizer, W[K][M] fp32 (widened weights) -> the layouts
  * above.  No counterpart in the reference tree (it holds only the consumer).  Per
- * column and group, fp32, sums in ascending k: q_bias = half(mean) (when asked
- * for); r = w - q_bias; per plane alpha = half(mean |r|), bit = r >= 0, r -=
- * +-alpha (the rounded value). */
+ * column and group, fp32: q_bias = half(mean) (when asked for); r = w - q_bias;
+ * per plane alpha = half(mean |r|), bit = r >= 0, r -= +-alpha (the rounded
+ * value).  A sum over a group is one sum per 32 consecutive inputs (ascending k)
+ * and those partial sums added in ascending order. */
+static float bcq_group_sum(const float* r, int n, int magnitude) {
+  float s = 0.f;
+  for (int k0 = 0; k0 < n; k0 += 32) {
+    float p = 0.f;
+    for (int k = k0; k < k0 + 32; k++) p += magnitude ? fabsf(r[k]) : r[k];
+    s += p;
+  }
+  return s;
+}
 void orc_lutgemm_quantize(const float* W, int K, int M, int nb, int group_size, uint32_t* bW,
                           uint16_t* alpha, uint16_t* q_bias) {
   const int G = K / group_size;
@@ -479,17 +489,13 @@ void orc_lutgemm_quantize(const float* W, int K, int M, int nb, int group_size, 
     for (int g = 0; g < G; g++) {
       for (int k = 0; k < group_size; k++) r[k] = W[(size_t)(g * group_size + k) * M + m];
       if (q_bias) {
-        float s = 0.f;
-        for (int k = 0; k < group_size; k++) s += r[k];
-        const uint16_t bh = orc_f2h(s / (float)group_size);
+        const uint16_t bh = orc_f2h(bcq_group_sum(r, group_size, 0) / (float)group_size);
         q_bias[(size_t)g * M + m] = bh;
         const float bias = orc_h2f(bh);
         for (int k = 0; k < group_size; k++) r[k] = r[k] - bias;
       }
       for (int b = 0; b < nb; b++) {
-        float s = 0.f;
-        for (int k = 0; k < group_size; k++) s += fabsf(r[k]);
-        const uint16_t ah = orc_f2h(s / (float)group_size);
+        const uint16_t ah = orc_f2h(bcq_group_sum(r, group_size, 1) / (float)group_size);
         alpha[((size_t)g * nb + b) * M + m] = ah;
         const float a = orc_h2f(ah);
         for (int k = 0; k < group_size; k++) {

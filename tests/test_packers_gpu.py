@@ -197,7 +197,7 @@ def test_q3_quantize_argument_errors(hq, dev):
 @pytest.mark.parametrize("dtype", ["float16", "bfloat16", "float32"])
 @pytest.mark.parametrize("K,M,nb,gs,bias", [(128, 128, 3, 128, True), (256, 136, 4, 64, True),
                                             (512, 1024, 1, 32, False), (1024, 264, 3, 256, False),
-                                            (384, 8, 8, 128, True)])
+                                            (384, 8, 8, 128, True), (1024, 72, 2, 512, True)])
 def test_bcq_quantize_against_oracle(hq, oracle, dev, dtype, K, M, nb, gs, bias):
     """Sign planes, scales and offsets bit for bit; columns of zeros and of one value
     (zero residuals: the bit of a zero is 1)."""
@@ -256,7 +256,7 @@ def test_bcq_quantize_argument_errors(hq, dev):
     assert lib.hq_lutgemm_quantize(p(w), 0, 128, 16, 9, 128, p(b), p(a), None, None) == -1
     assert lib.hq_lutgemm_quantize(p(w), 0, 128, 16, 3, 128, None, p(a), None, None) == -2
     assert lib.hq_lutgemm_quantize(p(w), 5, 128, 16, 3, 128, p(b), p(a), None, None) == -6
-    assert lib.hq_lutgemm_quantize(p(w), 0, 1024, 16, 3, 512, p(b), p(a), None, None) == -6
+    assert lib.hq_lutgemm_quantize(p(w), 0, 1024, 16, 3, 1024, p(b), p(a), None, None) == -6
     torch.cuda.synchronize()
 
 
