@@ -59,12 +59,9 @@ __device__ __forceinline__ float block_sum(float v, float* buf, int lane, int wa
 template <int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_fused_kernel(const FusedParams p) {
-  extern __shared__ __align__(16) unsigned char dsm_raw[];
-  // 4-bit formats: [pad up to shared address kLutImm] table | inputs;  else: inputs
+  extern __shared__ __align__(16) unsigned char dsm_raw[];  // the inputs
   __shared__ float s_part[kWarps];
-  unsigned char* dsm = dsm_raw;
-  if (BITS == 4) dsm = dsm_raw + (kLutImm - smem_u32(dsm_raw)) + kLutBytes;
-  __half* xs = reinterpret_cast<__half*>(dsm);
+  __half* xs = reinterpret_cast<__half*>(dsm_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int kPieces = BITS == 16 ? 1 : 16 / BITS;  // 16-byte pieces of inputs per chunk
   const int n = p.n;
@@ -75,9 +72,6 @@ gemv_fused_kernel(const FusedParams p) {
   // Programmatic dependent launch: nothing that earlier work of the stream may
   // have produced is read, and nothing is written, before the wait.
   pdl_launch_dependents();
-  if (BITS == 4) {
-    build_nibble_table(dsm - kLutBytes, [](int k) { return (float)k; }, true, tid, kThreads);
-  }
   pdl_wait();
 
   // ---- RMSNorm: sum of squares over the whole vector ----
@@ -117,8 +111,8 @@ gemv_fused_kernel(const FusedParams p) {
       }
       v = make_uint4(h[0], h[1], h[2], h[3]);
     }
-    // 16-byte piece q of chunk c goes to [q][c]
-    reinterpret_cast<uint4*>(xs)[(i % kPieces) * chunks + i / kPieces] = v;
+    // 16-byte piece q of chunk c goes to [q][c] (int4: in the order of its conversion)
+    reinterpret_cast<uint4*>(xs)[(i % kPieces) * chunks + i / kPieces] = BITS == 4 ? pair_inputs(v) : v;
     const float2 f0 = __half22float2(u32_as_half2(v.x)), f1 = __half22float2(u32_as_half2(v.y)),
                  f2 = __half22float2(u32_as_half2(v.z)), f3 = __half22float2(u32_as_half2(v.w));
     part += ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
@@ -126,7 +120,6 @@ gemv_fused_kernel(const FusedParams p) {
   const float sumx = block_sum(part, s_part, lane, warp);  // also: table and inputs complete
 
   // ---- row pairs of this warp ----
-  const uint32_t lane4 = (uint32_t)lane * 4u;
   const int warps_total = gridDim.x * kWarps;
   constexpr int kPerRow = kInFlight / kRows;
   const size_t mat_bytes = (size_t)rows_mat * row_bytes;
@@ -155,7 +148,7 @@ gemv_fused_kernel(const FusedParams p) {
         const int c = c0 + 32 * u;
         if (c < chunks) {
           float part2[kRows];
-          chunk_dot<BITS, kRows>(w[u], reinterpret_cast<const uint4*>(xs) + c, chunks, lane4, part2);
+          chunk_dot<BITS, kRows>(w[u], reinterpret_cast<const uint4*>(xs) + c, chunks, part2);
 #pragma unroll
           for (int r = 0; r < kRows; r++)
             acc[r] += part2[r];
@@ -191,11 +184,7 @@ int launch(FusedParams prm, hq_stream_t stream) {
     return HQ_ERR_BAD_SHAPE;
   if (!aligned16(prm.mat) || !aligned16(prm.x) || (prm.gamma && !aligned16(prm.gamma)))
     return HQ_ERR_MISALIGNED;
-  size_t smem = (size_t)prm.n * 2;
-  if (BITS == 4) {
-    if (reserved_smem_per_block() > kLutImm) return HQ_ERR_UNSUPPORTED;
-    smem += (size_t)kLutImm + kLutBytes;
-  }
+  const size_t smem = (size_t)prm.n * 2;
   if (smem > 226 * 1024) return HQ_ERR_TOO_LARGE;  // beyond 113 KiB only one CTA fits an SM
   constexpr auto kern = gemv_fused_kernel<BITS>;
   const cudaError_t e = ensure_dynamic_smem<kern>(smem);

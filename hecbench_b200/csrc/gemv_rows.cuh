@@ -12,18 +12,6 @@ constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 constexpr int kInFlight = 8;            // 16-byte loads per lane in flight
 constexpr int kRows = 2;                // adjacent rows a warp works on at a time
-constexpr int kLutImm = 2048;           // shared-window address of the int4 table
-constexpr int kLutBytes = 256 * 256;    // 256 rows of 256 bytes (first 128: one copy per bank)
-
-template <int IMM>
-__device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
-  uint32_t v;  // not volatile: the table is constant after the prologue barrier
-  asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
-  return v;
-}
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
 __device__ __forceinline__ float sum4(__half2 a0, __half2 a1, __half2 a2, __half2 a3) {
   const float2 f = __half22float2(__hadd2(__hadd2(a0, a1), __hadd2(a2, a3)));
   return f.x + f.y;
@@ -39,7 +27,7 @@ __device__ __forceinline__ float sum4(__half2 a0, __half2 a1, __half2 a2, __half
 // the same banks two or four at a time).
 template <int BITS, int R>
 __device__ __forceinline__ void chunk_dot(const uint4 (&w)[R], const uint4* xs, int pitch,
-                                          uint32_t lane4, float (&part)[R]) {
+                                          float (&part)[R]) {
   if (BITS == 16) {
     const uint4 x = xs[0];
 #pragma unroll
@@ -75,6 +63,14 @@ __device__ __forceinline__ void chunk_dot(const uint4 (&w)[R], const uint4* xs, 
       part[r] = sum4(a0, a1, a2, a3);
     }
   } else {
+    // A word holds 8 nibbles = elements 0 .. 7.  (w & 0x000f000f) | 0x64006400 is
+    // half2(1024 + e0, 1024 + e4), (w & 0x00f000f0) | 0x64006400 is half2(1024 +
+    // 16 e1, 1024 + 16 e5); w >> 8 brings e2, e6 and e3, e7 to the same places.
+    // One subtraction of 1024, or one fused x / 16 - 64, leaves the integers,
+    // exactly: two logic operations and one fp16 instruction per two weights, no
+    // table.  The inputs are staged in the matching order (pair_inputs).
+    const __half2 k1024 = __float2half2_rn(1024.f), k16th = __float2half2_rn(0.0625f),
+                  km64 = __float2half2_rn(-64.f);
     __half2 a[R][4];
 #pragma unroll
     for (int r = 0; r < R; r++) a[r][0] = a[r][1] = a[r][2] = a[r][3] = __float2half2_rn(0.f);
@@ -84,15 +80,15 @@ __device__ __forceinline__ void chunk_dot(const uint4 (&w)[R], const uint4* xs, 
 #pragma unroll
       for (int r = 0; r < R; r++) {
         const uint32_t wi = i == 0 ? w[r].x : i == 1 ? w[r].y : i == 2 ? w[r].z : w[r].w;
-        // byte k of the word -> (byte << 8) | lane*4: bytes {lane4.0, w.k, 0, 0}
-        const uint32_t l0 = lds_u32_imm<kLutImm>(__byte_perm(wi, lane4, 0x7604));
-        const uint32_t l1 = lds_u32_imm<kLutImm>(__byte_perm(wi, lane4, 0x7614));
-        const uint32_t l2 = lds_u32_imm<kLutImm>(__byte_perm(wi, lane4, 0x7624));
-        const uint32_t l3 = lds_u32_imm<kLutImm>(__byte_perm(wi, lane4, 0x7634));
-        a[r][0] = __hfma2(u32_as_half2(l0), u32_as_half2(x.x), a[r][0]);
-        a[r][1] = __hfma2(u32_as_half2(l1), u32_as_half2(x.y), a[r][1]);
-        a[r][2] = __hfma2(u32_as_half2(l2), u32_as_half2(x.z), a[r][2]);
-        a[r][3] = __hfma2(u32_as_half2(l3), u32_as_half2(x.w), a[r][3]);
+        const uint32_t hi = wi >> 8;
+        const __half2 e04 = __hsub2(u32_as_half2((wi & 0x000f000fu) | 0x64006400u), k1024);
+        const __half2 e15 = __hfma2(u32_as_half2((wi & 0x00f000f0u) | 0x64006400u), k16th, km64);
+        const __half2 e26 = __hsub2(u32_as_half2((hi & 0x000f000fu) | 0x64006400u), k1024);
+        const __half2 e37 = __hfma2(u32_as_half2((hi & 0x00f000f0u) | 0x64006400u), k16th, km64);
+        a[r][0] = __hfma2(e04, u32_as_half2(x.x), a[r][0]);
+        a[r][1] = __hfma2(e15, u32_as_half2(x.y), a[r][1]);
+        a[r][2] = __hfma2(e26, u32_as_half2(x.z), a[r][2]);
+        a[r][3] = __hfma2(e37, u32_as_half2(x.w), a[r][3]);
       }
     }
 #pragma unroll
@@ -100,24 +96,11 @@ __device__ __forceinline__ void chunk_dot(const uint4 (&w)[R], const uint4* xs, 
   }
 }
 
-
-// The 256-row byte table of the 4-bit formats: row b (256 bytes apart, 32 copies
-// of one word in its first 128 bytes, one per bank) holds half2(first element,
-// second element) of byte b.  level_of(k) = the value code k stands for;
-// low_first: element 2j is the low nibble of byte j (else the high nibble).
-template <class LevelOf>
-__device__ __forceinline__ void build_nibble_table(unsigned char* lut, LevelOf level_of,
-                                                    bool low_first, int tid, int nthreads) {
-  for (int e4 = tid; e4 < 256 * 4; e4 += nthreads) {
-    const int entry = e4 >> 2, quarter = e4 & 3;  // four threads per 128-byte table row
-    const int lo = entry & 15, hi = entry >> 4;
-    const float first = level_of(low_first ? lo : hi), second = level_of(low_first ? hi : lo);
-    const uint32_t u = half2_as_u32(__floats2half2_rn(first, second));
-    const uint4 u4 = make_uint4(u, u, u, u);
-    uint4* row = reinterpret_cast<uint4*>(lut + (size_t)entry * 256 + quarter * 32);
-    row[0] = u4;
-    row[1] = u4;
-  }
+// 8 consecutive inputs (x0,x1)(x2,x3)(x4,x5)(x6,x7) in the order the 4-bit
+// conversion above produces its weights: (x0,x4)(x1,x5)(x2,x6)(x3,x7)
+__device__ __forceinline__ uint4 pair_inputs(const uint4& v) {
+  return make_uint4(__byte_perm(v.x, v.z, 0x5410), __byte_perm(v.x, v.z, 0x7632),
+                    __byte_perm(v.y, v.w, 0x5410), __byte_perm(v.y, v.w, 0x7632));
 }
 
 }  // namespace rows

@@ -21,10 +21,12 @@
 //    permute places two of them under the exponent byte 0x64 (1024 + b + 128,
 //    exact), one half2 subtract of 1152 leaves the integers, one half2 fma
 //    multiplies with the inputs: 7 instructions per 4 weights.
-//  * int4: byte -> half2(low nibble, high nibble) through a 256-row table held
-//    once per bank (row stride 256 bytes at a fixed shared address, so the
-//    lookup address is one byte permute plus an immediate), one half2 fma per
-//    byte: 3 instructions per 2 weights.
+//  * int4: a 32-bit word holds 8 weights; (w & 0x000f000f) | 0x64006400 is
+//    half2(1024 + e0, 1024 + e4) and (w & 0x00f000f0) | 0x64006400 is half2(1024 +
+//    16 e1, 1024 + 16 e5) (w >> 8 for the other four); one half2 subtraction, or
+//    one fused x / 16 - 64, leaves the integers exactly: 13 instructions per 8
+//    weights, no table, no shared-memory lookups.  The inputs are staged in the
+//    matching order (x0, x4)(x1, x5)(x2, x6)(x3, x7).
 #include <algorithm>
 
 #include "gemv_rows.cuh"
@@ -39,26 +41,19 @@ template <int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
 gemv_uniform_kernel(const unsigned char* __restrict__ mat, const __half* __restrict__ vec,
                     __half* __restrict__ res, int rows, int n, float scale, float zero_point) {
-  extern __shared__ __align__(16) unsigned char dsm_raw[];
-  // int4: [pad up to shared address kLutImm] table | inputs;  else: inputs
+  extern __shared__ __align__(16) unsigned char dsm_raw[];  // the inputs
   __shared__ float s_part[kWarps];
-  unsigned char* dsm = dsm_raw;
-  if (BITS == 4) dsm = dsm_raw + (kLutImm - smem_u32(dsm_raw)) + kLutBytes;
-  __half* xs = reinterpret_cast<__half*>(dsm);
+  __half* xs = reinterpret_cast<__half*>(dsm_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int kPieces = 16 / BITS == 0 ? 1 : 16 / BITS;  // 16-byte pieces of inputs per chunk
   const size_t row_bytes = (size_t)n * BITS / 8;
   const int chunks = (int)(row_bytes / 16);   // 16-byte chunks per row
 
   // Programmatic dependent launch: the next kernel of the stream may become
-  // resident while this grid drains; the table (no global memory involved) is
-  // built before the wait, everything that earlier work may have produced - the
-  // input vector - is read after it, and nothing is written before it.
+  // resident while this grid drains; everything that earlier work may have
+  // produced - the input vector - is read after the wait, and nothing is written
+  // before it.
   pdl_launch_dependents();
-  if (BITS == 4) {
-    // byte b -> half2(low nibble, high nibble): element 2j sits in the low nibble
-    build_nibble_table(dsm - kLutBytes, [](int k) { return (float)k; }, true, tid, kThreads);
-  }
   pdl_wait();
   // ---- prologue: inputs to shared memory (piece-major) and their sum ----
   float part = 0.f;
@@ -66,8 +61,8 @@ gemv_uniform_kernel(const unsigned char* __restrict__ mat, const __half* __restr
     uint4 v = make_uint4(0, 0, 0, 0);
     if (HQ_IN_BOUNDS(reinterpret_cast<const uint4*>(vec) + i, 16, vec, (size_t)n * 2, 401))
       v = __ldg(reinterpret_cast<const uint4*>(vec) + i);
-    // 16-byte piece p of chunk c goes to [p][c]
-    reinterpret_cast<uint4*>(xs)[(i % kPieces) * chunks + i / kPieces] = v;
+    // 16-byte piece p of chunk c goes to [p][c] (int4: in the order of its conversion)
+    reinterpret_cast<uint4*>(xs)[(i % kPieces) * chunks + i / kPieces] = BITS == 4 ? pair_inputs(v) : v;
     const float2 f0 = __half22float2(u32_as_half2(v.x)), f1 = __half22float2(u32_as_half2(v.y)),
                  f2 = __half22float2(u32_as_half2(v.z)), f3 = __half22float2(u32_as_half2(v.w));
     part += ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
@@ -81,7 +76,6 @@ gemv_uniform_kernel(const unsigned char* __restrict__ mat, const __half* __restr
 
   // ---- rows of this warp: kRows adjacent rows at a time, so that a piece of the
   // input vector read from shared memory serves kRows rows ----
-  const uint32_t lane4 = (uint32_t)lane * 4u;
   const int warps_total = gridDim.x * kWarps;
   constexpr int kPerRow = kInFlight / kRows;  // loads per row and batch
   const size_t mat_bytes = (size_t)rows * row_bytes;
@@ -110,7 +104,7 @@ gemv_uniform_kernel(const unsigned char* __restrict__ mat, const __half* __restr
         const int c = c0 + 32 * u;
         if (c < chunks) {
           float part[kRows];
-          chunk_dot<BITS, kRows>(w[u], reinterpret_cast<const uint4*>(xs) + c, chunks, lane4, part);
+          chunk_dot<BITS, kRows>(w[u], reinterpret_cast<const uint4*>(xs) + c, chunks, part);
 #pragma unroll
           for (int r = 0; r < kRows; r++) acc[r] += part[r];
         }
@@ -133,11 +127,7 @@ int launch(const void* mat, const void* vec_half, void* res_half, int rows, int 
   // 16-byte groups: n a multiple of 8 (fp16), 16 (int8), 32 (int4)
   if (rows <= 0 || n <= 0 || n % (128 / BITS) != 0) return HQ_ERR_BAD_SHAPE;
   if (!aligned16(mat) || !aligned16(vec_half)) return HQ_ERR_MISALIGNED;
-  size_t smem = (size_t)n * 2;
-  if (BITS == 4) {
-    if (reserved_smem_per_block() > kLutImm) return HQ_ERR_UNSUPPORTED;
-    smem += (size_t)kLutImm + kLutBytes;
-  }
+  const size_t smem = (size_t)n * 2;
   if (smem > 226 * 1024) return HQ_ERR_TOO_LARGE;  // beyond 113 KiB only one CTA fits an SM
   constexpr auto kern = gemv_uniform_kernel<BITS>;
   const cudaError_t e = ensure_dynamic_smem<kern>(smem);
