@@ -116,6 +116,7 @@ nf4_quantize_kernel(const void* __restrict__ W, size_t nvec, int blocksize,
                     float* __restrict__ absmax) {
   __shared__ __align__(16) unsigned char s_cells[kCells * kCellStride];
   __shared__ float s_mid[16];
+  __shared__ float2 s_cell[kCells];
   __shared__ int s_dense;
   const int tid = threadIdx.x, lane = tid & 31;
   if (tid < 15) s_mid[tid] = 0.5f * (__ldg(lut16 + tid) + __ldg(lut16 + tid + 1));
@@ -131,10 +132,12 @@ nf4_quantize_kernel(const void* __restrict__ W, size_t nvec, int blocksize,
       else if (m < hi) { inside++; mid = m; }
     }
     if (inside > 1) s_dense = 1;
-    // the last cell also stands for everything above it, the first for everything below
-    const float2 e = make_float2(__uint_as_float(below), mid);
-    for (int l = 0; l < 32; l++) *reinterpret_cast<float2*>(s_cells + c * kCellStride + l * 8) = e;
+    s_cell[c] = make_float2(__uint_as_float(below), mid);
   }
+  __syncthreads();
+  // one copy per bank, written by all threads
+  for (int i = tid; i < kCells * 32; i += kThreads)
+    *reinterpret_cast<float2*>(s_cells + (i >> 5) * kCellStride + (i & 31) * 8) = s_cell[i >> 5];
   __syncthreads();
   const bool dense = s_dense != 0;
   const bool lf = low_first != 0;
@@ -205,7 +208,8 @@ int launch(const void* W, size_t n, int blocksize, const float* lut16, int flags
   const int low = (flags & HQ_NF4_LOW_NIBBLE_FIRST) ? 1 : 0;
   auto* b32 = reinterpret_cast<uint32_t*>(B);
   const size_t want = (nvec + kThreads - 1) / kThreads;
-  const int grid = (int)std::min<size_t>(want, (size_t)sm_count() * 8);
+  // every CTA builds the table once: no more CTAs than are resident together
+  const int grid = (int)std::min<size_t>(want, (size_t)sm_count() * 4);
 #define HQ_GO(LPB_)                                                                          \
   nf4_quantize_kernel<DTYPE, LPB_><<<grid, kThreads, 0, st>>>(W, nvec, blocksize, lut16, low, b32, \
                                                               absmax)
