@@ -34,11 +34,15 @@ def _ll_call(lib, *, A=None, A_ll=0, a_stride=1, B, absmax, lut, out=None, N, K,
         max_polls, status.data_ptr(), _stream())
 
 
-def test_ll_packets_chain_two_layers(hq, oracle, dev):
+@pytest.mark.parametrize("pairs", [False, True])
+def test_ll_packets_chain_two_layers(hq, oracle, dev, monkeypatch, pairs):
     """Layer 1 (4096 x 4096) writes packets; layer 2 (512 x 4096) reads its input
     from those packets; three rounds over two alternating packet vectors, so later
-    rounds meet the packets of earlier ones."""
+    rounds meet the packets of earlier ones.  pairs: the opt-in form that sends two
+    neighbouring rows in one 16-byte store."""
     import torch
+    if pairs:
+        monkeypatch.setenv("HQ_LL_PAIRS", "1")
     lib = hq.load_library()
     N1, K1, N2, bs = 4096, 4096, 512, 64
     A, B1, a1, lut = synth.nf4_case(N1, K1, bs, seed=21)
