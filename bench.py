@@ -1152,6 +1152,9 @@ def main():
                    "publish": "slices copied into every GPU's gathered buffer by our own kernel "
                               "(peer stores over NVLink + flags), bounded wait after every layer",
                    "nccl": "NCCL all-gather of the slices after every layer"}[gather]
+            if packets is not None and packets.multicast:
+                how += ("; each packet is ONE multimem.st through the NVSwitch multicast mapping of "
+                        "the vector (HQ_LL_MULTICAST=0: one store per GPU)")
             par = (f"output features sharded over {world} GPUs ({args.scaling} scaling), "
                    f"gather '{gather}': {how}")
         line = {

@@ -151,6 +151,7 @@ struct GemvParams {
   long long a_stride;
   unsigned* sync_words;         // local: [0] CTAs finished, [1] epoch of the latest completed gather
   int world, rank;
+  int multicast;                // peer_ll[0] is a multicast address: one multimem.st per result
   long long gather_offset;
   unsigned max_polls;           // limit of every wait for a packet, in polls
   // buffer extents in bytes, used only by the index-checked build
@@ -189,6 +190,11 @@ __device__ __forceinline__ uint2 ld_packet(const uint2* p) {
   uint2 v;
   asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
   return v;
+}
+// one store that the NVSwitch delivers to every GPU of the multicast group
+__device__ __forceinline__ void st_packet_multicast(uint2* p, uint32_t value, uint32_t epoch) {
+  const unsigned long long v = ((unsigned long long)epoch << 32) | value;
+  asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ void st_packet(uint2* p, uint32_t value, uint32_t epoch) {
   asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(value), "r"(epoch)
@@ -352,7 +358,8 @@ nf4_gemv_kernel(const GemvParams p) {
   const uint32_t epoch_in =
       p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
   uint2* my_peer = nullptr;  // lane r stores the packets that go to rank r
-  if (p.peer_ll != nullptr && lane < p.world) my_peer = p.peer_ll[lane] + p.gather_offset;
+  if (p.peer_ll != nullptr && lane < (p.multicast ? 1 : p.world))
+    my_peer = p.peer_ll[lane] + p.gather_offset;
   uint4 xr[C][4];
   if (p.A_ll == nullptr) {
 #pragma unroll
@@ -461,7 +468,8 @@ nf4_gemv_kernel(const GemvParams p) {
     if (p.peer_ll == nullptr) {
       if (lane == 0 && HQ_IN_BOUNDS(p.out + n, 2, p.out, p.out_bytes, 104)) p.out[n] = h;
     } else if (my_peer != nullptr) {
-      st_packet(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
+      if (p.multicast) st_packet_multicast(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
+      else st_packet(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
     }
   };
   // results of rows 2 m and 2 m + 1 (kPairPackets), or value and gate of output m
@@ -476,7 +484,10 @@ nf4_gemv_kernel(const GemvParams p) {
         *reinterpret_cast<uint32_t*>(p.out + 2 * m) = h0 | (h1 << 16);
     } else if (my_peer != nullptr) {
       uint2* at = my_peer + 2 * m;
-      if ((reinterpret_cast<uintptr_t>(at) & 15u) == 0) {
+      if (p.multicast) {
+        st_packet_multicast(at, h0, epoch_in + 1u);
+        st_packet_multicast(at + 1, h1, epoch_in + 1u);
+      } else if ((reinterpret_cast<uintptr_t>(at) & 15u) == 0) {
         // each 8-byte half carries its own epoch: the halves may land in any order
         asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(at), "r"(h0),
                      "r"(epoch_in + 1u), "r"(h1), "r"(epoch_in + 1u)
@@ -1154,6 +1165,7 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   prm.a_stride = ll.a_stride;
   prm.sync_words = ll.sync_words;
   prm.world = ll.world;
+  prm.multicast = (ll.peer_ll != nullptr && (flags & HQ_NF4_LL_MULTICAST)) ? 1 : 0;
   prm.rank = ll.rank;
   prm.gather_offset = ll.gather_offset;
   prm.max_polls = ll.max_polls ? ll.max_polls : kDefaultPolls;
@@ -1202,7 +1214,7 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   // 10.1 us against 7.8 us for the register pipeline on an 11008 x 4096 layer.
   // It takes rows of 1024 .. 4096 inputs whose codes and absmax runs start on
   // 16-byte boundaries (one warp per row).
-  if (fuse == nullptr && env_flag("HQ_NF4_BULK") && aligned && nchunks % 32 == 0 && cols <= 4 && aligned16(absmax) &&
+  if (fuse == nullptr && !prm.multicast && env_flag("HQ_NF4_BULK") && aligned && nchunks % 32 == 0 && cols <= 4 && aligned16(absmax) &&
       ((nchunks >> shift) * 4) % 16 == 0) {
     int rc;
     switch (cols) {

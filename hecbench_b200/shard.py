@@ -113,13 +113,27 @@ class PacketGather:
     `status` a rank-local word that becomes 1 if a bounded wait ran out.
     """
 
-    def __init__(self, shard: FeatureShard, slots: int, device, group=None, max_polls: int = 0):
+    def __init__(self, shard: FeatureShard, slots: int, device, group=None, max_polls: int = 0,
+                 multicast: bool | None = None):
+        """multicast: write every packet with one multimem.st through the NVSwitch
+        multicast mapping of the buffer instead of one store per GPU (None: when the
+        allocation has such a mapping and HQ_LL_MULTICAST is not 0)."""
+        import os
         if slots < 2:
             raise ValueError("a chain of gathers needs at least two packet vectors to alternate")
         self.shard, self.slots, self.max_polls = shard, slots, max_polls
         self.slot_elems = shard.world * shard.n_local
         self.buf, self.handle, ptrs = _symmetric(slots * self.slot_elems * 8, device, group)
         self._ptrs = ptrs
+        mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0) if shard.world > 1 else 0
+        if multicast is None:
+            multicast = mc_ptr != 0 and os.environ.get("HQ_LL_MULTICAST", "1") != "0"
+        if multicast and mc_ptr == 0:
+            raise RuntimeError("this symmetric-memory allocation has no multicast mapping")
+        self.multicast = bool(multicast)
+        # device arrays holding the multicast address of slot i
+        self.mc_ll = [torch.tensor([mc_ptr + i * self.slot_elems * 8], dtype=torch.int64,
+                                   device=device) for i in range(slots)] if self.multicast else None
         # device arrays of pointers to every rank's copy of slot i
         self.peer_ll = [torch.tensor([p + i * self.slot_elems * 8 for p in ptrs], dtype=torch.int64,
                                      device=device) for i in range(slots)]
@@ -142,14 +156,15 @@ class PacketGather:
         from ._lib import check, load_library
         lib = load_library()
         sh = self.shard
-        flags = nibble_order | (2 if weights_resident else 0)
+        flags = nibble_order | (2 if weights_resident else 0) | (4 if self.multicast else 0)
+        table = self.mc_ll[i] if self.multicast else self.peer_ll[i]
         a_ll = 0
         if a_slot is not None:
             a_ll = self.buf.data_ptr() + (a_slot * self.slot_elems + a_first) * 8
         check("hq_nf4_gemv_f16_ll", lib.hq_nf4_gemv_f16_ll(
             0 if a_slot is not None else A.data_ptr(), a_ll, a_stride, B.data_ptr(),
             absmax.data_ptr(), lut16.data_ptr(), 0, sh.n_local, K, blocksize, flags,
-            self.peer_ll[i].data_ptr(), sh.rank * sh.n_local, self.sync.data_ptr(), sh.world,
+            table.data_ptr(), sh.rank * sh.n_local, self.sync.data_ptr(), sh.world,
             sh.rank, self.max_polls, self.status.data_ptr(),
             torch.cuda.current_stream().cuda_stream))
 

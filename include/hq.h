@@ -94,6 +94,13 @@ int hq_bnb_quantize_u8(const float* code256, const float* A, uint8_t* out, size_
  * preceding kernel of the stream is still finishing (programmatic dependent
  * launch); the input vector is always read after that kernel has completed. */
 #define HQ_NF4_WEIGHTS_RESIDENT 2
+/* hq_nf4_gemv_f16_ll with packet output only: peer_ll[0] is the MULTICAST address
+ * of the packet vector (an NVSwitch multicast mapping that covers the vector on
+ * every GPU of the group, this one included - e.g. the multicast pointer of a
+ * symmetric-memory allocation); every result is then written with ONE
+ * multimem.st that the switch delivers to all GPUs, instead of one store per
+ * GPU.  The other entries of peer_ll are not read. */
+#define HQ_NF4_LL_MULTICAST 4
 
 /* NF4 blockwise dequantize (no counterpart in the reference tree):
  * out[e] = half_rn(lut16[code_e] * absmax[e / blocksize]), n elements, two

@@ -52,7 +52,27 @@ def main():
     dA, dl = t(A), t(lut)
 
     layers, slots = 6, 3
-    pg = PacketGather(sh, slots=slots, device=dev)
+    # the same chain once more through the NVSwitch multicast mapping, where there is one
+    pm = PacketGather(sh, slots=slots, device=dev, multicast=None)
+    if pm.multicast:
+        x_host, worst = A, 0.0
+        for l in range(layers):
+            if l == 0:
+                pm.gemv_nf4(0, dA, Bl, al, dl, K, bs, weights_resident=True)
+            else:
+                pm.gemv_nf4(l % slots, None, Bl, al, dl, K, bs, weights_resident=True,
+                            a_slot=(l - 1) % slots, a_stride=stride)
+            y = pm.unpack(l % slots)
+            torch.cuda.synchronize()
+            yh = y.cpu().numpy()
+            worst = max(worst, O.rel_err(yh.astype(np.float64),
+                                         O.nf4_gemv_f64(x_host, B, absmax, lut, N, K, bs)))
+            x_host = np.ascontiguousarray(yh[::stride][:K])
+            dist.barrier()
+        report["packets by multicast"] = worst
+        if int(pm.status.item()) != 0:
+            report["packets by multicast"] = 1.0
+    pg = PacketGather(sh, slots=slots, device=dev, multicast=False)
     worst = 0.0
     x_host = A
     finals = []
