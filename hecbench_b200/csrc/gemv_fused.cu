@@ -82,7 +82,7 @@ gemv_fused_kernel(const FusedParams p) {
     float sq = 0.f;
     for (int i = tid; i < n / 8; i += kThreads) {
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (HQ_IN_BOUNDS(xg + i, 16, p.x, (size_t)n * 2, 501)) v = __ldg(xg + i);
+      if (HQ_IN_BOUNDS(xg + i, 16, p.x, (size_t)n * 2, 501)) v = ld_dependent_u4(xg + i);
       const uint32_t h[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int k = 0; k < 4; k++) {
@@ -97,7 +97,7 @@ gemv_fused_kernel(const FusedParams p) {
   float part = 0.f;
   for (int i = tid; i < n / 8; i += kThreads) {
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (HQ_IN_BOUNDS(xg + i, 16, p.x, (size_t)n * 2, 502)) v = __ldg(xg + i);
+    if (HQ_IN_BOUNDS(xg + i, 16, p.x, (size_t)n * 2, 502)) v = ld_dependent_u4(xg + i);
     if (p.gamma != nullptr) {
       uint4 g = make_uint4(0, 0, 0, 0);
       if (HQ_IN_BOUNDS(gg + i, 16, p.gamma, (size_t)n * 2, 503)) g = __ldg(gg + i);

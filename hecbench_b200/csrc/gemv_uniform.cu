@@ -60,7 +60,7 @@ gemv_uniform_kernel(const unsigned char* __restrict__ mat, const __half* __restr
   for (int i = tid; i < n / 8; i += kThreads) {
     uint4 v = make_uint4(0, 0, 0, 0);
     if (HQ_IN_BOUNDS(reinterpret_cast<const uint4*>(vec) + i, 16, vec, (size_t)n * 2, 401))
-      v = __ldg(reinterpret_cast<const uint4*>(vec) + i);
+      v = ld_dependent_u4(reinterpret_cast<const uint4*>(vec) + i);
     // 16-byte piece p of chunk c goes to [p][c] (int4: in the order of its conversion)
     reinterpret_cast<uint4*>(xs)[(i % kPieces) * chunks + i / kPieces] = BITS == 4 ? pair_inputs(v) : v;
     const float2 f0 = __half22float2(u32_as_half2(v.x)), f1 = __half22float2(u32_as_half2(v.y)),

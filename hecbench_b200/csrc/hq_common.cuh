@@ -154,6 +154,31 @@ __device__ __forceinline__ uint32_t ldg_stream_u32(const void* p) {
   return v;
 }
 
+// Loads of data that an earlier kernel of the stream may have written (the input
+// vector of a mat-vec), for kernels launched with programmatic dependent launch:
+// they must stay behind griddepcontrol.wait.  A non-coherent load (ld.global.nc,
+// which __ldg and const __restrict__ pointers produce) promises that the data is
+// read-only for the whole kernel, so the assembler may move it above the wait;
+// these are ordinary coherent loads that the compiler may not reorder.
+__device__ __forceinline__ uint4 ld_dependent_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_dependent_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ __half ld_dependent_f16(const __half* p) {
+  unsigned short v;
+  asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(p) : "memory");
+  return __ushort_as_half(v);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -73,13 +73,6 @@ __device__ __forceinline__ float ldg_ordered_f32(const float* p) {
   asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
   return v;
 }
-__device__ __forceinline__ uint4 ldg_ordered_u4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
 
 // 16-byte asynchronous copy global -> shared (no register holds the data)
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
@@ -254,7 +247,9 @@ __device__ __forceinline__ void stage_packets(__half* xs, const uint2* ll, long 
 // FUSE: RMSNorm of the input vector before the product and / or a gated
 // activation of row pairs after it (rmsnorm-cuda/reference.h:4-25,
 // geglu-cuda/reference.h:8-16), see GemvParams; plain fp16 input and output only.
-template <int C, int D, int ST, bool ALIGNED, int THREADS, bool FUSE>
+// LL: packet input and / or packet output (hq_nf4_gemv_f16_ll); the plain
+// instantiations carry none of that code.
+template <int C, int D, int ST, bool ALIGNED, int THREADS, bool FUSE, bool LL>
 __global__ void __launch_bounds__(THREADS, 1)
 nf4_gemv_kernel(const GemvParams p) {
   constexpr int W = THREADS / 32;
@@ -356,19 +351,19 @@ nf4_gemv_kernel(const GemvParams p) {
   // epoch of the latest completed gather: the input packets carry it, the
   // output packets of this launch carry the next one
   const uint32_t epoch_in =
-      p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
+      LL && p.sync_words != nullptr ? *reinterpret_cast<volatile unsigned*>(p.sync_words + 1) : 0u;
   uint2* my_peer = nullptr;  // lane r stores the packets that go to rank r
-  if (p.peer_ll != nullptr && lane < (p.multicast ? 1 : p.world))
-    my_peer = p.peer_ll[lane] + p.gather_offset;
+  const bool packets_out = LL && p.peer_ll != nullptr, packets_in = LL && p.A_ll != nullptr;
+  if (packets_out && lane < (p.multicast ? 1 : p.world)) my_peer = p.peer_ll[lane] + p.gather_offset;
   uint4 xr[C][4];
-  if (p.A_ll == nullptr) {
+  if (!packets_in) {
 #pragma unroll
     for (int i = 0; i < C; i++) {
       const int c = (q * C + i) * 32 + lane;
       const uint4* xp = reinterpret_cast<const uint4*>(p.A) + 4 * (live[i] ? c : 0);
 #pragma unroll
       for (int t = 0; t < 4; t++) {
-        if (live[i] && HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 103)) xr[i][t] = ldg_ordered_u4(xp + t);
+        if (live[i] && HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 103)) xr[i][t] = ld_dependent_u4(xp + t);
         else xr[i][t] = make_uint4(0, 0, 0, 0);
       }
     }
@@ -399,7 +394,7 @@ nf4_gemv_kernel(const GemvParams p) {
     }
   }
   HQ_STAMP(3)
-  if (p.A_ll != nullptr) {
+  if (packets_in) {
     // the whole input arrives as packets: every thread waits for its share and
     // leaves plain fp16 in shared memory
     __half* xs = reinterpret_cast<__half*>(dsm + kLutBytes + (size_t)2 * W * D * 32 * sizeof(float));
@@ -465,7 +460,7 @@ nf4_gemv_kernel(const GemvParams p) {
   float held = 0.f;  // paired, one warp per row: the value row's sum until its gate row is done
   auto store_result = [&](long long n, float v) {
     const __half h = __float2half_rn(v);
-    if (p.peer_ll == nullptr) {
+    if (!packets_out) {
       if (lane == 0 && HQ_IN_BOUNDS(p.out + n, 2, p.out, p.out_bytes, 104)) p.out[n] = h;
     } else if (my_peer != nullptr) {
       if (p.multicast) st_packet_multicast(my_peer + n, (uint32_t)__half_as_ushort(h), epoch_in + 1u);
@@ -479,7 +474,7 @@ nf4_gemv_kernel(const GemvParams p) {
       return;
     }
     const uint32_t h0 = __half_as_ushort(__float2half_rn(v0)), h1 = __half_as_ushort(__float2half_rn(v1));
-    if (p.peer_ll == nullptr) {
+    if (!packets_out) {
       if (lane == 0 && HQ_IN_BOUNDS(p.out + 2 * m, 4, p.out, p.out_bytes, 106))
         *reinterpret_cast<uint32_t*>(p.out + 2 * m) = h0 | (h1 << 16);
     } else if (my_peer != nullptr) {
@@ -559,7 +554,7 @@ nf4_gemv_kernel(const GemvParams p) {
   }
   HQ_STAMP(15)
 #undef HQ_NF4_LOAD
-  if (p.peer_ll != nullptr) {
+  if (packets_out) {
     // the last CTA to finish records that this gather round is complete on the
     // sending side (the packets validate themselves on the receiving side)
     __syncthreads();
@@ -755,7 +750,7 @@ nf4_gemv_bulk_kernel(const GemvParams p, int rows_total) {
 #pragma unroll
       for (int t = 0; t < 4; t++) {
         if (p.A_ll != nullptr) xr[i][t] = xp[t];
-        else if (HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 123)) xr[i][t] = __ldg(xp + t);
+        else if (HQ_IN_BOUNDS(xp + t, 16, p.A, p.a_bytes, 123)) xr[i][t] = ld_dependent_u4(xp + t);
         else xr[i][t] = make_uint4(0, 0, 0, 0);
       }
     }
@@ -1052,7 +1047,7 @@ namespace hq {
 namespace {
 
 // N: rows of the matrix, or (FUSE with a gated activation) pairs of rows
-template <int C, int D, int ST, bool AL, int THREADS, bool FUSE>
+template <int C, int D, int ST, bool AL, int THREADS, bool FUSE, bool LL>
 int launch_gemv(GemvParams& prm, int N, cudaStream_t st) {
   constexpr int W = THREADS / 32;
   const int S = prm.S;
@@ -1079,7 +1074,7 @@ int launch_gemv(GemvParams& prm, int N, cudaStream_t st) {
   if (prm.A_ll != nullptr || (FUSE && prm.gamma != nullptr))
     smem += (size_t)prm.nchunks * 32 * sizeof(__half);
   if (smem > 227 * 1024) return HQ_ERR_TOO_LARGE;
-  constexpr auto kern = nf4_gemv_kernel<C, D, ST, AL, THREADS, FUSE>;
+  constexpr auto kern = nf4_gemv_kernel<C, D, ST, AL, THREADS, FUSE, LL>;
   cudaError_t e = ensure_dynamic_smem<kern>(smem);
   if (e != cudaSuccess) return cuda_status(e);
   return cuda_status(launch_pdl(kern, dim3(grid), dim3(THREADS), smem, st, prm));
@@ -1228,9 +1223,13 @@ static int nf4_gemv_impl(const void* A_half, const uint8_t* B, const float* absm
   // Chunks per lane C and warps per row S = cols / C.  512 threads with up to
   // 128 registers each hold C = 2 chunks of the input vector and D = 4 rows of
   // packed weights in flight per lane.
-#define HQ_NF4_GO(C_, D_, ST_, AL_)                                        \
-  ((fuse != nullptr || pair_packets) ? launch_gemv<C_, D_, ST_, AL_, 512, true>(prm, units, st) \
-                   : launch_gemv<C_, D_, ST_, AL_, 512, false>(prm, units, st))
+  const bool with_packets = ll.A_ll != nullptr || ll.peer_ll != nullptr;
+#define HQ_NF4_GO(C_, D_, ST_, AL_)                                                         \
+  (with_packets                                                                              \
+       ? (pair_packets ? launch_gemv<C_, D_, ST_, AL_, 512, true, true>(prm, units, st)      \
+                       : launch_gemv<C_, D_, ST_, AL_, 512, false, true>(prm, units, st))    \
+       : (fuse != nullptr ? launch_gemv<C_, D_, ST_, AL_, 512, true, false>(prm, units, st)  \
+                          : launch_gemv<C_, D_, ST_, AL_, 512, false, false>(prm, units, st)))
   if (aligned && cols == 4) { prm.S = 2; return HQ_NF4_GO(2, 4, 2, true); }
   int C = cols <= 1 ? 1 : (cols <= 32 ? 2 : 4);
   prm.S = (cols + C - 1) / C;

@@ -69,7 +69,8 @@ q3_gemv_kernel(const void* __restrict__ vec_, const int32_t* __restrict__ mat,
   const float* xf = reinterpret_cast<const float*>(vec_);
   const __half* xh = reinterpret_cast<const __half*>(vec_);
   auto load_x = [&](int k) -> float {
-    return F16IN ? __half2float(xh[(size_t)g0 * 32 + k]) : xf[(size_t)g0 * 32 + k];
+    return F16IN ? __half2float(ld_dependent_f16(xh + (size_t)g0 * 32 + k))
+                 : ld_dependent_f32(xf + (size_t)g0 * 32 + k);
   };
   float amax = 0.f;
   for (int i = tid; i < ng * 32; i += kThreads) amax = fmaxf(amax, fabsf(load_x(i)));
