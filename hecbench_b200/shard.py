@@ -15,9 +15,8 @@ the CPU tests of the partition / gather logic pass the oracle instead.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Tuple
+from typing import Callable
 
-import numpy as np
 import torch
 import torch.distributed as dist
 

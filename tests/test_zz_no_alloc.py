@@ -13,7 +13,6 @@ tolerance the other fp16-output tests use; it also checks that sizes beyond the
 fixed maximum are rejected before anything is launched.  The file sorts last so
 that a run stopping at the first failure has already run every other test.
 """
-import ctypes as C
 
 import numpy as np
 import pytest
