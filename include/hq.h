@@ -345,9 +345,9 @@ int hq_vllm_dynamic_scaled_int8_quant(int8_t* out, const void* input, int dtype,
  * with fp32 accumulation across 32- or 64-weight partial sums formed in fp16.
  * The reference drivers use square matrices (rows == n == size); here rows and
  * n are independent.  n must be a multiple of 8 (fp16), 16 (int8) or 32 (int4);
- * mat and vec 16-byte aligned; n <= 114688 (fp16, int8) or 81920 (int4), else
- * HQ_ERR_TOO_LARGE (the inputs are staged in shared memory; beyond half of those
- * lengths only one CTA fits an SM).  The grid and block shapes of the reference launchers
+ * mat and vec 16-byte aligned; n <= 115712, else HQ_ERR_TOO_LARGE (the inputs are
+ * staged in 226 KB of shared memory; beyond half of that length only one CTA fits
+ * an SM).  The grid and block shapes of the reference launchers
  * (block_dim_x, block_dim_y, num_per_thread) are tuning knobs of its kernels
  * and have no counterpart here. */
 int hq_gemv_f16(const void* mat_half, const void* vec_half, void* res_half, int rows, int n,
