@@ -140,3 +140,44 @@ def test_python_layer_rejects_cpu_tensors(hq):
     t = torch.zeros(256)
     with pytest.raises(TypeError):
         hq.vecquant3matmul(t, t.int(), t, t, t, 24, 256)
+
+
+def test_fused_and_packer_argument_errors_need_no_gpu(hq):
+    """The fused mat-vec entries and the packers reject bad arguments before any
+    CUDA call: fake (aligned, never dereferenced) pointers are enough."""
+    lib = hq.load_library()
+    p = 64
+    # fused RMSNorm -> mat-vec -> gated activation
+    assert lib.hq_gemv_fused_f16(p, None, 1e-5, None, p, 8, 64, 0, None) == -2
+    assert lib.hq_gemv_fused_int8_f16(p, None, 1e-5, p, p, 8, 64, 1.0, 0.0, 3, None) == -1
+    assert lib.hq_gemv_fused_int4_f16(p, None, 1e-5, p, p, 8, 48, 1.0, 0.0, 0, None) == -1
+    assert lib.hq_gemv_fused_int4_f16(p, p + 2, 1e-5, p, p, 8, 64, 1.0, 0.0, 0, None) == -3
+    assert lib.hq_gemv_fused_nf4_f16(p, None, 1e-5, p, None, p, p, 8, 64, 64, 0, 0, None) == -2
+    assert lib.hq_gemv_fused_nf4_f16(p, None, 1e-5, p, p, p, p, 8, 64, 64, 0, 5, None) == -1
+    assert lib.hq_gemv_fused_nf4_f16(p, None, 1e-5, p, p, p, p, 0, 64, 64, 0, 0, None) == -1
+    # zero point
+    assert lib.hq_zero_point(p, p, 5, 5, 8, 1, p, p, None) == -1
+    assert lib.hq_zero_point(None, p, -127, 127, 8, 1, p, p, None) == -2
+    assert lib.hq_zero_point(None, None, -127, 127, 0, 1, None, None, None) == 0
+    # MXFP4
+    assert lib.hq_mxfp4_qdq(p, p, 48, 0, None) == -1
+    assert lib.hq_mxfp4_qdq(p, p, 64, 2, None) == -6
+    assert lib.hq_mxfp4_qdq(None, p, 64, 0, None) == -2
+    assert lib.hq_mxfp4_qdq(p + 2, p, 32, 0, None) == -3
+    assert lib.hq_mxfp4_quantize(p, p, None, 64, 0, None) == -2
+    assert lib.hq_mxfp4_dequantize(p, None, p, 64, 1, None) == -2
+    assert lib.hq_mxfp4_qdq(None, None, 0, 1, None) == 0
+    # quantizers
+    assert lib.hq_nf4_quantize(p, 0, 128, 48, p, 0, p, p, None) == -1
+    assert lib.hq_nf4_quantize(p, 0, 100, 64, p, 0, p, p, None) == -1
+    assert lib.hq_nf4_quantize(p, 3, 128, 64, p, 0, p, p, None) == -6
+    assert lib.hq_nf4_quantize(p, 0, 128, 64, None, 0, p, p, None) == -2
+    assert lib.hq_q3_quantize_workspace_bytes(16) == 128
+    assert lib.hq_q3_quantize(p, 0, 48, 16, p, p, p, p, 128, None) == -1
+    assert lib.hq_q3_quantize(p, 0, 64, 12, p, p, p, p, 128, None) == -1
+    assert lib.hq_q3_quantize(p, 0, 64, 16, p, p, p, p, 64, None) == -5
+    assert lib.hq_q3_quantize(p, 7, 64, 16, p, p, p, p, 128, None) == -6
+    assert lib.hq_lutgemm_quantize(p, 0, 128, 16, 3, 48, p, p, None, None) == -1
+    assert lib.hq_lutgemm_quantize(p, 0, 128, 16, 9, 128, p, p, None, None) == -1
+    assert lib.hq_lutgemm_quantize(p, 0, 1024, 16, 3, 1024, p, p, None, None) == -6
+    assert lib.hq_lutgemm_quantize(p, 0, 128, 16, 3, 128, None, p, None, None) == -2
